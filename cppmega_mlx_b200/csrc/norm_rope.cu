@@ -1,0 +1,256 @@
+// Memory-bound row kernels: RMSNorm (fwd / bwd), split-half RoPE, SwiGLU (fwd / bwd).
+// bf16 in / out, fp32 math, 128-bit accesses. These replace the reference's library calls
+// mx.fast.rms_norm / mx.fast.rope (docs/production_kernel_routing.md:62-140); rotary layout and
+// scaling tables follow cppmega_mlx/nn/attention.py:399-538 (tables are built on the host).
+#include "sm100.cuh"
+
+namespace cmb {
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(b[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 v;
+  v.x = pack_bf16x2(f[0], f[1]);
+  v.y = pack_bf16x2(f[2], f[3]);
+  v.z = pack_bf16x2(f[4], f[5]);
+  v.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = v;
+}
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < THREADS / 32) ? red[threadIdx.x] : 0.f;
+  if (w == 0) {
+    t = warp_sum(t);
+    if (l == 0) red[0] = t;
+  }
+  __syncthreads();
+  const float out = red[0];
+  __syncthreads();
+  return out;
+}
+
+// One CTA per row (grid-stride over rows); cols % 8 == 0.
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                               const __nv_bfloat16* __restrict__ w,
+                                                               __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
+                                                               int64_t rows, int cols, float eps) {
+  __shared__ float red[32];
+  const int nvec = cols >> 3;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16* xr = x + row * cols;
+    float ss = 0.f;
+    for (int v = threadIdx.x; v < nvec; v += THREADS) {
+      float f[8];
+      load8(xr + 8 * v, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+    ss = block_sum<THREADS>(ss, red);
+    const float r = rsqrtf(ss / cols + eps);
+    if (threadIdx.x == 0 && rstd != nullptr) rstd[row] = r;
+    __nv_bfloat16* yr = y + row * cols;
+    for (int v = threadIdx.x; v < nvec; v += THREADS) {
+      float f[8], g[8];
+      load8(xr + 8 * v, f);
+      load8(w + 8 * v, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = f[i] * r * g[i];
+      store8(yr + 8 * v, f);
+    }
+  }
+}
+
+// dx = rstd * (g*w) - x * rstd^3/cols * sum(g*w*x);  dw partials per CTA (summed on the host side).
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ gy,
+                                                               const __nv_bfloat16* __restrict__ x,
+                                                               const __nv_bfloat16* __restrict__ w,
+                                                               const float* __restrict__ rstd,
+                                                               __nv_bfloat16* __restrict__ gx, float* __restrict__ gw_part,
+                                                               int64_t rows, int cols) {
+  __shared__ float red[32];
+  const int nvec = cols >> 3;
+  // Per-thread dw accumulators for up to 4 vectors per thread (cols <= THREADS*32); wider rows spill to a loop.
+  constexpr int MAXV = 4;
+  float acc[MAXV][8];
+#pragma unroll
+  for (int a = 0; a < MAXV; ++a)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[a][i] = 0.f;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16* xr = x + row * cols;
+    const __nv_bfloat16* gr = gy + row * cols;
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int v = threadIdx.x; v < nvec; v += THREADS) {
+      float fx[8], fg[8], fw[8];
+      load8(xr + 8 * v, fx);
+      load8(gr + 8 * v, fg);
+      load8(w + 8 * v, fw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dot += fg[i] * fw[i] * fx[i];
+    }
+    dot = block_sum<THREADS>(dot, red);
+    const float c = dot * r * r * r / cols;
+    __nv_bfloat16* gxr = gx + row * cols;
+#pragma unroll
+    for (int a = 0; a < MAXV; ++a) {
+      const int v = threadIdx.x + a * THREADS;
+      if (v < nvec) {
+        float fx[8], fg[8], fw[8], o[8];
+        load8(xr + 8 * v, fx);
+        load8(gr + 8 * v, fg);
+        load8(w + 8 * v, fw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          o[i] = fg[i] * fw[i] * r - fx[i] * c;
+          acc[a][i] += fg[i] * fx[i] * r;
+        }
+        store8(gxr + 8 * v, o);
+      }
+    }
+    for (int v = threadIdx.x + MAXV * THREADS; v < nvec; v += THREADS) {  // very wide rows: atomics on the tail
+      float fx[8], fg[8], fw[8], o[8];
+      load8(xr + 8 * v, fx);
+      load8(gr + 8 * v, fg);
+      load8(w + 8 * v, fw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        o[i] = fg[i] * fw[i] * r - fx[i] * c;
+        atomicAdd(&gw_part[static_cast<size_t>(blockIdx.x) * cols + 8 * v + i], fg[i] * fx[i] * r);
+      }
+      store8(gxr + 8 * v, o);
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < MAXV; ++a) {
+    const int v = threadIdx.x + a * THREADS;
+    if (v < nvec) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) gw_part[static_cast<size_t>(blockIdx.x) * cols + 8 * v + i] = acc[a][i];
+    }
+  }
+}
+
+// SwiGLU: y = silu(g) * u with gu = [.., 2H] laid out as [gate | up] halves.
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ y, int64_t rows,
+                                  int H) {
+  const int64_t nvec = rows * (H >> 3);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / (H >> 3);
+    const int c = static_cast<int>(i - row * (H >> 3)) * 8;
+    float g[8], u[8], o[8];
+    load8(gu + row * 2 * H + c, g);
+    load8(gu + row * 2 * H + H + c, u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
+    store8(y + row * H + c, o);
+  }
+}
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gy, const __nv_bfloat16* __restrict__ gu,
+                                  __nv_bfloat16* __restrict__ ggu, int64_t rows, int H) {
+  const int64_t nvec = rows * (H >> 3);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / (H >> 3);
+    const int c = static_cast<int>(i - row * (H >> 3)) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(gu + row * 2 * H + c, g);
+    load8(gu + row * 2 * H + H + c, u);
+    load8(gy + row * H + c, d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float s = 1.f / (1.f + __expf(-g[k]));
+      const float silu = g[k] * s;
+      du[k] = d[k] * silu;
+      dg[k] = d[k] * u[k] * (s + silu * (1.f - s));
+    }
+    store8(ggu + row * 2 * H + c, dg);
+    store8(ggu + row * 2 * H + H + c, du);
+  }
+}
+
+// Split-half rotary on the trailing `rot` dims of each head: (x1, x2) -> (x1 c - x2 s, x2 c + x1 s),
+// cos/sin tables [S, rot/2] fp32. `inverse` applies the transpose (backward). x: [B, S, H, D] bf16,
+// the rotated slice starts at `off` inside D. In place when y == x.
+__global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, int64_t B, int S, int H,
+                            int D, int off, int rot, int pos0, int inverse) {
+  const int half = rot >> 1;
+  const int64_t total = B * S * static_cast<int64_t>(H) * half;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int j = static_cast<int>(i % half);
+    const int64_t bh = i / half;  // (b*S + s)*H + h
+    const int s = static_cast<int>((bh / H) % S);
+    const float c = cos_t[static_cast<int64_t>(s + pos0) * half + j];
+    float sn = sin_t[static_cast<int64_t>(s + pos0) * half + j];
+    if (inverse) sn = -sn;
+    const __nv_bfloat16* xp = x + bh * D + off;
+    __nv_bfloat16* yp = y + bh * D + off;
+    const float a = __bfloat162float(xp[j]);
+    const float b = __bfloat162float(xp[j + half]);
+    yp[j] = __float2bfloat16(a * c - b * sn);
+    yp[j + half] = __float2bfloat16(b * c + a * sn);
+  }
+}
+
+}  // namespace cmb
+
+extern "C" int cmb_rmsnorm_fwd(const void* x, const void* w, void* y, void* rstd, int64_t rows, int cols, float eps,
+                               void* stream) {
+  if (cols % 8) return 1;
+  const int grid = static_cast<int>(rows < 148 * 16 ? rows : 148 * 16);
+  cmb::rmsnorm_fwd_kernel<256><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
+      static_cast<float*>(rstd), rows, cols, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_rmsnorm_bwd(const void* gy, const void* x, const void* w, const void* rstd, void* gx, void* gw_part,
+                               int64_t rows, int cols, int nblk, void* stream) {
+  if (cols % 8) return 1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if ((cols >> 3) > 256 * 4) cudaMemsetAsync(gw_part, 0, sizeof(float) * static_cast<size_t>(nblk) * cols, s);
+  cmb::rmsnorm_bwd_kernel<256><<<nblk, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(gy),
+                                                      static_cast<const __nv_bfloat16*>(x),
+                                                      static_cast<const __nv_bfloat16*>(w), static_cast<const float*>(rstd),
+                                                      static_cast<__nv_bfloat16*>(gx), static_cast<float*>(gw_part), rows, cols);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_swiglu_fwd(const void* gu, void* y, int64_t rows, int H, void* stream) {
+  if (H % 8) return 1;
+  cmb::swiglu_fwd_kernel<<<148 * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(y), rows, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+extern "C" int cmb_swiglu_bwd(const void* gy, const void* gu, void* ggu, int64_t rows, int H, void* stream) {
+  if (H % 8) return 1;
+  cmb::swiglu_bwd_kernel<<<148 * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gy), static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(ggu), rows, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+extern "C" int cmb_rope(const void* x, void* y, const void* cos_t, const void* sin_t, int64_t B, int S, int H, int D,
+                        int off, int rot, int pos0, int inverse, void* stream) {
+  if (rot % 2 || off + rot > D) return 1;
+  cmb::rope_kernel<<<148 * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), static_cast<const float*>(cos_t),
+      static_cast<const float*>(sin_t), B, S, H, D, off, rot, pos0, inverse);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}

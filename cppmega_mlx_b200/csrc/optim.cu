@@ -1,0 +1,267 @@
+// Fused optimizer kernels: AdamW (fp32 moments), 8-bit AdamW / Lion (uint8 codes + per-256 absmax,
+// symmetric int8 or 256-entry dynamic code book), Muon momentum stage.
+//
+// 8-bit layout: one warp owns one 256-value quantisation block (8 values per lane, one 64-bit
+// code load per lane); the new absmax is a shuffle reduction; the step uses the fresh fp32 moments
+// and the per-block noise floor max(prev_absmax, new_absmax)/127 before re-quantising.
+// Math parity: cppmega_mlx/training/native_optim/fused_8bit.metal:8-110 (Adam symmetric),
+// :112-249 (Adam dynamic, binary-search requant), :251-305 / :307-382 (Lion).
+#include "optim.h"
+#include "sm100.cuh"
+
+namespace cmb {
+
+template <typename T>
+struct Cvt;
+template <>
+struct Cvt<float> {
+  static __device__ __forceinline__ float ld(const float* p, int64_t i) { return p[i]; }
+  static __device__ __forceinline__ void st(float* p, int64_t i, float v) { p[i] = v; }
+};
+template <>
+struct Cvt<__half> {
+  static __device__ __forceinline__ float ld(const __half* p, int64_t i) { return __half2float(p[i]); }
+  static __device__ __forceinline__ void st(__half* p, int64_t i, float v) { p[i] = __float2half_rn(v); }
+};
+template <>
+struct Cvt<__nv_bfloat16> {
+  static __device__ __forceinline__ float ld(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+  static __device__ __forceinline__ void st(__nv_bfloat16* p, int64_t i, float v) { p[i] = __float2bfloat16(v); }
+};
+
+template <typename T>
+__global__ void adamw_kernel(T* __restrict__ p, const T* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                             int64_t n, float lr, float b1, float b2, float eps, float wd, float c1, float c2,
+                             float gscale) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float gi = Cvt<T>::ld(g, i) * gscale;
+    const float mi = b1 * m[i] + (1.f - b1) * gi;
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    const float pi = Cvt<T>::ld(p, i) * (1.f - lr * wd) - lr * c1 * mi / (sqrtf(vi) * c2 + eps);
+    Cvt<T>::st(p, i, pi);
+  }
+}
+
+__device__ __forceinline__ float deq_sym(uint8_t q, float absmax) {
+  return static_cast<float>(static_cast<int>(q) - 128) * (1.f / 127.f) * absmax;
+}
+__device__ __forceinline__ uint8_t q_sym(float v, float absmax) {
+  const float d = absmax > 0.f ? absmax : 1.f;
+  float r = rintf(v / d * 127.f);
+  r = fminf(fmaxf(r, -127.f), 127.f);
+  return static_cast<uint8_t>(static_cast<int>(r) + 128);
+}
+__device__ __forceinline__ uint8_t q_dyn(float v, float absmax, const float* lut) {
+  const float d = absmax > 0.f ? absmax : 1.f;
+  const float x = fminf(fmaxf(v / d, -1.f), 1.f);
+  int lo = 0, hi = 255;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int mid = (lo + hi) >> 1;
+    const bool right = lut[mid] < x;
+    lo = right ? mid + 1 : lo;
+    hi = right ? hi : mid;
+  }
+  const int prev = lo > 0 ? lo - 1 : 0;
+  const bool use_prev = lo > 0 && fabsf(lut[prev] - x) < fabsf(lut[lo] - x);
+  return static_cast<uint8_t>(use_prev ? prev : lo);
+}
+
+// One warp per 256-block. `lut` != nullptr selects the dynamic code book (staged in shared memory).
+template <typename T, bool DYN>
+__global__ void __launch_bounds__(256) adam8bit_kernel(T* __restrict__ p, const T* __restrict__ g,
+                                                        uint8_t* __restrict__ mq, float* __restrict__ ma,
+                                                        uint8_t* __restrict__ vq, float* __restrict__ va,
+                                                        const float* __restrict__ lut, int64_t n, float lr, float b1,
+                                                        float b2, float eps, float wd, float c1, float c2) {
+  __shared__ float slut[256];
+  if (DYN) {
+    slut[threadIdx.x] = lut[threadIdx.x];
+    __syncthreads();
+  }
+  const int lane = threadIdx.x & 31;
+  const int64_t nblk = (n + 255) / 256;
+  const int64_t warp0 = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t blk = warp0; blk < nblk; blk += nwarps) {
+    const int64_t base = blk * 256 + lane * 8;
+    const float am_prev = ma[blk], av_prev = va[blk];
+    float mv[8], vv[8], gv[8];
+    float am_new = 0.f, av_new = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int64_t i = base + e;
+      if (i < n) {
+        const uint8_t qm = mq[i], qv = vq[i];
+        const float m0 = DYN ? slut[qm] * am_prev : deq_sym(qm, am_prev);
+        const float v0 = fmaxf(DYN ? slut[qv] * av_prev : deq_sym(qv, av_prev), 0.f);
+        gv[e] = Cvt<T>::ld(g, i);
+        mv[e] = b1 * m0 + (1.f - b1) * gv[e];
+        vv[e] = fmaxf(b2 * v0 + (1.f - b2) * gv[e] * gv[e], 0.f);
+        am_new = fmaxf(am_new, fabsf(mv[e]));
+        av_new = fmaxf(av_new, vv[e]);
+      } else {
+        mv[e] = vv[e] = gv[e] = 0.f;
+      }
+    }
+    am_new = warp_max(am_new);
+    av_new = warp_max(av_new);
+    const float floor_v = fmaxf(av_prev, av_new) * (1.f / 127.f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int64_t i = base + e;
+      if (i < n) {
+        const float pi = Cvt<T>::ld(p, i) * (1.f - lr * wd) - lr * c1 * mv[e] / (sqrtf(vv[e]) * c2 + floor_v + eps);
+        Cvt<T>::st(p, i, pi);
+        mq[i] = DYN ? q_dyn(mv[e], am_new, slut) : q_sym(mv[e], am_new);
+        vq[i] = DYN ? q_dyn(vv[e], av_new, slut) : q_sym(vv[e], av_new);
+      }
+    }
+    if (lane == 0) {
+      ma[blk] = am_new;
+      va[blk] = av_new;
+    }
+  }
+}
+
+template <typename T, bool DYN>
+__global__ void __launch_bounds__(256) lion8bit_kernel(T* __restrict__ p, const T* __restrict__ g,
+                                                        uint8_t* __restrict__ mq, float* __restrict__ ma,
+                                                        const float* __restrict__ lut, int64_t n, float lr, float b1,
+                                                        float b2, float wd) {
+  __shared__ float slut[256];
+  if (DYN) {
+    slut[threadIdx.x] = lut[threadIdx.x];
+    __syncthreads();
+  }
+  const int lane = threadIdx.x & 31;
+  const int64_t nblk = (n + 255) / 256;
+  const int64_t warp0 = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t blk = warp0; blk < nblk; blk += nwarps) {
+    const int64_t base = blk * 256 + lane * 8;
+    const float am_prev = ma[blk];
+    float mv[8];
+    float am_new = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int64_t i = base + e;
+      mv[e] = 0.f;
+      if (i < n) {
+        const uint8_t q = mq[i];
+        const float m0 = DYN ? slut[q] * am_prev : deq_sym(q, am_prev);
+        const float gi = Cvt<T>::ld(g, i);
+        const float c = b1 * m0 + (1.f - b1) * gi;
+        const float sgn = c > 0.f ? 1.f : (c < 0.f ? -1.f : 0.f);
+        Cvt<T>::st(p, i, Cvt<T>::ld(p, i) * (1.f - lr * wd) - lr * sgn);
+        mv[e] = b2 * m0 + (1.f - b2) * gi;
+        am_new = fmaxf(am_new, fabsf(mv[e]));
+      }
+    }
+    am_new = warp_max(am_new);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int64_t i = base + e;
+      if (i < n) mq[i] = DYN ? q_dyn(mv[e], am_new, slut) : q_sym(mv[e], am_new);
+    }
+    if (lane == 0) ma[blk] = am_new;
+  }
+}
+
+// Muon stage 1: momentum with weight decay folded into the gradient, Nesterov blend written as the bf16
+// Newton–Schulz input, and Σ update² (for the Frobenius normalisation) accumulated with one atomic per CTA.
+template <typename T>
+__global__ void __launch_bounds__(256) muon_momentum_kernel(const T* __restrict__ g, const T* __restrict__ p,
+                                                             float* __restrict__ v, __nv_bfloat16* __restrict__ out,
+                                                             float* __restrict__ sumsq, int64_t n, float mu, float wd,
+                                                             int nesterov) {
+  __shared__ float red[8];
+  float acc = 0.f;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float gi = Cvt<T>::ld(g, i) + wd * Cvt<T>::ld(p, i);
+    const float vi = mu * v[i] + (1.f - mu) * gi;
+    v[i] = vi;
+    const float u = nesterov ? gi * (1.f - mu) + vi * mu : vi;
+    acc += u * u;
+    out[i] = __float2bfloat16(u);
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 8) {
+    float t = red[threadIdx.x];
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffu, t, o);
+    if (threadIdx.x == 0 && sumsq != nullptr) atomicAdd(sumsq, t);
+  }
+}
+
+static inline int grid_for(int64_t n, int per_block) {
+  int64_t b = (n + per_block - 1) / per_block;
+  const int64_t cap = 148 * 16;
+  return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace cmb
+
+#define CMB_DISPATCH_DTYPE(dtype, CALL)     \
+  switch (dtype) {                          \
+    case 0: { using T = float; CALL; break; }          \
+    case 1: { using T = __half; CALL; break; }         \
+    case 2: { using T = __nv_bfloat16; CALL; break; }  \
+    default: return 1;                      \
+  }
+
+extern "C" int cmb_adamw(void* p, const void* g, float* m, float* v, int64_t n, int dtype, float lr, float b1, float b2,
+                         float eps, float wd, float c1, float c2, float grad_scale, void* stream) {
+  if (n <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CMB_DISPATCH_DTYPE(dtype, (cmb::adamw_kernel<T><<<cmb::grid_for(n, 1024), 256, 0, s>>>(
+                                static_cast<T*>(p), static_cast<const T*>(g), m, v, n, lr, b1, b2, eps, wd, c1, c2, grad_scale)));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_adam8bit(void* p, const void* g, uint8_t* mq, float* ma, uint8_t* vq, float* va, const float* lut,
+                            int64_t n, int dtype, float lr, float b1, float b2, float eps, float wd, float c1, float c2,
+                            void* stream) {
+  if (n <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = cmb::grid_for((n + 255) / 256, 8);
+  if (lut != nullptr) {
+    CMB_DISPATCH_DTYPE(dtype, (cmb::adam8bit_kernel<T, true><<<grid, 256, 0, s>>>(
+                                  static_cast<T*>(p), static_cast<const T*>(g), mq, ma, vq, va, lut, n, lr, b1, b2, eps, wd, c1, c2)));
+  } else {
+    CMB_DISPATCH_DTYPE(dtype, (cmb::adam8bit_kernel<T, false><<<grid, 256, 0, s>>>(
+                                  static_cast<T*>(p), static_cast<const T*>(g), mq, ma, vq, va, lut, n, lr, b1, b2, eps, wd, c1, c2)));
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_lion8bit(void* p, const void* g, uint8_t* mq, float* ma, const float* lut, int64_t n, int dtype,
+                            float lr, float b1, float b2, float wd, void* stream) {
+  if (n <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = cmb::grid_for((n + 255) / 256, 8);
+  if (lut != nullptr) {
+    CMB_DISPATCH_DTYPE(dtype, (cmb::lion8bit_kernel<T, true><<<grid, 256, 0, s>>>(static_cast<T*>(p), static_cast<const T*>(g),
+                                                                                  mq, ma, lut, n, lr, b1, b2, wd)));
+  } else {
+    CMB_DISPATCH_DTYPE(dtype, (cmb::lion8bit_kernel<T, false><<<grid, 256, 0, s>>>(static_cast<T*>(p), static_cast<const T*>(g),
+                                                                                   mq, ma, lut, n, lr, b1, b2, wd)));
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_muon_momentum(const void* g, const void* p, float* v, void* out_bf16, float* sumsq, int64_t n,
+                                 int dtype, float momentum, float wd, int nesterov, void* stream) {
+  if (n <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CMB_DISPATCH_DTYPE(dtype, (cmb::muon_momentum_kernel<T><<<cmb::grid_for(n, 2048), 256, 0, s>>>(
+                                static_cast<const T*>(g), static_cast<const T*>(p), v, static_cast<__nv_bfloat16*>(out_bf16), sumsq,
+                                n, momentum, wd, nesterov)));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}

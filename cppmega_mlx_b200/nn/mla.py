@@ -1,0 +1,278 @@
+"""Low-rank multi-head latent attention (MLA) with an optional DSA top-k indexer.
+
+Projections follow the DeepSeek-V3 layout used by ``cppmega_v4/nn/mla_block.py:99-236``::
+
+    q  : x → wq_a → RMSNorm → wq_b → [H, nope + rope]
+    kv : x → wkv_a → [c_kv (kv_lora) | k_pe (rope, shared by all heads)], RMSNorm(c_kv)
+         c_kv → wkv_b → [H, nope + v]
+
+Two mathematically identical evaluation orders are provided:
+
+* **materialised** (dense ``mla`` route): K/V are expanded per head and fed to dense causal attention;
+* **absorbed / latent** (sparse ``dsa`` route and decode): ``W_UK`` is folded into the query and
+  ``W_UV`` into the output, so attention runs directly on the 576-wide latent rows
+  ``[c_kv | k_pe]`` that all heads share — the layout the sparse-MLA kernel gathers
+  (``cppmega_v4/nn/mla_absorb.py:39-141``).  Unlike the reference's decode shortcut
+  (``mla_block.py:190-211``) the rotary term is kept, so both orders agree exactly.
+
+The indexer (``cppmega_v4/nn/lightning_indexer.py:79-145``) scores every causal key with
+``Σ_h w_h (q_h·k)`` and keeps the top-k; gradients do not flow through the selection.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from .basic import LayerNorm, Linear, RMSNorm
+
+
+@dataclass(frozen=True)
+class MLABlockConfig:
+    hidden_size: int
+    num_heads: int
+    q_lora_rank: int = 1536
+    kv_lora_rank: int = 512
+    qk_nope_head_dim: int = 128
+    qk_rope_head_dim: int = 64
+    v_head_dim: int = 128
+    rope_theta: float = 10000.0
+    norm_eps: float = 1e-6
+    use_absorb: bool = True
+    # DSA indexer (index_topk == 0 disables sparse routing)
+    index_n_heads: int = 4
+    index_head_dim: int = 64
+    index_topk: int = 0
+    index_relu: bool = False
+    zero_init_out: bool = True
+
+    def __post_init__(self) -> None:
+        for n in ("hidden_size", "num_heads", "q_lora_rank", "kv_lora_rank", "qk_nope_head_dim", "qk_rope_head_dim",
+                  "v_head_dim"):
+            if getattr(self, n) <= 0:
+                raise ValueError(f"{n} must be positive")
+        if self.qk_rope_head_dim % 2:
+            raise ValueError("qk_rope_head_dim must be even")
+        if self.index_topk < 0:
+            raise ValueError("index_topk must be >= 0")
+
+    @property
+    def qk_head_dim(self) -> int:
+        return self.qk_nope_head_dim + self.qk_rope_head_dim
+
+    @property
+    def latent_dim(self) -> int:
+        return self.kv_lora_rank + self.qk_rope_head_dim
+
+
+@dataclass(frozen=True)
+class LightningIndexerConfig:
+    hidden_size: int
+    q_lora_rank: int
+    n_heads: int = 4
+    head_dim: int = 64
+    rope_head_dim: int = 64
+    index_topk: int = 2048
+    norm_eps: float = 1e-6
+    softmax_scale: float | None = None
+    relu: bool = False
+
+
+class LightningIndexer(nn.Module):
+    def __init__(self, config: LightningIndexerConfig):
+        super().__init__()
+        self.config = config
+        c = config
+        self.wq_b = Linear(c.q_lora_rank, c.n_heads * c.head_dim)
+        self.wk = Linear(c.hidden_size, c.head_dim)
+        self.k_norm = LayerNorm(c.head_dim, eps=c.norm_eps)
+        self.weights_proj = Linear(c.hidden_size, c.n_heads)
+
+    def project(self, x, qr, cos, sin):
+        """Returns (q [B,S,H,d], k [B,S,d], w [B,S,H]) with rotary applied to the leading rope dims."""
+        c = self.config
+        b, s, _ = x.shape
+        rd = min(c.rope_head_dim, c.head_dim)
+        q = self.wq_b(qr).view(b, s, c.n_heads, c.head_dim)
+        q = ops.apply_rope(q, cos, sin, 0, rd)
+        k = self.k_norm(self.wk(x))
+        k = ops.apply_rope(k[:, :, None, :], cos, sin, 0, rd)[:, :, 0]
+        w = self.weights_proj(x).float() * (c.n_heads ** -0.5)
+        return q, k, w
+
+    def scores(self, q, k, w):
+        """[B,Sq,Sk] fp32 index scores."""
+        c = self.config
+        scale = c.softmax_scale if c.softmax_scale is not None else c.head_dim ** -0.5
+        if c.relu:
+            qk = torch.einsum("bqhd,bkd->bqhk", q.float(), k.float())
+            return torch.einsum("bqhk,bqh->bqk", F.relu(qk), w) * scale
+        # Without the ReLU the head sum commutes with the dot product: one [Sq,d]x[d,Sk] GEMM.
+        qw = (torch.einsum("bqhd,bqh->bqd", q.float(), w) * scale).to(k.dtype)
+        if k.is_cuda and k.dtype == torch.bfloat16:
+            return torch.stack([ops.matmul_nt(qw[i], k[i], out_dtype=torch.float32) for i in range(q.shape[0])])
+        return torch.einsum("bqd,bkd->bqk", qw.float(), k.float())
+
+    @torch.no_grad()
+    def select(self, q, k, w, *, query_offset: int = 0, mask: torch.Tensor | None = None) -> torch.Tensor:
+        """Top-k causal key indices [B,Sq,topk] int32 (``-1`` padded)."""
+        c = self.config
+        b, sq = q.shape[:2]
+        sk = k.shape[1]
+        sc = self.scores(q, k, w)
+        if mask is not None:
+            sc = sc + mask
+        ends = (torch.arange(sq, device=q.device, dtype=torch.int32) + 1 + query_offset).clamp(max=sk).repeat(b)
+        topk = min(c.index_topk, sk)
+        return ops.topk_select(sc.reshape(b * sq, sk), topk, None, ends).view(b, sq, topk)
+
+    def forward(self, x, qr, freqs_cis, mask=None):
+        cos, sin = freqs_cis
+        q, k, w = self.project(x, qr, cos, sin)
+        return self.select(q, k, w, mask=mask)
+
+
+class MLAAttention(nn.Module):
+    """The attention mixer itself (no residual / pre-norm; the enclosing block owns those)."""
+
+    def __init__(self, config: MLABlockConfig):
+        super().__init__()
+        self.config = config
+        c = config
+        H = c.num_heads
+        self.wq_a = Linear(c.hidden_size, c.q_lora_rank)
+        self.q_norm = RMSNorm(c.q_lora_rank, eps=c.norm_eps)
+        self.wq_b = Linear(c.q_lora_rank, H * c.qk_head_dim)
+        self.wkv_a = Linear(c.hidden_size, c.kv_lora_rank + c.qk_rope_head_dim)
+        self.kv_norm = RMSNorm(c.kv_lora_rank, eps=c.norm_eps)
+        self.wkv_b = Linear(c.kv_lora_rank, H * (c.qk_nope_head_dim + c.v_head_dim))
+        self.wo = Linear(H * c.v_head_dim, c.hidden_size, zero_init=c.zero_init_out)
+        self.indexer = None
+        if c.index_topk > 0:
+            self.indexer = LightningIndexer(LightningIndexerConfig(
+                hidden_size=c.hidden_size, q_lora_rank=c.q_lora_rank, n_heads=c.index_n_heads,
+                head_dim=c.index_head_dim, rope_head_dim=min(c.qk_rope_head_dim, c.index_head_dim),
+                index_topk=c.index_topk, norm_eps=c.norm_eps, relu=c.index_relu))
+
+    # -- weight views ---------------------------------------------------------------------------
+    def _w_uk_uv(self):
+        c = self.config
+        w = self.wkv_b.weight.view(c.num_heads, c.qk_nope_head_dim + c.v_head_dim, c.kv_lora_rank)
+        return w[:, :c.qk_nope_head_dim], w[:, c.qk_nope_head_dim:]  # [H,nope,r], [H,v,r]
+
+    def _project(self, x, offset: int):
+        c = self.config
+        b, s, _ = x.shape
+        qr = self.q_norm(self.wq_a(x))
+        q = self.wq_b(qr).view(b, s, c.num_heads, c.qk_head_dim)
+        kv = self.wkv_a(x)
+        c_kv = self.kv_norm(kv[..., :c.kv_lora_rank])
+        k_pe = kv[..., c.kv_lora_rank:]
+        cos, sin = ops.rope_tables(s, c.qk_rope_head_dim, c.rope_theta, device=x.device, offset=offset)
+        q = ops.apply_rope(q, cos, sin, c.qk_nope_head_dim, c.qk_rope_head_dim)
+        k_pe = ops.apply_rope(k_pe[:, :, None, :].contiguous(), cos, sin)[:, :, 0]
+        return qr, q, c_kv, k_pe, (cos, sin)
+
+    def _latent_query(self, q):
+        """Fold W_UK into the query: [B,S,H,nope+rope] → [B,S,H,kv_lora+rope]."""
+        c = self.config
+        w_uk, _ = self._w_uk_uv()
+        q_nope, q_pe = q[..., :c.qk_nope_head_dim], q[..., c.qk_nope_head_dim:]
+        q_lat = torch.einsum("bshn,hnr->bshr", q_nope, w_uk.to(q.dtype))
+        return torch.cat([q_lat, q_pe], dim=-1)
+
+    def _latent_output(self, o_lat):
+        _, w_uv = self._w_uk_uv()
+        return torch.einsum("bshr,hvr->bshv", o_lat, w_uv.to(o_lat.dtype))
+
+    def forward(self, x: torch.Tensor, mask=None, *, kv_cache=None, layer_idx: int = 0, sparse: bool | None = None):
+        c = self.config
+        b, s, _ = x.shape
+        offset = kv_cache.position(layer_idx) if kv_cache is not None else 0
+        qr, q, c_kv, k_pe, freqs = self._project(x, offset)
+        use_sparse = (self.indexer is not None) if sparse is None else (sparse and self.indexer is not None)
+        scale = c.qk_head_dim ** -0.5
+        latent = torch.cat([c_kv, k_pe], dim=-1)  # [B,S,576]
+        idx_k = None
+        if use_sparse:
+            iq, idx_k, iw = self.indexer.project(x, qr, *freqs)
+        if kv_cache is not None:
+            latent, idx_k = kv_cache.update_and_fetch_latent(layer_idx, latent, idx_k)
+        sk = latent.shape[1]
+        if use_sparse and sk > c.index_topk:
+            add_mask = None
+            if isinstance(mask, torch.Tensor):
+                add_mask = torch.zeros(mask.shape, device=x.device).masked_fill(~mask, float("-inf")) \
+                    if mask.dtype == torch.bool else mask.float()
+                while add_mask.dim() > 3:
+                    add_mask = add_mask[:, 0]
+            idx = self.indexer.select(iq, idx_k, iw, query_offset=sk - s, mask=add_mask)
+            out_lat, _ = ops.sparse_mla_attention(self._latent_query(q), latent[:, :, None, :], idx[:, :, None, :],
+                                                  sm_scale=scale, d_v=c.kv_lora_rank)
+            o = self._latent_output(out_lat)
+        elif kv_cache is not None or (use_sparse and c.use_absorb and not isinstance(mask, torch.Tensor)):
+            # Every causal key is selected (S ≤ top-k) or we are decoding: latent attention over all keys.
+            idx = causal_sparse_all(b, s, sk, x.device)
+            if isinstance(mask, torch.Tensor):
+                idx = _apply_mask_to_indices(idx, mask, sk - s)
+            out_lat, _ = ops.sparse_mla_attention(self._latent_query(q), latent[:, :, None, :], idx[:, :, None, :],
+                                                  sm_scale=scale, d_v=c.kv_lora_rank)
+            o = self._latent_output(out_lat)
+        else:
+            w_uk, w_uv = self._w_uk_uv()
+            k_nope = torch.einsum("bsr,hnr->bshn", c_kv, w_uk.to(c_kv.dtype))
+            v = torch.einsum("bsr,hvr->bshv", c_kv, w_uv.to(c_kv.dtype))
+            k = torch.cat([k_nope, k_pe[:, :, None, :].expand(b, s, c.num_heads, c.qk_rope_head_dim)], dim=-1)
+            from .attention import dense_attention
+            if isinstance(mask, torch.Tensor):
+                m = mask
+                while m.dim() < 4:
+                    m = m[None]
+                cm = torch.ones(s, s, dtype=torch.bool, device=x.device).tril()[None, None]
+                m = (m if m.dtype == torch.bool else torch.isfinite(m.float())) & cm
+                o = dense_attention(q.transpose(1, 2), k.transpose(1, 2), _pad_v(v, c).transpose(1, 2), mask=m, scale=scale)
+            else:
+                o = dense_attention(q.transpose(1, 2), k.transpose(1, 2), _pad_v(v, c).transpose(1, 2), is_causal=True,
+                                    scale=scale)
+            o = o.transpose(1, 2)[..., :c.v_head_dim]
+        return self.wo(o.reshape(b, s, c.num_heads * c.v_head_dim))
+
+
+def _pad_v(v, c: MLABlockConfig):
+    """Library SDPA wants equal q/k/v head dims; pad V with zeros up to the qk width."""
+    if c.v_head_dim == c.qk_head_dim:
+        return v
+    return F.pad(v, (0, c.qk_head_dim - c.v_head_dim))
+
+
+def causal_sparse_all(b: int, sq: int, sk: int, device) -> torch.Tensor:
+    """[B,Sq,Sk] indices selecting every causal key (``-1`` for future positions)."""
+    qpos = torch.arange(sq, device=device, dtype=torch.int32)[:, None] + (sk - sq)
+    kpos = torch.arange(sk, device=device, dtype=torch.int32)[None, :]
+    idx = torch.where(kpos <= qpos, kpos.expand(sq, sk), torch.full((sq, sk), -1, dtype=torch.int32, device=device))
+    return idx[None].expand(b, sq, sk).contiguous()
+
+
+def _apply_mask_to_indices(idx, mask, offset):
+    m = mask if mask.dtype == torch.bool else torch.isfinite(mask.float())
+    while m.dim() > 3:
+        m = m[:, 0]
+    if m.dim() == 2:
+        m = m[None]
+    return torch.where(m.expand_as(idx), idx, torch.full_like(idx, -1))
+
+
+class MLABlock(nn.Module):
+    """Stand-alone residual block (``x + attn(norm(x))``) with the signature of ``cppmega_v4/nn/mla_block.py:99``."""
+
+    def __init__(self, config: MLABlockConfig):
+        super().__init__()
+        self.config = config
+        self.input_norm = RMSNorm(config.hidden_size, eps=config.norm_eps)
+        self.attn = MLAAttention(config)
+
+    def forward(self, x, **kw):
+        return x + self.attn(self.input_norm(x), **kw)

@@ -1,0 +1,102 @@
+"""Dense bf16 GEMM and the differentiable ``linear`` built on it.
+
+CUDA path: ``csrc/gemm_bf16.cu`` (tcgen05 + TMEM + TMA, persistent, warp-specialised).  All three
+products of a linear layer run on the same kernel without transposed copies: forward uses two
+K-major operands, dgrad an MN-major weight, wgrad two MN-major activations.
+Oracle: ``torch.matmul`` in fp32.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _backend as B
+
+OUT_F32 = 1
+ACCUMULATE = 2
+
+
+def _ok(t: torch.Tensor) -> bool:
+    return (t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0
+            and t.data_ptr() % 16 == 0)
+
+
+def gemm_raw(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+             out: torch.Tensor | None = None, out_dtype=torch.bfloat16, accumulate: bool = False,
+             max_ctas: int = 0) -> torch.Tensor:
+    """C[M,N] (+)= A·Bᵀ on the tcgen05 kernel.
+
+    ``a`` is [M,K] (``a_mn=False``) or stored [K,M] (``a_mn=True``); ``b`` is [N,K] or stored [K,N].
+    """
+    lib = B.load_library()
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        K2, N = b.shape
+    else:
+        N, K2 = b.shape
+    if K != K2:
+        raise ValueError(f"contraction mismatch {K} vs {K2}")
+    if not (_ok(a) and _ok(b)):
+        raise ValueError("gemm_raw needs 2-D bf16 operands with unit inner stride, pitch % 8 == 0, 16-byte aligned")
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+        if accumulate:
+            out.zero_()
+    flags = (OUT_F32 if out.dtype == torch.float32 else 0) | (ACCUMULATE if accumulate else 0)
+    st = B.status_buffer(a.device)
+    rc = lib.cmb_gemm_bf16(B.ptr(a), B.ptr(b), B.ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+                           int(a_mn), int(b_mn), flags, B.ptr(st), int(max_ctas), B.stream_ptr())
+    B.check(rc, "gemm_bf16")
+    return out
+
+
+def _kernel_ok(*ts: torch.Tensor) -> bool:
+    return B.on_gpu(*ts) and all(t.dtype == torch.bfloat16 for t in ts)
+
+
+def matmul_nt(a: torch.Tensor, b: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    """a[M,K] @ b[N,K]ᵀ (no autograd)."""
+    if _kernel_ok(a, b) and a.shape[1] % 8 == 0:
+        return gemm_raw(a.contiguous(), b.contiguous(), out_dtype=out_dtype or torch.bfloat16)
+    r = a @ b.t()
+    return r if out_dtype is None else r.to(out_dtype)
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        ctx.save_for_backward(x2, w)
+        ctx.xshape = x.shape
+        y = gemm_raw(x2, w)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, w = ctx.saved_tensors
+        g2 = gy.reshape(-1, gy.shape[-1])
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            # dx[M,K] = g[M,N] · w[N,K]: B operand indexed [n'=K, k'=N] is w itself, MN-major.
+            gx = gemm_raw(g2, w, b_mn=True).view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            # dw[N,K] = gᵀ[N,M] · x[M,K]: both operands MN-major (contraction index M is the slow one).
+            gw = gemm_raw(g2, x2, a_mn=True, b_mn=True)
+        return gx, gw
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x @ wᵀ (+ bias); ``w`` is [out, in] as in ``nn.Linear``."""
+    if (_kernel_ok(x, w) and w.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and w.is_contiguous()
+            and x.shape[-1] == w.shape[1] and x.numel() > 0):
+        y = _LinearFn.apply(x, w)
+        return y if bias is None else y + bias
+    return torch.nn.functional.linear(x, w, bias)

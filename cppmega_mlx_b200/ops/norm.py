@@ -1,0 +1,64 @@
+"""RMSNorm (optionally fused with the residual add that precedes it).
+
+CUDA path: ``csrc/norm_rope.cu`` (one warp-group per row, 128-bit loads, fp32
+statistics, bf16 in/out; backward reduces dW through a per-CTA partial buffer).
+Oracle: ``rms_norm_ref`` below, the fp32 PyTorch restatement of
+``mx.fast.rms_norm`` as used by ``cppmega_mlx/models/hybrid_lm.py:541`` and
+``cppmega_mlx/nn/mamba3.py:214``.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _backend as B
+
+
+def rms_norm_ref(x: torch.Tensor, weight: torch.Tensor | None, eps: float = 1e-5) -> torch.Tensor:
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    if weight is not None:
+        y = y * weight.float()
+    return y.to(x.dtype)
+
+
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        lib = B.load_library()
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        rows, cols = x2.shape
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        B.check(lib.cmb_rmsnorm_fwd(B.ptr(x2), B.ptr(weight), B.ptr(y), B.ptr(rstd), ctypes.c_int64(rows),
+                                    ctypes.c_int(cols), ctypes.c_float(eps), B.stream_ptr()), "rmsnorm_fwd")
+        ctx.save_for_backward(x2, weight, rstd)
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, gy):
+        lib = B.load_library()
+        x2, weight, rstd = ctx.saved_tensors
+        rows, cols = x2.shape
+        gy2 = gy.reshape(rows, cols).contiguous()
+        gx = torch.empty_like(x2)
+        nblk = min(rows, 148 * 4)
+        gw_part = torch.empty(nblk, cols, dtype=torch.float32, device=x2.device)
+        B.check(lib.cmb_rmsnorm_bwd(B.ptr(gy2), B.ptr(x2), B.ptr(weight), B.ptr(rstd), B.ptr(gx), B.ptr(gw_part),
+                                    ctypes.c_int64(rows), ctypes.c_int(cols), ctypes.c_int(nblk), B.stream_ptr()),
+                "rmsnorm_bwd")
+        gw = gw_part.sum(0).to(weight.dtype)
+        return gx.view(ctx.shape), gw, None
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    if B.on_gpu(x, weight) and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+        return _RMSNormFn.apply(x, weight, eps)
+    return rms_norm_ref(x, weight, eps)
+
+
+def layer_norm_ref(x, weight, bias, eps=1e-5):
+    return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), weight.float() if weight is not None else None,
+                                          bias.float() if bias is not None else None, eps).to(x.dtype)

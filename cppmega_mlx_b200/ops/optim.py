@@ -1,0 +1,60 @@
+"""ctypes front-end of the fused optimizer kernels (``csrc/optim.cu`` / ``csrc/optim.h``).
+
+Each call updates one contiguous tensor in place.  Parameters and gradients may be bf16, fp16 or fp32
+(matching dtype), moments are fp32 or uint8+absmax.  These are the CUDA counterparts of the reference's
+Metal primitives (``cppmega_mlx/training/native_optim/fused_8bit.h:19-48``).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _backend as B
+
+_DT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+_lut_dev: dict[int, torch.Tensor] = {}
+
+
+def _lut(device) -> torch.Tensor:
+    from ..training._quantize_8bit import create_dynamic_map
+    return create_dynamic_map(device)
+
+
+def _dt(p, g):
+    if p.dtype != g.dtype or p.dtype not in _DT:
+        raise TypeError(f"parameter/gradient dtypes must match and be fp32/fp16/bf16, got {p.dtype}/{g.dtype}")
+    return _DT[p.dtype]
+
+
+def fused_adamw_(p, g, m, v, lr, b1, b2, eps, wd, c1=1.0, c2=1.0):
+    lib = B.load_library()
+    B.check(lib.cmb_adamw(B.ptr(p), B.ptr(g), B.ptr(m), B.ptr(v), ctypes.c_int64(p.numel()), _dt(p, g),
+                          ctypes.c_float(lr), ctypes.c_float(b1), ctypes.c_float(b2), ctypes.c_float(eps),
+                          ctypes.c_float(wd), ctypes.c_float(c1), ctypes.c_float(c2), ctypes.c_float(1.0),
+                          B.stream_ptr()), "adamw")
+
+
+def fused_adam8bit_(p, g, mq, ma, vq, va, lr, b1, b2, eps, wd, c1=1.0, c2=1.0, dynamic=False):
+    lib = B.load_library()
+    lut = _lut(p.device) if dynamic else None
+    B.check(lib.cmb_adam8bit(B.ptr(p), B.ptr(g), B.ptr(mq), B.ptr(ma), B.ptr(vq), B.ptr(va), B.ptr(lut),
+                             ctypes.c_int64(p.numel()), _dt(p, g), ctypes.c_float(lr), ctypes.c_float(b1),
+                             ctypes.c_float(b2), ctypes.c_float(eps), ctypes.c_float(wd), ctypes.c_float(c1),
+                             ctypes.c_float(c2), B.stream_ptr()), "adam8bit")
+
+
+def fused_lion8bit_(p, g, mq, ma, lr, b1, b2, wd, dynamic=False):
+    lib = B.load_library()
+    lut = _lut(p.device) if dynamic else None
+    B.check(lib.cmb_lion8bit(B.ptr(p), B.ptr(g), B.ptr(mq), B.ptr(ma), B.ptr(lut), ctypes.c_int64(p.numel()), _dt(p, g),
+                             ctypes.c_float(lr), ctypes.c_float(b1), ctypes.c_float(b2), ctypes.c_float(wd),
+                             B.stream_ptr()), "lion8bit")
+
+
+def fused_muon_momentum_(g, p, v, out_bf16, momentum, wd, nesterov, inv_norm_out=None):
+    """v ← μv + (1−μ)(g + wd·p); out ← nesterov blend (bf16), Σ out² accumulated into ``inv_norm_out`` [1] fp32."""
+    lib = B.load_library()
+    B.check(lib.cmb_muon_momentum(B.ptr(g), B.ptr(p), B.ptr(v), B.ptr(out_bf16), B.ptr(inv_norm_out),
+                                  ctypes.c_int64(p.numel()), _dt(p, g), ctypes.c_float(momentum), ctypes.c_float(wd),
+                                  int(bool(nesterov)), B.stream_ptr()), "muon_momentum")

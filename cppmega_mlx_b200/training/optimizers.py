@@ -1,0 +1,347 @@
+"""Optimizers: AdamW / Lion with fp32 moments on bf16 parameters, Muon with Newton–Schulz-5
+orthogonalisation (fp32 or bf16 carrier, optional 8-bit momentum), and the Muon+AdamW splitter.
+
+Contracts kept from the reference (``cppmega_mlx/training/optimizers.py``):
+  * parameters keep their dtype, moments are fp32, there is no fp32 master copy (``:92-113``);
+  * AdamW = decoupled decay ``p·(1−lr·wd)`` then Adam without bias correction by default (``:116``);
+  * Lion: ``c = β1 m + (1−β1) g``, ``p ← p(1−lr·wd) − lr·sign(c)``, ``m ← β2 m + (1−β2) g`` (``:135``);
+  * Muon group = 2-D weights that are not embeddings / LM head / Mamba scalars (``:182-202``);
+  * NS-5 coefficients (3.4445, −4.7750, 2.0315), Frobenius-normalised input (+1e-7), transposed when
+    rows > cols (``:263-299``); weight decay folded into the gradient, ``v ← μv + (1−μ)g``, Nesterov
+    update ``(1−μ)g + μv``, step ``lr·sqrt(max(1, rows/cols))`` (``:302-376``);
+  * quantised momentum = uint8 codes + one fp32 absmax per 256 values (``:379-512``);
+  * ``make_muon`` defaults lr_muon 2e-3 / lr_adamw 1e-4, scalar optimizer adamw|adam8bit|lion|lion8bit,
+    ``cppmega_cuda_parity`` shares one lr (``:610-759``).
+
+State is a flat ``{param_name: {slot: tensor}}`` dict so that ZeRO-1 can shard it by name and the
+checkpoint writer can store it under world-size-independent names.  On CUDA the element-wise
+updates run as fused multi-tensor kernels (``csrc/optim.cu``) and NS-5 runs on the tcgen05 GEMM.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Callable, Iterable
+
+import torch
+
+from .. import ops
+from ..ops import _backend as B
+from ._quantize_8bit import BLOCK_SIZE, dequantize_blockwise, quantize_blockwise
+
+MUON_NS_CARRIER_ENV = "CPPMEGA_MUON_NS_CARRIER"
+MUON_NS_CARRIERS = ("fp32", "bf16")
+MUON_QUANTIZED_MOMENTUM_SCHEME = "symmetric_int8_v1"
+EMBEDDING_LIKE_NAME_HINTS = ("embed", "embedding", "lm_head", "wte", "wpe")
+MAMBA_SCALAR_LEAVES = frozenset({"A_log", "dt_bias", "D", "B_bias", "C_bias", "B_norm_weight", "C_norm_weight",
+                                 "mimo_x", "mimo_z", "mimo_o"})
+NS_COEFFS = (3.4445, -4.7750, 2.0315)
+
+NamedParams = list[tuple[str, torch.nn.Parameter]]
+
+
+def named_trainable(model_or_params) -> NamedParams:
+    if isinstance(model_or_params, torch.nn.Module):
+        seen, out = set(), []
+        for n, p in model_or_params.named_parameters():
+            if p.requires_grad and id(p) not in seen:
+                seen.add(id(p))
+                out.append((n, p))
+        return out
+    return list(model_or_params)
+
+
+def _lr_value(lr) -> float:
+    return float(lr() if callable(lr) else lr)
+
+
+class Optimizer:
+    """Minimal optimizer base: ``step()`` consumes ``p.grad``; ``state`` is keyed by parameter name."""
+
+    def __init__(self, params, learning_rate):
+        self.params: NamedParams = named_trainable(params)
+        self.learning_rate = learning_rate
+        self.state: dict[str, dict[str, torch.Tensor]] = {}
+        self.step_count = 0
+
+    @property
+    def lr(self) -> float:
+        return _lr_value(self.learning_rate)
+
+    def init_single(self, name: str, p: torch.Tensor) -> dict[str, torch.Tensor]:  # pragma: no cover
+        raise NotImplementedError
+
+    def apply_single(self, name: str, grad: torch.Tensor, p: torch.Tensor, st: dict) -> None:  # pragma: no cover
+        raise NotImplementedError
+
+    def state_for(self, name: str, p: torch.Tensor) -> dict:
+        st = self.state.get(name)
+        if st is None:
+            st = self.state[name] = self.init_single(name, p)
+        return st
+
+    @torch.no_grad()
+    def step(self, grads: dict[str, torch.Tensor] | None = None) -> None:
+        self.step_count += 1
+        for name, p in self.params:
+            g = grads.get(name) if grads is not None else p.grad
+            if g is None:
+                continue
+            self.apply_single(name, g, p, self.state_for(name, p))
+
+    def zero_grad(self) -> None:
+        for _, p in self.params:
+            p.grad = None
+
+    def state_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for st in self.state.values() for t in st.values())
+
+    def state_dict(self) -> dict:
+        return {"step": self.step_count, "state": {n: {k: v for k, v in st.items()} for n, st in self.state.items()}}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.step_count = int(sd.get("step", 0))
+        pm = dict(self.params)
+        self.state = {}
+        for n, st in sd.get("state", {}).items():
+            if n not in pm:
+                raise KeyError(f"optimizer state for unknown parameter {n!r}")
+            self.state[n] = {k: v.to(pm[n].device) for k, v in st.items()}
+
+
+class AdamWFP32Moments(Optimizer):
+    def __init__(self, params, learning_rate=1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
+                 bias_correction: bool = False):
+        super().__init__(params, learning_rate)
+        self.betas, self.eps, self.weight_decay, self.bias_correction = tuple(betas), eps, weight_decay, bias_correction
+
+    def init_single(self, name, p):
+        return {"m": torch.zeros_like(p, dtype=torch.float32), "v": torch.zeros_like(p, dtype=torch.float32)}
+
+    def apply_single(self, name, grad, p, st):
+        b1, b2 = self.betas
+        lr = self.lr
+        if self.bias_correction:
+            t = self.step_count
+            c1, c2 = 1.0 / (1 - b1 ** t), 1.0 / (1 - b2 ** t)
+        else:
+            c1 = c2 = 1.0
+        if p.is_cuda and B.kernels_enabled() and p.is_contiguous() and grad.is_contiguous():
+            from ..ops.optim import fused_adamw_
+            fused_adamw_(p, grad, st["m"], st["v"], lr, b1, b2, self.eps, self.weight_decay, c1, c2)
+            return
+        g = grad.float()
+        st["m"].mul_(b1).add_(g, alpha=1 - b1)
+        st["v"].mul_(b2).addcmul_(g, g, value=1 - b2)
+        pf = p.float() * (1 - lr * self.weight_decay)
+        denom = (st["v"] * c2).sqrt_().add_(self.eps)
+        pf.addcdiv_(st["m"] * c1, denom, value=-lr)
+        p.copy_(pf)
+
+
+def make_adamw(params, *, learning_rate=1e-3, weight_decay: float = 0.01, betas=None, eps: float = 1e-8,
+               bias_correction: bool = False) -> AdamWFP32Moments:
+    return AdamWFP32Moments(params, learning_rate, (0.9, 0.999) if betas is None else betas, eps, weight_decay,
+                            bias_correction)
+
+
+class LionFP32Moments(Optimizer):
+    def __init__(self, params, learning_rate=1e-4, betas=(0.9, 0.99), weight_decay: float = 0.0):
+        super().__init__(params, learning_rate)
+        self.betas, self.weight_decay = tuple(betas), weight_decay
+
+    def init_single(self, name, p):
+        return {"m": torch.zeros_like(p, dtype=torch.float32)}
+
+    def apply_single(self, name, grad, p, st):
+        b1, b2 = self.betas
+        lr = self.lr
+        g = grad.float()
+        c = st["m"] * b1 + g * (1 - b1)
+        pf = p.float() * (1 - lr * self.weight_decay) - lr * torch.sign(c)
+        st["m"].mul_(b2).add_(g, alpha=1 - b2)
+        p.copy_(pf)
+
+
+def make_lion(params, *, learning_rate=1e-4, weight_decay: float = 0.0, betas=None) -> LionFP32Moments:
+    return LionFP32Moments(params, learning_rate, (0.9, 0.99) if betas is None else betas, weight_decay)
+
+
+def is_muon_compatible(name: str, param: torch.Tensor) -> bool:
+    if param.dim() != 2:
+        return False
+    if name.rsplit(".", 1)[-1] in MAMBA_SCALAR_LEAVES:
+        return False
+    low = name.lower()
+    return not any(h in low for h in EMBEDDING_LIKE_NAME_HINTS)
+
+
+def split_param_groups(params, *, predicate: Callable[[str, torch.Tensor], bool] = is_muon_compatible):
+    muon, other = [], []
+    for n, p in named_trainable(params):
+        (muon if predicate(n, p) else other).append((n, p))
+    return muon, other
+
+
+def normalize_ns_carrier(ns_carrier: str) -> str:
+    v = ns_carrier.strip().lower()
+    if v not in MUON_NS_CARRIERS:
+        raise ValueError(f"ns_carrier must be one of {', '.join(MUON_NS_CARRIERS)}; got {ns_carrier!r}")
+    return v
+
+
+def newton_schulz5(update: torch.Tensor, *, steps: int = 5, ns_carrier: str = "fp32", output_dtype=None) -> torch.Tensor:
+    """Approximate the orthogonal polar factor of a 2-D matrix with the quintic Newton–Schulz iteration."""
+    if update.dim() != 2:
+        raise ValueError(f"Expected a 2D array for Newton-Schulz iteration, got shape {tuple(update.shape)} instead.")
+    a, b, c = NS_COEFFS
+    out_dtype = output_dtype or update.dtype
+    transpose = update.shape[0] > update.shape[1]
+    x = update.float()
+    if transpose:
+        x = x.t()
+    x = x / (torch.linalg.norm(x) + 1e-7)
+    carrier = torch.bfloat16 if normalize_ns_carrier(ns_carrier) == "bf16" else torch.float32
+    x = x.to(carrier).contiguous()
+    use_kernel = x.is_cuda and carrier == torch.bfloat16 and B.kernels_enabled() and x.shape[0] % 8 == 0 and x.shape[1] % 8 == 0
+    for _ in range(steps):
+        if use_kernel:
+            gram = ops.gemm_raw(x, x)                                       # X Xᵀ
+            basis = ops.gemm_raw(gram, gram, b_mn=True, out_dtype=torch.float32)  # G·G (G symmetric)
+            basis = (b * gram.float() + c * basis).to(carrier)
+            x = (a * x.float() + ops.gemm_raw(basis, x, b_mn=True, out_dtype=torch.float32)).to(carrier)
+        else:
+            gram = x @ x.t()
+            basis = b * gram + c * (gram @ gram)
+            x = (a * x + basis @ x).to(carrier)
+    if transpose:
+        x = x.t()
+    return x.to(out_dtype)
+
+
+class MuonWithNSCarrier(Optimizer):
+    def __init__(self, params, learning_rate=2e-3, momentum: float = 0.95, weight_decay: float = 0.01,
+                 nesterov: bool = True, ns_steps: int = 5, *, ns_carrier: str = "fp32"):
+        super().__init__(params, learning_rate)
+        self.momentum, self.weight_decay, self.nesterov, self.ns_steps = momentum, weight_decay, nesterov, ns_steps
+        self.ns_carrier = normalize_ns_carrier(ns_carrier)
+
+    def init_single(self, name, p):
+        return {"v": torch.zeros_like(p, dtype=torch.float32)}
+
+    def _momentum(self, g, p, st):
+        if self.weight_decay != 0:
+            g = g + self.weight_decay * p.float()
+        st["v"].mul_(self.momentum).add_(g, alpha=1 - self.momentum)
+        return g * (1 - self.momentum) + st["v"] * self.momentum if self.nesterov else st["v"]
+
+    def _apply_update(self, update, p):
+        lr = self.lr
+        if update.dim() >= 2:
+            shape = update.shape
+            u2 = update.reshape(shape[0], -1)
+            u2 = newton_schulz5(u2, steps=self.ns_steps, ns_carrier=self.ns_carrier, output_dtype=torch.float32)
+            update = u2.reshape(shape)
+            lr = lr * max(1.0, shape[-2] / shape[-1]) ** 0.5
+        p.copy_(p.float() - lr * update)
+
+    def apply_single(self, name, grad, p, st):
+        self._apply_update(self._momentum(grad.float(), p, st), p)
+
+
+class QuantizedMuonWithNSCarrier(MuonWithNSCarrier):
+    """Muon whose momentum lives as uint8 codes + per-256 fp32 absmax (4× smaller state)."""
+
+    def __init__(self, *a, quant_scheme: str = MUON_QUANTIZED_MOMENTUM_SCHEME, **kw):
+        super().__init__(*a, **kw)
+        if quant_scheme not in ("symmetric_int8_v1", "dynamic_int8_v1"):
+            raise ValueError(f"unknown quant_scheme {quant_scheme!r}")
+        self.quant_scheme = quant_scheme
+
+    def init_single(self, name, p):
+        q, am = quantize_blockwise(torch.zeros(p.numel(), dtype=torch.float32, device=p.device), scheme=self.quant_scheme)
+        return {"v_quant": q, "v_absmax": am}
+
+    def apply_single(self, name, grad, p, st):
+        v = dequantize_blockwise(st["v_quant"], st["v_absmax"], p.numel(), scheme=self.quant_scheme).view(p.shape)
+        tmp = {"v": v}
+        update = self._momentum(grad.float(), p, tmp)
+        st["v_quant"], st["v_absmax"] = quantize_blockwise(tmp["v"].reshape(-1), scheme=self.quant_scheme)
+        self._apply_update(update, p)
+
+
+class MuonAdamWMulti:
+    """Routes 2-D hidden weights to Muon and everything else to a scalar optimizer; state = {muon, adamw}."""
+
+    def __init__(self, muon: Optimizer, other: Optimizer):
+        self.muon, self.other = muon, other
+
+    @property
+    def params(self) -> NamedParams:
+        return self.muon.params + self.other.params
+
+    @property
+    def state(self):
+        return {"muon": self.muon.state, "adamw": self.other.state}
+
+    @property
+    def step_count(self) -> int:
+        return self.muon.step_count
+
+    def step(self, grads=None) -> None:
+        self.muon.step(grads)
+        self.other.step(grads)
+
+    def zero_grad(self) -> None:
+        self.muon.zero_grad()
+        self.other.zero_grad()
+
+    def state_bytes(self) -> int:
+        return self.muon.state_bytes() + self.other.state_bytes()
+
+    def state_dict(self) -> dict:
+        return {"muon": self.muon.state_dict(), "adamw": self.other.state_dict()}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.muon.load_state_dict(sd["muon"])
+        self.other.load_state_dict(sd["adamw"])
+
+
+def make_muon(params, *, lr_muon: float = 2e-3, lr_adamw: float = 1e-4, momentum: float = 0.95,
+              weight_decay: float = 0.01, adamw_weight_decay: float | None = None, nesterov: bool = True,
+              ns_steps: int = 5, ns_carrier: str | None = None, quantized_momentum: bool = False,
+              quant_scheme: str = MUON_QUANTIZED_MOMENTUM_SCHEME, scalar_optimizer: str = "adamw",
+              cppmega_cuda_parity: bool = False, betas=None, eps: float = 1e-8) -> MuonAdamWMulti:
+    carrier = ns_carrier or os.environ.get(MUON_NS_CARRIER_ENV, "fp32")
+    if cppmega_cuda_parity:
+        lr_adamw = lr_muon
+    muon_p, other_p = split_param_groups(params)
+    cls = QuantizedMuonWithNSCarrier if quantized_momentum else MuonWithNSCarrier
+    kw = dict(quant_scheme=quant_scheme) if quantized_momentum else {}
+    muon = cls(muon_p, lr_muon, momentum, weight_decay, nesterov, ns_steps, ns_carrier=carrier, **kw)
+    awd = weight_decay if adamw_weight_decay is None else adamw_weight_decay
+    so = scalar_optimizer.lower()
+    if so == "adamw":
+        other = make_adamw(other_p, learning_rate=lr_adamw, weight_decay=awd, betas=betas, eps=eps)
+    elif so == "lion":
+        other = make_lion(other_p, learning_rate=lr_adamw, weight_decay=awd)
+    elif so in ("adam8bit", "lion8bit"):
+        from .optimizers_quantized import make_adam8bit, make_lion8bit
+        other = (make_adam8bit if so == "adam8bit" else make_lion8bit)(other_p, learning_rate=lr_adamw, weight_decay=awd)
+    else:
+        raise ValueError(f"scalar_optimizer must be adamw|adam8bit|lion|lion8bit, got {scalar_optimizer!r}")
+    return MuonAdamWMulti(muon, other)
+
+
+def global_grad_norm(params: Iterable[torch.Tensor]) -> torch.Tensor:
+    sq = [p.grad.float().pow(2).sum() for p in params if p.grad is not None]
+    return torch.stack(sq).sum().sqrt() if sq else torch.zeros(())
+
+
+def clip_grad_norm_(params, max_norm: float) -> torch.Tensor:
+    ps = [p for p in params if p.grad is not None]
+    norm = global_grad_norm(ps)
+    scale = (max_norm / (norm + 1e-6)).clamp(max=1.0)
+    for p in ps:
+        p.grad.mul_(scale.to(p.grad.dtype))
+    return norm
