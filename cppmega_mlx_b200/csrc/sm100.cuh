@@ -27,7 +27,7 @@ enum : int {
 };
 
 #ifndef CMB_WAIT_LIMIT
-#define CMB_WAIT_LIMIT (1u << 22)
+#define CMB_WAIT_LIMIT (1u << 20)
 #endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

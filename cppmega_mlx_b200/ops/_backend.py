@@ -24,7 +24,7 @@ _CSRC = Path(__file__).resolve().parent.parent / "csrc"
 LIB_NAME = "libcppmega_b200.so"
 ABI_VERSION = 1
 
-_state = threading.local()
+_enabled = True  # process-wide on purpose: autograd runs backward (and checkpoint recomputation) on its own threads
 _lib = None
 _lib_lock = threading.Lock()
 
@@ -34,21 +34,23 @@ def lib_path() -> Path:
 
 
 def kernels_enabled() -> bool:
-    return getattr(_state, "enabled", True)
+    return _enabled
 
 
 @contextlib.contextmanager
 def use_kernels(flag: bool):
-    prev = kernels_enabled()
-    _state.enabled = bool(flag)
+    global _enabled
+    prev = _enabled
+    _enabled = bool(flag)
     try:
         yield
     finally:
-        _state.enabled = prev
+        _enabled = prev
 
 
 def set_kernels_enabled(flag: bool) -> None:
-    _state.enabled = bool(flag)
+    global _enabled
+    _enabled = bool(flag)
 
 
 def load_library():
@@ -131,9 +133,20 @@ def check_status(device=None) -> None:
             raise RuntimeError(f"kernel status words non-zero on cuda:{idx}: {vals}")
 
 
+_launches = 0
+
+
 def check(rc: int, what: str) -> None:
+    """Every library entry point is called through this: counts launches, raises on a non-zero code."""
+    global _launches
+    _launches += 1
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")
+
+
+def launch_count() -> int:
+    """Number of calls into the kernel library made by this process so far."""
+    return _launches
 
 
 def env_flag(name: str, default: bool = False) -> bool:

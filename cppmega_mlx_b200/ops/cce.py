@@ -43,7 +43,7 @@ def _chunk_loss_and_grads(h, w, t, valid, scale, want_grads, use_kernel):
         rows, V = logits.shape
         loss_rows = torch.empty(rows, dtype=torch.float32, device=h.device)
         B.check(lib.cmb_cce_rows(B.ptr(logits), B.ptr(t), B.ptr(valid), B.ptr(loss_rows), ctypes.c_int64(rows),
-                                 ctypes.c_int(V), ctypes.c_float(scale), ctypes.c_int(1 if want_grads else 0),
+                                 ctypes.c_int(V), B.ptr(scale), ctypes.c_int(1 if want_grads else 0),
                                  B.stream_ptr()), "cce_rows")
         return loss_rows.sum(), logits  # logits now hold scale*(softmax-onehot) when want_grads
     logits = (h @ w.t()).float()
@@ -54,7 +54,7 @@ def _chunk_loss_and_grads(h, w, t, valid, scale, want_grads, use_kernel):
         return loss, None
     p = torch.exp(logits - lse[:, None])
     p.scatter_add_(1, t.long()[:, None], -torch.ones_like(tgt)[:, None])
-    p = p * (valid.float() * scale)[:, None]
+    p = p * (valid.float() * scale.to(p.device))[:, None]
     return loss, p.to(h.dtype)
 
 
@@ -67,7 +67,8 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
         want = hidden.requires_grad or weight.requires_grad
         use_kernel = (B.on_gpu(hidden, weight) and hidden.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
                       and hasattr(B.load_library(), "cmb_cce_rows") and D % 8 == 0 and weight.shape[0] % 8 == 0)
-        scale = float(scale_t) if want else 1.0  # one host sync per step; the trainer overlaps it
+        # the kernel reads 1/n_valid from device memory, so no host sync; the PyTorch path keeps it as a tensor too
+        scale = scale_t.reshape(1).contiguous()
         dh = torch.empty_like(hidden) if want else None
         dw = torch.zeros(weight.shape, dtype=torch.float32 if use_kernel else weight.dtype, device=weight.device) if want else None
         total = hidden.new_zeros((), dtype=torch.float32)

@@ -50,6 +50,10 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool
     st = B.status_buffer(a.device)
     rc = lib.cmb_gemm_bf16(B.ptr(a), B.ptr(b), B.ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
                            int(a_mn), int(b_mn), flags, B.ptr(st), int(max_ctas), B.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"gemm_bf16 failed with code {rc}: a{tuple(a.shape)}/{a.stride()} ptr%16={a.data_ptr() % 16} "
+                           f"b{tuple(b.shape)}/{b.stride()} ptr%16={b.data_ptr() % 16} out{tuple(out.shape)}/{out.stride()} "
+                           f"a_mn={a_mn} b_mn={b_mn}")
     B.check(rc, "gemm_bf16")
     return out
 

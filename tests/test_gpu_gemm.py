@@ -1,0 +1,54 @@
+"""tcgen05 GEMM vs fp32 torch.matmul, all operand layouts, odd sizes, both output types."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, a_mn, b_mn):
+    A = a.float().t() if a_mn else a.float()
+    Bm = b.float().t() if b_mn else b.float()
+    return A @ Bm.t()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 320, 192), (1000, 136, 72), (4096, 2048, 2048),
+                                   (130, 128, 64), (64, 64, 4096)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B
+    torch.manual_seed(M + N + K)
+    dev = "cuda"
+    a = torch.randn((K, M) if a_mn else (M, K), device=dev).bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device=dev).bfloat16()
+    if (a.shape[1] % 8) or (b.shape[1] % 8):
+        pytest.skip("pitch not a multiple of 8")
+    c = ops.gemm_raw(a, b, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    B.check_status()
+    ref = _ref(a, b, a_mn, b_mn)
+    err = (c.float() - ref).abs().max().item()
+    tol = 2e-2 * (K ** 0.5) + 1e-2 * ref.abs().max().item()
+    assert err < tol, f"max err {err} (tol {tol})"
+    c32 = ops.gemm_raw(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert (c32 - ref).abs().max().item() < 1e-3 * (K ** 0.5) + 1e-4 * ref.abs().max().item()
+
+
+def test_gemm_accumulate_and_linear_grads():
+    from cppmega_mlx_b200 import ops
+    torch.manual_seed(0)
+    x = torch.randn(512, 256, device="cuda").bfloat16().requires_grad_()
+    w = torch.randn(384, 256, device="cuda").bfloat16().requires_grad_()
+    y = ops.linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = xr @ wr.t()
+    yr.backward(g.float())
+    assert (y.float() - yr).abs().max() < 0.5
+    assert (x.grad.float() - xr.grad).abs().max() < 0.6
+    assert (w.grad.float() - wr.grad).abs().max() < 0.8
+    acc = torch.ones(512, 384, device="cuda", dtype=torch.float32)
+    ops.gemm_raw(x.detach(), w.detach(), out=acc, accumulate=True)
+    assert (acc - 1 - yr.detach()).abs().max() < 1e-2
