@@ -1,22 +1,27 @@
-// bf16 GEMM on tcgen05 tensor cores (sm_100a), fp32 accumulation in TMEM.
+// bf16 GEMM on tcgen05 tensor cores (sm_100a), fp32 accumulation in TMEM, optionally batched.
 //
 //   C[M,N] (+)= A · Bᵀ      A: M×K, B: N×K, each either K-major (K contiguous, the natural
 //                           layout of activations and nn.Linear weights) or MN-major (the
 //                           contraction index is the slow one: what dgrad/wgrad see without
 //                           any transposed copies).
+//   Batched: up to three batch dimensions (n2, n3, n4), each operand with its own element strides;
+//   dimension 2 of A or B may be shared by `div` consecutive problems (heads of one group).
 //
-// Structure: persistent CTAs (one per SM), 192 threads in three roles —
-//   warp 0    TMA producer: fills a 4..6-deep ring of {A tile, B tile} stages (128-byte swizzle)
-//   warp 1    MMA issuer  : one elected thread issues tcgen05.mma (128×BN×16) into one of two
-//                           TMEM accumulators; tcgen05.commit hands stages back / signals the epilogue
-//   warps 2-5 epilogue    : tcgen05.ld the finished accumulator, convert, store; overlaps with the
-//                           mainloop of the next tile thanks to the double-buffered accumulator.
-// Every mbarrier wait is bounded (see sm100.cuh); a timeout is reported through `status`.
+// Structure: persistent CTAs (one per SM), 320 threads in three roles —
+//   warp 0     TMA producer: fills a 4..6-deep ring of {A tile, B tile} stages (128-byte swizzle)
+//   warp 1     MMA issuer  : one thread issues tcgen05.mma (128×BN×16) into one of two TMEM
+//                            accumulators; tcgen05.commit hands stages back / signals the epilogue
+//   warps 2-9  epilogue    : two warp-groups, each owning half of the tile's columns; every warp
+//                            reads its 32 TMEM lanes, applies the epilogue, stages a 32-row box in
+//                            swizzled shared memory and issues a TMA store (or TMA reduce-add when
+//                            accumulating).  Overlaps with the next tile's mainloop thanks to the
+//                            double-buffered accumulator.
+// Epilogues: plain; decay-mask `acc · exp(r[t] − c[s]) · [s ≤ t]` (the intra-chunk matrix of the
+// Mamba3 scan).  Every mbarrier wait is bounded (see sm100.cuh); a timeout is reported via `status`.
 //
 // Takes the role of the reference's dense `mx.matmul` call sites ("Path A",
 // docs/production_kernel_routing.md:62-140); there is no GEMM kernel in the reference to compare to.
 #include <mutex>
-#include <unordered_map>
 
 #include "sm100.cuh"
 
@@ -24,10 +29,23 @@ namespace cmb {
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;  // 64 bf16 = one 128-byte swizzle line
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_EPI_WARPS = 8;
+constexpr int GEMM_THREADS = 64 + 32 * GEMM_EPI_WARPS;
 constexpr int GEMM_GROUP_M = 16;
+constexpr int GEMM_CBOX_BYTES = 32 * 128;  // one epilogue warp's staging box: 32 rows × 128 bytes
 
-enum : int { GEMM_OUT_F32 = 1, GEMM_ACCUMULATE = 2 };
+enum : int { GEMM_OUT_F32 = 1, GEMM_ACCUMULATE = 2, GEMM_EPI_DECAY_MASK = 4 };
+
+struct GemmParams {
+  int M, N, K;
+  int nb2, nb3, nb4;
+  int a_div2, b_div2;
+  int flags;
+  const float* row_vec;
+  const float* col_vec;
+  long long sv2, sv3, sv4;  // element strides of the epilogue vectors over the batch dims
+  int* status;
+};
 
 template <int BN>
 struct GemmCfg {
@@ -36,41 +54,80 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int C_BYTES = GEMM_EPI_WARPS * GEMM_CBOX_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + C_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
-__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& tm, int& tn) {
+__device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+      "r"(c3), "r"(c4)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_5d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2, int c3,
+                                             int c4) {
+  asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+               : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_5d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2,
+                                                  int c3, int c4) {
+  asm volatile("cp.reduce.async.bulk.tensor.5d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+               : "memory");
+}
+
+struct TileCoord {
+  int tm, tn, i2, i3, i4;
+};
+
+__device__ __forceinline__ TileCoord tile_coords(int t, int num_m, int num_n, int nb2, int nb3) {
+  TileCoord c;
+  const int per_problem = num_m * num_n;
+  const int batch = t / per_problem;
+  const int r0 = t - batch * per_problem;
+  c.i2 = batch % nb2;
+  const int q = batch / nb2;
+  c.i3 = q % nb3;
+  c.i4 = q / nb3;
   const int per_group = GEMM_GROUP_M * num_n;
-  const int g = t / per_group;
+  const int g = r0 / per_group;
   const int first_m = g * GEMM_GROUP_M;
   const int gsz = min(num_m - first_m, GEMM_GROUP_M);
-  const int r = t - g * per_group;
-  tm = first_m + r % gsz;
-  tn = r / gsz;
+  const int r = r0 - g * per_group;
+  c.tm = first_m + r % gsz;
+  c.tn = r / gsz;
+  return c;
 }
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cv,
-                 int M, int N, int K, int ldc, int flags, int* __restrict__ status) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
-  uint64_t* full_bar = bars;                 // [STAGES]
-  uint64_t* empty_bar = bars + STAGES;       // [STAGES]
-  uint64_t* tfull_bar = bars + 2 * STAGES;   // [2]
+  uint8_t* csmem = smem + STAGES * Cfg::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(csmem + Cfg::C_BYTES);
+  uint64_t* full_bar = bars;                     // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;           // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * STAGES;       // [2]
   uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_m = (M + GEMM_BM - 1) / GEMM_BM;
-  const int num_n = (N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
-  const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+  const int num_m = (p.M + GEMM_BM - 1) / GEMM_BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n * p.nb2 * p.nb3 * p.nb4;
+  const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
+  int* status = p.status;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -79,12 +136,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
-      mbar_init(&tempty_bar[b], 4);
+      mbar_init(&tempty_bar[b], GEMM_EPI_WARPS);
     }
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -102,9 +160,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int tm, tn;
-        tile_coords(t, num_m, num_n, tm, tn);
-        const int m0 = tm * GEMM_BM, n0 = tn * BN;
+        const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3);
+        const int m0 = tc.tm * GEMM_BM, n0 = tc.tn * BN;
+        const int a2 = tc.i2 / p.a_div2, b2 = tc.i2 / p.b_div2;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) {
             ok = false;
@@ -116,15 +174,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int k0 = kb * GEMM_BK;
           if (A_MN) {
 #pragma unroll
-            for (int i = 0; i < GEMM_BM / 64; ++i) tma_load_2d(sa + i * (GEMM_BK * 128), &tmA, &full_bar[stage], m0 + 64 * i, k0);
+            for (int i = 0; i < GEMM_BM / 64; ++i)
+              tma_load_5d(sa + i * (GEMM_BK * 128), &tmA, &full_bar[stage], m0 + 64 * i, k0, a2, tc.i3, tc.i4);
           } else {
-            tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
+            tma_load_5d(sa, &tmA, &full_bar[stage], k0, m0, a2, tc.i3, tc.i4);
           }
           if (B_MN) {
 #pragma unroll
-            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * (GEMM_BK * 128), &tmB, &full_bar[stage], n0 + 64 * i, k0);
+            for (int i = 0; i < BN / 64; ++i)
+              tma_load_5d(sb + i * (GEMM_BK * 128), &tmB, &full_bar[stage], n0 + 64 * i, k0, b2, tc.i3, tc.i4);
           } else {
-            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+            tma_load_5d(sb, &tmB, &full_bar[stage], k0, n0, b2, tc.i3, tc.i4);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -173,80 +233,83 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps)
-    const int quarter = warp & 3;  // TMEM lanes this warp may read
-    const bool out_f32 = (flags & GEMM_OUT_F32) != 0;
-    const bool accum = (flags & GEMM_ACCUMULATE) != 0;
+    // ------------------------------------------------------------------ epilogue (8 warps)
+    const int ew = warp - 2;
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    const int half = ew >> 2;      // which half of the tile's columns
+    const bool out_f32 = (p.flags & GEMM_OUT_F32) != 0;
+    const bool accum = (p.flags & GEMM_ACCUMULATE) != 0;
+    const bool decay = (p.flags & GEMM_EPI_DECAY_MASK) != 0;
+    uint8_t* cbox = csmem + ew * GEMM_CBOX_BYTES;
     int local = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
       const int buf = local & 1;
       const uint32_t aphase = (local >> 1) & 1;
       if (!mbar_wait(&tfull_bar[buf], aphase, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
-      int tm, tn;
-      tile_coords(t, num_m, num_n, tm, tn);
-      const int row = tm * GEMM_BM + quarter * 32 + lane;
-      const int n0 = tn * BN;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+      const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3);
+      const int row0 = tc.tm * GEMM_BM + quarter * 32;
+      const int row = row0 + lane;
+      const int ncol0 = tc.tn * BN + half * (BN / 2);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + half * (BN / 2);
+      float rv = 0.f;
+      const float* colv = nullptr;
+      if (decay) {
+        const long long voff = tc.i2 * p.sv2 + tc.i3 * p.sv3 + tc.i4 * p.sv4;
+        rv = row < p.M ? p.row_vec[voff + row] : 0.f;
+        colv = p.col_vec + voff;
+      }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < (BN / 2) / 32; ++c) {
         uint32_t r[32];
         tmem_ld_x32(taddr + c * 32, r);
         tmem_wait_ld();
-        const int col0 = n0 + c * 32;
-        if (row < M && col0 < N) {
-          if (out_f32) {
-            float* dst = reinterpret_cast<float*>(Cv) + static_cast<size_t>(row) * ldc + col0;
-            if (col0 + 32 <= N && (ldc & 3) == 0) {
+        const int col0 = ncol0 + c * 32;
+        if (decay) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                       __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                if (accum) {
-                  const float4 o = *reinterpret_cast<const float4*>(dst + 4 * j);
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                }
-                *reinterpret_cast<float4*>(dst + 4 * j) = v;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < N; ++j) {
-                float v = __uint_as_float(r[j]);
-                if (accum) v += dst[j];
-                dst[j] = v;
-              }
-            }
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cv) + static_cast<size_t>(row) * ldc + col0;
-            if (col0 + 32 <= N && (ldc & 7) == 0) {
+          for (int j = 0; j < 32; ++j) {
+            const int s = col0 + j;
+            float v = 0.f;
+            if (s <= row && s < p.N) v = __uint_as_float(r[j]) * __expf(rv - colv[s]);
+            r[j] = __float_as_uint(v);
+          }
+        }
+        // Stage into the swizzled box: row `lane`, 16-byte chunk ch lands at chunk (ch ^ (lane & 7)).
+        const bool new_box = out_f32 || (c & 1) == 0;
+        if (new_box) {
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+        }
+        uint8_t* rowp = cbox + lane * 128;
+        if (out_f32) {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float f[8];
+          for (int ch = 0; ch < 8; ++ch) {
+            const uint4 v = make_uint4(r[4 * ch], r[4 * ch + 1], r[4 * ch + 2], r[4 * ch + 3]);
+            *reinterpret_cast<uint4*>(rowp + ((ch ^ (lane & 7)) << 4)) = v;
+          }
+        } else {
+          const int chbase = (c & 1) * 4;
 #pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]);
-                if (accum) {
-                  const uint4 o = *reinterpret_cast<const uint4*>(dst + 8 * j);
-                  const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&o);
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    const float2 of = __bfloat1622float2(ob[e]);
-                    f[2 * e] += of.x;
-                    f[2 * e + 1] += of.y;
-                  }
-                }
-                uint4 v;
-                v.x = pack_bf16x2(f[0], f[1]);
-                v.y = pack_bf16x2(f[2], f[3]);
-                v.z = pack_bf16x2(f[4], f[5]);
-                v.w = pack_bf16x2(f[6], f[7]);
-                *reinterpret_cast<uint4*>(dst + 8 * j) = v;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < N; ++j) {
-                float v = __uint_as_float(r[j]);
-                if (accum) v += __bfloat162float(dst[j]);
-                dst[j] = __float2bfloat16(v);
-              }
-            }
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * ch]), __uint_as_float(r[8 * ch + 1]));
+            v.y = pack_bf16x2(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+            v.z = pack_bf16x2(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+            v.w = pack_bf16x2(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+            *reinterpret_cast<uint4*>(rowp + (((chbase + ch) ^ (lane & 7)) << 4)) = v;
+          }
+        }
+        const bool box_done = out_f32 || (c & 1) == 1;
+        if (box_done) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          const int bcol0 = out_f32 ? col0 : col0 - 32;
+          if (lane == 0 && row0 < p.M && bcol0 < p.N) {
+            if (accum)
+              tma_reduce_add_5d(&tmC, cbox, bcol0, row0, tc.i2, tc.i3, tc.i4);
+            else
+              tma_store_5d(&tmC, cbox, bcol0, row0, tc.i2, tc.i3, tc.i4);
+            tma_store_commit();
           }
         }
       }
@@ -254,6 +317,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
     }
+    if (lane == 0) tma_store_wait<0>();  // all global writes done before the staging memory goes away
   }
 
   // ------------------------------------------------------------------ teardown
@@ -289,30 +353,64 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+void bind_context_once() {
+  // The driver-API encoder needs a current context; a thread whose first CUDA call is this one (an autograd
+  // worker, say) has none until a runtime call binds the primary context.
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
+static CUtensorMapDataType dtype_of(int elem_bytes) {
+  return elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                         : (elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8);
+}
+static CUtensorMapSwizzle swizzle_of(int bytes) {
+  return bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+         : bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+         : bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                       : CU_TENSOR_MAP_SWIZZLE_NONE;
+}
+
 int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
                  uint32_t box_rows, uint32_t box_cols, int swizzle_bytes) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return 101;
-  // The driver-API encoder needs a current context; a thread whose first CUDA call is this one (an autograd
-  // worker, say) has none until a runtime call binds the primary context.
-  static thread_local bool ctx_bound = false;
-  if (!ctx_bound) {
-    cudaFree(nullptr);
-    ctx_bound = true;
-  }
+  bind_context_once();
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((ld * elem_bytes) & 15) != 0) return 102;
-  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                           : (elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8);
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elem_bytes)};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUtensorMapSwizzle sw = swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                          : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
-                          : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
-                                                : CU_TENSOR_MAP_SWIZZLE_NONE;
-  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = fn(out, dtype_of(elem_bytes), 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_of(swizzle_bytes), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + static_cast<int>(r);
+}
+
+// 5-D map: (cols, rows, n2, n3, n4); strides in elements for rows and the three batch dims.
+static int make_tmap_5d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
+                        const uint64_t nb[3], const int64_t sb[3], uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return 101;
+  bind_context_once();
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ((ld * elem_bytes) & 15) != 0) return 102;
+  cuuint64_t dims[5] = {cols, rows, nb[0], nb[1], nb[2]};
+  cuuint64_t strides[4];
+  strides[0] = ld * static_cast<uint64_t>(elem_bytes);
+  for (int i = 0; i < 3; ++i) {
+    uint64_t s = static_cast<uint64_t>(sb[i]) * elem_bytes;
+    if (nb[i] <= 1 || s == 0) s = strides[0];  // unused batch dim: any legal stride
+    if (s & 15) return 105;
+    strides[i + 1] = s;
+  }
+  cuuint32_t box[5] = {box_cols, box_rows, 1, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(out, dtype_of(elem_bytes), 5, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : 1000 + static_cast<int>(r);
 }
 
@@ -326,59 +424,120 @@ static int sm_count() {
   return n;
 }
 
+struct GemmArgs {
+  const void* A;
+  const void* B;
+  void* C;
+  int M, N, K;
+  int64_t lda, ldb, ldc;
+  int flags;
+  uint64_t nb[3];
+  int64_t sA[3], sB[3], sC[3];
+  int a_div2, b_div2;
+  const float* row_vec;
+  const float* col_vec;
+  int64_t sv[3];
+  int* status;
+  int max_ctas;
+  cudaStream_t stream;
+};
+
 template <int BN, bool A_MN, bool B_MN>
-static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int flags,
-                       int* status, int max_ctas, cudaStream_t stream) {
+static int launch_gemm(const GemmArgs& g) {
   using Cfg = cmb::GemmCfg<BN>;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC;
   int rc;
+  uint64_t nbA[3] = {g.nb[0] / g.a_div2, g.nb[1], g.nb[2]};
+  uint64_t nbB[3] = {g.nb[0] / g.b_div2, g.nb[1], g.nb[2]};
   // K-major operand stored [rows=M|N, cols=K]; MN-major operand stored [rows=K, cols=M|N].
   if (A_MN)
-    rc = make_tmap_2d(&tmA, A, 2, K, M, lda, cmb::GEMM_BK, 64, 128);
+    rc = make_tmap_5d(&tmA, g.A, 2, g.K, g.M, g.lda, nbA, g.sA, cmb::GEMM_BK, 64);
   else
-    rc = make_tmap_2d(&tmA, A, 2, M, K, lda, cmb::GEMM_BM, cmb::GEMM_BK, 128);
+    rc = make_tmap_5d(&tmA, g.A, 2, g.M, g.K, g.lda, nbA, g.sA, cmb::GEMM_BM, cmb::GEMM_BK);
   if (rc) return rc;
   if (B_MN)
-    rc = make_tmap_2d(&tmB, B, 2, K, N, ldb, cmb::GEMM_BK, 64, 128);
+    rc = make_tmap_5d(&tmB, g.B, 2, g.K, g.N, g.ldb, nbB, g.sB, cmb::GEMM_BK, 64);
   else
-    rc = make_tmap_2d(&tmB, B, 2, N, K, ldb, BN, cmb::GEMM_BK, 128);
-  if (rc) return rc + 10;
+    rc = make_tmap_5d(&tmB, g.B, 2, g.N, g.K, g.ldb, nbB, g.sB, BN, cmb::GEMM_BK);
+  if (rc) return rc + 10000;
+  const bool f32 = (g.flags & cmb::GEMM_OUT_F32) != 0;
+  rc = make_tmap_5d(&tmC, g.C, f32 ? 4 : 2, g.M, g.N, g.ldc, g.nb, g.sC, 32, f32 ? 32 : 64);
+  if (rc) return rc + 20000;
   auto kern = cmb::gemm_bf16_kernel<BN, A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 103;
     attr_set = true;
   }
-  const int num_tiles = ((M + cmb::GEMM_BM - 1) / cmb::GEMM_BM) * ((N + BN - 1) / BN);
+  const long long num_tiles = static_cast<long long>((g.M + cmb::GEMM_BM - 1) / cmb::GEMM_BM) * ((g.N + BN - 1) / BN) *
+                              g.nb[0] * g.nb[1] * g.nb[2];
+  if (num_tiles > 0x7fffffffLL) return 106;
   int grid = sm_count();
-  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  if (num_tiles < grid) grid = num_tiles;
-  kern<<<grid, cmb::GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, C, M, N, K, ldc, flags, status);
+  if (g.max_ctas > 0 && g.max_ctas < grid) grid = g.max_ctas;
+  if (num_tiles < grid) grid = static_cast<int>(num_tiles);
+  cmb::GemmParams p;
+  p.M = g.M; p.N = g.N; p.K = g.K;
+  p.nb2 = static_cast<int>(g.nb[0]); p.nb3 = static_cast<int>(g.nb[1]); p.nb4 = static_cast<int>(g.nb[2]);
+  p.a_div2 = g.a_div2; p.b_div2 = g.b_div2;
+  p.flags = g.flags;
+  p.row_vec = g.row_vec; p.col_vec = g.col_vec;
+  p.sv2 = g.sv[0]; p.sv3 = g.sv[1]; p.sv4 = g.sv[2];
+  p.status = g.status;
+  kern<<<grid, cmb::GEMM_THREADS, Cfg::SMEM_BYTES, g.stream>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 104;
+}
+
+static int dispatch(const GemmArgs& g, int a_mn, int b_mn) {
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0 || g.nb[0] * g.nb[1] * g.nb[2] == 0) return 0;
+  if (g.a_div2 <= 0 || g.b_div2 <= 0 || g.nb[0] % g.a_div2 || g.nb[0] % g.b_div2) return 107;
+  const bool big = g.N > 128;
+#define CMB_GEMM_CASE(BN_, AM_, BM_) return launch_gemm<BN_, AM_, BM_>(g)
+  if (big) {
+    if (!a_mn && !b_mn) CMB_GEMM_CASE(256, false, false);
+    if (!a_mn && b_mn) CMB_GEMM_CASE(256, false, true);
+    if (a_mn && !b_mn) CMB_GEMM_CASE(256, true, false);
+    CMB_GEMM_CASE(256, true, true);
+  } else {
+    if (!a_mn && !b_mn) CMB_GEMM_CASE(128, false, false);
+    if (!a_mn && b_mn) CMB_GEMM_CASE(128, false, true);
+    if (a_mn && !b_mn) CMB_GEMM_CASE(128, true, false);
+    CMB_GEMM_CASE(128, true, true);
+  }
+#undef CMB_GEMM_CASE
 }
 
 }  // namespace cmb_host
 
 // C ABI. A is M×K (K-major, row pitch lda) or, with a_mn_major, stored K×M (row pitch lda).
 // B is N×K (K-major) or, with b_mn_major, stored K×N. C is M×N row-major (pitch ldc), bf16 unless
-// flags&1 (fp32); flags&2 accumulates into C. All pointers 16-byte aligned, pitches multiples of 8.
+// flags&1 (fp32); flags&2 accumulates into C. All pointers 16-byte aligned, every pitch a multiple of 16 bytes.
 extern "C" int cmb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                              int a_mn_major, int b_mn_major, int flags, int* status, int max_ctas, void* stream) {
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool big = N > 128;
-#define CMB_GEMM_CASE(BN_, AM_, BM_) \
-  return cmb_host::launch_gemm<BN_, AM_, BM_>(A, B, C, M, N, K, lda, ldb, ldc, flags, status, max_ctas, s)
-  if (big) {
-    if (!a_mn_major && !b_mn_major) CMB_GEMM_CASE(256, false, false);
-    if (!a_mn_major && b_mn_major) CMB_GEMM_CASE(256, false, true);
-    if (a_mn_major && !b_mn_major) CMB_GEMM_CASE(256, true, false);
-    CMB_GEMM_CASE(256, true, true);
-  } else {
-    if (!a_mn_major && !b_mn_major) CMB_GEMM_CASE(128, false, false);
-    if (!a_mn_major && b_mn_major) CMB_GEMM_CASE(128, false, true);
-    if (a_mn_major && !b_mn_major) CMB_GEMM_CASE(128, true, false);
-    CMB_GEMM_CASE(128, true, true);
+  cmb_host::GemmArgs g{};
+  g.A = A; g.B = B; g.C = C; g.M = M; g.N = N; g.K = K;
+  g.lda = lda; g.ldb = ldb; g.ldc = ldc;
+  g.flags = flags & 3;
+  for (int i = 0; i < 3; ++i) { g.nb[i] = 1; g.sA[i] = g.sB[i] = g.sC[i] = 0; g.sv[i] = 0; }
+  g.a_div2 = g.b_div2 = 1;
+  g.status = status; g.max_ctas = max_ctas; g.stream = static_cast<cudaStream_t>(stream);
+  return cmb_host::dispatch(g, a_mn_major, b_mn_major);
+}
+
+// Batched form. `ip` = {M, N, K, a_mn, b_mn, flags, a_div2, b_div2, max_ctas}; `lp` = {lda, ldb, ldc, nb2, nb3, nb4,
+// sA2, sA3, sA4, sB2, sB3, sB4, sC2, sC3, sC4, sv2, sv3, sv4} (element counts / strides). flags&4 selects the
+// decay-mask epilogue, which reads fp32 `row_vec[batch_off + t]` and `col_vec[batch_off + s]`.
+extern "C" int cmb_gemm_bf16_batched(const void* A, const void* B, void* C, const int* ip, const long long* lp,
+                                     const float* row_vec, const float* col_vec, int* status, void* stream) {
+  cmb_host::GemmArgs g{};
+  g.A = A; g.B = B; g.C = C; g.M = ip[0]; g.N = ip[1]; g.K = ip[2];
+  g.flags = ip[5]; g.a_div2 = ip[6]; g.b_div2 = ip[7]; g.max_ctas = ip[8];
+  g.lda = lp[0]; g.ldb = lp[1]; g.ldc = lp[2];
+  for (int i = 0; i < 3; ++i) {
+    g.nb[i] = static_cast<uint64_t>(lp[3 + i]);
+    g.sA[i] = lp[6 + i]; g.sB[i] = lp[9 + i]; g.sC[i] = lp[12 + i]; g.sv[i] = lp[15 + i];
   }
-#undef CMB_GEMM_CASE
+  g.row_vec = row_vec; g.col_vec = col_vec;
+  g.status = status; g.stream = static_cast<cudaStream_t>(stream);
+  if ((g.flags & cmb::GEMM_EPI_DECAY_MASK) && (row_vec == nullptr || col_vec == nullptr)) return 108;
+  return cmb_host::dispatch(g, ip[3], ip[4]);
 }

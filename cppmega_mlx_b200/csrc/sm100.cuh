@@ -281,6 +281,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn encode_tiled_fn();
+// Binds the primary context to the calling thread once (driver-API calls need a current context).
+void bind_context_once();
 
 // 2-D row-major tensor [rows, cols] of `elem_bytes`-wide elements with row pitch `ld` elements;
 // box = [box_rows, box_cols]. Returns 0 on success.

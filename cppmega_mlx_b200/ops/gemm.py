@@ -15,6 +15,7 @@ from . import _backend as B
 
 OUT_F32 = 1
 ACCUMULATE = 2
+EPI_DECAY_MASK = 4
 
 
 def _ok(t: torch.Tensor) -> bool:
@@ -46,6 +47,8 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool
         out = torch.empty(M, N, dtype=out_dtype, device=a.device)
         if accumulate:
             out.zero_()
+    elif out.stride(1) != 1 or (out.stride(0) * out.element_size()) % 16 or out.data_ptr() % 16:
+        raise ValueError("gemm_raw output needs unit inner stride, a 16-byte multiple pitch and 16-byte alignment")
     flags = (OUT_F32 if out.dtype == torch.float32 else 0) | (ACCUMULATE if accumulate else 0)
     st = B.status_buffer(a.device)
     rc = lib.cmb_gemm_bf16(B.ptr(a), B.ptr(b), B.ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
@@ -55,6 +58,32 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool
                            f"b{tuple(b.shape)}/{b.stride()} ptr%16={b.data_ptr() % 16} out{tuple(out.shape)}/{out.stride()} "
                            f"a_mn={a_mn} b_mn={b_mn}")
     B.check(rc, "gemm_bf16")
+    return out
+
+
+def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool, b_mn: bool,
+                 lda: int, ldb: int, ldc: int, nb: tuple[int, int, int], sA: tuple[int, int, int],
+                 sB: tuple[int, int, int], sC: tuple[int, int, int], a_div2: int = 1, b_div2: int = 1,
+                 accumulate: bool = False, row_vec: torch.Tensor | None = None, col_vec: torch.Tensor | None = None,
+                 sv: tuple[int, int, int] = (0, 0, 0), max_ctas: int = 0) -> torch.Tensor:
+    """Strided-batched C (+)= A·Bᵀ. ``a``/``b``/``out`` only supply base pointers; all geometry is explicit:
+    pitches ``ld*`` and per-operand element strides over the three batch dims ``nb = (n2, n3, n4)``.
+    ``a_div2``/``b_div2`` let ``div`` consecutive dim-2 problems share one operand slice (the operand then has
+    ``n2 // div`` slices).  With ``row_vec``/``col_vec`` (fp32) the epilogue writes
+    ``acc · exp(row_vec[t] − col_vec[s]) · [s ≤ t]``."""
+    lib = B.load_library()
+    flags = (OUT_F32 if out.dtype == torch.float32 else 0) | (ACCUMULATE if accumulate else 0)
+    if row_vec is not None:
+        flags |= EPI_DECAY_MASK
+    ip = (ctypes.c_int * 9)(M, N, K, int(a_mn), int(b_mn), flags, a_div2, b_div2, max_ctas)
+    lp = (ctypes.c_longlong * 18)(lda, ldb, ldc, *nb, *sA, *sB, *sC, *sv)
+    st = B.status_buffer(a.device)
+    rc = lib.cmb_gemm_bf16_batched(B.ptr(a), B.ptr(b), B.ptr(out), ip, lp, B.ptr(row_vec), B.ptr(col_vec), B.ptr(st),
+                                   B.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"gemm_bf16_batched failed with code {rc}: M{M} N{N} K{K} a_mn={a_mn} b_mn={b_mn} ld=({lda},{ldb},{ldc}) "
+                           f"nb={nb} sA={sA} sB={sB} sC={sC}")
+    B.check(rc, "gemm_bf16_batched")
     return out
 
 

@@ -52,3 +52,42 @@ def test_gemm_accumulate_and_linear_grads():
     acc = torch.ones(512, 384, device="cuda", dtype=torch.float32)
     ops.gemm_raw(x.detach(), w.detach(), out=acc, accumulate=True)
     assert (acc - 1 - yr.detach()).abs().max() < 1e-2
+
+
+def test_gemm_batched_shared_operand_and_decay_epilogue():
+    """[b, c, h] batch with the B operand shared per group of heads and the decay-mask epilogue."""
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as Bk
+    torch.manual_seed(1)
+    nb_, nc, H, G, L, N = 2, 3, 4, 2, 256, 128
+    C = torch.randn(nb_, nc, G, L, N, device="cuda").bfloat16()
+    Bm = torch.randn(nb_, nc, G, L, N, device="cuda").bfloat16()
+    cum = -torch.rand(nb_, nc, H, L, device="cuda").cumsum(-1) * 0.05
+    out = torch.empty(nb_, nc, H, L, L, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_batched(C, Bm, out, M=L, N=L, K=N, a_mn=False, b_mn=False, lda=N, ldb=N, ldc=L, nb=(H, nc, nb_),
+                     sA=(L * N, G * L * N, nc * G * L * N), sB=(L * N, G * L * N, nc * G * L * N),
+                     sC=(L * L, H * L * L, nc * H * L * L), a_div2=H // G, b_div2=H // G, row_vec=cum, col_vec=cum,
+                     sv=(L, H * L, nc * H * L))
+    torch.cuda.synchronize()
+    Bk.check_status()
+    Gm = torch.einsum("bcgln,bcgsn->bcgls", C.float(), Bm.float()).repeat_interleave(H // G, dim=2)
+    dec = torch.exp(cum[..., :, None] - cum[..., None, :])
+    ref = Gm * dec * torch.ones(L, L, device="cuda").tril()
+    err = (out.float() - ref).abs().max().item()
+    assert err < 0.02 * ref.abs().max().item() + 0.05, err
+
+
+def test_gemm_batched_mn_major_strided_views():
+    """Y[b,c,h] = M[b,c,h] (L×L) · X[b, cL:(c+1)L, h, :] with X addressed in place (MN-major, strided)."""
+    from cppmega_mlx_b200 import ops
+    torch.manual_seed(2)
+    nb_, nc, H, L, P = 2, 2, 3, 256, 64
+    S = nc * L
+    Mm = torch.randn(nb_, nc, H, L, L, device="cuda").bfloat16()
+    X = torch.randn(nb_, S, H, P, device="cuda").bfloat16()
+    Y = torch.empty(nb_, S, H, P, device="cuda", dtype=torch.float32)
+    ops.gemm_batched(Mm, X, Y, M=L, N=P, K=L, a_mn=False, b_mn=True, lda=L, ldb=H * P, ldc=H * P, nb=(H, nc, nb_),
+                     sA=(L * L, H * L * L, nc * H * L * L), sB=(P, L * H * P, S * H * P), sC=(P, L * H * P, S * H * P))
+    torch.cuda.synchronize()
+    ref = torch.einsum("bchls,bcshp->bclhp", Mm.float(), X.float().view(nb_, nc, L, H, P)).reshape(nb_, S, H, P)
+    assert (Y - ref).abs().max().item() < 1e-2 * ref.abs().max().item() + 1e-2
