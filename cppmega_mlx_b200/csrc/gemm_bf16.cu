@@ -17,7 +17,7 @@
 //                            accumulating).  Overlaps with the next tile's mainloop thanks to the
 //                            double-buffered accumulator.
 // Epilogues: plain; decay-mask `acc · exp(r[t] − c[s]) · [s ≤ t]` (the intra-chunk matrix of the
-// Mamba3 scan).  Every mbarrier wait is bounded (see sm100.cuh); a timeout is reported via `status`.
+// Mamba3 scan); row-exp `acc · exp(r[t])` (the carried-state term of the same scan).  Every mbarrier wait is bounded (see sm100.cuh); a timeout is reported via `status`.
 //
 // Takes the role of the reference's dense `mx.matmul` call sites ("Path A",
 // docs/production_kernel_routing.md:62-140); there is no GEMM kernel in the reference to compare to.
@@ -34,7 +34,7 @@ constexpr int GEMM_THREADS = 64 + 32 * GEMM_EPI_WARPS;
 constexpr int GEMM_GROUP_M = 16;
 constexpr int GEMM_CBOX_BYTES = 32 * 128;  // one epilogue warp's staging box: 32 rows × 128 bytes
 
-enum : int { GEMM_OUT_F32 = 1, GEMM_ACCUMULATE = 2, GEMM_EPI_DECAY_MASK = 4 };
+enum : int { GEMM_OUT_F32 = 1, GEMM_ACCUMULATE = 2, GEMM_EPI_DECAY_MASK = 4, GEMM_EPI_ROW_EXP = 8 };
 
 struct GemmParams {
   int M, N, K;
@@ -240,6 +240,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool out_f32 = (p.flags & GEMM_OUT_F32) != 0;
     const bool accum = (p.flags & GEMM_ACCUMULATE) != 0;
     const bool decay = (p.flags & GEMM_EPI_DECAY_MASK) != 0;
+    const bool rowexp = (p.flags & GEMM_EPI_ROW_EXP) != 0;
     uint8_t* cbox = csmem + ew * GEMM_CBOX_BYTES;
     int local = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
@@ -254,10 +255,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + half * (BN / 2);
       float rv = 0.f;
       const float* colv = nullptr;
-      if (decay) {
+      if (decay || rowexp) {
         const long long voff = tc.i2 * p.sv2 + tc.i3 * p.sv3 + tc.i4 * p.sv4;
         rv = row < p.M ? p.row_vec[voff + row] : 0.f;
-        colv = p.col_vec + voff;
+        if (decay) colv = p.col_vec + voff;
+        if (rowexp) rv = __expf(rv);
       }
 #pragma unroll 1
       for (int c = 0; c < (BN / 2) / 32; ++c) {
@@ -273,6 +275,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (s <= row && s < p.N) v = __uint_as_float(r[j]) * __expf(rv - colv[s]);
             r[j] = __float_as_uint(v);
           }
+        }
+        if (rowexp) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rv);
         }
         // Stage into the swizzled box: row `lane`, 16-byte chunk ch lands at chunk (ch ^ (lane & 7)).
         const bool new_box = out_f32 || (c & 1) == 0;
@@ -525,7 +531,7 @@ extern "C" int cmb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
 
 // Batched form. `ip` = {M, N, K, a_mn, b_mn, flags, a_div2, b_div2, max_ctas}; `lp` = {lda, ldb, ldc, nb2, nb3, nb4,
 // sA2, sA3, sA4, sB2, sB3, sB4, sC2, sC3, sC4, sv2, sv3, sv4} (element counts / strides). flags&4 selects the
-// decay-mask epilogue, which reads fp32 `row_vec[batch_off + t]` and `col_vec[batch_off + s]`.
+// decay-mask epilogue, which reads fp32 `row_vec[batch_off + t]` and `col_vec[batch_off + s]`; flags&8 the row-exp one.
 extern "C" int cmb_gemm_bf16_batched(const void* A, const void* B, void* C, const int* ip, const long long* lp,
                                      const float* row_vec, const float* col_vec, int* status, void* stream) {
   cmb_host::GemmArgs g{};
@@ -539,5 +545,6 @@ extern "C" int cmb_gemm_bf16_batched(const void* A, const void* B, void* C, cons
   g.row_vec = row_vec; g.col_vec = col_vec;
   g.status = status; g.stream = static_cast<cudaStream_t>(stream);
   if ((g.flags & cmb::GEMM_EPI_DECAY_MASK) && (row_vec == nullptr || col_vec == nullptr)) return 108;
+  if ((g.flags & cmb::GEMM_EPI_ROW_EXP) && row_vec == nullptr) return 108;
   return cmb_host::dispatch(g, ip[3], ip[4]);
 }

@@ -1,0 +1,486 @@
+// Element-wise stages of the chunked Mamba3 scan (the GEMM-shaped stages run on the batched tcgen05
+// GEMM; ops/mamba3_scan_cuda.py sequences both).  Shapes: x, z, y, dy … [B,S,H,P]; per-chunk vectors
+// [B,nc,H,L]; chunk states [B,nc,H,P,N].  All index arithmetic is 64-bit.
+//
+// Recurrence being computed: h_t = exp(A_t dt_t) h_{t-1} + x_t ⊗ B_t,  y_t = C_t·h_t + D x_t,
+// out_t = silu(z_t) y_t  — cppmega_mlx/nn/mamba3.py:339-408 (token loop) and
+// cppmega_mlx/nn/_tilelang/mamba3.py:71-144 / :168-327 (the reference's per-lane Metal kernels).
+#include "sm100.cuh"
+
+namespace cmb {
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + __expf(-v)); }
+
+// cum[b,c,h,t] = Σ_{t'≤t} A·dt over the chunk. One warp per (b,c,h); L ≤ 1024, L % 32 == 0.
+__global__ void m3_cumsum_kernel(const float* __restrict__ A, const float* __restrict__ dt, float* __restrict__ cum,
+                                 int Bn, int S, int H, int L) {
+  const int nc = S / L;
+  const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= static_cast<long long>(Bn) * nc * H) return;
+  const int h = static_cast<int>(row % H);
+  const int c = static_cast<int>((row / H) % nc);
+  const int b = static_cast<int>(row / (static_cast<long long>(H) * nc));
+  const int per = L / 32;
+  float run = 0.f;
+  float vals[32];
+  const long long base = (static_cast<long long>(b) * S + static_cast<long long>(c) * L) * H + h;
+  for (int i = 0; i < per; ++i) {
+    const int t = lane * per + i;
+    const long long idx = base + static_cast<long long>(t) * H;
+    run += A[idx] * dt[idx];
+    vals[i] = run;
+  }
+  // exclusive prefix of the lane totals
+  float tot = run;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float n = __shfl_up_sync(0xffffffffu, tot, o);
+    if (lane >= o) tot += n;
+  }
+  const float off = tot - run;
+  float* out = cum + row * L;
+  for (int i = 0; i < per; ++i) out[lane * per + i] = vals[i] + off;
+}
+
+// xw = x · exp(cum_L − cum_t)   (bf16 out, contiguous).  One thread per bf16 pair.
+__global__ void m3_xw_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ cum,
+                             __nv_bfloat16* __restrict__ xw, int Bn, int S, int H, int P, int L) {
+  const int nc = S / L;
+  const long long n2 = static_cast<long long>(Bn) * S * H * (P / 2);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n2;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long bsh = i / (P / 2);
+    const int h = static_cast<int>(bsh % H);
+    const long long bs = bsh / H;
+    const int s = static_cast<int>(bs % S);
+    const int b = static_cast<int>(bs / S);
+    const int c = s / L, t = s - c * L;
+    const float* cr = cum + ((static_cast<long long>(b) * nc + c) * H + h) * L;
+    const float w = __expf(cr[L - 1] - cr[t]);
+    const float2 v = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(x)[i]);
+    reinterpret_cast<__nv_bfloat162*>(xw)[i] = __floats2bfloat162_rn(v.x * w, v.y * w);
+  }
+}
+
+// Sequential carry over chunks: Hc[c] = state entering chunk c; state ← exp(cum_L[c]) state + S_loc[c].
+__global__ void m3_state_pass_kernel(const float* __restrict__ sloc, const float* __restrict__ cum,
+                                     const float* __restrict__ h0, __nv_bfloat16* __restrict__ hc,
+                                     float* __restrict__ hlast, int Bn, int nc, int H, int PN, int L) {
+  const long long n = static_cast<long long>(Bn) * H * PN;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int e = static_cast<int>(i % PN);
+    const int h = static_cast<int>((i / PN) % H);
+    const int b = static_cast<int>(i / (static_cast<long long>(PN) * H));
+    float st = h0 != nullptr ? h0[i] : 0.f;
+    for (int c = 0; c < nc; ++c) {
+      const long long idx = ((static_cast<long long>(b) * nc + c) * H + h) * PN + e;
+      hc[idx] = __float2bfloat16(st);
+      const float d = __expf(cum[((static_cast<long long>(b) * nc + c) * H + h) * L + L - 1]);
+      st = d * st + sloc[idx];
+    }
+    hlast[i] = st;
+  }
+}
+
+// y_pre = Y + D x ; out = silu(z) y_pre.   z may be a strided view (element strides zs_b, zs_s, zs_h).
+__global__ void m3_finalize_fwd_kernel(const float* __restrict__ Y, const __nv_bfloat16* __restrict__ x,
+                                       const __nv_bfloat16* __restrict__ z, const float* __restrict__ D,
+                                       __nv_bfloat16* __restrict__ ypre, __nv_bfloat16* __restrict__ out, int Bn, int S,
+                                       int H, int P, long long zs_b, long long zs_s, long long zs_h) {
+  const long long n2 = static_cast<long long>(Bn) * S * H * (P / 2);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n2;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int pp = static_cast<int>(i % (P / 2));
+    const long long bsh = i / (P / 2);
+    const int h = static_cast<int>(bsh % H);
+    const long long bs = bsh / H;
+    const int s = static_cast<int>(bs % S);
+    const int b = static_cast<int>(bs / S);
+    const float2 xv = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(x)[i]);
+    const float2 yv = reinterpret_cast<const float2*>(Y)[i];
+    const float d = D[h];
+    const float y0 = yv.x + d * xv.x, y1 = yv.y + d * xv.y;
+    const __nv_bfloat162 zz = *reinterpret_cast<const __nv_bfloat162*>(z + b * zs_b + s * zs_s + h * zs_h + 2 * pp);
+    const float2 zv = __bfloat1622float2(zz);
+    reinterpret_cast<__nv_bfloat162*>(ypre)[i] = __floats2bfloat162_rn(y0, y1);
+    reinterpret_cast<__nv_bfloat162*>(out)[i] = __floats2bfloat162_rn(silu_f(zv.x) * y0, silu_f(zv.y) * y1);
+  }
+}
+
+// Backward prologue. One warp per (b,s,h):
+//   dy = dout·silu(z) ; dz = dout·y_pre·silu'(z) ; dye = dy·exp(cum_t) ; dx_acc = D·dy (fp32)
+//   dcum[b,c,h,t] = Σ_p dy·(y_pre − D x)      (row-factor part of d/dcum)
+//   dD[h] += Σ dy·x                            (block-reduced, one atomic per block)
+// Blocks are laid out so that the 8 warps of a block share h (consecutive s).
+__global__ void __launch_bounds__(256) m3_bwd_pre_kernel(
+    const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ z, const __nv_bfloat16* __restrict__ ypre,
+    const __nv_bfloat16* __restrict__ x, const float* __restrict__ D, const float* __restrict__ cum,
+    __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dz, __nv_bfloat16* __restrict__ dye,
+    float* __restrict__ dx_acc, float* __restrict__ dcum, float* __restrict__ dD, int Bn, int S, int H, int P, int L,
+    long long zs_b, long long zs_s, long long zs_h) {
+  __shared__ float red[8];
+  const int nc = S / L;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // block index → (b, s-block, h)
+  const long long blk = blockIdx.x;
+  const int h = static_cast<int>(blk % H);
+  const long long q = blk / H;
+  const int sblocks = (S + 7) / 8;
+  const int sb = static_cast<int>(q % sblocks);
+  const int b = static_cast<int>(q / sblocks);
+  const int s = sb * 8 + warp;
+  float dacc = 0.f;
+  if (b < Bn && s < S) {
+    const int c = s / L, t = s - c * L;
+    const long long crow = ((static_cast<long long>(b) * nc + c) * H + h) * L;
+    const float e = __expf(cum[crow + t]);
+    const float d = D[h];
+    const long long base = ((static_cast<long long>(b) * S + s) * H + h) * P;
+    const __nv_bfloat16* zr = z + b * zs_b + s * zs_s + h * zs_h;
+    float rsum = 0.f;
+    for (int p = 2 * lane; p < P; p += 64) {
+      const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dout + base + p));
+      const float2 zv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(zr + p));
+      const float2 yv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(ypre + base + p));
+      const float2 xv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + base + p));
+      const float s0 = 1.f / (1.f + __expf(-zv.x)), s1 = 1.f / (1.f + __expf(-zv.y));
+      const float sl0 = zv.x * s0, sl1 = zv.y * s1;
+      const float dy0 = g.x * sl0, dy1 = g.y * sl1;
+      *reinterpret_cast<__nv_bfloat162*>(dy + base + p) = __floats2bfloat162_rn(dy0, dy1);
+      *reinterpret_cast<__nv_bfloat162*>(dz + base + p) =
+          __floats2bfloat162_rn(g.x * yv.x * (s0 + sl0 * (1.f - s0)), g.y * yv.y * (s1 + sl1 * (1.f - s1)));
+      *reinterpret_cast<__nv_bfloat162*>(dye + base + p) = __floats2bfloat162_rn(dy0 * e, dy1 * e);
+      *reinterpret_cast<float2*>(dx_acc + base + p) = make_float2(d * dy0, d * dy1);
+      rsum += dy0 * (yv.x - d * xv.x) + dy1 * (yv.y - d * xv.y);
+      dacc += dy0 * xv.x + dy1 * xv.y;
+    }
+    rsum = warp_sum(rsum);
+    if (lane == 0) dcum[crow + t] = rsum;
+  }
+  dacc = warp_sum(dacc);
+  if (lane == 0) red[warp] = dacc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < 8; ++w) t += red[w];
+    atomicAdd(&dD[h], t);
+  }
+}
+
+// [L,L] stage of the backward: per (b,c,g, 32-row block) loop over the heads of the group:
+//   Q = dM∘M ; dcum[b,c,h,s] −= Σ_t Q[t,s] ; dG_g[t,s] = Σ_h dM_h[t,s]·exp(cum_h[t] − cum_h[s])·[s ≤ t]
+// 8 warps × 4 rows; lane owns column pairs s = 2·lane + 64·j.  L ≤ 512, L % 64 == 0.
+template <int MAXJ>
+__global__ void __launch_bounds__(256) m3_bwd_q_kernel(const __nv_bfloat16* __restrict__ dM,
+                                                        const __nv_bfloat16* __restrict__ Mm,
+                                                        const float* __restrict__ cum, float* __restrict__ dcum,
+                                                        __nv_bfloat16* __restrict__ dG, int Bn, int nc, int H, int G,
+                                                        int L) {
+  extern __shared__ float sm[];  // [L] cum of current head, [L] column sums
+  float* scum = sm;
+  float* scol = sm + L;
+  const int hg = H / G;
+  const int rblocks = L / 32;
+  const long long blk = blockIdx.x;
+  const int rb = static_cast<int>(blk % rblocks);
+  const long long q = blk / rblocks;
+  const int g = static_cast<int>(q % G);
+  const int c = static_cast<int>((q / G) % nc);
+  const int b = static_cast<int>(q / (static_cast<long long>(G) * nc));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r0 = rb * 32 + warp * 4;
+  const int nj = L / 64;
+  const int smax = rb * 32 + 32;  // columns ≥ smax are above the diagonal for every row of this block
+  float acc[4][MAXJ][2];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) acc[r][j][0] = acc[r][j][1] = 0.f;
+  for (int hh = 0; hh < hg; ++hh) {
+    const int h = g * hg + hh;
+    const long long vrow = ((static_cast<long long>(b) * nc + c) * H + h) * L;
+    __syncthreads();
+    for (int i = threadIdx.x; i < L; i += 256) {
+      scum[i] = cum[vrow + i];
+      scol[i] = 0.f;
+    }
+    __syncthreads();
+    const long long mbase = vrow * L;  // [b,c,h] matrix base (L×L)
+    float csum[MAXJ][2];
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) csum[j][0] = csum[j][1] = 0.f;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int t = r0 + r;
+      const float ct = scum[t];
+#pragma unroll
+      for (int j = 0; j < MAXJ; ++j) {
+        const int s = 2 * lane + 64 * j;
+        if (j < nj && s < smax) {
+          const float2 dm = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dM + mbase + static_cast<long long>(t) * L + s));
+          const float2 mm = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(Mm + mbase + static_cast<long long>(t) * L + s));
+          if (s <= t) {
+            csum[j][0] += dm.x * mm.x;
+            acc[r][j][0] += dm.x * __expf(ct - scum[s]);
+          }
+          if (s + 1 <= t) {
+            csum[j][1] += dm.y * mm.y;
+            acc[r][j][1] += dm.y * __expf(ct - scum[s + 1]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) {
+      const int s = 2 * lane + 64 * j;
+      if (j < nj && s < smax) {
+        atomicAdd(&scol[s], csum[j][0]);
+        atomicAdd(&scol[s + 1], csum[j][1]);
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < smax && i < L; i += 256) atomicAdd(&dcum[vrow + i], -scol[i]);
+  }
+  const long long gbase = (((static_cast<long long>(b) * nc + c) * G + g) * L) * L;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int t = r0 + r;
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) {
+      const int s = 2 * lane + 64 * j;
+      if (j < nj)
+        *reinterpret_cast<__nv_bfloat162*>(dG + gbase + static_cast<long long>(t) * L + s) =
+            __floats2bfloat162_rn(acc[r][j][0], acc[r][j][1]);
+    }
+  }
+}
+
+// Reverse carry. One block per (b,h); threads stride over the P·N state entries.
+//   dS[c] = dHtot_{c+1} ; dcumL[b,c,h] += Σ dHtot_{c+1}·H_c·decay_c ; dHtot_c = dHy_c + decay_c·dHtot_{c+1}
+__global__ void __launch_bounds__(256) m3_state_bwd_kernel(const float* __restrict__ dHy,
+                                                            const __nv_bfloat16* __restrict__ hc,
+                                                            const float* __restrict__ cum,
+                                                            const float* __restrict__ dhlast,
+                                                            __nv_bfloat16* __restrict__ dS, float* __restrict__ dcumL,
+                                                            float* __restrict__ dh0, int Bn, int nc, int H, int PN,
+                                                            int L) {
+  __shared__ float red[8];
+  const int h = blockIdx.x % H;
+  const int b = blockIdx.x / H;
+  constexpr int MAXE = 64;  // P·N ≤ 256·64
+  float carry[MAXE];
+  const int per = (PN + 255) / 256;
+  for (int k = 0; k < per && k < MAXE; ++k) {
+    const int e = threadIdx.x + 256 * k;
+    carry[k] = (e < PN && dhlast != nullptr) ? dhlast[(static_cast<long long>(b) * H + h) * PN + e] : 0.f;
+  }
+  for (int c = nc - 1; c >= 0; --c) {
+    const long long row = (static_cast<long long>(b) * nc + c) * H + h;
+    const float d = __expf(cum[row * L + L - 1]);
+    float part = 0.f;
+    for (int k = 0; k < per && k < MAXE; ++k) {
+      const int e = threadIdx.x + 256 * k;
+      if (e < PN) {
+        const long long idx = row * PN + e;
+        dS[idx] = __float2bfloat16(carry[k]);
+        part += carry[k] * __bfloat162float(hc[idx]);
+        carry[k] = dHy[idx] + d * carry[k];
+      }
+    }
+    part = warp_sum(part);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < 8; ++w) t += red[w];
+      dcumL[row] = t * d;
+    }
+  }
+  if (dh0 != nullptr) {
+    for (int k = 0; k < per && k < MAXE; ++k) {
+      const int e = threadIdx.x + 256 * k;
+      if (e < PN) dh0[(static_cast<long long>(b) * H + h) * PN + e] = carry[k];
+    }
+  }
+}
+
+// dXw stage. One warp per (b,s,h):  dx_acc += dXw·w ; dw = Σ_p dXw·x ; dcum[t] −= dw·w ; dcumL += dw·w.
+__global__ void __launch_bounds__(256) m3_bwd_xw_kernel(const float* __restrict__ dXw, const __nv_bfloat16* __restrict__ x,
+                                                         const float* __restrict__ cum, float* __restrict__ dx_acc,
+                                                         float* __restrict__ dcum, float* __restrict__ dcumL, int Bn,
+                                                         int S, int H, int P, int L) {
+  const int nc = S / L;
+  const long long wid = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= static_cast<long long>(Bn) * S * H) return;
+  const int h = static_cast<int>(wid % H);
+  const long long bs = wid / H;
+  const int s = static_cast<int>(bs % S);
+  const int b = static_cast<int>(bs / S);
+  const int c = s / L, t = s - c * L;
+  const long long crow = (static_cast<long long>(b) * nc + c) * H + h;
+  const float w = __expf(cum[crow * L + L - 1] - cum[crow * L + t]);
+  const long long base = wid * P;
+  float dw = 0.f;
+  for (int p = 2 * lane; p < P; p += 64) {
+    const float2 g = *reinterpret_cast<const float2*>(dXw + base + p);
+    const float2 xv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + base + p));
+    float2 a = *reinterpret_cast<float2*>(dx_acc + base + p);
+    a.x += g.x * w;
+    a.y += g.y * w;
+    *reinterpret_cast<float2*>(dx_acc + base + p) = a;
+    dw += g.x * xv.x + g.y * xv.y;
+  }
+  dw = warp_sum(dw);
+  if (lane == 0) {
+    const float v = dw * w;
+    atomicAdd(&dcum[crow * L + t], -v);
+    atomicAdd(&dcumL[crow], v);
+  }
+}
+
+// Final: dcum[L−1] += dcumL ; dla = reverse-cumsum(dcum) ; dA = dla·dt ; ddt = dla·A.  One warp per (b,c,h).
+__global__ void m3_bwd_final_kernel(const float* __restrict__ dcum, const float* __restrict__ dcumL,
+                                    const float* __restrict__ A, const float* __restrict__ dt, float* __restrict__ dA,
+                                    float* __restrict__ ddt, int Bn, int S, int H, int L) {
+  const int nc = S / L;
+  const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= static_cast<long long>(Bn) * nc * H) return;
+  const int h = static_cast<int>(row % H);
+  const int c = static_cast<int>((row / H) % nc);
+  const int b = static_cast<int>(row / (static_cast<long long>(H) * nc));
+  const int per = L / 32;
+  const float* in = dcum + row * L;
+  float vals[32];
+  float run = 0.f;
+  // lane owns t in [lane·per, lane·per+per); build suffix sums inside the lane from the right
+  for (int i = per - 1; i >= 0; --i) {
+    const int t = lane * per + i;
+    float v = in[t];
+    if (t == L - 1) v += dcumL[row];
+    run += v;
+    vals[i] = run;
+  }
+  float tot = run;  // inclusive suffix over lanes to the right
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float n = __shfl_down_sync(0xffffffffu, tot, o);
+    if (lane + o < 32) tot += n;
+  }
+  const float off = tot - run;
+  const long long base = (static_cast<long long>(b) * S + static_cast<long long>(c) * L) * H + h;
+  for (int i = 0; i < per; ++i) {
+    const int t = lane * per + i;
+    const long long idx = base + static_cast<long long>(t) * H;
+    const float dla = vals[i] + off;
+    dA[idx] = dla * dt[idx];
+    ddt[idx] = dla * A[idx];
+  }
+}
+
+// fp32 → bf16 cast with optional accumulate-free copy (used for dx, dB, dC).
+__global__ void m3_cast_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long long n2) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n2;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float2 v = reinterpret_cast<const float2*>(in)[i];
+    reinterpret_cast<__nv_bfloat162*>(out)[i] = __floats2bfloat162_rn(v.x, v.y);
+  }
+}
+
+static inline int grid1d(long long n, int per_block) {
+  long long b = (n + per_block - 1) / per_block;
+  const long long cap = 148LL * 32;
+  return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace cmb
+
+#define CMB_OK() (cudaGetLastError() == cudaSuccess ? 0 : 2)
+
+extern "C" int cmb_m3_cumsum(const float* A, const float* dt, float* cum, int Bn, int S, int H, int L, void* stream) {
+  if (L % 32 || L > 1024 || S % L) return 1;
+  const long long rows = static_cast<long long>(Bn) * (S / L) * H;
+  cmb::m3_cumsum_kernel<<<static_cast<int>((rows * 32 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(A, dt, cum, Bn, S, H, L);
+  return CMB_OK();
+}
+extern "C" int cmb_m3_xw(const void* x, const float* cum, void* xw, int Bn, int S, int H, int P, int L, void* stream) {
+  if (P % 2) return 1;
+  const long long n2 = static_cast<long long>(Bn) * S * H * (P / 2);
+  cmb::m3_xw_kernel<<<cmb::grid1d(n2, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), cum, static_cast<__nv_bfloat16*>(xw), Bn, S, H, P, L);
+  return CMB_OK();
+}
+extern "C" int cmb_m3_state_pass(const float* sloc, const float* cum, const float* h0, void* hc, float* hlast, int Bn,
+                                 int nc, int H, int PN, int L, void* stream) {
+  const long long n = static_cast<long long>(Bn) * H * PN;
+  cmb::m3_state_pass_kernel<<<cmb::grid1d(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      sloc, cum, h0, static_cast<__nv_bfloat16*>(hc), hlast, Bn, nc, H, PN, L);
+  return CMB_OK();
+}
+extern "C" int cmb_m3_finalize_fwd(const float* Y, const void* x, const void* z, const float* D, void* ypre, void* out,
+                                   int Bn, int S, int H, int P, long long zs_b, long long zs_s, long long zs_h,
+                                   void* stream) {
+  if (P % 2) return 1;
+  const long long n2 = static_cast<long long>(Bn) * S * H * (P / 2);
+  cmb::m3_finalize_fwd_kernel<<<cmb::grid1d(n2, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      Y, static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(z), D, static_cast<__nv_bfloat16*>(ypre),
+      static_cast<__nv_bfloat16*>(out), Bn, S, H, P, zs_b, zs_s, zs_h);
+  return CMB_OK();
+}
+extern "C" int cmb_m3_bwd_pre(const void* dout, const void* z, const void* ypre, const void* x, const float* D,
+                              const float* cum, void* dy, void* dz, void* dye, float* dx_acc, float* dcum, float* dD,
+                              int Bn, int S, int H, int P, int L, long long zs_b, long long zs_s, long long zs_h,
+                              void* stream) {
+  if (P % 2) return 1;
+  const long long blocks = static_cast<long long>(Bn) * ((S + 7) / 8) * H;
+  if (blocks > 0x7fffffffLL) return 3;
+  using bf = __nv_bfloat16;
+  cmb::m3_bwd_pre_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const bf*>(dout), static_cast<const bf*>(z), static_cast<const bf*>(ypre), static_cast<const bf*>(x), D,
+      cum, static_cast<bf*>(dy), static_cast<bf*>(dz), static_cast<bf*>(dye), dx_acc, dcum, dD, Bn, S, H, P, L, zs_b, zs_s,
+      zs_h);
+  return CMB_OK();
+}
+extern "C" int cmb_m3_bwd_q(const void* dM, const void* Mm, const float* cum, float* dcum, void* dG, int Bn, int nc, int H,
+                            int G, int L, void* stream) {
+  if (L % 64 || L > 512 || H % G) return 1;
+  const long long blocks = static_cast<long long>(Bn) * nc * G * (L / 32);
+  if (blocks > 0x7fffffffLL) return 3;
+  using bf = __nv_bfloat16;
+  cmb::m3_bwd_q_kernel<8><<<static_cast<int>(blocks), 256, 2 * L * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const bf*>(dM), static_cast<const bf*>(Mm), cum, dcum, static_cast<bf*>(dG), Bn, nc, H, G, L);
+  return CMB_OK();
+}
+extern "C" int cmb_m3_state_bwd(const float* dHy, const void* hc, const float* cum, const float* dhlast, void* dS,
+                                float* dcumL, float* dh0, int Bn, int nc, int H, int PN, int L, void* stream) {
+  if (PN > 256 * 64) return 1;
+  using bf = __nv_bfloat16;
+  cmb::m3_state_bwd_kernel<<<Bn * H, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      dHy, static_cast<const bf*>(hc), cum, dhlast, static_cast<bf*>(dS), dcumL, dh0, Bn, nc, H, PN, L);
+  return CMB_OK();
+}
+extern "C" int cmb_m3_bwd_xw(const float* dXw, const void* x, const float* cum, float* dx_acc, float* dcum, float* dcumL,
+                             int Bn, int S, int H, int P, int L, void* stream) {
+  const long long warps = static_cast<long long>(Bn) * S * H;
+  cmb::m3_bwd_xw_kernel<<<static_cast<int>((warps * 32 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      dXw, static_cast<const __nv_bfloat16*>(x), cum, dx_acc, dcum, dcumL, Bn, S, H, P, L);
+  return CMB_OK();
+}
+extern "C" int cmb_m3_bwd_final(const float* dcum, const float* dcumL, const float* A, const float* dt, float* dA,
+                                float* ddt, int Bn, int S, int H, int L, void* stream) {
+  if (L % 32 || L > 1024) return 1;
+  const long long rows = static_cast<long long>(Bn) * (S / L) * H;
+  cmb::m3_bwd_final_kernel<<<static_cast<int>((rows * 32 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      dcum, dcumL, A, dt, dA, ddt, Bn, S, H, L);
+  return CMB_OK();
+}
+extern "C" int cmb_cast_f32_bf16(const float* in, void* out, long long n, void* stream) {
+  if (n % 2) return 1;
+  cmb::m3_cast_bf16_kernel<<<cmb::grid1d(n / 2, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      in, static_cast<__nv_bfloat16*>(out), n / 2);
+  return CMB_OK();
+}

@@ -16,6 +16,7 @@ from . import _backend as B
 OUT_F32 = 1
 ACCUMULATE = 2
 EPI_DECAY_MASK = 4
+EPI_ROW_EXP = 8
 
 
 def _ok(t: torch.Tensor) -> bool:
@@ -70,11 +71,11 @@ def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int,
     pitches ``ld*`` and per-operand element strides over the three batch dims ``nb = (n2, n3, n4)``.
     ``a_div2``/``b_div2`` let ``div`` consecutive dim-2 problems share one operand slice (the operand then has
     ``n2 // div`` slices).  With ``row_vec``/``col_vec`` (fp32) the epilogue writes
-    ``acc · exp(row_vec[t] − col_vec[s]) · [s ≤ t]``."""
+    ``acc · exp(row_vec[t] − col_vec[s]) · [s ≤ t]``; with ``row_vec`` alone, ``acc · exp(row_vec[t])``."""
     lib = B.load_library()
     flags = (OUT_F32 if out.dtype == torch.float32 else 0) | (ACCUMULATE if accumulate else 0)
     if row_vec is not None:
-        flags |= EPI_DECAY_MASK
+        flags |= EPI_DECAY_MASK if col_vec is not None else EPI_ROW_EXP
     ip = (ctypes.c_int * 9)(M, N, K, int(a_mn), int(b_mn), flags, a_div2, b_div2, max_ctas)
     lp = (ctypes.c_longlong * 18)(lda, ldb, ldc, *nb, *sA, *sB, *sC, *sv)
     st = B.status_buffer(a.device)
