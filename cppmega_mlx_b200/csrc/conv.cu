@@ -1,0 +1,183 @@
+// Causal depthwise conv1d (+bias) followed by SiLU over channel-last activations, forward and backward.
+//
+//   pre[b,s,c] = bias[c] + Σ_k w[c,k] · in[b, s−K+1+k, c]        (zero left padding)
+//   y          = silu(pre)
+//
+// The input is a column slice of a wider row-major matrix (row pitch `ld_in`, first channel `c_off`),
+// e.g. the [x|B|C] part of Mamba3's packed projection or the [q|k|v] part of M2RNN's, so no split copy is
+// needed; the output goes to two dense tensors (channels [0,C1) and [C1,C)).  Each thread owns one
+// bf16 channel pair and a run of TS consecutive tokens, sliding a K-tap window through registers.
+// Math parity: cppmega_mlx/nn/mamba3.py:322 (conv) followed by nn.silu at :715; weights are [C,K,1].
+#include "sm100.cuh"
+
+namespace cmb {
+
+constexpr int CONV_TS = 8;
+constexpr int CONV_MAXK = 8;
+
+__device__ __forceinline__ float2 ld2(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+
+__global__ void __launch_bounds__(256) conv_silu_fwd_kernel(const __nv_bfloat16* __restrict__ in, long long ld_in,
+                                                             int c_off, const __nv_bfloat16* __restrict__ w,
+                                                             const __nv_bfloat16* __restrict__ bias,
+                                                             __nv_bfloat16* __restrict__ out1,
+                                                             __nv_bfloat16* __restrict__ out2, int Bn, int S, int C,
+                                                             int C1, int K) {
+  const int cp = blockIdx.x * 32 + (threadIdx.x & 31);  // channel pair
+  const int c = cp * 2;
+  const long long tile = blockIdx.y * 8LL + (threadIdx.x >> 5);
+  const int tiles_per_seq = (S + CONV_TS - 1) / CONV_TS;
+  if (c >= C || tile >= static_cast<long long>(Bn) * tiles_per_seq) return;
+  const int b = static_cast<int>(tile / tiles_per_seq);
+  const int s0 = static_cast<int>(tile % tiles_per_seq) * CONV_TS;
+  float2 wk[CONV_MAXK];
+  for (int k = 0; k < K; ++k) wk[k] = make_float2(__bfloat162float(w[c * K + k]), __bfloat162float(w[(c + 1) * K + k]));
+  const float2 bs = bias != nullptr ? ld2(bias + c) : make_float2(0.f, 0.f);
+  const __nv_bfloat16* ib = in + static_cast<long long>(b) * S * ld_in + c_off + c;
+  float2 win[CONV_MAXK];  // win[k] = in[s-K+1+k]
+  for (int k = 0; k < K - 1; ++k) {
+    const int s = s0 - (K - 1) + k;
+    win[k + 1] = s >= 0 ? ld2(ib + s * ld_in) : make_float2(0.f, 0.f);
+  }
+  for (int i = 0; i < CONV_TS; ++i) {
+    const int s = s0 + i;
+    if (s >= S) break;
+    for (int k = 0; k < K - 1; ++k) win[k] = win[k + 1];
+    win[K - 1] = ld2(ib + s * ld_in);
+    float2 acc = bs;
+    for (int k = 0; k < K; ++k) {
+      acc.x += wk[k].x * win[k].x;
+      acc.y += wk[k].y * win[k].y;
+    }
+    const float y0 = acc.x / (1.f + __expf(-acc.x)), y1 = acc.y / (1.f + __expf(-acc.y));
+    __nv_bfloat16* dst = c < C1 ? out1 + (static_cast<long long>(b) * S + s) * C1 + c
+                                : out2 + (static_cast<long long>(b) * S + s) * (C - C1) + (c - C1);
+    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(y0, y1);
+  }
+}
+
+// Backward. dy comes from the two dense gradient tensors; din is written with row pitch `ld_din` (so it can
+// land directly inside the gradient of the packed projection);
+// dw [C,K] and dbias [C] are fp32 and must be zeroed by the caller (block-reduced atomics).
+__global__ void __launch_bounds__(256) conv_silu_bwd_kernel(const __nv_bfloat16* __restrict__ in, long long ld_in,
+                                                             int c_off, const __nv_bfloat16* __restrict__ w,
+                                                             const __nv_bfloat16* __restrict__ bias,
+                                                             const __nv_bfloat16* __restrict__ dy1,
+                                                             const __nv_bfloat16* __restrict__ dy2,
+                                                             __nv_bfloat16* __restrict__ din, long long ld_din,
+                                                             float* __restrict__ dw, float* __restrict__ dbias, int Bn,
+                                                             int S, int C, int C1, int K) {
+  __shared__ float red[8][32][2 * (CONV_MAXK + 1)];
+  const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
+  const int cp = blockIdx.x * 32 + lane;
+  const int c = cp * 2;
+  const long long tile = blockIdx.y * 8LL + wrp;
+  const int tiles_per_seq = (S + CONV_TS - 1) / CONV_TS;
+  const bool active = c < C && tile < static_cast<long long>(Bn) * tiles_per_seq;
+  float2 dwk[CONV_MAXK];
+  float2 db = make_float2(0.f, 0.f);
+  for (int k = 0; k < CONV_MAXK; ++k) dwk[k] = make_float2(0.f, 0.f);
+  if (active) {
+    const int b = static_cast<int>(tile / tiles_per_seq);
+    const int s0 = static_cast<int>(tile % tiles_per_seq) * CONV_TS;
+    float2 wk[CONV_MAXK];
+    for (int k = 0; k < K; ++k) wk[k] = make_float2(__bfloat162float(w[c * K + k]), __bfloat162float(w[(c + 1) * K + k]));
+    const float2 bs = bias != nullptr ? ld2(bias + c) : make_float2(0.f, 0.f);
+    const __nv_bfloat16* ib = in + static_cast<long long>(b) * S * ld_in + c_off + c;
+    const bool first = c < C1;
+    const __nv_bfloat16* gb = first ? dy1 + static_cast<long long>(b) * S * C1 + c
+                                    : dy2 + static_cast<long long>(b) * S * (C - C1) + (c - C1);
+    const long long gld = first ? C1 : (C - C1);
+    // inputs s0-(K-1) .. s0+TS+K-2 and dpre for s0 .. s0+TS+K-2
+    constexpr int NI = CONV_TS + 2 * (CONV_MAXK - 1);
+    float2 xin[NI];
+    const int ni = CONV_TS + 2 * (K - 1);
+    for (int j = 0; j < ni; ++j) {
+      const int s = s0 - (K - 1) + j;
+      xin[j] = (s >= 0 && s < S) ? ld2(ib + s * ld_in) : make_float2(0.f, 0.f);
+    }
+    constexpr int ND = CONV_TS + CONV_MAXK - 1;
+    float2 dpre[ND];
+    const int nd = CONV_TS + K - 1;
+    for (int j = 0; j < nd; ++j) {
+      const int s = s0 + j;
+      if (s < S) {
+        float2 acc = bs;
+        for (int k = 0; k < K; ++k) {  // pre[s] uses in[s-K+1+k] = xin[j+k]
+          acc.x += wk[k].x * xin[j + k].x;
+          acc.y += wk[k].y * xin[j + k].y;
+        }
+        const float2 g = ld2(gb + s * gld);
+        const float sg0 = 1.f / (1.f + __expf(-acc.x)), sg1 = 1.f / (1.f + __expf(-acc.y));
+        dpre[j] = make_float2(g.x * sg0 * (1.f + acc.x * (1.f - sg0)), g.y * sg1 * (1.f + acc.y * (1.f - sg1)));
+      } else {
+        dpre[j] = make_float2(0.f, 0.f);
+      }
+    }
+    for (int i = 0; i < CONV_TS; ++i) {
+      const int s = s0 + i;
+      if (s >= S) break;
+      // din[s] = Σ_k w[k] · dpre[s + K-1-k]
+      float2 acc = make_float2(0.f, 0.f);
+      for (int k = 0; k < K; ++k) {
+        acc.x += wk[k].x * dpre[i + K - 1 - k].x;
+        acc.y += wk[k].y * dpre[i + K - 1 - k].y;
+      }
+      *reinterpret_cast<__nv_bfloat162*>(din + (static_cast<long long>(b) * S + s) * ld_din + c) = __floats2bfloat162_rn(acc.x, acc.y);
+      // this thread's own dpre positions feed dw / dbias exactly once
+      db.x += dpre[i].x;
+      db.y += dpre[i].y;
+      for (int k = 0; k < K; ++k) {
+        dwk[k].x += dpre[i].x * xin[i + k].x;
+        dwk[k].y += dpre[i].y * xin[i + k].y;
+      }
+    }
+  }
+  for (int k = 0; k < K; ++k) {
+    red[wrp][lane][2 * k] = dwk[k].x;
+    red[wrp][lane][2 * k + 1] = dwk[k].y;
+  }
+  red[wrp][lane][2 * K] = db.x;
+  red[wrp][lane][2 * K + 1] = db.y;
+  __syncthreads();
+  if (wrp == 0 && c < C) {
+    for (int j = 0; j < 2 * (K + 1); ++j) {
+      float t = 0.f;
+      for (int q = 0; q < 8; ++q) t += red[q][lane][j];
+      const int which = j & 1;
+      if (j < 2 * K)
+        atomicAdd(&dw[(c + which) * K + (j >> 1)], t);
+      else
+        atomicAdd(&dbias[c + which], t);
+    }
+  }
+}
+
+}  // namespace cmb
+
+extern "C" int cmb_conv_silu_fwd(const void* in, long long ld_in, int c_off, const void* w, const void* bias, void* out1,
+                                 void* out2, int Bn, int S, int C, int C1, int K, void* stream) {
+  if (C % 2 || C1 % 2 || c_off % 2 || ld_in % 2 || K > cmb::CONV_MAXK || K < 1) return 1;
+  using bf = __nv_bfloat16;
+  const long long tiles = static_cast<long long>(Bn) * ((S + cmb::CONV_TS - 1) / cmb::CONV_TS);
+  dim3 grid((C / 2 + 31) / 32, static_cast<unsigned>((tiles + 7) / 8));
+  cmb::conv_silu_fwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const bf*>(in), ld_in, c_off, static_cast<const bf*>(w), static_cast<const bf*>(bias),
+      static_cast<bf*>(out1), static_cast<bf*>(out2), Bn, S, C, C1, K);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_conv_silu_bwd(const void* in, long long ld_in, int c_off, const void* w, const void* bias,
+                                 const void* dy1, const void* dy2, void* din, long long ld_din, float* dw, float* dbias, int Bn,
+                                 int S, int C, int C1, int K, void* stream) {
+  if (C % 2 || C1 % 2 || c_off % 2 || ld_in % 2 || K > cmb::CONV_MAXK || K < 1) return 1;
+  using bf = __nv_bfloat16;
+  const long long tiles = static_cast<long long>(Bn) * ((S + cmb::CONV_TS - 1) / cmb::CONV_TS);
+  dim3 grid((C / 2 + 31) / 32, static_cast<unsigned>((tiles + 7) / 8));
+  cmb::conv_silu_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const bf*>(in), ld_in, c_off, static_cast<const bf*>(w), static_cast<const bf*>(bias),
+      static_cast<const bf*>(dy1), static_cast<const bf*>(dy2), static_cast<bf*>(din), ld_din, dw, dbias, Bn, S, C, C1, K);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}

@@ -209,26 +209,33 @@ class Mamba3Block(nn.Module):
             raise ValueError("pass either h0 or cache, not both")
         c = self.config
         b, s, _ = hidden_states.shape
-        z, x, Bm, Cm, dd_dt, dd_A, trap, angles = self.split_in_proj(self.in_proj(hidden_states))
-        xBC_raw = torch.cat([x, Bm, Cm], dim=-1)
+        proj = self.in_proj(hidden_states)
+        if proj.shape[-1] != self.dims.total:
+            raise ValueError(f"projected last dim must be {self.dims.total}, got {tuple(proj.shape)}")
         prefix = cache.conv if (cache is not None and cache.conv is not None) else None
-        xBC = F.silu(causal_depthwise_conv1d(xBC_raw, self.conv_weight, self.conv_bias, prefix=prefix))
-        x, Bm, Cm = torch.split(xBC, [c.d_inner, self.dims.d_bc, self.dims.d_bc], dim=-1)
+        conv_ch = c.d_inner + 2 * self.dims.d_bc
+        # [z | x B C | dd_dt dd_A trap angles]: one node splits the packed projection and runs conv + SiLU
+        z, x, BC, tail = ops.packed_split_conv_silu(proj, c.d_inner, conv_ch, c.d_inner, self.conv_weight, self.conv_bias,
+                                                    prefix=prefix)
+        xBC_raw = proj[..., c.d_inner:c.d_inner + conv_ch]
+        Bm, Cm = BC[..., :self.dims.d_bc], BC[..., self.dims.d_bc:]
+        dd_dt, dd_A, trap, angles = torch.split(tail.float(), [c.nheads, c.nheads, c.nheads, self.dims.num_rope_angles], dim=-1)
         x = x.reshape(b, s, c.nheads, c.headdim)
         z = z.reshape(b, s, c.nheads, c.headdim)
         r = c.effective_mimo_rank
         B_mimo, C_mimo = self.transform_bc(Bm.reshape(b, s, r, c.ngroups, c.d_state), Cm.reshape(b, s, r, c.ngroups, c.d_state))
-        Bg, Cg = B_mimo.mean(2), C_mimo.mean(2)  # [B,S,G,N]
-        dt = F.softplus(dd_dt.float() + self.dt_bias.float())
+        Bg, Cg = (B_mimo.mean(2), C_mimo.mean(2)) if r > 1 else (B_mimo[:, :, 0], C_mimo[:, :, 0])  # [B,S,G,N]
+        dt = F.softplus(dd_dt + self.dt_bias.float())
         # The trapezoid looks one step ahead; across a cache boundary that future step is unknown, as in the reference.
-        Bg = Bg * heads_to_group_scale(compute_trapezoidal_scale(dt, trap.float()), c.ngroups)[..., None].to(Bg.dtype)
-        ang = angles.float()[:, :, None, :].expand(b, s, c.nheads, self.dims.num_rope_angles)
-        ang_cum = torch.cumsum(ang * dt[..., None], dim=1)
+        Bg = Bg * heads_to_group_scale(compute_trapezoidal_scale(dt, trap), c.ngroups)[..., None].to(Bg.dtype)
+        # Only the first `ngroups` heads' phases rotate B and C; the full per-head table is needed for the cache only.
+        nh_ang = c.nheads if return_cache else c.ngroups
+        ang_cum = torch.cumsum((angles[:, :, None, :] * dt[:, :, :nh_ang, None]).transpose(1, 3), dim=-1).transpose(1, 3)
         if cache is not None:
-            ang_cum = ang_cum + cache.angle_dt[:, None].float()
+            ang_cum = ang_cum + cache.angle_dt[:, None, :nh_ang].float()
         Bg = apply_rope_on_state_dim(Bg, ang_cum)
         Cg = apply_rope_on_state_dim(Cg, ang_cum)
-        A = torch.minimum(-F.softplus(dd_A.float()), torch.tensor(-c.A_floor, device=dd_A.device))
+        A = torch.clamp(-F.softplus(dd_A), max=-c.A_floor)
         state0 = cache.ssm if cache is not None else h0
         if state0 is not None and tuple(state0.shape) != (b, c.nheads, c.headdim, c.d_state):
             raise ValueError(f"h0 must have shape {(b, c.nheads, c.headdim, c.d_state)}, got {tuple(state0.shape)}")
