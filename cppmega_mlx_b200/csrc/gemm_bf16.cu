@@ -34,7 +34,18 @@ constexpr int GEMM_THREADS = 64 + 32 * GEMM_EPI_WARPS;
 constexpr int GEMM_GROUP_M = 16;
 constexpr int GEMM_CBOX_BYTES = 32 * 128;  // one epilogue warp's staging box: 32 rows × 128 bytes
 
-enum : int { GEMM_OUT_F32 = 1, GEMM_ACCUMULATE = 2, GEMM_EPI_DECAY_MASK = 4, GEMM_EPI_ROW_EXP = 8 };
+enum : int {
+  GEMM_OUT_F32 = 1,
+  GEMM_ACCUMULATE = 2,
+  GEMM_EPI_DECAY_MASK = 4,   // acc · exp(r[t] − c[s]) · [s ≤ t]
+  GEMM_EPI_ROW_EXP = 8,      // acc · exp(r[t])
+  GEMM_CAUSAL_SKIP = 16,     // tiles entirely above the diagonal (n0 ≥ m0 + BM) are not computed nor written
+  GEMM_K_UPPER = 32,         // contraction restricted to k < m0 + BM   (keys up to the query tile)
+  GEMM_K_LOWER = 64,         // contraction restricted to k ≥ m0        (queries from the key tile on)
+  GEMM_EPI_SOFTMAX_STATS = 128,  // no C; per (row, tile half): running max / Σexp of masked scale·acc
+  GEMM_EPI_EXP_MASK = 256,       // P = [mask] · exp(scale·acc − r[t])
+  GEMM_EPI_DS = 512,             // dS = aux · (acc − r[t]) · scale   (aux has C's layout, bf16)
+};
 
 struct GemmParams {
   int M, N, K;
@@ -44,6 +55,13 @@ struct GemmParams {
   const float* row_vec;
   const float* col_vec;
   long long sv2, sv3, sv4;  // element strides of the epilogue vectors over the batch dims
+  const __nv_bfloat16* aux;  // DS epilogue: matrix with C's geometry
+  long long ldc, sC2, sC3, sC4;
+  const unsigned* mask;      // attention epilogues: bit s of row t allows key s; nullptr = causal only
+  long long mask_sb;         // words between batches (dim 4)
+  int mask_words;            // words per row
+  float scale;
+  float* stats;              // SOFTMAX_STATS output: float2 per (problem, row, tile_n, half)
   int* status;
 };
 
@@ -102,6 +120,14 @@ __device__ __forceinline__ TileCoord tile_coords(int t, int num_m, int num_n, in
   c.tm = first_m + r % gsz;
   c.tn = r / gsz;
   return c;
+}
+
+__device__ __forceinline__ bool tile_skipped(int flags, int m0, int n0) {
+  return (flags & GEMM_CAUSAL_SKIP) && n0 >= m0 + GEMM_BM;
+}
+__device__ __forceinline__ void k_range(int flags, int m0, int num_kb, int& kb0, int& kb1) {
+  kb0 = (flags & GEMM_K_LOWER) ? m0 / GEMM_BK : 0;
+  kb1 = (flags & GEMM_K_UPPER) ? min(num_kb, (m0 + GEMM_BM + GEMM_BK - 1) / GEMM_BK) : num_kb;
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -163,7 +189,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3);
         const int m0 = tc.tm * GEMM_BM, n0 = tc.tn * BN;
         const int a2 = tc.i2 / p.a_div2, b2 = tc.i2 / p.b_div2;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        if (tile_skipped(p.flags, m0, n0)) continue;
+        int kb0, kb1;
+        k_range(p.flags, m0, num_kb, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) {
             ok = false;
             break;
@@ -201,13 +230,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3);
+        const int m0 = tc.tm * GEMM_BM;
+        if (tile_skipped(p.flags, m0, tc.tn * BN)) continue;
+        int kb0, kb1;
+        k_range(p.flags, m0, num_kb, kb0, kb1);
         const int buf = local & 1;
         const uint32_t aphase = (local >> 1) & 1;
+        ++local;
         if (!mbar_wait(&tempty_bar[buf], aphase ^ 1, abort_flag, status, ST_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, ST_TIMEOUT_FULL)) {
             ok = false;
             break;
@@ -221,7 +256,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                         : make_smem_desc_sw128(sa + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc_sw128(sb + k * 2048, GEMM_BK * 128, 1024)
                                         : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-            umma_f16(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16(tmem_d, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) {
@@ -241,32 +276,105 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool accum = (p.flags & GEMM_ACCUMULATE) != 0;
     const bool decay = (p.flags & GEMM_EPI_DECAY_MASK) != 0;
     const bool rowexp = (p.flags & GEMM_EPI_ROW_EXP) != 0;
+    const bool e_stats = (p.flags & GEMM_EPI_SOFTMAX_STATS) != 0;
+    const bool e_expm = (p.flags & GEMM_EPI_EXP_MASK) != 0;
+    const bool e_ds = (p.flags & GEMM_EPI_DS) != 0;
+    const bool attn = e_stats || e_expm || e_ds;
     uint8_t* cbox = csmem + ew * GEMM_CBOX_BYTES;
     int local = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3);
+      if (tile_skipped(p.flags, tc.tm * GEMM_BM, tc.tn * BN)) continue;
       const int buf = local & 1;
       const uint32_t aphase = (local >> 1) & 1;
+      ++local;
       if (!mbar_wait(&tfull_bar[buf], aphase, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
-      const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3);
       const int row0 = tc.tm * GEMM_BM + quarter * 32;
       const int row = row0 + lane;
       const int ncol0 = tc.tn * BN + half * (BN / 2);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + half * (BN / 2);
       float rv = 0.f;
       const float* colv = nullptr;
-      if (decay || rowexp) {
+      if (decay || rowexp || e_expm || e_ds) {
         const long long voff = tc.i2 * p.sv2 + tc.i3 * p.sv3 + tc.i4 * p.sv4;
         rv = row < p.M ? p.row_vec[voff + row] : 0.f;
         if (decay) colv = p.col_vec + voff;
         if (rowexp) rv = __expf(rv);
       }
+      const unsigned* mrow = nullptr;
+      if (attn && p.mask != nullptr && row < p.M)
+        mrow = p.mask + tc.i4 * p.mask_sb + static_cast<long long>(row) * p.mask_words;
+      const __nv_bfloat16* auxrow = nullptr;
+      if (e_ds && row < p.M)
+        auxrow = p.aux + tc.i2 * p.sC2 + tc.i3 * p.sC3 + tc.i4 * p.sC4 + static_cast<long long>(row) * p.ldc;
+      float run_m = -INFINITY, run_l = 0.f;
 #pragma unroll 1
       for (int c = 0; c < (BN / 2) / 32; ++c) {
         uint32_t r[32];
         tmem_ld_x32(taddr + c * 32, r);
         tmem_wait_ld();
         const int col0 = ncol0 + c * 32;
+        if (attn) {
+          // keys this row may see inside the 32-column chunk: mask word ∧ causal ∧ in range
+          unsigned bits = 0u;
+          if (row < p.M && col0 < p.N) {
+            bits = mrow != nullptr ? mrow[col0 >> 5] : 0xffffffffu;
+            const int lim = row - col0;  // columns j ≤ lim are causal
+            if (lim < 0) bits = 0u;
+            else if (lim < 31) bits &= (2u << lim) - 1u;
+            const int rem = p.N - col0;
+            if (rem < 32) bits &= (1u << rem) - 1u;
+          }
+          if (e_stats) {
+            float cm = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if ((bits >> j) & 1u) cm = fmaxf(cm, __uint_as_float(r[j]) * p.scale);
+            if (cm > -INFINITY) {
+              const float nm = fmaxf(run_m, cm);
+              float acc = 0.f;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if ((bits >> j) & 1u) acc += __expf(__uint_as_float(r[j]) * p.scale - nm);
+              run_l = run_l * __expf(run_m - nm) + acc;
+              run_m = nm;
+            }
+            continue;
+          }
+          if (e_expm) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float v = ((bits >> j) & 1u) ? __expf(__uint_as_float(r[j]) * p.scale - rv) : 0.f;
+              r[j] = __float_as_uint(v);
+            }
+          } else {  // e_ds
+            uint32_t pw[16];
+            if (auxrow != nullptr && col0 + 32 <= p.N) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 v = *reinterpret_cast<const uint4*>(auxrow + col0 + 8 * q);
+                pw[4 * q] = v.x; pw[4 * q + 1] = v.y; pw[4 * q + 2] = v.z; pw[4 * q + 3] = v.w;
+              }
+            } else {
+#pragma unroll
+              for (int q = 0; q < 16; ++q) {
+                float lo = 0.f, hi = 0.f;
+                if (auxrow != nullptr && col0 + 2 * q < p.N) lo = __bfloat162float(auxrow[col0 + 2 * q]);
+                if (auxrow != nullptr && col0 + 2 * q + 1 < p.N) hi = __bfloat162float(auxrow[col0 + 2 * q + 1]);
+                pw[q] = pack_bf16x2(lo, hi);
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+              const float2 pp = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pw[q]));
+              const float d0 = ((bits >> (2 * q)) & 1u) ? pp.x * (__uint_as_float(r[2 * q]) - rv) * p.scale : 0.f;
+              const float d1 = ((bits >> (2 * q + 1)) & 1u) ? pp.y * (__uint_as_float(r[2 * q + 1]) - rv) * p.scale : 0.f;
+              r[2 * q] = __float_as_uint(d0);
+              r[2 * q + 1] = __float_as_uint(d1);
+            }
+          }
+        }
         if (decay) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -318,6 +426,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tma_store_commit();
           }
         }
+      }
+      if (e_stats && row < p.M) {
+        const long long prob = (static_cast<long long>(tc.i4) * p.nb3 + tc.i3) * p.nb2 + tc.i2;
+        float2* dst = reinterpret_cast<float2*>(p.stats) + (prob * p.M + row) * (2 * num_n) + tc.tn * 2 + half;
+        *dst = make_float2(run_m, run_l);
       }
       tc_fence_before();
       __syncwarp();
@@ -443,6 +556,12 @@ struct GemmArgs {
   const float* row_vec;
   const float* col_vec;
   int64_t sv[3];
+  const void* aux;
+  const unsigned* mask;
+  int64_t mask_sb;
+  int mask_words;
+  float scale;
+  float* stats;
   int* status;
   int max_ctas;
   cudaStream_t stream;
@@ -467,8 +586,12 @@ static int launch_gemm(const GemmArgs& g) {
     rc = make_tmap_5d(&tmB, g.B, 2, g.N, g.K, g.ldb, nbB, g.sB, BN, cmb::GEMM_BK);
   if (rc) return rc + 10000;
   const bool f32 = (g.flags & cmb::GEMM_OUT_F32) != 0;
-  rc = make_tmap_5d(&tmC, g.C, f32 ? 4 : 2, g.M, g.N, g.ldc, g.nb, g.sC, 32, f32 ? 32 : 64);
-  if (rc) return rc + 20000;
+  if (g.flags & cmb::GEMM_EPI_SOFTMAX_STATS) {
+    tmC = tmA;  // no matrix output in this mode; the map is never used
+  } else {
+    rc = make_tmap_5d(&tmC, g.C, f32 ? 4 : 2, g.M, g.N, g.ldc, g.nb, g.sC, 32, f32 ? 32 : 64);
+    if (rc) return rc + 20000;
+  }
   auto kern = cmb::gemm_bf16_kernel<BN, A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -488,6 +611,10 @@ static int launch_gemm(const GemmArgs& g) {
   p.flags = g.flags;
   p.row_vec = g.row_vec; p.col_vec = g.col_vec;
   p.sv2 = g.sv[0]; p.sv3 = g.sv[1]; p.sv4 = g.sv[2];
+  p.aux = static_cast<const __nv_bfloat16*>(g.aux);
+  p.ldc = g.ldc; p.sC2 = g.sC[0]; p.sC3 = g.sC[1]; p.sC4 = g.sC[2];
+  p.mask = g.mask; p.mask_sb = g.mask_sb; p.mask_words = g.mask_words;
+  p.scale = g.scale; p.stats = g.stats;
   p.status = g.status;
   kern<<<grid, cmb::GEMM_THREADS, Cfg::SMEM_BYTES, g.stream>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 104;
@@ -529,22 +656,29 @@ extern "C" int cmb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   return cmb_host::dispatch(g, a_mn_major, b_mn_major);
 }
 
-// Batched form. `ip` = {M, N, K, a_mn, b_mn, flags, a_div2, b_div2, max_ctas}; `lp` = {lda, ldb, ldc, nb2, nb3, nb4,
-// sA2, sA3, sA4, sB2, sB3, sB4, sC2, sC3, sC4, sv2, sv3, sv4} (element counts / strides). flags&4 selects the
-// decay-mask epilogue, which reads fp32 `row_vec[batch_off + t]` and `col_vec[batch_off + s]`; flags&8 the row-exp one.
+// Batched form. `ip` = {M, N, K, a_mn, b_mn, flags, a_div2, b_div2, max_ctas, mask_words}; `lp` = {lda, ldb, ldc, nb2,
+// nb3, nb4, sA2, sA3, sA4, sB2, sB3, sB4, sC2, sC3, sC4, sv2, sv3, sv4, mask_sb} (element counts / strides).
+// `pp` = {row_vec, col_vec, aux, mask, stats} device pointers (any may be null). Flags select the epilogue, see the
+// enum at the top of this file.
 extern "C" int cmb_gemm_bf16_batched(const void* A, const void* B, void* C, const int* ip, const long long* lp,
-                                     const float* row_vec, const float* col_vec, int* status, void* stream) {
+                                     const void* const* pp, float scale, int* status, void* stream) {
   cmb_host::GemmArgs g{};
   g.A = A; g.B = B; g.C = C; g.M = ip[0]; g.N = ip[1]; g.K = ip[2];
-  g.flags = ip[5]; g.a_div2 = ip[6]; g.b_div2 = ip[7]; g.max_ctas = ip[8];
+  g.flags = ip[5]; g.a_div2 = ip[6]; g.b_div2 = ip[7]; g.max_ctas = ip[8]; g.mask_words = ip[9];
   g.lda = lp[0]; g.ldb = lp[1]; g.ldc = lp[2];
   for (int i = 0; i < 3; ++i) {
     g.nb[i] = static_cast<uint64_t>(lp[3 + i]);
     g.sA[i] = lp[6 + i]; g.sB[i] = lp[9 + i]; g.sC[i] = lp[12 + i]; g.sv[i] = lp[15 + i];
   }
-  g.row_vec = row_vec; g.col_vec = col_vec;
+  g.mask_sb = lp[18];
+  g.row_vec = static_cast<const float*>(pp[0]); g.col_vec = static_cast<const float*>(pp[1]);
+  g.aux = pp[2]; g.mask = static_cast<const unsigned*>(pp[3]); g.stats = static_cast<float*>(const_cast<void*>(pp[4]));
+  g.scale = scale;
   g.status = status; g.stream = static_cast<cudaStream_t>(stream);
-  if ((g.flags & cmb::GEMM_EPI_DECAY_MASK) && (row_vec == nullptr || col_vec == nullptr)) return 108;
-  if ((g.flags & cmb::GEMM_EPI_ROW_EXP) && row_vec == nullptr) return 108;
+  const int f = g.flags;
+  if ((f & cmb::GEMM_EPI_DECAY_MASK) && (g.row_vec == nullptr || g.col_vec == nullptr)) return 108;
+  if ((f & (cmb::GEMM_EPI_ROW_EXP | cmb::GEMM_EPI_EXP_MASK | cmb::GEMM_EPI_DS)) && g.row_vec == nullptr) return 108;
+  if ((f & cmb::GEMM_EPI_DS) && g.aux == nullptr) return 108;
+  if ((f & cmb::GEMM_EPI_SOFTMAX_STATS) && g.stats == nullptr) return 108;
   return cmb_host::dispatch(g, ip[3], ip[4]);
 }

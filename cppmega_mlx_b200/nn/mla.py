@@ -202,14 +202,27 @@ class MLAAttention(nn.Module):
         if kv_cache is not None:
             latent, idx_k = kv_cache.update_and_fetch_latent(layer_idx, latent, idx_k)
         sk = latent.shape[1]
+        add_mask = None
+        if isinstance(mask, torch.Tensor):
+            add_mask = torch.zeros(mask.shape, device=x.device).masked_fill(~mask, float("-inf")) \
+                if mask.dtype == torch.bool else mask.float()
+            while add_mask.dim() > 3:
+                add_mask = add_mask[:, 0]
+        idx = None
         if use_sparse and sk > c.index_topk:
-            add_mask = None
-            if isinstance(mask, torch.Tensor):
-                add_mask = torch.zeros(mask.shape, device=x.device).masked_fill(~mask, float("-inf")) \
-                    if mask.dtype == torch.bool else mask.float()
-                while add_mask.dim() > 3:
-                    add_mask = add_mask[:, 0]
             idx = self.indexer.select(iq, idx_k, iw, query_offset=sk - s, mask=add_mask)
+        if kv_cache is None and add_mask is None and x.is_cuda and x.dtype == torch.bfloat16 and ops.kernels_enabled():
+            # Training / prefill on the GPU: per-head K,V (192/128 wide) under the top-k bitmask.
+            from ..ops import attention as A
+            kv_up = self.wkv_b(c_kv).view(b, s, c.num_heads, c.qk_nope_head_dim + c.v_head_dim)
+            k = torch.cat([kv_up[..., :c.qk_nope_head_dim],
+                           k_pe[:, :, None, :].expand(b, s, c.num_heads, c.qk_rope_head_dim)], dim=-1)
+            v = kv_up[..., c.qk_nope_head_dim:]
+            if A.supported(q, k, v):
+                bits = A.build_mask_bits(idx, sk) if idx is not None else None
+                o, _ = A.masked_attention(q, k, v, bits, scale)
+                return self.wo(o.reshape(b, s, c.num_heads * c.v_head_dim))
+        if idx is not None:
             out_lat, _ = ops.sparse_mla_attention(self._latent_query(q), latent[:, :, None, :], idx[:, :, None, :],
                                                   sm_scale=scale, d_v=c.kv_lora_rank)
             o = self._latent_output(out_lat)

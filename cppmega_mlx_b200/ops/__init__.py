@@ -2,6 +2,7 @@
 from ._backend import check_status, has_library, kernels_enabled, load_library, set_kernels_enabled, use_kernels
 from .activations import squared_relu, swiglu, swiglu_reference
 from .conv import causal_conv1d_silu, packed_split_conv_silu
+from .attention import masked_attention, masked_attention_reference
 from .cce import linear_cross_entropy, linear_cross_entropy_reference
 from .gemm import gemm_batched, gemm_raw, linear, matmul_nt
 from .m2rnn_scan import broadcast_m2rnn_heads, m2rnn_scan, m2rnn_scan_reference

@@ -62,28 +62,41 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool
     return out
 
 
-def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool, b_mn: bool,
-                 lda: int, ldb: int, ldc: int, nb: tuple[int, int, int], sA: tuple[int, int, int],
+CAUSAL_SKIP = 16
+K_UPPER = 32
+K_LOWER = 64
+EPI_SOFTMAX_STATS = 128
+EPI_EXP_MASK = 256
+EPI_DS = 512
+
+
+def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, M: int, N: int, K: int, a_mn: bool,
+                 b_mn: bool, lda: int, ldb: int, ldc: int, nb: tuple[int, int, int], sA: tuple[int, int, int],
                  sB: tuple[int, int, int], sC: tuple[int, int, int], a_div2: int = 1, b_div2: int = 1,
                  accumulate: bool = False, row_vec: torch.Tensor | None = None, col_vec: torch.Tensor | None = None,
-                 sv: tuple[int, int, int] = (0, 0, 0), max_ctas: int = 0) -> torch.Tensor:
+                 sv: tuple[int, int, int] = (0, 0, 0), max_ctas: int = 0, flags: int = 0, aux: torch.Tensor | None = None,
+                 mask: torch.Tensor | None = None, mask_words: int = 0, mask_sb: int = 0, scale: float = 1.0,
+                 stats: torch.Tensor | None = None, out_f32: bool | None = None) -> torch.Tensor | None:
     """Strided-batched C (+)= A·Bᵀ. ``a``/``b``/``out`` only supply base pointers; all geometry is explicit:
     pitches ``ld*`` and per-operand element strides over the three batch dims ``nb = (n2, n3, n4)``.
     ``a_div2``/``b_div2`` let ``div`` consecutive dim-2 problems share one operand slice (the operand then has
-    ``n2 // div`` slices).  With ``row_vec``/``col_vec`` (fp32) the epilogue writes
-    ``acc · exp(row_vec[t] − col_vec[s]) · [s ≤ t]``; with ``row_vec`` alone, ``acc · exp(row_vec[t])``."""
+    ``n2 // div`` slices).  With ``row_vec``/``col_vec`` (fp32) and no explicit epilogue flag the epilogue writes
+    ``acc · exp(row_vec[t] − col_vec[s]) · [s ≤ t]``; with ``row_vec`` alone, ``acc · exp(row_vec[t])``.
+    ``flags`` adds the causal-range and attention epilogue modes (see ``csrc/gemm_bf16.cu``)."""
     lib = B.load_library()
-    flags = (OUT_F32 if out.dtype == torch.float32 else 0) | (ACCUMULATE if accumulate else 0)
-    if row_vec is not None:
-        flags |= EPI_DECAY_MASK if col_vec is not None else EPI_ROW_EXP
-    ip = (ctypes.c_int * 9)(M, N, K, int(a_mn), int(b_mn), flags, a_div2, b_div2, max_ctas)
-    lp = (ctypes.c_longlong * 18)(lda, ldb, ldc, *nb, *sA, *sB, *sC, *sv)
+    f32 = (out is not None and out.dtype == torch.float32) if out_f32 is None else out_f32
+    fl = flags | (OUT_F32 if f32 else 0) | (ACCUMULATE if accumulate else 0)
+    if row_vec is not None and not (flags & (EPI_EXP_MASK | EPI_DS)):
+        fl |= EPI_DECAY_MASK if col_vec is not None else EPI_ROW_EXP
+    ip = (ctypes.c_int * 10)(M, N, K, int(a_mn), int(b_mn), fl, a_div2, b_div2, max_ctas, mask_words)
+    lp = (ctypes.c_longlong * 19)(lda, ldb, ldc, *nb, *sA, *sB, *sC, *sv, mask_sb)
+    pp = (ctypes.c_void_p * 5)(*(None if t is None else t.data_ptr() for t in (row_vec, col_vec, aux, mask, stats)))
     st = B.status_buffer(a.device)
-    rc = lib.cmb_gemm_bf16_batched(B.ptr(a), B.ptr(b), B.ptr(out), ip, lp, B.ptr(row_vec), B.ptr(col_vec), B.ptr(st),
+    rc = lib.cmb_gemm_bf16_batched(B.ptr(a), B.ptr(b), B.ptr(out), ip, lp, pp, ctypes.c_float(scale), B.ptr(st),
                                    B.stream_ptr())
     if rc != 0:
         raise RuntimeError(f"gemm_bf16_batched failed with code {rc}: M{M} N{N} K{K} a_mn={a_mn} b_mn={b_mn} ld=({lda},{ldb},{ldc}) "
-                           f"nb={nb} sA={sA} sB={sB} sC={sC}")
+                           f"nb={nb} sA={sA} sB={sB} sC={sC} flags={fl}")
     B.check(rc, "gemm_bf16_batched")
     return out
 

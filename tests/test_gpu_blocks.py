@@ -79,3 +79,79 @@ def test_rmsnorm_block():
     with torch.no_grad():
         m.weight.uniform_(0.5, 1.5)
     _compare(m, torch.randn(3, 100, 512, device="cuda"), lambda mod, t: mod(t), rel=2e-2, grad_rel=3e-2)
+
+
+@pytest.mark.parametrize("S,H,Hk,Dq,Dv,topk", [(256, 4, 4, 64, 64, 0), (512, 4, 1, 192, 128, 96), (384, 2, 2, 192, 128, 200),
+                                               (128, 2, 1, 64, 32, 40)])
+def test_masked_attention_matches_reference(S, H, Hk, Dq, Dv, topk):
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops import attention as A
+    torch.manual_seed(S + H)
+    dev = "cuda"
+    Bn = 2
+    q = (torch.randn(Bn, S, H, Dq, device=dev) * 0.5).bfloat16().requires_grad_()
+    k = (torch.randn(Bn, S, Hk, Dq, device=dev) * 0.5).bfloat16().requires_grad_()
+    v = (torch.randn(Bn, S, Hk, Dv, device=dev) * 0.5).bfloat16().requires_grad_()
+    bits = mask_bool = None
+    if topk:
+        sc = torch.randn(Bn, S, S, device=dev)
+        ends = torch.arange(1, S + 1, device=dev, dtype=torch.int32).repeat(Bn)
+        idx = ops.topk_select_reference(sc.view(Bn * S, S), topk, None, ends).view(Bn, S, topk)
+        idx[0, 5, :] = -1  # a query with no key at all
+        bits = A.build_mask_bits(idx, S)
+        mask_bool = ops.indices_to_mask(idx[:, :, None, :], S)[:, 0]
+    assert A.supported(q, k, v)
+    O, lse = ops.masked_attention(q, k, v, bits)
+    gO = torch.randn_like(O)
+    gq, gk, gv = torch.autograd.grad(O, [q, k, v], gO)
+    torch.cuda.synchronize()
+    B.check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    Or, lser = ops.masked_attention_reference(qr, kr, vr, mask_bool)
+    rq, rk, rv = torch.autograd.grad(Or, [qr, kr, vr], gO.float())
+
+    def close(a, b, name, rel):
+        err = (a.float() - b.float()).abs().max().item()
+        scale = b.float().abs().max().item() + 1e-4
+        assert err <= rel * scale, f"{name}: err {err:.4g} scale {scale:.4g}"
+
+    close(O, Or, "O", 4e-2)
+    fin = torch.isfinite(lser)
+    assert (lse[fin] - lser[fin]).abs().max() < 5e-2
+    close(gq, rq, "dQ", 8e-2)
+    close(gk, rk, "dK", 8e-2)
+    close(gv, rv, "dV", 8e-2)
+
+
+def test_sparse_mla_op_cuda_matches_reference():
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import sparse_mla_cuda
+    torch.manual_seed(3)
+    dev = "cuda"
+    Bn, S, H, D, dv, topk = 1, 256, 8, 192, 128, 64
+    q = (torch.randn(Bn, S, H, D, device=dev) * 0.4).bfloat16().requires_grad_()
+    kv = (torch.randn(Bn, S, 1, D, device=dev) * 0.4).bfloat16().requires_grad_()
+    ends = torch.arange(1, S + 1, device=dev, dtype=torch.int32)
+    idx = ops.topk_select_reference(torch.randn(S, S, device=dev), topk, None, ends).view(Bn, S, 1, topk)
+    assert sparse_mla_cuda.supported(q, kv, idx, dv)
+    o, lse = ops.sparse_mla_attention(q, kv, idx, d_v=dv)
+    g = torch.randn_like(o)
+    gq, gkv = torch.autograd.grad(o, [q, kv], g)
+    qr, kvr = q.detach().float().requires_grad_(), kv.detach().float().requires_grad_()
+    orf, lr = ops.sparse_mla_reference(qr, kvr, idx, d_v=dv)
+    rq, rkv = torch.autograd.grad(orf, [qr, kvr], g.float())
+    assert (o.float() - orf).abs().max() < 4e-2 * orf.abs().max() + 1e-3
+    assert (lse - lr).abs().max() < 5e-2
+    assert (gq.float() - rq).abs().max() < 8e-2 * rq.abs().max() + 1e-3
+    assert (gkv.float() - rkv).abs().max() < 8e-2 * rkv.abs().max() + 1e-3
+
+
+def test_mla_attention_block_sparse():
+    from cppmega_mlx_b200.nn.mla import MLAAttention, MLABlockConfig
+    torch.manual_seed(0)
+    cfg = MLABlockConfig(hidden_size=256, num_heads=4, q_lora_rank=128, kv_lora_rank=128, qk_nope_head_dim=64,
+                         qk_rope_head_dim=32, v_head_dim=64, index_topk=64, index_head_dim=64, zero_init_out=False)
+    m = MLAAttention(cfg).cuda()
+    x = torch.randn(2, 256, 256, device="cuda") * 0.5
+    _compare(m, x, lambda mod, t: mod(t), rel=8e-2, grad_rel=1.5e-1)
