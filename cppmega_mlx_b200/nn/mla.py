@@ -112,8 +112,17 @@ class LightningIndexer(nn.Module):
             return torch.einsum("bqhk,bqh->bqk", F.relu(qk), w) * scale
         # Without the ReLU the head sum commutes with the dot product: one [Sq,d]x[d,Sk] GEMM.
         qw = (torch.einsum("bqhd,bqh->bqd", q.float(), w) * scale).to(k.dtype)
-        if k.is_cuda and k.dtype == torch.bfloat16:
-            return torch.stack([ops.matmul_nt(qw[i], k[i], out_dtype=torch.float32) for i in range(q.shape[0])])
+        b, sq, d = qw.shape
+        sk = k.shape[1]
+        if k.is_cuda and k.dtype == torch.bfloat16 and ops.kernels_enabled() and d % 8 == 0 and sk % 4 == 0:
+            # One batched GEMM; tiles entirely above the diagonal are skipped (the selector never reads them).
+            from ..ops import gemm as G
+            qw, kc = qw.contiguous(), k.contiguous()
+            out = torch.empty(b, sq, sk, dtype=torch.float32, device=k.device)
+            G.gemm_batched(qw, kc, out, M=sq, N=sk, K=d, a_mn=False, b_mn=False, lda=d, ldb=d, ldc=sk, nb=(1, 1, b),
+                           sA=(0, 0, sq * d), sB=(0, 0, sk * d), sC=(0, 0, sq * sk),
+                           flags=G.CAUSAL_SKIP if sq == sk else 0)
+            return out
         return torch.einsum("bqd,bkd->bqk", qw.float(), k.float())
 
     @torch.no_grad()
