@@ -45,6 +45,7 @@ enum : int {
   GEMM_EPI_SOFTMAX_STATS = 128,  // no C; per (row, tile half): running max / Σexp of masked scale·acc
   GEMM_EPI_EXP_MASK = 256,       // P = [mask] · exp(scale·acc − r[t])
   GEMM_EPI_DS = 512,             // dS = aux · (acc − r[t]) · scale   (aux has C's layout, bf16)
+  GEMM_EPI_AXPBY = 1024,         // scale · acc + scale2 · aux        (aux has C's layout, bf16)
 };
 
 struct GemmParams {
@@ -60,7 +61,7 @@ struct GemmParams {
   const unsigned* mask;      // attention epilogues: bit s of row t allows key s; nullptr = causal only
   long long mask_sb;         // words between batches (dim 4)
   int mask_words;            // words per row
-  float scale;
+  float scale, scale2;
   float* stats;              // SOFTMAX_STATS output: float2 per (problem, row, tile_n, half)
   int* status;
 };
@@ -280,6 +281,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool e_expm = (p.flags & GEMM_EPI_EXP_MASK) != 0;
     const bool e_ds = (p.flags & GEMM_EPI_DS) != 0;
     const bool attn = e_stats || e_expm || e_ds;
+    const bool e_axpby = (p.flags & GEMM_EPI_AXPBY) != 0;
     uint8_t* cbox = csmem + ew * GEMM_CBOX_BYTES;
     int local = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
@@ -306,7 +308,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (attn && p.mask != nullptr && row < p.M)
         mrow = p.mask + tc.i4 * p.mask_sb + static_cast<long long>(row) * p.mask_words;
       const __nv_bfloat16* auxrow = nullptr;
-      if (e_ds && row < p.M)
+      if ((e_ds || e_axpby) && row < p.M)
         auxrow = p.aux + tc.i2 * p.sC2 + tc.i3 * p.sC3 + tc.i4 * p.sC4 + static_cast<long long>(row) * p.ldc;
       float run_m = -INFINITY, run_l = 0.f;
 #pragma unroll 1
@@ -373,6 +375,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               r[2 * q] = __float_as_uint(d0);
               r[2 * q + 1] = __float_as_uint(d1);
             }
+          }
+        }
+        if (e_axpby) {
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {
+            float lo = 0.f, hi = 0.f;
+            if (auxrow != nullptr && col0 + 2 * q + 1 < p.N) {
+              const float2 pp = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(auxrow + col0 + 2 * q));
+              lo = pp.x;
+              hi = pp.y;
+            } else if (auxrow != nullptr && col0 + 2 * q < p.N) {
+              lo = __bfloat162float(auxrow[col0 + 2 * q]);
+            }
+            r[2 * q] = __float_as_uint(p.scale * __uint_as_float(r[2 * q]) + p.scale2 * lo);
+            r[2 * q + 1] = __float_as_uint(p.scale * __uint_as_float(r[2 * q + 1]) + p.scale2 * hi);
           }
         }
         if (decay) {
@@ -560,7 +577,7 @@ struct GemmArgs {
   const unsigned* mask;
   int64_t mask_sb;
   int mask_words;
-  float scale;
+  float scale, scale2;
   float* stats;
   int* status;
   int max_ctas;
@@ -614,7 +631,7 @@ static int launch_gemm(const GemmArgs& g) {
   p.aux = static_cast<const __nv_bfloat16*>(g.aux);
   p.ldc = g.ldc; p.sC2 = g.sC[0]; p.sC3 = g.sC[1]; p.sC4 = g.sC[2];
   p.mask = g.mask; p.mask_sb = g.mask_sb; p.mask_words = g.mask_words;
-  p.scale = g.scale; p.stats = g.stats;
+  p.scale = g.scale; p.scale2 = g.scale2; p.stats = g.stats;
   p.status = g.status;
   kern<<<grid, cmb::GEMM_THREADS, Cfg::SMEM_BYTES, g.stream>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 104;
@@ -661,7 +678,7 @@ extern "C" int cmb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
 // `pp` = {row_vec, col_vec, aux, mask, stats} device pointers (any may be null). Flags select the epilogue, see the
 // enum at the top of this file.
 extern "C" int cmb_gemm_bf16_batched(const void* A, const void* B, void* C, const int* ip, const long long* lp,
-                                     const void* const* pp, float scale, int* status, void* stream) {
+                                     const void* const* pp, float scale, float scale2, int* status, void* stream) {
   cmb_host::GemmArgs g{};
   g.A = A; g.B = B; g.C = C; g.M = ip[0]; g.N = ip[1]; g.K = ip[2];
   g.flags = ip[5]; g.a_div2 = ip[6]; g.b_div2 = ip[7]; g.max_ctas = ip[8]; g.mask_words = ip[9];
@@ -674,11 +691,12 @@ extern "C" int cmb_gemm_bf16_batched(const void* A, const void* B, void* C, cons
   g.row_vec = static_cast<const float*>(pp[0]); g.col_vec = static_cast<const float*>(pp[1]);
   g.aux = pp[2]; g.mask = static_cast<const unsigned*>(pp[3]); g.stats = static_cast<float*>(const_cast<void*>(pp[4]));
   g.scale = scale;
+  g.scale2 = scale2;
   g.status = status; g.stream = static_cast<cudaStream_t>(stream);
   const int f = g.flags;
   if ((f & cmb::GEMM_EPI_DECAY_MASK) && (g.row_vec == nullptr || g.col_vec == nullptr)) return 108;
   if ((f & (cmb::GEMM_EPI_ROW_EXP | cmb::GEMM_EPI_EXP_MASK | cmb::GEMM_EPI_DS)) && g.row_vec == nullptr) return 108;
-  if ((f & cmb::GEMM_EPI_DS) && g.aux == nullptr) return 108;
+  if ((f & (cmb::GEMM_EPI_DS | cmb::GEMM_EPI_AXPBY)) && g.aux == nullptr) return 108;
   if ((f & cmb::GEMM_EPI_SOFTMAX_STATS) && g.stats == nullptr) return 108;
   return cmb_host::dispatch(g, ip[3], ip[4]);
 }

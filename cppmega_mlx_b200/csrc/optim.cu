@@ -200,6 +200,22 @@ __global__ void __launch_bounds__(256) muon_momentum_kernel(const T* __restrict_
   }
 }
 
+// x ← x / (sqrt(*sumsq) + eps)   (bf16, in place): the Frobenius normalisation in front of Newton–Schulz.
+__global__ void scale_inv_norm_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ sumsq, int64_t n, float eps) {
+  const float inv = 1.f / (sqrtf(*sumsq) + eps);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    x[i] = __float2bfloat16(__bfloat162float(x[i]) * inv);
+}
+
+// p ← p − coef · u   (u bf16, the orthogonalised update).
+template <typename T>
+__global__ void axpy_update_kernel(T* __restrict__ p, const __nv_bfloat16* __restrict__ u, int64_t n, float coef) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    Cvt<T>::st(p, i, Cvt<T>::ld(p, i) - coef * __bfloat162float(u[i]));
+}
+
 static inline int grid_for(int64_t n, int per_block) {
   int64_t b = (n + per_block - 1) / per_block;
   const int64_t cap = 148 * 16;
@@ -263,5 +279,20 @@ extern "C" int cmb_muon_momentum(const void* g, const void* p, float* v, void* o
   CMB_DISPATCH_DTYPE(dtype, (cmb::muon_momentum_kernel<T><<<cmb::grid_for(n, 2048), 256, 0, s>>>(
                                 static_cast<const T*>(g), static_cast<const T*>(p), v, static_cast<__nv_bfloat16*>(out_bf16), sumsq,
                                 n, momentum, wd, nesterov)));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_scale_inv_norm(void* x, const float* sumsq, int64_t n, float eps, void* stream) {
+  if (n <= 0) return 0;
+  cmb::scale_inv_norm_kernel<<<cmb::grid_for(n, 2048), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(x), sumsq, n, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_axpy_update(void* p, const void* u, int64_t n, int dtype, float coef, void* stream) {
+  if (n <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CMB_DISPATCH_DTYPE(dtype, (cmb::axpy_update_kernel<T><<<cmb::grid_for(n, 2048), 256, 0, s>>>(
+                                static_cast<T*>(p), static_cast<const __nv_bfloat16*>(u), n, coef)));
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }

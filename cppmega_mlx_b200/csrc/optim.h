@@ -16,6 +16,8 @@ int cmb_lion8bit(void* p, const void* g, uint8_t* mq, float* ma, const float* lu
                  float b1, float b2, float wd, void* stream);
 int cmb_muon_momentum(const void* g, const void* p, float* v, void* out_bf16, float* sumsq, int64_t n, int dtype,
                       float momentum, float wd, int nesterov, void* stream);
+int cmb_scale_inv_norm(void* x_bf16, const float* sumsq, int64_t n, float eps, void* stream);
+int cmb_axpy_update(void* p, const void* u_bf16, int64_t n, int dtype, float coef, void* stream);
 #ifdef __cplusplus
 }
 #endif

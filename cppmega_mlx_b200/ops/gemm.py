@@ -68,6 +68,7 @@ K_LOWER = 64
 EPI_SOFTMAX_STATS = 128
 EPI_EXP_MASK = 256
 EPI_DS = 512
+EPI_AXPBY = 1024
 
 
 def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, M: int, N: int, K: int, a_mn: bool,
@@ -76,7 +77,7 @@ def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, 
                  accumulate: bool = False, row_vec: torch.Tensor | None = None, col_vec: torch.Tensor | None = None,
                  sv: tuple[int, int, int] = (0, 0, 0), max_ctas: int = 0, flags: int = 0, aux: torch.Tensor | None = None,
                  mask: torch.Tensor | None = None, mask_words: int = 0, mask_sb: int = 0, scale: float = 1.0,
-                 stats: torch.Tensor | None = None, out_f32: bool | None = None) -> torch.Tensor | None:
+                 scale2: float = 0.0, stats: torch.Tensor | None = None, out_f32: bool | None = None) -> torch.Tensor | None:
     """Strided-batched C (+)= A·Bᵀ. ``a``/``b``/``out`` only supply base pointers; all geometry is explicit:
     pitches ``ld*`` and per-operand element strides over the three batch dims ``nb = (n2, n3, n4)``.
     ``a_div2``/``b_div2`` let ``div`` consecutive dim-2 problems share one operand slice (the operand then has
@@ -92,7 +93,7 @@ def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, 
     lp = (ctypes.c_longlong * 19)(lda, ldb, ldc, *nb, *sA, *sB, *sC, *sv, mask_sb)
     pp = (ctypes.c_void_p * 5)(*(None if t is None else t.data_ptr() for t in (row_vec, col_vec, aux, mask, stats)))
     st = B.status_buffer(a.device)
-    rc = lib.cmb_gemm_bf16_batched(B.ptr(a), B.ptr(b), B.ptr(out), ip, lp, pp, ctypes.c_float(scale), B.ptr(st),
+    rc = lib.cmb_gemm_bf16_batched(B.ptr(a), B.ptr(b), B.ptr(out), ip, lp, pp, ctypes.c_float(scale), ctypes.c_float(scale2), B.ptr(st),
                                    B.stream_ptr())
     if rc != 0:
         raise RuntimeError(f"gemm_bf16_batched failed with code {rc}: M{M} N{N} K{K} a_mn={a_mn} b_mn={b_mn} ld=({lda},{ldb},{ldc}) "
@@ -147,3 +148,19 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -
         y = _LinearFn.apply(x, w)
         return y if bias is None else y + bias
     return torch.nn.functional.linear(x, w, bias)
+
+
+def gemm_axpby(a, b, aux, *, a_mn=False, b_mn=False, alpha: float = 1.0, beta: float = 0.0, out=None) -> torch.Tensor:
+    """out = alpha · (A·Bᵀ) + beta · aux, all bf16 2-D (``aux`` has the output's shape and pitch)."""
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    N = b.shape[1] if b_mn else b.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    if aux.stride(0) != out.stride(0) or aux.shape != out.shape:
+        raise ValueError("aux must have the output's shape and pitch")
+    return gemm_batched(a, b, out, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, lda=a.stride(0), ldb=b.stride(0), ldc=out.stride(0),
+                        nb=(1, 1, 1), sA=(0, 0, 0), sB=(0, 0, 0), sC=(0, 0, 0), flags=EPI_AXPBY, aux=aux, scale=alpha,
+                        scale2=beta)

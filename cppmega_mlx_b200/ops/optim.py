@@ -58,3 +58,42 @@ def fused_muon_momentum_(g, p, v, out_bf16, momentum, wd, nesterov, inv_norm_out
     B.check(lib.cmb_muon_momentum(B.ptr(g), B.ptr(p), B.ptr(v), B.ptr(out_bf16), B.ptr(inv_norm_out),
                                   ctypes.c_int64(p.numel()), _dt(p, g), ctypes.c_float(momentum), ctypes.c_float(wd),
                                   int(bool(nesterov)), B.stream_ptr()), "muon_momentum")
+
+
+def newton_schulz5_bf16_(u: torch.Tensor, sumsq: torch.Tensor, steps: int = 5, coeffs=(3.4445, -4.7750, 2.0315)) -> torch.Tensor:
+    """Orthogonalise the bf16 matrix ``u`` (normalised in place by ``sqrt(sumsq)``) with the quintic Newton–Schulz
+    iteration, entirely as tcgen05 GEMMs with fused ``alpha·acc + beta·aux`` epilogues: three launches per step and no
+    element-wise pass.  Tall matrices apply the polynomial from the right (``X ← aX + X(bG + cG²)``, ``G = XᵀX``) so no
+    transpose is ever materialised."""
+    from .gemm import gemm_axpby, gemm_raw
+    lib = B.load_library()
+    a, b, c = coeffs
+    B.check(lib.cmb_scale_inv_norm(B.ptr(u), B.ptr(sumsq), ctypes.c_int64(u.numel()), ctypes.c_float(1e-7), B.stream_ptr()),
+            "scale_inv_norm")
+    rows, cols = u.shape
+    x = u
+    nxt = torch.empty_like(u)
+    tall = rows > cols
+    for _ in range(steps):
+        if tall:
+            g = gemm_raw(x, x, a_mn=True, b_mn=True)                       # XᵀX  [c,c]
+            poly = gemm_axpby(g, g, g, alpha=c, beta=b)                   # bG + cG²   (G symmetric)
+            gemm_axpby(x, poly, x, alpha=1.0, beta=a, out=nxt)            # aX + X·poly
+        else:
+            g = gemm_raw(x, x)                                            # XXᵀ  [r,r]
+            poly = gemm_axpby(g, g, g, alpha=c, beta=b)
+            gemm_axpby(poly, x, x, b_mn=True, alpha=1.0, beta=a, out=nxt)  # aX + poly·X
+        x, nxt = nxt, x
+    return x
+
+
+def muon_step_(p, g, v, lr, momentum, wd, nesterov, ns_steps):
+    """One fused Muon update of a 2-D bf16/fp32 parameter: momentum (+decay) → NS-5 on tensor cores → p −= lr'·U."""
+    lib = B.load_library()
+    u = torch.empty(p.shape, dtype=torch.bfloat16, device=p.device)
+    sumsq = torch.zeros(1, dtype=torch.float32, device=p.device)
+    fused_muon_momentum_(g, p, v, u, momentum, wd, nesterov, sumsq)
+    o = newton_schulz5_bf16_(u, sumsq, ns_steps)
+    coef = lr * max(1.0, p.shape[0] / p.shape[1]) ** 0.5
+    B.check(lib.cmb_axpy_update(B.ptr(p), B.ptr(o), ctypes.c_int64(p.numel()), _DT[p.dtype], ctypes.c_float(coef),
+                                B.stream_ptr()), "axpy_update")

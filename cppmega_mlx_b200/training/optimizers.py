@@ -246,6 +246,12 @@ class MuonWithNSCarrier(Optimizer):
         p.copy_(p.float() - lr * update)
 
     def apply_single(self, name, grad, p, st):
+        if (p.is_cuda and B.kernels_enabled() and self.ns_carrier == "bf16" and p.dim() == 2 and p.is_contiguous()
+                and grad.is_contiguous() and p.dtype == grad.dtype and p.shape[0] % 8 == 0 and p.shape[1] % 8 == 0
+                and p.dtype in (torch.bfloat16, torch.float32) and type(self) is MuonWithNSCarrier):
+            from ..ops.optim import muon_step_
+            muon_step_(p, grad, st["v"], self.lr, self.momentum, self.weight_decay, self.nesterov, self.ns_steps)
+            return
         self._apply_update(self._momentum(grad.float(), p, st), p)
 
 
