@@ -2,6 +2,8 @@
 // bf16 in / out, fp32 math, 128-bit accesses. These replace the reference's library calls
 // mx.fast.rms_norm / mx.fast.rope (docs/production_kernel_routing.md:62-140); rotary layout and
 // scaling tables follow cppmega_mlx/nn/attention.py:399-538 (tables are built on the host).
+#include <mutex>
+
 #include "sm100.cuh"
 
 namespace cmb {
@@ -253,4 +255,61 @@ extern "C" int cmb_rope(const void* x, void* y, const void* cos_t, const void* s
       static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), static_cast<const float*>(cos_t),
       static_cast<const float*>(sin_t), B, S, H, D, off, rot, pos0, inverse);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// RMSNorm backward for callers that cannot allocate device memory (declared in rmsnorm_noalloc.h).
+//
+// The regular entry point above hands the per-CTA partial sums of dW back to the caller, who has to provide that
+// buffer. This variant keeps the partials in a fixed device array that lives inside the library image, and reduces
+// them into the caller's dW vector itself, so a caller needs nothing but its inputs and outputs.
+namespace cmb {
+
+constexpr int NOALLOC_MAX_COLS = 8192;   // widest row the entry point accepts
+constexpr int NOALLOC_MAX_BLOCKS = 148;  // partial rows (one per CTA, one CTA per SM)
+
+// 148 × 8192 fp32 = 4.6 MiB, resident on every GPU that loads the library until the process exits.
+static __device__ __align__(256) float g_rmsnorm_noalloc_partials[NOALLOC_MAX_BLOCKS * NOALLOC_MAX_COLS];
+
+__global__ void rmsnorm_noalloc_reduce_kernel(const float* __restrict__ part, float* __restrict__ gw, int nblk, int cols) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float acc = 0.f;
+  for (int b = 0; b < nblk; ++b) acc += part[static_cast<size_t>(b) * cols + c];
+  gw[c] = acc;
+}
+
+}  // namespace cmb
+
+extern "C" int cmb_rmsnorm_bwd_noalloc(const void* gy, const void* x, const void* w, const void* rstd, void* gx,
+                                       float* gw, int64_t rows, int cols, void* stream) {
+  if (gy == nullptr || x == nullptr || w == nullptr || rstd == nullptr || gx == nullptr || gw == nullptr) return -1;
+  if (rows <= 0 || cols <= 0 || cols % 8 != 0) return -2;
+  if (cols > cmb::NOALLOC_MAX_COLS) return -3;
+  // The array's name is only a host-side handle; kernels need its device address, which differs per GPU. It is looked
+  // up once per device (with that device current) on the first call made there and cached.
+  static std::mutex mu;
+  static float* dev_ptr[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -4;
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, cmb::g_rmsnorm_noalloc_partials) != cudaSuccess || p == nullptr) return -5;
+      dev_ptr[dev] = static_cast<float*>(p);
+    }
+    scratch = dev_ptr[dev];
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int nblk = static_cast<int>(rows < cmb::NOALLOC_MAX_BLOCKS ? rows : cmb::NOALLOC_MAX_BLOCKS);
+  // Every partial row that the reduction reads (rows 0..nblk-1, columns 0..cols-1) is fully overwritten by the first
+  // kernel, so nothing left over from an earlier call can leak in and no clearing is needed.
+  cmb::rmsnorm_bwd_kernel<256><<<nblk, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(gy), static_cast<const __nv_bfloat16*>(x),
+                                                    static_cast<const __nv_bfloat16*>(w), static_cast<const float*>(rstd),
+                                                    static_cast<__nv_bfloat16*>(gx), scratch, rows, cols);
+  if (cudaGetLastError() != cudaSuccess) return -6;
+  cmb::rmsnorm_noalloc_reduce_kernel<<<(cols + 255) / 256, 256, 0, s>>>(scratch, gw, nblk, cols);
+  return cudaGetLastError() == cudaSuccess ? 0 : -6;
 }
