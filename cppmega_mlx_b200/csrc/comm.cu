@@ -1,0 +1,239 @@
+// Kernels that talk to peer GPUs through symmetric memory over NVLink / NVSwitch (plain peer loads and stores
+// by default; `multimem` only where a multicast address is passed in).  Every rank maps every peer's
+// buffers, so `bufs[r]` below is rank r's copy of the same logical buffer.
+//
+//  * cmb_comm_barrier        epoch-flag barrier: release-store my epoch into every peer's pad, acquire-poll my pad.
+//                            The poll is bounded; on expiry a status word is set and the kernel returns.
+//  * cmb_zero1_adamw         ZeRO-1 for AdamW-owned tensors in ONE kernel: sum the W peers' bf16 gradients of the
+//                            owned range (the reduce-scatter), bf16→fp32, AdamW on local fp32 moments, and push the
+//                            new bf16 parameters into every rank's parameter buffer (the all-gather).
+//  * cmb_zero1_muon_reduce   same gradient reduction fused with Muon's momentum stage: writes the bf16 Newton–Schulz
+//                            input and accumulates its squared norm.
+//  * cmb_zero1_push_update   p ← p − coef·u for an owned tensor, stored to every rank (all-gather side of Muon).
+//
+// These replace the reference's per-leaf all_sum for gradients and its all_sum-of-zero-padded-shards "gather"
+// (cppmega_mlx/training/distributed_optimizer.py:302-324, :326-391).
+#include "sm100.cuh"
+
+namespace cmb {
+
+constexpr int COMM_MAX_RANKS = 16;
+
+struct PeerPtrs {
+  void* p[COMM_MAX_RANKS];
+};
+
+__device__ __forceinline__ void st_release_sys(int* addr, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// pads[r] = rank r's int32[COMM_MAX_RANKS] flag block. Thread t signals peer t and waits for peer t.
+__global__ void comm_barrier_kernel(PeerPtrs pads, int rank, int world, int epoch, long long spin_limit, int* status) {
+  const int t = threadIdx.x;
+  if (t < world) {
+    __threadfence_system();
+    st_release_sys(static_cast<int*>(pads.p[t]) + rank, epoch);
+    const int* mine = static_cast<const int*>(pads.p[rank]) + t;
+    bool ok = false;
+    for (long long i = 0; i < spin_limit; ++i) {
+      if (ld_acquire_sys(mine) >= epoch) {
+        ok = true;
+        break;
+      }
+      __nanosleep(64);
+    }
+    if (!ok && status != nullptr && atomicCAS(status, 0, ST_TIMEOUT_PEER_FLAG) == 0) {
+      status[1] = rank;
+      status[2] = t;
+      status[3] = epoch;
+    }
+    __threadfence_system();
+  }
+}
+
+__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(b[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  v.x = pack_bf16x2(f[0], f[1]);
+  v.y = pack_bf16x2(f[2], f[3]);
+  v.z = pack_bf16x2(f[4], f[5]);
+  v.w = pack_bf16x2(f[6], f[7]);
+  return v;
+}
+
+// Sum of the W ranks' gradients for 8 consecutive elements starting at flat offset `e` (16-byte aligned).
+__device__ __forceinline__ void reduce8(const PeerPtrs& grads, int world, long long e, float inv_world, float (&g)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) g[i] = 0.f;
+  for (int r = 0; r < world; ++r) {
+    const uint4 q = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grads.p[r]) + e);
+    float f[8];
+    unpack8(q, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] += f[i];
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) g[i] *= inv_world;
+}
+
+// off: element offset of the tensor inside the flat buffers (multiple of 8); n: element count (tail handled scalar).
+__global__ void __launch_bounds__(256) zero1_adamw_kernel(PeerPtrs grads, PeerPtrs params, int rank, int world,
+                                                           long long off, long long n, float* __restrict__ m,
+                                                           float* __restrict__ v, float lr, float b1, float b2, float eps,
+                                                           float wd, float c1, float c2, float inv_world) {
+  const long long nvec = n >> 3;
+  const __nv_bfloat16* myp = static_cast<const __nv_bfloat16*>(params.p[rank]);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = off + 8 * i;
+    float g[8], p[8];
+    reduce8(grads, world, e, inv_world, g);
+    unpack8(*reinterpret_cast<const uint4*>(myp + e), p);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const long long j = 8 * i + k;
+      const float mi = b1 * m[j] + (1.f - b1) * g[k];
+      const float vi = b2 * v[j] + (1.f - b2) * g[k] * g[k];
+      m[j] = mi;
+      v[j] = vi;
+      p[k] = p[k] * (1.f - lr * wd) - lr * c1 * mi / (sqrtf(vi) * c2 + eps);
+    }
+    const uint4 out = pack8(p);
+    for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + e) = out;
+  }
+  // scalar tail (n % 8)
+  const long long tail0 = nvec << 3;
+  for (long long j = tail0 + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; j < n;
+       j += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float g = 0.f;
+    for (int r = 0; r < world; ++r) g += __bfloat162float(static_cast<const __nv_bfloat16*>(grads.p[r])[off + j]);
+    g *= inv_world;
+    const float mi = b1 * m[j] + (1.f - b1) * g;
+    const float vi = b2 * v[j] + (1.f - b2) * g * g;
+    m[j] = mi;
+    v[j] = vi;
+    const float pn = __bfloat162float(myp[off + j]) * (1.f - lr * wd) - lr * c1 * mi / (sqrtf(vi) * c2 + eps);
+    const __nv_bfloat16 o = __float2bfloat16(pn);
+    for (int r = 0; r < world; ++r) static_cast<__nv_bfloat16*>(params.p[r])[off + j] = o;
+  }
+}
+
+// Gradient reduction fused with Muon's momentum stage (n % 8 == 0 for 2-D weights with cols % 8 == 0).
+__global__ void __launch_bounds__(256) zero1_muon_reduce_kernel(PeerPtrs grads, PeerPtrs params, int rank, int world,
+                                                                 long long off, long long n, float* __restrict__ v,
+                                                                 __nv_bfloat16* __restrict__ u, float* __restrict__ sumsq,
+                                                                 float mu, float wd, int nesterov, float inv_world) {
+  __shared__ float red[8];
+  const long long nvec = n >> 3;
+  const __nv_bfloat16* myp = static_cast<const __nv_bfloat16*>(params.p[rank]);
+  float acc = 0.f;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = off + 8 * i;
+    float g[8], p[8], o[8];
+    reduce8(grads, world, e, inv_world, g);
+    unpack8(*reinterpret_cast<const uint4*>(myp + e), p);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const long long j = 8 * i + k;
+      const float gi = g[k] + wd * p[k];
+      const float vi = mu * v[j] + (1.f - mu) * gi;
+      v[j] = vi;
+      o[k] = nesterov ? gi * (1.f - mu) + vi * mu : vi;
+      acc += o[k] * o[k];
+    }
+    *reinterpret_cast<uint4*>(u + 8 * i) = pack8(o);
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < 8; ++w) t += red[w];
+    atomicAdd(sumsq, t);
+  }
+}
+
+__global__ void __launch_bounds__(256) zero1_push_update_kernel(PeerPtrs params, int rank, int world, long long off,
+                                                                 long long n, const __nv_bfloat16* __restrict__ u,
+                                                                 float coef) {
+  const long long nvec = n >> 3;
+  const __nv_bfloat16* myp = static_cast<const __nv_bfloat16*>(params.p[rank]);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = off + 8 * i;
+    float p[8], d[8];
+    unpack8(*reinterpret_cast<const uint4*>(myp + e), p);
+    unpack8(*reinterpret_cast<const uint4*>(u + 8 * i), d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) p[k] -= coef * d[k];
+    const uint4 out = pack8(p);
+    for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + e) = out;
+  }
+}
+
+static inline int comm_grid(long long nvec) {
+  long long b = (nvec + 255) / 256;
+  const long long cap = 148LL * 4;
+  return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
+}
+static inline bool fill(PeerPtrs& out, const long long* ptrs, int world) {
+  if (world < 1 || world > COMM_MAX_RANKS) return false;
+  for (int r = 0; r < COMM_MAX_RANKS; ++r) out.p[r] = r < world ? reinterpret_cast<void*>(ptrs[r]) : nullptr;
+  return true;
+}
+
+}  // namespace cmb
+
+extern "C" int cmb_comm_barrier(const long long* pad_ptrs, int rank, int world, int epoch, long long spin_limit,
+                                int* status, void* stream) {
+  cmb::PeerPtrs pads;
+  if (!cmb::fill(pads, pad_ptrs, world)) return 1;
+  cmb::comm_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pads, rank, world, epoch, spin_limit, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_zero1_adamw(const long long* grad_ptrs, const long long* param_ptrs, int rank, int world, long long off,
+                               long long n, float* m, float* v, float lr, float b1, float b2, float eps, float wd, float c1,
+                               float c2, void* stream) {
+  cmb::PeerPtrs g, p;
+  if (!cmb::fill(g, grad_ptrs, world) || !cmb::fill(p, param_ptrs, world) || (off & 7)) return 1;
+  if (n <= 0) return 0;
+  cmb::zero1_adamw_kernel<<<cmb::comm_grid((n + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      g, p, rank, world, off, n, m, v, lr, b1, b2, eps, wd, c1, c2, 1.f / world);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_zero1_muon_reduce(const long long* grad_ptrs, const long long* param_ptrs, int rank, int world,
+                                     long long off, long long n, float* v, void* u, float* sumsq, float mu, float wd,
+                                     int nesterov, void* stream) {
+  cmb::PeerPtrs g, p;
+  if (!cmb::fill(g, grad_ptrs, world) || !cmb::fill(p, param_ptrs, world) || (off & 7) || (n & 7)) return 1;
+  if (n <= 0) return 0;
+  cmb::zero1_muon_reduce_kernel<<<cmb::comm_grid(n / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      g, p, rank, world, off, n, v, static_cast<__nv_bfloat16*>(u), sumsq, mu, wd, nesterov, 1.f / world);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_zero1_push_update(const long long* param_ptrs, int rank, int world, long long off, long long n,
+                                     const void* u, float coef, void* stream) {
+  cmb::PeerPtrs p;
+  if (!cmb::fill(p, param_ptrs, world) || (off & 7) || (n & 7)) return 1;
+  if (n <= 0) return 0;
+  cmb::zero1_push_update_kernel<<<cmb::comm_grid(n / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      p, rank, world, off, n, static_cast<const __nv_bfloat16*>(u), coef);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}

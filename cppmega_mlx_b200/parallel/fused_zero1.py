@@ -1,0 +1,101 @@
+"""Fused ZeRO-1 step over symmetric memory.
+
+With the flat gradient and parameter buffers living in symmetric memory, the optimizer step of the owner of
+a tensor is a single pass that (1) sums that tensor's bf16 gradients straight out of all W ranks' gradient
+buffers — the reduce-scatter —, (2) casts to fp32 and applies the update to its local state, and (3) stores
+the new bf16 parameters into all W ranks' parameter buffers — the all-gather.  AdamW-owned tensors do all
+three in one kernel; Muon-owned matrices do (1)+momentum in one kernel, run Newton–Schulz-5 locally on the
+tensor cores, and do the update+(3) in a second kernel.  Two epoch barriers bracket the step: "all gradients
+written" before, "all parameters delivered and all gradients consumed" after.  No NCCL call is on this path.
+
+Per step and rank this moves (W−1)/W of the owned segment over NVLink in each direction.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import _backend as B
+from .symm import EpochBarrier, SymmetricBuffer
+
+I64 = ctypes.c_longlong
+F32 = ctypes.c_float
+
+
+class FusedZeRO1Comm:
+    def __init__(self, group=None):
+        self.group = group
+        self.flat = None
+        self.bufs: list[SymmetricBuffer] = []
+        self.barrier: EpochBarrier | None = None
+        self.enabled = True
+
+    def alloc(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        buf = SymmetricBuffer(numel, dtype, torch.device("cuda", torch.cuda.current_device()), self.group)
+        self.bufs.append(buf)
+        return buf.tensor
+
+    def bind(self, flat) -> None:
+        self.flat = flat
+        self.params_buf, self.grads_buf = self.bufs[0], self.bufs[1]
+        if flat.dtype != torch.bfloat16 or flat.grad_dtype != torch.bfloat16:
+            self.enabled = False
+        self.barrier = EpochBarrier(flat.params.device, self.group)
+
+    # ------------------------------------------------------------------------------------------
+    def _supported(self, opt) -> bool:
+        from ..training.optimizers import AdamWFP32Moments, MuonAdamWMulti, MuonWithNSCarrier
+        inner = opt.inner
+        if not (self.enabled and B.kernels_enabled()):
+            return False
+        if isinstance(inner, AdamWFP32Moments):
+            return True
+        return (isinstance(inner, MuonAdamWMulti) and type(inner.muon) is MuonWithNSCarrier
+                and inner.muon.ns_carrier == "bf16" and isinstance(inner.other, AdamWFP32Moments))
+
+    def try_fused_step(self, opt) -> bool:
+        if not self._supported(opt):
+            return False
+        from ..ops.optim import newton_schulz5_bf16_
+        from ..training.optimizers import AdamWFP32Moments
+        lib = B.load_library()
+        flat, W, rank = self.flat, opt.world, opt.rank
+        gp, pp = self.grads_buf.peer_ptrs, self.params_buf.peer_ptrs
+        st = B.stream_ptr
+        inner = opt.inner
+        adamw = inner if isinstance(inner, AdamWFP32Moments) else inner.other
+        muon = None if isinstance(inner, AdamWFP32Moments) else inner.muon
+        self.barrier()  # every rank's backward has written its gradients
+        adamw.step_count += 1
+        b1, b2 = adamw.betas
+        if adamw.bias_correction:
+            t = adamw.step_count
+            c1, c2 = 1.0 / (1 - b1 ** t), 1.0 / (1 - b2 ** t)
+        else:
+            c1 = c2 = 1.0
+        for name, p in adamw.params:
+            owner, off, n = flat.slots[name]
+            s = adamw.state_for(name, p)
+            B.check(lib.cmb_zero1_adamw(gp, pp, rank, W, I64(owner * flat.segment + off), I64(n), B.ptr(s["m"]), B.ptr(s["v"]),
+                                        F32(adamw.lr), F32(b1), F32(b2), F32(adamw.eps), F32(adamw.weight_decay), F32(c1),
+                                        F32(c2), st()), "zero1_adamw")
+        if muon is not None:
+            muon.step_count += 1
+            for name, p in muon.params:
+                owner, off, n = flat.slots[name]
+                goff = owner * flat.segment + off
+                s = muon.state_for(name, p)
+                rows, cols = p.shape
+                if n % 8 or rows % 8 or cols % 8:
+                    raise RuntimeError(f"fused Muon needs dimensions that are multiples of 8, got {tuple(p.shape)} for {name}")
+                u = torch.empty(rows, cols, dtype=torch.bfloat16, device=p.device)
+                sumsq = torch.zeros(1, dtype=torch.float32, device=p.device)
+                B.check(lib.cmb_zero1_muon_reduce(gp, pp, rank, W, I64(goff), I64(n), B.ptr(s["v"]), B.ptr(u), B.ptr(sumsq),
+                                                  F32(muon.momentum), F32(muon.weight_decay), int(muon.nesterov), st()),
+                        "zero1_muon_reduce")
+                o = newton_schulz5_bf16_(u, sumsq, muon.ns_steps)
+                coef = muon.lr * max(1.0, rows / cols) ** 0.5
+                B.check(lib.cmb_zero1_push_update(pp, rank, W, I64(goff), I64(n), B.ptr(o), F32(coef), st()), "zero1_push_update")
+        self.barrier()  # all parameters delivered everywhere; all gradients consumed
+        return True

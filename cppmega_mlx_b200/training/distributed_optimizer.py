@@ -65,7 +65,7 @@ class FlatBuffers:
         self.segment = max(_round_up(max(offs), ALIGN), ALIGN)
         total = self.segment * world
         alloc = alloc or (lambda n, dt: torch.zeros(n, dtype=dt, device=device))
-        self.params = alloc(total, self.dtype)
+        self.params = alloc(total, self.dtype)   # allocation order matters to symmetric-memory users: params, then grads
         self.grads = alloc(total, self.grad_dtype)
         with torch.no_grad():
             for n, p in named:
