@@ -194,7 +194,7 @@ class WindowedTokenDataset:
         return BatchCursor(epoch + total // self.num_batches, total % self.num_batches, total)
 
     def token_id_range(self) -> tuple[int, int]:
-        return int(np.min(self._tokens)), int(np.max(self._tokens))
+        return int(self._tokens.min()), int(self._tokens.max())
 
 
 class TokenNpzDataset(WindowedTokenDataset):
