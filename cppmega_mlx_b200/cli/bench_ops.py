@@ -66,13 +66,15 @@ def bench_gemm(args) -> list[dict]:
     pk = peaks()
     rows = []
     for M, N, K, a_mn, b_mn, label in GEMM_SHAPES:
+        if args.only and args.only != label:
+            continue
         a = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
         b = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        ours = time_cuda(lambda: ops.gemm_raw(a, b, a_mn=a_mn, b_mn=b_mn, out=out))
+        ours = time_cuda(lambda: ops.gemm_raw(a, b, a_mn=a_mn, b_mn=b_mn, out=out), iters=args.iters, warmup=args.warmup)
         A = a.t() if a_mn else a
         Bt = b if b_mn else b.t()
-        lib = time_cuda(lambda: torch.matmul(A, Bt, out=out))
+        lib = time_cuda(lambda: torch.matmul(A, Bt, out=out), iters=args.iters, warmup=args.warmup)
         fl = 2.0 * M * N * K
         rows.append({"op": "gemm_bf16", "label": label, "M": M, "N": N, "K": K, "a_mn": a_mn, "b_mn": b_mn, "ms": ours,
                      "tflops": fl / ours / 1e9, "cublas_ms": lib, "cublas_tflops": fl / lib / 1e9,
@@ -81,14 +83,104 @@ def bench_gemm(args) -> list[dict]:
     return rows
 
 
+def _fb(fn_out, *leaves):
+    """Forward+backward closure with unit upstream gradient."""
+    def run():
+        for t in leaves:
+            t.grad = None
+        out = fn_out()
+        out.backward(torch.ones_like(out))
+    return run
+
+
+def bench_composite(args) -> list[dict]:
+    """Composite ops at the flagship model's shapes: kernels vs the PyTorch restatement on the same GPU."""
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B, optim
+    pk = peaks()
+    dev = "cuda"
+    rows = []
+
+    def add(label, make, algo_bytes=None, flops=None, eager=True):
+        if args.only and args.only != label:
+            return
+        fn = make()
+        ms = time_cuda(fn, iters=args.iters, warmup=args.warmup)
+        row = {"op": label, "ms": ms}
+        if algo_bytes:
+            row["gbs"] = algo_bytes / ms / 1e6
+            row["frac_of_measured_hbm"] = row["gbs"] / pk["hbm_gbs"]
+        if flops:
+            row["tflops"] = flops / ms / 1e9
+            row["frac_of_measured_peak"] = row["tflops"] / pk["bf16_tflops"]
+        if eager and not args.no_eager:
+            with B.use_kernels(False):
+                try:
+                    row["eager_ms"] = time_cuda(make(), iters=max(3, args.iters // 2), warmup=2)
+                    row["speedup_vs_eager"] = row["eager_ms"] / ms
+                except torch.OutOfMemoryError:
+                    row["eager_ms"] = None
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+
+    R, Dm = 16384, 2048
+    x = torch.randn(R, Dm, device=dev).bfloat16().requires_grad_()
+    w = torch.ones(Dm, device=dev).bfloat16().requires_grad_()
+    add("rmsnorm fwd+bwd 16384x2048", lambda: _fb(lambda: ops.rms_norm(x, w), x, w), algo_bytes=R * Dm * 2 * 5)
+    gu = torch.randn(R, 11264, device=dev).bfloat16().requires_grad_()
+    add("swiglu fwd+bwd 16384x5632", lambda: _fb(lambda: ops.swiglu(gu), gu), algo_bytes=R * 5632 * 2 * (3 + 5))
+
+    # cut cross-entropy: 16384 rows, vocab 65536
+    h = (torch.randn(R, Dm, device=dev) * 0.5).bfloat16().requires_grad_()
+    wv = (torch.randn(65536, Dm, device=dev) * 0.02).bfloat16().requires_grad_()
+    tg = torch.randint(0, 65536, (R,), device=dev)
+    add("cut-CE fwd+bwd 16384x65536x2048", lambda: _fb(lambda: ops.linear_cross_entropy(h, wv, tg), h, wv),
+        flops=3 * 2.0 * R * 65536 * Dm)
+
+    # mamba3 chunked scan: B4 S4096 H32 P64 N128 G8
+    Bz, S, H, P, N, G = 4, 4096, 32, 64, 128, 8
+    xs = (torch.randn(Bz, S, H, P, device=dev) * 0.5).bfloat16().requires_grad_()
+    Bm = (torch.randn(Bz, S, G, N, device=dev) * 0.3).bfloat16().requires_grad_()
+    Cm = (torch.randn(Bz, S, G, N, device=dev) * 0.3).bfloat16().requires_grad_()
+    z = torch.randn(Bz, S, H, P, device=dev).bfloat16().requires_grad_()
+    A = (-torch.rand(Bz, S, H, device=dev) - 0.5).requires_grad_()
+    dt = (torch.rand(Bz, S, H, device=dev) * 0.1 + 0.01).requires_grad_()
+    Dp = torch.ones(H, device=dev).requires_grad_()
+    add("mamba3 scan fwd+bwd B4 S4096 H32 P64 N128", lambda: _fb(lambda: ops.mamba3_scan(xs, Bm, Cm, z, A, dt, Dp, chunk_size=64)[0],
+                                                              xs, Bm, Cm, z, A, dt, Dp))
+
+    # masked attention (MLA multi-head form): B4 H16 S4096 dqk192 dv128, causal, no top-k mask
+    q = (torch.randn(4, 4096, 16, 192, device=dev) * 0.3).bfloat16().requires_grad_()
+    k = (torch.randn(4, 4096, 16, 192, device=dev) * 0.3).bfloat16().requires_grad_()
+    v = (torch.randn(4, 4096, 16, 128, device=dev) * 0.3).bfloat16().requires_grad_()
+    att_fl = 4 * 16 * 4096 * 4096 / 2 * 2.0 * (192 + 128) * 3.5
+    add("masked attention fwd+bwd B4 H16 S4096 d192/128", lambda: _fb(lambda: ops.masked_attention(q, k, v)[0], q, k, v), flops=att_fl)
+
+    sc = torch.randn(4 * 4096, 4096, device=dev)
+    add("topk 2048 of 4096, 16384 rows", lambda: (lambda: ops.topk_select(sc, 2048)), algo_bytes=sc.numel() * 4 + 16384 * 2048 * 4)
+
+    n = 64 * 1024 * 1024
+    p_ = torch.randn(n, device=dev).bfloat16(); g_ = torch.randn(n, device=dev).bfloat16()
+    m_ = torch.zeros(n, device=dev); v_ = torch.zeros(n, device=dev)
+    add("adamw 64M bf16 params fp32 moments", lambda: (lambda: optim.fused_adamw_(p_, g_, m_, v_, 1e-3, 0.9, 0.95, 1e-8, 0.1)),
+        algo_bytes=n * (2 + 2 + 2 + 16), eager=False)
+    return rows
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "all"])
+    ap.add_argument("op", choices=["gemm", "composite", "all"])
     ap.add_argument("--json", default=None)
+    ap.add_argument("--only", default=None, help="run the single case with this label (small captures under a profiler)")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-eager", action="store_true")
     args = ap.parse_args(argv)
     rows = []
     if args.op in ("gemm", "all"):
         rows += bench_gemm(args)
+    if args.op in ("composite", "all"):
+        rows += bench_composite(args)
     if args.json:
         with open(args.json, "w") as f:
             json.dump(rows, f, indent=1)
