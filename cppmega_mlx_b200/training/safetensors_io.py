@@ -50,7 +50,7 @@ def plan_layout(tensors: dict[str, torch.Tensor], metadata: dict[str, str] | Non
 
 
 def _raw_bytes(t: torch.Tensor) -> memoryview:
-    t = t.detach().contiguous().cpu()
+    t = t.detach().contiguous().cpu().reshape(-1)
     return memoryview(t.view(torch.uint8).reshape(-1).numpy()) if t.numel() else memoryview(b"")
 
 
