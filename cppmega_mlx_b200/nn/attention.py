@@ -234,9 +234,14 @@ class CausalSelfAttention(nn.Module):
         b, s, _ = hidden_states.shape
         offset = kv_cache.position(layer_idx) if kv_cache is not None else 0
         q = self._rope(self.q_proj(hidden_states).view(b, s, c.num_q_heads, c.q_head_dim), offset)
-        if c.mode == "dsa" and kv_cache is None:
+        if c.mode == "dsa":
             kv = self._rope(self.sparse_kv_proj(hidden_states).view(b, s, c.kv_heads, c.q_head_dim), offset)
-            if isinstance(mask, torch.Tensor):
+            if kv_cache is not None:     # decode: the shared key/value rows are the cache; newest top-k causal keys
+                flat, _ = kv_cache.update_and_fetch_latent(layer_idx, kv.reshape(b, s, -1), None)
+                kv = flat.view(b, flat.shape[1], c.kv_heads, c.q_head_dim)
+                idx = causal_sparse_indices(b, s, c.kv_heads, min(c.sparse_topk, kv.shape[1]), query_offset=offset,
+                                            key_length=kv.shape[1], device=hidden_states.device)
+            elif isinstance(mask, torch.Tensor):
                 idx = sparse_indices_from_attention_mask(mask, batch_size=b, seq_length=s, kv_group=c.kv_heads,
                                                          topk=min(c.sparse_topk, s), key_length=s)
             else:

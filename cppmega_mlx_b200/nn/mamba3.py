@@ -226,7 +226,7 @@ class Mamba3Block(nn.Module):
         B_mimo, C_mimo = self.transform_bc(Bm.reshape(b, s, r, c.ngroups, c.d_state), Cm.reshape(b, s, r, c.ngroups, c.d_state))
         Bg, Cg = (B_mimo.mean(2), C_mimo.mean(2)) if r > 1 else (B_mimo[:, :, 0], C_mimo[:, :, 0])  # [B,S,G,N]
         dt = F.softplus(dd_dt + self.dt_bias.float())
-        # The trapezoid looks one step ahead; across a cache boundary that future step is unknown, as in the reference.
+        # The trapezoid looks one step ahead; across a cache boundary the missing term is added when the next token arrives.
         Bg = Bg * heads_to_group_scale(compute_trapezoidal_scale(dt, trap), c.ngroups)[..., None].to(Bg.dtype)
         # Only the first `ngroups` heads' phases rotate B and C; the full per-head table is needed for the cache only.
         nh_ang = c.nheads if return_cache else c.ngroups
@@ -237,6 +237,13 @@ class Mamba3Block(nn.Module):
         Cg = apply_rope_on_state_dim(Cg, ang_cum)
         A = torch.clamp(-F.softplus(dd_A), max=-c.A_floor)
         state0 = cache.ssm if cache is not None else h0
+        if cache is not None and s > 0 and cache.k is not None and cache.v is not None:
+            # The cached state was built with the last token's look-ahead term missing (its successor was unknown); now that
+            # the successor is here, add x_last ⊗ B_last · dt[0]·(1−σ(trap[0])) so the continuation equals an uninterrupted run.
+            late = heads_to_group_scale(dt[:, :1] * (1.0 - torch.sigmoid(trap[:, :1])), c.ngroups)[:, 0]   # [B,G]
+            late_h = late.repeat_interleave(c.nheads // c.ngroups, dim=1)                                     # [B,H]
+            k_mean = cache.k.float().mean(1) * late_h[..., None]                                              # [B,H,N]
+            state0 = (state0.float() + cache.v.float()[..., None] * k_mean[:, :, None, :]).to(state0.dtype)
         if state0 is not None and tuple(state0.shape) != (b, c.nheads, c.headdim, c.d_state):
             raise ValueError(f"h0 must have shape {(b, c.nheads, c.headdim, c.d_state)}, got {tuple(state0.shape)}")
         y, h = ops.mamba3_scan(x, Bg, Cg, z, A, dt, self.D, state0, chunk_size=c.chunk_size)
@@ -247,8 +254,9 @@ class Mamba3Block(nn.Module):
             nxt = cache if cache is not None else self.zero_cache_state(b, dtype=hidden_states.dtype, device=hidden_states.device)
             return out, nxt
         heads_per_g = c.nheads // c.ngroups
-        k_src = B_mimo.repeat_interleave(heads_per_g, dim=3)  # [B,S,r,H,N]
-        k_last = torch.stack([apply_rope_on_state_dim(k_src[:, -1:, i], ang_cum[:, -1:])[:, 0] for i in range(r)], dim=1)
+        # Rotated exactly as the scan consumed it (group g turns with the phase of head index g), then laid out per head.
+        k_last = torch.stack([apply_rope_on_state_dim(B_mimo[:, -1:, i], ang_cum[:, -1:])[:, 0] for i in range(r)], dim=1)
+        k_last = k_last.repeat_interleave(heads_per_g, dim=2)  # [B,r,H,N]
         hist = c.d_conv - 1
         src = xBC_raw if prefix is None else torch.cat([prefix.to(xBC_raw.dtype), xBC_raw], dim=1)
         conv_state = src[:, -hist:] if src.shape[1] >= hist else F.pad(src, (0, 0, hist - src.shape[1], 0))
