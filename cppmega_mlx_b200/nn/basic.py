@@ -104,6 +104,7 @@ class FeedForward(nn.Module):
         else:
             self.up_proj = Linear(d_model, hidden)
         self.down_proj = Linear(hidden, d_model, zero_init=zero_init_out)
+        self._redo_probe = None   # set by training.plasticity.ReDoDiagnostics.attach
 
     def forward(self, x):
         if self.activation == "swiglu":
@@ -112,4 +113,6 @@ class FeedForward(nn.Module):
             h = F.gelu(self.up_proj(x))
         else:
             h = ops.squared_relu(self.up_proj(x))
+        if self._redo_probe is not None:
+            self._redo_probe(h)
         return self.down_proj(h)
