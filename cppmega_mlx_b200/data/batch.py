@@ -73,6 +73,11 @@ class LMTokenBatch:
               for f in fields(self)}
         return LMTokenBatch(**kw)
 
+    def slice_rows(self, start: int, stop: int) -> "LMTokenBatch":
+        """Rows ``start:stop`` of every field (a data-parallel rank's share of a global batch)."""
+        kw = {f.name: (getattr(self, f.name)[start:stop] if getattr(self, f.name) is not None else None) for f in fields(self)}
+        return LMTokenBatch(**kw)
+
     def pin_memory(self) -> "LMTokenBatch":
         kw = {f.name: (getattr(self, f.name).pin_memory() if getattr(self, f.name) is not None else None) for f in fields(self)}
         return LMTokenBatch(**kw)
