@@ -154,7 +154,9 @@ def bench_composite(args) -> list[dict]:
     k = (torch.randn(4, 4096, 16, 192, device=dev) * 0.3).bfloat16().requires_grad_()
     v = (torch.randn(4, 4096, 16, 128, device=dev) * 0.3).bfloat16().requires_grad_()
     att_fl = 4 * 16 * 4096 * 4096 / 2 * 2.0 * (192 + 128) * 3.5
-    add("masked attention fwd+bwd B4 H16 S4096 d192/128", lambda: _fb(lambda: ops.masked_attention(q, k, v)[0], q, k, v), flops=att_fl)
+    add("masked attention fwd+bwd B4 H16 S4096 d192/128",
+        lambda: _fb(lambda: (ops.masked_attention(q, k, v) if B.kernels_enabled() else ops.masked_attention_reference(q, k, v))[0], q, k, v),
+        flops=att_fl)
 
     sc = torch.randn(4 * 4096, 4096, device=dev)
     add("topk 2048 of 4096, 16384 rows", lambda: (lambda: ops.topk_select(sc, 2048)), algo_bytes=sc.numel() * 4 + 16384 * 2048 * 4)

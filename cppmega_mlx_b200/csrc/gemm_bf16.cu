@@ -63,6 +63,8 @@ struct GemmParams {
   int mask_words;            // words per row
   float scale, scale2;
   float* stats;              // SOFTMAX_STATS output: float2 per (problem, row, tile_n, half)
+  const int* tile_group;     // grouped (MoE) mode: B's dim-2 index for each 128-row tile of A / C; nullptr = batched rule
+  const int* k_ranges;       // grouped wgrad: contraction range [k_begin, k_end) per dim-2 problem (multiples of 64)
   int* status;
 };
 
@@ -126,9 +128,13 @@ __device__ __forceinline__ TileCoord tile_coords(int t, int num_m, int num_n, in
 __device__ __forceinline__ bool tile_skipped(int flags, int m0, int n0) {
   return (flags & GEMM_CAUSAL_SKIP) && n0 >= m0 + GEMM_BM;
 }
-__device__ __forceinline__ void k_range(int flags, int m0, int num_kb, int& kb0, int& kb1) {
+__device__ __forceinline__ void k_range(int flags, int m0, int num_kb, const int* k_ranges, int i2, int& kb0, int& kb1) {
   kb0 = (flags & GEMM_K_LOWER) ? m0 / GEMM_BK : 0;
   kb1 = (flags & GEMM_K_UPPER) ? min(num_kb, (m0 + GEMM_BM + GEMM_BK - 1) / GEMM_BK) : num_kb;
+  if (k_ranges != nullptr) {
+    kb0 = max(kb0, k_ranges[2 * i2] / GEMM_BK);
+    kb1 = min(kb1, (k_ranges[2 * i2 + 1] + GEMM_BK - 1) / GEMM_BK);
+  }
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -189,10 +195,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3);
         const int m0 = tc.tm * GEMM_BM, n0 = tc.tn * BN;
-        const int a2 = tc.i2 / p.a_div2, b2 = tc.i2 / p.b_div2;
+        const int a2 = tc.i2 / p.a_div2;
+        const int b2 = p.tile_group != nullptr ? p.tile_group[tc.tm] : tc.i2 / p.b_div2;
         if (tile_skipped(p.flags, m0, n0)) continue;
         int kb0, kb1;
-        k_range(p.flags, m0, num_kb, kb0, kb1);
+        k_range(p.flags, m0, num_kb, p.k_ranges, tc.i2, kb0, kb1);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) {
             ok = false;
@@ -236,7 +243,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int m0 = tc.tm * GEMM_BM;
         if (tile_skipped(p.flags, m0, tc.tn * BN)) continue;
         int kb0, kb1;
-        k_range(p.flags, m0, num_kb, kb0, kb1);
+        k_range(p.flags, m0, num_kb, p.k_ranges, tc.i2, kb0, kb1);
         const int buf = local & 1;
         const uint32_t aphase = (local >> 1) & 1;
         ++local;
@@ -292,6 +299,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       ++local;
       if (!mbar_wait(&tfull_bar[buf], aphase, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
+      bool empty_k = false;
+      if (p.k_ranges != nullptr) {  // a problem with no contraction steps leaves the accumulator unwritten: emit zeros
+        int kb0, kb1;
+        k_range(p.flags, tc.tm * GEMM_BM, num_kb, p.k_ranges, tc.i2, kb0, kb1);
+        empty_k = kb0 >= kb1;
+      }
       const int row0 = tc.tm * GEMM_BM + quarter * 32;
       const int row = row0 + lane;
       const int ncol0 = tc.tn * BN + half * (BN / 2);
@@ -316,6 +329,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t r[32];
         tmem_ld_x32(taddr + c * 32, r);
         tmem_wait_ld();
+        if (empty_k) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
         const int col0 = ncol0 + c * 32;
         if (attn) {
           // keys this row may see inside the 32-column chunk: mask word ∧ causal ∧ in range
@@ -579,6 +596,9 @@ struct GemmArgs {
   int mask_words;
   float scale, scale2;
   float* stats;
+  const int* tile_group;
+  const int* k_ranges;
+  int b_groups;  // grouped mode: number of dim-2 slices of B (independent of the problem batch count)
   int* status;
   int max_ctas;
   cudaStream_t stream;
@@ -590,7 +610,7 @@ static int launch_gemm(const GemmArgs& g) {
   CUtensorMap tmA, tmB, tmC;
   int rc;
   uint64_t nbA[3] = {g.nb[0] / g.a_div2, g.nb[1], g.nb[2]};
-  uint64_t nbB[3] = {g.nb[0] / g.b_div2, g.nb[1], g.nb[2]};
+  uint64_t nbB[3] = {g.tile_group != nullptr ? static_cast<uint64_t>(g.b_groups) : g.nb[0] / g.b_div2, g.nb[1], g.nb[2]};
   // K-major operand stored [rows=M|N, cols=K]; MN-major operand stored [rows=K, cols=M|N].
   if (A_MN)
     rc = make_tmap_5d(&tmA, g.A, 2, g.K, g.M, g.lda, nbA, g.sA, cmb::GEMM_BK, 64);
@@ -632,6 +652,7 @@ static int launch_gemm(const GemmArgs& g) {
   p.ldc = g.ldc; p.sC2 = g.sC[0]; p.sC3 = g.sC[1]; p.sC4 = g.sC[2];
   p.mask = g.mask; p.mask_sb = g.mask_sb; p.mask_words = g.mask_words;
   p.scale = g.scale; p.scale2 = g.scale2; p.stats = g.stats;
+  p.tile_group = g.tile_group; p.k_ranges = g.k_ranges;
   p.status = g.status;
   kern<<<grid, cmb::GEMM_THREADS, Cfg::SMEM_BYTES, g.stream>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 104;
@@ -673,10 +694,12 @@ extern "C" int cmb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   return cmb_host::dispatch(g, a_mn_major, b_mn_major);
 }
 
-// Batched form. `ip` = {M, N, K, a_mn, b_mn, flags, a_div2, b_div2, max_ctas, mask_words}; `lp` = {lda, ldb, ldc, nb2,
+// Batched form. `ip` = {M, N, K, a_mn, b_mn, flags, a_div2, b_div2, max_ctas, mask_words, b_groups}; `lp` = {lda, ldb, ldc, nb2,
 // nb3, nb4, sA2, sA3, sA4, sB2, sB3, sB4, sC2, sC3, sC4, sv2, sv3, sv4, mask_sb} (element counts / strides).
-// `pp` = {row_vec, col_vec, aux, mask, stats} device pointers (any may be null). Flags select the epilogue, see the
-// enum at the top of this file.
+// `pp` = {row_vec, col_vec, aux, mask, stats, tile_group, k_ranges} device pointers (any may be null). Flags select the
+// epilogue, see the enum at the top of this file. Grouped (MoE) use: `tile_group[i]` names B's dim-2 slice for the i-th
+// 128-row tile of A/C (A and C plain 2-D, B stacked per expert); `k_ranges[2e], k_ranges[2e+1]` bound the contraction
+// of dim-2 problem e (wgrad over one expert's rows of the token-sorted buffers).
 extern "C" int cmb_gemm_bf16_batched(const void* A, const void* B, void* C, const int* ip, const long long* lp,
                                      const void* const* pp, float scale, float scale2, int* status, void* stream) {
   cmb_host::GemmArgs g{};
@@ -690,6 +713,9 @@ extern "C" int cmb_gemm_bf16_batched(const void* A, const void* B, void* C, cons
   g.mask_sb = lp[18];
   g.row_vec = static_cast<const float*>(pp[0]); g.col_vec = static_cast<const float*>(pp[1]);
   g.aux = pp[2]; g.mask = static_cast<const unsigned*>(pp[3]); g.stats = static_cast<float*>(const_cast<void*>(pp[4]));
+  g.tile_group = static_cast<const int*>(pp[5]); g.k_ranges = static_cast<const int*>(pp[6]);
+  g.b_groups = ip[10];
+  if (g.tile_group != nullptr && g.b_groups <= 0) return 109;
   g.scale = scale;
   g.scale2 = scale2;
   g.status = status; g.stream = static_cast<cudaStream_t>(stream);

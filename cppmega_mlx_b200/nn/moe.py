@@ -219,6 +219,16 @@ class MoE(nn.Module):
             return ep_moe_forward(self, flat, top_idx, top_w)
         E = self.config.num_experts
         flat_e = top_idx.reshape(-1)
+        from ..ops import grouped_gemm_cuda as GG
+        if ops.kernels_enabled() and GG.supported(flat, self.experts.w_gate_up) and self.config.activation == "swiglu":
+            # GPU path: padded expert-sorted buffer + grouped tcgen05 GEMMs; nothing here synchronises with the host.
+            L = GG.build_layout(flat_e, E)
+            tok = torch.div(L.order, k, rounding_mode="floor")
+            xp = GG.scatter_to_padded(flat, tok, L)
+            h = ops.swiglu(GG.grouped_linear_padded(xp, self.experts.w_gate_up, L))
+            yp = GG.grouped_linear_padded(h, self.experts.w_down, L)
+            ys = yp.index_select(0, L.slot) * top_w.reshape(-1)[L.order].to(yp.dtype)[:, None]
+            return torch.zeros_like(flat).index_add_(0, tok, ys)
         order = torch.argsort(flat_e, stable=True)
         counts = torch.bincount(flat_e, minlength=E)
         tok = torch.div(order, k, rounding_mode="floor")

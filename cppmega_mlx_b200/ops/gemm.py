@@ -77,21 +77,24 @@ def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, 
                  accumulate: bool = False, row_vec: torch.Tensor | None = None, col_vec: torch.Tensor | None = None,
                  sv: tuple[int, int, int] = (0, 0, 0), max_ctas: int = 0, flags: int = 0, aux: torch.Tensor | None = None,
                  mask: torch.Tensor | None = None, mask_words: int = 0, mask_sb: int = 0, scale: float = 1.0,
-                 scale2: float = 0.0, stats: torch.Tensor | None = None, out_f32: bool | None = None) -> torch.Tensor | None:
+                 scale2: float = 0.0, stats: torch.Tensor | None = None, out_f32: bool | None = None,
+                 tile_group: torch.Tensor | None = None, k_ranges: torch.Tensor | None = None, b_groups: int = 0) -> torch.Tensor | None:
     """Strided-batched C (+)= A·Bᵀ. ``a``/``b``/``out`` only supply base pointers; all geometry is explicit:
     pitches ``ld*`` and per-operand element strides over the three batch dims ``nb = (n2, n3, n4)``.
     ``a_div2``/``b_div2`` let ``div`` consecutive dim-2 problems share one operand slice (the operand then has
     ``n2 // div`` slices).  With ``row_vec``/``col_vec`` (fp32) and no explicit epilogue flag the epilogue writes
     ``acc · exp(row_vec[t] − col_vec[s]) · [s ≤ t]``; with ``row_vec`` alone, ``acc · exp(row_vec[t])``.
-    ``flags`` adds the causal-range and attention epilogue modes (see ``csrc/gemm_bf16.cu``)."""
+    ``flags`` adds the causal-range and attention epilogue modes (see ``csrc/gemm_bf16.cu``).  Grouped (MoE) use:
+    ``tile_group`` (int32, one entry per 128-row tile of A/C) picks B's dim-2 slice among ``b_groups``; ``k_ranges``
+    (int32 ``[n2, 2]``) bounds the contraction of each dim-2 problem."""
     lib = B.load_library()
     f32 = (out is not None and out.dtype == torch.float32) if out_f32 is None else out_f32
     fl = flags | (OUT_F32 if f32 else 0) | (ACCUMULATE if accumulate else 0)
     if row_vec is not None and not (flags & (EPI_EXP_MASK | EPI_DS)):
         fl |= EPI_DECAY_MASK if col_vec is not None else EPI_ROW_EXP
-    ip = (ctypes.c_int * 10)(M, N, K, int(a_mn), int(b_mn), fl, a_div2, b_div2, max_ctas, mask_words)
+    ip = (ctypes.c_int * 11)(M, N, K, int(a_mn), int(b_mn), fl, a_div2, b_div2, max_ctas, mask_words, int(b_groups))
     lp = (ctypes.c_longlong * 19)(lda, ldb, ldc, *nb, *sA, *sB, *sC, *sv, mask_sb)
-    pp = (ctypes.c_void_p * 5)(*(None if t is None else t.data_ptr() for t in (row_vec, col_vec, aux, mask, stats)))
+    pp = (ctypes.c_void_p * 7)(*(None if t is None else t.data_ptr() for t in (row_vec, col_vec, aux, mask, stats, tile_group, k_ranges)))
     st = B.status_buffer(a.device)
     rc = lib.cmb_gemm_bf16_batched(B.ptr(a), B.ptr(b), B.ptr(out), ip, lp, pp, ctypes.c_float(scale), ctypes.c_float(scale2), B.ptr(st),
                                    B.stream_ptr())

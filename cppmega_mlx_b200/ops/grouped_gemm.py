@@ -1,8 +1,7 @@
 """Grouped (per-expert) linear: rows of ``xs`` are sorted by expert, expert e owns ``counts[e]`` rows.
 
-``y[r] = xs[r] @ w[e(r)]ᵀ`` with ``w`` [E, out, in].  CUDA path: ``csrc/grouped_gemm.cu`` walks a
-device-side tile list built from the counts (no host sync), same tcgen05 mainloop as the dense GEMM.
-Oracle: the per-expert loop below.  The reference has no grouped kernel (it loops densely over all
+``y[r] = xs[r] @ w[e(r)]ᵀ`` with ``w`` [E, out, in].  CUDA path: ``ops/grouped_gemm_cuda.py`` (padded expert-sorted
+layout built on the device, the tcgen05 GEMM of ``csrc/gemm_bf16.cu`` in grouped mode).  Oracle: the per-expert loop below.  The reference has no grouped kernel (it loops densely over all
 experts, ``cppmega_mlx/nn/moe.py:166-228``; the grouped ABI it only describes is
 ``cppmega_mlx/nn/_mxfp8_bridge.py:635-734``).
 """
@@ -49,24 +48,7 @@ class _GroupedLinearRef(torch.autograd.Function):
         return gx, gw, None
 
 
-class _GroupedLinearCuda(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, xs, w, counts):
-        from .grouped_gemm_cuda import grouped_fwd
-        ctx.save_for_backward(xs, w, counts)
-        return grouped_fwd(xs, w, counts)
-
-    @staticmethod
-    def backward(ctx, g):
-        from .grouped_gemm_cuda import grouped_dgrad, grouped_wgrad
-        xs, w, counts = ctx.saved_tensors
-        g = g.contiguous()
-        return grouped_dgrad(g, w, counts), grouped_wgrad(g, xs, counts, w.shape), None
-
-
 def grouped_linear(xs: torch.Tensor, w: torch.Tensor, counts) -> torch.Tensor:
-    if B.on_gpu(xs, w) and xs.dtype == torch.bfloat16 and isinstance(counts, torch.Tensor):
-        from . import grouped_gemm_cuda
-        if grouped_gemm_cuda.supported(xs, w):
-            return _GroupedLinearCuda.apply(xs.contiguous(), w, counts.int())
+    """Reference form over expert-sorted rows (CPU path and the eager comparison arm; reads ``counts`` on the host).
+    The GPU product path is ``grouped_gemm_cuda.grouped_linear_padded`` over a padded layout built on the device."""
     return _GroupedLinearRef.apply(xs, w, _offsets(counts))
