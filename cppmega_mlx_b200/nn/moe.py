@@ -239,6 +239,16 @@ class MoE(nn.Module):
         out.index_add_(0, tok, ys)
         return out
 
+    def local_expert_forward(self, xs: torch.Tensor, local_e: torch.Tensor) -> torch.Tensor:
+        """Rows ``xs`` sorted by local expert id ``local_e`` → expert outputs in the same order (expert-parallel ranks)."""
+        from ..ops import grouped_gemm_cuda as GG
+        if ops.kernels_enabled() and GG.supported(xs, self.experts.w_gate_up) and self.config.activation == "swiglu" and xs.shape[0] > 0:
+            L = GG.build_layout(local_e, self.local_experts)          # rows are already sorted: order is the identity
+            xp = GG.scatter_to_padded(xs, L.order, L)
+            h = ops.swiglu(GG.grouped_linear_padded(xp, self.experts.w_gate_up, L))
+            return GG.grouped_linear_padded(h, self.experts.w_down, L).index_select(0, L.slot)
+        return self.experts(xs, torch.bincount(local_e, minlength=self.local_experts))
+
     def forward(self, x: torch.Tensor) -> MoEOutput:
         c = self.config
         router = self.router(x)

@@ -90,6 +90,7 @@ def run_1f1b(stage: PipelineStage, micro_inputs: list[torch.Tensor] | None, micr
     saved_in: dict[int, torch.Tensor] = {}
     saved_out: dict[int, torch.Tensor] = {}
     total = None
+    pending: list = []   # (work handle, tensor kept alive): sends are asynchronous so that the two directions cannot block each other
     for kind, i in one_f_one_b_order(stage.stage, stage.num_stages, num_micro):
         if kind == "F":
             if stage.first:
@@ -106,7 +107,8 @@ def run_1f1b(stage: PipelineStage, micro_inputs: list[torch.Tensor] | None, micr
                 total = loss.detach() if total is None else total + loss.detach()
             else:
                 saved_out[i] = y
-                dist.send(y.detach().contiguous(), dst=next_rank, group=group)
+                buf = y.detach().contiguous()
+                pending.append((dist.isend(buf, dst=next_rank, group=group), buf))
         else:
             y, x = saved_out.pop(i), saved_in.pop(i)
             if stage.last:
@@ -116,5 +118,8 @@ def run_1f1b(stage: PipelineStage, micro_inputs: list[torch.Tensor] | None, micr
                 dist.recv(g, src=next_rank, group=group)
                 y.backward(g)
             if not stage.first:
-                dist.send(x.grad.contiguous(), dst=prev_rank, group=group)
+                buf = x.grad.contiguous()
+                pending.append((dist.isend(buf, dst=prev_rank, group=group), buf))
+    for work, _ in pending:
+        work.wait()
     return PipelineResult(total, num_micro)

@@ -1,0 +1,138 @@
+"""TP (+SP), EP and PP on CPU ranks (gloo): each must reproduce the single-process result."""
+import pytest
+import torch
+
+from cppmega_mlx_b200.parallel import pp as PP
+from cppmega_mlx_b200.parallel import state as PS
+from tests._dist_util import run_ranks
+
+pytestmark = pytest.mark.distributed
+
+
+def test_group_layout_is_a_partition():
+    lay = PS.group_ranks(8, tp=2, pp=2, ep=2)
+    assert lay["tp"] == [[0, 1], [2, 3], [4, 5], [6, 7]]
+    assert lay["dp"] == [[0, 2], [1, 3], [4, 6], [5, 7]]
+    assert lay["pp"] == [[0, 4], [1, 5], [2, 6], [3, 7]]
+    for kind in lay:
+        flat = sorted(r for g in lay[kind] for r in g)
+        assert flat == list(range(8)), kind
+    assert PS.rank_coordinates(5, 8, 2, 2) == (1, 0, 1)
+    with pytest.raises(ValueError):
+        PS.group_ranks(8, tp=3, pp=1, ep=1)
+    with pytest.raises(ValueError):
+        PS.group_ranks(8, tp=2, pp=2, ep=3)
+    assert PP.split_layers(7, 3) == [range(0, 3), range(3, 5), range(5, 7)]
+    assert PP.one_f_one_b_order(0, 2, 3) == [("F", 0), ("F", 1), ("B", 0), ("F", 2), ("B", 1), ("B", 2)]
+    assert PP.one_f_one_b_order(1, 2, 3) == [("F", 0), ("B", 0), ("F", 1), ("B", 1), ("F", 2), ("B", 2)]
+    for s in range(4):       # every stage runs each micro-batch once forward and once backward, B after F
+        o = PP.one_f_one_b_order(s, 4, 6)
+        assert sorted(i for k, i in o if k == "F") == list(range(6)) == sorted(i for k, i in o if k == "B")
+        assert all(o.index(("F", i)) < o.index(("B", i)) for i in range(6))
+
+
+def _tp_rank(rank, world, sp):
+    from cppmega_mlx_b200.nn.basic import FeedForward, RMSNorm
+    from cppmega_mlx_b200.parallel import tp as TP
+    st = PS.init_parallel_state(tp=world)
+    torch.manual_seed(0)
+    norm, ffn = RMSNorm(16), FeedForward(16, 24, "swiglu")
+    x = torch.randn(2, 8, 16)
+    ref_in = x.clone().requires_grad_()
+    ref = ffn(norm(ref_in))
+    ref.square().sum().backward()
+    ref_g = {"norm": norm.weight.grad.clone(), "up": ffn.gate_up_proj.weight.grad.clone(), "down": ffn.down_proj.weight.grad.clone(),
+             "x": ref_in.grad.clone()}
+    norm.weight.grad = None
+    tpf = TP.TPFeedForward(ffn, st.tp_group, sequence_parallel=sp)
+    xin = x.clone().requires_grad_()
+    h = TP.scatter_sequence(xin, st.tp_group) if sp else xin
+    out = tpf(norm(h))
+    full = TP._all_gather_dim(out.detach(), st.tp_group, 1) if sp else out.detach()
+    assert torch.allclose(full, ref.detach(), atol=1e-5)
+    out.square().sum().backward()
+    if sp:
+        TP.allreduce_replicated_grads(torch.nn.ModuleList([norm, tpf]), st.tp_group)
+        gx = xin.grad.clone()
+        torch.distributed.all_reduce(gx)
+    else:
+        gx = xin.grad
+    assert torch.allclose(gx, ref_g["x"], atol=1e-4)
+    assert torch.allclose(norm.weight.grad, ref_g["norm"], atol=1e-4)
+    assert torch.allclose(tpf.up.weight.grad, TP.shard_rows(ref_g["up"], st.tp_group, blocks=2), atol=1e-4)
+    assert torch.allclose(tpf.down.weight.grad, TP.shard_cols(ref_g["down"], st.tp_group), atol=1e-4)
+    return True
+
+
+@pytest.mark.parametrize("sp", [False, True])
+def test_tensor_parallel_ffn_matches_single_rank(sp):
+    assert all(run_ranks(_tp_rank, 2, sp))
+
+
+def _ep_rank(rank, world):
+    from cppmega_mlx_b200.nn.moe import MoE, MoEConfig
+    from cppmega_mlx_b200.parallel import ep as EP
+    st = PS.init_parallel_state(ep=world)
+    cfg = MoEConfig(d_model=16, num_experts=4, top_k=2, expert_hidden_size=8, shared_expert_hidden_size=8, scoring="sigmoid",
+                    aux_loss_free=True)
+    torch.manual_seed(0)
+    full = MoE(cfg)
+    torch.manual_seed(100)
+    xs = [torch.randn(1, 6 + r, 16) for r in range(world)]            # a different token count per rank
+    ref_outs = []
+    for x in xs:
+        ref_outs.append(full(x).output)
+    sum(o.square().sum() for o in ref_outs).backward()
+    local = MoE(cfg, ep_group=st.ep_group)
+    EP.shard_experts_(full, local)
+    assert local.local_experts == 2 and local.experts.w_down.shape[0] == 2
+    out = local(xs[rank]).output
+    assert torch.allclose(out, ref_outs[rank].detach(), atol=1e-5)
+    out.square().sum().backward()
+    EP.allreduce_replicated_grads(local, st.ep_group)
+    sl = slice(rank * 2, rank * 2 + 2)
+    assert torch.allclose(local.experts.w_gate_up.grad, full.experts.w_gate_up.grad[sl], atol=1e-4)
+    assert torch.allclose(local.experts.w_down.grad, full.experts.w_down.grad[sl], atol=1e-4)
+    assert torch.allclose(local.router.gate.weight.grad, full.router.gate.weight.grad, atol=1e-4)
+    assert torch.allclose(local.shared_expert.down_proj.weight.grad, full.shared_expert.down_proj.weight.grad, atol=1e-4)
+    return True
+
+
+def test_expert_parallel_matches_single_rank():
+    assert all(run_ranks(_ep_rank, 2))
+
+
+def _pp_rank(rank, world):
+    from cppmega_mlx_b200.ops import linear_cross_entropy
+    from cppmega_mlx_b200.recipes.model_factory import build_local_gb10_quarter_tiny_smoke_model
+    st = PS.init_parallel_state(pp=world)
+    torch.manual_seed(0)
+    model = build_local_gb10_quarter_tiny_smoke_model(pattern="AEMR", depth=4, dsa_a_layer_ranks=(), mtp_enabled=False)
+    torch.manual_seed(1)
+    micro = [torch.randint(4, 100, (2, 9)) for _ in range(3)]
+
+    def loss_of(hidden, lm_head, tgt):
+        return linear_cross_entropy(hidden.reshape(-1, hidden.shape[-1]), lm_head.weight, tgt.reshape(-1))
+    ref = sum(loss_of(model.decoder_hidden_states(m[:, :-1]), model.lm_head, m[:, 1:]) for m in micro) / 3
+    ref.backward()
+    ref_grads = {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}
+    model.zero_grad()
+    stage = PP.PipelineStage(model, st.pp_rank, world)
+    res = PP.run_1f1b(stage, [m[:, :-1] for m in micro], [m[:, 1:] for m in micro], num_micro=3, act_shape=(2, 8, model.config.hidden_size),
+                      act_dtype=torch.float32, loss_fn=lambda s, h, t: loss_of(h, s.lm_head, t), prev_rank=st.pp_prev, next_rank=st.pp_next)
+    if stage.last:
+        assert torch.allclose(res.loss, ref.detach(), atol=1e-5)
+    owned = {f"layers.{i}." for i in stage.layer_range}
+    checked = 0
+    for n, p in model.named_parameters():
+        mine = any(n.startswith(o) for o in owned) or (stage.first and n.startswith(("token_embedding", "position_embedding"))) or \
+            (stage.last and n.startswith(("norm.", "lm_head")))
+        if mine and n in ref_grads:
+            assert p.grad is not None and torch.allclose(p.grad, ref_grads[n], atol=1e-4), n
+            checked += 1
+    return checked
+
+
+def test_pipeline_1f1b_matches_single_rank():
+    counts = run_ranks(_pp_rank, 2)
+    assert all(c > 0 for c in counts)
