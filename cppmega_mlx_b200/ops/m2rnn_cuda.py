@@ -1,13 +1,94 @@
-"""ctypes front-end of the M2RNN recurrence kernels (csrc/m2rnn.cu)."""
+"""ctypes front-end of the M2RNN recurrence kernels (``csrc/m2rnn.cu``): forward (optionally recording h_{t-1} per step) and
+backward (recompute tanh from the recorded states, reverse sweep).  Handles grouped head counts without materialising broadcast
+copies: the kernels index q/k/v/W/f by ``head // (H / n)``; gradients come back per expanded head and are folded here."""
 from __future__ import annotations
+
+import ctypes
+
+import torch
 
 from . import _backend as B
 
+SUPPORTED_K = (32, 64)
+SUPPORTED_V = 16
+
+
+def _token_strided(t: torch.Tensor) -> bool:
+    """[B,S,n,d] with unit stride on d, heads packed (stride d) — any batch / token stride (a slice of a packed projection)."""
+    return t.stride(3) == 1 and t.stride(2) == t.shape[3] and t.data_ptr() % 4 == 0
+
 
 def supported(q, k, v, W, f) -> bool:
+    if not (B.kernels_enabled() and B.has_library()):
+        return False
     lib = B.load_library()
-    return hasattr(lib, "cmb_m2rnn_fwd") and False
+    if not hasattr(lib, "cmb_m2rnn_fwd"):
+        return False
+    H = max(q.shape[2], k.shape[2], v.shape[2], W.shape[0], f.shape[2])
+    return (q.shape[3] in SUPPORTED_K and k.shape[3] == q.shape[3] and v.shape[3] == SUPPORTED_V and tuple(W.shape[1:]) == (16, 16)
+            and all(H % n == 0 for n in (q.shape[2], k.shape[2], v.shape[2], W.shape[0], f.shape[2]))
+            and all(_token_strided(t) for t in (q, k, v)) and q.shape[1] > 0)
 
 
-def apply(q, k, v, W, f, h0):  # pragma: no cover - GPU only
-    raise NotImplementedError
+def _geom(q, k, v, W, f):
+    b, s, nq, K = q.shape
+    H = max(nq, k.shape[2], v.shape[2], W.shape[0], f.shape[2])
+    ip = (ctypes.c_int * 10)(b, s, H, K, v.shape[3], nq, k.shape[2], v.shape[2], W.shape[0], f.shape[2])
+    lp = (ctypes.c_longlong * 6)(q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1))
+    return H, ip, lp
+
+
+def _fold(g: torch.Tensor, n: int, dim: int = 2) -> torch.Tensor:
+    """Sum gradients of expanded heads back onto the ``n`` heads that were shared."""
+    H = g.shape[dim]
+    if n == H:
+        return g
+    shape = list(g.shape)
+    shape[dim:dim + 1] = [n, H // n]
+    return g.reshape(shape).sum(dim + 1)
+
+
+class _M2RNNFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, W, f, h0):
+        lib = B.load_library()
+        b, s, _, K = q.shape
+        V = v.shape[3]
+        H, ip, lp = _geom(q, k, v, W, f)
+        Wf, ff = W.float().contiguous(), f.float().contiguous()
+        h0f = None if h0 is None else h0.float().contiguous()
+        need = any(t.requires_grad for t in (q, k, v, W, f) + ((h0,) if h0 is not None else ()))
+        y = torch.empty(b, s, H, V, dtype=torch.bfloat16, device=q.device)
+        h_last = torch.empty(b, H, K, V, dtype=torch.float32, device=q.device)
+        hist = torch.empty(b, H, s, K, V, dtype=torch.bfloat16, device=q.device) if need else None
+        B.check(lib.cmb_m2rnn_fwd(B.ptr(q), B.ptr(k), B.ptr(v), B.ptr(ff), B.ptr(Wf), B.ptr(h0f), B.ptr(y), B.ptr(h_last), B.ptr(hist),
+                                  ip, lp, B.stream_ptr()), "m2rnn_fwd")
+        ctx.save_for_backward(q, k, v, Wf, ff, hist)
+        ctx.meta = (W.dtype, f.dtype, W.shape[0], f.shape[2], h0 is not None, None if h0 is None else h0.dtype)
+        return y, h_last.to(q.dtype if h0 is None else h0.dtype)
+
+    @staticmethod
+    def backward(ctx, gy, gh):
+        lib = B.load_library()
+        q, k, v, Wf, ff, hist = ctx.saved_tensors
+        w_dtype, f_dtype, nw, nf, has_h0, h0_dtype = ctx.meta
+        b, s, nq, K = q.shape
+        V = v.shape[3]
+        H, ip, lp = _geom(q, k, v, Wf, ff)
+        dev = q.device
+        gy = gy.to(torch.bfloat16).contiguous()
+        ghf = None if gh is None else gh.float().contiguous()
+        dq = torch.empty(b, s, H, K, dtype=torch.float32, device=dev)
+        dk = torch.empty_like(dq)
+        dv = torch.empty(b, s, H, V, dtype=torch.float32, device=dev)
+        df = torch.empty(b, s, H, dtype=torch.float32, device=dev)
+        dW = torch.empty(b, H, V, V, dtype=torch.float32, device=dev)
+        dh0 = torch.empty(b, H, K, V, dtype=torch.float32, device=dev)
+        B.check(lib.cmb_m2rnn_bwd(B.ptr(q), B.ptr(k), B.ptr(v), B.ptr(ff), B.ptr(Wf), B.ptr(hist), B.ptr(gy), B.ptr(ghf), B.ptr(dq),
+                                  B.ptr(dk), B.ptr(dv), B.ptr(df), B.ptr(dW), B.ptr(dh0), ip, lp, B.stream_ptr()), "m2rnn_bwd")
+        return (_fold(dq, nq).to(q.dtype), _fold(dk, k.shape[2]).to(k.dtype), _fold(dv, v.shape[2]).to(v.dtype),
+                _fold(dW.sum(0), nw, 0).to(w_dtype), _fold(df, nf).to(f_dtype), dh0.to(h0_dtype) if has_h0 else None)
+
+
+def apply(q, k, v, W, f, h0):
+    return _M2RNNFn.apply(q, k, v, W, f, h0)

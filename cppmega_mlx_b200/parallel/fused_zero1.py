@@ -58,7 +58,7 @@ class FusedZeRO1Comm:
         if not self._supported(opt):
             return False
         from ..ops.optim import newton_schulz5_bf16_
-        from ..training.optimizers import AdamWFP32Moments
+        from ..training.optimizers import AdamWFP32Moments, newton_schulz5
         lib = B.load_library()
         flat, W, rank = self.flat, opt.world, opt.rank
         gp, pp = self.grads_buf.peer_ptrs, self.params_buf.peer_ptrs
@@ -87,14 +87,17 @@ class FusedZeRO1Comm:
                 goff = owner * flat.segment + off
                 s = muon.state_for(name, p)
                 rows, cols = p.shape
-                if n % 8 or rows % 8 or cols % 8:
-                    raise RuntimeError(f"fused Muon needs dimensions that are multiples of 8, got {tuple(p.shape)} for {name}")
+                if n % 8:
+                    raise RuntimeError(f"fused Muon needs an element count that is a multiple of 8, got {tuple(p.shape)} for {name}")
                 u = torch.empty(rows, cols, dtype=torch.bfloat16, device=p.device)
                 sumsq = torch.zeros(1, dtype=torch.float32, device=p.device)
                 B.check(lib.cmb_zero1_muon_reduce(gp, pp, rank, W, I64(goff), I64(n), B.ptr(s["v"]), B.ptr(u), B.ptr(sumsq),
                                                   F32(muon.momentum), F32(muon.weight_decay), int(muon.nesterov), st()),
                         "zero1_muon_reduce")
-                o = newton_schulz5_bf16_(u, sumsq, muon.ns_steps)
+                if rows % 8 or cols % 8:   # too narrow for the tensor-core iteration (e.g. a 4-row gate): same maths in PyTorch ops
+                    o = newton_schulz5(u, steps=muon.ns_steps, ns_carrier="bf16", output_dtype=torch.bfloat16).contiguous()
+                else:
+                    o = newton_schulz5_bf16_(u, sumsq, muon.ns_steps)
                 coef = muon.lr * max(1.0, rows / cols) ** 0.5
                 B.check(lib.cmb_zero1_push_update(pp, rank, W, I64(goff), I64(n), B.ptr(o), F32(coef), st()), "zero1_push_update")
         self.barrier()  # all parameters delivered everywhere; all gradients consumed
