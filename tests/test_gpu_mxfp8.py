@@ -1,0 +1,56 @@
+"""MXFP8 quantiser and block-scaled tcgen05 GEMM against the PyTorch oracle."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_quantizer_matches_reference_and_layout():
+    from cppmega_mlx_b200.ops import mxfp8 as MX
+    torch.manual_seed(0)
+    x = (torch.randn(300, 384, device="cuda") * torch.logspace(-3, 2, 384, device="cuda")).bfloat16()
+    x[5, 64:96] = 0                                      # an all-zero block
+    x[7, 0] = 3.0e4
+    t, plain = MX.quantize_mxfp8(x, want_plain_scales=True)
+    q_ref, e_ref = MX.quantize_mxfp8_reference(x)
+    assert torch.equal(plain, e_ref)
+    assert torch.equal(t.data.view(torch.float8_e4m3fn).float(), q_ref.float())
+    idx = MX.tiled_scale_index(300, 384, device="cuda")
+    assert torch.equal(t.scales[idx], e_ref)
+    deq = MX.dequantize_mxfp8(t).float()
+    assert torch.equal(deq, MX.dequantize_mxfp8_reference(q_ref, e_ref).bfloat16().float())
+    rel = (deq - x.float()).abs() / x.float().abs().clamp_min(1e-30)
+    blockmax = x.float().abs().view(300, 12, 32).amax(-1).repeat_interleave(32, 1)
+    assert float(((deq - x.float()).abs() / blockmax.clamp_min(1e-30)).max()) < 0.07   # ≤ half an e4m3 ulp of the block max
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (300, 200, 1024), (4096, 2048, 2048)])
+def test_block_scaled_gemm(M, N, K):
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops import mxfp8 as MX
+    torch.manual_seed(1)
+    a = (torch.randn(M, K, device="cuda") * torch.logspace(-2, 1, K, device="cuda")).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    b[:, K // 2:] *= 40.0                                 # make the per-block scales matter along K
+    qa, qb = MX.quantize_mxfp8(a), MX.quantize_mxfp8(b)
+    out = MX.gemm_mxfp8(qa, qb).float()
+    ref = MX.dequantize_mxfp8(qa).float() @ MX.dequantize_mxfp8(qb).float().t()
+    B.check_status()
+    err = float((out - ref).abs().max()) / float(ref.abs().max())
+    assert err < 1e-2, err
+    full = a.float() @ b.float().t()
+    assert float((out - full).abs().max()) / float(full.abs().max()) < 0.08            # quantisation error itself
+
+
+def test_mxfp8_linear_forward_and_ste_backward():
+    from cppmega_mlx_b200.ops import mxfp8 as MX
+    torch.manual_seed(2)
+    x = (torch.randn(4, 64, 256, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(384, 256, device="cuda") * 0.05).bfloat16().requires_grad_()
+    y = MX.mxfp8_linear(x, w)
+    ref = x.float() @ w.float().t()
+    assert float((y.float() - ref).abs().max()) / float(ref.abs().max()) < 0.08
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    assert torch.allclose(x.grad.float(), gy.float() @ w.float(), atol=5e-2, rtol=5e-2)
+    assert torch.allclose(w.grad.float(), gy.float().reshape(-1, 384).t() @ x.float().reshape(-1, 256), atol=0.5, rtol=5e-2)
