@@ -169,9 +169,58 @@ def bench_composite(args) -> list[dict]:
     return rows
 
 
+def bench_mxfp8(args) -> list[dict]:
+    """Block-scaled MXFP8 GEMM against the bf16 tcgen05 GEMM and cuBLAS bf16 on the same shapes; quantiser bandwidth."""
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import mxfp8 as MX
+    pk = peaks()
+    rows = []
+    for M, N, K, label in [(16384, 11264, 2048, "ffn up fwd"), (16384, 2048, 5632, "ffn down fwd"), (8192, 8192, 8192, "square 8192"),
+                           (4096, 65536, 2048, "lm_head chunk fwd")]:
+        if args.only and args.only != label:
+            continue
+        Kp = (K + 127) // 128 * 128
+        a = torch.randn(M, Kp, device="cuda").bfloat16()
+        b = torch.randn(N, Kp, device="cuda").bfloat16()
+        qa, qb = MX.quantize_mxfp8(a), MX.quantize_mxfp8(b)
+        ms = time_cuda(lambda: MX.gemm_mxfp8(qa, qb), iters=args.iters, warmup=args.warmup)
+        ms128 = time_cuda(lambda: MX.gemm_mxfp8(qa, qb, tile_n=128), iters=args.iters, warmup=args.warmup)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms16 = time_cuda(lambda: ops.gemm_raw(a, b, out=out), iters=args.iters, warmup=args.warmup)
+        msq = time_cuda(lambda: MX.quantize_mxfp8(a), iters=args.iters, warmup=args.warmup)
+        fl = 2.0 * M * N * Kp
+        rows.append({"op": "gemm_mxfp8", "label": label, "M": M, "N": N, "K": Kp, "ms": ms, "tflops": fl / ms / 1e9,
+                     "ms_tile128": ms128, "bf16_kernel_ms": ms16, "speedup_vs_bf16_kernel": ms16 / ms, "frac_of_measured_bf16_peak": fl / ms / 1e9 / pk["bf16_tflops"],
+                     "quant_ms": msq, "quant_gbs": (M * Kp * 3 + M * Kp / 32) / msq / 1e6, "quant_frac_of_measured_hbm": (M * Kp * 3) / msq / 1e6 / pk["hbm_gbs"]})
+        print(json.dumps(rows[-1]), flush=True)
+    return rows
+
+
+def bench_m2rnn(args) -> list[dict]:
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops.m2rnn_scan import m2rnn_scan
+    rows = []
+    b, S, H, K, V = 4, 4096, 4, 64, 16
+    q = (torch.randn(b, S, H, K, device="cuda") * 0.5).bfloat16().requires_grad_()
+    k = (torch.randn(b, S, H, K, device="cuda") * 0.5).bfloat16().requires_grad_()
+    v = (torch.randn(b, S, H, V, device="cuda") * 0.5).bfloat16().requires_grad_()
+    W = (torch.randn(H, V, V, device="cuda") * 0.2).bfloat16().requires_grad_()
+    f = torch.rand(b, S, H, device="cuda").mul(0.5).add(0.4).bfloat16().requires_grad_()
+    run = _fb(lambda: m2rnn_scan(q, k, v, W, f)[0], q, k, v, W, f)
+    ms = time_cuda(run, iters=args.iters, warmup=args.warmup)
+    row = {"op": "m2rnn scan fwd+bwd B4 S4096 H4 K64 V16", "ms": ms, "us_per_token_step": ms * 1e3 / S / 2}
+    if not args.no_eager:
+        with B.use_kernels(False):
+            row["eager_ms"] = time_cuda(run, iters=1, warmup=1)
+        row["speedup_vs_eager"] = row["eager_ms"] / ms
+    rows.append(row)
+    print(json.dumps(row), flush=True)
+    return rows
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "composite", "all"])
+    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "all"])
     ap.add_argument("--json", default=None)
     ap.add_argument("--only", default=None, help="run the single case with this label (small captures under a profiler)")
     ap.add_argument("--iters", type=int, default=10)
@@ -183,6 +232,10 @@ def main(argv=None) -> int:
         rows += bench_gemm(args)
     if args.op in ("composite", "all"):
         rows += bench_composite(args)
+    if args.op in ("mxfp8", "all"):
+        rows += bench_mxfp8(args)
+    if args.op in ("m2rnn", "all"):
+        rows += bench_m2rnn(args)
     if args.json:
         with open(args.json, "w") as f:
             json.dump(rows, f, indent=1)

@@ -97,19 +97,29 @@ __global__ void mxfp8_dequant_kernel(const uint8_t* __restrict__ q, long long ld
 
 // ------------------------------------------------------------------------------------------- block-scaled GEMM
 constexpr int MX_BM = 128;
-constexpr int MX_BN = 128;
 constexpr int MX_BK = 128;      // fp8 elements = bytes = one 128-byte swizzle line
-constexpr int MX_STAGES = 6;
 constexpr int MX_EPI_WARPS = 4;
 constexpr int MX_THREADS = 64 + 32 * MX_EPI_WARPS;
 constexpr int MX_A_BYTES = MX_BM * MX_BK;
-constexpr int MX_B_BYTES = MX_BN * MX_BK;
 constexpr int MX_SF_BYTES = 512;
-constexpr int MX_STAGE_BYTES = MX_A_BYTES + MX_B_BYTES + 2 * MX_SF_BYTES;
 constexpr int MX_CBOX_BYTES = 32 * 128;
-constexpr int MX_SMEM_BYTES = MX_STAGES * MX_STAGE_BYTES + MX_EPI_WARPS * MX_CBOX_BYTES + 1024 + 256;
-constexpr int MX_TMEM_COLS = 512;                  // 2 × 128 accumulator columns + 8 scale columns per stage
-constexpr int MX_TMEM_SF0 = 2 * MX_BN;
+constexpr int MX_TMEM_COLS = 512;
+
+// BN = 128: two accumulators (the epilogue of one tile overlaps the next tile's mainloop), 6 stages.
+// BN = 256: one accumulator (TMEM has 512 columns and the scale factors need some), 4 stages; halves the shared-memory
+//           traffic per FLOP, which is what bounds 8-bit MMAs on 128-wide tiles.
+template <int BN>
+struct MxCfg {
+  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr int NBUF = BN == 256 ? 1 : 2;
+  static constexpr int B_BYTES = BN * MX_BK;
+  static constexpr int SFB_ATOMS = BN / 128;
+  static constexpr int STAGE_BYTES = MX_A_BYTES + B_BYTES + (1 + SFB_ATOMS) * MX_SF_BYTES;
+  static constexpr int SF_COLS = 4 * (1 + SFB_ATOMS);     // TMEM columns of scale factors per stage
+  static constexpr int TMEM_SF0 = NBUF * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + MX_EPI_WARPS * MX_CBOX_BYTES + 1024 + 256;
+  static_assert(TMEM_SF0 + STAGES * SF_COLS <= MX_TMEM_COLS, "TMEM budget");
+};
 
 struct MxParams {
   int M, N, K;
@@ -124,9 +134,16 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
                : "memory");
 }
 
+template <int BN>
 __global__ void __launch_bounds__(MX_THREADS, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmC, const MxParams p) {
+  using Cfg = MxCfg<BN>;
+  constexpr int MX_STAGES = Cfg::STAGES;
+  constexpr int MX_STAGE_BYTES = Cfg::STAGE_BYTES;
+  constexpr int MX_B_BYTES = Cfg::B_BYTES;
+  constexpr int MX_BN = BN;
+  constexpr int NBUF = Cfg::NBUF;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* csmem = smem + MX_STAGES * MX_STAGE_BYTES;
@@ -187,7 +204,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           tma_load_2d(sa, &tmA, &full_bar[stage], kb * MX_BK, tm * MX_BM);
           tma_load_2d(sb, &tmB, &full_bar[stage], kb * MX_BK, tn * MX_BN);
           bulk_load(ssfa, p.sfa + (static_cast<long long>(tm) * num_kb + kb) * MX_SF_BYTES, MX_SF_BYTES, &full_bar[stage]);
-          bulk_load(ssfb, p.sfb + (static_cast<long long>(tn) * num_kb + kb) * MX_SF_BYTES, MX_SF_BYTES, &full_bar[stage]);
+#pragma unroll
+          for (int a = 0; a < Cfg::SFB_ATOMS; ++a)   // a tile past the last row block reads the (zeroed) padding atoms
+            bulk_load(ssfb + a * MX_SF_BYTES, p.sfb + (static_cast<long long>(tn * Cfg::SFB_ATOMS + a) * num_kb + kb) * MX_SF_BYTES,
+                      MX_SF_BYTES, &full_bar[stage]);
           if (++stage == MX_STAGES) {
             stage = 0;
             phase ^= 1;
@@ -202,8 +222,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int local = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int buf = local & 1;
-        const uint32_t aphase = (local >> 1) & 1;
+        const int buf = NBUF == 2 ? (local & 1) : 0;
+        const uint32_t aphase = NBUF == 2 ? ((local >> 1) & 1) : (local & 1);
         ++local;
         if (!mbar_wait(&tempty_bar[buf], aphase ^ 1, abort_flag, status, ST_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
@@ -218,10 +238,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const uint32_t sb = sa + MX_A_BYTES;
           const uint32_t ssfa = sb + MX_B_BYTES;
           const uint32_t ssfb = ssfa + MX_SF_BYTES;
-          const uint32_t t_sfa = tmem_base + MX_TMEM_SF0 + stage * 8;
+          const uint32_t t_sfa = tmem_base + Cfg::TMEM_SF0 + stage * Cfg::SF_COLS;
           const uint32_t t_sfb = t_sfa + 4;
           tmem_cp_32x128b_warpx4(t_sfa, make_smem_desc_noswizzle(ssfa, 16, 128));
-          tmem_cp_32x128b_warpx4(t_sfb, make_smem_desc_noswizzle(ssfb, 16, 128));
+#pragma unroll
+          for (int a = 0; a < Cfg::SFB_ATOMS; ++a)
+            tmem_cp_32x128b_warpx4(t_sfb + 4 * a, make_smem_desc_noswizzle(ssfb + a * MX_SF_BYTES, 16, 128));
 #pragma unroll
           for (int k = 0; k < MX_BK / 32; ++k) {
             const uint64_t adesc = make_smem_desc_sw128(sa + k * 32, 16, 1024);
@@ -244,8 +266,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     int local = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       const int tm = t % num_m, tn = t / num_m;
-      const int buf = local & 1;
-      const uint32_t aphase = (local >> 1) & 1;
+      const int buf = NBUF == 2 ? (local & 1) : 0;
+      const uint32_t aphase = NBUF == 2 ? ((local >> 1) & 1) : (local & 1);
       ++local;
       if (!mbar_wait(&tfull_bar[buf], aphase, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
@@ -328,30 +350,42 @@ extern "C" int cmb_mxfp8_dequant(const void* q, long long ldq, const void* sf_ti
 }
 
 // C[M,N] bf16 (pitch ldc) = A[M,K] · B[N,K]ᵀ with 1×32 e8m0 block scales in the tiled layout. K % 128 == 0, pitches % 16 == 0.
-extern "C" int cmb_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N, int K,
-                              long long lda, long long ldb, long long ldc, int* status, int max_ctas, void* stream) {
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (K % cmb::MX_BK) return 110;
+template <int BN>
+static int launch_mx(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N, int K, long long lda,
+                     long long ldb, long long ldc, int* status, int max_ctas, void* stream) {
+  using Cfg = cmb::MxCfg<BN>;
   CUtensorMap tmA, tmB, tmC;
   int rc = cmb_host::make_tmap_2d(&tmA, A, 1, M, K, lda, cmb::MX_BM, cmb::MX_BK, 128);
   if (rc) return rc;
-  rc = cmb_host::make_tmap_2d(&tmB, B, 1, N, K, ldb, cmb::MX_BN, cmb::MX_BK, 128);
+  rc = cmb_host::make_tmap_2d(&tmB, B, 1, N, K, ldb, BN, cmb::MX_BK, 128);
   if (rc) return rc + 10000;
   rc = cmb_host::make_tmap_2d(&tmC, C, 2, M, N, ldc, 32, 64, 128);
   if (rc) return rc + 20000;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(cmb::gemm_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, cmb::MX_SMEM_BYTES) != cudaSuccess) return 103;
+    if (cudaFuncSetAttribute(cmb::gemm_mxfp8_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 103;
     attr_set = true;
   }
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const long long tiles = static_cast<long long>((M + cmb::MX_BM - 1) / cmb::MX_BM) * ((N + cmb::MX_BN - 1) / cmb::MX_BN);
+  const long long tiles = static_cast<long long>((M + cmb::MX_BM - 1) / cmb::MX_BM) * ((N + BN - 1) / BN);
   int grid = sms;
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = static_cast<int>(tiles);
   cmb::MxParams p{M, N, K, static_cast<const uint8_t*>(sfa), static_cast<const uint8_t*>(sfb), status};
-  cmb::gemm_mxfp8_kernel<<<grid, cmb::MX_THREADS, cmb::MX_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, tmC, p);
+  cmb::gemm_mxfp8_kernel<BN><<<grid, cmb::MX_THREADS, Cfg::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 104;
+}
+
+// `bn_hint`: 0 = choose, 128 / 256 = force the tile width.
+extern "C" int cmb_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N, int K,
+                              long long lda, long long ldb, long long ldc, int* status, int max_ctas, int bn_hint, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % cmb::MX_BK) return 110;
+  // 256-wide tiles need the B scale atoms of both row blocks of a tile to exist: the scale buffer of B must cover
+  // ceil(N/256)·2 row blocks (the quantiser's buffer does when N is padded to 256 by the caller; otherwise use 128).
+  const bool wide = N >= 256 && (N % 256 == 0 || bn_hint == 256) && bn_hint != 128;
+  return wide ? launch_mx<256>(A, sfa, B, sfb, C, M, N, K, lda, ldb, ldc, status, max_ctas, stream)
+              : launch_mx<128>(A, sfa, B, sfb, C, M, N, K, lda, ldb, ldc, status, max_ctas, stream);
 }

@@ -83,8 +83,9 @@ def dequantize_mxfp8(t: MXFP8Tensor) -> torch.Tensor:
     return out
 
 
-def gemm_mxfp8(a: MXFP8Tensor, b: MXFP8Tensor, *, max_ctas: int = 0) -> torch.Tensor:
-    """[M,K] × [N,K]ᵀ → bf16 [M,N] on the block-scaled tensor-core path. K % 128 == 0, N % 8 == 0."""
+def gemm_mxfp8(a: MXFP8Tensor, b: MXFP8Tensor, *, max_ctas: int = 0, tile_n: int = 0) -> torch.Tensor:
+    """[M,K] × [N,K]ᵀ → bf16 [M,N] on the block-scaled tensor-core path. K % 128 == 0, N % 8 == 0.
+    ``tile_n``: 0 = choose (256-wide tiles when N is a multiple of 256), or force 128 / 256."""
     M, K = a.shape
     N, K2 = b.shape
     if K != K2 or K % 128 or N % 8:
@@ -94,7 +95,7 @@ def gemm_mxfp8(a: MXFP8Tensor, b: MXFP8Tensor, *, max_ctas: int = 0) -> torch.Te
     st = B.status_buffer(a.data.device)
     ll = ctypes.c_longlong
     B.check(lib.cmb_gemm_mxfp8(B.ptr(a.data), B.ptr(a.scales), B.ptr(b.data), B.ptr(b.scales), B.ptr(out), M, N, K, ll(K), ll(K), ll(N), B.ptr(st),
-                               int(max_ctas), B.stream_ptr()), "gemm_mxfp8")
+                               int(max_ctas), int(tile_n if (tile_n != 256 or N % 256 == 0) else 0), B.stream_ptr()), "gemm_mxfp8")
     return out
 
 

@@ -24,8 +24,9 @@ def test_quantizer_matches_reference_and_layout():
     assert float(((deq - x.float()).abs() / blockmax.clamp_min(1e-30)).max()) < 0.07   # ≤ half an e4m3 ulp of the block max
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (300, 200, 1024), (4096, 2048, 2048)])
-def test_block_scaled_gemm(M, N, K):
+@pytest.mark.parametrize("M,N,K,tile_n", [(128, 128, 128, 0), (256, 384, 512, 0), (300, 200, 1024, 0), (4096, 2048, 2048, 128),
+                                          (4096, 2048, 2048, 256), (300, 512, 640, 256), (128, 256, 128, 0)])
+def test_block_scaled_gemm(M, N, K, tile_n):
     from cppmega_mlx_b200.ops import _backend as B
     from cppmega_mlx_b200.ops import mxfp8 as MX
     torch.manual_seed(1)
@@ -33,7 +34,7 @@ def test_block_scaled_gemm(M, N, K):
     b = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
     b[:, K // 2:] *= 40.0                                 # make the per-block scales matter along K
     qa, qb = MX.quantize_mxfp8(a), MX.quantize_mxfp8(b)
-    out = MX.gemm_mxfp8(qa, qb).float()
+    out = MX.gemm_mxfp8(qa, qb, tile_n=tile_n).float()
     ref = MX.dequantize_mxfp8(qa).float() @ MX.dequantize_mxfp8(qb).float().t()
     B.check_status()
     err = float((out - ref).abs().max()) / float(ref.abs().max())
