@@ -1,0 +1,6 @@
+from .blocks import (CSAHCAConfig, CSAHCAHybridV4, EngramV4Block, EngramV4Config, KimiDeltaAttentionBlock, KimiDeltaAttentionConfig,
+                     LinearAttentionBlock, LinearAttentionConfig, NativeSparseAttentionV4, NSAConfig, StreamingPoolCache)
+from .delta_rule import chunked_gated_delta_rule, gated_delta_rule, recurrent_gated_delta_rule
+from .mtp_adapter import MTPSpeculativeAdapter
+from .run_template import BlockSpec, MTPSpec, RunTemplate, dump_template, dumps_template, load_template, loads_template
+from .superblock import UnifiedLMV4, UnifiedSuperblockV4
