@@ -117,6 +117,7 @@ class HybridTinyConfig:
     dsa_indexer_heads: int = 4
     dsa_indexer_head_dim: int = 64
     dsa_all_a_layers: bool = False           # every A layer is sparse (DSA) regardless of dsa_a_layer_ranks
+    dsa_indexer_loss_coeff: float = 0.0      # > 0 trains the DSA indexer with KL(attention ‖ indexer), already scaled by this
     moe_scoring: str = "softmax"
     moe_aux_loss_free: bool = False
     moe_bias_update_rate: float = 1e-3
@@ -174,7 +175,7 @@ class HybridTinyConfig:
                               q_lora_rank=self.mla_q_lora_rank, kv_lora_rank=self.mla_kv_lora_rank,
                               qk_nope_head_dim=self.mla_qk_nope_head_dim, qk_rope_head_dim=self.mla_qk_rope_head_dim,
                               v_head_dim=self.mla_v_head_dim, index_n_heads=self.dsa_indexer_heads,
-                              index_head_dim=self.dsa_indexer_head_dim,
+                              index_head_dim=self.dsa_indexer_head_dim, index_loss_coeff=self.dsa_indexer_loss_coeff,
                               index_topk=self.attention_sparse_topk if sparse else 0)
 
     def mamba3_config(self) -> Mamba3Config:
@@ -411,6 +412,11 @@ class HybridTinyLM(nn.Module):
     def aux_losses(self) -> torch.Tensor | None:
         vals = [b.aux_loss for b in self.layers if b.backend == "moe" and b.aux_loss is not None]
         return torch.stack(vals).sum() if vals else None
+
+    def indexer_losses(self) -> torch.Tensor | None:
+        """Sum of the DSA indexer KL losses of the sparse attention layers (each already scaled by its coefficient)."""
+        vals = [b.block.aux_loss for b in self.layers if b.backend == "attention" and getattr(b.block, "aux_loss", None) is not None]
+        return torch.stack([v.float() for v in vals]).sum() if vals else None
 
     def update_router_biases(self) -> None:
         for b in self.layers:

@@ -47,6 +47,7 @@ class MLABlockConfig:
     index_head_dim: int = 64
     index_topk: int = 0
     index_relu: bool = False
+    index_loss_coeff: float = 0.0   # > 0: add the KL(attention ‖ indexer) loss while training (DSA indexer training signal)
     zero_init_out: bool = True
 
     def __post_init__(self) -> None:
@@ -160,6 +161,7 @@ class MLAAttention(nn.Module):
         self.wkv_b = Linear(c.kv_lora_rank, H * (c.qk_nope_head_dim + c.v_head_dim))
         self.wo = Linear(H * c.v_head_dim, c.hidden_size, zero_init=c.zero_init_out)
         self.indexer = None
+        self.aux_loss: torch.Tensor | None = None
         if c.index_topk > 0:
             self.indexer = LightningIndexer(LightningIndexerConfig(
                 hidden_size=c.hidden_size, q_lora_rank=c.q_lora_rank, n_heads=c.index_n_heads,
@@ -220,6 +222,13 @@ class MLAAttention(nn.Module):
         idx = None
         if use_sparse and sk > c.index_topk:
             idx = self.indexer.select(iq, idx_k, iw, query_offset=sk - s, mask=add_mask)
+        self.aux_loss = None
+        if use_sparse and c.index_loss_coeff > 0 and self.training and kv_cache is None and torch.is_grad_enabled():
+            from ..ops.dsa_indexer_loss import dsa_indexer_loss
+            # teacher: this layer's own attention over the latent keys (detached inside the loss); student: the indexer scores
+            k_lat = latent.detach()[:, :, None, :]
+            self.aux_loss = dsa_indexer_loss(self.indexer.scores(iq, idx_k, iw), self._latent_query(q.detach()), k_lat, softmax_scale=scale,
+                                             loss_coeff=c.index_loss_coeff, topk_indices=idx)
         if kv_cache is None and add_mask is None and x.is_cuda and x.dtype == torch.bfloat16 and ops.kernels_enabled():
             # Training / prefill on the GPU: per-head K,V (192/128 wide) under the top-k bitmask.
             from ..ops import attention as A

@@ -93,6 +93,10 @@ def make_loss_fn(*, backend: str = "cce", mtp: bool | None = None, stp_weight: f
             if aux is not None:
                 total = total + coeff * aux.to(total.dtype)
                 comps["moe_aux"] = aux.detach()
+        idx_loss = model.indexer_losses() if hasattr(model, "indexer_losses") else None
+        if idx_loss is not None:
+            total = total + idx_loss.to(total.dtype)
+            comps["dsa_indexer"] = idx_loss.detach()
         return LossOutput(total, valid.sum(), comps)
 
     return loss_fn

@@ -205,3 +205,28 @@ def test_masked_attention_reference_is_causal_and_masked():
     ref = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2).expand(1, 2, 6, 8), v.transpose(1, 2).expand(1, 2, 6, 4),
                                          is_causal=True).transpose(1, 2)
     assert torch.allclose(out, ref, atol=1e-5)
+
+
+def test_dsa_indexer_loss_properties_and_chunking():
+    from cppmega_mlx_b200.ops.dsa_indexer_loss import dsa_indexer_loss, dsa_indexer_loss_reference
+    torch.manual_seed(11)
+    b, s, h, d = 2, 40, 4, 8
+    q, k = torch.randn(b, s, h, d), torch.randn(b, s, 1, d)
+    scale = d ** -0.5
+    # an indexer that reproduces the mean attention distribution exactly has zero loss
+    logits = torch.einsum("bqhd,bkd->bhqk", q, k[:, :, 0]) * scale
+    causal = torch.tril(torch.ones(s, s, dtype=torch.bool))
+    p = torch.softmax(logits.masked_fill(~causal, float("-inf")), -1).mean(1)
+    perfect = torch.log(p.clamp_min(1e-30))
+    assert float(dsa_indexer_loss_reference(perfect, q, k, softmax_scale=scale)) < 1e-5
+    idx_scores = torch.randn(b, s, s, requires_grad=True)
+    full = dsa_indexer_loss_reference(idx_scores, q, k, softmax_scale=scale, loss_coeff=0.5)
+    assert float(full) > 0
+    chunked = dsa_indexer_loss(idx_scores, q, k, softmax_scale=scale, loss_coeff=0.5, q_chunk=16)
+    assert torch.allclose(full, chunked, atol=1e-5)
+    g, = torch.autograd.grad(chunked, idx_scores)
+    assert torch.isfinite(g).all() and float(g.abs().sum()) > 0 and float(g.triu(1).abs().max()) == 0.0     # nothing flows to masked keys
+    topk = torch.stack([torch.cat([torch.randperm(i + 1)[:5], torch.full((max(0, 5 - i - 1),), -1)]) for i in range(s)])[None].expand(b, s, 5)
+    sparse = dsa_indexer_loss(idx_scores, q, k, softmax_scale=scale, topk_indices=topk, q_chunk=16)
+    assert torch.allclose(sparse, dsa_indexer_loss_reference(idx_scores, q, k, softmax_scale=scale, topk_indices=topk), atol=1e-5)
+    assert float(dsa_indexer_loss(idx_scores[:, :0], q[:, :0], k, softmax_scale=scale)) == 0.0
