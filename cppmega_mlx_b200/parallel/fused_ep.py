@@ -1,0 +1,158 @@
+"""Expert-parallel MoE dispatch / combine over symmetric memory, fused with the gather / scatter around the grouped expert GEMM.
+
+Per layer call, on every rank of the expert-parallel group (rank r owns experts ``[r·Le, (r+1)·Le)``):
+
+1. route → per-(destination rank, expert) counts; every rank writes its count row into every peer's count matrix (tiny peer
+   stores), epoch barrier.  All ranks now know all counts, so every rank can compute, on the device and without a host
+   synchronisation, the slot of each of its assignments in the destination's receive buffer — which is laid out *directly* in the
+   padded expert-sorted form the grouped tcgen05 GEMM consumes (segments start on 128-row boundaries, inside a segment rows are
+   ordered by source rank).
+2. dispatch kernel: gathers token rows by index and stores them straight into the owners' receive buffers over NVLink; barrier.
+3. local grouped GEMMs (gate|up → SwiGLU → down) on the received rows; the result is published in symmetric memory; barrier.
+4. gather kernel: every source rank loads its assignments' output rows from the owners' buffers; gate weighting and the sum over
+   the k experts of a token happen locally.
+
+Backward runs the same two kernels in the opposite roles (the gradient of a gather is a dispatch and vice versa).  Oracle:
+``parallel/ep.py`` (NCCL / gloo all-to-all).  The reference has no expert parallelism (``cppmega_mlx/nn/moe.py:166-228`` loops over
+all experts on one device).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops import _backend as B
+from ..ops import grouped_gemm_cuda as GG
+from .symm import EpochBarrier, SymmetricBuffer
+
+I64 = ctypes.c_longlong
+
+
+class FusedEPComm:
+    def __init__(self, group, device, *, max_tokens: int, top_k: int, d_model: int, num_experts: int, capacity_rows: int | None = None):
+        self.group, self.device = group, device
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if num_experts % self.world:
+            raise ValueError("expert-parallel size must divide num_experts")
+        self.local_experts = num_experts // self.world
+        self.d = d_model
+        worst = GG.padded_rows(self.world * max_tokens * top_k, self.local_experts)
+        self.rows = worst if capacity_rows is None else min(worst, (capacity_rows + 127) // 128 * 128)
+        self.xbuf = SymmetricBuffer(self.rows * d_model, torch.bfloat16, device, group)
+        self.ybuf = SymmetricBuffer(self.rows * d_model, torch.bfloat16, device, group)
+        self.counts = SymmetricBuffer(self.world * self.world * self.local_experts, torch.int32, device, group)
+        self.barrier = EpochBarrier(device, group)
+
+    # -- kernels ---------------------------------------------------------------------------------
+    def dispatch_rows(self, buf: SymmetricBuffer, rows: torch.Tensor, tok: torch.Tensor, dest_rank: torch.Tensor, dest_slot: torch.Tensor) -> None:
+        lib = B.load_library()
+        B.check(lib.cmb_ep_dispatch(B.ptr(rows), B.ptr(tok), B.ptr(dest_rank), B.ptr(dest_slot), None, buf.peer_ptrs, self.world,
+                                    I64(tok.numel()), self.d, B.stream_ptr()), "ep_dispatch")
+
+    def gather_rows(self, buf: SymmetricBuffer, src_rank: torch.Tensor, src_slot: torch.Tensor) -> torch.Tensor:
+        lib = B.load_library()
+        out = torch.empty(src_slot.numel(), self.d, dtype=torch.bfloat16, device=self.device)
+        B.check(lib.cmb_ep_combine(buf.peer_ptrs, self.world, B.ptr(src_rank), B.ptr(src_slot), None, B.ptr(out), I64(src_slot.numel()), 1, self.d,
+                                   B.stream_ptr()), "ep_gather")
+        return out
+
+    def combine_weighted(self, src_rank, src_slot, weights, tokens: int, k: int) -> torch.Tensor:
+        """Inference form: gather + gate weighting + sum over k in one kernel (no autograd)."""
+        lib = B.load_library()
+        out = torch.empty(tokens, self.d, dtype=torch.bfloat16, device=self.device)
+        B.check(lib.cmb_ep_combine(self.ybuf.peer_ptrs, self.world, B.ptr(src_rank), B.ptr(src_slot), B.ptr(weights), B.ptr(out), I64(tokens), k,
+                                   self.d, B.stream_ptr()), "ep_combine")
+        return out
+
+    # -- routing plan ----------------------------------------------------------------------------
+    def plan(self, flat_e: torch.Tensor):
+        """Exchange counts and compute, for every assignment (original order), its destination rank and slot; also the grouped
+        layout of the rows this rank will receive.  Device-side only."""
+        W, Le, r = self.world, self.local_experts, self.rank
+        e = flat_e.long()
+        A = e.numel()
+        mine = torch.bincount(e, minlength=W * Le).int()                              # [W·Le] rows I send to (rank, expert)
+        self.xbuf.tensor.zero_()                                                      # padding rows of my receive buffer must be zero
+        for p in range(W):                                                            # my row of everyone's count matrix
+            self.counts.handle.get_buffer(p, (W * Le,), torch.int32, r * W * Le).copy_(mine)
+        self.barrier()
+        C = self.counts.tensor.view(W, W, Le).long()                                  # [src, dst, expert]
+        tot = C.sum(0)                                                                # [dst, expert]
+        pad = (tot + 127) // 128 * 128
+        pad_end = torch.cumsum(pad, 1)
+        pad_off = pad_end - pad
+        before_me = C[:r].sum(0)                                                      # rows of lower-ranked sources come first
+        start = pad_off + before_me                                                   # [dst, expert]: where my rows begin
+        order = torch.argsort(e, stable=True)
+        se = e[order]
+        my_first = torch.cumsum(mine.long(), 0) - mine.long()
+        slot_sorted = start.reshape(-1)[se] + (torch.arange(A, device=e.device) - my_first[se])
+        slot = torch.empty_like(slot_sorted).index_copy_(0, order, slot_sorted)
+        dest = (e // Le).int()
+        # layout of what I receive
+        tile_start = torch.arange(self.rows // 128, device=e.device) * 128
+        tile_group = torch.searchsorted(pad_end[r], tile_start, right=True).clamp_(max=Le - 1).int()
+        k_ranges = torch.stack([pad_off[r], pad_end[r]], 1).int().contiguous()
+        layout = GG.GroupedLayout(Le, self.rows, slot, order, tile_group, k_ranges, tot[r])
+        overflow = pad_end[:, -1].max() > self.rows
+        return dest, slot, layout, overflow
+
+
+class _Dispatch(torch.autograd.Function):
+    """flat [T,d] → this rank's received rows [rows,d] (padded expert-sorted). Backward gathers the row gradients back."""
+
+    @staticmethod
+    def forward(ctx, flat, tok, dest, slot, comm: FusedEPComm):
+        comm.dispatch_rows(comm.xbuf, flat, tok, dest, slot)
+        comm.barrier()                                           # all rows for me have landed
+        ctx.comm, ctx.T = comm, flat.shape[0]
+        ctx.save_for_backward(tok, dest, slot)
+        return comm.xbuf.tensor.view(comm.rows, comm.d).clone()
+
+    @staticmethod
+    def backward(ctx, g_rows):
+        tok, dest, slot = ctx.saved_tensors
+        comm = ctx.comm
+        comm.xbuf.tensor.view(comm.rows, comm.d).copy_(g_rows)
+        comm.barrier()                                           # every owner has published its row gradients
+        g = comm.gather_rows(comm.xbuf, dest, slot)              # [A,d]
+        comm.barrier()                                           # owners may reuse their buffers
+        return torch.zeros(ctx.T, comm.d, dtype=g.dtype, device=g.device).index_add_(0, tok, g), None, None, None, None
+
+
+class _Gather(torch.autograd.Function):
+    """this rank's expert outputs [rows,d] → the output rows of my own assignments [A,d]. Backward dispatches the gradients."""
+
+    @staticmethod
+    def forward(ctx, y_local, dest, slot, comm: FusedEPComm):
+        comm.ybuf.tensor.view(comm.rows, comm.d).copy_(y_local)
+        comm.barrier()                                           # every owner has published its outputs
+        out = comm.gather_rows(comm.ybuf, dest, slot)
+        ctx.comm = comm
+        ctx.save_for_backward(dest, slot)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        dest, slot = ctx.saved_tensors
+        comm = ctx.comm
+        comm.ybuf.tensor.zero_()
+        comm.barrier()                                           # everyone's gradient buffer is cleared (and the forward reads are over)
+        comm.dispatch_rows(comm.ybuf, g.contiguous(), torch.arange(g.shape[0], device=g.device), dest, slot)
+        comm.barrier()
+        return comm.ybuf.tensor.view(comm.rows, comm.d).clone(), None, None, None
+
+
+def fused_ep_moe_forward(moe, comm: FusedEPComm, flat: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor) -> torch.Tensor:
+    """Drop-in for ``parallel.ep.ep_moe_forward`` on GPUs sharing an NVSwitch domain."""
+    T, k = top_idx.shape
+    dest, slot, layout, _overflow = comm.plan(top_idx.reshape(-1))
+    tok = torch.arange(T * k, device=flat.device) // k
+    xp = _Dispatch.apply(flat.contiguous(), tok, dest, slot, comm)
+    h = ops.swiglu(GG.grouped_linear_padded(xp, moe.experts.w_gate_up, layout))
+    yp = GG.grouped_linear_padded(h, moe.experts.w_down, layout)
+    rows = _Gather.apply(yp, dest, slot, comm)                                   # [T·k, d] in assignment order
+    return (rows.view(T, k, -1) * top_w.to(rows.dtype)[..., None]).sum(1)

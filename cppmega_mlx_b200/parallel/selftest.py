@@ -2,7 +2,9 @@
 cppmega_mlx_b200.parallel.selftest <case>``.  Rank 0 prints one JSON line with the comparison result.
 
 Cases: ``zero1`` — the fused symmetric-memory ZeRO-1 step against the NCCL reduce-scatter / all-gather step on the same
-model, data and seeds (loss trajectory and final parameters must agree to bf16 tolerance).
+model, data and seeds (loss trajectory and final parameters must agree to bf16 tolerance); ``tp`` — a sequence-parallel
+tensor-parallel SwiGLU FFN, forward and backward, with the fused GEMM↔collective pairs of ``fused_tp.py`` against the NCCL
+pairs of ``tp.py`` (results and device time).
 """
 from __future__ import annotations
 
@@ -67,11 +69,114 @@ def case_zero1(rank, world, dev):
                           "max_param_diff": float(diff), "rank_spread": float(spread)}))
 
 
+def _time(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+def case_tp(rank, world, dev):
+    """Sequence-parallel TP FFN (column-parallel up, SwiGLU, row-parallel down): fused symmetric-memory pairs vs the NCCL pairs."""
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.parallel import tp as TP
+    from cppmega_mlx_b200.parallel.fused_tp import FusedTPComm, column_parallel_fused, row_parallel_fused
+    S, d, hid = (16384, 2048, 5632) if os.environ.get("CMB_TP_SMALL") != "1" else (1024, 256, 512)
+    torch.manual_seed(0)
+    x_full = (torch.randn(S, d, device=dev) * 0.5).bfloat16()
+    w_up = (torch.randn(2 * hid, d, device=dev) * 0.02).bfloat16()
+    w_dn = (torch.randn(d, hid, device=dev) * 0.02).bfloat16()
+    g = dist.group.WORLD
+    rows = S // world
+    x_shard = x_full[rank * rows:(rank + 1) * rows].clone()
+    wu = TP.shard_rows(w_up, g, blocks=2).clone()
+    wd = TP.shard_cols(w_dn, g).clone()
+    comm = FusedTPComm(g, dev, max_rows_per_rank=rows, max_cols=max(d, 2 * hid // world))
+
+    def run(fused: bool):
+        xs = x_shard.clone().requires_grad_()
+        a, b = wu.clone().requires_grad_(), wd.clone().requires_grad_()
+        if fused:
+            h = ops.swiglu(column_parallel_fused(xs, a, comm))
+            y = row_parallel_fused(h, b, comm)
+        else:
+            h = ops.swiglu(ops.linear(TP.gather_sequence(xs, g, 0), a))
+            y = TP.reduce_scatter_sequence(ops.linear(h, b), g, 0)
+        y.backward(torch.ones_like(y) * 0.01)
+        return y.detach(), xs.grad, a.grad, b.grad
+    ref, out = run(False), run(True)
+    torch.cuda.synchronize()
+    B.check_status()
+    errs = []
+    for r_, o_ in zip(ref, out):
+        e = (r_.float() - o_.float()).abs().max() / r_.float().abs().max().clamp_min(1e-6)
+        dist.all_reduce(e, op=dist.ReduceOp.MAX)
+        errs.append(float(e))
+    full_ref = ops.swiglu_reference((x_full.float() @ w_up.float().t())) @ w_dn.float().t()
+    e_abs = (out[0].float() - full_ref[rank * rows:(rank + 1) * rows]).abs().max() / full_ref.abs().max()
+    dist.all_reduce(e_abs, op=dist.ReduceOp.MAX)
+    t_nccl, t_fused = _time(lambda: run(False)), _time(lambda: run(True))
+    if rank == 0:
+        print(json.dumps({"case": "tp", "world": world, "shape": [S, d, hid], "rel_err_vs_nccl[y,dx,dw_up,dw_down]": errs,
+                          "rel_err_vs_fp32_single_gpu": float(e_abs), "ms_fwd_bwd_nccl": t_nccl, "ms_fwd_bwd_fused": t_fused}))
+
+
+def case_ep(rank, world, dev):
+    """Expert-parallel MoE layer, forward and backward: fused dispatch/combine kernels vs the NCCL all-to-all path."""
+    from cppmega_mlx_b200.nn.moe import MoE, MoEConfig
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.parallel import ep as EP
+    from cppmega_mlx_b200.parallel.fused_ep import FusedEPComm, fused_ep_moe_forward
+    small = os.environ.get("CMB_EP_SMALL") == "1"
+    T, d, E, k, hid = (512, 256, 8, 2, 128) if small else (16384, 2048, 64, 6, 1408)
+    cfg = MoEConfig(d_model=d, num_experts=E, top_k=k, expert_hidden_size=hid, shared_expert_hidden_size=None, activation="swiglu",
+                    scoring="sigmoid", aux_loss_free=True)
+    torch.manual_seed(0)
+    full = MoE(cfg).to(dev, torch.bfloat16)
+    g = dist.group.WORLD
+    local = MoE(cfg, ep_group=g).to(dev, torch.bfloat16)
+    EP.shard_experts_(full, local)
+    torch.manual_seed(100 + rank)
+    x = (torch.randn(T, d, device=dev) * 0.5).bfloat16()
+    comm = FusedEPComm(g, dev, max_tokens=T, top_k=k, d_model=d, num_experts=E, capacity_rows=None if small else 2 * T * k)
+
+    def run(fused: bool):
+        xs = x.clone().requires_grad_()
+        local.zero_grad()
+        r = local.router(xs[None])
+        idx, w = r.top_indices.reshape(-1, k), r.top_weights.reshape(-1, k)
+        y = fused_ep_moe_forward(local, comm, xs, idx, w) if fused else EP.ep_moe_forward(local, xs, idx, w)
+        y.backward(torch.ones_like(y) * 0.01)
+        return y.detach(), xs.grad.clone(), local.experts.w_gate_up.grad.clone(), local.experts.w_down.grad.clone(), local.router.gate.weight.grad.clone()
+    ref, out = run(False), run(True)
+    torch.cuda.synchronize()
+    B.check_status()
+    errs = []
+    for r_, o_ in zip(ref, out):
+        e = (r_.float() - o_.float()).abs().max() / r_.float().abs().max().clamp_min(1e-6)
+        dist.all_reduce(e, op=dist.ReduceOp.MAX)
+        errs.append(float(e))
+    t_nccl, t_fused = _time(lambda: run(False), iters=5), _time(lambda: run(True), iters=5)
+    if rank == 0:
+        print(json.dumps({"case": "ep", "world": world, "shape": {"tokens_per_rank": T, "d": d, "experts": E, "top_k": k, "hidden": hid},
+                          "rel_err_vs_nccl[y,dx,dw_gate_up,dw_down,dw_router]": errs, "ms_fwd_bwd_nccl": t_nccl, "ms_fwd_bwd_fused": t_fused}))
+
+
 def main():
     case = sys.argv[1] if len(sys.argv) > 1 else "zero1"
     rank, world, dev = _setup()
     try:
-        {"zero1": case_zero1}[case](rank, world, dev)
+        {"zero1": case_zero1, "tp": case_tp, "ep": case_ep}[case](rank, world, dev)
     finally:
         dist.barrier()
         dist.destroy_process_group()
