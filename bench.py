@@ -37,7 +37,8 @@ def parse_args():
     ap.add_argument("--micro-batch", type=int, default=4)
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--optimizer", default="muon_adamw", choices=["muon_adamw", "adamw"])
-    ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"])
+    ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused", "stub"],
+                    help="stub = no communication at all (measurement aid for exposed-communication time; not a valid training run)")
     ap.add_argument("--depth", type=int, default=0, help="override layer count (debugging only; makes the result non-headline)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--grad-checkpoint", default="auto", choices=["auto", "on", "off"],
@@ -231,6 +232,8 @@ def main():
                        "l2": "working set per step (weights + activations, tens of GB) far exceeds the 126 MB L2; no flush needed"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }
+        if comm == "stub":
+            out["invalid"] = "communication disabled: this line only serves to measure exposed communication time"
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

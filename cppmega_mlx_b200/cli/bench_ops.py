@@ -218,14 +218,52 @@ def bench_m2rnn(args) -> list[dict]:
     return rows
 
 
+def bench_sparse_mla(args) -> list[dict]:
+    """Sparse MLA in latent form at the long-context shape: B1 S8192, 64 heads, latent 512 + rope 64, top-2048 causal keys per query
+    chosen from N(0,1) indexer scores.  TFLOP/s are quoted against the *sparse* FLOPs 2·S·H·topk·(576 + 512) (forward; ×3.5 with
+    backward), whatever the kernel actually evaluates."""
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B
+    pk = peaks()
+    dev = "cuda"
+    b, S, H, d, dv, topk = 1, args.mla_seq, 64, 576, 512, 2048
+    torch.manual_seed(0)
+    q = torch.randn(b, S, H, d, device=dev).bfloat16().requires_grad_()
+    kv = torch.randn(b, S, 1, d, device=dev).bfloat16().requires_grad_()
+    scores = torch.randn(b * S, S, device=dev)
+    ends = torch.arange(1, S + 1, device=dev, dtype=torch.int32).repeat(b)
+    idx = ops.topk_select(scores, topk, None, ends).view(b, S, 1, topk)
+    del scores
+    scale = d ** -0.5
+    rows = []
+    kept = float((idx >= 0).sum()) * H
+    fl_f = 2.0 * kept * (d + dv)
+
+    def fwd():
+        return ops.sparse_mla_attention(q, kv, idx, sm_scale=scale, d_v=dv)[0]
+    with torch.no_grad():
+        ms_f = time_cuda(fwd, iters=args.iters, warmup=args.warmup)
+    ms_fb = time_cuda(_fb(fwd, q, kv), iters=args.iters, warmup=args.warmup)
+    row = {"op": f"sparse MLA bf16 B1 S{S} H64 d576/512 top2048", "fwd_ms": ms_f, "fwd_sparse_tflops": fl_f / ms_f / 1e9,
+           "fwd_bwd_ms": ms_fb, "fwd_bwd_sparse_tflops": 3.5 * fl_f / ms_fb / 1e9, "frac_of_measured_peak_fwd_bwd": 3.5 * fl_f / ms_fb / 1e9 / pk["bf16_tflops"]}
+    if not args.no_eager:
+        with B.use_kernels(False), torch.no_grad():
+            row["eager_fwd_ms"] = time_cuda(fwd, iters=2, warmup=1)
+        row["fwd_speedup_vs_eager"] = row["eager_fwd_ms"] / ms_f
+    rows.append(row)
+    print(json.dumps(row), flush=True)
+    return rows
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "all"])
+    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "all"])
     ap.add_argument("--json", default=None)
     ap.add_argument("--only", default=None, help="run the single case with this label (small captures under a profiler)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-eager", action="store_true")
+    ap.add_argument("--mla-seq", type=int, default=8192)
     args = ap.parse_args(argv)
     rows = []
     if args.op in ("gemm", "all"):
@@ -236,6 +274,8 @@ def main(argv=None) -> int:
         rows += bench_mxfp8(args)
     if args.op in ("m2rnn", "all"):
         rows += bench_m2rnn(args)
+    if args.op in ("sparse_mla", "all"):
+        rows += bench_sparse_mla(args)
     if args.json:
         with open(args.json, "w") as f:
             json.dump(rows, f, indent=1)

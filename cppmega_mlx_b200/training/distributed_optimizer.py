@@ -14,7 +14,8 @@ contributions used as a gather ``:326-391``; ownership there is per-leaf round-r
 The communication itself is pluggable: ``comm="nccl"`` uses ``torch.distributed`` collectives (gloo
 on CPU falls back to all_reduce + all_gather); ``comm="fused"`` uses the symmetric-memory kernels in
 ``parallel/fused_zero1.py`` that reduce peer gradients, apply the update and push fresh parameters to
-every rank from one kernel.  World size 1 short-circuits (``:416``).
+every rank from one kernel; ``comm="stub"`` performs the sharded update with no communication at all and exists only to measure
+exposed communication time (step time with communication − step time without).  World size 1 short-circuits (``:416``).
 """
 from __future__ import annotations
 
@@ -172,6 +173,9 @@ class DistributedZeRO1Optimizer:
             self.inner.step()
             return
         if self._fused is not None and self._fused.try_fused_step(self):
+            return
+        if self.comm == "stub":   # measurement aid: same sharded update, no communication (results are NOT consistent across ranks)
+            self.inner.step()
             return
         self._reduce_scatter_grads()
         self.inner.step()  # owned params' .grad are views of the (now reduced) own segment
