@@ -148,6 +148,16 @@ def bench_composite(args) -> list[dict]:
     Dp = torch.ones(H, device=dev).requires_grad_()
     add("mamba3 scan fwd+bwd B4 S4096 H32 P64 N128", lambda: _fb(lambda: ops.mamba3_scan(xs, Bm, Cm, z, A, dt, Dp, chunk_size=64)[0],
                                                               xs, Bm, Cm, z, A, dt, Dp))
+    # the flagship model's layer: 64 heads; chunk length is an implementation choice (the result does not depend on it)
+    H2 = 64
+    xs2 = (torch.randn(Bz, S, H2, P, device=dev) * 0.5).bfloat16().requires_grad_()
+    z2 = torch.randn(Bz, S, H2, P, device=dev).bfloat16().requires_grad_()
+    A2 = (-torch.rand(Bz, S, H2, device=dev) - 0.5).requires_grad_()
+    dt2 = (torch.rand(Bz, S, H2, device=dev) * 0.1 + 0.01).requires_grad_()
+    D2 = torch.ones(H2, device=dev).requires_grad_()
+    for L in (64, 128, 256):
+        add(f"mamba3 scan fwd+bwd B4 S4096 H64 P64 N128 chunk{L}",
+            lambda L=L: _fb(lambda: ops.mamba3_scan(xs2, Bm, Cm, z2, A2, dt2, D2, chunk_size=L)[0], xs2, Bm, Cm, z2, A2, dt2, D2), eager=False)
 
     # masked attention (MLA multi-head form): B4 H16 S4096 dqk192 dv128, causal, no top-k mask
     q = (torch.randn(4, 4096, 16, 192, device=dev) * 0.3).bfloat16().requires_grad_()

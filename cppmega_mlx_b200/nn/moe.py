@@ -215,6 +215,10 @@ class MoE(nn.Module):
     def routed_forward(self, flat: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor) -> torch.Tensor:
         T, k = top_idx.shape
         if self.ep_size > 1:
+            fused = getattr(self, "fused_ep", None)
+            if fused is not None and flat.is_cuda and flat.dtype == torch.bfloat16 and ops.kernels_enabled():
+                from ..parallel.fused_ep import fused_ep_moe_forward
+                return fused_ep_moe_forward(self, fused, flat, top_idx, top_w)
             from ..parallel.ep import ep_moe_forward
             return ep_moe_forward(self, flat, top_idx, top_w)
         E = self.config.num_experts

@@ -33,6 +33,7 @@ class GroupedLayout:
     tile_group: torch.Tensor     # [rows/128] int32
     k_ranges: torch.Tensor       # [E, 2] int32
     counts: torch.Tensor         # [E] int64
+    valid_rows: torch.Tensor | None = None   # [rows] bool, set by producers that do not clear their buffers
 
 
 def padded_rows(num_assignments: int, num_experts: int) -> int:

@@ -75,7 +75,6 @@ class FusedEPComm:
         e = flat_e.long()
         A = e.numel()
         mine = torch.bincount(e, minlength=W * Le).int()                              # [W·Le] rows I send to (rank, expert)
-        self.xbuf.tensor.zero_()                                                      # padding rows of my receive buffer must be zero
         for p in range(W):                                                            # my row of everyone's count matrix
             self.counts.handle.get_buffer(p, (W * Le,), torch.int32, r * W * Le).copy_(mine)
         self.barrier()
@@ -97,20 +96,28 @@ class FusedEPComm:
         tile_group = torch.searchsorted(pad_end[r], tile_start, right=True).clamp_(max=Le - 1).int()
         k_ranges = torch.stack([pad_off[r], pad_end[r]], 1).int().contiguous()
         layout = GG.GroupedLayout(Le, self.rows, slot, order, tile_group, k_ranges, tot[r])
+        # rows of my buffers that hold a real assignment (segment padding and unused capacity are not written by anyone)
+        grp = tile_group.long().repeat_interleave(128)
+        layout.valid_rows = (torch.arange(self.rows, device=e.device) - pad_off[r][grp]) < tot[r][grp]
         overflow = pad_end[:, -1].max() > self.rows
         return dest, slot, layout, overflow
+
+    def take(self, buf: SymmetricBuffer, valid_rows: torch.Tensor) -> torch.Tensor:
+        """Private copy of a receive buffer with every row nobody wrote set to zero (one pass; the buffer is never cleared)."""
+        t = buf.tensor.view(self.rows, self.d)
+        return torch.where(valid_rows[:, None], t, torch.zeros((), dtype=t.dtype, device=t.device))
 
 
 class _Dispatch(torch.autograd.Function):
     """flat [T,d] → this rank's received rows [rows,d] (padded expert-sorted). Backward gathers the row gradients back."""
 
     @staticmethod
-    def forward(ctx, flat, tok, dest, slot, comm: FusedEPComm):
+    def forward(ctx, flat, tok, dest, slot, valid_rows, comm: FusedEPComm):
         comm.dispatch_rows(comm.xbuf, flat, tok, dest, slot)
         comm.barrier()                                           # all rows for me have landed
         ctx.comm, ctx.T = comm, flat.shape[0]
         ctx.save_for_backward(tok, dest, slot)
-        return comm.xbuf.tensor.view(comm.rows, comm.d).clone()
+        return comm.take(comm.xbuf, valid_rows)
 
     @staticmethod
     def backward(ctx, g_rows):
@@ -120,30 +127,29 @@ class _Dispatch(torch.autograd.Function):
         comm.barrier()                                           # every owner has published its row gradients
         g = comm.gather_rows(comm.xbuf, dest, slot)              # [A,d]
         comm.barrier()                                           # owners may reuse their buffers
-        return torch.zeros(ctx.T, comm.d, dtype=g.dtype, device=g.device).index_add_(0, tok, g), None, None, None, None
+        return torch.zeros(ctx.T, comm.d, dtype=g.dtype, device=g.device).index_add_(0, tok, g), None, None, None, None, None
 
 
 class _Gather(torch.autograd.Function):
     """this rank's expert outputs [rows,d] → the output rows of my own assignments [A,d]. Backward dispatches the gradients."""
 
     @staticmethod
-    def forward(ctx, y_local, dest, slot, comm: FusedEPComm):
+    def forward(ctx, y_local, dest, slot, valid_rows, comm: FusedEPComm):
         comm.ybuf.tensor.view(comm.rows, comm.d).copy_(y_local)
         comm.barrier()                                           # every owner has published its outputs
         out = comm.gather_rows(comm.ybuf, dest, slot)
         ctx.comm = comm
-        ctx.save_for_backward(dest, slot)
+        ctx.save_for_backward(dest, slot, valid_rows)
         return out
 
     @staticmethod
     def backward(ctx, g):
-        dest, slot = ctx.saved_tensors
+        dest, slot, valid_rows = ctx.saved_tensors
         comm = ctx.comm
-        comm.ybuf.tensor.zero_()
-        comm.barrier()                                           # everyone's gradient buffer is cleared (and the forward reads are over)
+        comm.barrier()                                           # every rank is past its reads of the previous contents
         comm.dispatch_rows(comm.ybuf, g.contiguous(), torch.arange(g.shape[0], device=g.device), dest, slot)
         comm.barrier()
-        return comm.ybuf.tensor.view(comm.rows, comm.d).clone(), None, None, None
+        return comm.take(comm.ybuf, valid_rows), None, None, None, None
 
 
 def fused_ep_moe_forward(moe, comm: FusedEPComm, flat: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor) -> torch.Tensor:
@@ -151,8 +157,23 @@ def fused_ep_moe_forward(moe, comm: FusedEPComm, flat: torch.Tensor, top_idx: to
     T, k = top_idx.shape
     dest, slot, layout, _overflow = comm.plan(top_idx.reshape(-1))
     tok = torch.arange(T * k, device=flat.device) // k
-    xp = _Dispatch.apply(flat.contiguous(), tok, dest, slot, comm)
+    xp = _Dispatch.apply(flat.contiguous(), tok, dest, slot, layout.valid_rows, comm)
     h = ops.swiglu(GG.grouped_linear_padded(xp, moe.experts.w_gate_up, layout))
     yp = GG.grouped_linear_padded(h, moe.experts.w_down, layout)
-    rows = _Gather.apply(yp, dest, slot, comm)                                   # [T·k, d] in assignment order
+    rows = _Gather.apply(yp, dest, slot, layout.valid_rows, comm)                # [T·k, d] in assignment order
     return (rows.view(T, k, -1) * top_w.to(rows.dtype)[..., None]).sum(1)
+
+
+def enable_fused_ep(model: torch.nn.Module, group, device, *, max_tokens: int, capacity_factor: float | None = 2.0) -> FusedEPComm | None:
+    """Give every expert-parallel MoE layer of ``model`` one shared symmetric-memory communicator (layers run one after the other,
+    and nothing saved for backward lives in the shared buffers)."""
+    from ..nn.moe import MoE
+    layers = [m for m in model.modules() if isinstance(m, MoE) and m.ep_size > 1]
+    if not layers:
+        return None
+    c = layers[0].config
+    cap = None if capacity_factor is None else int(capacity_factor * max_tokens * c.top_k)
+    comm = FusedEPComm(group, device, max_tokens=max_tokens, top_k=c.top_k, d_model=c.d_model, num_experts=c.num_experts, capacity_rows=cap)
+    for m in layers:
+        m.fused_ep = comm
+    return comm
