@@ -296,3 +296,31 @@ extern "C" int cmb_axpy_update(void* p, const void* u, int64_t n, int dtype, flo
                                 static_cast<T*>(p), static_cast<const __nv_bfloat16*>(u), n, coef)));
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
+
+// ---------------------------------------------------------------------------------------------- symmetric completion
+namespace cmb {
+// G[i][j] = G[j][i] for j > i (n×n bf16, row pitch ld): completes a matrix whose lower triangle was computed by a GEMM that
+// skipped the tiles above the diagonal.  32×32 tiles through shared memory so both sides are coalesced.
+__global__ void mirror_lower_kernel(__nv_bfloat16* __restrict__ g, int n, long long ld) {
+  __shared__ __nv_bfloat16 tile[32][33];
+  const int bi = blockIdx.y, bj = blockIdx.x;        // destination tile (rows bi, cols bj), only bj >= bi
+  if (bj < bi) return;
+  const int tx = threadIdx.x, ty = threadIdx.y;      // 32 × 8
+  for (int r = ty; r < 32; r += 8) {                 // load source tile (rows bj·32.., cols bi·32..)
+    const int sr = bj * 32 + r, sc = bi * 32 + tx;
+    tile[r][tx] = (sr < n && sc < n) ? g[sr * ld + sc] : __float2bfloat16(0.f);
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    const int dr = bi * 32 + r, dc = bj * 32 + tx;
+    if (dr < n && dc < n && dc > dr) g[dr * ld + dc] = tile[tx][r];
+  }
+}
+}  // namespace cmb
+
+extern "C" int cmb_mirror_lower(void* g, int n, long long ld, void* stream) {
+  if (n <= 0) return 0;
+  const int t = (n + 31) / 32;
+  cmb::mirror_lower_kernel<<<dim3(t, t), dim3(32, 8), 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(g), n, ld);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}

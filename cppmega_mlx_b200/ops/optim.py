@@ -65,7 +65,7 @@ def newton_schulz5_bf16_(u: torch.Tensor, sumsq: torch.Tensor, steps: int = 5, c
     iteration, entirely as tcgen05 GEMMs with fused ``alpha·acc + beta·aux`` epilogues: three launches per step and no
     element-wise pass.  Tall matrices apply the polynomial from the right (``X ← aX + X(bG + cG²)``, ``G = XᵀX``) so no
     transpose is ever materialised."""
-    from .gemm import gemm_axpby, gemm_raw
+    from .gemm import CAUSAL_SKIP, EPI_AXPBY, gemm_axpby, gemm_batched, gemm_raw
     lib = B.load_library()
     a, b, c = coeffs
     B.check(lib.cmb_scale_inv_norm(B.ptr(u), B.ptr(sumsq), ctypes.c_int64(u.numel()), ctypes.c_float(1e-7), B.stream_ptr()),
@@ -74,15 +74,29 @@ def newton_schulz5_bf16_(u: torch.Tensor, sumsq: torch.Tensor, steps: int = 5, c
     x = u
     nxt = torch.empty_like(u)
     tall = rows > cols
+    m = min(rows, cols)
+    g = torch.empty(m, m, dtype=torch.bfloat16, device=u.device)
+    poly = torch.empty_like(g)
+    sym = m >= 512                     # Gram matrix and its square are symmetric: compute the lower triangle, mirror the rest
+    tri = dict(M=m, N=m, lda=0, ldb=0, ldc=m, nb=(1, 1, 1), sA=(0, 0, 0), sB=(0, 0, 0), sC=(0, 0, 0), flags=CAUSAL_SKIP)
+
+    def mirror(t):
+        B.check(lib.cmb_mirror_lower(B.ptr(t), m, ctypes.c_longlong(m), B.stream_ptr()), "mirror_lower")
     for _ in range(steps):
-        if tall:
-            g = gemm_raw(x, x, a_mn=True, b_mn=True)                       # XᵀX  [c,c]
-            poly = gemm_axpby(g, g, g, alpha=c, beta=b)                   # bG + cG²   (G symmetric)
-            gemm_axpby(x, poly, x, alpha=1.0, beta=a, out=nxt)            # aX + X·poly
+        if sym:
+            kw = {**tri, "lda": x.stride(0), "ldb": x.stride(0)}
+            gemm_batched(x, x, g, K=rows if tall else cols, a_mn=tall, b_mn=tall, **kw)
+            mirror(g)
+            gemm_batched(g, g, poly, K=m, a_mn=False, b_mn=False, **{**tri, "lda": m, "ldb": m, "flags": CAUSAL_SKIP | EPI_AXPBY}, aux=g,
+                         scale=c, scale2=b)
+            mirror(poly)
         else:
-            g = gemm_raw(x, x)                                            # XXᵀ  [r,r]
-            poly = gemm_axpby(g, g, g, alpha=c, beta=b)
-            gemm_axpby(poly, x, x, b_mn=True, alpha=1.0, beta=a, out=nxt)  # aX + poly·X
+            g = gemm_raw(x, x, a_mn=True, b_mn=True) if tall else gemm_raw(x, x)           # XᵀX [c,c]  or  XXᵀ [r,r]
+            poly = gemm_axpby(g, g, g, alpha=c, beta=b)                                    # bG + cG²   (G symmetric)
+        if tall:
+            gemm_axpby(x, poly, x, alpha=1.0, beta=a, out=nxt)                             # aX + X·poly
+        else:
+            gemm_axpby(poly, x, x, b_mn=True, alpha=1.0, beta=a, out=nxt)                  # aX + poly·X
         x, nxt = nxt, x
     return x
 
