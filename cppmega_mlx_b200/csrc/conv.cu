@@ -13,18 +13,21 @@
 namespace cmb {
 
 constexpr int CONV_TS = 8;
+constexpr int CONV_RUN = 128;  // tokens per warp in the backward kernel
 constexpr int CONV_MAXK = 8;
 
 __device__ __forceinline__ float2 ld2(const __nv_bfloat16* p) {
   return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
 }
 
+template <int KC>  // KC > 0: compile-time tap count (everything stays in registers); 0: run-time K
 __global__ void __launch_bounds__(256) conv_silu_fwd_kernel(const __nv_bfloat16* __restrict__ in, long long ld_in,
                                                              int c_off, const __nv_bfloat16* __restrict__ w,
                                                              const __nv_bfloat16* __restrict__ bias,
                                                              __nv_bfloat16* __restrict__ out1,
                                                              __nv_bfloat16* __restrict__ out2, int Bn, int S, int C,
-                                                             int C1, int K) {
+                                                             int C1, int Krt) {
+  const int K = KC > 0 ? KC : Krt;
   const int cp = blockIdx.x * 32 + (threadIdx.x & 31);  // channel pair
   const int c = cp * 2;
   const long long tile = blockIdx.y * 8LL + (threadIdx.x >> 5);
@@ -33,20 +36,25 @@ __global__ void __launch_bounds__(256) conv_silu_fwd_kernel(const __nv_bfloat16*
   const int b = static_cast<int>(tile / tiles_per_seq);
   const int s0 = static_cast<int>(tile % tiles_per_seq) * CONV_TS;
   float2 wk[CONV_MAXK];
+#pragma unroll
   for (int k = 0; k < K; ++k) wk[k] = make_float2(__bfloat162float(w[c * K + k]), __bfloat162float(w[(c + 1) * K + k]));
   const float2 bs = bias != nullptr ? ld2(bias + c) : make_float2(0.f, 0.f);
   const __nv_bfloat16* ib = in + static_cast<long long>(b) * S * ld_in + c_off + c;
   float2 win[CONV_MAXK];  // win[k] = in[s-K+1+k]
+#pragma unroll
   for (int k = 0; k < K - 1; ++k) {
     const int s = s0 - (K - 1) + k;
     win[k + 1] = s >= 0 ? ld2(ib + s * ld_in) : make_float2(0.f, 0.f);
   }
+#pragma unroll
   for (int i = 0; i < CONV_TS; ++i) {
     const int s = s0 + i;
     if (s >= S) break;
+#pragma unroll
     for (int k = 0; k < K - 1; ++k) win[k] = win[k + 1];
     win[K - 1] = ld2(ib + s * ld_in);
     float2 acc = bs;
+#pragma unroll
     for (int k = 0; k < K; ++k) {
       acc.x += wk[k].x * win[k].x;
       acc.y += wk[k].y * win[k].y;
@@ -61,6 +69,7 @@ __global__ void __launch_bounds__(256) conv_silu_fwd_kernel(const __nv_bfloat16*
 // Backward. dy comes from the two dense gradient tensors; din is written with row pitch `ld_din` (so it can
 // land directly inside the gradient of the packed projection);
 // dw [C,K] and dbias [C] are fp32 and must be zeroed by the caller (block-reduced atomics).
+template <int KC>
 __global__ void __launch_bounds__(256) conv_silu_bwd_kernel(const __nv_bfloat16* __restrict__ in, long long ld_in,
                                                              int c_off, const __nv_bfloat16* __restrict__ w,
                                                              const __nv_bfloat16* __restrict__ bias,
@@ -68,21 +77,25 @@ __global__ void __launch_bounds__(256) conv_silu_bwd_kernel(const __nv_bfloat16*
                                                              const __nv_bfloat16* __restrict__ dy2,
                                                              __nv_bfloat16* __restrict__ din, long long ld_din,
                                                              float* __restrict__ dw, float* __restrict__ dbias, int Bn,
-                                                             int S, int C, int C1, int K) {
+                                                             int S, int C, int C1, int Krt) {
+  const int K = KC > 0 ? KC : Krt;
   __shared__ float red[8][32][2 * (CONV_MAXK + 1)];
   const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;
   const int cp = blockIdx.x * 32 + lane;
   const int c = cp * 2;
+  // each warp walks a run of CONV_RUN tokens in sub-tiles of CONV_TS, so the weight / bias partial sums are reduced (and the
+  // atomics issued) once per run instead of once per sub-tile
   const long long tile = blockIdx.y * 8LL + wrp;
-  const int tiles_per_seq = (S + CONV_TS - 1) / CONV_TS;
+  const int tiles_per_seq = (S + CONV_RUN - 1) / CONV_RUN;
   const bool active = c < C && tile < static_cast<long long>(Bn) * tiles_per_seq;
   float2 dwk[CONV_MAXK];
   float2 db = make_float2(0.f, 0.f);
   for (int k = 0; k < CONV_MAXK; ++k) dwk[k] = make_float2(0.f, 0.f);
   if (active) {
     const int b = static_cast<int>(tile / tiles_per_seq);
-    const int s0 = static_cast<int>(tile % tiles_per_seq) * CONV_TS;
+    const int run0 = static_cast<int>(tile % tiles_per_seq) * CONV_RUN;
     float2 wk[CONV_MAXK];
+#pragma unroll
     for (int k = 0; k < K; ++k) wk[k] = make_float2(__bfloat162float(w[c * K + k]), __bfloat162float(w[(c + 1) * K + k]));
     const float2 bs = bias != nullptr ? ld2(bias + c) : make_float2(0.f, 0.f);
     const __nv_bfloat16* ib = in + static_cast<long long>(b) * S * ld_in + c_off + c;
@@ -90,10 +103,12 @@ __global__ void __launch_bounds__(256) conv_silu_bwd_kernel(const __nv_bfloat16*
     const __nv_bfloat16* gb = first ? dy1 + static_cast<long long>(b) * S * C1 + c
                                     : dy2 + static_cast<long long>(b) * S * (C - C1) + (c - C1);
     const long long gld = first ? C1 : (C - C1);
+    for (int s0 = run0; s0 < min(S, run0 + CONV_RUN); s0 += CONV_TS) {
     // inputs s0-(K-1) .. s0+TS+K-2 and dpre for s0 .. s0+TS+K-2
     constexpr int NI = CONV_TS + 2 * (CONV_MAXK - 1);
     float2 xin[NI];
     const int ni = CONV_TS + 2 * (K - 1);
+#pragma unroll
     for (int j = 0; j < ni; ++j) {
       const int s = s0 - (K - 1) + j;
       xin[j] = (s >= 0 && s < S) ? ld2(ib + s * ld_in) : make_float2(0.f, 0.f);
@@ -101,11 +116,14 @@ __global__ void __launch_bounds__(256) conv_silu_bwd_kernel(const __nv_bfloat16*
     constexpr int ND = CONV_TS + CONV_MAXK - 1;
     float2 dpre[ND];
     const int nd = CONV_TS + K - 1;
+#pragma unroll
     for (int j = 0; j < nd; ++j) {
       const int s = s0 + j;
       if (s < S) {
         float2 acc = bs;
-        for (int k = 0; k < K; ++k) {  // pre[s] uses in[s-K+1+k] = xin[j+k]
+    #pragma unroll
+#pragma unroll
+    for (int k = 0; k < K; ++k) {  // pre[s] uses in[s-K+1+k] = xin[j+k]
           acc.x += wk[k].x * xin[j + k].x;
           acc.y += wk[k].y * xin[j + k].y;
         }
@@ -116,11 +134,13 @@ __global__ void __launch_bounds__(256) conv_silu_bwd_kernel(const __nv_bfloat16*
         dpre[j] = make_float2(0.f, 0.f);
       }
     }
+#pragma unroll
     for (int i = 0; i < CONV_TS; ++i) {
       const int s = s0 + i;
       if (s >= S) break;
       // din[s] = Σ_k w[k] · dpre[s + K-1-k]
       float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
       for (int k = 0; k < K; ++k) {
         acc.x += wk[k].x * dpre[i + K - 1 - k].x;
         acc.y += wk[k].y * dpre[i + K - 1 - k].y;
@@ -129,12 +149,15 @@ __global__ void __launch_bounds__(256) conv_silu_bwd_kernel(const __nv_bfloat16*
       // this thread's own dpre positions feed dw / dbias exactly once
       db.x += dpre[i].x;
       db.y += dpre[i].y;
+#pragma unroll
       for (int k = 0; k < K; ++k) {
         dwk[k].x += dpre[i].x * xin[i + k].x;
         dwk[k].y += dpre[i].y * xin[i + k].y;
       }
     }
+    }
   }
+#pragma unroll
   for (int k = 0; k < K; ++k) {
     red[wrp][lane][2 * k] = dwk[k].x;
     red[wrp][lane][2 * k + 1] = dwk[k].y;
@@ -163,9 +186,10 @@ extern "C" int cmb_conv_silu_fwd(const void* in, long long ld_in, int c_off, con
   using bf = __nv_bfloat16;
   const long long tiles = static_cast<long long>(Bn) * ((S + cmb::CONV_TS - 1) / cmb::CONV_TS);
   dim3 grid((C / 2 + 31) / 32, static_cast<unsigned>((tiles + 7) / 8));
-  cmb::conv_silu_fwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const bf*>(in), ld_in, c_off, static_cast<const bf*>(w), static_cast<const bf*>(bias),
-      static_cast<bf*>(out1), static_cast<bf*>(out2), Bn, S, C, C1, K);
+  auto kern = K == 4 ? cmb::conv_silu_fwd_kernel<4> : cmb::conv_silu_fwd_kernel<0>;
+  kern<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const bf*>(in), ld_in, c_off, static_cast<const bf*>(w),
+                                                            static_cast<const bf*>(bias), static_cast<bf*>(out1), static_cast<bf*>(out2), Bn, S, C,
+                                                            C1, K);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
@@ -174,10 +198,11 @@ extern "C" int cmb_conv_silu_bwd(const void* in, long long ld_in, int c_off, con
                                  int S, int C, int C1, int K, void* stream) {
   if (C % 2 || C1 % 2 || c_off % 2 || ld_in % 2 || K > cmb::CONV_MAXK || K < 1) return 1;
   using bf = __nv_bfloat16;
-  const long long tiles = static_cast<long long>(Bn) * ((S + cmb::CONV_TS - 1) / cmb::CONV_TS);
+  const long long tiles = static_cast<long long>(Bn) * ((S + cmb::CONV_RUN - 1) / cmb::CONV_RUN);
   dim3 grid((C / 2 + 31) / 32, static_cast<unsigned>((tiles + 7) / 8));
-  cmb::conv_silu_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const bf*>(in), ld_in, c_off, static_cast<const bf*>(w), static_cast<const bf*>(bias),
-      static_cast<const bf*>(dy1), static_cast<const bf*>(dy2), static_cast<bf*>(din), ld_din, dw, dbias, Bn, S, C, C1, K);
+  auto kern = K == 4 ? cmb::conv_silu_bwd_kernel<4> : cmb::conv_silu_bwd_kernel<0>;
+  kern<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const bf*>(in), ld_in, c_off, static_cast<const bf*>(w),
+                                                            static_cast<const bf*>(bias), static_cast<const bf*>(dy1), static_cast<const bf*>(dy2),
+                                                            static_cast<bf*>(din), ld_din, dw, dbias, Bn, S, C, C1, K);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }

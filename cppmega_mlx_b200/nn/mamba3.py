@@ -218,6 +218,18 @@ class Mamba3Block(nn.Module):
         z, x, BC, tail = ops.packed_split_conv_silu(proj, c.d_inner, conv_ch, c.d_inner, self.conv_weight, self.conv_bias,
                                                     prefix=prefix)
         xBC_raw = proj[..., c.d_inner:c.d_inner + conv_ch]
+        if cache is None and not return_cache and c.effective_mimo_rank == 1 and ops.kernels_enabled():
+            from ..ops import mamba3_prep as MP
+            norm_params = (self.B_norm_weight, self.B_bias, self.C_norm_weight, self.C_bias)
+            if MP.supported(BC, tail, norm_params + (self.dt_bias,), c.nheads, c.ngroups, c.d_state, self.dims.num_rope_angles):
+                # fused preparation: norm + bias, trapezoid scale, phase accumulation and rotation, dt and A in four kernels
+                Bg, Cg, dt, A = MP.mamba3_prep(BC, tail, self.dt_bias, *norm_params, nheads=c.nheads, ngroups=c.ngroups, d_state=c.d_state,
+                                               num_angles=self.dims.num_rope_angles, a_floor=c.A_floor)
+                xh, zh = x.reshape(b, s, c.nheads, c.headdim), z.reshape(b, s, c.nheads, c.headdim)
+                if h0 is not None and tuple(h0.shape) != (b, c.nheads, c.headdim, c.d_state):
+                    raise ValueError(f"h0 must have shape {(b, c.nheads, c.headdim, c.d_state)}, got {tuple(h0.shape)}")
+                y, h = ops.mamba3_scan(xh, Bg, Cg, zh, A, dt, self.D, h0, chunk_size=c.chunk_size)
+                return self.out_proj(y.reshape(b, s, c.d_inner)), h
         Bm, Cm = BC[..., :self.dims.d_bc], BC[..., self.dims.d_bc:]
         dd_dt, dd_A, trap, angles = torch.split(tail.float(), [c.nheads, c.nheads, c.nheads, self.dims.num_rope_angles], dim=-1)
         x = x.reshape(b, s, c.nheads, c.headdim)

@@ -25,6 +25,9 @@ import torch.nn.functional as F
 from . import _backend as B
 
 
+KERNEL_CHUNK = 128
+
+
 def _expand_groups(t: torch.Tensor, nheads: int) -> torch.Tensor:
     g = t.shape[2]
     if g == nheads:
@@ -137,6 +140,9 @@ def mamba3_scan(x, Bm, Cm, z, A, dt, D, h0=None, chunk_size: int = 64):
     """Dispatch: CUDA chunked kernels for bf16 CUDA tensors, PyTorch chunked form otherwise."""
     if B.on_gpu(x, Bm, Cm, z) and x.dtype == torch.bfloat16:
         from . import mamba3_scan_cuda
+        # the chunk length does not change the result; 128 keeps the materialised intra-chunk matrices half the size of 256
+        if chunk_size > KERNEL_CHUNK and x.shape[1] % KERNEL_CHUNK == 0:
+            chunk_size = KERNEL_CHUNK
         if mamba3_scan_cuda.supported(x, Bm, chunk_size):
             return _Mamba3ScanFn.apply(x, Bm, Cm, z, A, dt, D, h0, chunk_size)
     return mamba3_scan_chunked(x, Bm, Cm, z, A, dt, D, h0, chunk_size)

@@ -48,3 +48,41 @@ def test_mamba3_scan_matches_sequential(shape, with_h0):
     names = [n for n, t in zip(["x", "B", "C", "z", "A", "dt", "D", "h0"], ins) if t is not None]
     for n, a, b in zip(names, grads, rgrads):
         close(a, b, "d" + n, rel=5e-2)
+
+
+def test_fused_prep_matches_framework_ops(monkeypatch):
+    """The fused B/C/dt/A preparation against the PyTorch statement of the same math (both feeding the kernel scan)."""
+    import copy
+
+    from cppmega_mlx_b200.nn.mamba3 import Mamba3Block, Mamba3Config
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops import mamba3_prep as MP
+    torch.manual_seed(0)
+    blk = Mamba3Block(Mamba3Config(d_model=512, headdim=64, d_state=128, ngroups=8, chunk_size=64, d_conv=4)).cuda().bfloat16()
+    with torch.no_grad():
+        for n in ("B_norm_weight", "C_norm_weight", "B_bias", "C_bias"):
+            getattr(blk, n).add_(torch.randn_like(getattr(blk, n)) * 0.2)
+    ref = copy.deepcopy(blk)
+    x = (torch.randn(2, 320, 512, device="cuda") * 0.5).bfloat16()
+    g = torch.randn(2, 320, 512, device="cuda").bfloat16()
+
+    def run(mod, fused):
+        monkeypatch.setattr(MP, "supported", (lambda *a, **k: fused) if not fused else MP.__dict__["_orig_supported"])
+        xi = x.clone().requires_grad_()
+        y = mod(xi)[0]
+        y.backward(g)
+        return y.detach().float(), xi.grad.float(), {n: p.grad.float() for n, p in mod.named_parameters()}
+    MP.__dict__.setdefault("_orig_supported", MP.supported)
+    n0 = B.launch_count()
+    yf, gxf, gpf = run(blk, True)
+    fused_launches = B.launch_count() - n0
+    yr, gxr, gpr = run(ref, False)
+    B.check_status()
+    assert fused_launches > 0
+
+    def rel(a, b):
+        return float((a - b).abs().max()) / (float(b.abs().max()) + 1e-6)
+    assert rel(yf, yr) < 3e-2
+    assert rel(gxf, gxr) < 5e-2
+    for n in gpr:
+        assert rel(gpf[n], gpr[n]) < 6e-2, (n, rel(gpf[n], gpr[n]))
