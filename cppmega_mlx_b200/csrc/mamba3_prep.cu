@@ -324,3 +324,78 @@ extern "C" int cmb_m3_prep_bc_bwd(const void* BC, const float* scale_g, const fl
 #undef CMB_PREP_BWD
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
+
+// ---------------------------------------------------------------------------------------------- prefix sum along the sequence
+// out[b,t,c] = Σ_{t' ≤ t} in[b,t',c]  (or Σ_{t' ≥ t} with `reverse`), fp32, C contiguous.  Three tiny kernels: per-segment local
+// scans (thread per (b, segment, c), c fastest → coalesced), an exclusive scan of the segment totals, and the offset add.
+namespace cmb {
+constexpr int SCAN_SEG = 64;
+
+template <bool REV>
+__global__ void scan_local_kernel(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ totals, int S, int C, int nseg,
+                                  long long total_threads) {
+  const long long idx = blockIdx.x * 256LL + threadIdx.x;
+  if (idx >= total_threads) return;
+  const int c = static_cast<int>(idx % C);
+  const int seg = static_cast<int>((idx / C) % nseg);
+  const long long b = idx / (static_cast<long long>(C) * nseg);
+  const int t0 = seg * SCAN_SEG, t1 = min(S, t0 + SCAN_SEG);
+  float acc = 0.f;
+  if (REV) {
+    for (int t = t1 - 1; t >= t0; --t) {
+      acc += in[(b * S + t) * C + c];
+      out[(b * S + t) * C + c] = acc;
+    }
+  } else {
+    for (int t = t0; t < t1; ++t) {
+      acc += in[(b * S + t) * C + c];
+      out[(b * S + t) * C + c] = acc;
+    }
+  }
+  totals[(b * nseg + seg) * C + c] = acc;
+}
+
+template <bool REV>
+__global__ void scan_totals_kernel(float* __restrict__ totals, int C, int nseg, long long cols) {
+  const long long idx = blockIdx.x * 256LL + threadIdx.x;   // (b, c)
+  if (idx >= cols) return;
+  const int c = static_cast<int>(idx % C);
+  const long long b = idx / C;
+  float acc = 0.f;
+  for (int k = 0; k < nseg; ++k) {
+    const int seg = REV ? nseg - 1 - k : k;
+    float* p = totals + (b * nseg + seg) * C + c;
+    const float v = *p;
+    *p = acc;          // exclusive offset for this segment
+    acc += v;
+  }
+}
+
+__global__ void scan_add_kernel(float* __restrict__ out, const float* __restrict__ offsets, int S, int C, int nseg, long long n) {
+  const long long idx = blockIdx.x * 256LL + threadIdx.x;
+  if (idx >= n) return;
+  const int c = static_cast<int>(idx % C);
+  const long long bt = idx / C;
+  const int t = static_cast<int>(bt % S);
+  const long long b = bt / S;
+  out[idx] += offsets[(b * nseg + t / SCAN_SEG) * C + c];
+}
+}  // namespace cmb
+
+// `totals` is scratch of Bn · ceil(S/64) · C floats.
+extern "C" int cmb_cumsum_seq(const float* in, float* out, float* totals, int Bn, int S, int C, int reverse, void* stream) {
+  if (Bn <= 0 || S <= 0 || C <= 0) return 0;
+  const int nseg = (S + cmb::SCAN_SEG - 1) / cmb::SCAN_SEG;
+  const long long th = static_cast<long long>(Bn) * nseg * C, cols = static_cast<long long>(Bn) * C, n = static_cast<long long>(Bn) * S * C;
+  auto st = static_cast<cudaStream_t>(stream);
+  const unsigned g1 = static_cast<unsigned>((th + 255) / 256), g2 = static_cast<unsigned>((cols + 255) / 256), g3 = static_cast<unsigned>((n + 255) / 256);
+  if (reverse) {
+    cmb::scan_local_kernel<true><<<g1, 256, 0, st>>>(in, out, totals, S, C, nseg, th);
+    cmb::scan_totals_kernel<true><<<g2, 256, 0, st>>>(totals, C, nseg, cols);
+  } else {
+    cmb::scan_local_kernel<false><<<g1, 256, 0, st>>>(in, out, totals, S, C, nseg, th);
+    cmb::scan_totals_kernel<false><<<g2, 256, 0, st>>>(totals, C, nseg, cols);
+  }
+  cmb::scan_add_kernel<<<g3, 256, 0, st>>>(out, totals, S, C, nseg, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}

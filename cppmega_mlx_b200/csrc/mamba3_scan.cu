@@ -257,8 +257,10 @@ __global__ void __launch_bounds__(256) m3_bwd_q_kernel(const __nv_bfloat16* __re
   }
 }
 
-// Reverse carry. One block per (b,h); threads stride over the P·N state entries.
+// Reverse carry. Block (b·H + h, slice): 256 threads × 4 state entries each, so the P·N entries of one (b,h) are spread over
+// several blocks; the per-chunk scalar is combined with one atomic per block (dcumL must be zeroed by the caller).
 //   dS[c] = dHtot_{c+1} ; dcumL[b,c,h] += Σ dHtot_{c+1}·H_c·decay_c ; dHtot_c = dHy_c + decay_c·dHtot_{c+1}
+constexpr int SB_EPT = 4;
 __global__ void __launch_bounds__(256) m3_state_bwd_kernel(const float* __restrict__ dHy,
                                                             const __nv_bfloat16* __restrict__ hc,
                                                             const float* __restrict__ cum,
@@ -269,21 +271,19 @@ __global__ void __launch_bounds__(256) m3_state_bwd_kernel(const float* __restri
   __shared__ float red[8];
   const int h = blockIdx.x % H;
   const int b = blockIdx.x / H;
-  constexpr int MAXE = 64;  // P·N ≤ 256·64
-  float carry[MAXE];
-  const int per = (PN + 255) / 256;
-  for (int k = 0; k < per && k < MAXE; ++k) {
-    const int e = threadIdx.x + 256 * k;
-    carry[k] = (e < PN && dhlast != nullptr) ? dhlast[(static_cast<long long>(b) * H + h) * PN + e] : 0.f;
-  }
+  const int e0 = (blockIdx.y * 256 + threadIdx.x) * SB_EPT;
+  float carry[SB_EPT];
+#pragma unroll
+  for (int k = 0; k < SB_EPT; ++k)
+    carry[k] = (e0 + k < PN && dhlast != nullptr) ? dhlast[(static_cast<long long>(b) * H + h) * PN + e0 + k] : 0.f;
   for (int c = nc - 1; c >= 0; --c) {
     const long long row = (static_cast<long long>(b) * nc + c) * H + h;
     const float d = __expf(cum[row * L + L - 1]);
     float part = 0.f;
-    for (int k = 0; k < per && k < MAXE; ++k) {
-      const int e = threadIdx.x + 256 * k;
-      if (e < PN) {
-        const long long idx = row * PN + e;
+#pragma unroll
+    for (int k = 0; k < SB_EPT; ++k) {
+      if (e0 + k < PN) {
+        const long long idx = row * PN + e0 + k;
         dS[idx] = __float2bfloat16(carry[k]);
         part += carry[k] * __bfloat162float(hc[idx]);
         carry[k] = dHy[idx] + d * carry[k];
@@ -296,14 +296,13 @@ __global__ void __launch_bounds__(256) m3_state_bwd_kernel(const float* __restri
     if (threadIdx.x == 0) {
       float t = 0.f;
       for (int w = 0; w < 8; ++w) t += red[w];
-      dcumL[row] = t * d;
+      atomicAdd(&dcumL[row], t * d);
     }
   }
   if (dh0 != nullptr) {
-    for (int k = 0; k < per && k < MAXE; ++k) {
-      const int e = threadIdx.x + 256 * k;
-      if (e < PN) dh0[(static_cast<long long>(b) * H + h) * PN + e] = carry[k];
-    }
+#pragma unroll
+    for (int k = 0; k < SB_EPT; ++k)
+      if (e0 + k < PN) dh0[(static_cast<long long>(b) * H + h) * PN + e0 + k] = carry[k];
   }
 }
 
@@ -457,9 +456,9 @@ extern "C" int cmb_m3_bwd_q(const void* dM, const void* Mm, const float* cum, fl
 }
 extern "C" int cmb_m3_state_bwd(const float* dHy, const void* hc, const float* cum, const float* dhlast, void* dS,
                                 float* dcumL, float* dh0, int Bn, int nc, int H, int PN, int L, void* stream) {
-  if (PN > 256 * 64) return 1;
   using bf = __nv_bfloat16;
-  cmb::m3_state_bwd_kernel<<<Bn * H, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  const dim3 grid(Bn * H, (PN + 256 * cmb::SB_EPT - 1) / (256 * cmb::SB_EPT));
+  cmb::m3_state_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       dHy, static_cast<const bf*>(hc), cum, dhlast, static_cast<bf*>(dS), dcumL, dh0, Bn, nc, H, PN, L);
   return CMB_OK();
 }

@@ -21,6 +21,17 @@ def supported(BC, tail, params, H: int, G: int, N: int, R: int) -> bool:
             and B.has_library() and hasattr(B.load_library(), "cmb_m3_prep_bc_fwd"))
 
 
+def _cumsum_seq(t: torch.Tensor, reverse: bool = False) -> torch.Tensor:
+    """Prefix (or suffix) sum over dim 1 of an fp32 [B, S, ...] tensor with a segmented three-kernel scan."""
+    lib = B.load_library()
+    b, s = t.shape[:2]
+    c = t[0, 0].numel()
+    out = torch.empty_like(t)
+    scratch = torch.empty(b * ((s + 63) // 64) * c, dtype=torch.float32, device=t.device)
+    B.check(lib.cmb_cumsum_seq(B.ptr(t), B.ptr(out), B.ptr(scratch), b, s, c, int(reverse), B.stream_ptr()), "cumsum_seq")
+    return out
+
+
 class _Mamba3PrepFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, BC, tail, dt_bias, wB, bB, wC, bC, H, G, N, R, a_floor, eps):
@@ -36,7 +47,7 @@ class _Mamba3PrepFn(torch.autograd.Function):
         inc = torch.empty(b, s, G, R, **f32)
         B.check(lib.cmb_m3_prep_dt_fwd(B.ptr(tail), I64(tail.shape[-1]), B.ptr(bias32), B.ptr(dt), B.ptr(A), B.ptr(sc), B.ptr(inc), b, s, H, G, R,
                                        F32(a_floor), B.stream_ptr()), "m3_prep_dt_fwd")
-        ang = torch.cumsum(inc, dim=1)
+        ang = _cumsum_seq(inc)
         Bg = torch.empty(b, s, G, N, dtype=torch.bfloat16, device=dev)
         Cg = torch.empty_like(Bg)
         rstd = torch.empty(b, s, G, 2, **f32)
@@ -65,7 +76,7 @@ class _Mamba3PrepFn(torch.autograd.Function):
         B.check(lib.cmb_m3_prep_bc_bwd(B.ptr(BC), B.ptr(scale_g), B.ptr(ang), B.ptr(rstd), B.ptr(wB), B.ptr(bB), B.ptr(wC), B.ptr(bC), B.ptr(gBg),
                                        B.ptr(gCg), B.ptr(gBC), B.ptr(g_scale), B.ptr(g_ang), B.ptr(gw[0]), B.ptr(gw[1]), B.ptr(gw[2]), B.ptr(gw[3]),
                                        I64(b * s), G, N, R, B.stream_ptr()), "m3_prep_bc_bwd")
-        g_inc = torch.flip(torch.cumsum(torch.flip(g_ang, (1,)), dim=1), (1,)).contiguous()     # adjoint of the prefix sum
+        g_inc = _cumsum_seq(g_ang, reverse=True)                                             # adjoint of the prefix sum
         g_dt = g_dt.float().contiguous() if g_dt is not None else torch.zeros(b, s, H, **f32)
         g_A = g_A.float().contiguous() if g_A is not None else torch.zeros(b, s, H, **f32)
         g_tail = torch.empty(b, s, 3 * H + R, dtype=torch.bfloat16, device=dev)

@@ -169,7 +169,7 @@ def scan_backward(g_out, g_hlast, x, Bm, Cm, z, A, dt, D, h0, saved, chunk):
                  sA=geo.x_s, sB=geo.bc_s, sC=geo.st_s, b_div2=hg)
     # 4. reverse carry over chunks
     dS = torch.empty(Bn, nc, H, P, N, dtype=bf, device=dev)
-    dcumL = torch.empty(Bn, nc, H, dtype=torch.float32, device=dev)
+    dcumL = torch.zeros(Bn, nc, H, dtype=torch.float32, device=dev)
     dh0 = torch.empty(Bn, H, P, N, dtype=torch.float32, device=dev) if h0 is not None else None
     ghl = None if g_hlast is None else _f32c(g_hlast)
     B.check(lib.cmb_m3_state_bwd(B.ptr(dHy), B.ptr(hc), B.ptr(cum), B.ptr(ghl), B.ptr(dS), B.ptr(dcumL), B.ptr(dh0), Bn, nc,
