@@ -255,6 +255,50 @@ class MuonWithNSCarrier(Optimizer):
         self._apply_update(self._momentum(grad.float(), p, st), p)
 
 
+NS_STREAMS = 4
+_ns_stream_pool: dict = {}
+
+
+def ns_streams(device) -> list:
+    """Side streams on which independent Newton–Schulz chains run concurrently: one chain's Gram products only fill about half
+    of the SMs (72–128 tiles of a 2048² matrix on 148 SMs), so several matrices are orthogonalised at the same time."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _ns_stream_pool:
+        _ns_stream_pool[key] = [torch.cuda.Stream(device=key) for _ in range(NS_STREAMS)]
+    return _ns_stream_pool[key]
+
+
+def _muon_step_multistream(self, grads=None) -> None:
+    self.step_count += 1
+    work = []
+    for name, p in self.params:
+        g = grads.get(name) if grads is not None else p.grad
+        if g is not None:
+            work.append((name, g, p, self.state_for(name, p)))
+    if not work:
+        return
+    dev = work[0][2].device
+    if dev.type != "cuda" or not B.kernels_enabled() or len(work) < 2:
+        for name, g, p, st in work:
+            self.apply_single(name, g, p, st)
+        return
+    main = torch.cuda.current_stream(dev)
+    ready = main.record_event()
+    streams = ns_streams(dev)
+    # largest first, dealt round-robin: the streams finish at about the same time
+    work.sort(key=lambda w: -w[2].numel())
+    for s in streams:
+        s.wait_event(ready)
+    for i, (name, g, p, st) in enumerate(work):
+        with torch.cuda.stream(streams[i % len(streams)]):
+            self.apply_single(name, g, p, st)
+    for s in streams:
+        main.wait_stream(s)
+
+
+MuonWithNSCarrier.step = torch.no_grad()(_muon_step_multistream)
+
+
 class QuantizedMuonWithNSCarrier(MuonWithNSCarrier):
     """Muon whose momentum lives as uint8 codes + per-256 fp32 absmax (4× smaller state)."""
 
