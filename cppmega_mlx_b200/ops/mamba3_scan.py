@@ -120,7 +120,7 @@ class _Mamba3ScanFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, Bm, Cm, z, A, dt, D, h0, chunk):
         from .mamba3_scan_cuda import scan_forward
-        out, h_last, saved = scan_forward(x, Bm, Cm, z, A, dt, D, h0, chunk)
+        out, h_last, saved = scan_forward(x, Bm, Cm, z, A, dt, D, h0, chunk, keep_for_backward=any(ctx.needs_input_grad[:7]))
         ctx.save_for_backward(x, Bm, Cm, z, A, dt, D, h0 if h0 is not None else x.new_zeros(0), *saved)
         ctx.chunk = chunk
         ctx.has_h0 = h0 is not None

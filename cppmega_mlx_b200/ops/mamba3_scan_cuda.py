@@ -23,6 +23,7 @@ from . import _backend as B
 from .gemm import gemm_batched
 
 I64 = ctypes.c_longlong
+KEEP_M_BYTES = 1 << 30   # keep the intra-chunk matrices for the backward when they are at most 1 GiB per call
 
 
 def _shape_ok(x, Bm, chunk) -> bool:
@@ -76,7 +77,7 @@ def _intra_matrix(Cg, Bg, cum, geo: _Geo):
     return M
 
 
-def scan_forward(x, Bm, Cm, z, A, dt, D, h0, chunk):
+def scan_forward(x, Bm, Cm, z, A, dt, D, h0, chunk, keep_for_backward: bool = False):
     lib = B.load_library()
     Bn, S, H, P = x.shape
     G, N = Bm.shape[2], Bm.shape[3]
@@ -111,18 +112,20 @@ def scan_forward(x, Bm, Cm, z, A, dt, D, h0, chunk):
     M = _intra_matrix(Cg, Bg, cum, geo)
     gemm_batched(M, x, Y, M=L, N=P, K=L, a_mn=False, b_mn=True, lda=geo.m_ld, ldb=geo.x_ld, ldc=geo.x_ld, nb=geo.nbH,
                  sA=geo.m_s, sB=geo.x_s, sC=geo.x_s, accumulate=True)
+    keep_m = M if keep_for_backward and M.numel() * 2 <= KEEP_M_BYTES else None
     del M
     ypre = torch.empty_like(x)
     out = torch.empty_like(x)
     B.check(lib.cmb_m3_finalize_fwd(B.ptr(Y), B.ptr(x), B.ptr(z), B.ptr(D32), B.ptr(ypre), B.ptr(out), Bn, S, H, P,
                                     I64(zs[0]), I64(zs[1]), I64(zs[2]), st()), "m3_finalize_fwd")
     h_dtype = x.dtype if h0 is None else h0.dtype
-    return out, hlast.to(h_dtype), (cum, hc, ypre, xw)
+    return out, hlast.to(h_dtype), (cum, hc, ypre, xw) + ((keep_m,) if keep_m is not None else ())
 
 
 def scan_backward(g_out, g_hlast, x, Bm, Cm, z, A, dt, D, h0, saved, chunk):
     lib = B.load_library()
-    cum, hc, ypre, xw = saved
+    cum, hc, ypre, xw = saved[:4]
+    M_saved = saved[4] if len(saved) > 4 else None
     Bn, S, H, P = x.shape
     G, N = Bm.shape[2], Bm.shape[3]
     L = chunk
@@ -144,8 +147,8 @@ def scan_backward(g_out, g_hlast, x, Bm, Cm, z, A, dt, D, h0, saved, chunk):
     B.check(lib.cmb_m3_bwd_pre(B.ptr(g_out), B.ptr(z), B.ptr(ypre), B.ptr(x), B.ptr(D32), B.ptr(cum), B.ptr(dy), B.ptr(dz),
                                B.ptr(dye), B.ptr(dx_acc), B.ptr(dcum), B.ptr(dD), Bn, S, H, P, L, I64(zs[0]), I64(zs[1]),
                                I64(zs[2]), st()), "m3_bwd_pre")
-    # 2. intra-chunk term  Y1 = M X
-    M = _intra_matrix(Cg, Bg, cum, geo)
+    # 2. intra-chunk term  Y1 = M X   (M kept from the forward when it is small enough, else recomputed)
+    M = M_saved if M_saved is not None else _intra_matrix(Cg, Bg, cum, geo)
     dM = torch.empty_like(M)
     gemm_batched(dy, x, dM, M=L, N=L, K=P, a_mn=False, b_mn=False, lda=geo.x_ld, ldb=geo.x_ld, ldc=geo.m_ld, nb=geo.nbH,
                  sA=geo.x_s, sB=geo.x_s, sC=geo.m_s)

@@ -81,24 +81,35 @@ class FusedZeRO1Comm:
                                         F32(adamw.lr), F32(b1), F32(b2), F32(adamw.eps), F32(adamw.weight_decay), F32(c1),
                                         F32(c2), st()), "zero1_adamw")
         if muon is not None:
+            from ..training.optimizers import ns_streams
             muon.step_count += 1
-            for name, p in muon.params:
-                owner, off, n = flat.slots[name]
-                goff = owner * flat.segment + off
-                s = muon.state_for(name, p)
-                rows, cols = p.shape
-                if n % 8:
-                    raise RuntimeError(f"fused Muon needs an element count that is a multiple of 8, got {tuple(p.shape)} for {name}")
-                u = torch.empty(rows, cols, dtype=torch.bfloat16, device=p.device)
-                sumsq = torch.zeros(1, dtype=torch.float32, device=p.device)
-                B.check(lib.cmb_zero1_muon_reduce(gp, pp, rank, W, I64(goff), I64(n), B.ptr(s["v"]), B.ptr(u), B.ptr(sumsq),
-                                                  F32(muon.momentum), F32(muon.weight_decay), int(muon.nesterov), st()),
-                        "zero1_muon_reduce")
-                if rows % 8 or cols % 8:   # too narrow for the tensor-core iteration (e.g. a 4-row gate): same maths in PyTorch ops
-                    o = newton_schulz5(u, steps=muon.ns_steps, ns_carrier="bf16", output_dtype=torch.bfloat16).contiguous()
-                else:
-                    o = newton_schulz5_bf16_(u, sumsq, muon.ns_steps)
-                coef = muon.lr * max(1.0, rows / cols) ** 0.5
-                B.check(lib.cmb_zero1_push_update(pp, rank, W, I64(goff), I64(n), B.ptr(o), F32(coef), st()), "zero1_push_update")
+            dev = flat.params.device
+            main = torch.cuda.current_stream(dev)
+            ready = main.record_event()
+            streams = ns_streams(dev)
+            for s_ in streams:
+                s_.wait_event(ready)
+            work = sorted(muon.params, key=lambda np_: -np_[1].numel())
+            for i, (name, p) in enumerate(work):          # independent matrices: reduce → Newton–Schulz → push, several at a time
+                with torch.cuda.stream(streams[i % len(streams)]):
+                    owner, off, n = flat.slots[name]
+                    goff = owner * flat.segment + off
+                    s = muon.state_for(name, p)
+                    rows, cols = p.shape
+                    if n % 8:
+                        raise RuntimeError(f"fused Muon needs an element count that is a multiple of 8, got {tuple(p.shape)} for {name}")
+                    u = torch.empty(rows, cols, dtype=torch.bfloat16, device=p.device)
+                    sumsq = torch.zeros(1, dtype=torch.float32, device=p.device)
+                    B.check(lib.cmb_zero1_muon_reduce(gp, pp, rank, W, I64(goff), I64(n), B.ptr(s["v"]), B.ptr(u), B.ptr(sumsq),
+                                                      F32(muon.momentum), F32(muon.weight_decay), int(muon.nesterov), st()),
+                            "zero1_muon_reduce")
+                    if rows % 8 or cols % 8:   # too narrow for the tensor-core iteration (e.g. a 4-row gate): same maths in PyTorch ops
+                        o = newton_schulz5(u, steps=muon.ns_steps, ns_carrier="bf16", output_dtype=torch.bfloat16).contiguous()
+                    else:
+                        o = newton_schulz5_bf16_(u, sumsq, muon.ns_steps)
+                    coef = muon.lr * max(1.0, rows / cols) ** 0.5
+                    B.check(lib.cmb_zero1_push_update(pp, rank, W, I64(goff), I64(n), B.ptr(o), F32(coef), st()), "zero1_push_update")
+            for s_ in streams:
+                main.wait_stream(s_)
         self.barrier()  # all parameters delivered everywhere; all gradients consumed
         return True
