@@ -40,6 +40,7 @@ def parse_args():
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused", "stub"],
                     help="stub = no communication at all (measurement aid for exposed-communication time; not a valid training run)")
     ap.add_argument("--depth", type=int, default=0, help="override layer count (debugging only; makes the result non-headline)")
+    ap.add_argument("--ep", type=int, default=1, help="expert-parallel size for MoE profiles (1 = experts replicated; N = world size)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--grad-checkpoint", default="auto", choices=["auto", "on", "off"],
                     help="per-block activation recomputation; auto = on for the eager arm (it does not fit otherwise)")
@@ -144,7 +145,12 @@ def main():
     # auto: the kernel arm keeps all activations (it fits in 180 GB); the eager arm needs per-block recomputation to fit at all
     ckpt = args.grad_checkpoint == "on" or (args.grad_checkpoint == "auto" and not ours)
     overrides["grad_checkpoint"] = ckpt
-    model = profile.build_model(dtype=torch.bfloat16, device=dev, **overrides)
+    ep_group = None
+    if args.ep > 1:
+        if args.ep != world:
+            raise SystemExit("--ep must equal the number of GPUs")
+        ep_group = dist.group.WORLD
+    model = profile.build_model(dtype=torch.bfloat16, device=dev, ep_group=ep_group, **overrides)
     cfg = model.config
     nparams = model.num_parameters()
 
@@ -155,7 +161,14 @@ def main():
     comm = args.comm
     if comm == "auto":
         comm = "fused" if (ours and world > 1 and os.environ.get("CPPMEGA_FUSED_ZERO1", "1") != "0") else "nccl"
-    opt = DistributedZeRO1Optimizer(model, factory, comm=comm)
+    if ep_group is not None:
+        from cppmega_mlx_b200.training.distributed_optimizer import ExpertParallelZeRO1Optimizer
+        opt = ExpertParallelZeRO1Optimizer(model, factory, ep_size=world, comm=comm)
+        if ours and os.environ.get("CPPMEGA_FUSED_EP", "1") != "0":
+            from cppmega_mlx_b200.parallel.fused_ep import enable_fused_ep
+            enable_fused_ep(model, ep_group, dev, max_tokens=args.micro_batch * args.seq_len)
+    else:
+        opt = DistributedZeRO1Optimizer(model, factory, comm=comm)
     opt.zero_grad()
     stepper = PretrainingStep(model, opt, loss_fn=make_loss_fn(backend="cce"), sync_metrics=False, device=dev)
 
@@ -221,13 +234,13 @@ def main():
 
     if rank == 0:
         out = {
-            "metric": "tokens/sec/box, 1B hybrid ZeRO-1 bf16", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "metric": "tokens/sec/box, 1B hybrid ZeRO-1 bf16" if args.profile == "hybrid_1b" else f"tokens/sec/box, {args.profile} bf16", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights",
             "impl": args.impl,
             "config": {"model": f"{args.profile}: {cfg.pattern}x{cfg.depth // len(cfg.pattern)} d{cfg.hidden_size} "
                                 f"ffn{cfg.ffn_hidden_size} vocab{cfg.vocab_size} mtp{cfg.mtp_depth if cfg.mtp_enabled else 0}",
-                       "params": nparams, "global_batch": mb * world, "seq_len": S, "parallelism": f"dp{world} zero1 ({comm})",
+                       "params": nparams, "global_batch": mb * world, "seq_len": S, "parallelism": f"dp{world} zero1 ({comm})" + (f" ep{args.ep}" if args.ep > 1 else ""),
                        "optimizer": args.optimizer, "micro_batch_per_gpu": mb, "grad_checkpoint": ckpt,
                        "l2": "working set per step (weights + activations, tens of GB) far exceeds the 126 MB L2; no flush needed"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,

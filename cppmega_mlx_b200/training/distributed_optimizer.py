@@ -219,3 +219,63 @@ def _merge_state_dicts(parts: list[dict]) -> dict:
             else:
                 out[k] = v
     return out
+
+
+def is_expert_parameter(name: str) -> bool:
+    """Routed-expert weights (sharded over the expert-parallel group, hence *not* replicated over it)."""
+    return ".experts.w_gate_up" in name or ".experts.w_down" in name
+
+
+class ExpertParallelZeRO1Optimizer:
+    """ZeRO-1 for a model whose MoE layers are expert-parallel over the whole data-parallel group.
+
+    Replicated parameters (everything except the routed experts) go through ``DistributedZeRO1Optimizer`` as usual.  The routed
+    experts exist once per expert-parallel group, so their gradients are already complete after the backward all-to-all and need
+    no reduction; they are scaled by ``1 / ep_size`` (the loss is a mean over ranks) and updated by a local inner optimizer.
+    When the expert-parallel group is smaller than the world, the experts' own data-parallel replicas are averaged over
+    ``expert_dp_group`` by a second ZeRO-1 instance."""
+
+    def __init__(self, model, inner_factory: Callable[[NamedParams], object], *, ep_size: int, group=None, expert_dp_group=None, comm: str = "nccl"):
+        named = named_trainable(model)
+        dense = [(n, p) for n, p in named if not is_expert_parameter(n)]
+        experts = [(n, p) for n, p in named if is_expert_parameter(n)]
+        self.ep_size = ep_size
+        self.dense = DistributedZeRO1Optimizer(dense, inner_factory, group=group, comm=comm)
+        self.expert_params = experts
+        if expert_dp_group is not None and dist.get_world_size(expert_dp_group) > 1:
+            self.experts = DistributedZeRO1Optimizer(experts, inner_factory, group=expert_dp_group, comm="nccl")
+        else:
+            self.experts = inner_factory(experts) if experts else None
+        self.step_count = 0
+
+    @property
+    def state(self):
+        return {"dense": self.dense.state, "experts": self.experts.state if self.experts is not None else {}}
+
+    def shard_owned_state_bytes(self) -> int:
+        e = self.experts
+        eb = 0 if e is None else int(e.shard_owned_state_bytes() if hasattr(e, "shard_owned_state_bytes") else e.state_bytes())
+        return self.dense.shard_owned_state_bytes() + eb
+
+    def zero_grad(self) -> None:
+        self.dense.zero_grad()
+        if self.experts is not None:
+            self.experts.zero_grad()
+
+    @torch.no_grad()
+    def step(self) -> None:
+        self.step_count += 1
+        if self.ep_size > 1:
+            torch._foreach_mul_([p.grad for _, p in self.expert_params if p.grad is not None], 1.0 / self.ep_size)
+        self.dense.step()
+        if self.experts is not None:
+            self.experts.step()
+
+    def state_dict(self) -> dict:
+        return {"step": self.step_count, "dense": self.dense.state_dict(), "experts": self.experts.state_dict() if self.experts is not None else {}}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.step_count = int(sd.get("step", 0))
+        self.dense.load_state_dict(sd["dense"])
+        if self.experts is not None and sd.get("experts"):
+            self.experts.load_state_dict(sd["experts"])

@@ -136,3 +136,33 @@ def _pp_rank(rank, world):
 def test_pipeline_1f1b_matches_single_rank():
     counts = run_ranks(_pp_rank, 2)
     assert all(c > 0 for c in counts)
+
+
+def _ep_zero1_rank(rank, world):
+    import torch.distributed as dist
+    from cppmega_mlx_b200.data.batch import synthetic_token_batch
+    from cppmega_mlx_b200.models.hybrid_lm import HybridTinyLM
+    from cppmega_mlx_b200.recipes.model_factory import build_local_gb10_quarter_tiny_smoke_model
+    from cppmega_mlx_b200.training.compiled import PretrainingStep
+    from cppmega_mlx_b200.training.distributed_optimizer import ExpertParallelZeRO1Optimizer, is_expert_parameter
+    from cppmega_mlx_b200.training.optimizers import make_adamw
+    torch.manual_seed(0)
+    cfg = build_local_gb10_quarter_tiny_smoke_model(pattern="AE", depth=2, dsa_a_layer_ranks=(), mtp_enabled=False).config
+    torch.manual_seed(0)
+    m = HybridTinyLM(cfg, ep_group=dist.group.WORLD)
+    opt = ExpertParallelZeRO1Optimizer(m, lambda ps: make_adamw(ps, learning_rate=1e-2), ep_size=world)
+    opt.zero_grad()
+    step = PretrainingStep(m, opt)
+    b = synthetic_token_batch(2, 16, vocab_size=cfg.vocab_size, seed=rank)
+    losses = [step(b).loss for _ in range(4)]
+    dense = torch.cat([p.detach().reshape(-1) for n, p in m.named_parameters() if not is_expert_parameter(n)])
+    ref = dense.clone()
+    dist.broadcast(ref, 0)
+    n_local = m.layers[1].block.experts.w_down.shape[0]
+    return losses, float((dense - ref).abs().max()), n_local
+
+
+def test_expert_parallel_zero1_trains_and_keeps_replicas_in_sync():
+    out = run_ranks(_ep_zero1_rank, 2)
+    for losses, spread, n_local in out:
+        assert losses[-1] < losses[0] and spread == 0.0 and n_local == 2      # 4 experts over 2 ranks; dense weights identical everywhere
