@@ -41,6 +41,7 @@ def parse_args():
                     help="stub = no communication at all (measurement aid for exposed-communication time; not a valid training run)")
     ap.add_argument("--depth", type=int, default=0, help="override layer count (debugging only; makes the result non-headline)")
     ap.add_argument("--ep", type=int, default=1, help="expert-parallel size for MoE profiles (1 = experts replicated; N = world size)")
+    ap.add_argument("--expert-gemm", default="bf16", choices=["bf16", "mxfp8"], help="routed-expert forward GEMMs (MoE profiles)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--grad-checkpoint", default="auto", choices=["auto", "on", "off"],
                     help="per-block activation recomputation; auto = on for the eager arm (it does not fit otherwise)")
@@ -145,6 +146,8 @@ def main():
     # auto: the kernel arm keeps all activations (it fits in 180 GB); the eager arm needs per-block recomputation to fit at all
     ckpt = args.grad_checkpoint == "on" or (args.grad_checkpoint == "auto" and not ours)
     overrides["grad_checkpoint"] = ckpt
+    if args.expert_gemm != "bf16":
+        overrides["moe_expert_gemm"] = args.expert_gemm
     ep_group = None
     if args.ep > 1:
         if args.ep != world:
@@ -241,7 +244,7 @@ def main():
             "config": {"model": f"{args.profile}: {cfg.pattern}x{cfg.depth // len(cfg.pattern)} d{cfg.hidden_size} "
                                 f"ffn{cfg.ffn_hidden_size} vocab{cfg.vocab_size} mtp{cfg.mtp_depth if cfg.mtp_enabled else 0}",
                        "params": nparams, "global_batch": mb * world, "seq_len": S, "parallelism": f"dp{world} zero1 ({comm})" + (f" ep{args.ep}" if args.ep > 1 else ""),
-                       "optimizer": args.optimizer, "micro_batch_per_gpu": mb, "grad_checkpoint": ckpt,
+                       "optimizer": args.optimizer, "expert_gemm": args.expert_gemm, "micro_batch_per_gpu": mb, "grad_checkpoint": ckpt,
                        "l2": "working set per step (weights + activations, tens of GB) far exceeds the 126 MB L2; no flush needed"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }

@@ -126,6 +126,7 @@ struct MxParams {
   const uint8_t* sfa;   // tiled atoms [ceil(M/128)][K/128][512]
   const uint8_t* sfb;   // tiled atoms [ceil(N/128)][K/128][512]
   int* status;
+  const int* tile_group;   // grouped (MoE) mode: expert of each 128-row tile of A / C; B is the experts' weights stacked [E·N, K]
 };
 
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -191,6 +192,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const int tm = t % num_m, tn = t / num_m;
+        // grouped mode: the B rows (and their scale atoms) of this tile start at expert·N
+        const int brow0 = (p.tile_group != nullptr ? p.tile_group[tm] * p.N : 0) + tn * MX_BN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, status, ST_TIMEOUT_EMPTY)) {
             ok = false;
@@ -202,11 +205,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           uint8_t* ssfb = ssfa + MX_SF_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], MX_STAGE_BYTES);
           tma_load_2d(sa, &tmA, &full_bar[stage], kb * MX_BK, tm * MX_BM);
-          tma_load_2d(sb, &tmB, &full_bar[stage], kb * MX_BK, tn * MX_BN);
+          tma_load_2d(sb, &tmB, &full_bar[stage], kb * MX_BK, brow0);
           bulk_load(ssfa, p.sfa + (static_cast<long long>(tm) * num_kb + kb) * MX_SF_BYTES, MX_SF_BYTES, &full_bar[stage]);
 #pragma unroll
           for (int a = 0; a < Cfg::SFB_ATOMS; ++a)   // a tile past the last row block reads the (zeroed) padding atoms
-            bulk_load(ssfb + a * MX_SF_BYTES, p.sfb + (static_cast<long long>(tn * Cfg::SFB_ATOMS + a) * num_kb + kb) * MX_SF_BYTES,
+            bulk_load(ssfb + a * MX_SF_BYTES, p.sfb + (static_cast<long long>(brow0 / 128 + a) * num_kb + kb) * MX_SF_BYTES,
                       MX_SF_BYTES, &full_bar[stage]);
           if (++stage == MX_STAGES) {
             stage = 0;
@@ -352,12 +355,12 @@ extern "C" int cmb_mxfp8_dequant(const void* q, long long ldq, const void* sf_ti
 // C[M,N] bf16 (pitch ldc) = A[M,K] · B[N,K]ᵀ with 1×32 e8m0 block scales in the tiled layout. K % 128 == 0, pitches % 16 == 0.
 template <int BN>
 static int launch_mx(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N, int K, long long lda,
-                     long long ldb, long long ldc, int* status, int max_ctas, void* stream) {
+                     long long ldb, long long ldc, int* status, int max_ctas, void* stream, const int* tile_group = nullptr, int groups = 1) {
   using Cfg = cmb::MxCfg<BN>;
   CUtensorMap tmA, tmB, tmC;
   int rc = cmb_host::make_tmap_2d(&tmA, A, 1, M, K, lda, cmb::MX_BM, cmb::MX_BK, 128);
   if (rc) return rc;
-  rc = cmb_host::make_tmap_2d(&tmB, B, 1, N, K, ldb, BN, cmb::MX_BK, 128);
+  rc = cmb_host::make_tmap_2d(&tmB, B, 1, static_cast<uint64_t>(N) * groups, K, ldb, BN, cmb::MX_BK, 128);
   if (rc) return rc + 10000;
   rc = cmb_host::make_tmap_2d(&tmC, C, 2, M, N, ldc, 32, 64, 128);
   if (rc) return rc + 20000;
@@ -373,7 +376,7 @@ static int launch_mx(const void* A, const void* sfa, const void* B, const void* 
   int grid = sms;
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = static_cast<int>(tiles);
-  cmb::MxParams p{M, N, K, static_cast<const uint8_t*>(sfa), static_cast<const uint8_t*>(sfb), status};
+  cmb::MxParams p{M, N, K, static_cast<const uint8_t*>(sfa), static_cast<const uint8_t*>(sfb), status, tile_group};
   cmb::gemm_mxfp8_kernel<BN><<<grid, cmb::MX_THREADS, Cfg::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 104;
 }
@@ -388,4 +391,16 @@ extern "C" int cmb_gemm_mxfp8(const void* A, const void* sfa, const void* B, con
   const bool wide = N >= 256 && (N % 256 == 0 || bn_hint == 256) && bn_hint != 128;
   return wide ? launch_mx<256>(A, sfa, B, sfb, C, M, N, K, lda, ldb, ldc, status, max_ctas, stream)
               : launch_mx<128>(A, sfa, B, sfb, C, M, N, K, lda, ldb, ldc, status, max_ctas, stream);
+}
+
+// Grouped (MoE) form: A [M, K] rows sorted by expert in 128-row aligned segments, `tile_group[i]` = expert of the i-th 128-row
+// tile, B = the experts' weights stacked [groups·N, K] (N a multiple of the tile width), scales of B tiled over groups·N rows.
+extern "C" int cmb_gemm_mxfp8_grouped(const void* A, const void* sfa, const void* B, const void* sfb, void* C, const int* tile_group,
+                                      int groups, int M, int N, int K, long long lda, long long ldb, long long ldc, int* status,
+                                      void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || groups <= 0) return 0;
+  if (K % cmb::MX_BK || M % 128 || tile_group == nullptr) return 110;
+  if (N % 256 == 0) return launch_mx<256>(A, sfa, B, sfb, C, M, N, K, lda, ldb, ldc, status, 0, stream, tile_group, groups);
+  if (N % 128 == 0) return launch_mx<128>(A, sfa, B, sfb, C, M, N, K, lda, ldb, ldc, status, 0, stream, tile_group, groups);
+  return 111;
 }

@@ -124,6 +124,7 @@ class HybridTinyConfig:
     moe_num_shared_experts: int = 1
     moe_node_limited_routing: int | None = None
     moe_aux_loss_coeff: float = 0.0
+    moe_expert_gemm: str = "bf16"             # "mxfp8": routed-expert forward GEMMs in block-scaled MXFP8
     mtp_sequential: bool = False
     tie_embeddings: bool = False
     init_std: float = 0.02
@@ -197,7 +198,7 @@ class HybridTinyConfig:
                          shared_expert_hidden_size=self.moe_shared_expert_hidden_size, activation=self.moe_activation,
                          scoring=self.moe_scoring, aux_loss_free=self.moe_aux_loss_free,
                          bias_update_rate=self.moe_bias_update_rate, num_shared_experts=self.moe_num_shared_experts,
-                         node_limited_routing=self.moe_node_limited_routing)
+                         node_limited_routing=self.moe_node_limited_routing, expert_gemm=self.moe_expert_gemm)
 
     def structure_embedding_config(self) -> dict[str, Any]:
         for n in ("structure_bottleneck_dim", "structure_num_categories", "structure_max_dep_level",

@@ -49,6 +49,7 @@ class MoEConfig:
     node_limited_routing: int | None = None
     num_shared_experts: int = 1
     expert_parallel_size: int = 1
+    expert_gemm: str = "bf16"        # "mxfp8": routed-expert forward products in block-scaled MXFP8 (bf16 straight-through backward)
 
     def __post_init__(self) -> None:
         for n in ("d_model", "num_experts", "top_k", "expert_hidden_size"):
@@ -58,6 +59,8 @@ class MoEConfig:
             raise ValueError("top_k must be <= num_experts")
         if self.shared_expert_hidden_size is not None and self.shared_expert_hidden_size <= 0:
             raise ValueError("shared_expert_hidden_size must be positive")
+        if self.expert_gemm not in ("bf16", "mxfp8"):
+            raise ValueError("expert_gemm must be 'bf16' or 'mxfp8'")
         if self.activation not in ACTIVATIONS:
             raise ValueError(f"unsupported MoE activation={self.activation!r}")
         if self.router_dtype not in (None, "fp32"):
@@ -229,8 +232,7 @@ class MoE(nn.Module):
             L = GG.build_layout(flat_e, E)
             tok = torch.div(L.order, k, rounding_mode="floor")
             xp = GG.scatter_to_padded(flat, tok, L)
-            h = ops.swiglu(GG.grouped_linear_padded(xp, self.experts.w_gate_up, L))
-            yp = GG.grouped_linear_padded(h, self.experts.w_down, L)
+            yp = self.expert_ffn_padded(xp, L)
             ys = yp.index_select(0, L.slot) * top_w.reshape(-1)[L.order].to(yp.dtype)[:, None]
             return torch.zeros_like(flat).index_add_(0, tok, ys)
         order = torch.argsort(flat_e, stable=True)
@@ -243,14 +245,24 @@ class MoE(nn.Module):
         out.index_add_(0, tok, ys)
         return out
 
+    def expert_ffn_padded(self, xp: torch.Tensor, layout) -> torch.Tensor:
+        """gate|up → SwiGLU → down over a padded expert-sorted buffer, in bf16 or (forward only) block-scaled MXFP8."""
+        from ..ops import grouped_gemm_cuda as GG
+        if self.config.expert_gemm == "mxfp8":
+            from ..ops import mxfp8 as MX
+            if MX.grouped_mxfp8_supported(xp, self.experts.w_gate_up) and self.experts.w_down.shape[2] % 128 == 0:
+                h = ops.swiglu(MX.grouped_linear_padded_mxfp8(xp, self.experts.w_gate_up, layout))
+                return MX.grouped_linear_padded_mxfp8(h, self.experts.w_down, layout)
+        h = ops.swiglu(GG.grouped_linear_padded(xp, self.experts.w_gate_up, layout))
+        return GG.grouped_linear_padded(h, self.experts.w_down, layout)
+
     def local_expert_forward(self, xs: torch.Tensor, local_e: torch.Tensor) -> torch.Tensor:
         """Rows ``xs`` sorted by local expert id ``local_e`` → expert outputs in the same order (expert-parallel ranks)."""
         from ..ops import grouped_gemm_cuda as GG
         if ops.kernels_enabled() and GG.supported(xs, self.experts.w_gate_up) and self.config.activation == "swiglu" and xs.shape[0] > 0:
             L = GG.build_layout(local_e, self.local_experts)          # rows are already sorted: order is the identity
             xp = GG.scatter_to_padded(xs, L.order, L)
-            h = ops.swiglu(GG.grouped_linear_padded(xp, self.experts.w_gate_up, L))
-            return GG.grouped_linear_padded(h, self.experts.w_down, L).index_select(0, L.slot)
+            return self.expert_ffn_padded(xp, L).index_select(0, L.slot)
         return self.experts(xs, torch.bincount(local_e, minlength=self.local_experts))
 
     def forward(self, x: torch.Tensor) -> MoEOutput:

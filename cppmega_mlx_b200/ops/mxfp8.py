@@ -129,3 +129,49 @@ def mxfp8_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     y = xq + (x2 - x2.detach()) * 0                      # keep the graph of x for the straight-through backward
     y = (x2 + (xq - x2).detach()) @ (w + (wq - w).detach()).t()
     return y.view(*x.shape[:-1], w.shape[0])
+
+
+def gemm_mxfp8_grouped(a: MXFP8Tensor, w: MXFP8Tensor, tile_group: torch.Tensor, groups: int) -> torch.Tensor:
+    """a [rows, K] (rows % 128 == 0, expert-sorted in 128-row aligned segments) × stacked expert weights w [groups·N, K] → [rows, N]."""
+    M, K = a.shape
+    GN, K2 = w.shape
+    N = GN // groups
+    if K != K2 or K % 128 or M % 128 or N % 128:
+        raise ValueError(f"grouped MXFP8 GEMM needs K % 128 == 0, rows % 128 == 0 and N % 128 == 0, got {a.shape} x {w.shape} / {groups}")
+    lib = B.load_library()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=a.data.device)
+    st = B.status_buffer(a.data.device)
+    ll = ctypes.c_longlong
+    B.check(lib.cmb_gemm_mxfp8_grouped(B.ptr(a.data), B.ptr(a.scales), B.ptr(w.data), B.ptr(w.scales), B.ptr(out), B.ptr(tile_group), groups, M, N,
+                                       K, ll(K), ll(K), ll(N), B.ptr(st), B.stream_ptr()), "gemm_mxfp8_grouped")
+    return out
+
+
+class _GroupedMXFP8Fn(torch.autograd.Function):
+    """Grouped expert product with an MXFP8 forward (block-scaled tcgen05) and a bf16 straight-through backward."""
+
+    @staticmethod
+    def forward(ctx, x, w, layout):
+        E, N, K = w.shape
+        ctx.save_for_backward(x, w)
+        ctx.layout = layout
+        return gemm_mxfp8_grouped(quantize_mxfp8(x), quantize_mxfp8(w.reshape(E * N, K)), layout.tile_group, E)
+
+    @staticmethod
+    def backward(ctx, gy):
+        from . import grouped_gemm_cuda as GG
+        x, w = ctx.saved_tensors
+        L = ctx.layout
+        gy = gy.contiguous()
+        gx = GG._fwd(gy, w, L, True) if ctx.needs_input_grad[0] else None
+        gw = GG._wgrad(gy, x, L, w.shape) if ctx.needs_input_grad[1] else None
+        return gx, gw, None
+
+
+def grouped_linear_padded_mxfp8(x: torch.Tensor, w: torch.Tensor, layout) -> torch.Tensor:
+    return _GroupedMXFP8Fn.apply(x.contiguous(), w, layout)
+
+
+def grouped_mxfp8_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (B.on_gpu(x, w) and x.dtype == torch.bfloat16 and w.dim() == 3 and w.is_contiguous() and x.shape[-1] % 128 == 0
+            and w.shape[1] % 128 == 0 and w.shape[2] == x.shape[-1])

@@ -158,8 +158,7 @@ def fused_ep_moe_forward(moe, comm: FusedEPComm, flat: torch.Tensor, top_idx: to
     dest, slot, layout, _overflow = comm.plan(top_idx.reshape(-1))
     tok = torch.arange(T * k, device=flat.device) // k
     xp = _Dispatch.apply(flat.contiguous(), tok, dest, slot, layout.valid_rows, comm)
-    h = ops.swiglu(GG.grouped_linear_padded(xp, moe.experts.w_gate_up, layout))
-    yp = GG.grouped_linear_padded(h, moe.experts.w_down, layout)
+    yp = moe.expert_ffn_padded(xp, layout)
     rows = _Gather.apply(yp, dest, slot, layout.valid_rows, comm)                # [T·k, d] in assignment order
     return (rows.view(T, k, -1) * top_w.to(rows.dtype)[..., None]).sum(1)
 

@@ -55,3 +55,28 @@ def test_mxfp8_linear_forward_and_ste_backward():
     y.backward(gy)
     assert torch.allclose(x.grad.float(), gy.float() @ w.float(), atol=5e-2, rtol=5e-2)
     assert torch.allclose(w.grad.float(), gy.float().reshape(-1, 384).t() @ x.float().reshape(-1, 256), atol=0.5, rtol=5e-2)
+
+
+def test_grouped_mxfp8_expert_ffn_matches_bf16_grouped():
+    from cppmega_mlx_b200.nn.moe import MoE, MoEConfig
+    from cppmega_mlx_b200.ops import _backend as B
+    torch.manual_seed(3)
+    kw = dict(d_model=256, num_experts=8, top_k=2, expert_hidden_size=128, shared_expert_hidden_size=None, activation="swiglu", scoring="sigmoid",
+              aux_loss_free=True)
+    a = MoE(MoEConfig(**kw)).cuda().bfloat16()
+    b = MoE(MoEConfig(**kw, expert_gemm="mxfp8")).cuda().bfloat16()
+    b.load_state_dict(a.state_dict())
+    x = (torch.randn(2, 200, 256, device="cuda") * 0.5).bfloat16()
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    n0 = B.launch_count()
+    ya, yb = a(xa).output, b(xb).output
+    assert B.launch_count() > n0
+    err = float((ya.float() - yb.float()).abs().max()) / float(ya.float().abs().max())
+    assert 0 < err < 0.1                                   # fp8 forward: close to, but not identical with, the bf16 product
+    g = torch.randn_like(ya)
+    ya.backward(g)
+    yb.backward(g)
+    assert float((xa.grad.float() - xb.grad.float()).abs().max()) < 0.15 * float(xa.grad.float().abs().max())
+    ga, gb = a.experts.w_down.grad.float(), b.experts.w_down.grad.float()
+    assert float((ga - gb).abs().max()) < 0.15 * float(ga.abs().max())
+    B.check_status()
