@@ -265,9 +265,98 @@ def bench_sparse_mla(args) -> list[dict]:
     return rows
 
 
+def bench_decode(args) -> list[dict]:
+    """Decode-step attention over a paged cache (one query per sequence).  Latent MLA rows are 1152 bytes (576 bf16) shared by
+    key and value; GB/s counts each attended row once per 16-head group, which is what the kernel has to read."""
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops.decode_attention import decode_attention
+    pk = peaks()
+    dev = "cuda"
+    rows = []
+    cases = [("latent MLA dense", 32, 16, 16384, None), ("latent MLA dense", 4, 16, 131072, None),
+             ("latent MLA top2048", 64, 16, 32768, 2048), ("latent MLA dense H64", 8, 64, 16384, None),
+             ("GQA d128 kv4", 32, 16, 16384, "gqa")]
+    page = 64
+    for label, b, h, length, mode in cases:
+        if args.only and args.only != label:
+            continue
+        torch.manual_seed(0)
+        n_pages = b * length // page
+        gqa = mode == "gqa"
+        d, kvh = (128, 4) if gqa else (576, 1)
+        kpool = torch.randn(n_pages, page, kvh, d, device=dev).bfloat16()
+        vpool = torch.randn(n_pages, page, kvh, d, device=dev).bfloat16() if gqa else None
+        table = torch.randperm(n_pages, device=dev).int().view(b, -1)
+        lengths = torch.full((b,), length, dtype=torch.int32, device=dev)
+        q = torch.randn(b, h, d, device=dev).bfloat16()
+        topk = None
+        if isinstance(mode, int):
+            topk = torch.stack([torch.randperm(length, device=dev)[:mode] for _ in range(b)]).int()
+        kw = dict(scale=d ** -0.5, topk=topk, d_v=None if gqa else 512, max_keys=mode if isinstance(mode, int) else length)
+
+        def run():
+            return decode_attention(q, kpool, vpool, table, lengths, **kw)
+        ms = time_cuda(run, iters=args.iters, warmup=args.warmup)
+        keys = (mode if isinstance(mode, int) else length) * b
+        groups = kvh if gqa else (h + 15) // 16
+        nbytes = keys * groups * d * 2 * (2 if gqa else 1)
+        row = {"op": f"decode attention {label} B{b} H{h} len{length}", "ms": ms, "gbs": nbytes / ms / 1e6,
+               "frac_of_measured_hbm": nbytes / ms / 1e6 / pk["hbm_gbs"]}
+        if not args.no_eager:
+            with B.use_kernels(False):
+                row["eager_ms"] = time_cuda(run, iters=2, warmup=1)
+            row["speedup_vs_eager"] = row["eager_ms"] / ms
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+        del kpool, vpool
+    B.check_status()
+    return rows
+
+
+def bench_decode_loop(args) -> list[dict]:
+    """Greedy generation with the 1B hybrid (random weights): per-token latency of the eagerly launched decode step
+    (``DecodeSession``) against the CUDA-graph replay of the same step (``GraphDecodeSession``)."""
+    from cppmega_mlx_b200 import inference as I
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.recipes.model_factory import get_model_profile
+    torch.manual_seed(0)
+    model = get_model_profile("hybrid_1b").build_model(dtype=torch.bfloat16, device="cuda").eval()
+    rows = []
+    for batch, prompt, new in ((1, 512, 64), (8, 2048, 64), (32, 2048, 64)):
+        ids = torch.randint(4, 60000, (batch, prompt), device="cuda")
+
+        def timed(step, first):
+            tok = first
+            for _ in range(4):
+                tok = step(tok).argmax(-1, keepdim=True)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(new):
+                tok = step(tok).argmax(-1, keepdim=True)
+            e1.record()
+            e1.synchronize()
+            return e0.elapsed_time(e1) / new
+        with torch.no_grad():
+            s = I.DecodeSession(model)
+            first = s.forward(ids, last_only=True)[:, 0].argmax(-1, keepdim=True)
+            eager_ms = timed(lambda t: s.forward(t)[:, 0], first)
+            del s
+            g = I.GraphDecodeSession(model, capacity=prompt + new + 16)
+            first = g.prefill(ids).argmax(-1, keepdim=True)
+            graph_ms = timed(g.step, first)
+            del g
+        row = {"op": f"decode loop hybrid_1b B{batch} prompt{prompt}", "eager_launch_ms_per_token": eager_ms,
+               "graph_ms_per_token": graph_ms, "speedup": eager_ms / graph_ms, "graph_tokens_per_s": batch * 1e3 / graph_ms}
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+    B.check_status()
+    return rows
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "all"])
+    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "decode", "decode_loop", "all"])
     ap.add_argument("--json", default=None)
     ap.add_argument("--only", default=None, help="run the single case with this label (small captures under a profiler)")
     ap.add_argument("--iters", type=int, default=10)
@@ -286,6 +375,10 @@ def main(argv=None) -> int:
         rows += bench_m2rnn(args)
     if args.op in ("sparse_mla", "all"):
         rows += bench_sparse_mla(args)
+    if args.op in ("decode", "all"):
+        rows += bench_decode(args)
+    if args.op in ("decode_loop", "all"):
+        rows += bench_decode_loop(args)
     if args.json:
         with open(args.json, "w") as f:
             json.dump(rows, f, indent=1)

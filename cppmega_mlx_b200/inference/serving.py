@@ -16,6 +16,8 @@ from dataclasses import dataclass, field
 
 import torch
 
+from ..ops.decode_attention import decode_attention
+
 
 class OutOfBlocks(RuntimeError):
     pass
@@ -106,43 +108,17 @@ def build_paged_block_table(manager: PagedKVBlockManager, seq_ids, *, pad: int =
 
 def paged_decode_attention(q: torch.Tensor, manager: PagedKVBlockManager, layer: int, block_table: torch.Tensor,
                            lengths: torch.Tensor, *, scale: float | None = None) -> torch.Tensor:
-    """One new query per sequence. q [B,H,D] → [B,H,Dv]; keys/values are read through ``block_table`` (GQA by head groups)."""
-    b, h, d = q.shape
-    bs = manager.block_size
-    scale = d ** -0.5 if scale is None else scale
-    nb = block_table.shape[1]
-    tbl = block_table.clamp_min(0).long()
-    k = manager.k_pool[tbl, layer]            # [B, nb, bs, kvh, D]
-    v = manager.v_pool[tbl, layer]
-    kvh = k.shape[3]
-    k = k.reshape(b, nb * bs, kvh, d).float()
-    v = v.reshape(b, nb * bs, kvh, -1).float()
-    qg = q.view(b, kvh, h // kvh, d).float()
-    sc = torch.einsum("bghd,bkgd->bghk", qg, k) * scale
-    valid = torch.arange(nb * bs, device=q.device)[None] < lengths[:, None]
-    sc = sc.masked_fill(~valid[:, None, None], float("-inf"))
-    p = torch.softmax(sc, -1)
-    return torch.einsum("bghk,bkgv->bghv", p, v).reshape(b, h, -1).to(q.dtype)
+    """One new query per sequence. q [B,H,D] → [B,H,Dv]; keys/values are read through ``block_table`` (GQA by head groups).
+    CUDA tensors run the split-KV tcgen05 decode kernel (``ops/decode_attention.py``); nothing is gathered into a contiguous copy."""
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    return decode_attention(q, manager.k_pool[:, layer], manager.v_pool[:, layer], block_table, lengths, scale=scale)
 
 
 def paged_latent_decode_attention(q_lat: torch.Tensor, manager: PagedKVBlockManager, layer: int, block_table, lengths, *,
                                   d_v: int, scale: float, topk_idx: torch.Tensor | None = None) -> torch.Tensor:
     """MLA decode in latent form: q_lat [B,H,576]; pool rows hold the 576-wide latent in ``k_pool`` (kv_heads = 1); the value is
     the first ``d_v`` columns. ``topk_idx`` [B,K] (−1 padded) restricts attention to the indexer's selection."""
-    b, h, d = q_lat.shape
-    bs = manager.block_size
-    if topk_idx is None:
-        nb = block_table.shape[1]
-        pos = torch.arange(nb * bs, device=q_lat.device)[None].expand(b, -1)
-        valid = pos < lengths[:, None]
-    else:
-        pos, valid = topk_idx.clamp_min(0).long(), (topk_idx >= 0) & (topk_idx < lengths[:, None])
-    blk = torch.gather(block_table.clamp_min(0).long(), 1, pos // bs)
-    rows = manager.k_pool[blk, layer, pos % bs, 0].float()        # [B, K, 576]
-    sc = torch.einsum("bhd,bkd->bhk", q_lat.float(), rows) * scale
-    sc = sc.masked_fill(~valid[:, None], float("-inf"))
-    p = torch.nan_to_num(torch.softmax(sc, -1))
-    return torch.einsum("bhk,bkv->bhv", p, rows[..., :d_v]).to(q_lat.dtype)
+    return decode_attention(q_lat, manager.k_pool[:, layer], None, block_table, lengths, scale=scale, topk=topk_idx, d_v=d_v)
 
 
 # ----------------------------------------------------------------------------------------------- scheduler

@@ -1,0 +1,77 @@
+"""Fixed-capacity decode cache whose write position lives on the device.
+
+``HybridKVCache`` grows its buffers and keeps positions as Python integers, so every decode step launches kernels with new
+arguments.  ``StaticDecodeCache`` holds ``[B, capacity, …]`` buffers per attention layer and a single device-side position;
+a one-token step writes row ``pos`` with ``index_copy_`` and attends over ``lengths = pos + 1`` keys, so the *same* kernel
+arguments serve every step and the whole step can be captured once in a CUDA graph and replayed
+(``inference/graph_decode.py``).  The reference has no counterpart: its caches are the growing kind
+(``cppmega_mlx/inference/engine.py:52-138``) and its step is traced by ``mx.compile``.
+"""
+from __future__ import annotations
+
+import torch
+
+
+class StaticDecodeCache:
+    static = True
+
+    def __init__(self, num_layers: int, batch: int, capacity: int, device):
+        self.num_layers, self.batch, self.capacity = num_layers, batch, capacity
+        self.pos = torch.zeros(1, dtype=torch.int64, device=device)      # next row to write == tokens stored so far
+        self.a: list[torch.Tensor | None] = [None] * num_layers           # keys or the MLA latent
+        self.b: list[torch.Tensor | None] = [None] * num_layers           # values or the indexer keys
+
+    # -- HybridKVCache-compatible surface used by the layers ------------------------------------
+    def position(self, layer_idx: int) -> torch.Tensor:
+        return self.pos
+
+    @property
+    def offset(self) -> torch.Tensor:
+        return self.pos
+
+    def lengths(self) -> torch.Tensor:
+        """[B] int32: keys visible to the token being decoded (its own row included)."""
+        return (self.pos + 1).to(torch.int32).expand(self.batch).contiguous()
+
+    def _buf(self, store: list, layer_idx: int, x: torch.Tensor) -> torch.Tensor:
+        buf = store[layer_idx]
+        if buf is None:
+            buf = torch.zeros((self.batch, self.capacity, *x.shape[2:]), dtype=x.dtype, device=x.device)
+            store[layer_idx] = buf
+        return buf
+
+    def write_a(self, layer_idx: int, x: torch.Tensor) -> torch.Tensor:
+        """Store ``x`` [B,1,…] at the current position; returns the whole ``[B, capacity, …]`` buffer."""
+        buf = self._buf(self.a, layer_idx, x)
+        buf.index_copy_(1, self.pos, x.to(buf.dtype))
+        return buf
+
+    def write_b(self, layer_idx: int, x: torch.Tensor) -> torch.Tensor:
+        buf = self._buf(self.b, layer_idx, x)
+        buf.index_copy_(1, self.pos, x.to(buf.dtype))
+        return buf
+
+    def advance(self, n: int = 1) -> None:
+        self.pos += n
+
+    # -- hand-over from a prefill done with the growing cache -----------------------------------
+    def load_from(self, kv, tokens_seen: int | None = None) -> None:
+        """Copy the contents of a ``HybridKVCache`` (after prefill) and take over its position (``tokens_seen`` when the
+        model has no attention layer to read it from)."""
+        n = kv.offset if tokens_seen is None else tokens_seen
+        if n > self.capacity:
+            raise ValueError(f"prefill of {n} tokens exceeds the static capacity {self.capacity}")
+        for i in range(self.num_layers):
+            if kv.lengths[i] != n:
+                raise ValueError("all attention layers must be at the same position")
+            src_a = kv.a[i].fetch(n)
+            self.a[i] = torch.zeros((self.batch, self.capacity, *src_a.shape[2:]), dtype=src_a.dtype, device=src_a.device)
+            self.a[i][:, :n] = src_a
+            if kv.has_b[i]:
+                src_b = kv.b[i].fetch(n)
+                self.b[i] = torch.zeros((self.batch, self.capacity, *src_b.shape[2:]), dtype=src_b.dtype, device=src_b.device)
+                self.b[i][:, :n] = src_b
+        self.pos.fill_(n)
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.a + self.b if t is not None)

@@ -440,9 +440,12 @@ class HybridTinyLM(nn.Module):
             position_offset = kv_cache.offset if kv_cache is not None else 0
         h = self.token_embedding(input_ids)
         if self.position_embedding is not None:
-            if position_offset + s > cfg.max_seq_length:
-                raise ValueError(f"sequence length {position_offset + s} exceeds max_seq_length {cfg.max_seq_length}")
-            pos = torch.arange(position_offset, position_offset + s, device=input_ids.device)
+            if isinstance(position_offset, torch.Tensor):     # device-side position (static decode cache): no host read
+                pos = position_offset.reshape(-1)[:1] + torch.arange(s, device=input_ids.device)
+            else:
+                if position_offset + s > cfg.max_seq_length:
+                    raise ValueError(f"sequence length {position_offset + s} exceeds max_seq_length {cfg.max_seq_length}")
+                pos = torch.arange(position_offset, position_offset + s, device=input_ids.device)
             h = h + self.position_embedding(pos)[None]
         if self.ngram_hash_embedding is not None:
             h = h + self.ngram_hash_embedding(input_ids).to(h.dtype)

@@ -228,10 +228,40 @@ class CausalSelfAttention(nn.Module):
         cos, sin = ops.rope_tables(s, c.q_head_dim, c.rope_theta, c.rope_scaling(), device=x.device, offset=offset)
         return ops.apply_rope(x, cos, sin)
 
+    @torch.no_grad()
+    def _static_step(self, x, cache, layer_idx: int) -> torch.Tensor:
+        """One-token step against a ``StaticDecodeCache`` (device-side position; CUDA-graph replayable)."""
+        from ..ops import decode_attention as DA
+        c = self.config
+        b = x.shape[0]
+        cos, sin = ops.rope_tables_at(cache.pos, c.q_head_dim, c.rope_theta, c.rope_scaling(), capacity=cache.capacity)
+        rope = (lambda t: ops.apply_rope(t, cos, sin)) if c.use_rope else (lambda t: t)
+        q = rope(self.q_proj(x).view(b, 1, c.num_q_heads, c.q_head_dim))[:, 0]
+        lengths = cache.lengths()
+        scale = c.q_head_dim ** -0.5
+        if c.mode == "dsa":   # shared key/value rows; the newest ``sparse_topk`` causal keys
+            rows = cache.write_a(layer_idx, rope(self.sparse_kv_proj(x).view(b, 1, c.kv_heads, c.q_head_dim)).reshape(b, 1, -1))
+            rows = rows.view(b, cache.capacity, c.kv_heads, c.q_head_dim)      # stored flat, like the growing cache
+            k = min(c.sparse_topk, cache.capacity)
+            idx = cache.pos.to(torch.int32) - torch.arange(k, device=x.device, dtype=torch.int32)
+            idx = torch.where(idx >= 0, idx, torch.full_like(idx, -1))[None].expand(b, k).contiguous()
+            out = DA.decode_attention(q, rows, None, None, lengths, scale=scale, topk=idx, d_v=c.q_head_dim, max_keys=k)
+        else:
+            if c.sliding_window is not None:
+                raise ValueError("sliding-window attention has no static decode path")
+            kk = cache.write_a(layer_idx, rope(self.k_proj(x).view(b, 1, c.kv_heads, c.q_head_dim)))
+            vv = cache.write_b(layer_idx, self.v_proj(x).view(b, 1, c.kv_heads, c.q_head_dim))
+            out = DA.decode_attention(q, kk, vv, None, lengths, scale=scale, max_keys=cache.capacity)
+        return self.out_proj(out.reshape(b, 1, c.q_proj_dim))
+
     def forward(self, hidden_states: torch.Tensor, mask: torch.Tensor | str | None = "causal", *, kv_cache=None,
                 layer_idx: int = 0, sinks: torch.Tensor | None = None) -> torch.Tensor:
         c = self.config
         b, s, _ = hidden_states.shape
+        if getattr(kv_cache, "static", False):
+            if s != 1 or isinstance(mask, torch.Tensor) or sinks is not None:
+                raise ValueError("a static decode cache serves one-token steps without an explicit mask or sinks")
+            return self._static_step(hidden_states, kv_cache, layer_idx)
         offset = kv_cache.position(layer_idx) if kv_cache is not None else 0
         q = self._rope(self.q_proj(hidden_states).view(b, s, c.num_q_heads, c.q_head_dim), offset)
         if c.mode == "dsa":
@@ -253,8 +283,14 @@ class CausalSelfAttention(nn.Module):
         if kv_cache is not None:
             k, v = kv_cache.update_and_fetch(layer_idx, k, v)
         klen = k.shape[1]
-        qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
         plain_causal = isinstance(mask, str) or mask is None
+        if kv_cache is not None and s == 1 and plain_causal and c.sliding_window is None and sinks is None:
+            from ..ops import decode_attention as DA
+            if DA.kernel_supported(q[:, 0], k, v, None):   # decode step on the GPU: split-KV tensor-core kernel over the cache
+                lengths = torch.full((b,), klen, dtype=torch.int32, device=q.device)
+                out = DA.decode_attention(q[:, 0], k, v, None, lengths, scale=c.q_head_dim ** -0.5, max_keys=klen)
+                return self.out_proj(out.reshape(b, s, c.q_proj_dim))
+        qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
         if plain_causal and c.sliding_window is None and klen == s and sinks is None:
             out = dense_attention(qh, kh, vh, is_causal=True)
         else:

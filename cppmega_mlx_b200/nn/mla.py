@@ -174,7 +174,7 @@ class MLAAttention(nn.Module):
         w = self.wkv_b.weight.view(c.num_heads, c.qk_nope_head_dim + c.v_head_dim, c.kv_lora_rank)
         return w[:, :c.qk_nope_head_dim], w[:, c.qk_nope_head_dim:]  # [H,nope,r], [H,v,r]
 
-    def _project(self, x, offset: int):
+    def _project(self, x, offset: int, freqs=None):
         c = self.config
         b, s, _ = x.shape
         qr = self.q_norm(self.wq_a(x))
@@ -182,7 +182,7 @@ class MLAAttention(nn.Module):
         kv = self.wkv_a(x)
         c_kv = self.kv_norm(kv[..., :c.kv_lora_rank])
         k_pe = kv[..., c.kv_lora_rank:]
-        cos, sin = ops.rope_tables(s, c.qk_rope_head_dim, c.rope_theta, device=x.device, offset=offset)
+        cos, sin = freqs if freqs is not None else ops.rope_tables(s, c.qk_rope_head_dim, c.rope_theta, device=x.device, offset=offset)
         q = ops.apply_rope(q, cos, sin, c.qk_nope_head_dim, c.qk_rope_head_dim)
         k_pe = ops.apply_rope(k_pe[:, :, None, :].contiguous(), cos, sin)[:, :, 0]
         return qr, q, c_kv, k_pe, (cos, sin)
@@ -199,9 +199,36 @@ class MLAAttention(nn.Module):
         _, w_uv = self._w_uk_uv()
         return torch.einsum("bshr,hvr->bshv", o_lat, w_uv.to(o_lat.dtype))
 
+    @torch.no_grad()
+    def _static_step(self, x, cache, layer_idx: int, sparse: bool | None):
+        """One-token step against a ``StaticDecodeCache``: the position, the key count and the top-k list all stay on the device,
+        so the launch arguments are the same at every step (CUDA-graph replay)."""
+        from ..ops import decode_attention as DA
+        c = self.config
+        b = x.shape[0]
+        freqs = ops.rope_tables_at(cache.pos, c.qk_rope_head_dim, c.rope_theta, capacity=cache.capacity)
+        qr, q, c_kv, k_pe, _ = self._project(x, 0, freqs)
+        rows = cache.write_a(layer_idx, torch.cat([c_kv, k_pe], dim=-1))          # [B, capacity, 576]
+        lengths = cache.lengths()
+        use_sparse = (self.indexer is not None) if sparse is None else (sparse and self.indexer is not None)
+        topk = None
+        if use_sparse and cache.capacity > c.index_topk:
+            iq, ik, iw = self.indexer.project(x, qr, *freqs)
+            keys = cache.write_b(layer_idx, ik)
+            sc = self.indexer.scores(iq, keys, iw).reshape(b, cache.capacity)
+            topk = ops.topk_select(sc, c.index_topk, None, lengths)               # −1 padded while fewer keys exist
+        out_lat = DA.decode_attention(self._latent_query(q)[:, 0], rows[:, :, None, :], None, None, lengths,
+                                      scale=c.qk_head_dim ** -0.5, d_v=c.kv_lora_rank, topk=topk,
+                                      max_keys=c.index_topk if topk is not None else cache.capacity)
+        return self.wo(self._latent_output(out_lat[:, None]).reshape(b, 1, c.num_heads * c.v_head_dim))
+
     def forward(self, x: torch.Tensor, mask=None, *, kv_cache=None, layer_idx: int = 0, sparse: bool | None = None):
         c = self.config
         b, s, _ = x.shape
+        if getattr(kv_cache, "static", False):
+            if s != 1 or isinstance(mask, torch.Tensor):
+                raise ValueError("a static decode cache serves one-token steps without an explicit mask")
+            return self._static_step(x, kv_cache, layer_idx, sparse)
         offset = kv_cache.position(layer_idx) if kv_cache is not None else 0
         qr, q, c_kv, k_pe, freqs = self._project(x, offset)
         use_sparse = (self.indexer is not None) if sparse is None else (sparse and self.indexer is not None)
@@ -240,6 +267,16 @@ class MLAAttention(nn.Module):
                 bits = A.build_mask_bits(idx, sk) if idx is not None else None
                 o, _ = A.masked_attention(q, k, v, bits, scale)
                 return self.wo(o.reshape(b, s, c.num_heads * c.v_head_dim))
+        if kv_cache is not None and s == 1 and add_mask is None:
+            from ..ops import decode_attention as DA
+            rows = latent[:, :, None, :]
+            q_lat = self._latent_query(q)[:, 0]
+            if DA.kernel_supported(q_lat, rows, None, c.kv_lora_rank):
+                # Decode step on the GPU: split-KV tensor-core kernel straight over the cached latent rows.
+                lengths = torch.full((b,), sk, dtype=torch.int32, device=x.device)
+                out_lat = DA.decode_attention(q_lat, rows, None, None, lengths, scale=scale, d_v=c.kv_lora_rank, max_keys=sk,
+                                              topk=None if idx is None else idx[:, 0].contiguous())
+                return self.wo(self._latent_output(out_lat[:, None]).reshape(b, s, c.num_heads * c.v_head_dim))
         if idx is not None:
             out_lat, _ = ops.sparse_mla_attention(self._latent_query(q), latent[:, :, None, :], idx[:, :, None, :],
                                                   sm_scale=scale, d_v=c.kv_lora_rank)

@@ -90,6 +90,15 @@ def rope_tables(seq_len: int, rot_dim: int, theta: float = 10000.0, scaling: Rop
     return cos[offset:offset + seq_len], sin[offset:offset + seq_len]
 
 
+def rope_tables_at(positions: torch.Tensor, rot_dim: int, theta: float = 10000.0, scaling: RopeScaling | None = None, *,
+                   capacity: int):
+    """cos/sin [len(positions), rot_dim/2] for positions held in a device tensor (rows of the cached table for
+    ``0..capacity-1``): no host read of the position, so a decode step using it can be captured in a CUDA graph."""
+    cos, sin = rope_tables(capacity, rot_dim, theta, scaling, device=positions.device)
+    idx = positions.reshape(-1).long()
+    return cos.index_select(0, idx), sin.index_select(0, idx)
+
+
 def apply_rope_reference(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, off: int = 0, rot: int | None = None):
     """x [B,S,H,D] (or [B,S,D]); rotates x[..., off:off+rot] split-half with tables [S, rot/2]."""
     squeeze = x.dim() == 3

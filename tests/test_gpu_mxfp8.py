@@ -80,3 +80,22 @@ def test_grouped_mxfp8_expert_ffn_matches_bf16_grouped():
     ga, gb = a.experts.w_down.grad.float(), b.experts.w_down.grad.float()
     assert float((ga - gb).abs().max()) < 0.15 * float(ga.abs().max())
     B.check_status()
+
+
+def test_sparse_mla_blockscaled_gpu_matches_cpu_semantics():
+    """GPU round trip (fused quantise + dequantise kernels) + tensor-core sparse MLA vs the CPU restatement of the same op."""
+    from cppmega_mlx_b200 import ops
+    torch.manual_seed(5)
+    b, s, h, d, dv, topk = 1, 256, 16, 576, 512, 64
+    q = torch.randn(b, s, h, d, device="cuda").bfloat16().requires_grad_()
+    kv = torch.randn(b, s, 1, d, device="cuda").bfloat16().requires_grad_()
+    ends = torch.arange(1, s + 1, device="cuda", dtype=torch.int32)
+    idx = ops.topk_select(torch.randn(s, s, device="cuda"), topk, None, ends).view(b, s, 1, topk)
+    out, _ = ops.sparse_mla_blockscaled(q, kv, idx, d_v=dv)
+    ref, _ = ops.sparse_mla_blockscaled(q.detach().float().cpu(), kv.detach().float().cpu(), idx.cpu(), d_v=dv)
+    assert (out.float().cpu() - ref).abs().max() < 3e-2
+    rt = ops.mxfp8_roundtrip_ste(kv)
+    rt_ref = ops.mxfp8_roundtrip_ste(kv.detach().float().cpu())
+    assert torch.equal(rt.float().cpu(), rt_ref)           # the kernels reproduce the reference quantiser bit for bit
+    out.float().sum().backward()
+    assert q.grad is not None and kv.grad is not None and torch.isfinite(kv.grad.float()).all()

@@ -247,3 +247,24 @@ def test_scheduler_priority_preemption_and_adapters():
     fifo.add_request(1, 2, 1, priority=0)
     fifo.add_request(2, 2, 1, priority=9)
     assert fifo.schedule().prefill == [1]
+
+
+@pytest.mark.parametrize("pattern,kw", [("AE", {}), ("A", {"dsa_a_layer_ranks": (0,)}), ("MR", {}),
+                                        ("A", {"mla_low_rank": True, "dsa_a_layer_ranks": (0,)}),
+                                        ("AM", {"mla_low_rank": True})])
+def test_static_cache_steps_equal_growing_cache_steps(pattern, kw):
+    """The fixed-capacity, device-position step (the one a CUDA graph replays) produces the same logits as DecodeSession."""
+    m = _model(pattern, **kw)
+    ids = torch.randint(4, 100, (2, 15))
+    with torch.no_grad():
+        ref = I.DecodeSession(m)
+        want = [ref.forward(ids[:, :9], last_only=True)[:, 0]] + [ref.forward(ids[:, i:i + 1])[:, 0] for i in range(9, 15)]
+        g = I.GraphDecodeSession(m, capacity=32, use_graph=False)
+        got = [g.prefill(ids[:, :9]).clone()] + [g.step(ids[:, i]).clone() for i in range(9, 15)]
+    for a, b in zip(got, want):
+        assert torch.allclose(a, b, atol=2e-5)
+    assert int(g.cache.pos) == 15 and g.tokens_seen == 15
+    with pytest.raises(ValueError):
+        I.GraphDecodeSession(m, capacity=8).prefill(ids[:, :9])
+    out = I.GraphDecodeSession(m, capacity=32, use_graph=False).generate(ids[:, :9], 4)
+    assert torch.equal(out, I.generate_tokens_with_kv_cache(m, ids[:, :9], max_new_tokens=4))

@@ -230,3 +230,34 @@ def test_dsa_indexer_loss_properties_and_chunking():
     sparse = dsa_indexer_loss(idx_scores, q, k, softmax_scale=scale, topk_indices=topk, q_chunk=16)
     assert torch.allclose(sparse, dsa_indexer_loss_reference(idx_scores, q, k, softmax_scale=scale, topk_indices=topk), atol=1e-5)
     assert float(dsa_indexer_loss(idx_scores[:, :0], q[:, :0], k, softmax_scale=scale)) == 0.0
+
+
+def test_sparse_mla_blockscaled_roundtrip_semantics():
+    """MXFP8 round trip (1x32 e8m0 scales) on q and kv, straight-through gradients, then the ordinary sparse attention."""
+    from cppmega_mlx_b200.ops import mxfp8 as MX
+    torch.manual_seed(11)
+    b, s, h, d, dv, topk = 1, 12, 2, 64, 32, 5
+    q = torch.randn(b, s, h, d, requires_grad=True)
+    kv = (torch.randn(b, s, 1, d) * torch.logspace(-2, 1, d)).requires_grad_()
+    idx = torch.stack([torch.randperm(s)[:topk] for _ in range(b * s)]).view(b, s, 1, topk).int()
+    idx[0, 0, 0, 2:] = -1
+    out, lse = ops.sparse_mla_blockscaled(q, kv, idx, d_v=dv)
+
+    def rt(x):
+        qv, e = MX.quantize_mxfp8_reference(x.detach().reshape(-1, d))
+        return MX.dequantize_mxfp8_reference(qv, e).view(x.shape)
+    ref, ref_lse = ops.sparse_mla_reference(rt(q), rt(kv), idx, d_v=dv)
+    assert torch.allclose(out, ref, atol=1e-6) and torch.allclose(lse, ref_lse, atol=1e-6)
+    assert not torch.allclose(out, ops.sparse_mla_reference(q, kv, idx, d_v=dv)[0], atol=1e-4)   # the quantisation is visible
+    # e8m0 scales are powers of two and every recovered value is e4m3-representable after scaling
+    r = rt(kv).view(-1, d // 32, 32)
+    sc = torch.exp2(torch.ceil(torch.log2(kv.detach().reshape(-1, d // 32, 32).abs().amax(-1) / 448.0)))[..., None]
+    assert torch.equal((r / sc).to(torch.float8_e4m3fn).float() * sc, r)
+    out.sum().backward()
+    q2, kv2 = rt(q).requires_grad_(), rt(kv).requires_grad_()
+    ops.sparse_mla_reference(q2, kv2, idx, d_v=dv)[0].sum().backward()
+    assert torch.allclose(q.grad, q2.grad, atol=1e-6) and torch.allclose(kv.grad, kv2.grad, atol=1e-6)   # straight-through
+    # a head dimension that is not a multiple of 32 bypasses the quantisation
+    q3, kv3 = torch.randn(1, 4, 2, 24), torch.randn(1, 4, 1, 24)
+    i3 = torch.arange(4).view(1, 1, 1, 4).expand(1, 4, 1, 4).int().contiguous()
+    assert torch.equal(ops.sparse_mla_blockscaled(q3, kv3, i3)[0], ops.sparse_mla_attention(q3, kv3, i3)[0])
