@@ -12,7 +12,7 @@
 // (cppmega_mlx/nn/sparse_mla.py:125-210 for the sparse form; cppmega_mlx/inference/serving.py:47-215 describes the paged
 // pools): masked softmax over valid keys, zeros when no key is valid.
 //
-// Roles in a 256-thread CTA: warps 0-3 softmax / TMEM read-back, warps 4-5 cp.async gather (8 lanes per 128-byte line,
+// Roles in a 256-thread CTA: warps 0-3 softmax / TMEM read-back, warps 4-5 cp.async gather (alternating tiles; 8 lanes per 128-byte line,
 // hand-swizzled into the 128B-swizzle layout the MMA descriptors expect), warp 6 issues tcgen05.mma.  Tiles of 64 keys are
 // double-buffered.  Every mbarrier wait is bounded (sm100.cuh); an abandoned wait raises the CTA's abort flag, everything
 // drains, TMEM is freed and the status word reports the site.
@@ -138,8 +138,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
 
   // ---------------------------------------------------------------- setup
   if (threadIdx.x == 0) {
-    mbar_init(&full_bar[0], 64);
-    mbar_init(&full_bar[1], 64);
+    mbar_init(&full_bar[0], 32);
+    mbar_init(&full_bar[1], 32);
     mbar_init(&empty_bar[0], 1);
     mbar_init(&empty_bar[1], 1);
     mbar_init(&sfull_bar[0], 1);
@@ -173,36 +173,47 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
 
   if (warp == 4 || warp == 5) {
     // ---------------------------------------------------------------- gather
-    const int lt = threadIdx.x - 128;                 // 0..63
-    const int sub = lt >> 3, c = lt & 7;
+    // The two gather warps alternate tiles (warp 4: even, warp 5: odd). Each waits only for its own buffer to be released and
+    // for its own copies to land, so tile t+1 is in flight while tile t is being consumed and neither warp ever waits on
+    // work that needs the other's arrival first.
+    const int lw = warp - 4;
+    const int sub = lane >> 3, c = lane & 7;
     const __nv_bfloat16* kbase = p.k + kvh * p.k_head + (p.table == nullptr ? b * p.k_batch : 0);
     const __nv_bfloat16* vbase = SHARED ? nullptr : p.v + kvh * p.v_head + (p.table == nullptr ? b * p.v_batch : 0);
-    bool ok = true;
-    for (int t = 0; t < T && ok; ++t) {
+    for (int t = lw; t < T; t += 2) {
       const int buf = t & 1;
-      if (!mbar_wait(&empty_bar[buf], ((t >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) {
-        ok = false;
-        break;
-      }
+      if (!mbar_wait(&empty_bar[buf], ((t >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
       uint8_t* kb_s = bufs + buf * Cfg::BUF_BYTES;
       uint8_t* vb_s = kb_s + DKB * DEC_BLK;
-#pragma unroll 1
-      for (int it = 0; it < 8; ++it) {
-        const int row = it * 8 + sub;
-        const int ki = (t_begin + t) * DEC_TILE + row;
-        int pos = -1;
-        if (ki < total) pos = p.topk != nullptr ? p.topk[static_cast<long long>(b) * p.topk_n + ki] : ki;
-        const bool ok_row = pos >= 0 && pos < length;
+      // Phase 1: all index / page-table reads of this lane's 16 rows are issued before anything depends on them (they
+      // are dependent global loads; serialising them row by row would cost a memory latency per row).
+      constexpr int RPL = DEC_TILE / 4;   // rows per lane group
+      int pos[RPL];
+#pragma unroll
+      for (int it = 0; it < RPL; ++it) {
+        const int ki = (t_begin + t) * DEC_TILE + it * 4 + sub;
+        pos[it] = -1;
+        if (ki < total) pos[it] = p.topk != nullptr ? __ldg(p.topk + static_cast<long long>(b) * p.topk_n + ki) : ki;
+        if (pos[it] >= length || (p.table != nullptr && pos[it] / p.page_size >= p.table_w)) pos[it] = -1;
+      }
+      int page[RPL];
+#pragma unroll
+      for (int it = 0; it < RPL; ++it)
+        page[it] = (p.table != nullptr && pos[it] >= 0) ? __ldg(p.table + static_cast<long long>(b) * p.table_w + pos[it] / p.page_size) : 0;
+      // Phase 2: the copies.
+#pragma unroll
+      for (int it = 0; it < RPL; ++it) {
+        const int row = it * 4 + sub;
+        const bool ok_row = pos[it] >= 0;
         long long koff = 0, voff = 0;
         if (ok_row) {
           if (p.table != nullptr) {
-            const int pg = p.table[static_cast<long long>(b) * p.table_w + pos / p.page_size];
-            const int in = pos % p.page_size;
-            koff = pg * p.k_page + in * p.k_row;
-            voff = pg * p.v_page + in * p.v_row;
+            const int in = pos[it] % p.page_size;
+            koff = page[it] * p.k_page + in * p.k_row;
+            voff = page[it] * p.v_page + in * p.v_row;
           } else {
-            koff = pos * p.k_row;
-            voff = pos * p.v_row;
+            koff = pos[it] * p.k_row;
+            voff = pos[it] * p.v_row;
           }
         }
         if (c == 0) valid[buf * DEC_TILE + row] = ok_row ? 1 : 0;
@@ -218,17 +229,11 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
         }
       }
       cp_async_commit();
-      if (t > 0) {
-        cp_async_wait<1>();
-        fence_proxy_async_smem();
-        mbar_arrive(&full_bar[(t - 1) & 1]);
-      }
+      cp_async_wait<0>();
+      fence_proxy_async_smem();
+      mbar_arrive(&full_bar[buf]);
     }
     cp_async_wait<0>();
-    if (ok) {
-      fence_proxy_async_smem();
-      mbar_arrive(&full_bar[(T - 1) & 1]);
-    }
   } else if (warp == 6) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {

@@ -144,8 +144,32 @@ class _LinearFn(torch.autograd.Function):
         return gx, gw
 
 
+SKINNY_MAX_ROWS = 8
+
+
+def skinny_linear(x2: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """[M ≤ 8, K] × [N, K]ᵀ without autograd: the weight-streaming kernel of ``csrc/skinny_gemm.cu`` (decode steps)."""
+    lib = B.load_library()
+    M, K = x2.shape
+    N = w.shape[0]
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=x2.device)
+    ll = ctypes.c_longlong
+    B.check(lib.cmb_skinny_gemm(B.ptr(x2), ll(x2.stride(0)), B.ptr(w), ll(w.stride(0)), B.ptr(y), ll(N),
+                                B.ptr(bias if bias is not None and bias.dtype == torch.bfloat16 else None), M, N, K, B.stream_ptr()),
+            "skinny_gemm")
+    return y if bias is None or bias.dtype == torch.bfloat16 else y + bias
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """y = x @ wᵀ (+ bias); ``w`` is [out, in] as in ``nn.Linear``."""
+    if (_kernel_ok(x, w) and x.numel() > 0 and x.shape[-1] == w.shape[1] and x.numel() // x.shape[-1] <= SKINNY_MAX_ROWS
+            and w.shape[1] % 8 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0
+            and not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad))):
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16 or w.data_ptr() % 16:
+            x2 = x2.contiguous()
+        if x2.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+            return skinny_linear(x2, w, bias).view(*x.shape[:-1], w.shape[0])
     if (_kernel_ok(x, w) and w.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and w.is_contiguous()
             and x.shape[-1] == w.shape[1] and x.numel() > 0):
         y = _LinearFn.apply(x, w)

@@ -26,7 +26,7 @@ def test_latent_paged_dense(splits, heads):
     torch.manual_seed(1)
     page, n_pages = 64, 40
     k, _ = _pools(n_pages, page, 1, 576)
-    lengths = torch.tensor([100, 700, 1, 0], dtype=torch.int32, device="cuda")
+    lengths = torch.tensor([100, 500, 1, 0], dtype=torch.int32, device="cuda")
     table = torch.randperm(n_pages, device="cuda").int()[:36].view(4, 9)
     q = torch.randn(4, heads, 576, device="cuda").bfloat16()
     out = D.decode_attention(q, k, None, table, lengths, scale=576 ** -0.5, d_v=512, splits=splits)

@@ -91,3 +91,23 @@ def test_gemm_batched_mn_major_strided_views():
     torch.cuda.synchronize()
     ref = torch.einsum("bchls,bcshp->bclhp", Mm.float(), X.float().view(nb_, nc, L, H, P)).reshape(nb_, S, H, P)
     assert (Y - ref).abs().max().item() < 1e-2 * ref.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("M,N,K,bias", [(1, 2048, 2048, False), (3, 1000, 5632, True), (8, 65536, 2048, False), (5, 24, 4104, False)])
+def test_skinny_linear_matches_fp32(M, N, K, bias):
+    """Decode-shape linears (≤ 8 rows, no autograd) take the weight-streaming kernel."""
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B
+    torch.manual_seed(M + N)
+    x = torch.randn(2, M, K, device="cuda").bfloat16()[0]          # a row-sliced view
+    w = torch.randn(N, K, device="cuda").bfloat16()
+    bvec = torch.randn(N, device="cuda").bfloat16() if bias else None
+    before = B.launch_count()
+    with torch.no_grad():
+        y = ops.linear(x, w, bvec)
+    assert B.launch_count() == before + 1
+    ref = x.float() @ w.float().t() + (bvec.float() if bias else 0)
+    assert y.shape == (M, N)
+    assert (y.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
+    xr = x.clone().requires_grad_()                                # with autograd the tensor-core GEMM path is kept
+    assert ops.linear(xr, w).requires_grad
