@@ -1,0 +1,182 @@
+// One decode step of a Mamba3 mixer (rank-1 B/C) in a single launch: causal depthwise conv + SiLU on the packed
+// projection, RMS-norm + bias of B and C, dt / decay / trapezoid terms, phase advance and rotation of B and C, completion of
+// the previous token's look-ahead term, state update, read-out, D skip and SiLU(z) gate, and the next cache
+// (phase, state, rotated B, x, conv window).  The layer math is that of the sequence path
+// (cppmega_mlx/nn/mamba3.py:238 trapezoid, :270 state rotation, :339-408 recurrence, :182-189 decode cache); doing it with
+// framework ops takes ~200 tiny launches per layer per token, which is what dominates small-batch decoding.
+// One CTA per (head, batch row); everything out of place, so CTAs of one group may read the same previous cache rows.
+#include "sm100.cuh"
+
+namespace cmb {
+
+struct M3StepParams {
+  const __nv_bfloat16* proj;  // [B, total]: z | x B C | dd_dt dd_A trap angles
+  long long ld_proj;
+  const __nv_bfloat16* conv_w;     // [C, K]
+  const __nv_bfloat16* conv_b;     // [C] or null
+  const __nv_bfloat16* conv_prev;  // [B, K-1, C]
+  __nv_bfloat16* conv_next;
+  const __nv_bfloat16 *dt_bias, *Bw, *Bb, *Cw, *Cb, *D;  // [H], [G,N] ×4, [H]
+  const __nv_bfloat16* ang_prev;   // [B,H,R]
+  __nv_bfloat16* ang_next;
+  const __nv_bfloat16* ssm_prev;   // [B,H,P,N]
+  __nv_bfloat16* ssm_next;
+  const __nv_bfloat16* k_prev;     // [B,H,N]
+  __nv_bfloat16* k_next;
+  const __nv_bfloat16* v_prev;     // [B,H,P]
+  __nv_bfloat16* v_next;
+  __nv_bfloat16* y;                // [B, H·P]
+  int H, G, P, N, R, K, d_inner, C;
+  float a_floor, eps;
+};
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
+
+// conv + SiLU of channel `ch` of row b (current input from proj, history from conv_prev); also forwards the window.
+__device__ __forceinline__ float conv_silu_step(const M3StepParams& p, int b, int ch, bool write_window) {
+  const int hist = p.K - 1;
+  const float cur = __bfloat162float(p.proj[b * p.ld_proj + p.d_inner + ch]);
+  float acc = p.conv_b != nullptr ? __bfloat162float(p.conv_b[ch]) : 0.f;
+  const __nv_bfloat16* prev = p.conv_prev + static_cast<long long>(b) * hist * p.C + ch;
+  for (int j = 0; j < hist; ++j) {
+    const __nv_bfloat16 v = prev[static_cast<long long>(j) * p.C];
+    acc = fmaf(__bfloat162float(p.conv_w[ch * p.K + j]), __bfloat162float(v), acc);
+    if (write_window && j > 0) p.conv_next[(static_cast<long long>(b) * hist + j - 1) * p.C + ch] = v;
+  }
+  acc = fmaf(__bfloat162float(p.conv_w[ch * p.K + hist]), cur, acc);
+  if (write_window && hist > 0)
+    p.conv_next[(static_cast<long long>(b) * hist + hist - 1) * p.C + ch] = p.proj[b * p.ld_proj + p.d_inner + ch];
+  return silu_f(acc);
+}
+
+__global__ void __launch_bounds__(128) mamba3_step_kernel(const M3StepParams p) {
+  extern __shared__ float sm[];
+  float* Bs = sm;             // [N] rotated, scaled B (scan input)
+  float* Cr = Bs + p.N;       // [N] rotated C
+  float* kp = Cr + p.N;       // [N] previous rotated B · late factor
+  float* xs = kp + p.N;       // [P]
+  float* red = xs + p.P;      // [8]
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int hpg = p.H / p.G, g = h / hpg;
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const __nv_bfloat16* tail = p.proj + b * p.ld_proj + p.d_inner + p.C;
+  const int d_bc = p.G * p.N;
+
+  // ---- per-head and per-group scalars (every thread computes them; a handful of flops)
+  float scale_g = 0.f, late_g = 0.f;
+  for (int i = 0; i < hpg; ++i) {
+    const int hh = g * hpg + i;
+    const float dth = softplus_f(__bfloat162float(tail[hh]) + __bfloat162float(p.dt_bias[hh]));
+    const float sg = sigmoid_f(__bfloat162float(tail[2 * p.H + hh]));
+    scale_g += dth * sg;
+    late_g += dth * (1.f - sg);
+  }
+  scale_g /= hpg;
+  late_g /= hpg;
+  const float dt_h = softplus_f(__bfloat162float(tail[h]) + __bfloat162float(p.dt_bias[h]));
+  const float dt_gh = softplus_f(__bfloat162float(tail[g]) + __bfloat162float(p.dt_bias[g]));   // head index g drives group g's phase
+  const float A_h = fminf(-softplus_f(__bfloat162float(tail[p.H + h])), -p.a_floor);
+  const float decay = __expf(A_h * dt_h);
+
+  // ---- B and C of this group: conv + SiLU, RMS norm, weight + bias
+  float ssB = 0.f, ssC = 0.f;
+  for (int n = t; n < p.N; n += 128) {
+    const bool own = (h % hpg) == 0;   // the first head of a group forwards the group's conv window
+    const float bv = conv_silu_step(p, b, p.d_inner + g * p.N + n, own);
+    const float cv = conv_silu_step(p, b, p.d_inner + d_bc + g * p.N + n, own);
+    Bs[n] = bv;
+    Cr[n] = cv;
+    ssB += bv * bv;
+    ssC += cv * cv;
+  }
+  ssB = warp_sum(ssB);
+  ssC = warp_sum(ssC);
+  if (lane == 0) {
+    red[warp] = ssB;
+    red[4 + warp] = ssC;
+  }
+  __syncthreads();
+  const float rB = rsqrtf((red[0] + red[1] + red[2] + red[3]) / p.N + p.eps);
+  const float rC = rsqrtf((red[4] + red[5] + red[6] + red[7]) / p.N + p.eps);
+  for (int n = t; n < p.N; n += 128) {
+    Bs[n] = Bs[n] * rB * __bfloat162float(p.Bw[g * p.N + n]) + __bfloat162float(p.Bb[g * p.N + n]);
+    Cr[n] = Cr[n] * rC * __bfloat162float(p.Cw[g * p.N + n]) + __bfloat162float(p.Cb[g * p.N + n]);
+  }
+  // ---- x of this head: conv + SiLU (and the head's share of the conv window); v cache
+  for (int i = t; i < p.P; i += 128) {
+    const float xv = conv_silu_step(p, b, h * p.P + i, true);
+    xs[i] = xv;
+    p.v_next[(static_cast<long long>(b) * p.H + h) * p.P + i] = __float2bfloat16(xv);
+  }
+  __syncthreads();
+  // ---- phase advance (own head, for the cache) and rotation of B, C by the phase of head index g
+  const __nv_bfloat16* ang_in = tail + 3 * p.H;
+  for (int i = t; i < p.R; i += 128) {
+    const float a = __bfloat162float(ang_in[i]) * dt_h + __bfloat162float(p.ang_prev[(static_cast<long long>(b) * p.H + h) * p.R + i]);
+    const float two_pi = 6.283185307179586f;
+    p.ang_next[(static_cast<long long>(b) * p.H + h) * p.R + i] = __float2bfloat16(a - two_pi * floorf(a / two_pi));
+  }
+  const int rr = min(p.R, p.N / 2);
+  for (int i = t; i < rr; i += 128) {
+    const float a = __bfloat162float(ang_in[i]) * dt_gh + __bfloat162float(p.ang_prev[(static_cast<long long>(b) * p.H + g) * p.R + i]);
+    float sn, cs;
+    __sincosf(a, &sn, &cs);
+    const float b0 = Bs[2 * i], b1 = Bs[2 * i + 1], c0 = Cr[2 * i], c1 = Cr[2 * i + 1];
+    Bs[2 * i] = b0 * cs - b1 * sn;
+    Bs[2 * i + 1] = b0 * sn + b1 * cs;
+    Cr[2 * i] = c0 * cs - c1 * sn;
+    Cr[2 * i + 1] = c0 * sn + c1 * cs;
+  }
+  __syncthreads();
+  for (int n = t; n < p.N; n += 128) {
+    const long long o = (static_cast<long long>(b) * p.H + h) * p.N + n;
+    p.k_next[o] = __float2bfloat16(Bs[n]);            // rotated, not yet trapezoid-scaled: what the next step completes
+    kp[n] = __bfloat162float(p.k_prev[o]) * late_g;
+    Bs[n] *= scale_g;
+  }
+  __syncthreads();
+  // ---- state update and read-out: warp w owns rows p ≡ w (mod 4); lanes sweep the state dimension
+  const float Dh = __bfloat162float(p.D[h]);
+  const long long sbase = (static_cast<long long>(b) * p.H + h) * p.P * p.N;
+  for (int pr = warp; pr < p.P; pr += 4) {
+    const float xv = xs[pr];
+    const float vp = __bfloat162float(p.v_prev[(static_cast<long long>(b) * p.H + h) * p.P + pr]);
+    float acc = 0.f;
+    for (int n = lane * 2; n < p.N; n += 64) {
+      const float2 s2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p.ssm_prev + sbase + pr * p.N + n));
+      const float n0 = decay * (s2.x + vp * kp[n]) + xv * Bs[n];
+      const float n1 = decay * (s2.y + vp * kp[n + 1]) + xv * Bs[n + 1];
+      *reinterpret_cast<__nv_bfloat162*>(p.ssm_next + sbase + pr * p.N + n) = __floats2bfloat162_rn(n0, n1);
+      acc = fmaf(n0, Cr[n], fmaf(n1, Cr[n + 1], acc));
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      const float zv = __bfloat162float(p.proj[b * p.ld_proj + h * p.P + pr]);
+      p.y[(static_cast<long long>(b) * p.H + h) * p.P + pr] = __float2bfloat16((acc + Dh * xv) * silu_f(zv));
+    }
+  }
+}
+
+}  // namespace cmb
+
+// ip = {B, H, G, P, N, R, K, d_inner, C}; pointers in `pp` in the order of M3StepParams (19 entries; conv_b may be null).
+// Requirements: N even, H % G == 0, bf16 everywhere. Returns 1 for an unsupported shape.
+extern "C" int cmb_mamba3_step(const void* const* pp, const int* ip, long long ld_proj, float a_floor, float eps, void* stream) {
+  cmb::M3StepParams p{};
+  const int B = ip[0];
+  p.H = ip[1], p.G = ip[2], p.P = ip[3], p.N = ip[4], p.R = ip[5], p.K = ip[6], p.d_inner = ip[7], p.C = ip[8];
+  if (B <= 0 || p.H <= 0 || p.G <= 0 || p.H % p.G || p.N % 2 || p.N > 1024 || p.P > 1024 || p.K < 1 || p.K > 16 || B > 65535) return 1;
+  auto bf = [&](int i) { return static_cast<const __nv_bfloat16*>(pp[i]); };
+  auto bfm = [&](int i) { return static_cast<__nv_bfloat16*>(const_cast<void*>(pp[i])); };
+  p.proj = bf(0), p.ld_proj = ld_proj;
+  p.conv_w = bf(1), p.conv_b = bf(2), p.conv_prev = bf(3), p.conv_next = bfm(4);
+  p.dt_bias = bf(5), p.Bw = bf(6), p.Bb = bf(7), p.Cw = bf(8), p.Cb = bf(9), p.D = bf(10);
+  p.ang_prev = bf(11), p.ang_next = bfm(12), p.ssm_prev = bf(13), p.ssm_next = bfm(14);
+  p.k_prev = bf(15), p.k_next = bfm(16), p.v_prev = bf(17), p.v_next = bfm(18), p.y = bfm(19);
+  p.a_floor = a_floor, p.eps = eps;
+  const size_t smem = (3 * p.N + p.P + 8) * sizeof(float);
+  cmb::mamba3_step_kernel<<<dim3(p.H, B), 128, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}

@@ -214,6 +214,18 @@ class Mamba3Block(nn.Module):
             raise ValueError(f"projected last dim must be {self.dims.total}, got {tuple(proj.shape)}")
         prefix = cache.conv if (cache is not None and cache.conv is not None) else None
         conv_ch = c.d_inner + 2 * self.dims.d_bc
+        if cache is not None and return_cache and s == 1 and h0 is None and ops.kernels_enabled() and not torch.is_grad_enabled():
+            from ..ops import mamba3_step as MS
+            params = (self.conv_weight, self.conv_bias, self.dt_bias, self.B_norm_weight, self.B_bias, self.C_norm_weight, self.C_bias,
+                      self.D)
+            if MS.supported(proj, cache, params, mimo_rank=c.effective_mimo_rank, d_state=c.d_state) and self.D.dim() == 1:
+                # decode step on the GPU: the whole mixer between in_proj and out_proj is one kernel
+                y, (ang, ssm, k, v, conv) = MS.mamba3_step(
+                    proj, cache, conv_weight=self.conv_weight, conv_bias=self.conv_bias, dt_bias=self.dt_bias,
+                    B_norm_weight=self.B_norm_weight, B_bias=self.B_bias, C_norm_weight=self.C_norm_weight, C_bias=self.C_bias,
+                    D=self.D, nheads=c.nheads, ngroups=c.ngroups, headdim=c.headdim, d_state=c.d_state,
+                    num_angles=self.dims.num_rope_angles, d_inner=c.d_inner, a_floor=c.A_floor)
+                return self.out_proj(y), Mamba3CacheState(angle_dt=ang, ssm=ssm, k=k, v=v, conv=conv)
         # [z | x B C | dd_dt dd_A trap angles]: one node splits the packed projection and runs conv + SiLU
         z, x, BC, tail = ops.packed_split_conv_silu(proj, c.d_inner, conv_ch, c.d_inner, self.conv_weight, self.conv_bias,
                                                     prefix=prefix)

@@ -86,3 +86,36 @@ def test_fused_prep_matches_framework_ops(monkeypatch):
     assert rel(gxf, gxr) < 5e-2
     for n in gpr:
         assert rel(gpf[n], gpr[n]) < 6e-2, (n, rel(gpf[n], gpr[n]))
+
+
+@pytest.mark.parametrize("groups,state", [(8, 128), (2, 64), (1, 16)])
+def test_single_step_kernel_matches_sequence_path(groups, state):
+    """The one-launch decode step reproduces the sequence path run with S == 1 (outputs and every cache tensor)."""
+    from cppmega_mlx_b200.nn.mamba3 import Mamba3Block, Mamba3Config
+    from cppmega_mlx_b200.ops import _backend as B
+    torch.manual_seed(3)
+    blk = Mamba3Block(Mamba3Config(d_model=512, headdim=64, d_state=state, ngroups=groups, chunk_size=64)).cuda().bfloat16().eval()
+    with torch.no_grad():
+        for prm in (blk.B_bias, blk.C_bias, blk.conv_bias):
+            prm.normal_(0, 0.3)
+        blk.D.normal_(1, 0.2)
+        x = torch.randn(3, 20, 512, device="cuda").bfloat16()
+        _, cache = blk(x[:, :16], return_cache=True)
+        got_c, ref_c = cache, cache
+        for i in range(16, 20):
+            before = B.launch_count()
+            got, got_c = blk(x[:, i:i + 1], cache=got_c, return_cache=True)
+            launches = B.launch_count() - before
+            with B.use_kernels(False):
+                ref, ref_c = blk(x[:, i:i + 1], cache=ref_c, return_cache=True)
+            assert launches <= 4        # in_proj, step, out_proj
+            assert (got.float() - ref.float()).abs().max() <= 3e-2 * max(1.0, float(ref.float().abs().max()))
+            for name in ("angle_dt", "ssm", "k", "v", "conv"):
+                a, r = getattr(got_c, name).float(), getattr(ref_c, name).float()
+                assert a.shape == r.shape
+                if name == "angle_dt":   # phases are compared on the circle
+                    d = (a - r).abs()
+                    d = torch.minimum(d, (2 * torch.pi - d).abs())
+                    assert d.max() < 5e-2
+                else:
+                    assert (a - r).abs().max() <= 3e-2 * max(1.0, float(r.abs().max())), name
