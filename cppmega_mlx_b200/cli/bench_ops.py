@@ -309,6 +309,28 @@ def bench_decode(args) -> list[dict]:
         rows.append(row)
         print(json.dumps(row), flush=True)
         del kpool, vpool
+    from cppmega_mlx_b200 import ops
+    for M, N, K, label in ((1, 11264, 2048, "ffn up"), (1, 2048, 5632, "ffn down"), (8, 11264, 2048, "ffn up"),
+                           (8, 2048, 5632, "ffn down"), (1, 65536, 2048, "lm_head"), (8, 65536, 2048, "lm_head")):
+        name = f"skinny linear {label} M{M} N{N} K{K}"
+        if args.only and args.only != name:
+            continue
+        x = torch.randn(M, K, device=dev).bfloat16()
+        ws = [torch.randn(N, K, device=dev).bfloat16() for _ in range(max(2, (300 << 20) // (N * K * 2)))]   # rotate past the L2
+        it = [0]
+
+        def run():
+            it[0] = (it[0] + 1) % len(ws)
+            with torch.no_grad():
+                return ops.linear(x, ws[it[0]])
+        ms = time_cuda(run, iters=max(args.iters, 20), warmup=args.warmup, flush=False)
+        row = {"op": name, "ms": ms, "gbs": N * K * 2 / ms / 1e6, "frac_of_measured_hbm": N * K * 2 / ms / 1e6 / pk["hbm_gbs"]}
+        if not args.no_eager:
+            with B.use_kernels(False), torch.no_grad():
+                row["eager_ms"] = time_cuda(run, iters=20, warmup=3, flush=False)
+            row["speedup_vs_eager"] = row["eager_ms"] / ms
+        rows.append(row)
+        print(json.dumps(row), flush=True)
     B.check_status()
     return rows
 

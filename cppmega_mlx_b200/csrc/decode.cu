@@ -182,7 +182,6 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
     const __nv_bfloat16* vbase = SHARED ? nullptr : p.v + kvh * p.v_head + (p.table == nullptr ? b * p.v_batch : 0);
     for (int t = lw; t < T; t += 2) {
       const int buf = t & 1;
-      if (!mbar_wait(&empty_bar[buf], ((t >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
       uint8_t* kb_s = bufs + buf * Cfg::BUF_BYTES;
       uint8_t* vb_s = kb_s + DKB * DEC_BLK;
       // Phase 1: all index / page-table reads of this lane's 16 rows are issued before anything depends on them (they
@@ -200,7 +199,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
 #pragma unroll
       for (int it = 0; it < RPL; ++it)
         page[it] = (p.table != nullptr && pos[it] >= 0) ? __ldg(p.table + static_cast<long long>(b) * p.table_w + pos[it] / p.page_size) : 0;
-      // Phase 2: the copies.
+      // Phase 2: the copies, once the buffer has been released (the index reads above overlap that wait).
+      if (!mbar_wait(&empty_bar[buf], ((t >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
 #pragma unroll
       for (int it = 0; it < RPL; ++it) {
         const int row = it * 4 + sub;
@@ -244,13 +244,15 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
         if (!mbar_wait(pfull_bar, t & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) return false;
         tc_fence_after();
         const uint32_t vb_s = smem_u32(bufs + (t & 1) * Cfg::BUF_BYTES + (SHARED ? 0 : DKB * DEC_BLK));
+        const uint64_t adesc0 = make_smem_desc_sw128(vb_s, DEC_BLK, 1024);
+        const uint64_t bdesc0 = make_smem_desc_sw128(p_s, 16, 1024);
 #pragma unroll
         for (int j = 0; j < MB; ++j) {
 #pragma unroll
           for (int k = 0; k < DEC_TILE / 16; ++k) {
-            const uint64_t adesc = make_smem_desc_sw128(vb_s + (2 * j) * DEC_BLK + k * 2048, DEC_BLK, 1024);
-            const uint64_t bdesc = make_smem_desc_sw128(p_s + k * 32, 16, 1024);
-            umma_f16(tmem_o + j * DEC_N, adesc, bdesc, idesc2, (t > 0 || k > 0) ? 1u : 0u);
+            // offsets are added to the descriptors' 16-byte-unit address field (all buffers sit below 256 KB: no carry)
+            umma_f16(tmem_o + j * DEC_N, adesc0 + (((2 * j) * DEC_BLK + k * 2048) >> 4), bdesc0 + ((k * 32) >> 4), idesc2,
+                     (t > 0 || k > 0) ? 1u : 0u);
           }
         }
         umma_commit(&empty_bar[t & 1]);
@@ -264,13 +266,14 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
         if (!mbar_wait(&sfree_bar[buf], ((t >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t kb_s = smem_u32(bufs + buf * Cfg::BUF_BYTES);
+        const uint64_t adesc0 = make_smem_desc_sw128(kb_s, 16, 1024);
+        const uint64_t bdesc0 = make_smem_desc_sw128(q_s, 16, 1024);
 #pragma unroll
         for (int kb = 0; kb < DKB; ++kb) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint64_t adesc = make_smem_desc_sw128(kb_s + kb * DEC_BLK + k * 32, 16, 1024);
-            const uint64_t bdesc = make_smem_desc_sw128(q_s + kb * (DEC_N * 128) + k * 32, 16, 1024);
-            umma_f16(tmem_s + buf * DEC_N, adesc, bdesc, idesc1, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_f16(tmem_s + buf * DEC_N, adesc0 + ((kb * DEC_BLK + k * 32) >> 4), bdesc0 + ((kb * (DEC_N * 128) + k * 32) >> 4),
+                     idesc1, (kb > 0 || k > 0) ? 1u : 0u);
           }
         }
         umma_commit(&sfull_bar[buf]);

@@ -9,10 +9,10 @@
 namespace cmb {
 
 constexpr int SK_THREADS = 256;
-constexpr int SK_COLS = 2;       // output columns per warp per pass
+constexpr int SK_UNROLL = 4;     // 16-byte weight loads in flight per lane and column
 constexpr int SK_SLAB = 2048;    // K columns of x staged at a time (M ≤ 8 → ≤ 32 KB)
 
-template <int M>
+template <int M, int SK_COLS>
 __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                                                  const __nv_bfloat16* __restrict__ w, long long ldw,
                                                                  __nv_bfloat16* __restrict__ y, long long ldy,
@@ -36,22 +36,29 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(const __nv_bflo
     }
     __syncthreads();
     if (n0 < N) {
-      for (int k = lane * 8; k < kw; k += 256) {
-        uint4 wv[SK_COLS];
+      for (int k = lane * 8; k < kw; k += 256 * SK_UNROLL) {
+        uint4 wv[SK_UNROLL][SK_COLS];
 #pragma unroll
-        for (int c = 0; c < SK_COLS; ++c)
-          wv[c] = n0 + c < N ? __ldcs(reinterpret_cast<const uint4*>(w + (n0 + c) * ldw + k0 + k)) : make_uint4(0, 0, 0, 0);
+        for (int u = 0; u < SK_UNROLL; ++u)
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-          const uint4 xv = *reinterpret_cast<const uint4*>(xs + m * SK_SLAB + k);
-          const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+          for (int c = 0; c < SK_COLS; ++c)
+            wv[u][c] = (n0 + c < N && k + u * 256 < kw) ? __ldcs(reinterpret_cast<const uint4*>(w + (n0 + c) * ldw + k0 + k + u * 256))
+                                                        : make_uint4(0, 0, 0, 0);
 #pragma unroll
-          for (int c = 0; c < SK_COLS; ++c) {
-            const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv[c]);
+        for (int u = 0; u < SK_UNROLL; ++u) {
+          if (k + u * 256 >= kw) break;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 a = __bfloat1622float2(xp[j]), b = __bfloat1622float2(wp[j]);
-              acc[c][m] = fmaf(a.x, b.x, fmaf(a.y, b.y, acc[c][m]));
+          for (int m = 0; m < M; ++m) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(xs + m * SK_SLAB + k + u * 256);
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+            for (int c = 0; c < SK_COLS; ++c) {
+              const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv[u][c]);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 a = __bfloat1622float2(xp[j]), b = __bfloat1622float2(wp[j]);
+                acc[c][m] = fmaf(a.x, b.x, fmaf(a.y, b.y, acc[c][m]));
+              }
             }
           }
         }
@@ -77,22 +84,27 @@ extern "C" int cmb_skinny_gemm(const void* x, long long ldx, const void* w, long
                                const void* bias, int M, int N, int K, void* stream) {
   if (M < 1 || M > 8 || K % 8 || ldx % 8 || ldw % 8 || N <= 0) return 1;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return 1;
-  const int cols_per_cta = (cmb::SK_THREADS / 32) * cmb::SK_COLS;
-  const unsigned grid = static_cast<unsigned>((N + cols_per_cta - 1) / cols_per_cta);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto X = static_cast<const __nv_bfloat16*>(x);
   auto W = static_cast<const __nv_bfloat16*>(w);
   auto Y = static_cast<__nv_bfloat16*>(y);
   auto Bv = static_cast<const __nv_bfloat16*>(bias);
+  const int warps = cmb::SK_THREADS / 32;
+  // two columns per warp halve the x reads from shared memory, but a narrow output needs the CTAs more than that
+  const bool two = (N + 2 * warps - 1) / (2 * warps) >= 2 * 148;
+  const unsigned grid = static_cast<unsigned>((N + (two ? 2 : 1) * warps - 1) / ((two ? 2 : 1) * warps));
+#define CMB_SK_CASE(MM)                                                                                               \
+  case MM:                                                                                                            \
+    if (two) cmb::skinny_gemm_kernel<MM, 2><<<grid, cmb::SK_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, N, K);        \
+    else cmb::skinny_gemm_kernel<MM, 1><<<grid, cmb::SK_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, N, K);            \
+    break;
   switch (M) {
-    case 1: cmb::skinny_gemm_kernel<1><<<grid, cmb::SK_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, N, K); break;
-    case 2: cmb::skinny_gemm_kernel<2><<<grid, cmb::SK_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, N, K); break;
-    case 3: cmb::skinny_gemm_kernel<3><<<grid, cmb::SK_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, N, K); break;
-    case 4: cmb::skinny_gemm_kernel<4><<<grid, cmb::SK_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, N, K); break;
-    case 5: cmb::skinny_gemm_kernel<5><<<grid, cmb::SK_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, N, K); break;
-    case 6: cmb::skinny_gemm_kernel<6><<<grid, cmb::SK_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, N, K); break;
-    case 7: cmb::skinny_gemm_kernel<7><<<grid, cmb::SK_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, N, K); break;
-    default: cmb::skinny_gemm_kernel<8><<<grid, cmb::SK_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, N, K); break;
+    CMB_SK_CASE(1) CMB_SK_CASE(2) CMB_SK_CASE(3) CMB_SK_CASE(4) CMB_SK_CASE(5) CMB_SK_CASE(6) CMB_SK_CASE(7)
+    default:
+      if (two) cmb::skinny_gemm_kernel<8, 2><<<grid, cmb::SK_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, N, K);
+      else cmb::skinny_gemm_kernel<8, 1><<<grid, cmb::SK_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, N, K);
+      break;
   }
+#undef CMB_SK_CASE
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
