@@ -41,6 +41,7 @@ def parse_args():
                     help="stub = no communication at all (measurement aid for exposed-communication time; not a valid training run)")
     ap.add_argument("--depth", type=int, default=0, help="override layer count (debugging only; makes the result non-headline)")
     ap.add_argument("--ep", type=int, default=1, help="expert-parallel size for MoE profiles (1 = experts replicated; N = world size)")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree for the dense FFNs (sequence parallel); ZeRO-1 runs over the remaining ranks")
     ap.add_argument("--expert-gemm", default="bf16", choices=["bf16", "mxfp8"], help="routed-expert forward GEMMs (MoE profiles)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--grad-checkpoint", default="auto", choices=["auto", "on", "off"],
@@ -155,6 +156,16 @@ def main():
         ep_group = dist.group.WORLD
     model = profile.build_model(dtype=torch.bfloat16, device=dev, ep_group=ep_group, **overrides)
     cfg = model.config
+    tp_group = dp_group = None
+    dp = world
+    if args.tp > 1:
+        if world % args.tp or args.ep > 1:
+            raise SystemExit("--tp must divide the number of GPUs and cannot be combined with --ep")
+        from cppmega_mlx_b200.parallel.state import init_parallel_state
+        from cppmega_mlx_b200.parallel.tp import tensor_parallelize_ffn
+        pstate = init_parallel_state(tp=args.tp)
+        tp_group, dp_group, dp = pstate.tp_group, pstate.dp_group, world // args.tp
+        tensor_parallelize_ffn(model, tp_group, sequence_parallel=False)   # FFN weights sharded; activations replicated in the TP group
     nparams = model.num_parameters()
 
     if args.optimizer == "muon_adamw":
@@ -171,15 +182,15 @@ def main():
             from cppmega_mlx_b200.parallel.fused_ep import enable_fused_ep
             enable_fused_ep(model, ep_group, dev, max_tokens=args.micro_batch * args.seq_len)
     else:
-        opt = DistributedZeRO1Optimizer(model, factory, comm=comm)
+        opt = DistributedZeRO1Optimizer(model, factory, comm=comm if tp_group is None else "nccl", group=dp_group)
     opt.zero_grad()
     stepper = PretrainingStep(model, opt, loss_fn=make_loss_fn(backend="cce"), sync_metrics=False, device=dev)
 
     mb, S, V = args.micro_batch, args.seq_len, cfg.vocab_size
-    gen = torch.Generator().manual_seed(100 + rank)
+    gen = torch.Generator().manual_seed(100 + rank // args.tp)   # ranks of one TP group see the same batch
     n_batches = args.warmup + args.steps
     host_batches = [torch.randint(0, V, (mb, S + 1), generator=gen, dtype=torch.int64).pin_memory() for _ in range(n_batches)]
-    tokens_per_step = mb * S * world
+    tokens_per_step = mb * S * dp
 
     def barrier():
         if world > 1:
@@ -243,7 +254,7 @@ def main():
             "impl": args.impl,
             "config": {"model": f"{args.profile}: {cfg.pattern}x{cfg.depth // len(cfg.pattern)} d{cfg.hidden_size} "
                                 f"ffn{cfg.ffn_hidden_size} vocab{cfg.vocab_size} mtp{cfg.mtp_depth if cfg.mtp_enabled else 0}",
-                       "params": nparams, "global_batch": mb * world, "seq_len": S, "parallelism": f"dp{world} zero1 ({comm})" + (f" ep{args.ep}" if args.ep > 1 else ""),
+                       "params": nparams, "global_batch": mb * dp, "seq_len": S, "parallelism": f"dp{dp} zero1 ({comm if args.tp == 1 else 'nccl'})" + (f" ep{args.ep}" if args.ep > 1 else "") + (f" tp{args.tp} (dense FFNs)" if args.tp > 1 else ""),
                        "optimizer": args.optimizer, "expert_gemm": args.expert_gemm, "micro_batch_per_gpu": mb, "grad_checkpoint": ckpt,
                        "l2": "working set per step (weights + activations, tens of GB) far exceeds the 126 MB L2; no flush needed"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,

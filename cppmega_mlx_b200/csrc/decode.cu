@@ -44,7 +44,14 @@ struct DecodeParams {
   float* ws_m;                   // [B, H, splits] reference max (log2 domain)
   float* ws_l;                   // [B, H, splits] partial denominators
   int* status;
+  long long* trace;              // optional: per-tile clock samples of CTA (0,0,0), TRACE_SLOTS per tile (nullptr = off)
 };
+
+constexpr int TRACE_SLOTS = 16;
+// Record the SM clock at pipeline point `slot` of tile `t` (only CTA 0; one elected thread per role calls it).
+__device__ __forceinline__ void trace_mark(const DecodeParams& p, int t, int slot) {
+  if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && t < 64) p.trace[t * TRACE_SLOTS + slot] = clock64();
+}
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -199,8 +206,10 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
 #pragma unroll
       for (int it = 0; it < RPL; ++it)
         page[it] = (p.table != nullptr && pos[it] >= 0) ? __ldg(p.table + static_cast<long long>(b) * p.table_w + pos[it] / p.page_size) : 0;
+      if (lane == 0) trace_mark(p, t, 0);
       // Phase 2: the copies, once the buffer has been released (the index reads above overlap that wait).
       if (!mbar_wait(&empty_bar[buf], ((t >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
+      if (lane == 0) trace_mark(p, t, 1);
 #pragma unroll
       for (int it = 0; it < RPL; ++it) {
         const int row = it * 4 + sub;
@@ -229,9 +238,11 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
         }
       }
       cp_async_commit();
+      if (lane == 0) trace_mark(p, t, 2);
       cp_async_wait<0>();
       fence_proxy_async_smem();
       mbar_arrive(&full_bar[buf]);
+      if (lane == 0) trace_mark(p, t, 3);
     }
     cp_async_wait<0>();
   } else if (warp == 6) {
@@ -243,6 +254,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
       auto gemm2 = [&](int t) -> bool {
         if (!mbar_wait(pfull_bar, t & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) return false;
         tc_fence_after();
+        trace_mark(p, t, 7);
         const uint32_t vb_s = smem_u32(bufs + (t & 1) * Cfg::BUF_BYTES + (SHARED ? 0 : DKB * DEC_BLK));
         const uint64_t adesc0 = make_smem_desc_sw128(vb_s, DEC_BLK, 1024);
         const uint64_t bdesc0 = make_smem_desc_sw128(p_s, 16, 1024);
@@ -257,14 +269,17 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
         }
         umma_commit(&empty_bar[t & 1]);
         umma_commit(odone_bar);
+        trace_mark(p, t, 8);
         return true;
       };
       bool ok = true;
       for (int t = 0; t < T && ok; ++t) {
         const int buf = t & 1;
         if (!mbar_wait(&full_bar[buf], (t >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_FULL)) break;
+        trace_mark(p, t, 4);
         if (!mbar_wait(&sfree_bar[buf], ((t >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
+        trace_mark(p, t, 5);
         const uint32_t kb_s = smem_u32(bufs + buf * Cfg::BUF_BYTES);
         const uint64_t adesc0 = make_smem_desc_sw128(kb_s, 16, 1024);
         const uint64_t bdesc0 = make_smem_desc_sw128(q_s, 16, 1024);
@@ -277,6 +292,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
           }
         }
         umma_commit(&sfull_bar[buf]);
+        trace_mark(p, t, 6);
         if (t > 0) ok = gemm2(t - 1);
       }
       if (ok) gemm2(T - 1);
@@ -299,6 +315,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
       // Exit decisions are taken at the two barriers below so that all 128 threads leave the loop together.
       bool got = mbar_wait(&sfull_bar[buf], (t >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       tc_fence_after();
+      if (tid == 0) trace_mark(p, t, 9);
       uint32_t sr[16];
       tmem_ld_x16(tmem_s + buf * DEC_N + lane_addr, sr);
       tmem_wait_ld();
@@ -316,6 +333,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
         ok = false;
         break;
       }
+      if (tid == 0) trace_mark(p, t, 10);
       float alpha[DEC_N];
       bool rescale = false;
 #pragma unroll
@@ -334,6 +352,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
         ok = false;
         break;
       }
+      if (tid == 0) trace_mark(p, t, 11);
       if (t > 0) {
         tc_fence_after();
         if (rescale) {  // uniform over the 128 threads: every thread derived it from the same shared values
@@ -367,6 +386,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(pfull_bar);
+      if (tid == 0) trace_mark(p, t, 12);
     }
     // ------------------------------------------------------------ partial results
     if (ok) ok = mbar_wait(odone_bar, (T - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
@@ -433,6 +453,8 @@ __global__ void decode_combine_kernel(const float* __restrict__ ws_o, const floa
 
 namespace {
 
+long long* g_decode_trace = nullptr;
+
 template <int DKB, int DVB, bool SHARED>
 int launch_decode(const cmb::DecodeParams& p, cudaStream_t stream) {
   using Cfg = cmb::DecCfg<DKB, DVB, SHARED>;
@@ -473,6 +495,7 @@ extern "C" int cmb_paged_decode(const void* q, const void* k, const void* v, con
   p.v_page = lp[6], p.v_row = lp[7], p.v_batch = lp[8], p.v_head = lp[9];
   p.scale_log2 = scale * 1.4426950408889634f;
   p.ws_o = ws_o, p.ws_m = ws_m, p.ws_l = ws_l, p.status = status;
+  p.trace = g_decode_trace;
   if (p.B <= 0 || p.H <= 0 || p.kv_heads <= 0 || p.H % p.kv_heads || p.splits <= 0 || p.splits > 65535) return 1;
   if ((p.q_sb | p.q_sh | p.k_page | p.k_row | p.k_batch | p.k_head | p.v_page | p.v_row | p.v_batch | p.v_head) & 7) return 1;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) return 1;
@@ -488,3 +511,9 @@ extern "C" int cmb_paged_decode(const void* q, const void* k, const void* v, con
                                                                               lse, p.splits, Dv);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
+
+// Diagnostic: subsequent launches of the decode kernel record SM-clock samples of CTA 0 into `buf`
+// (int64[64 tiles][16 slots]: 0 indices ready, 1 buffer released, 2 copies issued, 3 copies landed, 4 MMA saw the tile,
+// 5 score buffer free, 6 score MMAs issued, 7 P ready, 8 output MMAs issued, 9 scores ready, 10 max exchanged,
+// 11 previous output done, 12 P written). Pass null to switch it off.
+extern "C" void cmb_paged_decode_set_trace(long long* buf) { g_decode_trace = buf; }

@@ -555,7 +555,8 @@ static int make_tmap_5d(CUtensorMap* out, const void* base, int elem_bytes, uint
   strides[0] = ld * static_cast<uint64_t>(elem_bytes);
   for (int i = 0; i < 3; ++i) {
     uint64_t s = static_cast<uint64_t>(sb[i]) * elem_bytes;
-    if (nb[i] <= 1 || s == 0) s = strides[0];  // unused batch dim: any legal stride
+    if (nb[i] > 1 && s == 0) return 108;       // a zero stride cannot broadcast an operand: use a_div2 / b_div2
+    if (nb[i] <= 1) s = strides[0];            // unused batch dim: any legal stride
     if (s & 15) return 105;
     strides[i + 1] = s;
   }

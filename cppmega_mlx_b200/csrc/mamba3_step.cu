@@ -35,19 +35,27 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf
 __device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
 
 // conv + SiLU of channel `ch` of row b (current input from proj, history from conv_prev); also forwards the window.
+// All taps are loaded before any is used (K ≤ 16), so one call costs one memory latency, not one per tap.
 __device__ __forceinline__ float conv_silu_step(const M3StepParams& p, int b, int ch, bool write_window) {
   const int hist = p.K - 1;
-  const float cur = __bfloat162float(p.proj[b * p.ld_proj + p.d_inner + ch]);
-  float acc = p.conv_b != nullptr ? __bfloat162float(p.conv_b[ch]) : 0.f;
+  const __nv_bfloat16 cur = p.proj[b * p.ld_proj + p.d_inner + ch];
   const __nv_bfloat16* prev = p.conv_prev + static_cast<long long>(b) * hist * p.C + ch;
-  for (int j = 0; j < hist; ++j) {
-    const __nv_bfloat16 v = prev[static_cast<long long>(j) * p.C];
-    acc = fmaf(__bfloat162float(p.conv_w[ch * p.K + j]), __bfloat162float(v), acc);
-    if (write_window && j > 0) p.conv_next[(static_cast<long long>(b) * hist + j - 1) * p.C + ch] = v;
+  __nv_bfloat16 v[16], w[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    if (j < hist) v[j] = prev[static_cast<long long>(j) * p.C];
+    if (j < p.K) w[j] = p.conv_w[ch * p.K + j];
   }
-  acc = fmaf(__bfloat162float(p.conv_w[ch * p.K + hist]), cur, acc);
-  if (write_window && hist > 0)
-    p.conv_next[(static_cast<long long>(b) * hist + hist - 1) * p.C + ch] = p.proj[b * p.ld_proj + p.d_inner + ch];
+  float acc = p.conv_b != nullptr ? __bfloat162float(p.conv_b[ch]) : 0.f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    if (j < hist) {
+      acc = fmaf(__bfloat162float(w[j]), __bfloat162float(v[j]), acc);
+      if (write_window && j > 0) p.conv_next[(static_cast<long long>(b) * hist + j - 1) * p.C + ch] = v[j];
+    }
+  }
+  acc = fmaf(__bfloat162float(p.conv_w[ch * p.K + hist]), __bfloat162float(cur), acc);
+  if (write_window && hist > 0) p.conv_next[(static_cast<long long>(b) * hist + hist - 1) * p.C + ch] = cur;
   return silu_f(acc);
 }
 
@@ -58,6 +66,7 @@ __global__ void __launch_bounds__(128) mamba3_step_kernel(const M3StepParams p) 
   float* kp = Cr + p.N;       // [N] previous rotated B · late factor
   float* xs = kp + p.N;       // [P]
   float* red = xs + p.P;      // [8]
+  float* ys = red + 8;        // [P][32] per-lane partial read-outs (row pr is touched by warp pr % 4 only)
   const int h = blockIdx.x, b = blockIdx.y;
   const int hpg = p.H / p.G, g = h / hpg;
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -138,23 +147,41 @@ __global__ void __launch_bounds__(128) mamba3_step_kernel(const M3StepParams p) 
   }
   __syncthreads();
   // ---- state update and read-out: warp w owns rows p ≡ w (mod 4); lanes sweep the state dimension
+  for (int pr = warp; pr < p.P; pr += 4) ys[pr * 32 + lane] = 0.f;
   const float Dh = __bfloat162float(p.D[h]);
   const long long sbase = (static_cast<long long>(b) * p.H + h) * p.P * p.N;
-  for (int pr = warp; pr < p.P; pr += 4) {
-    const float xv = xs[pr];
-    const float vp = __bfloat162float(p.v_prev[(static_cast<long long>(b) * p.H + h) * p.P + pr]);
-    float acc = 0.f;
+  constexpr int RU = 4;   // rows in flight per warp
+  for (int pr0 = warp; pr0 < p.P; pr0 += 4 * RU) {
     for (int n = lane * 2; n < p.N; n += 64) {
-      const float2 s2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p.ssm_prev + sbase + pr * p.N + n));
-      const float n0 = decay * (s2.x + vp * kp[n]) + xv * Bs[n];
-      const float n1 = decay * (s2.y + vp * kp[n + 1]) + xv * Bs[n + 1];
-      *reinterpret_cast<__nv_bfloat162*>(p.ssm_next + sbase + pr * p.N + n) = __floats2bfloat162_rn(n0, n1);
-      acc = fmaf(n0, Cr[n], fmaf(n1, Cr[n + 1], acc));
+      float2 s2[RU];
+      float vp[RU], xv[RU];
+#pragma unroll
+      for (int u = 0; u < RU; ++u) {
+        const int pr = pr0 + 4 * u;
+        if (pr < p.P) {
+          s2[u] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p.ssm_prev + sbase + pr * p.N + n));
+          vp[u] = __bfloat162float(p.v_prev[(static_cast<long long>(b) * p.H + h) * p.P + pr]);
+          xv[u] = xs[pr];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < RU; ++u) {
+        const int pr = pr0 + 4 * u;
+        if (pr < p.P) {
+          const float n0 = decay * (s2[u].x + vp[u] * kp[n]) + xv[u] * Bs[n];
+          const float n1 = decay * (s2[u].y + vp[u] * kp[n + 1]) + xv[u] * Bs[n + 1];
+          *reinterpret_cast<__nv_bfloat162*>(p.ssm_next + sbase + pr * p.N + n) = __floats2bfloat162_rn(n0, n1);
+          ys[pr * 32 + lane] += n0 * Cr[n] + n1 * Cr[n + 1];
+        }
+      }
     }
-    acc = warp_sum(acc);
+  }
+  __syncwarp();
+  for (int pr = warp; pr < p.P; pr += 4) {
+    const float acc = warp_sum(ys[pr * 32 + lane]);
     if (lane == 0) {
       const float zv = __bfloat162float(p.proj[b * p.ld_proj + h * p.P + pr]);
-      p.y[(static_cast<long long>(b) * p.H + h) * p.P + pr] = __float2bfloat16((acc + Dh * xv) * silu_f(zv));
+      p.y[(static_cast<long long>(b) * p.H + h) * p.P + pr] = __float2bfloat16((acc + Dh * xs[pr]) * silu_f(zv));
     }
   }
 }
@@ -176,7 +203,7 @@ extern "C" int cmb_mamba3_step(const void* const* pp, const int* ip, long long l
   p.ang_prev = bf(11), p.ang_next = bfm(12), p.ssm_prev = bf(13), p.ssm_next = bfm(14);
   p.k_prev = bf(15), p.k_next = bfm(16), p.v_prev = bf(17), p.v_next = bfm(18), p.y = bfm(19);
   p.a_floor = a_floor, p.eps = eps;
-  const size_t smem = (3 * p.N + p.P + 8) * sizeof(float);
+  const size_t smem = (3 * p.N + p.P + 8 + 32 * p.P) * sizeof(float);
   cmb::mamba3_step_kernel<<<dim3(p.H, B), 128, smem, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }

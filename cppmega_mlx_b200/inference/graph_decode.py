@@ -4,7 +4,9 @@ A decode step of a hybrid model is hundreds of small launches (projections, norm
 recurrent layer); at batch sizes that fit a latency budget the GPU finishes each of them faster than the host can issue
 the next.  ``GraphDecodeSession`` removes the host from the loop: after a normal prefill it moves the KV cache into a
 ``StaticDecodeCache`` (device-side position) and the recurrent states into fixed tensors, captures ONE step — embedding →
-all layers → logits → state write-back → position increment — with ``torch.cuda.graph`` and replays it per token.
+all layers → logits → next recurrent state → position increment — with ``torch.cuda.graph`` and replays it per token.
+The recurrent state ping-pongs between two fixed sets of tensors (two captured graphs, replayed alternately), so a layer whose
+step kernel writes its next state out of place needs no copy back.
 The reference gets the same effect from ``mx.compile`` tracing its step function (``cppmega_mlx/training/compiled.py:345``
 for training; its generation loop ``cppmega_mlx/inference/generation.py`` re-launches eagerly); here it is explicit stream
 capture over the hand-written kernels, which take their stream from PyTorch and make no host reads.
@@ -35,11 +37,21 @@ class GraphDecodeSession:
         self.model = model
         self.capacity = capacity
         self.cache: StaticDecodeCache | None = None
-        self.state: HybridDecodeState | None = None
-        self.graph = None
+        self.states: list[HybridDecodeState] = []     # two fixed sets of recurrent state; step k reads [k % 2], writes [(k+1) % 2]
+        self.graphs: list | None = None
         self.use_graph = use_graph
         self._tok = self._logits = None
+        self._parity = 0
         self.tokens_seen = 0
+
+    @property
+    def state(self) -> HybridDecodeState:
+        """The recurrent state after the last step."""
+        return self.states[self._parity]
+
+    @property
+    def graph(self):
+        return None if self.graphs is None else self.graphs[0]
 
     # ------------------------------------------------------------------------------------------ prefill
     @torch.no_grad()
@@ -54,52 +66,68 @@ class GraphDecodeSession:
         dev = input_ids.device
         self.cache = StaticDecodeCache(sess.kv.num_layers, b, self.capacity, dev)
         self.cache.load_from(sess.kv, sess.tokens_seen)
-        self.state = sess.state.clone()           # these tensors are the fixed storage every replay updates in place
+        first = sess.state.clone()                # fixed storage from here on: replays only ever write into these tensors
+        for d, key, name, val in list(_state_tensors(first)):
+            if not val.is_contiguous():
+                setattr(d[key], name, val.contiguous())
+        self.states = [first, first.clone()]
+        self._parity = 0
         self._tok = torch.zeros(b, 1, dtype=torch.long, device=dev)
         self._logits = torch.zeros_like(logits)
         self.tokens_seen = n
-        self.graph = None
+        self.graphs = None
         graph = self.use_graph if self.use_graph is not None else dev.type == "cuda"
         if graph:
             self._capture()
         return logits
 
     # ------------------------------------------------------------------------------------------ one step
-    def _step_body(self) -> None:
-        fixed = list(_state_tensors(self.state))
+    def _step_body(self, parity: int) -> None:
+        """Read the recurrent state set ``parity``, leave the next state in set ``1 - parity``.  Layers that can write their
+        next state straight into given tensors do so (no copy); anything else is copied across afterwards."""
+        src, dst = self.states[parity], self.states[1 - parity]
         work = HybridDecodeState()
-        work.mamba, work.m2rnn = dict(self.state.mamba), dict(self.state.m2rnn)
+        work.mamba, work.m2rnn, work.mamba_out = dict(src.mamba), dict(src.m2rnn), dst.mamba
         h = self.model.decoder_hidden_states(self._tok, kv_cache=self.cache, state=work, position_offset=self.cache.pos)
         self._logits.copy_(self.model.lm_head(h)[:, 0])
-        for d, key, name, old in fixed:           # write the new recurrent state back into the fixed tensors
-            new = getattr((work.mamba if d is self.state.mamba else work.m2rnn)[key], name)
-            if new is not old:
-                old.copy_(new)
+        for dd, wd in ((dst.mamba, work.mamba), (dst.m2rnn, work.m2rnn)):
+            for key, fixed in dd.items():
+                new = wd[key]
+                if new is fixed:
+                    continue
+                for name, old in vars(fixed).items():
+                    val = getattr(new, name)
+                    if isinstance(old, torch.Tensor) and val is not old and val.data_ptr() != old.data_ptr():
+                        old.copy_(val)
         self.cache.advance()
 
+    def _snapshot(self):
+        tens = [t for st in self.states for *_, t in _state_tensors(st)] + [t for t in self.cache.a + self.cache.b if t is not None]
+        return tens, [t.clone() for t in tens], self.cache.pos.clone()
+
     def _capture(self) -> None:
-        # Warm up on a side stream (lazy allocations, cuBLAS handles, function attributes), restoring the state afterwards.
-        keep_pos = self.cache.pos.clone()
-        keep = [t.clone() for *_, t in _state_tensors(self.state)]
-        keep_kv = [None if t is None else t.clone() for t in self.cache.a + self.cache.b]
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side), torch.no_grad():
-            for _ in range(2):
-                self._step_body()
-        torch.cuda.current_stream().wait_stream(side)
+        # Warm up on a side stream (lazy allocations, cuBLAS handles, function attributes), restoring everything afterwards.
+        tens, keep, keep_pos = self._snapshot()
 
         def restore():
             self.cache.pos.copy_(keep_pos)
-            for (*_, t), k in zip(_state_tensors(self.state), keep):
+            for t, k in zip(tens, keep):
                 t.copy_(k)
-            for t, k in zip(self.cache.a + self.cache.b, keep_kv):
-                if t is not None:
-                    t.copy_(k)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.no_grad():
+            for parity in (0, 1):
+                self._step_body(parity)
+        torch.cuda.current_stream().wait_stream(side)
         restore()
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.no_grad(), torch.cuda.graph(self.graph):
-            self._step_body()
+        self.graphs = []
+        pool = None
+        for parity in (0, 1):
+            g = torch.cuda.CUDAGraph()
+            with torch.no_grad(), torch.cuda.graph(g, pool=pool):
+                self._step_body(parity)
+            pool = g.pool()
+            self.graphs.append(g)
         restore()                                  # capture does not execute, but keep the invariant explicit
 
     @torch.no_grad()
@@ -110,10 +138,11 @@ class GraphDecodeSession:
         if self.tokens_seen >= self.capacity:
             raise RuntimeError(f"static cache capacity {self.capacity} exhausted")
         self._tok.copy_(token_ids.reshape(-1, 1))
-        if self.graph is not None:
-            self.graph.replay()
+        if self.graphs is not None:
+            self.graphs[self._parity].replay()
         else:
-            self._step_body()
+            self._step_body(self._parity)
+        self._parity ^= 1
         self.tokens_seen += 1
         return self._logits
 

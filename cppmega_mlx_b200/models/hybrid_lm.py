@@ -281,6 +281,7 @@ class HybridDecodeState:
     def __init__(self):
         self.mamba: dict[int, Any] = {}
         self.m2rnn: dict[int, Any] = {}
+        self.mamba_out: dict[int, Any] | None = None   # optional destinations for the next Mamba3 caches (ping-pong decode)
 
     def clone(self) -> "HybridDecodeState":
         import copy
@@ -344,7 +345,8 @@ class HybridTinyBlock(nn.Module):
             return self.block(x, mask, kv_cache=kv_cache, layer_idx=attention_layer_idx or 0)
         if b == "mamba3":
             if state is not None:
-                out, nxt = self.block(x, cache=state.mamba.get(layer_idx), return_cache=True)
+                out, nxt = self.block(x, cache=state.mamba.get(layer_idx), return_cache=True,
+                                      cache_out=(state.mamba_out or {}).get(layer_idx))
                 state.mamba[layer_idx] = nxt
                 return out
             return self.block(x)[0]

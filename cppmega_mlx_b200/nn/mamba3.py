@@ -202,7 +202,8 @@ class Mamba3Block(nn.Module):
         return Bm, Cm
 
     def forward(self, hidden_states: torch.Tensor, *, h0: torch.Tensor | None = None,
-                cache: Mamba3CacheState | None = None, return_cache: bool = False):
+                cache: Mamba3CacheState | None = None, return_cache: bool = False, cache_out: Mamba3CacheState | None = None):
+        """``cache_out``: optional destination for the next cache of a one-token GPU step (tensors distinct from ``cache``)."""
         if hidden_states.dim() != 3:
             raise ValueError(f"hidden_states must be shaped (B,S,D), got {tuple(hidden_states.shape)}")
         if h0 is not None and cache is not None:
@@ -224,7 +225,7 @@ class Mamba3Block(nn.Module):
                     proj, cache, conv_weight=self.conv_weight, conv_bias=self.conv_bias, dt_bias=self.dt_bias,
                     B_norm_weight=self.B_norm_weight, B_bias=self.B_bias, C_norm_weight=self.C_norm_weight, C_bias=self.C_bias,
                     D=self.D, nheads=c.nheads, ngroups=c.ngroups, headdim=c.headdim, d_state=c.d_state,
-                    num_angles=self.dims.num_rope_angles, d_inner=c.d_inner, a_floor=c.A_floor)
+                    num_angles=self.dims.num_rope_angles, d_inner=c.d_inner, a_floor=c.A_floor, out=cache_out)
                 return self.out_proj(y), Mamba3CacheState(angle_dt=ang, ssm=ssm, k=k, v=v, conv=conv)
         # [z | x B C | dd_dt dd_A trap angles]: one node splits the packed projection and runs conv + SiLU
         z, x, BC, tail = ops.packed_split_conv_silu(proj, c.d_inner, conv_ch, c.d_inner, self.conv_weight, self.conv_bias,

@@ -144,7 +144,7 @@ class _LinearFn(torch.autograd.Function):
         return gx, gw
 
 
-SKINNY_MAX_ROWS = 8
+SKINNY_MAX_ROWS = 4   # above this the FMA issue rate, not the weight stream, bounds the CUDA-core kernel
 
 
 def skinny_linear(x2: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
@@ -160,8 +160,44 @@ def skinny_linear(x2: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None =
     return y if bias is None or bias.dtype == torch.bfloat16 else y + bias
 
 
+SMALL_M_MAX_ROWS = 64
+_split_ranges: dict[tuple, torch.Tensor] = {}
+
+
+def small_m_linear(x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """[8 < M ≤ 64, K] × [N, K]ᵀ without autograd, memory-bound on the weights.  The 128-row tensor-core tile would give
+    N/256 CTAs for the whole matrix; instead the operands are swapped (the weight rows are the MMA M dimension, the few
+    activations its N) and the contraction is split over enough CTAs to fill the GPU: ``yᵀ[N, M] = Σ_s W[:, K_s] · x[:, K_s]ᵀ``
+    as one batched launch with a per-split contraction range, fp32 partials, then one small reduction."""
+    M, K = x2.shape
+    N = w.shape[0]
+    mp = (M + 7) // 8 * 8
+    if mp != M:
+        x2 = torch.nn.functional.pad(x2, (0, 0, 0, mp - M))
+    m_tiles = (N + 127) // 128
+    splits = max(1, min(K // 256, (2 * 148 + m_tiles - 1) // m_tiles, 16))
+    chunk = ((K + splits - 1) // splits + 63) // 64 * 64
+    key = (K, splits, x2.device.index)
+    kr = _split_ranges.get(key)
+    if kr is None:
+        kr = torch.tensor([[min(K, i * chunk), min(K, (i + 1) * chunk)] for i in range(splits)], dtype=torch.int32, device=x2.device)
+        _split_ranges[key] = kr
+    part = torch.empty(splits, N, mp, dtype=torch.float32, device=x2.device)
+    # every split reads the same W and x: ``div2 = splits`` makes all dim-2 problems share operand slice 0 (a batch stride of
+    # zero is not a way to say that: tensor maps have no zero strides)
+    gemm_batched(w, x2, part, M=N, N=mp, K=K, a_mn=False, b_mn=False, lda=w.stride(0), ldb=x2.stride(0), ldc=mp, nb=(splits, 1, 1),
+                 sA=(0, 0, 0), sB=(0, 0, 0), sC=(N * mp, 0, 0), a_div2=splits, b_div2=splits, k_ranges=kr, out_f32=True)
+    y = part.sum(0) if splits > 1 else part[0]
+    return y.t()[:M].to(torch.bfloat16)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """y = x @ wᵀ (+ bias); ``w`` is [out, in] as in ``nn.Linear``."""
+    rows = x.numel() // x.shape[-1] if x.numel() else 0
+    if (SKINNY_MAX_ROWS < rows <= SMALL_M_MAX_ROWS and _kernel_ok(x, w) and x.shape[-1] == w.shape[1] and w.shape[1] % 64 == 0
+            and w.is_contiguous() and w.shape[0] >= 1024 and not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad))):
+        y = small_m_linear(x.reshape(rows, x.shape[-1]).contiguous(), w).reshape(*x.shape[:-1], w.shape[0])
+        return y if bias is None else y + bias
     if (_kernel_ok(x, w) and x.numel() > 0 and x.shape[-1] == w.shape[1] and x.numel() // x.shape[-1] <= SKINNY_MAX_ROWS
             and w.shape[1] % 8 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0
             and not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad))):

@@ -24,15 +24,21 @@ def supported(proj: torch.Tensor, cache, params, *, mimo_rank: int, d_state: int
 
 
 def mamba3_step(proj, cache, *, conv_weight, conv_bias, dt_bias, B_norm_weight, B_bias, C_norm_weight, C_bias, D, nheads: int,
-                ngroups: int, headdim: int, d_state: int, num_angles: int, d_inner: int, a_floor: float, eps: float = 1e-5):
+                ngroups: int, headdim: int, d_state: int, num_angles: int, d_inner: int, a_floor: float, eps: float = 1e-5, out=None):
     """proj [B,1,total] → (y [B,1,d_inner] gated mixer output before ``out_proj``, next-cache tensors
-    (angle_dt, ssm, k, v, conv)). Nothing is updated in place."""
+    (angle_dt, ssm, k, v, conv)). Nothing is updated in place; ``out`` (a cache object with tensors of the same shapes, distinct
+    from ``cache``) receives the next cache when given, which lets a caller ping-pong two fixed sets of state tensors."""
     lib = B.load_library()
     b = proj.shape[0]
     C, K = conv_weight.shape[0], conv_weight.shape[1]
     cw = conv_weight.reshape(C, K).contiguous()
     prev = [cache.angle_dt.contiguous(), cache.ssm.contiguous(), cache.k.contiguous(), cache.v.contiguous(), cache.conv.contiguous()]
     nxt = [torch.empty_like(t) for t in prev]
+    if out is not None:
+        cand = [out.angle_dt, out.ssm, out.k, out.v, out.conv]
+        if all(o is not None and o.shape == t.shape and o.dtype == t.dtype and o.is_contiguous() and o.data_ptr() != t.data_ptr()
+               for o, t in zip(cand, prev)):
+            nxt = cand
     y = torch.empty(b, 1, d_inner, dtype=torch.bfloat16, device=proj.device)
     c = lambda t: None if t is None else t.contiguous()
     ptrs = [proj, cw, c(conv_bias), prev[4], nxt[4], c(dt_bias), c(B_norm_weight), c(B_bias), c(C_norm_weight), c(C_bias), c(D),
