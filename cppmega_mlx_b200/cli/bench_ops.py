@@ -16,36 +16,7 @@ import torch
 REPO = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-def peaks() -> dict:
-    p = os.path.join(REPO, "MEASURED_PEAKS.json")
-    if os.path.exists(p):
-        return json.load(open(p))
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "fallback": True}
-
-
-_flush = None
-
-
-def time_cuda(fn, iters: int = 10, warmup: int = 3, flush: bool = True) -> float:
-    """Median milliseconds per call."""
-    global _flush
-    if flush and _flush is None:
-        _flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
-    for _ in range(warmup):
-        fn()
-    torch.cuda.synchronize()
-    ts = []
-    for _ in range(iters):
-        if flush:
-            _flush.zero_()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        fn()
-        e1.record()
-        e1.synchronize()
-        ts.append(e0.elapsed_time(e1))
-    ts.sort()
-    return ts[len(ts) // 2]
+from ..utils.measure import measured_peaks as peaks, time_cuda  # noqa: E402
 
 
 GEMM_SHAPES = [

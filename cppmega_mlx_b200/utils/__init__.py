@@ -1,0 +1,2 @@
+"""Shared utilities: measurement helpers (``measure``)."""
+from .measure import ClockSampler, measured_peaks, time_cuda
