@@ -148,6 +148,111 @@ __global__ void __launch_bounds__(THREADS) rmsnorm_bwd_kernel(const __nv_bfloat1
   }
 }
 
+// Warp-per-row variants for rows of up to VPL·256 columns: the whole row stays in registers (VPL 16-byte vectors per
+// lane), so a row costs one pass over memory, one warp reduction and no block barrier, and every lane has VPL independent
+// loads in flight.  Four warps (rows) per CTA, grid-stride over rows.
+template <int VPL>
+__global__ void __launch_bounds__(128) rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                const __nv_bfloat16* __restrict__ w,
+                                                                __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
+                                                                int64_t rows, int cols, float eps) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = cols >> 3;
+  for (int64_t row = blockIdx.x * 4 + warp; row < rows; row += static_cast<int64_t>(gridDim.x) * 4) {
+    const __nv_bfloat16* xr = x + row * cols;
+    float f[VPL][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int a = 0; a < VPL; ++a) {
+      const int v = lane + 32 * a;
+      if (v < nvec) {
+        load8(xr + 8 * v, f[a]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += f[a][i] * f[a][i];
+      }
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / cols + eps);
+    if (lane == 0 && rstd != nullptr) rstd[row] = r;
+    __nv_bfloat16* yr = y + row * cols;
+#pragma unroll
+    for (int a = 0; a < VPL; ++a) {
+      const int v = lane + 32 * a;
+      if (v < nvec) {
+        float g[8];
+        load8(w + 8 * v, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[a][i] = f[a][i] * r * g[i];
+        store8(yr + 8 * v, f[a]);
+      }
+    }
+  }
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(128) rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ gy,
+                                                                const __nv_bfloat16* __restrict__ x,
+                                                                const __nv_bfloat16* __restrict__ w,
+                                                                const float* __restrict__ rstd, __nv_bfloat16* __restrict__ gx,
+                                                                float* __restrict__ gw_part, int64_t rows, int cols) {
+  extern __shared__ float gws[];   // [cols] CTA-level dw partial
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = cols >> 3;
+  for (int i = threadIdx.x; i < cols; i += 128) gws[i] = 0.f;
+  __syncthreads();
+  float acc[VPL][8];
+#pragma unroll
+  for (int a = 0; a < VPL; ++a)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[a][i] = 0.f;
+  for (int64_t row = blockIdx.x * 4 + warp; row < rows; row += static_cast<int64_t>(gridDim.x) * 4) {
+    const __nv_bfloat16* xr = x + row * cols;
+    const __nv_bfloat16* gr = gy + row * cols;
+    const float r = rstd[row];
+    float fx[VPL][8], fg[VPL][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int a = 0; a < VPL; ++a) {
+      const int v = lane + 32 * a;
+      if (v < nvec) {
+        float fw[8];
+        load8(xr + 8 * v, fx[a]);
+        load8(gr + 8 * v, fg[a]);
+        load8(w + 8 * v, fw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          acc[a][i] += fg[a][i] * fx[a][i] * r;
+          fg[a][i] *= fw[i];                 // from here on g·w
+          dot += fg[a][i] * fx[a][i];
+        }
+      }
+    }
+    dot = warp_sum(dot);
+    const float c = dot * r * r * r / cols;
+    __nv_bfloat16* gxr = gx + row * cols;
+#pragma unroll
+    for (int a = 0; a < VPL; ++a) {
+      const int v = lane + 32 * a;
+      if (v < nvec) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = fg[a][i] * r - fx[a][i] * c;
+        store8(gxr + 8 * v, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < VPL; ++a) {
+    const int v = lane + 32 * a;
+    if (v < nvec) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(&gws[8 * v + i], acc[a][i]);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < cols; i += 128) gw_part[static_cast<size_t>(blockIdx.x) * cols + i] = gws[i];
+}
+
 // SwiGLU: y = silu(g) * u with gu = [.., 2H] laid out as [gate | up] halves.
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ y, int64_t rows,
                                   int H) {
@@ -217,6 +322,14 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* 
 extern "C" int cmb_rmsnorm_fwd(const void* x, const void* w, void* y, void* rstd, int64_t rows, int cols, float eps,
                                void* stream) {
   if (cols % 8) return 1;
+  if (cols <= 2048 && rows >= 4) {   // whole row in registers, one warp per row
+    const int64_t want = (rows + 3) / 4;
+    const int wgrid = static_cast<int>(want < 148 * 16 ? want : 148 * 16);
+    cmb::rmsnorm_fwd_warp_kernel<8><<<wgrid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
+        static_cast<float*>(rstd), rows, cols, eps);
+    return cudaGetLastError() == cudaSuccess ? 0 : 2;
+  }
   const int grid = static_cast<int>(rows < 148 * 16 ? rows : 148 * 16);
   cmb::rmsnorm_fwd_kernel<256><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
@@ -228,6 +341,12 @@ extern "C" int cmb_rmsnorm_bwd(const void* gy, const void* x, const void* w, con
                                int64_t rows, int cols, int nblk, void* stream) {
   if (cols % 8) return 1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cols <= 2048 && rows >= 4LL * nblk) {   // every CTA gets rows: its dw partial is fully written
+    cmb::rmsnorm_bwd_warp_kernel<8><<<nblk, 128, cols * sizeof(float), s>>>(
+        static_cast<const __nv_bfloat16*>(gy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+        static_cast<const float*>(rstd), static_cast<__nv_bfloat16*>(gx), static_cast<float*>(gw_part), rows, cols);
+    return cudaGetLastError() == cudaSuccess ? 0 : 2;
+  }
   if ((cols >> 3) > 256 * 4) cudaMemsetAsync(gw_part, 0, sizeof(float) * static_cast<size_t>(nblk) * cols, s);
   cmb::rmsnorm_bwd_kernel<256><<<nblk, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(gy),
                                                       static_cast<const __nv_bfloat16*>(x),
