@@ -13,9 +13,12 @@
 // pools): masked softmax over valid keys, zeros when no key is valid.
 //
 // Roles in a 256-thread CTA: warps 0-3 softmax / TMEM read-back, warps 4-5 cp.async gather (alternating tiles; 8 lanes per 128-byte line,
-// hand-swizzled into the 128B-swizzle layout the MMA descriptors expect), warp 6 issues tcgen05.mma.  Tiles of 64 keys are
+// hand-swizzled into the 128B-swizzle layout the MMA descriptors expect; dense key ranges use TMA boxes instead), warp 6 issues the
+// score MMAs and warp 7 the output MMAs.  Tiles of 64 keys are
 // double-buffered.  Every mbarrier wait is bounded (sm100.cuh); an abandoned wait raises the CTA's abort flag, everything
 // drains, TMEM is freed and the status word reports the site.
+#include <cstring>
+
 #include "sm100.cuh"
 
 namespace cmb {
@@ -44,6 +47,8 @@ struct DecodeParams {
   float* ws_m;                   // [B, H, splits] reference max (log2 domain)
   float* ws_l;                   // [B, H, splits] partial denominators
   int* status;
+  int tma;                       // 1: tiles are fetched with TMA boxes (dense key ranges); 0: per-row cp.async gather
+  int box_rows;                  // rows per TMA box (min(64, page_size))
   long long* trace;              // optional: per-tile clock samples of CTA (0,0,0), TRACE_SLOTS per tile (nullptr = off)
 };
 
@@ -94,7 +99,8 @@ struct DecCfg {
 };
 
 template <int DKB, int DVB, bool SHARED>
-__global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(DEC_THREADS, 1)
+paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const DecodeParams p) {
   using Cfg = DecCfg<DKB, DVB, SHARED>;
   constexpr int MB = Cfg::MB;
   constexpr int DV = DVB * 64;
@@ -145,8 +151,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
 
   // ---------------------------------------------------------------- setup
   if (threadIdx.x == 0) {
-    mbar_init(&full_bar[0], 32);
-    mbar_init(&full_bar[1], 32);
+    mbar_init(&full_bar[0], p.tma ? 1 : 32);
+    mbar_init(&full_bar[1], p.tma ? 1 : 32);
     mbar_init(&empty_bar[0], 1);
     mbar_init(&empty_bar[1], 1);
     mbar_init(&sfull_bar[0], 1);
@@ -178,7 +184,53 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
   const uint32_t tmem_s = tmem_base;                 // 2 × 16 columns
   const uint32_t tmem_o = tmem_base + 2 * DEC_N;     // MB × 16 columns
 
-  if (warp == 4 || warp == 5) {
+  if (p.tma && (warp == 4 || warp == 5)) {
+    // ---------------------------------------------------------------- TMA producer (dense key ranges)
+    // A 64-key tile is 64/box_rows boxes of [box_rows keys × 64 columns] per 128-byte column block, fetched straight into
+    // the 128B-swizzled layout; completion is counted in bytes on the tile's mbarrier, so the producer never waits for data.
+    if (warp == 4) {
+      if (lane == 0) {
+        tma_prefetch_desc(&tmK);
+        if (!SHARED) tma_prefetch_desc(&tmV);
+      }
+      const int R = p.box_rows;
+      const int last_page = p.table != nullptr ? (length - 1) / p.page_size : 0;
+      for (int t = 0; t < T; ++t) {
+        const int buf = t & 1;
+        const int pos0 = (t_begin + t) * DEC_TILE;
+        int ok = lane == 0 ? static_cast<int>(mbar_wait(&empty_bar[buf], ((t >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);   // one lane waits; the whole warp takes the same exit
+        if (!ok) break;
+        valid[buf * DEC_TILE + lane] = pos0 + lane < length ? 1 : 0;
+        valid[buf * DEC_TILE + 32 + lane] = pos0 + 32 + lane < length ? 1 : 0;
+        __syncwarp();
+        if (lane == 0) {
+          trace_mark(p, t, 1);
+          uint8_t* kb_s = bufs + buf * Cfg::BUF_BYTES;
+          uint8_t* vb_s = kb_s + DKB * DEC_BLK;
+          mbar_arrive_expect_tx(&full_bar[buf], Cfg::BUF_BYTES);
+          for (int r0 = 0; r0 < DEC_TILE; r0 += R) {
+            const int pos = pos0 + r0;
+            int c2, c3;
+            if (p.table != nullptr) {   // keys past the sequence re-read its last page (finite rows, masked by the softmax)
+              c3 = p.table[static_cast<long long>(b) * p.table_w + min(pos / p.page_size, last_page)];
+              c2 = pos % p.page_size;
+            } else {
+              c3 = b;
+              c2 = pos;                 // rows past the cache extent are zero-filled by the TMA unit
+            }
+#pragma unroll
+            for (int kb = 0; kb < DKB; ++kb) tma_load_4d(kb_s + kb * DEC_BLK + r0 * 128, &tmK, &full_bar[buf], kb * 64, kvh, c2, c3);
+            if (!SHARED) {
+#pragma unroll
+              for (int kb = 0; kb < DVB; ++kb) tma_load_4d(vb_s + kb * DEC_BLK + r0 * 128, &tmV, &full_bar[buf], kb * 64, kvh, c2, c3);
+            }
+          }
+          trace_mark(p, t, 2);
+        }
+      }
+    }
+  } else if (warp == 4 || warp == 5) {
     // ---------------------------------------------------------------- gather
     // The two gather warps alternate tiles (warp 4: even, warp 5: odd). Each waits only for its own buffer to be released and
     // for its own copies to land, so tile t+1 is in flight while tile t is being consumed and neither warp ever waits on
@@ -246,56 +298,56 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) paged_decode_kernel(const Deco
     }
     cp_async_wait<0>();
   } else if (warp == 6) {
-    // ---------------------------------------------------------------- MMA issuer
+    // ---------------------------------------------------------------- score MMAs (one thread)
+    // The two GEMMs are issued by two different threads (this one and warp 7's): each only waits for what its own GEMM
+    // needs, so the output MMAs of tile t are never queued behind the load of tile t+1 and a tile buffer is released as
+    // early as the data flow allows.  They touch disjoint TMEM columns and never the same shared-memory tile at once.
     if (lane == 0) {
       constexpr uint32_t idesc1 = make_idesc(DEC_TILE, DEC_N, 1, 1, 0, 0);
-      constexpr uint32_t idesc2 = make_idesc(128, DEC_N, 1, 1, 1, 0);
-      const uint32_t q_s = smem_u32(qs), p_s = smem_u32(ps);
-      auto gemm2 = [&](int t) -> bool {
-        if (!mbar_wait(pfull_bar, t & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) return false;
-        tc_fence_after();
-        trace_mark(p, t, 7);
-        const uint32_t vb_s = smem_u32(bufs + (t & 1) * Cfg::BUF_BYTES + (SHARED ? 0 : DKB * DEC_BLK));
-        const uint64_t adesc0 = make_smem_desc_sw128(vb_s, DEC_BLK, 1024);
-        const uint64_t bdesc0 = make_smem_desc_sw128(p_s, 16, 1024);
-#pragma unroll
-        for (int j = 0; j < MB; ++j) {
-#pragma unroll
-          for (int k = 0; k < DEC_TILE / 16; ++k) {
-            // offsets are added to the descriptors' 16-byte-unit address field (all buffers sit below 256 KB: no carry)
-            umma_f16(tmem_o + j * DEC_N, adesc0 + (((2 * j) * DEC_BLK + k * 2048) >> 4), bdesc0 + ((k * 32) >> 4), idesc2,
-                     (t > 0 || k > 0) ? 1u : 0u);
-          }
-        }
-        umma_commit(&empty_bar[t & 1]);
-        umma_commit(odone_bar);
-        trace_mark(p, t, 8);
-        return true;
-      };
-      bool ok = true;
-      for (int t = 0; t < T && ok; ++t) {
+      const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(qs), 16, 1024);
+      for (int t = 0; t < T; ++t) {
         const int buf = t & 1;
         if (!mbar_wait(&full_bar[buf], (t >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_FULL)) break;
         trace_mark(p, t, 4);
         if (!mbar_wait(&sfree_bar[buf], ((t >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
         trace_mark(p, t, 5);
-        const uint32_t kb_s = smem_u32(bufs + buf * Cfg::BUF_BYTES);
-        const uint64_t adesc0 = make_smem_desc_sw128(kb_s, 16, 1024);
-        const uint64_t bdesc0 = make_smem_desc_sw128(q_s, 16, 1024);
+        const uint64_t adesc0 = make_smem_desc_sw128(smem_u32(bufs + buf * Cfg::BUF_BYTES), 16, 1024);
 #pragma unroll
         for (int kb = 0; kb < DKB; ++kb) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
+            // offsets are added to the descriptors' 16-byte-unit address field (all buffers sit below 256 KB: no carry)
             umma_f16(tmem_s + buf * DEC_N, adesc0 + ((kb * DEC_BLK + k * 32) >> 4), bdesc0 + ((kb * (DEC_N * 128) + k * 32) >> 4),
                      idesc1, (kb > 0 || k > 0) ? 1u : 0u);
           }
         }
         umma_commit(&sfull_bar[buf]);
         trace_mark(p, t, 6);
-        if (t > 0) ok = gemm2(t - 1);
       }
-      if (ok) gemm2(T - 1);
+    }
+  } else if (warp == 7) {
+    // ---------------------------------------------------------------- output MMAs (one thread)
+    if (lane == 0) {
+      constexpr uint32_t idesc2 = make_idesc(128, DEC_N, 1, 1, 1, 0);
+      const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(ps), 16, 1024);
+      for (int t = 0; t < T; ++t) {
+        if (!mbar_wait(pfull_bar, t & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
+        tc_fence_after();
+        trace_mark(p, t, 7);
+        const uint32_t vb_s = smem_u32(bufs + (t & 1) * Cfg::BUF_BYTES + (SHARED ? 0 : DKB * DEC_BLK));
+        const uint64_t adesc0 = make_smem_desc_sw128(vb_s, DEC_BLK, 1024);
+#pragma unroll
+        for (int j = 0; j < MB; ++j) {
+#pragma unroll
+          for (int k = 0; k < DEC_TILE / 16; ++k)
+            umma_f16(tmem_o + j * DEC_N, adesc0 + (((2 * j) * DEC_BLK + k * 2048) >> 4), bdesc0 + ((k * 32) >> 4), idesc2,
+                     (t > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[t & 1]);
+        umma_commit(odone_bar);
+        trace_mark(p, t, 8);
+      }
     }
   } else if (warp < 4) {
     // ---------------------------------------------------------------- softmax / read-back (128 threads)
@@ -455,8 +507,29 @@ namespace {
 
 long long* g_decode_trace = nullptr;
 
+// 4-D map over a cache: (columns, kv heads, rows per page | cache length, pages | batch); strides in elements.
+int make_tmap_cache(CUtensorMap* out, const void* base, int cols, int kv_heads, long long ext2, long long ext3, long long s_head,
+                    long long s_row, long long s_outer, int box_rows) {
+  cmb_host::EncodeTiledFn fn = cmb_host::encode_tiled_fn();
+  if (fn == nullptr) return 101;
+  cmb_host::bind_context_once();
+  if (reinterpret_cast<uintptr_t>(base) & 15) return 102;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(kv_heads), static_cast<cuuint64_t>(ext2),
+                        static_cast<cuuint64_t>(ext3)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>((kv_heads > 1 ? s_head : s_row) * 2), static_cast<cuuint64_t>(s_row * 2),
+                           static_cast<cuuint64_t>((ext3 > 1 ? s_outer : s_row * ext2) * 2)};
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] == 0 || (strides[i] & 15)) return 105;
+  cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + static_cast<int>(r);
+}
+
 template <int DKB, int DVB, bool SHARED>
-int launch_decode(const cmb::DecodeParams& p, cudaStream_t stream) {
+int launch_decode(cmb::DecodeParams& p, long long ext2, long long ext3, cudaStream_t stream) {
   using Cfg = cmb::DecCfg<DKB, DVB, SHARED>;
   auto kern = cmb::paged_decode_kernel<DKB, DVB, SHARED>;
   static bool attr_set = false;
@@ -464,17 +537,33 @@ int launch_decode(const cmb::DecodeParams& p, cudaStream_t stream) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 103;
     attr_set = true;
   }
+  // Dense key ranges whose 64-key tiles decompose into whole boxes inside one page go through TMA.
+  const bool paged = p.table != nullptr;
+  const int ps = p.page_size;
+  p.tma = p.topk == nullptr && ext2 > 0 && ext3 > 0 &&
+          (!paged || (ps % 8 == 0 && (ps >= cmb::DEC_TILE ? ps % cmb::DEC_TILE == 0 : cmb::DEC_TILE % ps == 0)));
+  p.box_rows = paged && ps < cmb::DEC_TILE ? ps : cmb::DEC_TILE;
+  CUtensorMap tmK, tmV;
+  memset(&tmK, 0, sizeof(tmK));
+  memset(&tmV, 0, sizeof(tmV));
+  if (p.tma) {
+    int rc = make_tmap_cache(&tmK, p.k, DKB * 64, p.kv_heads, ext2, ext3, p.k_head, p.k_row, paged ? p.k_page : p.k_batch, p.box_rows);
+    if (rc == 0 && !SHARED)
+      rc = make_tmap_cache(&tmV, p.v, DVB * 64, p.kv_heads, ext2, ext3, p.v_head, p.v_row, paged ? p.v_page : p.v_batch, p.box_rows);
+    if (rc != 0) p.tma = 0;   // fall back to the per-row gather (e.g. strides the tensor-map encoder refuses)
+  }
   const int g = p.H / p.kv_heads;
   const int gchunks = (g + cmb::DEC_N - 1) / cmb::DEC_N;
   dim3 grid(p.splits, p.B, p.kv_heads * gchunks);
-  kern<<<grid, cmb::DEC_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
+  kern<<<grid, cmb::DEC_THREADS, Cfg::SMEM_BYTES, stream>>>(tmK, tmV, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
 }  // namespace
 
 // One decode step of attention for B sequences. q [B,H,Dk] bf16 (strides in elements), out [B,H,Dv] bf16 contiguous.
-// ip = {B, H, kv_heads, Dk, Dv, shared_kv, table_w, page_size, topk_n, splits}; lp = {q_sb, q_sh, k_page, k_row, k_batch,
+// ip = {B, H, kv_heads, Dk, Dv, shared_kv, table_w, page_size, topk_n, splits, ext2, ext3} (ext2 = rows per page or the
+// contiguous cache's length, ext3 = pages in the pool or batch rows: the extents of the cache tensor, 0 = unknown); lp = {q_sb, q_sh, k_page, k_row, k_batch,
 // k_head, v_page, v_row, v_batch, v_head} (elements). table / topk / v / lse may be null. Workspaces: ws_o
 // [B,H,splits,Dv], ws_m and ws_l [B,H,splits] fp32. Returns 0, or 1 for an unsupported shape.
 extern "C" int cmb_paged_decode(const void* q, const void* k, const void* v, const int* table, const int* lengths,
@@ -501,11 +590,12 @@ extern "C" int cmb_paged_decode(const void* q, const void* k, const void* v, con
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) return 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc = 1;
-  if (shared && Dk == 576 && Dv == 512) rc = launch_decode<9, 8, true>(p, st);
-  else if (!shared && v != nullptr && Dk == 128 && Dv == 128) rc = launch_decode<2, 2, false>(p, st);
-  else if (!shared && v != nullptr && Dk == 192 && Dv == 128) rc = launch_decode<3, 2, false>(p, st);
-  else if (!shared && v != nullptr && Dk == 64 && Dv == 128) rc = launch_decode<1, 2, false>(p, st);
-  else if (!shared && v != nullptr && Dk == 256 && Dv == 256) rc = launch_decode<4, 4, false>(p, st);
+  const long long e2 = ip[10], e3 = ip[11];
+  if (shared && Dk == 576 && Dv == 512) rc = launch_decode<9, 8, true>(p, e2, e3, st);
+  else if (!shared && v != nullptr && Dk == 128 && Dv == 128) rc = launch_decode<2, 2, false>(p, e2, e3, st);
+  else if (!shared && v != nullptr && Dk == 192 && Dv == 128) rc = launch_decode<3, 2, false>(p, e2, e3, st);
+  else if (!shared && v != nullptr && Dk == 64 && Dv == 128) rc = launch_decode<1, 2, false>(p, e2, e3, st);
+  else if (!shared && v != nullptr && Dk == 256 && Dv == 256) rc = launch_decode<4, 4, false>(p, e2, e3, st);
   if (rc) return rc;
   cmb::decode_combine_kernel<<<static_cast<unsigned>(p.B) * p.H, 128, 0, st>>>(ws_o, ws_m, ws_l, static_cast<__nv_bfloat16*>(out),
                                                                               lse, p.splits, Dv);

@@ -341,7 +341,7 @@ extern "C" int cmb_rmsnorm_bwd(const void* gy, const void* x, const void* w, con
                                int64_t rows, int cols, int nblk, void* stream) {
   if (cols % 8) return 1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (cols <= 2048 && rows >= 4LL * nblk) {   // every CTA gets rows: its dw partial is fully written
+  if (cols <= 2048 && rows >= 4) {   // a CTA without rows still writes its (zero) dw partial
     cmb::rmsnorm_bwd_warp_kernel<8><<<nblk, 128, cols * sizeof(float), s>>>(
         static_cast<const __nv_bfloat16*>(gy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
         static_cast<const float*>(rstd), static_cast<__nv_bfloat16*>(gx), static_cast<float*>(gw_part), rows, cols);
@@ -425,9 +425,15 @@ extern "C" int cmb_rmsnorm_bwd_noalloc(const void* gy, const void* x, const void
   const int nblk = static_cast<int>(rows < cmb::NOALLOC_MAX_BLOCKS ? rows : cmb::NOALLOC_MAX_BLOCKS);
   // Every partial row that the reduction reads (rows 0..nblk-1, columns 0..cols-1) is fully overwritten by the first
   // kernel, so nothing left over from an earlier call can leak in and no clearing is needed.
-  cmb::rmsnorm_bwd_kernel<256><<<nblk, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(gy), static_cast<const __nv_bfloat16*>(x),
-                                                    static_cast<const __nv_bfloat16*>(w), static_cast<const float*>(rstd),
-                                                    static_cast<__nv_bfloat16*>(gx), scratch, rows, cols);
+  // Same kernel choice as cmb_rmsnorm_bwd, so both entry points return identical bits.
+  if (cols <= 2048 && rows >= 4)
+    cmb::rmsnorm_bwd_warp_kernel<8><<<nblk, 128, cols * sizeof(float), s>>>(
+        static_cast<const __nv_bfloat16*>(gy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+        static_cast<const float*>(rstd), static_cast<__nv_bfloat16*>(gx), scratch, rows, cols);
+  else
+    cmb::rmsnorm_bwd_kernel<256><<<nblk, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(gy), static_cast<const __nv_bfloat16*>(x),
+                                                      static_cast<const __nv_bfloat16*>(w), static_cast<const float*>(rstd),
+                                                      static_cast<__nv_bfloat16*>(gx), scratch, rows, cols);
   if (cudaGetLastError() != cudaSuccess) return -6;
   cmb::rmsnorm_noalloc_reduce_kernel<<<(cols + 255) / 256, 256, 0, s>>>(scratch, gw, nblk, cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -6;

@@ -107,8 +107,9 @@ def decode_attention(q, k_rows, v_rows, table, lengths, *, scale: float, topk=No
     ws_ml = torch.empty(2, b, h, splits, dtype=torch.float32, device=dev)
     ks, vs = k_rows.stride(), (k_rows.stride() if v_rows is None else v_rows.stride())
     paged = tbl is not None
-    ip = (ctypes.c_int * 10)(b, h, kvh, dk, dv, int(v_rows is None), tbl.shape[1] if paged else 0,
-                             k_rows.shape[1] if paged else 0, tk.shape[1] if tk is not None else 0, splits)
+    ip = (ctypes.c_int * 12)(b, h, kvh, dk, dv, int(v_rows is None), tbl.shape[1] if paged else 0,
+                             k_rows.shape[1] if paged else 0, tk.shape[1] if tk is not None else 0, splits, k_rows.shape[1],
+                             k_rows.shape[0])
     lp = (ctypes.c_longlong * 10)(q.stride(0), q.stride(1), ks[0] if paged else 0, ks[1], 0 if paged else ks[0], ks[2],
                                   vs[0] if paged else 0, vs[1], 0 if paged else vs[0], vs[2])
     B.check(lib.cmb_paged_decode(B.ptr(q), B.ptr(k_rows), B.ptr(v_rows), B.ptr(tbl), B.ptr(lengths), B.ptr(tk), B.ptr(out),
