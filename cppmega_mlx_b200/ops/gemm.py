@@ -144,7 +144,7 @@ class _LinearFn(torch.autograd.Function):
         return gx, gw
 
 
-SKINNY_MAX_ROWS = 4   # above this the FMA issue rate, not the weight stream, bounds the CUDA-core kernel
+SKINNY_MAX_ROWS = 8
 
 
 def skinny_linear(x2: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
@@ -160,7 +160,8 @@ def skinny_linear(x2: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None =
     return y if bias is None or bias.dtype == torch.bfloat16 else y + bias
 
 
-SMALL_M_MAX_ROWS = 64
+SMALL_M_MAX_ROWS = 0   # dispatch threshold for small_m_linear; 0 = off: measured on the 1B decode step (batch 8 and 32) the
+                       # split-contraction route (GEMM + reduction + transpose) did not beat the skinny kernel / the plain GEMM
 _split_ranges: dict[tuple, torch.Tensor] = {}
 
 
@@ -188,7 +189,9 @@ def small_m_linear(x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     gemm_batched(w, x2, part, M=N, N=mp, K=K, a_mn=False, b_mn=False, lda=w.stride(0), ldb=x2.stride(0), ldc=mp, nb=(splits, 1, 1),
                  sA=(0, 0, 0), sB=(0, 0, 0), sC=(N * mp, 0, 0), a_div2=splits, b_div2=splits, k_ranges=kr, out_f32=True)
     y = part.sum(0) if splits > 1 else part[0]
-    return y.t()[:M].to(torch.bfloat16)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x2.device)     # contiguous rows, whatever the layout of the partials
+    out.copy_(y.t()[:M])
+    return out
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
