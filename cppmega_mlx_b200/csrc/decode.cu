@@ -12,7 +12,7 @@
 // (cppmega_mlx/nn/sparse_mla.py:125-210 for the sparse form; cppmega_mlx/inference/serving.py:47-215 describes the paged
 // pools): masked softmax over valid keys, zeros when no key is valid.
 //
-// Roles in a 256-thread CTA: warps 0-3 softmax / TMEM read-back, warps 4-5 cp.async gather (alternating tiles; 8 lanes per 128-byte line,
+// Roles in a 320-thread CTA: warps 0-3 softmax / TMEM read-back, warps 4-5 and 8-9 cp.async gather (pairs alternate tiles; 8 lanes per 128-byte line,
 // hand-swizzled into the 128B-swizzle layout the MMA descriptors expect; dense key ranges use TMA boxes instead), warp 6 issues the
 // score MMAs and warp 7 the output MMAs.  Tiles of 64 keys are
 // double-buffered.  Every mbarrier wait is bounded (sm100.cuh); an abandoned wait raises the CTA's abort flag, everything
@@ -26,7 +26,7 @@ namespace cmb {
 constexpr int DEC_TILE = 64;       // keys per tile
 constexpr int DEC_N = 16;          // heads per CTA (MMA N)
 constexpr int DEC_BLK = 8192;      // bytes of one [64 keys × 64 bf16] block
-constexpr int DEC_THREADS = 256;
+constexpr int DEC_THREADS = 320;   // warps 0-3 softmax, 4-5 and 8-9 gather, 6 score MMAs, 7 output MMAs
 constexpr float DEC_RESCALE_THRESHOLD = 8.f;  // log2 units a tile max may exceed the reference before O is rescaled
 
 struct DecodeParams {
@@ -151,8 +151,8 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
 
   // ---------------------------------------------------------------- setup
   if (threadIdx.x == 0) {
-    mbar_init(&full_bar[0], p.tma ? 1 : 32);
-    mbar_init(&full_bar[1], p.tma ? 1 : 32);
+    mbar_init(&full_bar[0], p.tma ? 1 : 64);
+    mbar_init(&full_bar[1], p.tma ? 1 : 64);
     mbar_init(&empty_bar[0], 1);
     mbar_init(&empty_bar[1], 1);
     mbar_init(&sfull_bar[0], 1);
@@ -184,7 +184,8 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
   const uint32_t tmem_s = tmem_base;                 // 2 × 16 columns
   const uint32_t tmem_o = tmem_base + 2 * DEC_N;     // MB × 16 columns
 
-  if (p.tma && (warp == 4 || warp == 5)) {
+  const bool gather_warp = warp == 4 || warp == 5 || warp >= 8;
+  if (p.tma && gather_warp) {
     // ---------------------------------------------------------------- TMA producer (dense key ranges)
     // A 64-key tile is 64/box_rows boxes of [box_rows keys × 64 columns] per 128-byte column block, fetched straight into
     // the 128B-swizzled layout; completion is counted in bytes on the tile's mbarrier, so the producer never waits for data.
@@ -230,12 +231,13 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
         }
       }
     }
-  } else if (warp == 4 || warp == 5) {
+  } else if (gather_warp) {
     // ---------------------------------------------------------------- gather
-    // The two gather warps alternate tiles (warp 4: even, warp 5: odd). Each waits only for its own buffer to be released and
-    // for its own copies to land, so tile t+1 is in flight while tile t is being consumed and neither warp ever waits on
-    // work that needs the other's arrival first.
-    const int lw = warp - 4;
+    // Two pairs of gather warps alternate tiles (warps 4,5: even tiles; warps 8,9: odd tiles), each warp fetching half of
+    // the tile's rows.  A pair waits only for its own buffer to be released and for its own copies to land, so tile t+1 is
+    // in flight while tile t is being consumed and no warp ever waits on work that needs another pair's arrival first.
+    const int lw = warp >= 8 ? 1 : 0;
+    const int half = warp & 1;
     const int sub = lane >> 3, c = lane & 7;
     const __nv_bfloat16* kbase = p.k + kvh * p.k_head + (p.table == nullptr ? b * p.k_batch : 0);
     const __nv_bfloat16* vbase = SHARED ? nullptr : p.v + kvh * p.v_head + (p.table == nullptr ? b * p.v_batch : 0);
@@ -245,11 +247,11 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
       uint8_t* vb_s = kb_s + DKB * DEC_BLK;
       // Phase 1: all index / page-table reads of this lane's 16 rows are issued before anything depends on them (they
       // are dependent global loads; serialising them row by row would cost a memory latency per row).
-      constexpr int RPL = DEC_TILE / 4;   // rows per lane group
+      constexpr int RPL = DEC_TILE / 8;   // rows per lane group (half a tile per warp)
       int pos[RPL];
 #pragma unroll
       for (int it = 0; it < RPL; ++it) {
-        const int ki = (t_begin + t) * DEC_TILE + it * 4 + sub;
+        const int ki = (t_begin + t) * DEC_TILE + half * 32 + it * 4 + sub;
         pos[it] = -1;
         if (ki < total) pos[it] = p.topk != nullptr ? __ldg(p.topk + static_cast<long long>(b) * p.topk_n + ki) : ki;
         if (pos[it] >= length || (p.table != nullptr && pos[it] / p.page_size >= p.table_w)) pos[it] = -1;
@@ -264,7 +266,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
       if (lane == 0) trace_mark(p, t, 1);
 #pragma unroll
       for (int it = 0; it < RPL; ++it) {
-        const int row = it * 4 + sub;
+        const int row = half * 32 + it * 4 + sub;
         const bool ok_row = pos[it] >= 0;
         long long koff = 0, voff = 0;
         if (ok_row) {
