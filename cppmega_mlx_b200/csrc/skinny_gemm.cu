@@ -27,6 +27,18 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(const __nv_bflo
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[c][m] = 0.f;
 
+  // The first weight vectors do not depend on x: they are requested before x is staged, so the stream from HBM starts with
+  // the kernel instead of after the first barrier.
+  uint4 wv[SK_UNROLL][SK_COLS];
+  auto load_w = [&](int k0, int kw, int k) {
+#pragma unroll
+    for (int u = 0; u < SK_UNROLL; ++u)
+#pragma unroll
+      for (int c = 0; c < SK_COLS; ++c)
+        wv[u][c] = (n0 + c < N && k + u * 256 < kw) ? __ldcs(reinterpret_cast<const uint4*>(w + (n0 + c) * ldw + k0 + k + u * 256))
+                                                    : make_uint4(0, 0, 0, 0);
+  };
+  load_w(0, min(SK_SLAB, K), lane * 8);
   for (int k0 = 0; k0 < K; k0 += SK_SLAB) {
     const int kw = min(SK_SLAB, K - k0);            // multiple of 8
     __syncthreads();
@@ -35,30 +47,22 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(const __nv_bflo
       *reinterpret_cast<uint4*>(xs + m * SK_SLAB + c8 * 8) = *reinterpret_cast<const uint4*>(x + m * ldx + k0 + c8 * 8);
     }
     __syncthreads();
-    if (n0 < N) {
-      for (int k = lane * 8; k < kw; k += 256 * SK_UNROLL) {
-        uint4 wv[SK_UNROLL][SK_COLS];
+    for (int k = lane * 8; k < kw; k += 256 * SK_UNROLL) {
+      if (k0 > 0 || k > lane * 8) load_w(k0, kw, k);   // the very first batch is already in flight
 #pragma unroll
-        for (int u = 0; u < SK_UNROLL; ++u)
+      for (int u = 0; u < SK_UNROLL; ++u) {
+        if (k + u * 256 >= kw) break;
 #pragma unroll
-          for (int c = 0; c < SK_COLS; ++c)
-            wv[u][c] = (n0 + c < N && k + u * 256 < kw) ? __ldcs(reinterpret_cast<const uint4*>(w + (n0 + c) * ldw + k0 + k + u * 256))
-                                                        : make_uint4(0, 0, 0, 0);
+        for (int m = 0; m < M; ++m) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(xs + m * SK_SLAB + k + u * 256);
+          const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
 #pragma unroll
-        for (int u = 0; u < SK_UNROLL; ++u) {
-          if (k + u * 256 >= kw) break;
+          for (int c = 0; c < SK_COLS; ++c) {
+            const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv[u][c]);
 #pragma unroll
-          for (int m = 0; m < M; ++m) {
-            const uint4 xv = *reinterpret_cast<const uint4*>(xs + m * SK_SLAB + k + u * 256);
-            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
-#pragma unroll
-            for (int c = 0; c < SK_COLS; ++c) {
-              const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv[u][c]);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 a = __bfloat1622float2(xp[j]), b = __bfloat1622float2(wp[j]);
-                acc[c][m] = fmaf(a.x, b.x, fmaf(a.y, b.y, acc[c][m]));
-              }
+            for (int j = 0; j < 4; ++j) {
+              const float2 a = __bfloat1622float2(xp[j]), b = __bfloat1622float2(wp[j]);
+              acc[c][m] = fmaf(a.x, b.x, fmaf(a.y, b.y, acc[c][m]));
             }
           }
         }

@@ -147,12 +147,23 @@ class GraphDecodeSession:
         return self._logits
 
     @torch.no_grad()
-    def generate(self, input_ids: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
-        """Greedy continuation; the argmax → next-token hand-off stays on the device."""
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int, *, temperature: float = 0.0, top_k: int | None = None,
+                 top_p: float | None = None, generator: torch.Generator | None = None, eos_token_id: int | None = None) -> torch.Tensor:
+        """Continuation of ``input_ids`` [B,S]: greedy at ``temperature == 0``, otherwise temperature / top-k / top-p sampling.
+        The logits → next-token hand-off stays on the device (no host read per token unless ``eos_token_id`` asks for the
+        all-finished test, which is checked every 16 tokens)."""
+        from .sampling import sample_next_token
         logits = self.prefill(input_ids)
         out = [input_ids]
-        for _ in range(max_new_tokens):
-            nxt = logits.argmax(-1, keepdim=True)
+        done = torch.zeros(input_ids.shape[0], dtype=torch.bool, device=input_ids.device)
+        for i in range(max_new_tokens):
+            nxt = sample_next_token(logits, temperature=temperature, top_k=top_k, top_p=top_p, generator=generator).reshape(-1, 1)
+            if eos_token_id is not None:
+                nxt = torch.where(done[:, None], torch.full_like(nxt, eos_token_id), nxt)
+                done |= nxt[:, 0] == eos_token_id
             out.append(nxt)
-            logits = self.step(nxt)
+            if eos_token_id is not None and i % 16 == 15 and bool(done.all()):
+                break
+            if i + 1 < max_new_tokens:
+                logits = self.step(nxt)
         return torch.cat(out, dim=1)

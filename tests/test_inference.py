@@ -268,3 +268,17 @@ def test_static_cache_steps_equal_growing_cache_steps(pattern, kw):
         I.GraphDecodeSession(m, capacity=8).prefill(ids[:, :9])
     out = I.GraphDecodeSession(m, capacity=32, use_graph=False).generate(ids[:, :9], 4)
     assert torch.equal(out, I.generate_tokens_with_kv_cache(m, ids[:, :9], max_new_tokens=4))
+
+
+def test_graph_session_sampling_and_eos():
+    m = _model("AM", mla_low_rank=True)
+    ids = torch.randint(4, 100, (2, 9))
+    g = torch.Generator().manual_seed(3)
+    a = I.GraphDecodeSession(m, capacity=64, use_graph=False).generate(ids, 6, temperature=0.8, top_k=20, top_p=0.9, generator=g)
+    g = torch.Generator().manual_seed(3)
+    b = I.GraphDecodeSession(m, capacity=64, use_graph=False).generate(ids, 6, temperature=0.8, top_k=20, top_p=0.9, generator=g)
+    assert a.shape == (2, 15) and torch.equal(a, b)
+    greedy = I.GraphDecodeSession(m, capacity=64, use_graph=False).generate(ids, 6)
+    eos = int(greedy[0, 10])
+    c = I.GraphDecodeSession(m, capacity=64, use_graph=False).generate(ids, 6, eos_token_id=eos)
+    assert torch.equal(c[0, :11], greedy[0, :11]) and bool((c[0, 11:] == eos).all())
