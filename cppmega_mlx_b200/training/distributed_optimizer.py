@@ -112,6 +112,8 @@ class DistributedZeRO1Optimizer:
                 self._fused = FusedZeRO1Comm(group)
                 alloc = self._fused.alloc
             self.flat = FlatBuffers(self.named, self.owners, self.world, alloc=alloc)
+            from ..parallel.consistency import check_rank_consistency
+            check_rank_consistency(self.named, slots=self.flat.slots, group=group, what="ZeRO-1 flat-buffer layouts")
             if self._fused is not None:
                 self._fused.bind(self.flat)
         self.inner = inner_factory(self.owned if self.world > 1 else self.named)

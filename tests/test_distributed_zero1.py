@@ -72,3 +72,22 @@ def test_owner_assignment_is_balanced_and_disjoint():
         load[owners[n]] += p.numel()
     biggest = max(p.numel() for _, p in named)
     assert max(load) <= max(biggest, 1.5 * (sum(load) / 4))
+
+
+def _consistency(rank, world, mismatch):
+    from cppmega_mlx_b200.parallel.consistency import check_rank_consistency
+    torch.manual_seed(0)
+    named = [("a.weight", torch.zeros(4, 8)), ("b.weight", torch.zeros(3 if (mismatch and rank == 1) else 5))]
+    try:
+        return "ok:" + check_rank_consistency(named, slots={"a.weight": (0, 0, 32)})[:8]
+    except RuntimeError as e:
+        return "error:" + str(e)
+
+
+def test_rank_consistency_check_passes_and_names_the_first_difference():
+    """Every rank must describe the same tensors before a kernel addresses peers' buffers by offset."""
+    same = run_ranks(_consistency, 2, False)
+    assert same[0] == same[1] and same[0].startswith("ok:")
+    diff = run_ranks(_consistency, 2, True)
+    for r in diff:                                   # raised on every rank, pointing at the entry
+        assert r.startswith("error:") and "b.weight" in r and "entry 1" in r
