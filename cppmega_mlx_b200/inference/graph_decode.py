@@ -103,6 +103,7 @@ class GraphDecodeSession:
 
     def _snapshot(self):
         tens = [t for st in self.states for *_, t in _state_tensors(st)] + [t for t in self.cache.a + self.cache.b if t is not None]
+        tens.append(self.cache.lengths())
         return tens, [t.clone() for t in tens], self.cache.pos.clone()
 
     def _capture(self) -> None:

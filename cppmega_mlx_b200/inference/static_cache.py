@@ -18,6 +18,8 @@ class StaticDecodeCache:
     def __init__(self, num_layers: int, batch: int, capacity: int, device):
         self.num_layers, self.batch, self.capacity = num_layers, batch, capacity
         self.pos = torch.zeros(1, dtype=torch.int64, device=device)      # next row to write == tokens stored so far
+        self._len32 = torch.ones(batch, dtype=torch.int32, device=device)   # pos + 1 per sequence, kept in step with pos
+        self._rope: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}      # per-step memo of rope rows at ``pos``
         self.a: list[torch.Tensor | None] = [None] * num_layers           # keys or the MLA latent
         self.b: list[torch.Tensor | None] = [None] * num_layers           # values or the indexer keys
 
@@ -30,8 +32,18 @@ class StaticDecodeCache:
         return self.pos
 
     def lengths(self) -> torch.Tensor:
-        """[B] int32: keys visible to the token being decoded (its own row included)."""
-        return (self.pos + 1).to(torch.int32).expand(self.batch).contiguous()
+        """[B] int32: keys visible to the token being decoded (its own row included). One fixed tensor, updated by ``advance``."""
+        return self._len32
+
+    def rope(self, rot_dim: int, theta: float, scaling=None) -> tuple[torch.Tensor, torch.Tensor]:
+        """cos/sin rows [1, rot_dim/2] at the current position, computed once per step however many layers ask."""
+        from ..ops.rope import rope_tables_at
+        key = (rot_dim, theta, scaling)
+        hit = self._rope.get(key)
+        if hit is None:
+            hit = rope_tables_at(self.pos, rot_dim, theta, scaling, capacity=self.capacity)
+            self._rope[key] = hit
+        return hit
 
     def _buf(self, store: list, layer_idx: int, x: torch.Tensor) -> torch.Tensor:
         buf = store[layer_idx]
@@ -53,6 +65,8 @@ class StaticDecodeCache:
 
     def advance(self, n: int = 1) -> None:
         self.pos += n
+        self._len32 += n
+        self._rope.clear()
 
     # -- hand-over from a prefill done with the growing cache -----------------------------------
     def load_from(self, kv, tokens_seen: int | None = None) -> None:
@@ -72,6 +86,8 @@ class StaticDecodeCache:
                 self.b[i] = torch.zeros((self.batch, self.capacity, *src_b.shape[2:]), dtype=src_b.dtype, device=src_b.device)
                 self.b[i][:, :n] = src_b
         self.pos.fill_(n)
+        self._len32.fill_(n + 1)
+        self._rope.clear()
 
     def nbytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.a + self.b if t is not None)

@@ -234,7 +234,7 @@ class CausalSelfAttention(nn.Module):
         from ..ops import decode_attention as DA
         c = self.config
         b = x.shape[0]
-        cos, sin = ops.rope_tables_at(cache.pos, c.q_head_dim, c.rope_theta, c.rope_scaling(), capacity=cache.capacity)
+        cos, sin = cache.rope(c.q_head_dim, c.rope_theta, c.rope_scaling())
         rope = (lambda t: ops.apply_rope(t, cos, sin)) if c.use_rope else (lambda t: t)
         q = rope(self.q_proj(x).view(b, 1, c.num_q_heads, c.q_head_dim))[:, 0]
         lengths = cache.lengths()

@@ -206,7 +206,7 @@ class MLAAttention(nn.Module):
         from ..ops import decode_attention as DA
         c = self.config
         b = x.shape[0]
-        freqs = ops.rope_tables_at(cache.pos, c.qk_rope_head_dim, c.rope_theta, capacity=cache.capacity)
+        freqs = cache.rope(c.qk_rope_head_dim, c.rope_theta)
         qr, q, c_kv, k_pe, _ = self._project(x, 0, freqs)
         rows = cache.write_a(layer_idx, torch.cat([c_kv, k_pe], dim=-1))          # [B, capacity, 576]
         lengths = cache.lengths()
