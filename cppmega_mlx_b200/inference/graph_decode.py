@@ -121,14 +121,21 @@ class GraphDecodeSession:
                 self._step_body(parity)
         torch.cuda.current_stream().wait_stream(side)
         restore()
-        self.graphs = []
+        graphs = []
         pool = None
-        for parity in (0, 1):
-            g = torch.cuda.CUDAGraph()
-            with torch.no_grad(), torch.cuda.graph(g, pool=pool):
-                self._step_body(parity)
-            pool = g.pool()
-            self.graphs.append(g)
+        try:
+            for parity in (0, 1):
+                g = torch.cuda.CUDAGraph()
+                with torch.no_grad(), torch.cuda.graph(g, pool=pool):
+                    self._step_body(parity)
+                pool = g.pool()
+                graphs.append(g)
+            self.graphs = graphs
+        except RuntimeError as e:   # a layer that reads a value on the host cannot be captured: keep the eager static step
+            import warnings
+            warnings.warn(f"decode step could not be captured in a CUDA graph ({e}); launching it eagerly")
+            torch.cuda.synchronize()
+            self.graphs = None
         restore()                                  # capture does not execute, but keep the invariant explicit
 
     @torch.no_grad()
