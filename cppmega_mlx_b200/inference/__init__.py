@@ -3,6 +3,7 @@ from .generation import (GenerationChunk, build_prompt_cache, generate_from_prom
                          generate_tokens_with_kv_cache, next_token_logits, stream_generate_tokens)
 from .graph_decode import GraphDecodeSession
 from .static_cache import StaticDecodeCache
+from .serving_engine import ServingEngine, ServingRequest
 from .infilling import build_infilling_prompt, splice_infill
 from .sampling import apply_top_k, apply_top_p, sample_next_token
 from .serving import (ContinuousBatchScheduler, PagedKVBlockManager, build_paged_block_table, paged_decode_attention,

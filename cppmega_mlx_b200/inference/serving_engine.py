@@ -1,0 +1,255 @@
+"""Continuous batching on the static decode cache: requests join and leave a fixed set of batch slots between decode steps.
+
+The reference's serving layer ends at the scheduler: ``ContinuousBatchScheduler`` decides who runs and
+``PagedKVBlockManager`` accounts for blocks, but nothing drives the model from them
+(``cppmega_mlx/inference/serving.py:265-489`` scheduler, ``:522`` "paged attention not wired").  ``ServingEngine`` is that
+missing driver.  It owns ``max_batch`` slots of a ``StaticDecodeCache`` (per-slot device-side positions) and two fixed sets of
+recurrent state; a waiting request is prefilled on the ordinary growing-cache path and its cache rows, recurrent state and
+position are copied into a free slot; every ``step()`` then runs ONE one-token decode step for all slots — the same captured
+CUDA graph whatever the mix of requests, because slot contents change but tensor addresses do not — samples a token per
+active slot and retires the requests that hit EOS, their token budget or the cache capacity.  Admission order and preemption
+policy come from a ``ContinuousBatchScheduler`` when one is given (its block manager then bounds the admitted tokens);
+otherwise requests are admitted first-come first-served.
+
+Idle slots run along (their rows are never read and never advance), which is the price of a fixed launch shape.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..models.hybrid_lm import HybridDecodeState
+from .engine import DecodeSession
+from .graph_decode import _state_tensors
+from .sampling import sample_next_token
+from .static_cache import StaticDecodeCache
+
+
+@dataclass
+class ServingRequest:
+    request_id: int
+    prompt: torch.Tensor                     # [S] token ids
+    max_new_tokens: int
+    temperature: float = 0.0
+    top_k: int | None = None
+    top_p: float | None = None
+    priority: int = 0
+    generated: list[int] = field(default_factory=list)
+    slot: int | None = None
+    finished: bool = False
+    finish_reason: str | None = None
+
+
+class ServingEngine:
+    def __init__(self, model, *, max_batch: int, capacity: int, eos_token_id: int | None = None, use_graph: bool | None = None,
+                 scheduler=None, seed: int = 0):
+        self.model = model
+        self.max_batch, self.capacity, self.eos = max_batch, capacity, eos_token_id
+        self.use_graph = use_graph
+        self.scheduler = scheduler
+        if scheduler is not None and scheduler.max_batch_size > max_batch:
+            raise ValueError("the scheduler's max_batch_size must not exceed the engine's slot count")
+        self._finished_now: list[int] = []
+        self.device = next(model.parameters()).device
+        self.cache: StaticDecodeCache | None = None
+        self.states: list[HybridDecodeState] = []
+        self.graphs = None
+        self._parity = 0
+        self._tok = torch.zeros(max_batch, 1, dtype=torch.long, device=self.device)
+        self._logits: torch.Tensor | None = None
+        self.slots: list[ServingRequest | None] = [None] * max_batch
+        self.waiting: list[ServingRequest] = []
+        self.requests: dict[int, ServingRequest] = {}
+        self._next_id = 0
+        self._gen = torch.Generator(device=self.device).manual_seed(seed)
+        self.steps = 0
+
+    # ------------------------------------------------------------------------------------------ requests
+    def submit(self, prompt, max_new_tokens: int, *, temperature: float = 0.0, top_k: int | None = None, top_p: float | None = None,
+               priority: int = 0) -> int:
+        """Queue a request; returns its id.  ``run()`` / ``step()`` do the work."""
+        prompt = torch.as_tensor(prompt, dtype=torch.long, device=self.device).reshape(-1)
+        if prompt.numel() == 0 or prompt.numel() >= self.capacity:
+            raise ValueError(f"prompt length must be in [1, {self.capacity - 1}]")
+        if max_new_tokens < 1:
+            raise ValueError("max_new_tokens must be positive")
+        rid = self._next_id
+        self._next_id += 1
+        req = ServingRequest(rid, prompt, max_new_tokens, temperature, top_k, top_p, priority)
+        self.requests[rid] = req
+        self.waiting.append(req)
+        if self.scheduler is not None:
+            self.scheduler.add_request(rid, int(prompt.numel()), max_new_tokens, priority=priority)
+        return rid
+
+    @property
+    def num_active(self) -> int:
+        return sum(r is not None for r in self.slots)
+
+    def idle(self) -> bool:
+        return not self.waiting and self.num_active == 0
+
+    # ------------------------------------------------------------------------------------------ admission
+    @torch.no_grad()
+    def _admit(self, req: ServingRequest, slot: int) -> None:
+        """Prefill on the growing-cache path, then move cache rows, recurrent state and position into ``slot``."""
+        sess = DecodeSession(self.model)
+        history = req.prompt if not req.generated else torch.cat([req.prompt, torch.tensor(req.generated, device=self.device)])
+        logits = sess.forward(history[None], last_only=True)[:, 0]   # a preempted request recomputes what it had generated
+        n = sess.tokens_seen
+        if self.cache is None:
+            self.cache = StaticDecodeCache(sess.kv.num_layers, self.max_batch, self.capacity, self.device)
+            self.cache.active.zero_()
+            self._logits = torch.zeros(self.max_batch, logits.shape[-1], dtype=logits.dtype, device=self.device)
+        self.cache.load_slot(slot, sess.kv, n)
+        if not self.states:       # fixed recurrent-state storage for all slots, shaped after the first request's
+            first = HybridDecodeState()
+            for name in ("mamba", "m2rnn"):
+                for key, obj in getattr(sess.state, name).items():
+                    clone = type(obj)(**{k: (torch.zeros((self.max_batch, *v.shape[1:]), dtype=v.dtype, device=v.device)
+                                             if isinstance(v, torch.Tensor) else v) for k, v in vars(obj).items()})
+                    getattr(first, name)[key] = clone
+            self.states = [first, first.clone()]
+        for st in self.states:
+            for name in ("mamba", "m2rnn"):
+                for key, obj in getattr(sess.state, name).items():
+                    fixed = getattr(st, name)[key]
+                    for k, v in vars(obj).items():
+                        if isinstance(v, torch.Tensor):
+                            getattr(fixed, k)[slot] = v[0]
+        self.cache.active[slot] = 1
+        req.slot = slot
+        self.slots[slot] = req
+        self.waiting.remove(req)
+        tok = self._sample(logits, req)
+        self._emit(req, int(tok))
+        self._tok[slot, 0] = tok
+
+    def _sample(self, logits_row: torch.Tensor, req: ServingRequest) -> torch.Tensor:
+        return sample_next_token(logits_row.reshape(1, -1), temperature=req.temperature, top_k=req.top_k, top_p=req.top_p,
+                                 generator=self._gen).reshape(())
+
+    def _emit(self, req: ServingRequest, token: int) -> None:
+        req.generated.append(token)
+        total = int(req.prompt.numel()) + len(req.generated)
+        if self.eos is not None and token == self.eos:
+            self._retire(req, "eos")
+        elif len(req.generated) >= req.max_new_tokens:
+            self._retire(req, "length")
+        elif total >= self.capacity:
+            self._retire(req, "capacity")
+
+    def _retire(self, req: ServingRequest, reason: str) -> None:
+        req.finished, req.finish_reason = True, reason
+        self._finished_now.append(req.request_id)
+        self._release(req)
+
+    def _release(self, req: ServingRequest) -> None:
+        if req.slot is not None:
+            self.cache.active[req.slot] = 0
+            self.slots[req.slot] = None
+            req.slot = None
+
+    def _preempt(self, req: ServingRequest) -> None:
+        """The scheduler took this request's blocks away: drop its slot; it is prefilled again (prompt + tokens so far) later."""
+        self._release(req)
+        if req not in self.waiting:
+            self.waiting.insert(0, req)
+
+    # ------------------------------------------------------------------------------------------ the shared decode step
+    def _step_body(self, parity: int) -> None:
+        src, dst = self.states[parity], self.states[1 - parity]
+        work = HybridDecodeState()
+        work.mamba, work.m2rnn, work.mamba_out = dict(src.mamba), dict(src.m2rnn), dst.mamba
+        h = self.model.decoder_hidden_states(self._tok, kv_cache=self.cache, state=work, position_offset=self.cache.pos)
+        self._logits.copy_(self.model.lm_head(h)[:, 0])
+        for dd, wd in ((dst.mamba, work.mamba), (dst.m2rnn, work.m2rnn)):
+            for key, fixed in dd.items():
+                new = wd[key]
+                if new is fixed:
+                    continue
+                for name, old in vars(fixed).items():
+                    val = getattr(new, name)
+                    if isinstance(old, torch.Tensor) and val is not old and val.data_ptr() != old.data_ptr():
+                        old.copy_(val)
+        self.cache.advance()
+
+    def _maybe_capture(self) -> None:
+        want = self.use_graph if self.use_graph is not None else self.device.type == "cuda"
+        if not want or self.graphs is not None:
+            return
+        tens = [t for st in self.states for *_, t in _state_tensors(st)] + [t for t in self.cache.a + self.cache.b if t is not None]
+        tens += [self.cache.pos, self.cache.lengths()]
+        keep = [t.clone() for t in tens]
+
+        def restore():
+            for t, k in zip(tens, keep):
+                t.copy_(k)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for parity in (0, 1):
+                self._step_body(parity)
+        torch.cuda.current_stream().wait_stream(side)
+        restore()
+        graphs, pool = [], None
+        try:
+            for parity in (0, 1):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, pool=pool):
+                    self._step_body(parity)
+                pool = g.pool()
+                graphs.append(g)
+            self.graphs = graphs
+        except RuntimeError as e:
+            import warnings
+            warnings.warn(f"decode step could not be captured in a CUDA graph ({e}); launching it eagerly")
+            torch.cuda.synchronize()
+            self.graphs = False
+        restore()
+
+    # ------------------------------------------------------------------------------------------ public loop
+    @torch.no_grad()
+    def step(self) -> list[tuple[int, int]]:
+        """One scheduling step: every running request decodes one token (one replay of the shared step for all slots), then
+        waiting requests are admitted into free slots and emit their first token from the prefill.  Returns the
+        ``(request_id, token)`` pairs emitted now."""
+        before = {rid: len(r.generated) for rid, r in self.requests.items()}
+        self._finished_now = []
+        sched = self.scheduler.schedule() if self.scheduler is not None else None
+        if sched is not None:
+            for rid in sched.preempted:
+                self._preempt(self.requests[rid])
+        if self.num_active:
+            self._maybe_capture()
+            if self.graphs:
+                self.graphs[self._parity].replay()
+            else:
+                self._step_body(self._parity)
+            self._parity ^= 1          # the step read recurrent-state set `parity` and left the next state in the other set
+            self.steps += 1
+            greedy = self._logits.argmax(-1)
+            for slot, req in enumerate(self.slots):
+                if req is None:
+                    continue
+                tok = greedy[slot] if req.temperature == 0 else self._sample(self._logits[slot], req)
+                self._tok[slot, 0] = tok
+                self._emit(req, int(tok))
+        order = list(self.waiting) if sched is None else [self.requests[rid] for rid in sched.prefill]
+        for req in order:
+            free = next((i for i, r in enumerate(self.slots) if r is None), None)
+            if free is None:
+                break
+            self._admit(req, free)
+        if sched is not None:
+            self.scheduler.complete_step(sched, finished_ids=self._finished_now)
+        return [(rid, t) for rid, r in self.requests.items() for t in r.generated[before.get(rid, 0):]]
+
+    def run(self, max_steps: int = 1_000_000) -> dict[int, list[int]]:
+        """Step until every submitted request has finished; returns the generated tokens per request id."""
+        for _ in range(max_steps):
+            if self.idle():
+                break
+            self.step()
+        return {rid: list(r.generated) for rid, r in self.requests.items()}

@@ -1,10 +1,12 @@
 """Fixed-capacity decode cache whose write position lives on the device.
 
 ``HybridKVCache`` grows its buffers and keeps positions as Python integers, so every decode step launches kernels with new
-arguments.  ``StaticDecodeCache`` holds ``[B, capacity, …]`` buffers per attention layer and a single device-side position;
-a one-token step writes row ``pos`` with ``index_copy_`` and attends over ``lengths = pos + 1`` keys, so the *same* kernel
-arguments serve every step and the whole step can be captured once in a CUDA graph and replayed
-(``inference/graph_decode.py``).  The reference has no counterpart: its caches are the growing kind
+arguments.  ``StaticDecodeCache`` holds ``[B, capacity, …]`` buffers per attention layer and one device-side position *per
+sequence*; a one-token step writes row ``pos[b]`` of sequence ``b`` and attends over ``lengths = pos + 1`` keys, so the *same*
+kernel arguments serve every step and the whole step can be captured once in a CUDA graph and replayed
+(``inference/graph_decode.py``).  Because the positions are per sequence, the rows of one batch may be at different points of
+different requests (``inference/serving_engine.py`` admits and retires requests slot by slot between replays); ``active``
+marks which rows advance.  The reference has no counterpart: its caches are the growing kind
 (``cppmega_mlx/inference/engine.py:52-138``) and its step is traced by ``mx.compile``.
 """
 from __future__ import annotations
@@ -17,7 +19,9 @@ class StaticDecodeCache:
 
     def __init__(self, num_layers: int, batch: int, capacity: int, device):
         self.num_layers, self.batch, self.capacity = num_layers, batch, capacity
-        self.pos = torch.zeros(1, dtype=torch.int64, device=device)      # next row to write == tokens stored so far
+        self.pos = torch.zeros(batch, dtype=torch.int64, device=device)   # per sequence: next row to write == tokens stored
+        self.active = torch.ones(batch, dtype=torch.int64, device=device)  # 1 = this row advances at the end of a step
+        self._rows = torch.arange(batch, device=device)
         self._len32 = torch.ones(batch, dtype=torch.int32, device=device)   # pos + 1 per sequence, kept in step with pos
         self._rope: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}      # per-step memo of rope rows at ``pos``
         self.a: list[torch.Tensor | None] = [None] * num_layers           # keys or the MLA latent
@@ -36,7 +40,8 @@ class StaticDecodeCache:
         return self._len32
 
     def rope(self, rot_dim: int, theta: float, scaling=None) -> tuple[torch.Tensor, torch.Tensor]:
-        """cos/sin rows [1, rot_dim/2] at the current position, computed once per step however many layers ask."""
+        """cos/sin rows [B, rot_dim/2] at each sequence's position, computed once per step however many layers ask. The layers
+        apply them by treating the batch as the sequence axis of a single row (a one-token step has nothing else there)."""
         from ..ops.rope import rope_tables_at
         key = (rot_dim, theta, scaling)
         hit = self._rope.get(key)
@@ -55,20 +60,39 @@ class StaticDecodeCache:
     def write_a(self, layer_idx: int, x: torch.Tensor) -> torch.Tensor:
         """Store ``x`` [B,1,…] at the current position; returns the whole ``[B, capacity, …]`` buffer."""
         buf = self._buf(self.a, layer_idx, x)
-        buf.index_copy_(1, self.pos, x.to(buf.dtype))
+        buf[self._rows, self.pos] = x[:, 0].to(buf.dtype)
         return buf
 
     def write_b(self, layer_idx: int, x: torch.Tensor) -> torch.Tensor:
         buf = self._buf(self.b, layer_idx, x)
-        buf.index_copy_(1, self.pos, x.to(buf.dtype))
+        buf[self._rows, self.pos] = x[:, 0].to(buf.dtype)
         return buf
 
     def advance(self, n: int = 1) -> None:
-        self.pos += n
-        self._len32 += n
+        self.pos += self.active * n
+        self._len32 += (self.active * n).to(torch.int32)
         self._rope.clear()
 
     # -- hand-over from a prefill done with the growing cache -----------------------------------
+    def load_slot(self, slot: int, kv, tokens_seen: int) -> None:
+        """Put a single-sequence ``HybridKVCache`` (after its prefill) into row ``slot`` and set that row's position."""
+        n = tokens_seen
+        if n >= self.capacity:
+            raise ValueError(f"prefill of {n} tokens leaves no room in a static cache of {self.capacity}")
+        for i in range(self.num_layers):
+            src_a = kv.a[i].fetch(n)
+            if self.a[i] is None:
+                self.a[i] = torch.zeros((self.batch, self.capacity, *src_a.shape[2:]), dtype=src_a.dtype, device=src_a.device)
+            self.a[i][slot, :n] = src_a[0]
+            if kv.has_b[i]:
+                src_b = kv.b[i].fetch(n)
+                if self.b[i] is None:
+                    self.b[i] = torch.zeros((self.batch, self.capacity, *src_b.shape[2:]), dtype=src_b.dtype, device=src_b.device)
+                self.b[i][slot, :n] = src_b[0]
+        self.pos[slot] = n
+        self._len32[slot] = n + 1
+        self._rope.clear()
+
     def load_from(self, kv, tokens_seen: int | None = None) -> None:
         """Copy the contents of a ``HybridKVCache`` (after prefill) and take over its position (``tokens_seen`` when the
         model has no attention layer to read it from)."""

@@ -443,12 +443,18 @@ class HybridTinyLM(nn.Module):
         h = self.token_embedding(input_ids)
         if self.position_embedding is not None:
             if isinstance(position_offset, torch.Tensor):     # device-side position (static decode cache): no host read
-                pos = position_offset.reshape(-1)[:1] + torch.arange(s, device=input_ids.device)
+                po = position_offset.reshape(-1)
+                if po.numel() == b and s == 1:                # one position per sequence (ragged decode batch)
+                    h = h + self.position_embedding(po)[:, None]
+                    pos = None
+                else:
+                    pos = po[:1] + torch.arange(s, device=input_ids.device)
             else:
                 if position_offset + s > cfg.max_seq_length:
                     raise ValueError(f"sequence length {position_offset + s} exceeds max_seq_length {cfg.max_seq_length}")
                 pos = torch.arange(position_offset, position_offset + s, device=input_ids.device)
-            h = h + self.position_embedding(pos)[None]
+            if pos is not None:
+                h = h + self.position_embedding(pos)[None]
         if self.ngram_hash_embedding is not None:
             h = h + self.ngram_hash_embedding(input_ids).to(h.dtype)
         side = (structure_ids, dep_levels, ast_depth_ids, sibling_index_ids, node_type_ids)

@@ -234,23 +234,25 @@ class CausalSelfAttention(nn.Module):
         from ..ops import decode_attention as DA
         c = self.config
         b = x.shape[0]
-        cos, sin = cache.rope(c.q_head_dim, c.rope_theta, c.rope_scaling())
+        cos, sin = cache.rope(c.q_head_dim, c.rope_theta, c.rope_scaling())    # [B, D/2]: one row per sequence
+        xt = x.transpose(0, 1)                                                 # [1, B, d]: the batch plays the sequence axis
         rope = (lambda t: ops.apply_rope(t, cos, sin)) if c.use_rope else (lambda t: t)
-        q = rope(self.q_proj(x).view(b, 1, c.num_q_heads, c.q_head_dim))[:, 0]
+        q = rope(self.q_proj(xt).view(1, b, c.num_q_heads, c.q_head_dim))[0]   # [B, H, D]
         lengths = cache.lengths()
         scale = c.q_head_dim ** -0.5
         if c.mode == "dsa":   # shared key/value rows; the newest ``sparse_topk`` causal keys
-            rows = cache.write_a(layer_idx, rope(self.sparse_kv_proj(x).view(b, 1, c.kv_heads, c.q_head_dim)).reshape(b, 1, -1))
+            new = rope(self.sparse_kv_proj(xt).view(1, b, c.kv_heads, c.q_head_dim))
+            rows = cache.write_a(layer_idx, new.reshape(b, 1, -1))
             rows = rows.view(b, cache.capacity, c.kv_heads, c.q_head_dim)      # stored flat, like the growing cache
             k = min(c.sparse_topk, cache.capacity)
-            idx = cache.pos.to(torch.int32) - torch.arange(k, device=x.device, dtype=torch.int32)
-            idx = torch.where(idx >= 0, idx, torch.full_like(idx, -1))[None].expand(b, k).contiguous()
+            idx = cache.pos.to(torch.int32)[:, None] - torch.arange(k, device=x.device, dtype=torch.int32)[None, :]
+            idx = torch.where(idx >= 0, idx, torch.full_like(idx, -1)).contiguous()
             out = DA.decode_attention(q, rows, None, None, lengths, scale=scale, topk=idx, d_v=c.q_head_dim, max_keys=k)
         else:
             if c.sliding_window is not None:
                 raise ValueError("sliding-window attention has no static decode path")
-            kk = cache.write_a(layer_idx, rope(self.k_proj(x).view(b, 1, c.kv_heads, c.q_head_dim)))
-            vv = cache.write_b(layer_idx, self.v_proj(x).view(b, 1, c.kv_heads, c.q_head_dim))
+            kk = cache.write_a(layer_idx, rope(self.k_proj(xt).view(1, b, c.kv_heads, c.q_head_dim)).transpose(0, 1))
+            vv = cache.write_b(layer_idx, self.v_proj(xt).view(b, 1, c.kv_heads, c.q_head_dim))
             out = DA.decode_attention(q, kk, vv, None, lengths, scale=scale, max_keys=cache.capacity)
         return self.out_proj(out.reshape(b, 1, c.q_proj_dim))
 

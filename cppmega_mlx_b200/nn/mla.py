@@ -206,16 +206,18 @@ class MLAAttention(nn.Module):
         from ..ops import decode_attention as DA
         c = self.config
         b = x.shape[0]
-        freqs = cache.rope(c.qk_rope_head_dim, c.rope_theta)
-        qr, q, c_kv, k_pe, _ = self._project(x, 0, freqs)
-        rows = cache.write_a(layer_idx, torch.cat([c_kv, k_pe], dim=-1))          # [B, capacity, 576]
+        freqs = cache.rope(c.qk_rope_head_dim, c.rope_theta)               # [B, rope/2]: one row per sequence
+        xt = x.transpose(0, 1)                                             # [1, B, d]: the batch plays the sequence axis
+        qr, q, c_kv, k_pe, _ = self._project(xt, 0, freqs)
+        q = q.transpose(0, 1)                                              # [B, 1, H, D]
+        rows = cache.write_a(layer_idx, torch.cat([c_kv, k_pe], dim=-1).transpose(0, 1))   # [B, capacity, 576]
         lengths = cache.lengths()
         use_sparse = (self.indexer is not None) if sparse is None else (sparse and self.indexer is not None)
         topk = None
         if use_sparse and cache.capacity > c.index_topk:
-            iq, ik, iw = self.indexer.project(x, qr, *freqs)
-            keys = cache.write_b(layer_idx, ik)
-            sc = self.indexer.scores(iq, keys, iw).reshape(b, cache.capacity)
+            iq, ik, iw = self.indexer.project(xt, qr, *freqs)
+            keys = cache.write_b(layer_idx, ik.transpose(0, 1))
+            sc = self.indexer.scores(iq.transpose(0, 1), keys, iw.transpose(0, 1)).reshape(b, cache.capacity)
             topk = ops.topk_select(sc, c.index_topk, None, lengths)               # −1 padded while fewer keys exist
         out_lat = DA.decode_attention(self._latent_query(q)[:, 0], rows[:, :, None, :], None, None, lengths,
                                       scale=c.qk_head_dim ** -0.5, d_v=c.kv_lora_rank, topk=topk,

@@ -263,7 +263,7 @@ def test_static_cache_steps_equal_growing_cache_steps(pattern, kw):
         got = [g.prefill(ids[:, :9]).clone()] + [g.step(ids[:, i]).clone() for i in range(9, 15)]
     for a, b in zip(got, want):
         assert torch.allclose(a, b, atol=2e-5)
-    assert int(g.cache.pos) == 15 and g.tokens_seen == 15
+    assert g.cache.pos.tolist() == [15, 15] and g.tokens_seen == 15
     with pytest.raises(ValueError):
         I.GraphDecodeSession(m, capacity=8).prefill(ids[:, :9])
     out = I.GraphDecodeSession(m, capacity=32, use_graph=False).generate(ids[:, :9], 4)
@@ -282,3 +282,45 @@ def test_graph_session_sampling_and_eos():
     eos = int(greedy[0, 10])
     c = I.GraphDecodeSession(m, capacity=64, use_graph=False).generate(ids, 6, eos_token_id=eos)
     assert torch.equal(c[0, :11], greedy[0, :11]) and bool((c[0, 11:] == eos).all())
+
+
+@pytest.mark.parametrize("pattern,kw", [("AM", {"mla_low_rank": True, "dsa_a_layer_ranks": (0,)}), ("AER", {})])
+def test_serving_engine_continuous_batching_matches_single_request_generation(pattern, kw):
+    """Requests of different lengths join and leave two slots at different times; each gets exactly the tokens it would get
+    alone (per-slot positions, recurrent state and cache rows never leak between requests)."""
+    m = _model(pattern, **kw)
+    torch.manual_seed(5)
+    prompts = [torch.randint(4, 100, (n,)) for n in (5, 11, 3, 8, 6)]
+    budgets = [6, 3, 7, 2, 5]
+    eng = I.ServingEngine(m, max_batch=2, capacity=32, use_graph=False)
+    ids = [eng.submit(p, b) for p, b in zip(prompts, budgets)]
+    out = eng.run()
+    assert eng.idle() and all(eng.requests[i].finish_reason == "length" for i in ids)
+    for i, p, b in zip(ids, prompts, budgets):
+        want = I.generate_tokens_with_kv_cache(m, p[None], max_new_tokens=b)[0, p.numel():].tolist()
+        assert out[i] == want
+    assert eng.steps < sum(budgets)                  # slots really were shared
+
+
+def test_serving_engine_with_scheduler_preemption_and_eos():
+    from cppmega_mlx_b200.inference.serving import ContinuousBatchScheduler, PagedKVBlockManager
+    m = _model("AM")
+    torch.manual_seed(6)
+    prompts = [torch.randint(4, 100, (n,)) for n in (6, 7, 5)]
+    alone = [I.generate_tokens_with_kv_cache(m, p[None], max_new_tokens=8)[0, p.numel():].tolist() for p in prompts]
+    # 5 blocks of 4 tokens: not enough for all three to grow, so the scheduler must preempt and the engine must recompute
+    mgr = PagedKVBlockManager(num_blocks=7, num_layers=1, block_size=4, kv_heads=1, head_dim=4)
+    sch = ContinuousBatchScheduler(mgr, max_batch_size=3)
+    eng = I.ServingEngine(m, max_batch=3, capacity=32, use_graph=False, scheduler=sch)
+    ids = [eng.submit(p, 8, priority=pr) for p, pr in zip(prompts, (2, 1, 0))]
+    out = eng.run(max_steps=200)
+    assert eng.idle() and sch.idle()
+    assert sum(sch.requests[i].preemptions for i in ids) >= 1
+    for i, w in zip(ids, alone):
+        assert out[i] == w
+    # EOS retires a request early
+    eos = alone[0][2]
+    eng2 = I.ServingEngine(m, max_batch=2, capacity=32, use_graph=False, eos_token_id=eos)
+    r = eng2.submit(prompts[0], 8)
+    got = eng2.run()[r]
+    assert got == alone[0][:alone[0].index(eos) + 1] and eng2.requests[r].finish_reason == "eos"
