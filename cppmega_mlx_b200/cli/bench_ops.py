@@ -347,9 +347,45 @@ def bench_decode_loop(args) -> list[dict]:
     return rows
 
 
+def bench_serving(args) -> list[dict]:
+    """Continuous batching with the 1B hybrid: 64 requests (prompts of 64-1024 tokens, 64 new tokens each) through a
+    ``ServingEngine`` with 32 slots; wall-clock end to end (prefills included) and decode-step rate."""
+    import time
+
+    from cppmega_mlx_b200 import inference as I
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.recipes.model_factory import get_model_profile
+    torch.manual_seed(0)
+    model = get_model_profile("hybrid_1b").build_model(dtype=torch.bfloat16, device="cuda").eval()
+    g = torch.Generator().manual_seed(1)
+    lens = torch.randint(64, 1025, (64,), generator=g).tolist()
+    prompts = [torch.randint(4, 60000, (n,), generator=g) for n in lens]
+    rows = []
+    for slots in (8, 32):
+        eng = I.ServingEngine(model, max_batch=slots, capacity=1024 + 64 + 16)
+        warm = eng.submit(prompts[0], 4)          # first admission allocates the cache and captures the step
+        eng.run()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        ids = [eng.submit(p, 64) for p in prompts]
+        steps0 = eng.steps
+        out = eng.run()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        new = sum(len(out[i]) for i in ids)
+        row = {"op": f"serving engine hybrid_1b, 64 requests, {slots} slots", "seconds": dt, "generated_tokens": new,
+               "tokens_per_s_end_to_end": new / dt, "prompt_tokens": sum(lens), "decode_steps": eng.steps - steps0,
+               "graph": bool(eng.graphs)}
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+        del eng
+    B.check_status()
+    return rows
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "decode", "decode_loop", "all"])
+    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "decode", "decode_loop", "serving", "all"])
     ap.add_argument("--json", default=None)
     ap.add_argument("--only", default=None, help="run the single case with this label (small captures under a profiler)")
     ap.add_argument("--iters", type=int, default=10)
@@ -372,6 +408,8 @@ def main(argv=None) -> int:
         rows += bench_decode(args)
     if args.op in ("decode_loop", "all"):
         rows += bench_decode_loop(args)
+    if args.op in ("serving", "all"):
+        rows += bench_serving(args)
     if args.json:
         with open(args.json, "w") as f:
             json.dump(rows, f, indent=1)
