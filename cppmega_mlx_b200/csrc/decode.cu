@@ -138,7 +138,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
   const long long ws_row = (static_cast<long long>(b) * p.H + h0) * p.splits + split;   // + h * splits
 
   if (T == 0) {  // nothing to attend to in this split: neutral partial
-    for (int i = threadIdx.x; i < nh * DV; i += DEC_THREADS) {
+    for (int i = threadIdx.x; i < nh * DV; i += blockDim.x) {
       const int h = i / DV, d = i % DV;
       p.ws_o[(ws_row + static_cast<long long>(h) * p.splits) * DV + d] = 0.f;
     }
@@ -169,7 +169,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     tmem_relinquish();
   }
   // Q → shared memory, K-major 128B-swizzled blocks of [16 rows × 64 cols]; rows past `nh` are zero.
-  for (int i = threadIdx.x; i < DKB * DEC_N * 8; i += DEC_THREADS) {
+  for (int i = threadIdx.x; i < DKB * DEC_N * 8; i += blockDim.x) {
     const int c = i & 7, h = (i >> 3) % DEC_N, kb = i / (8 * DEC_N);
     uint4 val = make_uint4(0, 0, 0, 0);
     if (h < nh)
@@ -557,7 +557,8 @@ int launch_decode(cmb::DecodeParams& p, long long ext2, long long ext3, cudaStre
   const int g = p.H / p.kv_heads;
   const int gchunks = (g + cmb::DEC_N - 1) / cmb::DEC_N;
   dim3 grid(p.splits, p.B, p.kv_heads * gchunks);
-  kern<<<grid, cmb::DEC_THREADS, Cfg::SMEM_BYTES, stream>>>(tmK, tmV, p);
+  // The second pair of gather warps only exists in per-row mode; without it two CTAs of the small variants fit an SM's registers.
+  kern<<<grid, p.tma ? 256 : cmb::DEC_THREADS, Cfg::SMEM_BYTES, stream>>>(tmK, tmV, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
