@@ -230,12 +230,16 @@ class ServingEngine:
             self._parity ^= 1          # the step read recurrent-state set `parity` and left the next state in the other set
             self.steps += 1
             greedy = self._logits.argmax(-1)
+            self._tok.copy_(greedy[:, None])              # next input of every slot, on the device
+            host = greedy.tolist()                        # one device→host read per step for all slots
             for slot, req in enumerate(self.slots):
                 if req is None:
                     continue
-                tok = greedy[slot] if req.temperature == 0 else self._sample(self._logits[slot], req)
-                self._tok[slot, 0] = tok
-                self._emit(req, int(tok))
+                if req.temperature != 0:
+                    tok = self._sample(self._logits[slot], req)
+                    self._tok[slot, 0] = tok
+                    host[slot] = int(tok)
+                self._emit(req, host[slot])
         order = list(self.waiting) if sched is None else [self.requests[rid] for rid in sched.prefill]
         for req in order:
             free = next((i for i, r in enumerate(self.slots) if r is None), None)
