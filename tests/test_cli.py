@@ -64,3 +64,55 @@ def test_resume_through_cli_equals_uninterrupted(shard, tmp_path, opt):
     a = [m["loss"] for m in full["metrics"]]
     b = [m["loss"] for m in first["metrics"]] + [m["loss"] for m in second["metrics"]]
     assert a == b
+
+
+def _run_main(mod, argv, capsys):
+    rc = mod.main(argv)
+    out = capsys.readouterr().out.strip().splitlines()
+    return rc, out
+
+
+def test_check_environment_and_data_smoke_and_audit(capsys, tmp_path):
+    import json
+
+    import numpy as np
+
+    from cppmega_mlx_b200.cli import audit_memory, check_environment, data_smoke
+    rc, out = _run_main(check_environment, ["--json"], capsys)
+    rep = json.loads("\n".join(out))
+    assert rc == 0 and rep["distributed_backends"]["gloo"] and "kernel_library" in rep and "environment" in rep
+    rc, out = _run_main(data_smoke, ["--synthetic", "--seq-len", "16", "--batch-size", "3"], capsys)
+    rep = json.loads(out[-1])
+    assert rc == 0 and rep["status"] == "ok" and rep["batches"][0]["inputs"] == [3, 16] and rep["cursor_after"]["global"] == 2
+    bad = tmp_path / "bad.npz"
+    np.savez(bad, tokens=np.arange(400, dtype=np.int32))
+    rc, out = _run_main(data_smoke, [str(bad), "--seq-len", "16", "--vocab-size", "100"], capsys)
+    assert rc == 2 and json.loads(out[-1])["ids_within_vocab"] is False           # ids beyond the vocabulary fail closed
+    rc, out = _run_main(audit_memory, ["--profile", "hybrid_1b", "--dp", "8"], capsys)
+    rep = json.loads(out[-1])
+    assert rc == 0 and rep["parameters"] == 1756904002 and 0 < rep["zero1"]["fraction_of_b200_hbm"] < 1
+
+
+def test_train_tiny_npz_and_optimizer_receipts(capsys, tmp_path):
+    import json
+
+    from cppmega_mlx_b200.cli import bench_optimizers, train_tiny_npz
+    rc, out = _run_main(train_tiny_npz, ["--steps", "25", "--json"], capsys)
+    rep = json.loads(out[-1])
+    assert rc == 0 and rep["status"] == "ok" and rep["last_loss"] < rep["first_loss"] - 0.5
+    rc, out = _run_main(train_tiny_npz, ["--data", str(tmp_path / "missing.npz"), "--json"], capsys)
+    assert rc == 2 and json.loads(out[-1])["status"] == "error"
+    rc, out = _run_main(bench_optimizers, ["--matrices", "2", "--rows", "64", "--cols", "128", "--steps", "2"], capsys)
+    rows = {r["optimizer"]: r for r in map(json.loads, out)}
+    assert rc == 0 and rows["adam8bit_symmetric"]["state_vs_adamw_fp32"] < 0.3 and rows["lion8bit_symmetric"]["state_vs_adamw_fp32"] < 0.15
+    assert rows["muon_quantized_momentum"]["state_bytes"] < 0.35 * rows["muon_fp32_carrier"]["state_bytes"]
+    assert rows["muon_bf16_carrier"]["max_param_drift_vs_family_fp32"] < 1e-3
+
+
+def test_zero1_loopback_receipt(capsys):
+    import json
+
+    from cppmega_mlx_b200.cli import bench_zero1_loopback
+    rc, out = _run_main(bench_zero1_loopback, ["--steps", "3", "--port", "29741"], capsys)
+    rep = json.loads(out[-1])
+    assert rc == 0 and rep["status"] == "ok" and rep["max_loss_gap"] < 1e-4 and rep["state_fraction_largest_rank"] < 0.6
