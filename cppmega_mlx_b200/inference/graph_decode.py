@@ -32,22 +32,108 @@ def _state_tensors(state: HybridDecodeState):
                     yield d, key, name, val
 
 
+class StaticStepRunner:
+    """The one-token step over fixed storage, launched eagerly or replayed from two captured graphs.
+
+    Owns nothing but references: the model, a ``StaticDecodeCache``, two sets of recurrent state (step k reads set ``parity``
+    and leaves the next state in the other), the ``[B,1]`` token buffer the step reads and the ``[B,V]`` logits buffer it writes.
+    ``GraphDecodeSession`` (one batch of sequences in lockstep) and ``ServingEngine`` (slots with turnover) both drive it."""
+
+    def __init__(self, model, cache: StaticDecodeCache, states: list[HybridDecodeState], tok: torch.Tensor, logits: torch.Tensor,
+                 *, use_graph: bool | None):
+        self.model, self.cache, self.states, self.tok, self.logits = model, cache, states, tok, logits
+        self.use_graph = use_graph
+        self.graphs: list | None = None
+        self.capture_failed = False
+        self.parity = 0
+
+    def step_body(self, parity: int) -> None:
+        """Read the recurrent state set ``parity``, leave the next state in set ``1 - parity``.  Layers that can write their
+        next state straight into given tensors do so (no copy); anything else is copied across afterwards."""
+        src, dst = self.states[parity], self.states[1 - parity]
+        work = HybridDecodeState()
+        work.mamba, work.m2rnn, work.mamba_out = dict(src.mamba), dict(src.m2rnn), dst.mamba
+        h = self.model.decoder_hidden_states(self.tok, kv_cache=self.cache, state=work, position_offset=self.cache.pos)
+        self.logits.copy_(self.model.lm_head(h)[:, 0])
+        for dd, wd in ((dst.mamba, work.mamba), (dst.m2rnn, work.m2rnn)):
+            for key, fixed in dd.items():
+                new = wd[key]
+                if new is fixed:
+                    continue
+                for name, old in vars(fixed).items():
+                    val = getattr(new, name)
+                    if isinstance(old, torch.Tensor) and val is not old and val.data_ptr() != old.data_ptr():
+                        old.copy_(val)
+        self.cache.advance()
+
+    def _mutable_tensors(self) -> list[torch.Tensor]:
+        tens = [t for st in self.states for *_, t in _state_tensors(st)] + [t for t in self.cache.a + self.cache.b if t is not None]
+        return tens + [self.cache.pos, self.cache.lengths()]
+
+    def capture(self) -> None:
+        """Warm up on a side stream (lazy allocations, library handles, function attributes), capture both parities, and put
+        every tensor the warm-up touched back.  A refused capture (a layer that reads a value on the host) leaves the eager
+        static step in place."""
+        tens = self._mutable_tensors()
+        keep = [t.clone() for t in tens]
+
+        def restore():
+            for t, k in zip(tens, keep):
+                t.copy_(k)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.no_grad():
+            for parity in (0, 1):
+                self.step_body(parity)
+        torch.cuda.current_stream().wait_stream(side)
+        restore()
+        graphs, pool = [], None
+        try:
+            for parity in (0, 1):
+                g = torch.cuda.CUDAGraph()
+                with torch.no_grad(), torch.cuda.graph(g, pool=pool):
+                    self.step_body(parity)
+                pool = g.pool()
+                graphs.append(g)
+            self.graphs = graphs
+        except RuntimeError as e:
+            import warnings
+            warnings.warn(f"decode step could not be captured in a CUDA graph ({e}); launching it eagerly")
+            torch.cuda.synchronize()
+            self.graphs, self.capture_failed = None, True
+        restore()                                  # capture does not execute, but keep the invariant explicit
+
+    def ensure_captured(self) -> None:
+        want = self.use_graph if self.use_graph is not None else self.tok.device.type == "cuda"
+        if want and self.graphs is None and not self.capture_failed:
+            self.capture()
+
+    @torch.no_grad()
+    def run(self) -> None:
+        """One step: the token buffer is consumed, the logits buffer holds the result, positions and states have advanced."""
+        if self.graphs is not None:
+            self.graphs[self.parity].replay()
+        else:
+            self.step_body(self.parity)
+        self.parity ^= 1
+
+
 class GraphDecodeSession:
     def __init__(self, model, *, capacity: int, use_graph: bool | None = None):
         self.model = model
         self.capacity = capacity
-        self.cache: StaticDecodeCache | None = None
-        self.states: list[HybridDecodeState] = []     # two fixed sets of recurrent state; step k reads [k % 2], writes [(k+1) % 2]
-        self.graphs: list | None = None
         self.use_graph = use_graph
-        self._tok = self._logits = None
-        self._parity = 0
+        self.runner: StaticStepRunner | None = None
         self.tokens_seen = 0
+
+    cache = property(lambda self: None if self.runner is None else self.runner.cache)
+    states = property(lambda self: [] if self.runner is None else self.runner.states)
+    graphs = property(lambda self: None if self.runner is None else self.runner.graphs)
 
     @property
     def state(self) -> HybridDecodeState:
         """The recurrent state after the last step."""
-        return self.states[self._parity]
+        return self.runner.states[self.runner.parity]
 
     @property
     def graph(self):
@@ -64,95 +150,29 @@ class GraphDecodeSession:
         sess = DecodeSession(self.model)
         logits = sess.forward(input_ids, last_only=True)[:, 0]
         dev = input_ids.device
-        self.cache = StaticDecodeCache(sess.kv.num_layers, b, self.capacity, dev)
-        self.cache.load_from(sess.kv, sess.tokens_seen)
+        cache = StaticDecodeCache(sess.kv.num_layers, b, self.capacity, dev)
+        cache.load_from(sess.kv, sess.tokens_seen)
         first = sess.state.clone()                # fixed storage from here on: replays only ever write into these tensors
         for d, key, name, val in list(_state_tensors(first)):
             if not val.is_contiguous():
                 setattr(d[key], name, val.contiguous())
-        self.states = [first, first.clone()]
-        self._parity = 0
-        self._tok = torch.zeros(b, 1, dtype=torch.long, device=dev)
-        self._logits = torch.zeros_like(logits)
+        self.runner = StaticStepRunner(self.model, cache, [first, first.clone()], torch.zeros(b, 1, dtype=torch.long, device=dev),
+                                       torch.zeros_like(logits), use_graph=self.use_graph)
         self.tokens_seen = n
-        self.graphs = None
-        graph = self.use_graph if self.use_graph is not None else dev.type == "cuda"
-        if graph:
-            self._capture()
+        self.runner.ensure_captured()
         return logits
-
-    # ------------------------------------------------------------------------------------------ one step
-    def _step_body(self, parity: int) -> None:
-        """Read the recurrent state set ``parity``, leave the next state in set ``1 - parity``.  Layers that can write their
-        next state straight into given tensors do so (no copy); anything else is copied across afterwards."""
-        src, dst = self.states[parity], self.states[1 - parity]
-        work = HybridDecodeState()
-        work.mamba, work.m2rnn, work.mamba_out = dict(src.mamba), dict(src.m2rnn), dst.mamba
-        h = self.model.decoder_hidden_states(self._tok, kv_cache=self.cache, state=work, position_offset=self.cache.pos)
-        self._logits.copy_(self.model.lm_head(h)[:, 0])
-        for dd, wd in ((dst.mamba, work.mamba), (dst.m2rnn, work.m2rnn)):
-            for key, fixed in dd.items():
-                new = wd[key]
-                if new is fixed:
-                    continue
-                for name, old in vars(fixed).items():
-                    val = getattr(new, name)
-                    if isinstance(old, torch.Tensor) and val is not old and val.data_ptr() != old.data_ptr():
-                        old.copy_(val)
-        self.cache.advance()
-
-    def _snapshot(self):
-        tens = [t for st in self.states for *_, t in _state_tensors(st)] + [t for t in self.cache.a + self.cache.b if t is not None]
-        tens.append(self.cache.lengths())
-        return tens, [t.clone() for t in tens], self.cache.pos.clone()
-
-    def _capture(self) -> None:
-        # Warm up on a side stream (lazy allocations, cuBLAS handles, function attributes), restoring everything afterwards.
-        tens, keep, keep_pos = self._snapshot()
-
-        def restore():
-            self.cache.pos.copy_(keep_pos)
-            for t, k in zip(tens, keep):
-                t.copy_(k)
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side), torch.no_grad():
-            for parity in (0, 1):
-                self._step_body(parity)
-        torch.cuda.current_stream().wait_stream(side)
-        restore()
-        graphs = []
-        pool = None
-        try:
-            for parity in (0, 1):
-                g = torch.cuda.CUDAGraph()
-                with torch.no_grad(), torch.cuda.graph(g, pool=pool):
-                    self._step_body(parity)
-                pool = g.pool()
-                graphs.append(g)
-            self.graphs = graphs
-        except RuntimeError as e:   # a layer that reads a value on the host cannot be captured: keep the eager static step
-            import warnings
-            warnings.warn(f"decode step could not be captured in a CUDA graph ({e}); launching it eagerly")
-            torch.cuda.synchronize()
-            self.graphs = None
-        restore()                                  # capture does not execute, but keep the invariant explicit
 
     @torch.no_grad()
     def step(self, token_ids: torch.Tensor) -> torch.Tensor:
         """Feed one token per sequence ([B] or [B,1]); returns logits [B, V] (a view of a fixed buffer: copy to keep)."""
-        if self.cache is None:
+        if self.runner is None:
             raise RuntimeError("call prefill() first")
         if self.tokens_seen >= self.capacity:
             raise RuntimeError(f"static cache capacity {self.capacity} exhausted")
-        self._tok.copy_(token_ids.reshape(-1, 1))
-        if self.graphs is not None:
-            self.graphs[self._parity].replay()
-        else:
-            self._step_body(self._parity)
-        self._parity ^= 1
+        self.runner.tok.copy_(token_ids.reshape(-1, 1))
+        self.runner.run()
         self.tokens_seen += 1
-        return self._logits
+        return self.runner.logits
 
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, max_new_tokens: int, *, temperature: float = 0.0, top_k: int | None = None,

@@ -21,7 +21,7 @@ import torch
 
 from ..models.hybrid_lm import HybridDecodeState
 from .engine import DecodeSession
-from .graph_decode import _state_tensors
+from .graph_decode import StaticStepRunner
 from .sampling import sample_next_token
 from .static_cache import StaticDecodeCache
 
@@ -52,10 +52,9 @@ class ServingEngine:
             raise ValueError("the scheduler's max_batch_size must not exceed the engine's slot count")
         self._finished_now: list[int] = []
         self.device = next(model.parameters()).device
+        self.runner: StaticStepRunner | None = None
         self.cache: StaticDecodeCache | None = None
         self.states: list[HybridDecodeState] = []
-        self.graphs = None
-        self._parity = 0
         self._tok = torch.zeros(max_batch, 1, dtype=torch.long, device=self.device)
         self._logits: torch.Tensor | None = None
         self.slots: list[ServingRequest | None] = [None] * max_batch
@@ -157,57 +156,7 @@ class ServingEngine:
         if req not in self.waiting:
             self.waiting.insert(0, req)
 
-    # ------------------------------------------------------------------------------------------ the shared decode step
-    def _step_body(self, parity: int) -> None:
-        src, dst = self.states[parity], self.states[1 - parity]
-        work = HybridDecodeState()
-        work.mamba, work.m2rnn, work.mamba_out = dict(src.mamba), dict(src.m2rnn), dst.mamba
-        h = self.model.decoder_hidden_states(self._tok, kv_cache=self.cache, state=work, position_offset=self.cache.pos)
-        self._logits.copy_(self.model.lm_head(h)[:, 0])
-        for dd, wd in ((dst.mamba, work.mamba), (dst.m2rnn, work.m2rnn)):
-            for key, fixed in dd.items():
-                new = wd[key]
-                if new is fixed:
-                    continue
-                for name, old in vars(fixed).items():
-                    val = getattr(new, name)
-                    if isinstance(old, torch.Tensor) and val is not old and val.data_ptr() != old.data_ptr():
-                        old.copy_(val)
-        self.cache.advance()
-
-    def _maybe_capture(self) -> None:
-        want = self.use_graph if self.use_graph is not None else self.device.type == "cuda"
-        if not want or self.graphs is not None:
-            return
-        tens = [t for st in self.states for *_, t in _state_tensors(st)] + [t for t in self.cache.a + self.cache.b if t is not None]
-        tens += [self.cache.pos, self.cache.lengths()]
-        keep = [t.clone() for t in tens]
-
-        def restore():
-            for t, k in zip(tens, keep):
-                t.copy_(k)
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for parity in (0, 1):
-                self._step_body(parity)
-        torch.cuda.current_stream().wait_stream(side)
-        restore()
-        graphs, pool = [], None
-        try:
-            for parity in (0, 1):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, pool=pool):
-                    self._step_body(parity)
-                pool = g.pool()
-                graphs.append(g)
-            self.graphs = graphs
-        except RuntimeError as e:
-            import warnings
-            warnings.warn(f"decode step could not be captured in a CUDA graph ({e}); launching it eagerly")
-            torch.cuda.synchronize()
-            self.graphs = False
-        restore()
+    graphs = property(lambda self: None if self.runner is None else self.runner.graphs)
 
     # ------------------------------------------------------------------------------------------ public loop
     @torch.no_grad()
@@ -222,12 +171,10 @@ class ServingEngine:
             for rid in sched.preempted:
                 self._preempt(self.requests[rid])
         if self.num_active:
-            self._maybe_capture()
-            if self.graphs:
-                self.graphs[self._parity].replay()
-            else:
-                self._step_body(self._parity)
-            self._parity ^= 1          # the step read recurrent-state set `parity` and left the next state in the other set
+            if self.runner is None:
+                self.runner = StaticStepRunner(self.model, self.cache, self.states, self._tok, self._logits, use_graph=self.use_graph)
+            self.runner.ensure_captured()
+            self.runner.run()
             self.steps += 1
             greedy = self._logits.argmax(-1)
             self._tok.copy_(greedy[:, None])              # next input of every slot, on the device
