@@ -347,6 +347,71 @@ def bench_decode_loop(args) -> list[dict]:
     return rows
 
 
+def decode_trace(args) -> list[dict]:
+    """Per-tile pipeline clock samples of CTA 0 of the decode attention kernel (latent MLA, B32, 16384 keys, 64-token pages):
+    where a 64-key tile spends its cycles.  Columns are SM clocks relative to the first sample."""
+    import ctypes
+
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops.decode_attention import decode_attention
+    lib = B.load_library()
+    dev = "cuda"
+    b, h, length, page = 32, 16, 16384, 64
+    n_pages = b * length // page
+    kpool = torch.randn(n_pages, page, 1, 576, device=dev).bfloat16()
+    table = torch.randperm(n_pages, device=dev).int().view(b, -1)
+    lengths = torch.full((b,), length, dtype=torch.int32, device=dev)
+    q = torch.randn(b, h, 576, device=dev).bfloat16()
+    run = lambda: decode_attention(q, kpool, None, table, lengths, scale=576 ** -0.5, d_v=512, max_keys=length)
+    for _ in range(3):
+        run()
+    trace = torch.zeros(64, 16, dtype=torch.int64, device=dev)
+    lib.cmb_paged_decode_set_trace(ctypes.c_void_p(trace.data_ptr()))
+    run()
+    torch.cuda.synchronize()
+    lib.cmb_paged_decode_set_trace(ctypes.c_void_p(0))
+    t = trace.cpu()
+    nz = t[t > 0]
+    t0 = int(nz.min()) if nz.numel() else 0
+    names = ["idx", "released", "issued", "landed", "mma_full", "s_free", "g1_issued", "p_ready", "g2_issued", "s_ready", "max_x",
+             "o_done", "p_written"]
+    print("tile " + " ".join(f"{n:>9}" for n in names))
+    rows = []
+    for i in range(12):
+        vals = [int(t[i, j]) - t0 if int(t[i, j]) else None for j in range(13)]
+        print(f"{i:4d} " + " ".join(f"{v:9d}" if v is not None else "        -" for v in vals))
+        rows.append({"op": "decode trace", "tile": i, **{n: v for n, v in zip(names, vals)}})
+    return rows
+
+
+def decode_profile(args) -> list[dict]:
+    """Kernel-time breakdown of one decode step of the 1B hybrid at batch 1 (torch.profiler over four eagerly launched static
+    steps; an analysis aid — the figures include profiler overhead and are not benchmark values)."""
+    from torch.profiler import ProfilerActivity, profile
+
+    from cppmega_mlx_b200 import inference as I
+    from cppmega_mlx_b200.recipes.model_factory import get_model_profile
+    torch.manual_seed(0)
+    model = get_model_profile("hybrid_1b").build_model(dtype=torch.bfloat16, device="cuda").eval()
+    ids = torch.randint(4, 60000, (1, 512), device="cuda")
+    with torch.no_grad():
+        g = I.GraphDecodeSession(model, capacity=1024, use_graph=False)
+        tok = g.prefill(ids).argmax(-1, keepdim=True)
+        for _ in range(3):
+            tok = g.step(tok).argmax(-1, keepdim=True)
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+            for _ in range(4):
+                tok = g.step(tok).argmax(-1, keepdim=True)
+            torch.cuda.synchronize()
+    ev = sorted([e for e in prof.key_averages() if e.device_time_total > 0], key=lambda e: -e.device_time_total)
+    rows = [{"op": "decode step kernel", "name": e.key[:100], "us_per_step": e.device_time_total / 4, "launches_per_step": e.count / 4}
+            for e in ev[:30]]
+    for r in rows:
+        print(json.dumps(r), flush=True)
+    return rows
+
+
 def bench_serving(args) -> list[dict]:
     """Continuous batching with the 1B hybrid: 64 requests (prompts of 64-1024 tokens, 64 new tokens each) through a
     ``ServingEngine`` with 32 slots; wall-clock end to end (prefills included) and decode-step rate."""
@@ -385,7 +450,7 @@ def bench_serving(args) -> list[dict]:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "decode", "decode_loop", "serving", "all"])
+    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "decode", "decode_loop", "serving", "decode_trace", "decode_profile", "all"])
     ap.add_argument("--json", default=None)
     ap.add_argument("--only", default=None, help="run the single case with this label (small captures under a profiler)")
     ap.add_argument("--iters", type=int, default=10)
@@ -410,6 +475,10 @@ def main(argv=None) -> int:
         rows += bench_decode_loop(args)
     if args.op in ("serving", "all"):
         rows += bench_serving(args)
+    if args.op == "decode_trace":
+        rows += decode_trace(args)
+    if args.op == "decode_profile":
+        rows += decode_profile(args)
     if args.json:
         with open(args.json, "w") as f:
             json.dump(rows, f, indent=1)
