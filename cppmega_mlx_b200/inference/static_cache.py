@@ -68,6 +68,19 @@ class StaticDecodeCache:
         buf[self._rows, self.pos] = x[:, 0].to(buf.dtype)
         return buf
 
+    # -- how the layers address the stored rows (overridden by the paged cache) -------------------
+    def attention_rows(self, buf: torch.Tensor, kv_heads: int, dim: int) -> torch.Tensor:
+        """``buf`` as the ``[B | pages, rows, kv_heads, dim]`` view ``decode_attention`` reads."""
+        return buf.view(buf.shape[0], buf.shape[1], kv_heads, dim)
+
+    def table(self) -> torch.Tensor | None:
+        """Page table for ``decode_attention`` (``None``: rows of sequence ``b`` are ``buf[b]``)."""
+        return None
+
+    def dense_rows(self, buf: torch.Tensor) -> torch.Tensor:
+        """``[B, capacity, …]`` rows in logical order (the indexer scores all of them)."""
+        return buf
+
     def advance(self, n: int = 1) -> None:
         self.pos += self.active * n
         self._len32 += (self.active * n).to(torch.int32)
@@ -115,3 +128,78 @@ class StaticDecodeCache:
 
     def nbytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.a + self.b if t is not None)
+
+
+class PagedDecodeCache(StaticDecodeCache):
+    """The same device-position cache over *pages*: per layer one pool ``[num_pages, page_size, …]`` shared by all sequences and
+    a device page table ``[B, max_pages]`` mapping each sequence's logical pages to pool pages.  A step writes row
+    ``(table[b, pos // page_size], pos % page_size)`` and attention reads through the table (``ops/decode_attention.py``), so
+    no sequence reserves more memory than the pages it has been given.  Which pages those are is the caller's business
+    (``ServingEngine`` takes them from the scheduler's ``PagedKVBlockManager``); ``set_pages`` publishes them to the device."""
+
+    def __init__(self, num_layers: int, batch: int, *, num_pages: int, page_size: int, max_pages_per_seq: int, device):
+        super().__init__(num_layers, batch, max_pages_per_seq * page_size, device)
+        self.num_pages, self.page_size, self.max_pages = num_pages, page_size, max_pages_per_seq
+        self._table = torch.zeros(batch, max_pages_per_seq, dtype=torch.int32, device=device)
+        self._published: list[int] = [0] * batch           # how many table entries of each row are valid
+
+    def _buf(self, store: list, layer_idx: int, x: torch.Tensor) -> torch.Tensor:
+        buf = store[layer_idx]
+        if buf is None:
+            buf = torch.zeros((self.num_pages, self.page_size, *x.shape[2:]), dtype=x.dtype, device=x.device)
+            store[layer_idx] = buf
+        return buf
+
+    def _write(self, store: list, layer_idx: int, x: torch.Tensor) -> torch.Tensor:
+        buf = self._buf(store, layer_idx, x)
+        page = self._table[self._rows, self.pos // self.page_size].long()
+        buf[page, self.pos % self.page_size] = x[:, 0].to(buf.dtype)
+        return buf
+
+    def write_a(self, layer_idx: int, x: torch.Tensor) -> torch.Tensor:
+        return self._write(self.a, layer_idx, x)
+
+    def write_b(self, layer_idx: int, x: torch.Tensor) -> torch.Tensor:
+        return self._write(self.b, layer_idx, x)
+
+    def table(self) -> torch.Tensor:
+        return self._table
+
+    def dense_rows(self, buf: torch.Tensor) -> torch.Tensor:
+        g = buf[self._table.long()]                        # [B, max_pages, page_size, …]
+        return g.reshape(self.batch, self.capacity, *buf.shape[2:])
+
+    def set_pages(self, slot: int, pages: list[int]) -> None:
+        """Publish ``pages`` (pool page ids, in logical order) as row ``slot`` of the table; only new entries are written."""
+        if len(pages) > self.max_pages:
+            raise ValueError(f"{len(pages)} pages exceed the per-sequence limit {self.max_pages}")
+        have = self._published[slot]
+        if len(pages) < have or have == 0:
+            have = 0
+        if len(pages) > have:
+            self._table[slot, have:len(pages)] = torch.tensor(pages[have:], dtype=torch.int32, device=self._table.device)
+        self._published[slot] = len(pages)
+
+    def clear_pages(self, slot: int) -> None:
+        self._published[slot] = 0
+        self._table[slot].zero_()
+
+    def load_slot(self, slot: int, kv, tokens_seen: int) -> None:
+        """Scatter a single-sequence ``HybridKVCache`` (after its prefill) into the pages already published for ``slot``."""
+        n = tokens_seen
+        if n >= self.capacity or (n + self.page_size) // self.page_size > self._published[slot]:
+            raise ValueError(f"slot {slot} has {self._published[slot]} pages, {n + 1} tokens need more")
+        idx = torch.arange(n, device=self.pos.device)
+        pages = self._table[slot, idx // self.page_size].long()
+        for i in range(self.num_layers):
+            src_a = kv.a[i].fetch(n)
+            self._buf(self.a, i, src_a)[pages, idx % self.page_size] = src_a[0]
+            if kv.has_b[i]:
+                src_b = kv.b[i].fetch(n)
+                self._buf(self.b, i, src_b)[pages, idx % self.page_size] = src_b[0]
+        self.pos[slot] = n
+        self._len32[slot] = n + 1
+        self._rope.clear()
+
+    def load_from(self, kv, tokens_seen: int | None = None) -> None:
+        raise NotImplementedError("a paged cache is filled slot by slot (load_slot)")

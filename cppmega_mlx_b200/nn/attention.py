@@ -243,17 +243,18 @@ class CausalSelfAttention(nn.Module):
         if c.mode == "dsa":   # shared key/value rows; the newest ``sparse_topk`` causal keys
             new = rope(self.sparse_kv_proj(xt).view(1, b, c.kv_heads, c.q_head_dim))
             rows = cache.write_a(layer_idx, new.reshape(b, 1, -1))
-            rows = rows.view(b, cache.capacity, c.kv_heads, c.q_head_dim)      # stored flat, like the growing cache
+            rows = cache.attention_rows(rows, c.kv_heads, c.q_head_dim)        # stored flat, like the growing cache
             k = min(c.sparse_topk, cache.capacity)
             idx = cache.pos.to(torch.int32)[:, None] - torch.arange(k, device=x.device, dtype=torch.int32)[None, :]
             idx = torch.where(idx >= 0, idx, torch.full_like(idx, -1)).contiguous()
-            out = DA.decode_attention(q, rows, None, None, lengths, scale=scale, topk=idx, d_v=c.q_head_dim, max_keys=k)
+            out = DA.decode_attention(q, rows, None, cache.table(), lengths, scale=scale, topk=idx, d_v=c.q_head_dim, max_keys=k)
         else:
             if c.sliding_window is not None:
                 raise ValueError("sliding-window attention has no static decode path")
             kk = cache.write_a(layer_idx, rope(self.k_proj(xt).view(1, b, c.kv_heads, c.q_head_dim)).transpose(0, 1))
             vv = cache.write_b(layer_idx, self.v_proj(xt).view(b, 1, c.kv_heads, c.q_head_dim))
-            out = DA.decode_attention(q, kk, vv, None, lengths, scale=scale, max_keys=cache.capacity)
+            out = DA.decode_attention(q, cache.attention_rows(kk, c.kv_heads, c.q_head_dim), cache.attention_rows(vv, c.kv_heads, c.q_head_dim),
+                                      cache.table(), lengths, scale=scale, max_keys=cache.capacity)
         return self.out_proj(out.reshape(b, 1, c.q_proj_dim))
 
     def forward(self, hidden_states: torch.Tensor, mask: torch.Tensor | str | None = "causal", *, kv_cache=None,

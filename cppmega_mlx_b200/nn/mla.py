@@ -216,10 +216,10 @@ class MLAAttention(nn.Module):
         topk = None
         if use_sparse and cache.capacity > c.index_topk:
             iq, ik, iw = self.indexer.project(xt, qr, *freqs)
-            keys = cache.write_b(layer_idx, ik.transpose(0, 1))
+            keys = cache.dense_rows(cache.write_b(layer_idx, ik.transpose(0, 1)))
             sc = self.indexer.scores(iq.transpose(0, 1), keys, iw.transpose(0, 1)).reshape(b, cache.capacity)
             topk = ops.topk_select(sc, c.index_topk, None, lengths)               # −1 padded while fewer keys exist
-        out_lat = DA.decode_attention(self._latent_query(q)[:, 0], rows[:, :, None, :], None, None, lengths,
+        out_lat = DA.decode_attention(self._latent_query(q)[:, 0], cache.attention_rows(rows, 1, rows.shape[-1]), None, cache.table(), lengths,
                                       scale=c.qk_head_dim ** -0.5, d_v=c.kv_lora_rank, topk=topk,
                                       max_keys=c.index_topk if topk is not None else cache.capacity)
         return self.wo(self._latent_output(out_lat[:, None]).reshape(b, 1, c.num_heads * c.v_head_dim))
