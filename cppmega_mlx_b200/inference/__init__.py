@@ -2,7 +2,7 @@ from .engine import DecodeSession, HybridKVCache, PromptCacheEntry, make_kv_cach
 from .generation import (GenerationChunk, build_prompt_cache, generate_from_prompt_cache, generate_tokens,
                          generate_tokens_with_kv_cache, next_token_logits, stream_generate_tokens)
 from .graph_decode import GraphDecodeSession, StaticStepRunner
-from .static_cache import StaticDecodeCache
+from .static_cache import PagedDecodeCache, StaticDecodeCache
 from .serving_engine import ServingEngine, ServingRequest
 from .infilling import build_infilling_prompt, splice_infill
 from .sampling import apply_top_k, apply_top_p, sample_next_token

@@ -66,16 +66,16 @@ class StaticStepRunner:
                         old.copy_(val)
         self.cache.advance()
 
-    def _mutable_tensors(self) -> list[torch.Tensor]:
-        tens = [t for st in self.states for *_, t in _state_tensors(st)] + [t for t in self.cache.a + self.cache.b if t is not None]
-        return tens + [self.cache.pos, self.cache.lengths()]
-
     def capture(self) -> None:
         """Warm up on a side stream (lazy allocations, library handles, function attributes), capture both parities, and put
-        every tensor the warm-up touched back.  A refused capture (a layer that reads a value on the host) leaves the eager
-        static step in place."""
-        tens = self._mutable_tensors()
+        what the warm-up touched back.  The warm-up runs with every row inactive, so positions do not move and the only cache
+        rows it writes are the ones at the current positions — which the next real step rewrites before anything reads them;
+        the recurrent states are snapshotted and restored.  A refused capture (a layer that reads a value on the host) leaves
+        the eager static step in place."""
+        tens = [t for st in self.states for *_, t in _state_tensors(st)]
         keep = [t.clone() for t in tens]
+        keep_active = self.cache.active.clone()
+        self.cache.active.zero_()
 
         def restore():
             for t, k in zip(tens, keep):
@@ -102,6 +102,7 @@ class StaticStepRunner:
             torch.cuda.synchronize()
             self.graphs, self.capture_failed = None, True
         restore()                                  # capture does not execute, but keep the invariant explicit
+        self.cache.active.copy_(keep_active)
 
     def ensure_captured(self) -> None:
         want = self.use_graph if self.use_graph is not None else self.tok.device.type == "cuda"

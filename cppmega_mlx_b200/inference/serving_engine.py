@@ -23,7 +23,7 @@ from ..models.hybrid_lm import HybridDecodeState
 from .engine import DecodeSession
 from .graph_decode import StaticStepRunner
 from .sampling import sample_next_token
-from .static_cache import StaticDecodeCache
+from .static_cache import PagedDecodeCache, StaticDecodeCache
 
 
 @dataclass
@@ -43,10 +43,25 @@ class ServingRequest:
 
 class ServingEngine:
     def __init__(self, model, *, max_batch: int, capacity: int, eos_token_id: int | None = None, use_graph: bool | None = None,
-                 scheduler=None, seed: int = 0):
+                 scheduler=None, seed: int = 0, page_size: int | None = None, num_pages: int | None = None):
+        """``page_size`` switches the physical cache to pages (``PagedDecodeCache``): the pool has ``num_pages`` pages shared by
+        all slots, each request holds exactly the pages the scheduler's block manager has given it, and attention reads
+        through the page table.  A scheduler is created over an internal block manager when none is passed."""
         self.model = model
         self.max_batch, self.capacity, self.eos = max_batch, capacity, eos_token_id
         self.use_graph = use_graph
+        self.page_size = page_size
+        self._trash_page = None
+        if page_size is not None:
+            from .serving import ContinuousBatchScheduler, PagedKVBlockManager
+            if scheduler is None:
+                if not num_pages:
+                    raise ValueError("a paged engine needs num_pages (or a scheduler with a block manager)")
+                mgr = PagedKVBlockManager(num_blocks=num_pages, num_layers=1, block_size=page_size, kv_heads=1, head_dim=1)
+                scheduler = ContinuousBatchScheduler(mgr, max_batch_size=max_batch)
+            if scheduler.manager.block_size != page_size:
+                raise ValueError("the scheduler's block size must equal page_size")
+            self.capacity = capacity = (capacity + page_size - 1) // page_size * page_size
         self.scheduler = scheduler
         if scheduler is not None and scheduler.max_batch_size > max_batch:
             raise ValueError("the scheduler's max_batch_size must not exceed the engine's slot count")
@@ -98,9 +113,20 @@ class ServingEngine:
         logits = sess.forward(history[None], last_only=True)[:, 0]   # a preempted request recomputes what it had generated
         n = sess.tokens_seen
         if self.cache is None:
-            self.cache = StaticDecodeCache(sess.kv.num_layers, self.max_batch, self.capacity, self.device)
+            if self.page_size is None:
+                self.cache = StaticDecodeCache(sess.kv.num_layers, self.max_batch, self.capacity, self.device)
+            else:
+                mgr = self.scheduler.manager
+                self.cache = PagedDecodeCache(sess.kv.num_layers, self.max_batch, num_pages=mgr.num_blocks, page_size=self.page_size,
+                                              max_pages_per_seq=self.capacity // self.page_size, device=self.device)
+                # idle slots still write one row per step: give them a page of their own that no request ever owns
+                self._trash_page = mgr.allocate(-1, 1)[0]
+                for i in range(self.max_batch):
+                    self.cache.clear_pages(i, fill=self._trash_page)
             self.cache.active.zero_()
             self._logits = torch.zeros(self.max_batch, logits.shape[-1], dtype=logits.dtype, device=self.device)
+        if self.page_size is not None:
+            self.cache.set_pages(slot, self.scheduler.manager.tables[req.request_id])
         self.cache.load_slot(slot, sess.kv, n)
         if not self.states:       # fixed recurrent-state storage for all slots, shaped after the first request's
             first = HybridDecodeState()
@@ -147,6 +173,9 @@ class ServingEngine:
     def _release(self, req: ServingRequest) -> None:
         if req.slot is not None:
             self.cache.active[req.slot] = 0
+            if self.page_size is not None:      # park the idle row on the scratch page, at row 0
+                self.cache.clear_pages(req.slot, fill=self._trash_page)
+                self.cache.pos[req.slot] = 0
             self.slots[req.slot] = None
             req.slot = None
 
@@ -171,6 +200,10 @@ class ServingEngine:
             for rid in sched.preempted:
                 self._preempt(self.requests[rid])
         if self.num_active:
+            if self.page_size is not None:      # the scheduler may have given running requests another page for this token
+                for slot, req in enumerate(self.slots):
+                    if req is not None:
+                        self.cache.set_pages(slot, self.scheduler.manager.tables[req.request_id])
             if self.runner is None:
                 self.runner = StaticStepRunner(self.model, self.cache, self.states, self._tok, self._logits, use_graph=self.use_graph)
             self.runner.ensure_captured()

@@ -180,9 +180,10 @@ class PagedDecodeCache(StaticDecodeCache):
             self._table[slot, have:len(pages)] = torch.tensor(pages[have:], dtype=torch.int32, device=self._table.device)
         self._published[slot] = len(pages)
 
-    def clear_pages(self, slot: int) -> None:
+    def clear_pages(self, slot: int, fill: int = 0) -> None:
+        """Forget ``slot``'s pages; its table row points at page ``fill`` (a scratch page for rows that idle along)."""
         self._published[slot] = 0
-        self._table[slot].zero_()
+        self._table[slot].fill_(fill)
 
     def load_slot(self, slot: int, kv, tokens_seen: int) -> None:
         """Scatter a single-sequence ``HybridKVCache`` (after its prefill) into the pages already published for ``slot``."""

@@ -137,7 +137,8 @@ def test_graph_replay_matches_eager_static_steps():
     assert out.shape == (2, 26)
 
 
-def test_serving_engine_graph_replay_with_slot_turnover():
+@pytest.mark.parametrize("paged", [False, True])
+def test_serving_engine_graph_replay_with_slot_turnover(paged):
     """Continuous batching on the GPU: the captured step serves a changing mix of requests; results equal the eager engine's."""
     from cppmega_mlx_b200 import inference as I
     from cppmega_mlx_b200.ops import _backend as B
@@ -148,7 +149,8 @@ def test_serving_engine_graph_replay_with_slot_turnover():
     budgets = [8, 4, 9, 3, 6]
 
     def serve(use_graph):
-        eng = I.ServingEngine(m, max_batch=2, capacity=64, use_graph=use_graph)
+        kw = dict(page_size=16, num_pages=12) if paged else {}
+        eng = I.ServingEngine(m, max_batch=2, capacity=64, use_graph=use_graph, **kw)
         ids = [eng.submit(p, b) for p, b in zip(prompts, budgets)]
         out = eng.run()
         return [out[i] for i in ids], eng

@@ -324,3 +324,22 @@ def test_serving_engine_with_scheduler_preemption_and_eos():
     r = eng2.submit(prompts[0], 8)
     got = eng2.run()[r]
     assert got == alone[0][:alone[0].index(eos) + 1] and eng2.requests[r].finish_reason == "eos"
+
+
+@pytest.mark.parametrize("pattern,kw", [("AM", {"mla_low_rank": True, "dsa_a_layer_ranks": (0,)}), ("AA", {})])
+def test_serving_engine_paged_cache_with_preemption(pattern, kw):
+    """Paged physical cache: attention reads through the page table, requests hold only the pages the block manager gave
+    them, and a pool too small for everybody forces preemption + recompute — the tokens still equal single-request generation."""
+    m = _model(pattern, **kw)
+    torch.manual_seed(7)
+    prompts = [torch.randint(4, 100, (n,)) for n in (6, 9, 5, 7)]
+    alone = [I.generate_tokens_with_kv_cache(m, p[None], max_new_tokens=9)[0, p.numel():].tolist() for p in prompts]
+    eng = I.ServingEngine(m, max_batch=3, capacity=32, use_graph=False, page_size=4, num_pages=10)
+    ids = [eng.submit(p, 9, priority=pr) for p, pr in zip(prompts, (3, 2, 1, 0))]
+    out = eng.run(max_steps=400)
+    assert eng.idle() and isinstance(eng.cache, I.PagedDecodeCache)
+    for i, w in zip(ids, alone):
+        assert out[i] == w
+    sch = eng.scheduler
+    assert sum(sch.requests[i].preemptions for i in ids) >= 1                 # 9 usable pages of 4 tokens cannot hold them all
+    assert sch.manager.num_free_blocks == sch.manager.num_blocks - 1          # everything returned except the scratch page
