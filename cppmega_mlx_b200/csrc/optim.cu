@@ -300,13 +300,47 @@ extern "C" int cmb_axpy_update(void* p, const void* u, int64_t n, int dtype, flo
 // ---------------------------------------------------------------------------------------------- symmetric completion
 namespace cmb {
 // G[i][j] = G[j][i] for j > i (n×n bf16, row pitch ld): completes a matrix whose lower triangle was computed by a GEMM that
-// skipped the tiles above the diagonal.  32×32 tiles through shared memory so both sides are coalesced.
-__global__ void mirror_lower_kernel(__nv_bfloat16* __restrict__ g, int n, long long ld) {
-  __shared__ __nv_bfloat16 tile[32][33];
+// skipped the tiles above the diagonal.  64×64 tiles through shared memory; both sides move whole 128-byte lines as bf16 pairs
+// (n and ld even; the entry point falls back to the scalar form otherwise).
+__global__ void __launch_bounds__(256) mirror_lower_kernel(__nv_bfloat16* __restrict__ g, int n, long long ld) {
+  __shared__ __nv_bfloat16 tile[64][66];
   const int bi = blockIdx.y, bj = blockIdx.x;        // destination tile (rows bi, cols bj), only bj >= bi
   if (bj < bi) return;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 column pairs × 8 rows per pass
+#pragma unroll
+  for (int r = ty; r < 64; r += 8) {                 // source tile: rows bj·64.., cols bi·64..
+    const int sr = bj * 64 + r, sc = bi * 64 + 2 * tx;
+    __nv_bfloat162 v = __floats2bfloat162_rn(0.f, 0.f);
+    if (sr < n && sc + 1 < n) v = *reinterpret_cast<const __nv_bfloat162*>(g + sr * ld + sc);
+    else if (sr < n && sc < n) v.x = g[sr * ld + sc];
+    tile[r][2 * tx] = v.x;
+    tile[r][2 * tx + 1] = v.y;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = ty; r < 64; r += 8) {
+    const int dr = bi * 64 + r, dc = bj * 64 + 2 * tx;
+    if (dr >= n || dc >= n) continue;
+    const __nv_bfloat16 a = tile[2 * tx][r], b = tile[2 * tx + 1][r];
+    if (dc > dr && dc + 1 < n) {                     // the whole pair lies above the diagonal
+      __nv_bfloat162 v;
+      v.x = a;
+      v.y = b;
+      *reinterpret_cast<__nv_bfloat162*>(g + dr * ld + dc) = v;
+    } else {                                         // pair straddles the diagonal or the edge
+      if (dc > dr) g[dr * ld + dc] = a;
+      if (dc + 1 > dr && dc + 1 < n) g[dr * ld + dc + 1] = b;
+    }
+  }
+}
+
+// Scalar form for odd sizes / pitches.
+__global__ void mirror_lower_scalar_kernel(__nv_bfloat16* __restrict__ g, int n, long long ld) {
+  __shared__ __nv_bfloat16 tile[32][33];
+  const int bi = blockIdx.y, bj = blockIdx.x;
+  if (bj < bi) return;
   const int tx = threadIdx.x, ty = threadIdx.y;      // 32 × 8
-  for (int r = ty; r < 32; r += 8) {                 // load source tile (rows bj·32.., cols bi·32..)
+  for (int r = ty; r < 32; r += 8) {
     const int sr = bj * 32 + r, sc = bi * 32 + tx;
     tile[r][tx] = (sr < n && sc < n) ? g[sr * ld + sc] : __float2bfloat16(0.f);
   }
@@ -320,7 +354,13 @@ __global__ void mirror_lower_kernel(__nv_bfloat16* __restrict__ g, int n, long l
 
 extern "C" int cmb_mirror_lower(void* g, int n, long long ld, void* stream) {
   if (n <= 0) return 0;
-  const int t = (n + 31) / 32;
-  cmb::mirror_lower_kernel<<<dim3(t, t), dim3(32, 8), 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(g), n, ld);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((n % 2) == 0 && (ld % 2) == 0 && (reinterpret_cast<uintptr_t>(g) & 3) == 0) {
+    const int t = (n + 63) / 64;
+    cmb::mirror_lower_kernel<<<dim3(t, t), 256, 0, st>>>(static_cast<__nv_bfloat16*>(g), n, ld);
+  } else {
+    const int t = (n + 31) / 32;
+    cmb::mirror_lower_scalar_kernel<<<dim3(t, t), dim3(32, 8), 0, st>>>(static_cast<__nv_bfloat16*>(g), n, ld);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }

@@ -55,3 +55,20 @@ def test_newton_schulz_orthogonalises():
         o = newton_schulz5_bf16_(u.clone(), ss)
         sv = torch.linalg.svdvals(o.float())
         assert sv.max() < 1.35 and sv.min() > 0.4, (sv.min().item(), sv.max().item())
+
+
+@pytest.mark.parametrize("n,pad", [(64, 0), (100, 4), (2048, 0), (511, 1), (130, 0)])
+def test_mirror_lower_completes_symmetric_matrix(n, pad):
+    """The Gram GEMM only computes tiles on or below the diagonal; the mirror kernel fills in the rest (vector and scalar forms)."""
+    import ctypes
+
+    from cppmega_mlx_b200.ops import _backend as B
+    lib = B.load_library()
+    torch.manual_seed(n)
+    full = torch.randn(n, n + pad, device="cuda").bfloat16()
+    g = full[:, :n]                                   # row pitch n + pad
+    want = torch.tril(g.float()) + torch.tril(g.float(), -1).t()
+    rc = lib.cmb_mirror_lower(ctypes.c_void_p(g.data_ptr()), n, ctypes.c_longlong(full.stride(0)),
+                              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert rc == 0 and torch.equal(g.float(), want)
