@@ -412,6 +412,41 @@ def decode_profile(args) -> list[dict]:
     return rows
 
 
+def step_profile(args) -> list[dict]:
+    """Kernel-time breakdown of one training step of the flagship (hybrid_1b, Muon + AdamW, 4 × 4096 tokens, one GPU) with
+    torch.profiler: which kernels the 367 ms go to.  An analysis aid (profiler overhead included; kernels on the optimizer's
+    side streams overlap, so the sum exceeds the step time) — not a benchmark value."""
+    from torch.profiler import ProfilerActivity, profile
+
+    from cppmega_mlx_b200.data.batch import LMTokenBatch
+    from cppmega_mlx_b200.recipes.model_factory import get_model_profile
+    from cppmega_mlx_b200.training.compiled import PretrainingStep
+    from cppmega_mlx_b200.training.distributed_optimizer import DistributedZeRO1Optimizer
+    from cppmega_mlx_b200.training.loss import make_loss_fn
+    from cppmega_mlx_b200.training.optimizers import make_muon
+    torch.manual_seed(0)
+    dev = torch.device("cuda", 0)
+    model = get_model_profile("hybrid_1b").build_model(dtype=torch.bfloat16, device=dev, max_seq_length=4096, grad_checkpoint=False)
+    opt = DistributedZeRO1Optimizer(model, lambda ps: make_muon(ps, lr_muon=2e-3, lr_adamw=1e-4, ns_carrier="bf16"))
+    opt.zero_grad()
+    step = PretrainingStep(model, opt, loss_fn=make_loss_fn(backend="cce"), sync_metrics=False, device=dev)
+    batches = [LMTokenBatch(tokens=torch.randint(0, 65536, (4, 4097), device=dev)) for _ in range(4)]
+    for b in batches[:3]:
+        step(b)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step(batches[3])
+        torch.cuda.synchronize()
+    ev = sorted([e for e in prof.key_averages() if e.device_time_total > 0], key=lambda e: -e.device_time_total)
+    total = sum(e.device_time_total for e in ev)
+    rows = [{"op": "training step kernel", "name": e.key[:110], "ms": e.device_time_total / 1e3, "launches": e.count,
+             "share": e.device_time_total / total} for e in ev[:40]]
+    print(json.dumps({"op": "training step kernel time, total", "ms": total / 1e3}), flush=True)
+    for r in rows:
+        print(json.dumps(r), flush=True)
+    return rows
+
+
 def bench_serving(args) -> list[dict]:
     """Continuous batching with the 1B hybrid: 64 requests (prompts of 64-1024 tokens, 64 new tokens each) through a
     ``ServingEngine`` with 32 slots; wall-clock end to end (prefills included) and decode-step rate."""
@@ -450,7 +485,7 @@ def bench_serving(args) -> list[dict]:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "decode", "decode_loop", "serving", "decode_trace", "decode_profile", "all"])
+    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "decode", "decode_loop", "serving", "decode_trace", "decode_profile", "step_profile", "all"])
     ap.add_argument("--json", default=None)
     ap.add_argument("--only", default=None, help="run the single case with this label (small captures under a profiler)")
     ap.add_argument("--iters", type=int, default=10)
@@ -479,6 +514,8 @@ def main(argv=None) -> int:
         rows += decode_trace(args)
     if args.op == "decode_profile":
         rows += decode_profile(args)
+    if args.op == "step_profile":
+        rows += step_profile(args)
     if args.json:
         with open(args.json, "w") as f:
             json.dump(rows, f, indent=1)
