@@ -343,3 +343,34 @@ def test_serving_engine_paged_cache_with_preemption(pattern, kw):
     sch = eng.scheduler
     assert sum(sch.requests[i].preemptions for i in ids) >= 1                 # 9 usable pages of 4 tokens cannot hold them all
     assert sch.manager.num_free_blocks == sch.manager.num_blocks - 1          # everything returned except the scratch page
+
+
+def test_paged_decode_cache_addressing_and_errors():
+    c = I.PagedDecodeCache(1, 2, num_pages=6, page_size=4, max_pages_per_seq=3, device="cpu")
+    assert c.capacity == 12 and c.table().shape == (2, 3)
+    c.set_pages(0, [5, 2])
+    c.set_pages(1, [1])
+    kv = I.HybridKVCache(1)
+    rows = torch.arange(6 * 3, dtype=torch.float32).view(1, 6, 3)
+    kv.update_and_fetch_latent(0, rows, None)
+    c.load_slot(0, kv, 6)                                           # 6 tokens → pages 5 (rows 0-3) and 2 (rows 0-1)
+    pool = c.a[0]
+    assert torch.equal(pool[5], rows[0, :4]) and torch.equal(pool[2, :2], rows[0, 4:6]) and c.pos.tolist() == [6, 0]
+    new = torch.full((2, 1, 3), 7.0)
+    c.write_a(0, new)                                               # slot 0 → page 2 row 2; slot 1 → page 1 row 0
+    assert torch.equal(pool[2, 2], new[0, 0]) and torch.equal(pool[1, 0], new[1, 0])
+    dense = c.dense_rows(pool)
+    assert dense.shape == (2, 12, 3) and torch.equal(dense[0, :6], rows[0]) and torch.equal(dense[0, 6], new[0, 0])
+    c.advance()
+    assert c.pos.tolist() == [7, 1] and c.lengths().tolist() == [8, 2]
+    c.active[1] = 0
+    c.advance()
+    assert c.pos.tolist() == [8, 1]                                 # an inactive row stays where it is
+    with pytest.raises(ValueError):
+        c.set_pages(0, [0, 1, 2, 3])                                # more pages than a sequence may hold
+    with pytest.raises(ValueError):
+        c.load_slot(1, kv, 6)                                       # one page published, two needed
+    c.clear_pages(0, fill=4)
+    assert c.table()[0].tolist() == [4, 4, 4]
+    with pytest.raises(NotImplementedError):
+        c.load_from(kv)
