@@ -201,6 +201,25 @@ class Mamba3Block(nn.Module):
         Cm = _rms_norm_last(Cm) * self.C_norm_weight.to(Cm.dtype) + self.C_bias.to(Cm.dtype)
         return Bm, Cm
 
+    @torch.no_grad()
+    def _cache_after_prefill(self, BC, tail, dt, xh, xBC_raw, h, dtype) -> Mamba3CacheState:
+        """Decode cache after a from-scratch prefill on the fused path, from last-position quantities only: the accumulated
+        phase of every head (one contraction over the sequence), the last token's normalised B rotated by its group's phase
+        (not yet trapezoid-scaled: its look-ahead term is completed by the next token), the last x, and the conv window."""
+        c = self.config
+        b, s = BC.shape[:2]
+        H, G, N, R = c.nheads, c.ngroups, c.d_state, self.dims.num_rope_angles
+        angles = tail[..., 3 * H:].float()                                            # [B,S,R]
+        ang_total = torch.einsum("bsr,bsh->bhr", angles, dt.float())                  # [B,H,R]
+        B_last = BC[:, -1:, :self.dims.d_bc].reshape(b, 1, 1, G, N)
+        B_last = (_rms_norm_last(B_last) * self.B_norm_weight.to(B_last.dtype) + self.B_bias.to(B_last.dtype))[:, :, 0]   # [B,1,G,N]
+        k_last = apply_rope_on_state_dim(B_last, ang_total[:, None])[:, 0]            # group g turns with the phase of head g
+        k_last = k_last[:, None].repeat_interleave(H // G, dim=2)                     # [B,1,H,N]
+        hist = c.d_conv - 1
+        conv_state = xBC_raw[:, -hist:] if s >= hist else F.pad(xBC_raw, (0, 0, hist - s, 0))
+        return Mamba3CacheState(angle_dt=torch.remainder(ang_total, 2 * math.pi).to(dtype), ssm=h, k=k_last.to(dtype),
+                                v=xh[:, -1], conv=conv_state.contiguous())
+
     def forward(self, hidden_states: torch.Tensor, *, h0: torch.Tensor | None = None,
                 cache: Mamba3CacheState | None = None, return_cache: bool = False, cache_out: Mamba3CacheState | None = None):
         """``cache_out``: optional destination for the next cache of a one-token GPU step (tensors distinct from ``cache``)."""
@@ -231,7 +250,7 @@ class Mamba3Block(nn.Module):
         z, x, BC, tail = ops.packed_split_conv_silu(proj, c.d_inner, conv_ch, c.d_inner, self.conv_weight, self.conv_bias,
                                                     prefix=prefix)
         xBC_raw = proj[..., c.d_inner:c.d_inner + conv_ch]
-        if cache is None and not return_cache and c.effective_mimo_rank == 1 and ops.kernels_enabled():
+        if cache is None and c.effective_mimo_rank == 1 and ops.kernels_enabled():
             from ..ops import mamba3_prep as MP
             norm_params = (self.B_norm_weight, self.B_bias, self.C_norm_weight, self.C_bias)
             if MP.supported(BC, tail, norm_params + (self.dt_bias,), c.nheads, c.ngroups, c.d_state, self.dims.num_rope_angles):
@@ -242,7 +261,10 @@ class Mamba3Block(nn.Module):
                 if h0 is not None and tuple(h0.shape) != (b, c.nheads, c.headdim, c.d_state):
                     raise ValueError(f"h0 must have shape {(b, c.nheads, c.headdim, c.d_state)}, got {tuple(h0.shape)}")
                 y, h = ops.mamba3_scan(xh, Bg, Cg, zh, A, dt, self.D, h0, chunk_size=c.chunk_size)
-                return self.out_proj(y.reshape(b, s, c.d_inner)), h
+                out = self.out_proj(y.reshape(b, s, c.d_inner))
+                if not return_cache:
+                    return out, h
+                return out, self._cache_after_prefill(BC, tail, dt, xh, xBC_raw, h, hidden_states.dtype)
         Bm, Cm = BC[..., :self.dims.d_bc], BC[..., self.dims.d_bc:]
         dd_dt, dd_A, trap, angles = torch.split(tail.float(), [c.nheads, c.nheads, c.nheads, self.dims.num_rope_angles], dim=-1)
         x = x.reshape(b, s, c.nheads, c.headdim)
