@@ -258,7 +258,8 @@ class MLAAttention(nn.Module):
             k_lat = latent.detach()[:, :, None, :]
             self.aux_loss = dsa_indexer_loss(self.indexer.scores(iq, idx_k, iw), self._latent_query(q.detach()), k_lat, softmax_scale=scale,
                                              loss_coeff=c.index_loss_coeff, topk_indices=idx)
-        if kv_cache is None and add_mask is None and x.is_cuda and x.dtype == torch.bfloat16 and ops.kernels_enabled():
+        fresh = kv_cache is None or (offset == 0 and sk == s)     # nothing cached before these tokens (training, or a prefill from scratch)
+        if fresh and add_mask is None and x.is_cuda and x.dtype == torch.bfloat16 and ops.kernels_enabled():
             # Training / prefill on the GPU: per-head K,V (192/128 wide) under the top-k bitmask.
             from ..ops import attention as A
             kv_up = self.wkv_b(c_kv).view(b, s, c.num_heads, c.qk_nope_head_dim + c.v_head_dim)
