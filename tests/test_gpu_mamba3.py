@@ -134,7 +134,7 @@ def test_prefill_cache_on_fused_path_matches_framework_path(groups, state, seq):
         x = torch.randn(2, seq, 512, device="cuda").bfloat16()
         before = B.launch_count()
         got_y, got = blk(x, return_cache=True)
-        assert B.launch_count() - before >= 6            # the kernel path ran
+        assert B.launch_count() - before >= 3            # the kernel path ran
         with B.use_kernels(False):
             ref_y, ref = blk(x, return_cache=True)
     assert (got_y.float() - ref_y.float()).abs().max() <= 3e-2 * max(1.0, float(ref_y.float().abs().max()))
