@@ -101,6 +101,17 @@ def bench_composite(args) -> list[dict]:
     gu = torch.randn(R, 11264, device=dev).bfloat16().requires_grad_()
     add("swiglu fwd+bwd 16384x5632", lambda: _fb(lambda: ops.swiglu(gu), gu), algo_bytes=R * 5632 * 2 * (3 + 5))
 
+    # Mamba3's packed projection [z | x B C | tail] of the 1B model: causal conv (4 taps) + SiLU on the 6144 middle channels
+    proj = torch.randn(4, 4096, 10464, device=dev).bfloat16().requires_grad_()
+    cw = (torch.randn(6144, 4, 1, device=dev) * 0.3).bfloat16().requires_grad_()
+    cb = torch.zeros(6144, device=dev).bfloat16().requires_grad_()
+
+    def conv_run():
+        z, xo, bc, tail = ops.packed_split_conv_silu(proj, 4096, 6144, 4096, cw, cb)
+        return xo.float().sum() + bc.float().sum()
+    add("conv4+silu fwd+bwd 16384x6144 (packed projection)", lambda: _fb(conv_run, proj, cw, cb),
+        algo_bytes=R * 6144 * 2 * (2 + 3), eager=False)
+
     # cut cross-entropy: 16384 rows, vocab 65536
     h = (torch.randn(R, Dm, device=dev) * 0.5).bfloat16().requires_grad_()
     wv = (torch.randn(65536, Dm, device=dev) * 0.02).bfloat16().requires_grad_()

@@ -104,6 +104,18 @@ __global__ void __launch_bounds__(256) conv_silu_bwd_kernel(const __nv_bfloat16*
                                     : dy2 + static_cast<long long>(b) * S * (C - C1) + (c - C1);
     const long long gld = first ? C1 : (C - C1);
     for (int s0 = run0; s0 < min(S, run0 + CONV_RUN); s0 += CONV_TS) {
+    // The kernel is latency-bound (each sub-tile's loads are consumed right away): ask L2 for the rows the next sub-tile
+    // will add to the window while this one is being computed.
+    if (s0 + CONV_TS < min(S, run0 + CONV_RUN)) {
+#pragma unroll
+      for (int j = 0; j < CONV_TS; ++j) {
+        const int sn = s0 + CONV_TS + (K - 1) + j;
+        if (sn < S) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(ib + sn * ld_in));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(gb + sn * gld));
+        }
+      }
+    }
     // inputs s0-(K-1) .. s0+TS+K-2 and dpre for s0 .. s0+TS+K-2
     constexpr int NI = CONV_TS + 2 * (CONV_MAXK - 1);
     float2 xin[NI];
