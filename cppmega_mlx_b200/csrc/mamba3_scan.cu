@@ -208,6 +208,19 @@ __global__ void __launch_bounds__(256) m3_bwd_q_kernel(const __nv_bfloat16* __re
     }
     __syncthreads();
     const long long mbase = vrow * L;  // [b,c,h] matrix base (L×L)
+    if (hh + 1 < hg) {  // the loop is latency-bound: ask L2 for the next head's rows of dM and M while this head is processed
+      const long long nbase = mbase + static_cast<long long>(L) * L;
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int j = 0; j < MAXJ; ++j) {
+          const int s = 2 * lane + 64 * j;
+          if (j < nj && s < smax) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(dM + nbase + static_cast<long long>(r0 + r) * L + s));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(Mm + nbase + static_cast<long long>(r0 + r) * L + s));
+          }
+        }
+    }
     float csum[MAXJ][2];
 #pragma unroll
     for (int j = 0; j < MAXJ; ++j) csum[j][0] = csum[j][1] = 0.f;
