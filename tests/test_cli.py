@@ -116,3 +116,20 @@ def test_zero1_loopback_receipt(capsys):
     rc, out = _run_main(bench_zero1_loopback, ["--steps", "3", "--port", "29741"], capsys)
     rep = json.loads(out[-1])
     assert rc == 0 and rep["status"] == "ok" and rep["max_loss_gap"] < 1e-4 and rep["state_fraction_largest_rank"] < 0.6
+
+
+def test_bench_tiny_archives_and_refuses_unmatched_comparisons(capsys, tmp_path):
+    import json
+
+    from cppmega_mlx_b200.cli import bench_tiny
+    arch = str(tmp_path / "rows")
+    rc, out = _run_main(bench_tiny, ["--steps", "5", "--warmup", "2", "--pattern", "AM", "--archive", arch], capsys)
+    rep = json.loads(out[-1])
+    assert rc == 0 and rep["row"]["value"] > 0 and (tmp_path / "rows" / "index.json").exists()
+    rc, out = _run_main(bench_tiny, ["--steps", "5", "--warmup", "2", "--pattern", "AM", "--compare-to", arch, "--min-ratio", "0.05"], capsys)
+    cmp = json.loads(out[-1])["comparisons"]
+    assert rc == 0 and cmp[0]["status"] == "ok" and cmp[0]["ratio"] > 0.05
+    rc, out = _run_main(bench_tiny, ["--steps", "5", "--warmup", "2", "--pattern", "AM", "--batch-size", "4", "--compare-to", arch,
+                                     "--min-ratio", "0.05"], capsys)
+    cmp = json.loads(out[-1])["comparisons"]
+    assert rc == 3 and cmp[0]["status"] == "refused" and "global_batch" in cmp[0]["reason"]   # no matched row → gate fails closed
