@@ -116,14 +116,9 @@ class LightningIndexer(nn.Module):
         b, sq, d = qw.shape
         sk = k.shape[1]
         if k.is_cuda and k.dtype == torch.bfloat16 and ops.kernels_enabled() and d % 8 == 0 and sk % 4 == 0:
-            # One batched GEMM; tiles entirely above the diagonal are skipped (the selector never reads them).
-            from ..ops import gemm as G
-            qw, kc = qw.contiguous(), k.contiguous()
-            out = torch.empty(b, sq, sk, dtype=torch.float32, device=k.device)
-            G.gemm_batched(qw, kc, out, M=sq, N=sk, K=d, a_mn=False, b_mn=False, lda=d, ldb=d, ldc=sk, nb=(1, 1, b),
-                           sA=(0, 0, sq * d), sB=(0, 0, sk * d), sC=(0, 0, sq * sk),
-                           flags=G.CAUSAL_SKIP if sq == sk else 0)
-            return out
+            # One batched GEMM (differentiable); tiles entirely above the diagonal are skipped (the selector never reads them).
+            from ..ops.dsa_indexer_loss import index_score_matmul
+            return index_score_matmul(qw, k, sq == sk)
         return torch.einsum("bqd,bkd->bqk", qw.float(), k.float())
 
     @torch.no_grad()
