@@ -247,6 +247,33 @@ def bench_sparse_mla(args) -> list[dict]:
     return rows
 
 
+def bench_dsa_loss(args) -> list[dict]:
+    """DSA indexer KL loss, forward + gradient with respect to the index scores, at the flagship attention shape (B4 S4096, 16
+    latent-query heads of width 576, top-2048 keys) against the same loss written with PyTorch ops."""
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops.dsa_indexer_loss import dsa_indexer_loss
+    b, S, H, d, topk = 4, 4096, 16, 576, 2048
+    torch.manual_seed(0)
+    q = (torch.randn(b, S, H, d, device="cuda") * 0.2).bfloat16()
+    k = (torch.randn(b, S, 1, d, device="cuda") * 0.2).bfloat16()
+    x = torch.randn(b, S, S, device="cuda").requires_grad_()
+    ends = torch.arange(1, S + 1, device="cuda", dtype=torch.int32).repeat(b)
+    idx = ops.topk_select(x.detach().view(b * S, S), topk, None, ends).view(b, S, topk)
+    rows = []
+    for label, ix in (("causal", None), (f"top{topk}", idx)):
+        run = _fb(lambda ix=ix: dsa_indexer_loss(x, q, k, softmax_scale=d ** -0.5, topk_indices=ix), x)
+        ms = time_cuda(run, iters=args.iters, warmup=args.warmup)
+        row = {"op": f"dsa indexer KL loss fwd+bwd B{b} S{S} H{H} d{d} {label}", "ms": ms}
+        if not args.no_eager:
+            with B.use_kernels(False):
+                row["eager_ms"] = time_cuda(run, iters=1, warmup=1)
+            row["speedup_vs_eager"] = row["eager_ms"] / ms
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+    return rows
+
+
 def bench_decode(args) -> list[dict]:
     """Decode-step attention over a paged cache (one query per sequence).  Latent MLA rows are 1152 bytes (576 bf16) shared by
     key and value; GB/s counts each attended row once per 16-head group, which is what the kernel has to read."""
@@ -496,7 +523,7 @@ def bench_serving(args) -> list[dict]:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "decode", "decode_loop", "serving", "decode_trace", "decode_profile", "step_profile", "all"])
+    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "dsa_loss", "decode", "decode_loop", "serving", "decode_trace", "decode_profile", "step_profile", "all"])
     ap.add_argument("--json", default=None)
     ap.add_argument("--only", default=None, help="run the single case with this label (small captures under a profiler)")
     ap.add_argument("--iters", type=int, default=10)
@@ -515,6 +542,8 @@ def main(argv=None) -> int:
         rows += bench_m2rnn(args)
     if args.op in ("sparse_mla", "all"):
         rows += bench_sparse_mla(args)
+    if args.op in ("dsa_loss", "all"):
+        rows += bench_dsa_loss(args)
     if args.op in ("decode", "all"):
         rows += bench_decode(args)
     if args.op in ("decode_loop", "all"):

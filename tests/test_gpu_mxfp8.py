@@ -99,3 +99,18 @@ def test_sparse_mla_blockscaled_gpu_matches_cpu_semantics():
     assert torch.equal(rt.float().cpu(), rt_ref)           # the kernels reproduce the reference quantiser bit for bit
     out.float().sum().backward()
     assert q.grad is not None and kv.grad is not None and torch.isfinite(kv.grad.float()).all()
+
+
+def test_fp8_block_dequant_kernel_matches_reference():
+    from cppmega_mlx_b200.v4 import moe_fp8 as F8
+    torch.manual_seed(0)
+    w = torch.randn(3, 384, 1040, device="cuda") * 0.3
+    q, s = F8.quantize_linear_to_fp8(w)
+    got = F8.dequantize_fp8_blocks(q, s)
+    ref = F8.dequantize_fp8_blocks_reference(q, s)
+    assert got.dtype == torch.bfloat16 and torch.equal(got, ref)
+    lin = F8.FP8Linear(1040, 384, device="cuda")
+    lin.weight_fp8, lin.weight_scale_inv = q[0], s[0]
+    x = torch.randn(64, 1040, device="cuda").bfloat16()
+    y = lin(x)
+    assert torch.allclose(y.float(), x.float() @ ref[0].float().t(), rtol=2e-2, atol=5e-2)

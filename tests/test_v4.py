@@ -140,3 +140,61 @@ def test_superblock_every_kind_trains():
         h = lm.decoder_hidden_states(b.inputs)
         toks, logits = adapter.draft(h[:, -1], b.inputs[:, -1])
     assert toks.shape == (2, 1) and logits.shape == (2, 1, 120)
+
+
+def test_fp8_block_quantiser_round_trip_and_layout():
+    from cppmega_mlx_b200.v4 import moe_fp8 as F8
+    torch.manual_seed(0)
+    w = torch.randn(200, 300) * torch.linspace(0.01, 3.0, 300)
+    q, s = F8.quantize_linear_to_fp8(w)
+    assert q.dtype == torch.float8_e4m3fn and q.shape == w.shape and s.shape == (2, 3) and s.dtype == torch.float32
+    assert torch.allclose(s[0, 0], w[:128, :128].abs().max() / 448.0)
+    back = F8.dequantize_fp8_blocks_reference(q, s, torch.float32)
+    blocks_max = s.repeat_interleave(128, 0)[:200].repeat_interleave(128, 1)[:, :300] * 448.0
+    assert ((back - w).abs() <= blocks_max * 2 ** -4 + 1e-7).all()        # e4m3: 3 mantissa bits → half-ulp 2^-4 of the block max
+    assert F8.quantize_linear_to_fp8(torch.zeros(4, 4))[1].item() == pytest.approx(1e-6 / 448.0)
+    stacked_q, stacked_s = F8.quantize_linear_to_fp8(torch.stack([w, 2 * w]))
+    assert torch.equal(stacked_q[0].view(torch.uint8), q.view(torch.uint8)) and torch.allclose(stacked_s[1], 2 * s)
+
+
+def test_fp8_linear_and_ste_master_weight_step():
+    from cppmega_mlx_b200.nn.basic import Linear
+    from cppmega_mlx_b200.v4 import moe_fp8 as F8
+    torch.manual_seed(1)
+    lin = Linear(256, 192)
+    x = torch.randn(5, 256)
+    f8 = F8.FP8Linear.from_linear(lin)
+    assert not list(f8.parameters()) and f8.weight_fp8.element_size() == 1
+    ref = lin(x)
+    assert (f8(x) - ref).abs().max() < 5e-2 * ref.abs().max()
+    # bf16/fp32 master weight, fp8 forward: the gradient lands on the master and a step lowers the loss
+    opt = torch.optim.SGD(lin.parameters(), lr=0.05)
+    losses = []
+    for _ in range(3):
+        loss = torch.nn.functional.linear(x, F8.fp8_roundtrip_ste(lin.weight)).square().mean()
+        opt.zero_grad()
+        loss.backward()
+        assert lin.weight.grad is not None and lin.weight.grad.abs().sum() > 0
+        opt.step()
+        losses.append(float(loss.detach()))
+    assert losses[-1] < losses[0]
+
+
+def test_convert_moe_to_fp8_keeps_the_layer_function_and_halves_expert_bytes():
+    from cppmega_mlx_b200.nn.moe import MoE, MoEConfig
+    from cppmega_mlx_b200.v4 import moe_fp8 as F8
+    torch.manual_seed(2)
+    cfg = MoEConfig(d_model=128, num_experts=4, top_k=2, expert_hidden_size=256, shared_expert_hidden_size=128)
+    moe = MoE(cfg).eval()
+    x = torch.randn(2, 6, 128)
+    with torch.no_grad():
+        ref = moe(x).output
+        before = sum(p.numel() * p.element_size() for p in moe.experts.parameters())
+        F8.convert_moe_to_fp8(moe)
+        got = moe(x).output
+        dense = moe.dense_reference_forward(x)
+    assert isinstance(moe.experts, F8.FP8GroupedExperts) and isinstance(moe.shared_expert, F8.FP8FeedForwardExpert)
+    assert moe.experts.stored_bytes() < before * 0.27          # fp32 → one byte per weight plus block scales
+    assert (got - ref).abs().max() < 6e-2 * ref.abs().max()
+    assert torch.allclose(got, dense, atol=1e-4, rtol=1e-3)
+    assert "experts.w_gate_up_fp8" in moe.state_dict() and "experts.w_down_scale_inv" in moe.state_dict()
