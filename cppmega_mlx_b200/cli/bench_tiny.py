@@ -20,7 +20,10 @@ def measure(args) -> "BaselineRow":
     cfg = TrainHybridTinyConfig(steps=args.steps, batch_size=args.batch_size, seq_len=args.seq_len, hidden_size=args.hidden_size,
                                 pattern=args.pattern, depth=len(args.pattern), num_attention_heads=args.heads, dtype=args.dtype,
                                 optimizer=args.optimizer, loss_backend=args.loss_backend, seed=args.seed)
-    rep = run(cfg)
+    cfg.validate()
+    from ..ops import _backend as B
+    with B.use_kernels(args.path == "kernels"):
+        rep = run(cfg)
     if rep.get("status") != "ok":
         raise RuntimeError(f"trainer failed: {rep.get('error')}")
     rates = [m["tokens_per_second"] for m in rep["metrics"][args.warmup:]]
@@ -28,7 +31,7 @@ def measure(args) -> "BaselineRow":
         raise ValueError("steps must exceed warmup")
     model = f"hybrid {args.pattern} d{args.hidden_size} h{args.heads} ({rep['parameter_count']} parameters)"
     workload = {"model": model, "global_batch": args.batch_size, "seq_len": args.seq_len, "dtype": args.dtype,
-                "optimizer": args.optimizer, "n_gpus": 1 if rep["device"].startswith("cuda") else 0, "parallelism": "single"}
+                "optimizer": args.optimizer, "loss_backend": args.loss_backend, "path": args.path, "n_gpus": 1 if rep["device"].startswith("cuda") else 0, "parallelism": "single"}
     from .. import __version__ as pkg_version
     software = {"torch": torch.__version__, "cuda": torch.version.cuda, "package": pkg_version}
     hardware = torch.cuda.get_device_name(0) if rep["device"].startswith("cuda") else f"cpu:{platform.machine()}"
@@ -52,6 +55,8 @@ def main(argv=None) -> int:
     ap.add_argument("--optimizer", default="adamw")
     ap.add_argument("--loss-backend", default="cross_entropy")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--path", choices=["kernels", "eager"], default="kernels",
+                    help="eager: the same model with the kernel library switched off (PyTorch ops only)")
     ap.add_argument("--archive", help="directory to store the row in (one JSON per row + index.json)")
     ap.add_argument("--compare-to", help="directory of archived rows to compare with")
     ap.add_argument("--min-ratio", type=float, help="fail (exit 3) when a matched comparison falls below this ratio")

@@ -194,7 +194,9 @@ def build_optimizer(cfg: TrainHybridTinyConfig, model, world: int):
             return O.make_lion(params, learning_rate=lr, weight_decay=wd)
         if o == "adam8bit":
             return make_adam8bit(params, learning_rate=lr, weight_decay=wd)
-        return make_lion8bit(params, learning_rate=lr, weight_decay=wd)
+        if o == "lion8bit":
+            return make_lion8bit(params, learning_rate=lr, weight_decay=wd)
+        raise ValueError(f"optimizer must be one of {OPTIMIZERS}")
     if world > 1:
         from ..training.distributed_optimizer import DistributedZeRO1Optimizer
         return DistributedZeRO1Optimizer(model, factory, comm=cfg.comm)

@@ -133,3 +133,25 @@ def test_bench_tiny_archives_and_refuses_unmatched_comparisons(capsys, tmp_path)
                                      "--min-ratio", "0.05"], capsys)
     cmp = json.loads(out[-1])["comparisons"]
     assert rc == 3 and cmp[0]["status"] == "refused" and "global_batch" in cmp[0]["reason"]   # no matched row → gate fails closed
+
+
+def test_bench_matrix_runs_cells_in_fresh_processes_and_renders(tmp_path):
+    from cppmega_mlx_b200.cli import bench_matrix as BM
+    dry = subprocess.run([sys.executable, "-m", "cppmega_mlx_b200.cli.bench_matrix", "--dry-run", "--optimizers", "adamw,lion"],
+                         capture_output=True, text=True, cwd=ROOT)
+    rep = json.loads(dry.stdout.strip().splitlines()[-1])
+    assert rep["status"] == "dry_run" and rep["cells"] == 4 and all("bench_tiny" in c for c in rep["commands"])
+    out = tmp_path / "m"
+    run = subprocess.run([sys.executable, "-m", "cppmega_mlx_b200.cli.bench_matrix", "--optimizers", "adamw,nonsense", "--paths", "eager",
+                          "--pattern", "AM", "--steps", "4", "--warmup", "1", "--out-dir", str(out)], capture_output=True, text=True, cwd=ROOT)
+    rep = json.loads(run.stdout.strip().splitlines()[-1])
+    assert run.returncode == 1 and rep["status"] == "partial" and rep["failed"] == 1      # the bad cell is kept, with its error
+    good, bad = rep["matrix"]
+    assert good["status"] == "ok" and good["tokens_per_second"] > 0 and bad["status"] == "error" and "optimizer" in bad["error"]
+    assert "| float32 | adamw | cross_entropy | eager |" in (out / "matrix.md").read_text()
+    page = (out / "matrix.html").read_text()
+    assert page.startswith("<!doctype html>") and "adamw" in page and 'class="bad"' in page
+    cells = [{"dtype": "f", "optimizer": "o", "loss_backend": "l", "path": "kernels", "status": "ok", "tokens_per_second": 30.0},
+             {"dtype": "f", "optimizer": "o", "loss_backend": "l", "path": "eager", "status": "ok", "tokens_per_second": 10.0}]
+    BM.add_ratios(cells)
+    assert cells[0]["ratio_vs_eager"] == 3.0 and "ratio_vs_eager" not in cells[1]
