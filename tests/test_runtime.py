@@ -115,3 +115,40 @@ def test_step_watchdog():
         w.check(now=w.last_time + 6.0)
     w.progress(2)
     w.check()
+
+
+def test_lint_rules_fire_and_the_package_is_clean(tmp_path):
+    import os
+    from cppmega_mlx_b200.runtime.lint import lint_paths, lint_source
+    hot = tmp_path / "nn"
+    hot.mkdir()
+    bad = hot / "layer.py"
+    bad.write_text(
+        "import triton\n"
+        "import torch\n"
+        "class L:\n"
+        "    def forward(self, x):\n"
+        "        n = x.sum().item()\n"
+        "        m = x.max().item()  # lint: allow HS001 needed for the test\n"
+        "        torch.cuda.synchronize()\n"
+        "        return x * n * m\n"
+        "    def helper(self, x):\n"
+        "        return x.tolist()\n"
+        "def f():\n"
+        "    try:\n"
+        "        pass\n"
+        "    except:\n"
+        "        pass\n"
+        "    import os, subprocess\n"
+        "    os.environ['MASTER_ADDR'] = 'localhost'\n"
+        "    subprocess.run(['pkill', '-f', 'python'])\n"
+        "    return torch.compile(f)\n")
+    rules = sorted((v.rule, v.line) for v in lint_paths([str(tmp_path)]))
+    assert rules == [("CL001", 1), ("CL001", 19), ("EX001", 14), ("HS001", 5), ("HS001", 7), ("PK001", 18), ("RZ001", 17)]
+    # the same sync outside a hot directory, or outside a hot function, is not flagged
+    assert not lint_source("def forward(x):\n    return x.item()\n", "cli/tool.py")
+    assert not lint_source("import torch.distributed as d\nd.init_process_group('gloo', init_method='tcp://127.0.0.1:29500')\n", "x.py")
+    assert [v.rule for v in lint_source("import torch.distributed as d\nd.init_process_group('gloo', init_method='tcp://myhost:1')\n", "x.py")] == ["RZ001"]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    found = lint_paths([os.path.join(root, "cppmega_mlx_b200"), os.path.join(root, "bench.py"), os.path.join(root, "__graft_entry__.py")])
+    assert not found, "\n".join(map(str, found))
