@@ -114,6 +114,10 @@ class DistributedZeRO1Optimizer:
             self.flat = FlatBuffers(self.named, self.owners, self.world, alloc=alloc)
             from ..parallel.consistency import check_rank_consistency
             check_rank_consistency(self.named, slots=self.flat.slots, group=group, what="ZeRO-1 flat-buffer layouts")
+            from ..runtime.memory_audit import audit_grad_buffer_aliasing
+            clash = audit_grad_buffer_aliasing(self.named)["overlaps"]      # host-side pointer arithmetic, once per run
+            if clash:
+                raise RuntimeError(f"flat ZeRO-1 storage: {len(clash)} overlapping tensors, first {clash[0]}")
             if self._fused is not None:
                 self._fused.bind(self.flat)
         self.inner = inner_factory(self.owned if self.world > 1 else self.named)

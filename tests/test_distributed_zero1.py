@@ -91,3 +91,24 @@ def test_rank_consistency_check_passes_and_names_the_first_difference():
     diff = run_ranks(_consistency, 2, True)
     for r in diff:                                   # raised on every rank, pointing at the entry
         assert r.startswith("error:") and "b.weight" in r and "entry 1" in r
+
+
+def test_flat_buffers_alias_nothing_and_the_audit_sees_a_planted_overlap():
+    from cppmega_mlx_b200.runtime.memory_audit import audit_grad_buffer_aliasing
+    from cppmega_mlx_b200.training.distributed_optimizer import FlatBuffers
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(12, 7), torch.nn.Linear(7, 5), torch.nn.Linear(5, 3))
+    named = list(model.named_parameters())
+    owners = {n: i % 2 for i, (n, _) in enumerate(named)}
+    FlatBuffers(named, owners, 2)
+    rep = audit_grad_buffer_aliasing(model)
+    assert rep["tensors"] == 12 and rep["overlaps"] == [] and rep["flat_storages"] == 2     # params buffer and grads buffer
+    # plant a wrong slot: the second layer's bias now sits on top of the first layer's weight
+    w = model[0].weight
+    model[1].bias.data = w.data.view(-1)[3:10]
+    rep = audit_grad_buffer_aliasing(model)
+    assert [(a, b) for a, b, _ in rep["overlaps"]] == [("0.weight", "1.bias")] and rep["overlaps"][0][2] == 7 * 4
+    # tied weights are one tensor, not an overlap
+    tied = torch.nn.Sequential(torch.nn.Linear(4, 4, bias=False), torch.nn.Linear(4, 4, bias=False))
+    tied[1].weight = tied[0].weight
+    assert audit_grad_buffer_aliasing(tied)["overlaps"] == []
