@@ -166,11 +166,17 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
+    marks = []
     for i in range(args.steps):
         stepper(dev_batches[args.warmup + i])
+        marks.append(torch.cuda.Event(enable_timing=True))
+        marks[-1].record()                      # per-step spread (this rank); the headline number stays the whole bracket
     e1.record()
     barrier()
     ms = max_over_ranks(e0.elapsed_time(e1))
+    per_step = sorted(a.elapsed_time(b) for a, b in zip([e0] + marks[:-1], marks))
+    spread = {"median": per_step[len(per_step) // 2], "p10": per_step[int(0.1 * (len(per_step) - 1))],
+              "p90": per_step[int(round(0.9 * (len(per_step) - 1)))], "min": per_step[0], "max": per_step[-1]}
     launches = B.launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else {}
     B.check_status()
@@ -206,7 +212,7 @@ def main():
                        "params": nparams, "global_batch": mb * dp, "seq_len": S, "parallelism": f"dp{dp} zero1 ({comm if args.tp == 1 else 'nccl'})" + (f" ep{args.ep}" if args.ep > 1 else "") + (f" tp{args.tp} (dense FFNs)" if args.tp > 1 else ""),
                        "optimizer": args.optimizer, "expert_gemm": args.expert_gemm, "micro_batch_per_gpu": mb, "grad_checkpoint": ckpt,
                        "l2": "working set per step (weights + activations, tens of GB) far exceeds the 126 MB L2; no flush needed"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "step_ms": spread,
         }
         if comm == "stub":
             out["invalid"] = "communication disabled: this line only serves to measure exposed communication time"
