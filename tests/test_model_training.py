@@ -238,3 +238,35 @@ def test_moe_sorted_dispatch_equals_dense_reference_and_bias_update():
             moe.router.expert_bias.fill_(0.0)
             w_a = moe(x).router.top_weights
             assert torch.isfinite(w_a).all()
+
+
+def test_external_trainer_adapter_probe_batch_mapping_and_refusal():
+    import types
+    from cppmega_mlx_b200.data.batch import LMTokenBatch
+    from cppmega_mlx_b200.training import external_trainer_adapter as X
+    # a stand-in trainer module: one API complete, one with a missing parameter, one absent
+    fake = types.ModuleType("fake_trainer_mod")
+    fake.__version__ = "0.0"
+    fake.Trainer = lambda model, args, train_dataset, eval_dataset, data_collator: None
+    fake.TrainingArguments = lambda per_device_train_batch_size, max_steps: None
+    import sys
+    sys.modules["fake_trainer_mod"] = fake
+    try:
+        info = X.describe_external_trainer_apis("fake_trainer_mod")
+    finally:
+        del sys.modules["fake_trainer_mod"]
+    assert info.available and info.missing_apis == ("DataCollatorForLanguageModeling",) and info.incompatible_apis == ("TrainingArguments",)
+    assert "train_dataset" in info.api_signatures["Trainer"] and not info.integration_supported
+    assert not X.describe_external_trainer_apis("no_such_trainer_module_anywhere").available
+    toks = torch.tensor([[5, 6, 7, 8], [9, 10, 0, 0]])
+    mask = torch.tensor([[1, 1, 1, 1], [1, 1, 0, 0]])
+    batch = LMTokenBatch(tokens=toks, attention_mask=mask, structure_ids=torch.zeros_like(toks), document_ids=torch.ones_like(toks))
+    dense = X.as_dense_trainer_batch(batch)
+    assert tuple(dense) == X.DENSE_BATCH_KEYS and torch.equal(dense["input_ids"], toks)
+    assert dense["labels"][1].tolist() == [9, 10, -100, -100] and torch.equal(dense["attention_mask"], mask)
+    meta = X.describe_batch_route_metadata(batch)
+    assert meta.dropped == ("structure_ids", "document_ids") and meta.has_attention_mask and (meta.batch_size, meta.seq_len) == (2, 4)
+    with pytest.raises(X.ExternalTrainerIntegrationUnsupported, match="unsupported"):
+        X.require_supported_external_trainer_integration(info)
+    with pytest.raises(ValueError):
+        X.as_dense_trainer_batch({"tokens": torch.tensor([[1, -2, 3]])})
