@@ -247,6 +247,51 @@ def bench_sparse_mla(args) -> list[dict]:
     return rows
 
 
+def bench_linears(args) -> list[dict]:
+    """Decode-step linears for 1–32 activation rows: the CUDA-core streaming kernel (≤ 8 rows), the warp-MMA streaming kernel
+    (≤ 32 rows), the 128-row tcgen05 GEMM and cuBLAS (``F.linear``), each as a CUDA graph of calls over a rotation of weight
+    matrices larger than the L2, so the figures are device time per call without host launch latency."""
+    from cppmega_mlx_b200.ops import gemm as G
+    pk = peaks()
+    dev = "cuda"
+    rows = []
+    for N, K, label in ((2048, 2048, "attn out"), (11264, 2048, "ffn up"), (2048, 5632, "ffn down"), (10464, 2048, "mamba in_proj"),
+                        (65536, 2048, "lm_head")):
+        ws = [torch.randn(N, K, device=dev).bfloat16() for _ in range(max(2, (400 << 20) // (N * K * 2)))]
+        for M in (1, 2, 8, 16, 32):
+            name = f"linear {label} M{M} N{N} K{K}"
+            if args.only and args.only != name:
+                continue
+            x = torch.randn(M, K, device=dev).bfloat16()
+            cands = {"cublas": lambda w: torch.nn.functional.linear(x, w), "tcgen05_gemm": lambda w: G.gemm_raw(x, w),
+                     "warp_mma": lambda w: G.skinny_mma_linear(x, w)}
+            if M <= G.SKINNY_MAX_ROWS:
+                cands["cuda_core"] = lambda w: G.skinny_linear(x, w)
+            row = {"op": name, "weight_mb": N * K * 2 / 1e6}
+            for cname, fn in cands.items():
+                with torch.no_grad():
+                    for w in ws[:2]:
+                        fn(w)
+                    torch.cuda.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        for w in ws:
+                            fn(w)
+                ms = time_cuda(graph.replay, iters=max(args.iters, 10), warmup=args.warmup, flush=False) / len(ws)
+                row[cname + "_us"] = ms * 1e3
+                row[cname + "_gbs"] = N * K * 2 / ms / 1e6
+                del graph
+            best = min((k for k in row if k.endswith("_us")), key=lambda k: row[k])
+            row["best"] = best[:-3]
+            row["best_frac_of_measured_hbm"] = row[best[:-3] + "_gbs"] / pk["hbm_gbs"]
+            rows.append(row)
+            print(json.dumps(row), flush=True)
+        del ws
+    B_ = __import__("cppmega_mlx_b200.ops._backend", fromlist=["x"])
+    B_.check_status()
+    return rows
+
+
 def bench_dsa_loss(args) -> list[dict]:
     """DSA indexer KL loss, forward + gradient with respect to the index scores, at the flagship attention shape (B4 S4096, 16
     latent-query heads of width 576, top-2048 keys) against the same loss written with PyTorch ops."""
@@ -523,7 +568,7 @@ def bench_serving(args) -> list[dict]:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "dsa_loss", "decode", "decode_loop", "serving", "decode_trace", "decode_profile", "step_profile", "all"])
+    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "dsa_loss", "linears", "decode", "decode_loop", "serving", "decode_trace", "decode_profile", "step_profile", "all"])
     ap.add_argument("--json", default=None)
     ap.add_argument("--only", default=None, help="run the single case with this label (small captures under a profiler)")
     ap.add_argument("--iters", type=int, default=10)
@@ -544,6 +589,8 @@ def main(argv=None) -> int:
         rows += bench_sparse_mla(args)
     if args.op in ("dsa_loss", "all"):
         rows += bench_dsa_loss(args)
+    if args.op in ("linears", "all"):
+        rows += bench_linears(args)
     if args.op in ("decode", "all"):
         rows += bench_decode(args)
     if args.op in ("decode_loop", "all"):

@@ -160,6 +160,22 @@ def skinny_linear(x2: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None =
     return y if bias is None or bias.dtype == torch.bfloat16 else y + bias
 
 
+MMA_MIN_ROWS, MMA_MAX_ROWS = 2, 32    # rows served by the warp-MMA weight-streaming kernel (below: the CUDA-core kernel)
+
+
+def skinny_mma_linear(x2: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """[M ≤ 32, K] × [N, K]ᵀ without autograd: ``csrc/skinny_mma.cu`` (split-contraction warps, fp32 accumulation)."""
+    lib = B.load_library()
+    M, K = x2.shape
+    N = w.shape[0]
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=x2.device)
+    ll = ctypes.c_longlong
+    B.check(lib.cmb_skinny_mma(B.ptr(x2), ll(x2.stride(0)), B.ptr(w), ll(w.stride(0)), B.ptr(y), ll(N),
+                               B.ptr(bias if bias is not None and bias.dtype == torch.bfloat16 else None), M, N, K, B.stream_ptr()),
+            "skinny_mma")
+    return y if bias is None or bias.dtype == torch.bfloat16 else y + bias
+
+
 SMALL_M_MAX_ROWS = 0   # dispatch threshold for small_m_linear; 0 = off: measured on the 1B decode step (batch 8 and 32) the
                        # split-contraction route (GEMM + reduction + transpose) did not beat the skinny kernel / the plain GEMM
 _split_ranges: dict[tuple, torch.Tensor] = {}
@@ -201,14 +217,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -
             and w.is_contiguous() and w.shape[0] >= 1024 and not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad))):
         y = small_m_linear(x.reshape(rows, x.shape[-1]).contiguous(), w).reshape(*x.shape[:-1], w.shape[0])
         return y if bias is None else y + bias
-    if (_kernel_ok(x, w) and x.numel() > 0 and x.shape[-1] == w.shape[1] and x.numel() // x.shape[-1] <= SKINNY_MAX_ROWS
+    if (_kernel_ok(x, w) and x.numel() > 0 and x.shape[-1] == w.shape[1] and rows <= max(SKINNY_MAX_ROWS, MMA_MAX_ROWS)
             and w.shape[1] % 8 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0
             and not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad))):
         x2 = x.reshape(-1, x.shape[-1])
         if x2.stride(1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16 or w.data_ptr() % 16:
             x2 = x2.contiguous()
         if x2.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
-            return skinny_linear(x2, w, bias).view(*x.shape[:-1], w.shape[0])
+            if MMA_MIN_ROWS <= rows <= MMA_MAX_ROWS:
+                return skinny_mma_linear(x2, w, bias).view(*x.shape[:-1], w.shape[0])
+            if rows <= SKINNY_MAX_ROWS:
+                return skinny_linear(x2, w, bias).view(*x.shape[:-1], w.shape[0])
     if (_kernel_ok(x, w) and w.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and w.is_contiguous()
             and x.shape[-1] == w.shape[1] and x.numel() > 0):
         y = _LinearFn.apply(x, w)

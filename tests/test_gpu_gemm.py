@@ -113,6 +113,26 @@ def test_skinny_linear_matches_fp32(M, N, K, bias):
     assert ops.linear(xr, w).requires_grad
 
 
+@pytest.mark.parametrize("M,N,K,bias", [(2, 2048, 2048, False), (8, 1000, 5632, True), (16, 65536, 2048, False), (17, 2048, 5632, True),
+                                        (32, 11264, 2048, False), (5, 24, 4104, False), (31, 9480, 40, True), (1, 4096, 2048, False)])
+def test_skinny_mma_linear_matches_fp32(M, N, K, bias):
+    """2–32 activation rows: warp-MMA weight streaming with the contraction split over the warps of a CTA."""
+    from cppmega_mlx_b200.ops import gemm as G
+    torch.manual_seed(M * 7 + N)
+    x = torch.randn(2, M, K, device="cuda").bfloat16()[1]
+    w = torch.randn(N + 3, K, device="cuda").bfloat16()[3:]         # a row-offset view (still 16-byte aligned rows)
+    bvec = torch.randn(N, device="cuda").bfloat16() if bias else None
+    with torch.no_grad():
+        y = G.skinny_mma_linear(x, w, bvec)
+    ref = x.float() @ w.float().t() + (bvec.float() if bias else 0)
+    assert y.shape == (M, N) and y.dtype == torch.bfloat16
+    assert (y.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
+    if G.MMA_MIN_ROWS <= M <= G.MMA_MAX_ROWS:                       # and ``linear`` routes these row counts here
+        from cppmega_mlx_b200 import ops
+        with torch.no_grad():
+            assert torch.equal(ops.linear(x, w, bvec), y)
+
+
 @pytest.mark.parametrize("M,N,K", [(9, 2048, 5632), (32, 11264, 2048), (64, 2048, 2048), (33, 4096, 320)])
 def test_small_m_linear_split_k_matches_fp32(M, N, K):
     """Swapped operands + contraction split over the GPU (fp32 partial sums) for a few dozen activation rows."""
