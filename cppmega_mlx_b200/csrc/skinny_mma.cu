@@ -1,9 +1,9 @@
 // y[M,N] = x[M,K]·W[N,K]ᵀ (+bias) for 2 ≤ M ≤ 32 activation rows: the decode-step linear for small batches (sm_100a).
 //
 // The work is a weight stream (every weight byte is used once), so the kernel is organised around keeping 16-byte weight
-// loads in flight on every SM rather than around a large MMA tile: a CTA of eight warps owns 8·NT output columns and the
-// warps split the contraction between them in interleaved 32-element chunks (split-K inside the CTA, folded through shared
-// memory at the end), which gives N/(8·NT) CTAs even for the narrow projections (N = 2048 → 128 CTAs at NT = 2).  Each lane
+// loads in flight on every SM rather than around a large MMA tile: a warp owns 8·NT output columns, and KS warps of a
+// CTA share one column group and split its contraction in interleaved 32-element chunks (folded through shared memory at the
+// end); KS is chosen at launch so that even the narrow projections put about a dozen warps on every SM.  Each lane
 // loads 8 consecutive bf16 of one weight row and of two activation rows per chunk; those 8 values feed two
 // `mma.sync.m16n8k16` instructions — the contraction index inside a chunk is permuted (the same way for both operands, which
 // leaves the sum unchanged) so that one 16-byte load is exactly one lane's fragment pair.  Accumulation is fp32.
@@ -34,16 +34,19 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   return v;
 }
 
-// MT: 16-row activation tiles (1 → M ≤ 16, 2 → M ≤ 32).  NT: 8-column weight tiles per CTA.
-template <int MT, int NT>
-__global__ void __launch_bounds__(SM_THREADS) skinny_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+// MT: 16-row activation tiles (1 → M ≤ 16, 2 → M ≤ 32).  NT: 8-column weight tiles per warp.  KS: warps that share one
+// column group and split its contraction (a CTA holds 8 / KS column groups).
+template <int MT, int NT, int KS>
+__global__ void __launch_bounds__(SM_THREADS, 2) skinny_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                                                 const __nv_bfloat16* __restrict__ w, long long ldw,
                                                                 __nv_bfloat16* __restrict__ y, long long ldy,
                                                                 const __nv_bfloat16* __restrict__ bias, int M, int N, int K) {
-  __shared__ float red[SM_WARPS][MT][NT][32][4];
+  constexpr int GROUPS = SM_WARPS / KS;
+  __shared__ float red[KS > 1 ? SM_WARPS : 1][MT][NT][32][4];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * 8 * NT;
+  const int kslice = warp % KS, group = warp / KS;
+  const int n0 = (blockIdx.x * GROUPS + group) * 8 * NT;
   float acc[MT][NT][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
@@ -71,8 +74,8 @@ __global__ void __launch_bounds__(SM_THREADS) skinny_mma_kernel(const __nv_bfloa
       xrow[mt][hf] = x + static_cast<long long>(xok[mt][hf] ? m : 0) * ldx + t * 8;
     }
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll 2
-  for (int k0 = warp * 32; k0 < K; k0 += SM_WARPS * 32) {
+#pragma unroll(MT == 2 ? 2 : 4)
+  for (int k0 = kslice * 32; k0 < K; k0 += KS * 32) {
     const bool kok = k0 + t * 8 < K;      // K is a multiple of 8, so a lane's 8 values are all inside or all outside
     uint4 wb[NT], xa[MT][2];
 #pragma unroll
@@ -89,25 +92,64 @@ __global__ void __launch_bounds__(SM_THREADS) skinny_mma_kernel(const __nv_bfloa
         mma_bf16_16816(acc[mt][nt], xa[mt][0].z, xa[mt][1].z, xa[mt][0].w, xa[mt][1].w, wb[nt].z, wb[nt].w);
       }
   }
+  if (KS > 1) {
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) red[warp][mt][nt][lane][i] = acc[mt][nt][i];
+    __syncthreads();
+    if (kslice != 0) return;
+    // the first warp of each column group folds the other contraction slices into its own accumulators
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float s = acc[mt][nt][i];
+#pragma unroll
+          for (int ks = 1; ks < KS; ++ks) s += red[warp + ks][mt][nt][lane][i];
+          acc[mt][nt][i] = s;
+        }
+  }
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) red[warp][mt][nt][lane][i] = acc[mt][nt][i];
-  __syncthreads();
-  // fold the eight contraction slices; thread i takes fragment element i of (mt, nt, lane)
-  for (int e = threadIdx.x; e < MT * NT * 32 * 4; e += SM_THREADS) {
-    const int i = e & 3, ln = (e >> 2) & 31, nt = (e >> 7) % NT, mt = (e >> 7) / NT;
-    float s = 0.f;
-#pragma unroll
-    for (int wv = 0; wv < SM_WARPS; ++wv) s += red[wv][mt][nt][ln][i];
-    const int m = mt * 16 + (ln >> 2) + ((i >> 1) << 3);
-    const int n = n0 + nt * 8 + (ln & 3) * 2 + (i & 1);
-    if (m < M && n < N) {
-      if (bias != nullptr) s += __bfloat162float(bias[n]);
-      y[static_cast<long long>(m) * ldy + n] = __float2bfloat16(s);
-    }
+      for (int hf = 0; hf < 2; ++hf) {
+        const int m = mt * 16 + hf * 8 + g;
+        const int n = n0 + nt * 8 + t * 2;
+        if (m >= M || n >= N) continue;
+        float c0 = acc[mt][nt][2 * hf], c1 = acc[mt][nt][2 * hf + 1];
+        __nv_bfloat16* dst = y + static_cast<long long>(m) * ldy + n;
+        if (n + 1 < N) {
+          if (bias != nullptr) { c0 += __bfloat162float(bias[n]); c1 += __bfloat162float(bias[n + 1]); }
+          if ((reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
+            *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(c0, c1);
+          } else {
+            dst[0] = __float2bfloat16(c0);
+            dst[1] = __float2bfloat16(c1);
+          }
+        } else {
+          if (bias != nullptr) c0 += __bfloat162float(bias[n]);
+          dst[0] = __float2bfloat16(c0);
+        }
+      }
+}
+
+template <int MT, int NT>
+static void launch_skinny_mma(int ks, unsigned tiles, cudaStream_t st, const __nv_bfloat16* X, long long ldx, const __nv_bfloat16* W,
+                              long long ldw, __nv_bfloat16* Y, long long ldy, const __nv_bfloat16* Bv, int M, int N, int K) {
+  const unsigned groups = SM_WARPS / ks;
+  const unsigned grid = (tiles + groups - 1) / groups;
+  switch (ks) {
+    case 1: skinny_mma_kernel<MT, NT, 1><<<grid, SM_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, M, N, K); break;
+    case 2: skinny_mma_kernel<MT, NT, 2><<<grid, SM_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, M, N, K); break;
+    case 4: skinny_mma_kernel<MT, NT, 4><<<grid, SM_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, M, N, K); break;
+    default: skinny_mma_kernel<MT, NT, 8><<<grid, SM_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, M, N, K); break;
   }
 }
 
@@ -124,15 +166,19 @@ extern "C" int cmb_skinny_mma(const void* x, long long ldx, const void* w, long 
   auto W = static_cast<const __nv_bfloat16*>(w);
   auto Y = static_cast<__nv_bfloat16*>(y);
   auto Bv = static_cast<const __nv_bfloat16*>(bias);
-  const bool wide = N >= 32 * 2 * 148;     // enough columns for two waves of 32-column CTAs: halve the activation re-reads
-  const int cols = wide ? 32 : 16;
-  const unsigned grid = static_cast<unsigned>((N + cols - 1) / cols);
+  // Columns per warp: more columns amortise the activation loads (which matter most with two row tiles), fewer give narrow
+  // matrices enough warps.  Contraction split: the smallest power of two that puts about twelve warps on every SM.
+  const int nt = (M > 16 && N >= 8192) ? 4 : (N >= 4096 || M > 16 ? 2 : 1);
+  const unsigned tiles = static_cast<unsigned>((N + 8 * nt - 1) / (8 * nt));
+  int ks = 1;
+  while (ks < 8 && tiles * ks < 148u * 12u && K / (ks * 2) >= 256) ks *= 2;
   if (M <= 16) {
-    if (wide) cmb::skinny_mma_kernel<1, 4><<<grid, cmb::SM_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, M, N, K);
-    else cmb::skinny_mma_kernel<1, 2><<<grid, cmb::SM_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, M, N, K);
+    if (nt == 4) cmb::launch_skinny_mma<1, 4>(ks, tiles, st, X, ldx, W, ldw, Y, ldy, Bv, M, N, K);
+    else if (nt == 2) cmb::launch_skinny_mma<1, 2>(ks, tiles, st, X, ldx, W, ldw, Y, ldy, Bv, M, N, K);
+    else cmb::launch_skinny_mma<1, 1>(ks, tiles, st, X, ldx, W, ldw, Y, ldy, Bv, M, N, K);
   } else {
-    if (wide) cmb::skinny_mma_kernel<2, 4><<<grid, cmb::SM_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, M, N, K);
-    else cmb::skinny_mma_kernel<2, 2><<<grid, cmb::SM_THREADS, 0, st>>>(X, ldx, W, ldw, Y, ldy, Bv, M, N, K);
+    if (nt == 4) cmb::launch_skinny_mma<2, 4>(ks, tiles, st, X, ldx, W, ldw, Y, ldy, Bv, M, N, K);
+    else cmb::launch_skinny_mma<2, 2>(ks, tiles, st, X, ldx, W, ldw, Y, ldy, Bv, M, N, K);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
