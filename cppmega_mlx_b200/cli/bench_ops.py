@@ -468,17 +468,17 @@ def decode_trace(args) -> list[dict]:
 
 
 def decode_profile(args) -> list[dict]:
-    """Kernel-time breakdown of one decode step of the 1B hybrid at batch 1 (torch.profiler over four eagerly launched static
-    steps; an analysis aid — the figures include profiler overhead and are not benchmark values)."""
+    """Kernel-time breakdown of one decode step of the 1B hybrid at batch ``--batch`` (default 1; torch.profiler over four eagerly
+    launched static steps; an analysis aid — the figures include profiler overhead and are not benchmark values)."""
     from torch.profiler import ProfilerActivity, profile
 
     from cppmega_mlx_b200 import inference as I
     from cppmega_mlx_b200.recipes.model_factory import get_model_profile
     torch.manual_seed(0)
     model = get_model_profile("hybrid_1b").build_model(dtype=torch.bfloat16, device="cuda").eval()
-    ids = torch.randint(4, 60000, (1, 512), device="cuda")
+    ids = torch.randint(4, 60000, (args.batch, args.prompt), device="cuda")
     with torch.no_grad():
-        g = I.GraphDecodeSession(model, capacity=1024, use_graph=False)
+        g = I.GraphDecodeSession(model, capacity=args.prompt + 512, use_graph=False)
         tok = g.prefill(ids).argmax(-1, keepdim=True)
         for _ in range(3):
             tok = g.step(tok).argmax(-1, keepdim=True)
@@ -488,6 +488,8 @@ def decode_profile(args) -> list[dict]:
                 tok = g.step(tok).argmax(-1, keepdim=True)
             torch.cuda.synchronize()
     ev = sorted([e for e in prof.key_averages() if e.device_time_total > 0], key=lambda e: -e.device_time_total)
+    total = sum(e.device_time_total for e in ev) / 4
+    print(json.dumps({"op": f"decode step B{args.batch} prompt{args.prompt}", "kernel_us_per_step": total}), flush=True)
     rows = [{"op": "decode step kernel", "name": e.key[:100], "us_per_step": e.device_time_total / 4, "launches_per_step": e.count / 4}
             for e in ev[:30]]
     for r in rows:
@@ -575,6 +577,8 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-eager", action="store_true")
     ap.add_argument("--mla-seq", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=1, help="decode_profile: sequences in the batch")
+    ap.add_argument("--prompt", type=int, default=512, help="decode_profile: prompt length")
     args = ap.parse_args(argv)
     rows = []
     if args.op in ("gemm", "all"):

@@ -2,7 +2,7 @@
 //
 // The work is a weight stream (every weight byte is used once), so the kernel is organised around keeping 16-byte weight
 // loads in flight on every SM rather than around a large MMA tile: a warp owns 8·NT output columns, and KS warps of a
-// CTA share one column group and split its contraction in interleaved 32-element chunks (folded through shared memory at the
+// CTA share one column group and split its contraction into contiguous ranges (folded through shared memory at the
 // end); KS is chosen at launch so that even the narrow projections put about a dozen warps on every SM.  Each lane
 // loads 8 consecutive bf16 of one weight row and of two activation rows per chunk; those 8 values feed two
 // `mma.sync.m16n8k16` instructions — the contraction index inside a chunk is permuted (the same way for both operands, which
@@ -74,8 +74,11 @@ __global__ void __launch_bounds__(SM_THREADS, 2) skinny_mma_kernel(const __nv_bf
       xrow[mt][hf] = x + static_cast<long long>(xok[mt][hf] ? m : 0) * ldx + t * 8;
     }
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  // contiguous contraction range per slice, so that a lane's consecutive 16-byte loads walk along one weight row
+  const int chunks = (K + 31) / 32, per = (chunks + KS - 1) / KS;
+  const int k_begin = kslice * per * 32, k_end = min(K, k_begin + per * 32);
 #pragma unroll(MT == 2 ? 2 : 4)
-  for (int k0 = kslice * 32; k0 < K; k0 += KS * 32) {
+  for (int k0 = k_begin; k0 < k_end; k0 += 32) {
     const bool kok = k0 + t * 8 < K;      // K is a multiple of 8, so a lane's 8 values are all inside or all outside
     uint4 wb[NT], xa[MT][2];
 #pragma unroll

@@ -224,7 +224,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -
         if x2.stride(1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16 or w.data_ptr() % 16:
             x2 = x2.contiguous()
         if x2.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
-            if MMA_MIN_ROWS <= rows <= MMA_MAX_ROWS:
+            # measured per shape (``cli.bench_ops linears``): one or two rows stream best through the CUDA-core kernel unless the
+            # matrix is narrow; 17-32 rows against a very wide matrix (the lm_head) are better off on the tcgen05 GEMM
+            n_out = w.shape[0]
+            use_mma = (MMA_MIN_ROWS <= rows <= MMA_MAX_ROWS and not (rows > 16 and n_out >= 32768)) or \
+                (rows < MMA_MIN_ROWS and n_out <= 4096 and MMA_MAX_ROWS > 0)
+            if use_mma:
                 return skinny_mma_linear(x2, w, bias).view(*x.shape[:-1], w.shape[0])
             if rows <= SKINNY_MAX_ROWS:
                 return skinny_linear(x2, w, bias).view(*x.shape[:-1], w.shape[0])
