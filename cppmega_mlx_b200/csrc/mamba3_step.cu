@@ -36,30 +36,36 @@ __device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
 
 // conv + SiLU of channel `ch` of row b (current input from proj, history from conv_prev); also forwards the window.
 // All taps are loaded before any is used (K ≤ 16), so one call costs one memory latency, not one per tap.
+// KC > 0 fixes the kernel width at compile time (the loops below then hold KC taps instead of 16 predicated ones, which is
+// what keeps the register count low enough for every CTA of a 32-sequence batch to be resident at once); KC = 0 reads p.K.
+template <int KC>
 __device__ __forceinline__ float conv_silu_step(const M3StepParams& p, int b, int ch, bool write_window) {
-  const int hist = p.K - 1;
+  constexpr int KMAX = KC > 0 ? KC : 16;
+  const int K = KC > 0 ? KC : p.K;
+  const int hist = K - 1;
   const __nv_bfloat16 cur = p.proj[b * p.ld_proj + p.d_inner + ch];
   const __nv_bfloat16* prev = p.conv_prev + static_cast<long long>(b) * hist * p.C + ch;
-  __nv_bfloat16 v[16], w[16];
+  __nv_bfloat16 v[KMAX], w[KMAX];
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
+  for (int j = 0; j < KMAX; ++j) {
     if (j < hist) v[j] = prev[static_cast<long long>(j) * p.C];
-    if (j < p.K) w[j] = p.conv_w[ch * p.K + j];
+    if (j < K) w[j] = p.conv_w[ch * K + j];
   }
   float acc = p.conv_b != nullptr ? __bfloat162float(p.conv_b[ch]) : 0.f;
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
+  for (int j = 0; j < KMAX; ++j) {
     if (j < hist) {
       acc = fmaf(__bfloat162float(w[j]), __bfloat162float(v[j]), acc);
       if (write_window && j > 0) p.conv_next[(static_cast<long long>(b) * hist + j - 1) * p.C + ch] = v[j];
     }
   }
-  acc = fmaf(__bfloat162float(p.conv_w[ch * p.K + hist]), __bfloat162float(cur), acc);
+  acc = fmaf(__bfloat162float(w[hist]), __bfloat162float(cur), acc);
   if (write_window && hist > 0) p.conv_next[(static_cast<long long>(b) * hist + hist - 1) * p.C + ch] = cur;
   return silu_f(acc);
 }
 
-__global__ void __launch_bounds__(128) mamba3_step_kernel(const M3StepParams p) {
+template <int KC>
+__global__ void __launch_bounds__(128, KC > 0 ? 7 : 2) mamba3_step_kernel(const M3StepParams p) {
   extern __shared__ float sm[];
   float* Bs = sm;             // [N] rotated, scaled B (scan input)
   float* Cr = Bs + p.N;       // [N] rotated C
@@ -73,17 +79,25 @@ __global__ void __launch_bounds__(128) mamba3_step_kernel(const M3StepParams p) 
   const __nv_bfloat16* tail = p.proj + b * p.ld_proj + p.d_inner + p.C;
   const int d_bc = p.G * p.N;
 
-  // ---- per-head and per-group scalars (every thread computes them; a handful of flops)
+  // ---- per-group scalars: one head per thread, folded over the CTA (a group can span all heads)
   float scale_g = 0.f, late_g = 0.f;
-  for (int i = 0; i < hpg; ++i) {
+  for (int i = t; i < hpg; i += 128) {
     const int hh = g * hpg + i;
     const float dth = softplus_f(__bfloat162float(tail[hh]) + __bfloat162float(p.dt_bias[hh]));
     const float sg = sigmoid_f(__bfloat162float(tail[2 * p.H + hh]));
     scale_g += dth * sg;
     late_g += dth * (1.f - sg);
   }
-  scale_g /= hpg;
-  late_g /= hpg;
+  scale_g = warp_sum(scale_g);
+  late_g = warp_sum(late_g);
+  if (lane == 0) {
+    red[warp] = scale_g;
+    red[4 + warp] = late_g;
+  }
+  __syncthreads();
+  scale_g = (red[0] + red[1] + red[2] + red[3]) / hpg;
+  late_g = (red[4] + red[5] + red[6] + red[7]) / hpg;
+  __syncthreads();     // `red` is used again for the norms below
   const float dt_h = softplus_f(__bfloat162float(tail[h]) + __bfloat162float(p.dt_bias[h]));
   const float dt_gh = softplus_f(__bfloat162float(tail[g]) + __bfloat162float(p.dt_bias[g]));   // head index g drives group g's phase
   const float A_h = fminf(-softplus_f(__bfloat162float(tail[p.H + h])), -p.a_floor);
@@ -93,8 +107,8 @@ __global__ void __launch_bounds__(128) mamba3_step_kernel(const M3StepParams p) 
   float ssB = 0.f, ssC = 0.f;
   for (int n = t; n < p.N; n += 128) {
     const bool own = (h % hpg) == 0;   // the first head of a group forwards the group's conv window
-    const float bv = conv_silu_step(p, b, p.d_inner + g * p.N + n, own);
-    const float cv = conv_silu_step(p, b, p.d_inner + d_bc + g * p.N + n, own);
+    const float bv = conv_silu_step<KC>(p, b, p.d_inner + g * p.N + n, own);
+    const float cv = conv_silu_step<KC>(p, b, p.d_inner + d_bc + g * p.N + n, own);
     Bs[n] = bv;
     Cr[n] = cv;
     ssB += bv * bv;
@@ -115,7 +129,7 @@ __global__ void __launch_bounds__(128) mamba3_step_kernel(const M3StepParams p) 
   }
   // ---- x of this head: conv + SiLU (and the head's share of the conv window); v cache
   for (int i = t; i < p.P; i += 128) {
-    const float xv = conv_silu_step(p, b, h * p.P + i, true);
+    const float xv = conv_silu_step<KC>(p, b, h * p.P + i, true);
     xs[i] = xv;
     p.v_next[(static_cast<long long>(b) * p.H + h) * p.P + i] = __float2bfloat16(xv);
   }
@@ -204,6 +218,7 @@ extern "C" int cmb_mamba3_step(const void* const* pp, const int* ip, long long l
   p.k_prev = bf(15), p.k_next = bfm(16), p.v_prev = bf(17), p.v_next = bfm(18), p.y = bfm(19);
   p.a_floor = a_floor, p.eps = eps;
   const size_t smem = (3 * p.N + p.P + 8 + 32 * p.P) * sizeof(float);
-  cmb::mamba3_step_kernel<<<dim3(p.H, B), 128, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  if (p.K == 4) cmb::mamba3_step_kernel<4><<<dim3(p.H, B), 128, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  else cmb::mamba3_step_kernel<0><<<dim3(p.H, B), 128, smem, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
