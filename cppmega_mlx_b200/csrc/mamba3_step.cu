@@ -30,6 +30,10 @@ struct M3StepParams {
   float a_floor, eps;
 };
 
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
@@ -64,9 +68,11 @@ __device__ __forceinline__ float conv_silu_step(const M3StepParams& p, int b, in
   return silu_f(acc);
 }
 
-template <int KC>
+// PRE: the CTA's previous state tile (P·N bf16, the one large read) is fetched into shared memory with cp.async at the very
+// start, so that its latency overlaps the chain of small dependent loads before the update instead of following it.
+template <int KC, bool PRE>
 __global__ void __launch_bounds__(128, KC > 0 ? 7 : 2) mamba3_step_kernel(const M3StepParams p) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   float* Bs = sm;             // [N] rotated, scaled B (scan input)
   float* Cr = Bs + p.N;       // [N] rotated C
   float* kp = Cr + p.N;       // [N] previous rotated B · late factor
@@ -76,6 +82,12 @@ __global__ void __launch_bounds__(128, KC > 0 ? 7 : 2) mamba3_step_kernel(const 
   const int h = blockIdx.x, b = blockIdx.y;
   const int hpg = p.H / p.G, g = h / hpg;
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const long long sbase = (static_cast<long long>(b) * p.H + h) * p.P * p.N;
+  __nv_bfloat16* stile = reinterpret_cast<__nv_bfloat16*>(sm + ((3 * p.N + p.P + 8 + 32 * p.P + 3) & ~3));   // 16-byte aligned
+  if (PRE) {
+    for (int i = t * 8; i < p.P * p.N; i += 128 * 8) cp_async_16(stile + i, p.ssm_prev + sbase + i);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   const __nv_bfloat16* tail = p.proj + b * p.ld_proj + p.d_inner + p.C;
   const int d_bc = p.G * p.N;
 
@@ -163,8 +175,12 @@ __global__ void __launch_bounds__(128, KC > 0 ? 7 : 2) mamba3_step_kernel(const 
   // ---- state update and read-out: warp w owns rows p ≡ w (mod 4); lanes sweep the state dimension
   for (int pr = warp; pr < p.P; pr += 4) ys[pr * 32 + lane] = 0.f;
   const float Dh = __bfloat162float(p.D[h]);
-  const long long sbase = (static_cast<long long>(b) * p.H + h) * p.P * p.N;
   constexpr int RU = 4;   // rows in flight per warp
+  if (PRE) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();      // every thread's pieces of the tile have landed
+  }
+  const __nv_bfloat16* sprev = PRE ? stile : p.ssm_prev + sbase;
   for (int pr0 = warp; pr0 < p.P; pr0 += 4 * RU) {
     for (int n = lane * 2; n < p.N; n += 64) {
       float2 s2[RU];
@@ -173,7 +189,7 @@ __global__ void __launch_bounds__(128, KC > 0 ? 7 : 2) mamba3_step_kernel(const 
       for (int u = 0; u < RU; ++u) {
         const int pr = pr0 + 4 * u;
         if (pr < p.P) {
-          s2[u] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p.ssm_prev + sbase + pr * p.N + n));
+          s2[u] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sprev + pr * p.N + n));
           vp[u] = __bfloat162float(p.v_prev[(static_cast<long long>(b) * p.H + h) * p.P + pr]);
           xv[u] = xs[pr];
         }
@@ -217,8 +233,14 @@ extern "C" int cmb_mamba3_step(const void* const* pp, const int* ip, long long l
   p.ang_prev = bf(11), p.ang_next = bfm(12), p.ssm_prev = bf(13), p.ssm_next = bfm(14);
   p.k_prev = bf(15), p.k_next = bfm(16), p.v_prev = bf(17), p.v_next = bfm(18), p.y = bfm(19);
   p.a_floor = a_floor, p.eps = eps;
-  const size_t smem = (3 * p.N + p.P + 8 + 32 * p.P) * sizeof(float);
-  if (p.K == 4) cmb::mamba3_step_kernel<4><<<dim3(p.H, B), 128, smem, static_cast<cudaStream_t>(stream)>>>(p);
-  else cmb::mamba3_step_kernel<0><<<dim3(p.H, B), 128, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  const size_t base = ((3 * p.N + p.P + 8 + 32 * p.P + 3) & ~3) * sizeof(float);
+  const size_t tile = static_cast<size_t>(p.P) * p.N * sizeof(__nv_bfloat16);
+  // the prefetch needs 16-byte pieces (tile size and base pointer) and a tile small enough for seven CTAs per SM
+  const bool pre = p.K == 4 && (static_cast<size_t>(p.P) * p.N) % 8 == 0 && (reinterpret_cast<uintptr_t>(pp[13]) & 15) == 0 &&
+                   base + tile <= 30 * 1024;
+  auto st = static_cast<cudaStream_t>(stream);
+  if (pre) cmb::mamba3_step_kernel<4, true><<<dim3(p.H, B), 128, base + tile, st>>>(p);
+  else if (p.K == 4) cmb::mamba3_step_kernel<4, false><<<dim3(p.H, B), 128, base, st>>>(p);
+  else cmb::mamba3_step_kernel<0, false><<<dim3(p.H, B), 128, base, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
