@@ -189,6 +189,51 @@ __global__ void __launch_bounds__(128) rmsnorm_fwd_warp_kernel(const __nv_bfloat
   }
 }
 
+// Residual add fused with the RMS norm that follows it (inference: no statistics kept).  `sum = bf16(h + delta)` is written
+// out as the new residual stream and the norm is taken of that rounded value, so the pair of outputs is bit-identical to an
+// element-wise add followed by the norm kernel above; one launch and one pass instead of two launches and three passes.
+template <int VPL>
+__global__ void __launch_bounds__(128) add_rmsnorm_warp_kernel(const __nv_bfloat16* __restrict__ h,
+                                                                const __nv_bfloat16* __restrict__ delta,
+                                                                const __nv_bfloat16* __restrict__ w,
+                                                                __nv_bfloat16* __restrict__ sum, __nv_bfloat16* __restrict__ y,
+                                                                int64_t rows, int cols, float eps) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = cols >> 3;
+  for (int64_t row = blockIdx.x * 4 + warp; row < rows; row += static_cast<int64_t>(gridDim.x) * 4) {
+    float f[VPL][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int a = 0; a < VPL; ++a) {
+      const int v = lane + 32 * a;
+      if (v < nvec) {
+        float d[8];
+        load8(h + row * cols + 8 * v, f[a]);
+        load8(delta + row * cols + 8 * v, d);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          f[a][i] = __bfloat162float(__float2bfloat16(f[a][i] + d[i]));
+          ss += f[a][i] * f[a][i];
+        }
+        store8(sum + row * cols + 8 * v, f[a]);
+      }
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / cols + eps);
+#pragma unroll
+    for (int a = 0; a < VPL; ++a) {
+      const int v = lane + 32 * a;
+      if (v < nvec) {
+        float g[8];
+        load8(w + 8 * v, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[a][i] = f[a][i] * r * g[i];
+        store8(y + row * cols + 8 * v, f[a]);
+      }
+    }
+  }
+}
+
 template <int VPL>
 __global__ void __launch_bounds__(128) rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ gy,
                                                                 const __nv_bfloat16* __restrict__ x,
@@ -334,6 +379,18 @@ extern "C" int cmb_rmsnorm_fwd(const void* x, const void* w, void* y, void* rstd
   cmb::rmsnorm_fwd_kernel<256><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
       static_cast<float*>(rstd), rows, cols, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// sum = h + delta (bf16), y = rmsnorm(sum)·w.  cols a multiple of 8 and at most 2048; all tensors contiguous [rows, cols].
+extern "C" int cmb_add_rmsnorm(const void* h, const void* delta, const void* w, void* sum, void* y, int64_t rows, int cols, float eps,
+                               void* stream) {
+  if (cols % 8 || cols > 2048 || rows <= 0) return 1;
+  const int64_t want = (rows + 3) / 4;
+  const int grid = static_cast<int>(want < 148 * 16 ? want : 148 * 16);
+  cmb::add_rmsnorm_warp_kernel<8><<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(w),
+      static_cast<__nv_bfloat16*>(sum), static_cast<__nv_bfloat16*>(y), rows, cols, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

@@ -59,6 +59,24 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.
     return rms_norm_ref(x, weight, eps)
 
 
+def add_rms_norm(h: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5):
+    """``(h + delta, rms_norm(h + delta, weight))`` — one kernel launch on the GPU when no gradient is needed (decode steps),
+    bit-identical to the two separate ops."""
+    if (not torch.is_grad_enabled() and B.kernels_enabled() and B.on_gpu(h, delta, weight) and h.dtype == torch.bfloat16
+            and delta.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and h.shape == delta.shape
+            and h.shape[-1] % 8 == 0 and h.shape[-1] <= 2048 and h.numel() > 0):
+        lib = B.load_library()
+        cols = h.shape[-1]
+        h2, d2 = h.reshape(-1, cols).contiguous(), delta.reshape(-1, cols).contiguous()
+        out = torch.empty_like(h2)
+        y = torch.empty_like(h2)
+        B.check(lib.cmb_add_rmsnorm(B.ptr(h2), B.ptr(d2), B.ptr(weight), B.ptr(out), B.ptr(y), ctypes.c_int64(h2.shape[0]),
+                                    ctypes.c_int(cols), ctypes.c_float(eps), B.stream_ptr()), "add_rmsnorm")
+        return out.view(h.shape), y.view(h.shape)
+    s = h + delta
+    return s, rms_norm(s, weight, eps)
+
+
 def layer_norm_ref(x, weight, bias, eps=1e-5):
     return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), weight.float() if weight is not None else None,
                                           bias.float() if bias is not None else None, eps).to(x.dtype)

@@ -155,3 +155,22 @@ def test_mla_attention_block_sparse():
     m = MLAAttention(cfg).cuda()
     x = torch.randn(2, 256, 256, device="cuda") * 0.5
     _compare(m, x, lambda mod, t: mod(t), rel=8e-2, grad_rel=1.5e-1)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 2048), (32, 2048), (7, 1000), (300, 512)])
+def test_add_rms_norm_is_bit_identical_to_add_then_norm(rows, cols):
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B
+    torch.manual_seed(rows + cols)
+    h = torch.randn(rows, cols, device="cuda").bfloat16()
+    d = (torch.randn(rows, cols, device="cuda") * 0.3).bfloat16()
+    w = (1 + 0.1 * torch.randn(cols, device="cuda")).bfloat16()
+    with torch.no_grad():
+        before = B.launch_count()
+        s, y = ops.add_rms_norm(h, d, w, 1e-5)
+        assert B.launch_count() == before + 1
+        ref_s = h + d
+        ref_y = ops.rms_norm(ref_s, w, 1e-5)
+    assert torch.equal(s, ref_s) and torch.equal(y, ref_y)
+    fp = ops.rms_norm_ref(ref_s, w, 1e-5)
+    assert torch.allclose(y.float(), fp.float(), rtol=2e-2, atol=2e-2)
