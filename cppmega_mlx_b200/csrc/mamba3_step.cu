@@ -77,21 +77,28 @@ __global__ void __launch_bounds__(128, KC > 0 ? 7 : 2) mamba3_step_kernel(const 
   float* Cr = Bs + p.N;       // [N] rotated C
   float* kp = Cr + p.N;       // [N] previous rotated B · late factor
   float* xs = kp + p.N;       // [P]
-  float* red = xs + p.P;      // [8]
-  float* ys = red + 8;        // [P][32] per-lane partial read-outs (row pr is touched by warp pr % 4 only)
+  float* vps = xs + p.P;      // [P] previous step's x (the look-ahead term's other factor)
+  float* zs = vps + p.P;      // [P] gate input z of this head
+  float* red = zs + p.P;      // [16]
+  float* ys = red + 16;       // [P][32] per-lane partial read-outs (row pr is touched by warp pr % 4 only)
   const int h = blockIdx.x, b = blockIdx.y;
   const int hpg = p.H / p.G, g = h / hpg;
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   const long long sbase = (static_cast<long long>(b) * p.H + h) * p.P * p.N;
-  __nv_bfloat16* stile = reinterpret_cast<__nv_bfloat16*>(sm + ((3 * p.N + p.P + 8 + 32 * p.P + 3) & ~3));   // 16-byte aligned
+  __nv_bfloat16* stile = reinterpret_cast<__nv_bfloat16*>(sm + ((3 * p.N + 3 * p.P + 16 + 32 * p.P + 3) & ~3));   // 16-byte aligned
   if (PRE) {
     for (int i = t * 8; i < p.P * p.N; i += 128 * 8) cp_async_16(stile + i, p.ssm_prev + sbase + i);
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
   const __nv_bfloat16* tail = p.proj + b * p.ld_proj + p.d_inner + p.C;
   const int d_bc = p.G * p.N;
+  const long long bh = static_cast<long long>(b) * p.H + h;
+  const __nv_bfloat16* ang_in = tail + 3 * p.H;
+  const int rr = min(p.R, p.N / 2);
 
-  // ---- per-group scalars: one head per thread, folded over the CTA (a group can span all heads)
+  // ================= stage 1: every global read of the step, issued before the first barrier =================
+  // (the stages below only touch shared memory and registers, so a CTA pays for one memory round trip, not for one per stage)
+  // per-group scalars: one head per thread, folded over the CTA below (a group can span all heads)
   float scale_g = 0.f, late_g = 0.f;
   for (int i = t; i < hpg; i += 128) {
     const int hh = g * hpg + i;
@@ -100,22 +107,32 @@ __global__ void __launch_bounds__(128, KC > 0 ? 7 : 2) mamba3_step_kernel(const 
     scale_g += dth * sg;
     late_g += dth * (1.f - sg);
   }
-  scale_g = warp_sum(scale_g);
-  late_g = warp_sum(late_g);
-  if (lane == 0) {
-    red[warp] = scale_g;
-    red[4 + warp] = late_g;
-  }
-  __syncthreads();
-  scale_g = (red[0] + red[1] + red[2] + red[3]) / hpg;
-  late_g = (red[4] + red[5] + red[6] + red[7]) / hpg;
-  __syncthreads();     // `red` is used again for the norms below
   const float dt_h = softplus_f(__bfloat162float(tail[h]) + __bfloat162float(p.dt_bias[h]));
   const float dt_gh = softplus_f(__bfloat162float(tail[g]) + __bfloat162float(p.dt_bias[g]));   // head index g drives group g's phase
   const float A_h = fminf(-softplus_f(__bfloat162float(tail[p.H + h])), -p.a_floor);
   const float decay = __expf(A_h * dt_h);
-
-  // ---- B and C of this group: conv + SiLU, RMS norm, weight + bias
+  const float Dh = __bfloat162float(p.D[h]);
+  // first-iteration operands of the later loops (for N, R ≤ 128 that is all of them), fetched now
+  float nw[4] = {0.f, 0.f, 0.f, 0.f}, a_rot = 0.f;
+  if (t < p.N) {
+    nw[0] = __bfloat162float(p.Bw[g * p.N + t]);
+    nw[1] = __bfloat162float(p.Bb[g * p.N + t]);
+    nw[2] = __bfloat162float(p.Cw[g * p.N + t]);
+    nw[3] = __bfloat162float(p.Cb[g * p.N + t]);
+  }
+  if (t < rr) a_rot = __bfloat162float(ang_in[t]) * dt_gh + __bfloat162float(p.ang_prev[(static_cast<long long>(b) * p.H + g) * p.R + t]);
+  for (int n = t; n < p.N; n += 128) kp[n] = __bfloat162float(p.k_prev[bh * p.N + n]);      // scaled by late_g in stage 4
+  for (int i = t; i < p.P; i += 128) {
+    vps[i] = __bfloat162float(p.v_prev[bh * p.P + i]);
+    zs[i] = __bfloat162float(p.proj[b * p.ld_proj + h * p.P + i]);
+  }
+  // phase advance of the own head (cache only)
+  for (int i = t; i < p.R; i += 128) {
+    const float a = __bfloat162float(ang_in[i]) * dt_h + __bfloat162float(p.ang_prev[bh * p.R + i]);
+    const float two_pi = 6.283185307179586f;
+    p.ang_next[bh * p.R + i] = __float2bfloat16(a - two_pi * floorf(a / two_pi));
+  }
+  // B and C of this group: conv + SiLU (raw), sums of squares for the RMS norm
   float ssB = 0.f, ssC = 0.f;
   for (int n = t; n < p.N; n += 128) {
     const bool own = (h % hpg) == 0;   // the first head of a group forwards the group's conv window
@@ -126,36 +143,40 @@ __global__ void __launch_bounds__(128, KC > 0 ? 7 : 2) mamba3_step_kernel(const 
     ssB += bv * bv;
     ssC += cv * cv;
   }
-  ssB = warp_sum(ssB);
-  ssC = warp_sum(ssC);
-  if (lane == 0) {
-    red[warp] = ssB;
-    red[4 + warp] = ssC;
-  }
-  __syncthreads();
-  const float rB = rsqrtf((red[0] + red[1] + red[2] + red[3]) / p.N + p.eps);
-  const float rC = rsqrtf((red[4] + red[5] + red[6] + red[7]) / p.N + p.eps);
-  for (int n = t; n < p.N; n += 128) {
-    Bs[n] = Bs[n] * rB * __bfloat162float(p.Bw[g * p.N + n]) + __bfloat162float(p.Bb[g * p.N + n]);
-    Cr[n] = Cr[n] * rC * __bfloat162float(p.Cw[g * p.N + n]) + __bfloat162float(p.Cb[g * p.N + n]);
-  }
-  // ---- x of this head: conv + SiLU (and the head's share of the conv window); v cache
+  // x of this head: conv + SiLU (and the head's share of the conv window); v cache
   for (int i = t; i < p.P; i += 128) {
     const float xv = conv_silu_step<KC>(p, b, h * p.P + i, true);
     xs[i] = xv;
-    p.v_next[(static_cast<long long>(b) * p.H + h) * p.P + i] = __float2bfloat16(xv);
+    p.v_next[bh * p.P + i] = __float2bfloat16(xv);
+  }
+  scale_g = warp_sum(scale_g);
+  late_g = warp_sum(late_g);
+  ssB = warp_sum(ssB);
+  ssC = warp_sum(ssC);
+  if (lane == 0) {
+    red[warp] = scale_g;
+    red[4 + warp] = late_g;
+    red[8 + warp] = ssB;
+    red[12 + warp] = ssC;
   }
   __syncthreads();
-  // ---- phase advance (own head, for the cache) and rotation of B, C by the phase of head index g
-  const __nv_bfloat16* ang_in = tail + 3 * p.H;
-  for (int i = t; i < p.R; i += 128) {
-    const float a = __bfloat162float(ang_in[i]) * dt_h + __bfloat162float(p.ang_prev[(static_cast<long long>(b) * p.H + h) * p.R + i]);
-    const float two_pi = 6.283185307179586f;
-    p.ang_next[(static_cast<long long>(b) * p.H + h) * p.R + i] = __float2bfloat16(a - two_pi * floorf(a / two_pi));
+  // ================= stage 2: norm, weight + bias =================
+  scale_g = (red[0] + red[1] + red[2] + red[3]) / hpg;
+  late_g = (red[4] + red[5] + red[6] + red[7]) / hpg;
+  const float rB = rsqrtf((red[8] + red[9] + red[10] + red[11]) / p.N + p.eps);
+  const float rC = rsqrtf((red[12] + red[13] + red[14] + red[15]) / p.N + p.eps);
+  for (int n = t; n < p.N; n += 128) {
+    const bool first = n == t;
+    const float bw = first ? nw[0] : __bfloat162float(p.Bw[g * p.N + n]), bb = first ? nw[1] : __bfloat162float(p.Bb[g * p.N + n]);
+    const float cw = first ? nw[2] : __bfloat162float(p.Cw[g * p.N + n]), cb = first ? nw[3] : __bfloat162float(p.Cb[g * p.N + n]);
+    Bs[n] = Bs[n] * rB * bw + bb;
+    Cr[n] = Cr[n] * rC * cw + cb;
   }
-  const int rr = min(p.R, p.N / 2);
+  __syncthreads();
+  // ================= stage 3: rotation of B, C by the phase of head index g =================
   for (int i = t; i < rr; i += 128) {
-    const float a = __bfloat162float(ang_in[i]) * dt_gh + __bfloat162float(p.ang_prev[(static_cast<long long>(b) * p.H + g) * p.R + i]);
+    const float a = i == t ? a_rot
+                           : __bfloat162float(ang_in[i]) * dt_gh + __bfloat162float(p.ang_prev[(static_cast<long long>(b) * p.H + g) * p.R + i]);
     float sn, cs;
     __sincosf(a, &sn, &cs);
     const float b0 = Bs[2 * i], b1 = Bs[2 * i + 1], c0 = Cr[2 * i], c1 = Cr[2 * i + 1];
@@ -165,21 +186,17 @@ __global__ void __launch_bounds__(128, KC > 0 ? 7 : 2) mamba3_step_kernel(const 
     Cr[2 * i + 1] = c0 * sn + c1 * cs;
   }
   __syncthreads();
+  // ================= stage 4: next-step cache of the rotated B, trapezoid scaling =================
   for (int n = t; n < p.N; n += 128) {
-    const long long o = (static_cast<long long>(b) * p.H + h) * p.N + n;
-    p.k_next[o] = __float2bfloat16(Bs[n]);            // rotated, not yet trapezoid-scaled: what the next step completes
-    kp[n] = __bfloat162float(p.k_prev[o]) * late_g;
+    p.k_next[bh * p.N + n] = __float2bfloat16(Bs[n]);   // rotated, not yet trapezoid-scaled: what the next step completes
+    kp[n] *= late_g;
     Bs[n] *= scale_g;
   }
-  __syncthreads();
+  if (PRE) asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();      // stage 4's shared-memory writes, and every thread's pieces of the state tile
   // ---- state update and read-out: warp w owns rows p ≡ w (mod 4); lanes sweep the state dimension
   for (int pr = warp; pr < p.P; pr += 4) ys[pr * 32 + lane] = 0.f;
-  const float Dh = __bfloat162float(p.D[h]);
   constexpr int RU = 4;   // rows in flight per warp
-  if (PRE) {
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();      // every thread's pieces of the tile have landed
-  }
   const __nv_bfloat16* sprev = PRE ? stile : p.ssm_prev + sbase;
   for (int pr0 = warp; pr0 < p.P; pr0 += 4 * RU) {
     for (int n = lane * 2; n < p.N; n += 64) {
@@ -190,7 +207,7 @@ __global__ void __launch_bounds__(128, KC > 0 ? 7 : 2) mamba3_step_kernel(const 
         const int pr = pr0 + 4 * u;
         if (pr < p.P) {
           s2[u] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sprev + pr * p.N + n));
-          vp[u] = __bfloat162float(p.v_prev[(static_cast<long long>(b) * p.H + h) * p.P + pr]);
+          vp[u] = vps[pr];
           xv[u] = xs[pr];
         }
       }
@@ -210,7 +227,7 @@ __global__ void __launch_bounds__(128, KC > 0 ? 7 : 2) mamba3_step_kernel(const 
   for (int pr = warp; pr < p.P; pr += 4) {
     const float acc = warp_sum(ys[pr * 32 + lane]);
     if (lane == 0) {
-      const float zv = __bfloat162float(p.proj[b * p.ld_proj + h * p.P + pr]);
+      const float zv = zs[pr];
       p.y[(static_cast<long long>(b) * p.H + h) * p.P + pr] = __float2bfloat16((acc + Dh * xs[pr]) * silu_f(zv));
     }
   }
@@ -233,7 +250,7 @@ extern "C" int cmb_mamba3_step(const void* const* pp, const int* ip, long long l
   p.ang_prev = bf(11), p.ang_next = bfm(12), p.ssm_prev = bf(13), p.ssm_next = bfm(14);
   p.k_prev = bf(15), p.k_next = bfm(16), p.v_prev = bf(17), p.v_next = bfm(18), p.y = bfm(19);
   p.a_floor = a_floor, p.eps = eps;
-  const size_t base = ((3 * p.N + p.P + 8 + 32 * p.P + 3) & ~3) * sizeof(float);
+  const size_t base = ((3 * p.N + 3 * p.P + 16 + 32 * p.P + 3) & ~3) * sizeof(float);
   const size_t tile = static_cast<size_t>(p.P) * p.N * sizeof(__nv_bfloat16);
   // the prefetch needs 16-byte pieces (tile size and base pointer) and a tile small enough for seven CTAs per SM
   const bool pre = p.K == 4 && (static_cast<size_t>(p.P) * p.N) % 8 == 0 && (reinterpret_cast<uintptr_t>(pp[13]) & 15) == 0 &&

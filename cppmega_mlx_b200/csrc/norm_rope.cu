@@ -190,47 +190,47 @@ __global__ void __launch_bounds__(128) rmsnorm_fwd_warp_kernel(const __nv_bfloat
 }
 
 // Residual add fused with the RMS norm that follows it (inference: no statistics kept).  `sum = bf16(h + delta)` is written
-// out as the new residual stream and the norm is taken of that rounded value, so the pair of outputs is bit-identical to an
-// element-wise add followed by the norm kernel above; one launch and one pass instead of two launches and three passes.
-template <int VPL>
-__global__ void __launch_bounds__(128) add_rmsnorm_warp_kernel(const __nv_bfloat16* __restrict__ h,
-                                                                const __nv_bfloat16* __restrict__ delta,
-                                                                const __nv_bfloat16* __restrict__ w,
-                                                                __nv_bfloat16* __restrict__ sum, __nv_bfloat16* __restrict__ y,
-                                                                int64_t rows, int cols, float eps) {
+// out as the new residual stream and the norm is taken of that rounded value, i.e. the same arithmetic as an element-wise add
+// followed by the norm; one launch and one pass instead of two launches and three passes.  One CTA per row, one 16-byte
+// vector per thread (cols ≤ 2048), and all three operands are loaded before anything is used: a decode step has one to a few
+// dozen rows, so the launch is a single memory round trip plus one block reduction.
+__global__ void __launch_bounds__(256) add_rmsnorm_block_kernel(const __nv_bfloat16* __restrict__ h,
+                                                                 const __nv_bfloat16* __restrict__ delta,
+                                                                 const __nv_bfloat16* __restrict__ w,
+                                                                 __nv_bfloat16* __restrict__ sum, __nv_bfloat16* __restrict__ y,
+                                                                 int64_t rows, int cols, float eps) {
+  __shared__ float red[8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int nvec = cols >> 3;
-  for (int64_t row = blockIdx.x * 4 + warp; row < rows; row += static_cast<int64_t>(gridDim.x) * 4) {
-    float f[VPL][8];
+  const int v = threadIdx.x;
+  const bool active = v < (cols >> 3);
+  float g[8];
+  if (active) load8(w + 8 * v, g);
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    float f[8], d[8];
     float ss = 0.f;
+    if (active) {
+      load8(h + row * cols + 8 * v, f);
+      load8(delta + row * cols + 8 * v, d);
 #pragma unroll
-    for (int a = 0; a < VPL; ++a) {
-      const int v = lane + 32 * a;
-      if (v < nvec) {
-        float d[8];
-        load8(h + row * cols + 8 * v, f[a]);
-        load8(delta + row * cols + 8 * v, d);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          f[a][i] = __bfloat162float(__float2bfloat16(f[a][i] + d[i]));
-          ss += f[a][i] * f[a][i];
-        }
-        store8(sum + row * cols + 8 * v, f[a]);
+      for (int i = 0; i < 8; ++i) {
+        f[i] = __bfloat162float(__float2bfloat16(f[i] + d[i]));
+        ss += f[i] * f[i];
       }
+      store8(sum + row * cols + 8 * v, f);
     }
     ss = warp_sum(ss);
-    const float r = rsqrtf(ss / cols + eps);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
 #pragma unroll
-    for (int a = 0; a < VPL; ++a) {
-      const int v = lane + 32 * a;
-      if (v < nvec) {
-        float g[8];
-        load8(w + 8 * v, g);
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float r = rsqrtf(tot / cols + eps);
+    if (active) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[a][i] = f[a][i] * r * g[i];
-        store8(y + row * cols + 8 * v, f[a]);
-      }
+      for (int i = 0; i < 8; ++i) f[i] = f[i] * r * g[i];
+      store8(y + row * cols + 8 * v, f);
     }
+    __syncthreads();     // `red` is rewritten by the next row
   }
 }
 
@@ -386,9 +386,8 @@ extern "C" int cmb_rmsnorm_fwd(const void* x, const void* w, void* y, void* rstd
 extern "C" int cmb_add_rmsnorm(const void* h, const void* delta, const void* w, void* sum, void* y, int64_t rows, int cols, float eps,
                                void* stream) {
   if (cols % 8 || cols > 2048 || rows <= 0) return 1;
-  const int64_t want = (rows + 3) / 4;
-  const int grid = static_cast<int>(want < 148 * 16 ? want : 148 * 16);
-  cmb::add_rmsnorm_warp_kernel<8><<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  const int grid = static_cast<int>(rows < 148 * 8 ? rows : 148 * 8);
+  cmb::add_rmsnorm_block_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(w),
       static_cast<__nv_bfloat16*>(sum), static_cast<__nv_bfloat16*>(y), rows, cols, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
