@@ -292,6 +292,35 @@ def bench_linears(args) -> list[dict]:
     return rows
 
 
+def bench_mamba3_step(args) -> list[dict]:
+    """One-token Mamba3 mixer step (in_proj → step kernel → out_proj) at the 1B model's layer shape (d 2048, 32 heads of 64,
+    state 128) for ``--batch`` sequences, as a CUDA graph of 16 steps over 16 different caches (so the state comes from HBM)."""
+    from cppmega_mlx_b200.nn.mamba3 import Mamba3Block, Mamba3Config
+    torch.manual_seed(0)
+    bsz = args.batch
+    blk = Mamba3Block(Mamba3Config(d_model=2048, headdim=64, d_state=128, ngroups=args.groups, chunk_size=64)).cuda().bfloat16().eval()
+    rows = []
+    with torch.no_grad():
+        x0 = torch.randn(bsz, 8, 2048, device="cuda").bfloat16()
+        _, cache = blk(x0, return_cache=True)
+        caches = [type(cache)(**{k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in vars(cache).items()}) for _ in range(16)]
+        x = torch.randn(bsz, 1, 2048, device="cuda").bfloat16()
+        for c in caches[:2]:
+            blk(x, cache=c, return_cache=True)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for c in caches:
+                blk(x, cache=c, return_cache=True)
+        ms = time_cuda(graph.replay, iters=max(args.iters, 10), warmup=args.warmup, flush=False) / len(caches)
+    state_mb = bsz * 32 * 64 * 128 * 2 * 2 / 1e6
+    row = {"op": f"mamba3 mixer step B{bsz} d2048 H32 P64 N128 G{args.groups}", "us_per_step_layer": ms * 1e3, "state_read_write_mb": state_mb,
+           "state_gbs": state_mb / ms}
+    rows.append(row)
+    print(json.dumps(row), flush=True)
+    return rows
+
+
 def bench_dsa_loss(args) -> list[dict]:
     """DSA indexer KL loss, forward + gradient with respect to the index scores, at the flagship attention shape (B4 S4096, 16
     latent-query heads of width 576, top-2048 keys) against the same loss written with PyTorch ops."""
@@ -570,7 +599,7 @@ def bench_serving(args) -> list[dict]:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "dsa_loss", "linears", "decode", "decode_loop", "serving", "decode_trace", "decode_profile", "step_profile", "all"])
+    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "dsa_loss", "linears", "mamba3_step", "decode", "decode_loop", "serving", "decode_trace", "decode_profile", "step_profile", "all"])
     ap.add_argument("--json", default=None)
     ap.add_argument("--only", default=None, help="run the single case with this label (small captures under a profiler)")
     ap.add_argument("--iters", type=int, default=10)
@@ -579,6 +608,7 @@ def main(argv=None) -> int:
     ap.add_argument("--mla-seq", type=int, default=8192)
     ap.add_argument("--batch", type=int, default=1, help="decode_profile: sequences in the batch")
     ap.add_argument("--prompt", type=int, default=512, help="decode_profile: prompt length")
+    ap.add_argument("--groups", type=int, default=8, help="mamba3_step: B/C groups")
     args = ap.parse_args(argv)
     rows = []
     if args.op in ("gemm", "all"):
@@ -595,6 +625,8 @@ def main(argv=None) -> int:
         rows += bench_dsa_loss(args)
     if args.op in ("linears", "all"):
         rows += bench_linears(args)
+    if args.op in ("mamba3_step", "all"):
+        rows += bench_mamba3_step(args)
     if args.op in ("decode", "all"):
         rows += bench_decode(args)
     if args.op in ("decode_loop", "all"):

@@ -367,7 +367,7 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* 
 extern "C" int cmb_rmsnorm_fwd(const void* x, const void* w, void* y, void* rstd, int64_t rows, int cols, float eps,
                                void* stream) {
   if (cols % 8) return 1;
-  if (cols <= 2048 && rows >= 4) {   // whole row in registers, one warp per row
+  if (cols <= 2048 && rows >= 256) {   // whole row in registers, one warp per row (fewer rows: one CTA per row has more loads in flight)
     const int64_t want = (rows + 3) / 4;
     const int wgrid = static_cast<int>(want < 148 * 16 ? want : 148 * 16);
     cmb::rmsnorm_fwd_warp_kernel<8><<<wgrid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
