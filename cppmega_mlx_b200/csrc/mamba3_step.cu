@@ -80,12 +80,11 @@ __global__ void __launch_bounds__(128, KC > 0 ? 7 : 2) mamba3_step_kernel(const 
   float* vps = xs + p.P;      // [P] previous step's x (the look-ahead term's other factor)
   float* zs = vps + p.P;      // [P] gate input z of this head
   float* red = zs + p.P;      // [16]
-  float* ys = red + 16;       // [P][32] per-lane partial read-outs (row pr is touched by warp pr % 4 only)
   const int h = blockIdx.x, b = blockIdx.y;
   const int hpg = p.H / p.G, g = h / hpg;
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   const long long sbase = (static_cast<long long>(b) * p.H + h) * p.P * p.N;
-  __nv_bfloat16* stile = reinterpret_cast<__nv_bfloat16*>(sm + ((3 * p.N + 3 * p.P + 16 + 32 * p.P + 3) & ~3));   // 16-byte aligned
+  __nv_bfloat16* stile = reinterpret_cast<__nv_bfloat16*>(sm + ((3 * p.N + 3 * p.P + 16 + 3) & ~3));   // 16-byte aligned
   if (PRE) {
     for (int i = t * 8; i < p.P * p.N; i += 128 * 8) cp_async_16(stile + i, p.ssm_prev + sbase + i);
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -194,41 +193,36 @@ __global__ void __launch_bounds__(128, KC > 0 ? 7 : 2) mamba3_step_kernel(const 
   }
   if (PRE) asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();      // stage 4's shared-memory writes, and every thread's pieces of the state tile
-  // ---- state update and read-out: warp w owns rows p ≡ w (mod 4); lanes sweep the state dimension
-  for (int pr = warp; pr < p.P; pr += 4) ys[pr * 32 + lane] = 0.f;
-  constexpr int RU = 4;   // rows in flight per warp
+  // ---- state update and read-out.  Warp w owns rows p ≡ w (mod 4), sixteen of them per pass; a lane owns two adjacent state
+  // columns per 64-column chunk.  The per-column operands live in registers for the whole chunk and the read-out sums in
+  // registers for the whole pass (shared-memory accumulators would force every operand to be re-read after each store),
+  // so a state element costs one shared-memory read, a handful of FMAs and one global store.
+  constexpr int RPW = 16;   // rows per warp and pass
   const __nv_bfloat16* sprev = PRE ? stile : p.ssm_prev + sbase;
-  for (int pr0 = warp; pr0 < p.P; pr0 += 4 * RU) {
+  for (int pb = 0; pb < p.P; pb += 4 * RPW) {
+    float yacc[RPW];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) yacc[r] = 0.f;
     for (int n = lane * 2; n < p.N; n += 64) {
-      float2 s2[RU];
-      float vp[RU], xv[RU];
+      const float k0 = kp[n], k1 = kp[n + 1], b0 = Bs[n], b1 = Bs[n + 1], c0 = Cr[n], c1 = Cr[n + 1];
 #pragma unroll
-      for (int u = 0; u < RU; ++u) {
-        const int pr = pr0 + 4 * u;
+      for (int r = 0; r < RPW; ++r) {
+        const int pr = pb + warp + 4 * r;
         if (pr < p.P) {
-          s2[u] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sprev + pr * p.N + n));
-          vp[u] = vps[pr];
-          xv[u] = xs[pr];
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < RU; ++u) {
-        const int pr = pr0 + 4 * u;
-        if (pr < p.P) {
-          const float n0 = decay * (s2[u].x + vp[u] * kp[n]) + xv[u] * Bs[n];
-          const float n1 = decay * (s2[u].y + vp[u] * kp[n + 1]) + xv[u] * Bs[n + 1];
+          const float2 s2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sprev + pr * p.N + n));
+          const float vp = vps[pr], xv = xs[pr];
+          const float n0 = decay * (s2.x + vp * k0) + xv * b0;
+          const float n1 = decay * (s2.y + vp * k1) + xv * b1;
           *reinterpret_cast<__nv_bfloat162*>(p.ssm_next + sbase + pr * p.N + n) = __floats2bfloat162_rn(n0, n1);
-          ys[pr * 32 + lane] += n0 * Cr[n] + n1 * Cr[n + 1];
+          yacc[r] = fmaf(n0, c0, fmaf(n1, c1, yacc[r]));
         }
       }
     }
-  }
-  __syncwarp();
-  for (int pr = warp; pr < p.P; pr += 4) {
-    const float acc = warp_sum(ys[pr * 32 + lane]);
-    if (lane == 0) {
-      const float zv = zs[pr];
-      p.y[(static_cast<long long>(b) * p.H + h) * p.P + pr] = __float2bfloat16((acc + Dh * xs[pr]) * silu_f(zv));
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+      const int pr = pb + warp + 4 * r;
+      const float acc = warp_sum(yacc[r]);
+      if (lane == 0 && pr < p.P) p.y[bh * p.P + pr] = __float2bfloat16((acc + Dh * xs[pr]) * silu_f(zs[pr]));
     }
   }
 }
@@ -250,7 +244,7 @@ extern "C" int cmb_mamba3_step(const void* const* pp, const int* ip, long long l
   p.ang_prev = bf(11), p.ang_next = bfm(12), p.ssm_prev = bf(13), p.ssm_next = bfm(14);
   p.k_prev = bf(15), p.k_next = bfm(16), p.v_prev = bf(17), p.v_next = bfm(18), p.y = bfm(19);
   p.a_floor = a_floor, p.eps = eps;
-  const size_t base = ((3 * p.N + 3 * p.P + 16 + 32 * p.P + 3) & ~3) * sizeof(float);
+  const size_t base = ((3 * p.N + 3 * p.P + 16 + 3) & ~3) * sizeof(float);
   const size_t tile = static_cast<size_t>(p.P) * p.N * sizeof(__nv_bfloat16);
   // the prefetch needs 16-byte pieces (tile size and base pointer) and a tile small enough for seven CTAs per SM
   const bool pre = p.K == 4 && (static_cast<size_t>(p.P) * p.N) % 8 == 0 && (reinterpret_cast<uintptr_t>(pp[13]) & 15) == 0 &&
