@@ -270,3 +270,24 @@ def test_external_trainer_adapter_probe_batch_mapping_and_refusal():
         X.require_supported_external_trainer_integration(info)
     with pytest.raises(ValueError):
         X.as_dense_trainer_batch({"tokens": torch.tensor([[1, -2, 3]])})
+
+
+def test_no_grad_forward_with_deferred_residual_adds_equals_the_plain_forward():
+    """Without gradients every residual add is handed to the next norm (one fused launch on the GPU); the result must be the
+    stack's ordinary output, for blocks with and without an FFN and for the final norm."""
+    from cppmega_mlx_b200 import ops
+    torch.manual_seed(0)
+    for kw in ({}, {"ffn_hidden_size": 48}):
+        model = _tiny(**kw).eval()
+        ids = torch.randint(0, model.config.vocab_size, (2, 12))
+        with torch.enable_grad():
+            ref = model(ids)
+        with torch.no_grad():
+            got = model(ids)
+        ref = ref[0] if isinstance(ref, tuple) else ref
+        got = got[0] if isinstance(got, tuple) else got
+        assert torch.allclose(got, ref.detach(), atol=1e-5, rtol=1e-5)
+    h, d, w = torch.randn(3, 16), torch.randn(3, 16), torch.rand(16) + 0.5
+    with torch.no_grad():
+        s, y = ops.add_rms_norm(h, d, w, 1e-5)
+    assert torch.equal(s, h + d) and torch.allclose(y, ops.rms_norm_ref(h + d, w, 1e-5))
