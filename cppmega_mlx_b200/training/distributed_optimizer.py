@@ -115,7 +115,10 @@ class DistributedZeRO1Optimizer:
             from ..parallel.consistency import check_rank_consistency
             check_rank_consistency(self.named, slots=self.flat.slots, group=group, what="ZeRO-1 flat-buffer layouts")
             from ..runtime.memory_audit import audit_grad_buffer_aliasing
-            clash = audit_grad_buffer_aliasing(self.named)["overlaps"]      # host-side pointer arithmetic, once per run
+            try:
+                clash = audit_grad_buffer_aliasing(self.named)["overlaps"]      # host-side pointer arithmetic, once per run
+            except RuntimeError:      # storage without a queryable base pointer: nothing to compare
+                clash = []
             if clash:
                 raise RuntimeError(f"flat ZeRO-1 storage: {len(clash)} overlapping tensors, first {clash[0]}")
             if self._fused is not None:
