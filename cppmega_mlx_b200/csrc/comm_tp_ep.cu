@@ -8,6 +8,9 @@
 //  * cmb_ep_combine     the way back: for every token, load its k expert outputs from the peers' output buffers, weight them
 //                       with the gate and add them up (no atomics: one warp owns one token).
 //  * cmb_ep_combine_bwd backward of combine with respect to the gate weights: dw[t,j] = ⟨dout[t], y_peer[slot(t,j)]⟩.
+// Every expert-parallel kernel takes the receive buffers' row capacity: a slot of −1 means "dropped by the routing plan" and
+// is skipped silently; any other slot outside [0, rows) is a caller error that is reported through the status block and
+// skipped, so no store or load ever leaves a peer's buffer.
 //
 // The reference has neither tensor nor expert parallelism (config fields only, cppmega_mlx/config/model.py:56-91).
 #include "sm100.cuh"
@@ -55,16 +58,34 @@ __global__ void __launch_bounds__(256) sum_slots_kernel(const __nv_bfloat16* __r
   }
 }
 
+// A slot outside [0, rows) or a rank outside [0, world) is never dereferenced: the first offender is recorded in the
+// status block (code ST_BAD_ARGUMENT, then assignment index, slot, rank) and the access is skipped.
+__device__ __forceinline__ void te_report(int* status, long long a, long long slot, int rank, int lane) {
+  if (status != nullptr && lane == 0 && atomicCAS(status, 0, ST_BAD_ARGUMENT) == 0) {
+    status[1] = static_cast<int>(a);
+    status[2] = static_cast<int>(slot < 0x7fffffffLL ? slot : 0x7fffffffLL);
+    status[3] = rank;
+  }
+}
+
 // One warp per assignment a: row tok[a] of x (scaled by scale[a] if given) → peer dest_rank[a], row dest_slot[a] of its buffer.
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const long long* __restrict__ tok,
                                                            const int* __restrict__ dest_rank, const long long* __restrict__ dest_slot,
-                                                           const float* __restrict__ scale, TePeers bufs, long long assignments, int d) {
+                                                           const float* __restrict__ scale, TePeers bufs, long long assignments, int d,
+                                                           long long rows, int world, int* status) {
   const int lane = threadIdx.x & 31;
   const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   for (long long a = warp; a < assignments; a += nwarps) {
+    const long long slot = dest_slot[a];
+    const int dr = dest_rank[a];
+    if (slot < 0) continue;                       // dropped by the routing plan (no capacity at the destination)
+    if (slot >= rows || dr < 0 || dr >= world) {  // never address memory outside a receive buffer: record and skip
+      te_report(status, a, slot, dr, lane);
+      continue;
+    }
     const __nv_bfloat16* src = x + tok[a] * d;
-    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(bufs.p[dest_rank[a]]) + dest_slot[a] * d;
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(bufs.p[dr]) + slot * d;
     const float sc = scale != nullptr ? scale[a] : 1.f;
     for (int c = lane * 8; c < d; c += 256) {
       uint4 q = *reinterpret_cast<const uint4*>(src + c);
@@ -84,7 +105,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const __nv_bfloat16* _
 // One warp per token t: out[t] = Σ_j w[t,j] · ybuf[rank(t,j)][slot(t,j)]  (assignment index = t·k + j; a negative slot is skipped).
 __global__ void __launch_bounds__(256) ep_combine_kernel(TePeers ybufs, const int* __restrict__ src_rank, const long long* __restrict__ src_slot,
                                                           const float* __restrict__ w, __nv_bfloat16* __restrict__ out, long long tokens, int k,
-                                                          int d) {
+                                                          int d, long long rows, int world, int* status) {
   const int lane = threadIdx.x & 31;
   const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
@@ -97,8 +118,13 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(TePeers ybufs, const in
         const long long a = t * k + j;
         const long long slot = src_slot[a];
         if (slot < 0) continue;
+        const int sr = src_rank[a];
+        if (slot >= rows || sr < 0 || sr >= world) {
+          if (c == lane * 8) te_report(status, a, slot, sr, lane);
+          continue;
+        }
         const float wj = w != nullptr ? w[a] : 1.f;
-        const uint4 q = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(ybufs.p[src_rank[a]]) + slot * d + c);
+        const uint4 q = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(ybufs.p[sr]) + slot * d + c);
         const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&q);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -120,15 +146,18 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(TePeers ybufs, const in
 // One warp per assignment a = t·k + j: dw[a] = ⟨g[t], ybuf[rank(a)][slot(a)]⟩.
 __global__ void __launch_bounds__(256) ep_combine_bwd_kernel(TePeers ybufs, const int* __restrict__ src_rank, const long long* __restrict__ src_slot,
                                                               const __nv_bfloat16* __restrict__ g, float* __restrict__ dw, long long assignments,
-                                                              int k, int d) {
+                                                              int k, int d, long long rows, int world, int* status) {
   const int lane = threadIdx.x & 31;
   const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   for (long long a = warp; a < assignments; a += nwarps) {
     const long long slot = src_slot[a];
+    const int sr = src_rank[a];
     float acc = 0.f;
-    if (slot >= 0) {
-      const __nv_bfloat16* y = static_cast<const __nv_bfloat16*>(ybufs.p[src_rank[a]]) + slot * d;
+    if (slot >= 0 && (slot >= rows || sr < 0 || sr >= world)) {
+      te_report(status, a, slot, sr, lane);
+    } else if (slot >= 0) {
+      const __nv_bfloat16* y = static_cast<const __nv_bfloat16*>(ybufs.p[sr]) + slot * d;
       const __nv_bfloat16* gr = g + (a / k) * d;
       for (int c = lane * 8; c < d; c += 256) {
         const uint4 qy = *reinterpret_cast<const uint4*>(y + c);
@@ -171,31 +200,32 @@ extern "C" int cmb_sum_slots(const void* slots, int nslots, long long n, const v
 }
 
 extern "C" int cmb_ep_dispatch(const void* x, const long long* tok, const int* dest_rank, const long long* dest_slot, const float* scale,
-                               const long long* buf_ptrs, int world, long long assignments, int d, void* stream) {
+                               const long long* buf_ptrs, int world, long long assignments, int d, long long rows, int* status,
+                               void* stream) {
   cmb::TePeers bufs;
-  if (!cmb::te_fill(bufs, buf_ptrs, world) || (d & 7)) return 1;
+  if (!cmb::te_fill(bufs, buf_ptrs, world) || (d & 7) || rows < 0) return 1;
   if (assignments <= 0) return 0;
   cmb::ep_dispatch_kernel<<<cmb::te_grid(assignments, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), tok, dest_rank, dest_slot, scale, bufs, assignments, d);
+      static_cast<const __nv_bfloat16*>(x), tok, dest_rank, dest_slot, scale, bufs, assignments, d, rows, world, status);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
 extern "C" int cmb_ep_combine(const long long* ybuf_ptrs, int world, const int* src_rank, const long long* src_slot, const float* w, void* out,
-                              long long tokens, int k, int d, void* stream) {
+                              long long tokens, int k, int d, long long rows, int* status, void* stream) {
   cmb::TePeers bufs;
-  if (!cmb::te_fill(bufs, ybuf_ptrs, world) || (d & 7)) return 1;
+  if (!cmb::te_fill(bufs, ybuf_ptrs, world) || (d & 7) || rows < 0) return 1;
   if (tokens <= 0) return 0;
-  cmb::ep_combine_kernel<<<cmb::te_grid(tokens, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(bufs, src_rank, src_slot, w,
-                                                                                              static_cast<__nv_bfloat16*>(out), tokens, k, d);
+  cmb::ep_combine_kernel<<<cmb::te_grid(tokens, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      bufs, src_rank, src_slot, w, static_cast<__nv_bfloat16*>(out), tokens, k, d, rows, world, status);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
 extern "C" int cmb_ep_combine_bwd(const long long* ybuf_ptrs, int world, const int* src_rank, const long long* src_slot, const void* g, float* dw,
-                                  long long assignments, int k, int d, void* stream) {
+                                  long long assignments, int k, int d, long long rows, int* status, void* stream) {
   cmb::TePeers bufs;
-  if (!cmb::te_fill(bufs, ybuf_ptrs, world) || (d & 7)) return 1;
+  if (!cmb::te_fill(bufs, ybuf_ptrs, world) || (d & 7) || rows < 0) return 1;
   if (assignments <= 0) return 0;
   cmb::ep_combine_bwd_kernel<<<cmb::te_grid(assignments, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      bufs, src_rank, src_slot, static_cast<const __nv_bfloat16*>(g), dw, assignments, k, d);
+      bufs, src_rank, src_slot, static_cast<const __nv_bfloat16*>(g), dw, assignments, k, d, rows, world, status);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }

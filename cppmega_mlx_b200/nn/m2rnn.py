@@ -134,17 +134,20 @@ class M2RNNMixer(nn.Module):
             if tuple(mixer_state.conv_state.shape) != exp:
                 raise ValueError(f"mixer_state.conv_state must have shape {exp}, got {tuple(mixer_state.conv_state.shape)}")
             prefix, h0 = mixer_state.conv_state, mixer_state.h
-        conv = F.silu(causal_depthwise_conv1d(raw, self.conv_weight, self.conv_bias, prefix=prefix))
-        q = conv[..., :self.q_dim].reshape(b, s, c.num_q_heads, c.k_head_dim)
-        k = conv[..., self.q_dim:self.q_dim + self.k_dim].reshape(b, s, c.num_k_heads, c.k_head_dim)
-        v = conv[..., self.q_dim + self.k_dim:].reshape(b, s, c.num_v_heads, c.v_head_dim)
-        f = m2rnn_softplus_decay_gate(proj[..., conv_end:f_end], self.A_log, self.dt_bias)
+        # One node splits the packed projection: the conv + SiLU kernel writes q|k and v as two dense tensors (heads packed,
+        # unit inner stride: the layout the recurrence kernels read in place) and the backward fills one gradient buffer.
+        _, qk, vflat, tail = ops.packed_split_conv_silu(proj, 0, self.conv_dim, self.q_dim + self.k_dim, self.conv_weight,
+                                                     self.conv_bias, prefix=prefix)
+        q = qk[..., :self.q_dim].reshape(b, s, c.num_q_heads, c.k_head_dim)
+        k = qk[..., self.q_dim:].reshape(b, s, c.num_k_heads, c.k_head_dim)
+        v = vflat.reshape(b, s, c.num_v_heads, c.v_head_dim)
+        f = m2rnn_softplus_decay_gate(tail[..., :self.f_dim], self.A_log, self.dt_bias)
         out, h = ops.m2rnn_scan(q, k, v, self.state_weight.to(q.dtype), f, h0=h0)
         H = c.num_heads
         if self.D is not None:
             vb = v if c.num_v_heads == H else v.repeat_interleave(H // c.num_v_heads, dim=2)
             out = out + vb * self.D.to(out.dtype)
-        g = proj[..., f_end:].reshape(b, s, c.num_g_heads, c.v_head_dim)
+        g = tail[..., self.f_dim:].reshape(b, s, c.num_g_heads, c.v_head_dim)
         if c.num_g_heads != H:
             g = g.repeat_interleave(H // c.num_g_heads, dim=2)
         out = (out * F.silu(g)).reshape(b, s, H * c.v_head_dim)

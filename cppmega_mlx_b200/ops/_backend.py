@@ -134,19 +134,30 @@ def check_status(device=None) -> None:
 
 
 _launches = 0
+_launches_by_name: dict[str, int] = {}
 
 
 def check(rc: int, what: str) -> None:
-    """Every library entry point is called through this: counts launches, raises on a non-zero code."""
+    """Every library entry point is called through this: counts launches (in total and per entry point), raises on a
+    non-zero code."""
     global _launches
     _launches += 1
+    _launches_by_name[what] = _launches_by_name.get(what, 0) + 1
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")
 
 
-def launch_count() -> int:
-    """Number of calls into the kernel library made by this process so far."""
-    return _launches
+def launch_count(what: str | None = None) -> int:
+    """Number of calls into the kernel library made by this process so far; with ``what``, the calls of that one entry
+    point (the label its wrapper passes to ``check``: ``"m2rnn_fwd"``, ``"conv_silu_fwd"``, ``"flash_fwd"`` …), which is
+    what a test must assert to prove that a specific kernel ran rather than any kernel."""
+    if what is None:
+        return _launches
+    return _launches_by_name.get(what, 0)
+
+
+def launch_counts() -> dict[str, int]:
+    return dict(_launches_by_name)
 
 
 def env_flag(name: str, default: bool = False) -> bool:

@@ -18,7 +18,8 @@ def _token_strided(t: torch.Tensor) -> bool:
     return t.stride(3) == 1 and t.stride(2) == t.shape[3] and t.data_ptr() % 4 == 0
 
 
-def supported(q, k, v, W, f) -> bool:
+def shape_supported(q, k, v, W, f) -> bool:
+    """Head sizes and head counts the kernels cover (layout is checked separately)."""
     if not (B.kernels_enabled() and B.has_library()):
         return False
     lib = B.load_library()
@@ -26,8 +27,15 @@ def supported(q, k, v, W, f) -> bool:
         return False
     H = max(q.shape[2], k.shape[2], v.shape[2], W.shape[0], f.shape[2])
     return (q.shape[3] in SUPPORTED_K and k.shape[3] == q.shape[3] and v.shape[3] == SUPPORTED_V and tuple(W.shape[1:]) == (16, 16)
-            and all(H % n == 0 for n in (q.shape[2], k.shape[2], v.shape[2], W.shape[0], f.shape[2]))
-            and all(_token_strided(t) for t in (q, k, v)) and q.shape[1] > 0)
+            and all(H % n == 0 for n in (q.shape[2], k.shape[2], v.shape[2], W.shape[0], f.shape[2])) and q.shape[1] > 0)
+
+
+def layout_supported(q, k, v) -> bool:
+    return all(_token_strided(t) for t in (q, k, v))
+
+
+def supported(q, k, v, W, f) -> bool:
+    return shape_supported(q, k, v, W, f) and layout_supported(q, k, v)
 
 
 def _geom(q, k, v, W, f):

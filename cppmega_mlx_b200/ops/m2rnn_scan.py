@@ -49,8 +49,13 @@ def m2rnn_scan_reference(q, k, v, W, f, h0=None):
 
 
 def m2rnn_scan(q, k, v, W, f, h0=None):
+    """CUDA bf16 inputs of a head size the kernels cover run ``csrc/m2rnn.cu``; a layout the kernels cannot read in place
+    (head slices not packed with unit inner stride) is made dense here rather than sent to the per-token PyTorch loop, so
+    the product path never degrades silently.  Everything else (CPU, fp32, other head sizes) runs the oracle."""
     if B.on_gpu(q, k, v, W, f) and q.dtype == torch.bfloat16:
         from . import m2rnn_cuda
-        if m2rnn_cuda.supported(q, k, v, W, f):
+        if m2rnn_cuda.shape_supported(q, k, v, W, f):
+            if not m2rnn_cuda.layout_supported(q, k, v):
+                q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
             return m2rnn_cuda.apply(q, k, v, W, f, h0)
     return m2rnn_scan_reference(q, k, v, W, f, h0)

@@ -44,12 +44,53 @@ def exchange_counts(counts: torch.Tensor, group) -> torch.Tensor:
     return out
 
 
-def ep_moe_forward(moe, flat: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor) -> torch.Tensor:
-    """Routed-expert output for ``flat`` [T, D] given global expert ids ``top_idx`` [T, k] and gate weights ``top_w``."""
+def plan_slots(flat_e: torch.Tensor, counts: torch.Tensor, rank: int, local_experts: int, capacity_rows: int | None):
+    """Where every assignment of rank ``rank`` lands in its destination's receive buffer.
+
+    ``flat_e`` [A] global expert ids (original assignment order); ``counts`` [src, dst, expert] rows every rank sends to every
+    (rank, local expert).  A destination's buffer is laid out in padded expert-sorted form: expert segments start on 128-row
+    boundaries, inside a segment the rows are ordered by source rank.  Returns ``(dest [A] int32, slot [A] int64, keep [A]
+    bool, pad_off [dst, expert], pad_end [dst, expert], tot [dst, expert])``.  With a finite ``capacity_rows`` an assignment
+    whose slot falls at or beyond the capacity is *dropped*: ``keep`` is False and ``slot`` is −1, which the dispatch /
+    combine kernels skip, so a skewed router can never address memory past a receive buffer.  Every rank derives the same
+    drops from the same count matrix.  Pure device-side tensor ops (also runs on CPU tensors for the gloo tests).
+    """
+    Le = local_experts
+    e = flat_e.long()
+    A = e.numel()
+    C = counts.long()
+    tot = C.sum(0)                                                                # [dst, expert]
+    pad = (tot + 127) // 128 * 128
+    pad_end = torch.cumsum(pad, 1)
+    pad_off = pad_end - pad
+    start = pad_off + C[:rank].sum(0)                                             # rows of lower-ranked sources come first
+    mine = C[rank].reshape(-1)                                                    # [W·Le] rows I send to (rank, expert)
+    order = torch.argsort(e, stable=True)
+    se = e[order]
+    my_first = torch.cumsum(mine, 0) - mine
+    slot_sorted = start.reshape(-1)[se] + (torch.arange(A, device=e.device) - my_first[se])
+    slot = torch.empty_like(slot_sorted).index_copy_(0, order, slot_sorted)
+    keep = torch.ones_like(slot, dtype=torch.bool) if capacity_rows is None else slot < capacity_rows
+    slot = torch.where(keep, slot, torch.full_like(slot, -1))
+    return (e // Le).int(), slot, keep, pad_off, pad_end, tot
+
+
+def ep_moe_forward(moe, flat: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor,
+                   capacity_rows: int | None = None) -> torch.Tensor:
+    """Routed-expert output for ``flat`` [T, D] given global expert ids ``top_idx`` [T, k] and gate weights ``top_w``.
+
+    ``capacity_rows`` reproduces the drop rule of the fused path (``plan_slots``): assignments that would not fit a receive
+    buffer of that many rows contribute nothing (their gate weight is zeroed), which makes the two paths comparable under skew."""
     group = moe.ep_group
     W, Le = moe.ep_size, moe.local_experts
     T, k = top_idx.shape
     flat_e = top_idx.reshape(-1)
+    if capacity_rows is not None:
+        mine = torch.bincount(flat_e, minlength=W * Le).view(W, Le)
+        allc = [torch.empty_like(mine) for _ in range(W)]
+        dist.all_gather(allc, mine, group=group)
+        _, _, keep, _, _, _ = plan_slots(flat_e, torch.stack(allc), dist.get_rank(group), Le, capacity_rows)
+        top_w = top_w * keep.view(T, k).to(top_w.dtype)
     order = torch.argsort(flat_e, stable=True)                   # by global expert = by (destination rank, local expert)
     tok = torch.div(order, k, rounding_mode="floor")
     send_counts = torch.bincount(flat_e, minlength=W * Le).view(W, Le)

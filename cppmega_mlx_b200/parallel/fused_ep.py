@@ -45,18 +45,20 @@ class FusedEPComm:
         self.ybuf = SymmetricBuffer(self.rows * d_model, torch.bfloat16, device, group)
         self.counts = SymmetricBuffer(self.world * self.world * self.local_experts, torch.int32, device, group)
         self.barrier = EpochBarrier(device, group)
+        self.dropped: torch.Tensor | None = None
 
     # -- kernels ---------------------------------------------------------------------------------
     def dispatch_rows(self, buf: SymmetricBuffer, rows: torch.Tensor, tok: torch.Tensor, dest_rank: torch.Tensor, dest_slot: torch.Tensor) -> None:
         lib = B.load_library()
         B.check(lib.cmb_ep_dispatch(B.ptr(rows), B.ptr(tok), B.ptr(dest_rank), B.ptr(dest_slot), None, buf.peer_ptrs, self.world,
-                                    I64(tok.numel()), self.d, B.stream_ptr()), "ep_dispatch")
+                                    I64(tok.numel()), self.d, I64(self.rows), B.ptr(B.status_buffer(self.device)), B.stream_ptr()),
+                "ep_dispatch")
 
     def gather_rows(self, buf: SymmetricBuffer, src_rank: torch.Tensor, src_slot: torch.Tensor) -> torch.Tensor:
         lib = B.load_library()
         out = torch.empty(src_slot.numel(), self.d, dtype=torch.bfloat16, device=self.device)
         B.check(lib.cmb_ep_combine(buf.peer_ptrs, self.world, B.ptr(src_rank), B.ptr(src_slot), None, B.ptr(out), I64(src_slot.numel()), 1, self.d,
-                                   B.stream_ptr()), "ep_gather")
+                                   I64(self.rows), B.ptr(B.status_buffer(self.device)), B.stream_ptr()), "ep_gather")
         return out
 
     def combine_weighted(self, src_rank, src_slot, weights, tokens: int, k: int) -> torch.Tensor:
@@ -64,43 +66,43 @@ class FusedEPComm:
         lib = B.load_library()
         out = torch.empty(tokens, self.d, dtype=torch.bfloat16, device=self.device)
         B.check(lib.cmb_ep_combine(self.ybuf.peer_ptrs, self.world, B.ptr(src_rank), B.ptr(src_slot), B.ptr(weights), B.ptr(out), I64(tokens), k,
-                                   self.d, B.stream_ptr()), "ep_combine")
+                                   self.d, I64(self.rows), B.ptr(B.status_buffer(self.device)), B.stream_ptr()), "ep_combine")
         return out
 
     # -- routing plan ----------------------------------------------------------------------------
     def plan(self, flat_e: torch.Tensor):
         """Exchange counts and compute, for every assignment (original order), its destination rank and slot; also the grouped
-        layout of the rows this rank will receive.  Device-side only."""
+        layout of the rows this rank will receive.  Device-side only.  Assignments that do not fit the destination's receive
+        buffer (``self.rows``) are dropped: their slot is −1, the kernels skip them, they contribute zeros forward and backward,
+        and ``self.dropped`` (a device counter, summed over calls) records how many this rank lost."""
+        from .ep import plan_slots
         W, Le, r = self.world, self.local_experts, self.rank
         e = flat_e.long()
-        A = e.numel()
         mine = torch.bincount(e, minlength=W * Le).int()                              # [W·Le] rows I send to (rank, expert)
         for p in range(W):                                                            # my row of everyone's count matrix
             self.counts.handle.get_buffer(p, (W * Le,), torch.int32, r * W * Le).copy_(mine)
         self.barrier()
-        C = self.counts.tensor.view(W, W, Le).long()                                  # [src, dst, expert]
-        tot = C.sum(0)                                                                # [dst, expert]
-        pad = (tot + 127) // 128 * 128
-        pad_end = torch.cumsum(pad, 1)
-        pad_off = pad_end - pad
-        before_me = C[:r].sum(0)                                                      # rows of lower-ranked sources come first
-        start = pad_off + before_me                                                   # [dst, expert]: where my rows begin
+        C = self.counts.tensor.view(W, W, Le)                                         # [src, dst, expert]
+        dest, slot, keep, pad_off, pad_end, tot = plan_slots(e, C, r, Le, self.rows)
         order = torch.argsort(e, stable=True)
-        se = e[order]
-        my_first = torch.cumsum(mine.long(), 0) - mine.long()
-        slot_sorted = start.reshape(-1)[se] + (torch.arange(A, device=e.device) - my_first[se])
-        slot = torch.empty_like(slot_sorted).index_copy_(0, order, slot_sorted)
-        dest = (e // Le).int()
-        # layout of what I receive
+        # layout of what I receive (segments beyond the capacity are cut: nobody writes there)
         tile_start = torch.arange(self.rows // 128, device=e.device) * 128
         tile_group = torch.searchsorted(pad_end[r], tile_start, right=True).clamp_(max=Le - 1).int()
-        k_ranges = torch.stack([pad_off[r], pad_end[r]], 1).int().contiguous()
+        k_ranges = torch.stack([pad_off[r], pad_end[r]], 1).clamp_(max=self.rows).int().contiguous()
         layout = GG.GroupedLayout(Le, self.rows, slot, order, tile_group, k_ranges, tot[r])
         # rows of my buffers that hold a real assignment (segment padding and unused capacity are not written by anyone)
         grp = tile_group.long().repeat_interleave(128)
         layout.valid_rows = (torch.arange(self.rows, device=e.device) - pad_off[r][grp]) < tot[r][grp]
-        overflow = pad_end[:, -1].max() > self.rows
-        return dest, slot, layout, overflow
+        dropped = (~keep).sum()
+        self.dropped = dropped if self.dropped is None else self.dropped + dropped
+        return dest, slot, layout, dropped
+
+    def dropped_assignments(self) -> int:
+        """Assignments this rank dropped for lack of receive-buffer capacity since the last call (synchronises with the device;
+        call it between steps).  Raise the communicator's ``capacity_rows`` / ``capacity_factor`` if this is not zero."""
+        n = 0 if self.dropped is None else int(self.dropped.item())
+        self.dropped = None
+        return n
 
     def take(self, buf: SymmetricBuffer, valid_rows: torch.Tensor) -> torch.Tensor:
         """Private copy of a receive buffer with every row nobody wrote set to zero (one pass; the buffer is never cleared)."""
@@ -155,7 +157,7 @@ class _Gather(torch.autograd.Function):
 def fused_ep_moe_forward(moe, comm: FusedEPComm, flat: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor) -> torch.Tensor:
     """Drop-in for ``parallel.ep.ep_moe_forward`` on GPUs sharing an NVSwitch domain."""
     T, k = top_idx.shape
-    dest, slot, layout, _overflow = comm.plan(top_idx.reshape(-1))
+    dest, slot, layout, _dropped = comm.plan(top_idx.reshape(-1))     # drops are counted in comm.dropped (see dropped_assignments)
     tok = torch.arange(T * k, device=flat.device) // k
     xp = _Dispatch.apply(flat.contiguous(), tok, dest, slot, layout.valid_rows, comm)
     yp = moe.expert_ffn_padded(xp, layout)

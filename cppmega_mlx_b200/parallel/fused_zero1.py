@@ -71,7 +71,7 @@ class FusedZeRO1Comm:
         b1, b2 = adamw.betas
         if adamw.bias_correction:
             t = adamw.step_count
-            c1, c2 = 1.0 / (1 - b1 ** t), 1.0 / (1 - b2 ** t)
+            c1, c2 = 1.0 / (1 - b1 ** t), (1 - b2 ** t) ** -0.5      # c2 scales sqrt(v) (kernel convention)
         else:
             c1 = c2 = 1.0
         for name, p in adamw.params:

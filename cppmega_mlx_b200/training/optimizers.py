@@ -123,7 +123,9 @@ class AdamWFP32Moments(Optimizer):
         lr = self.lr
         if self.bias_correction:
             t = self.step_count
-            c1, c2 = 1.0 / (1 - b1 ** t), 1.0 / (1 - b2 ** t)
+            # the update is m·c1 / (sqrt(v)·c2 + eps): c2 multiplies the root, so it is (1 − b2^t)^(−1/2)
+            # (same convention as the kernels and as the 8-bit optimizers; cppmega_mlx/training/optimizers_quantized.py:211-218)
+            c1, c2 = 1.0 / (1 - b1 ** t), (1 - b2 ** t) ** -0.5
         else:
             c1 = c2 = 1.0
         if p.is_cuda and B.kernels_enabled() and p.is_contiguous() and grad.is_contiguous():
@@ -134,7 +136,7 @@ class AdamWFP32Moments(Optimizer):
         st["m"].mul_(b1).add_(g, alpha=1 - b1)
         st["v"].mul_(b2).addcmul_(g, g, value=1 - b2)
         pf = p.float() * (1 - lr * self.weight_decay)
-        denom = (st["v"] * c2).sqrt_().add_(self.eps)
+        denom = st["v"].sqrt().mul_(c2).add_(self.eps)
         pf.addcdiv_(st["m"] * c1, denom, value=-lr)
         p.copy_(pf)
 

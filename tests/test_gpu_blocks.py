@@ -7,18 +7,19 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _compare(module, x, call, rel=6e-2, grad_rel=1e-1):
+def _compare(module, x, call, rel=6e-2, grad_rel=1e-1, expect=()):
     from cppmega_mlx_b200.ops import _backend as B
     ref = copy.deepcopy(module).float()
     xr = x.detach().float().requires_grad_()
     xk = x.detach().bfloat16().requires_grad_()
     mod = module.bfloat16()
     with B.use_kernels(True):
-        before = B.launch_count()
+        before = {name: B.launch_count(name) for name in expect}
         yk = call(mod, xk)
         g = torch.randn_like(yk)
         yk.backward(g)
-        assert B.launch_count() > before
+        for name in expect:      # the named entry points of the kernel library ran, not merely some kernel
+            assert B.launch_count(name) > before[name], f"{name} was not launched"
     with B.use_kernels(False):
         yr = call(ref, xr)
         yr.backward(g.float())
@@ -62,14 +63,14 @@ def test_mamba3_block():
     torch.manual_seed(0)
     m = Mamba3Block(Mamba3Config(d_model=256, headdim=64, d_state=64, ngroups=2, chunk_size=64, d_conv=4)).cuda()
     x = torch.randn(2, 256, 256, device="cuda") * 0.5
-    _compare(m, x, lambda mod, t: mod(t)[0])
+    _compare(m, x, lambda mod, t: mod(t)[0], expect=("conv_silu_fwd", "m3_prep_dt_fwd", "m3_xw", "gemm_bf16_batched"))
 
 
 def test_feed_forward_block():
     from cppmega_mlx_b200.nn.basic import FeedForward
     torch.manual_seed(0)
     m = FeedForward(256, 512, "swiglu").cuda()
-    _compare(m, torch.randn(4, 128, 256, device="cuda"), lambda mod, t: mod(t))
+    _compare(m, torch.randn(4, 128, 256, device="cuda"), lambda mod, t: mod(t), expect=("gemm_bf16", "swiglu_fwd"))
 
 
 def test_rmsnorm_block():
@@ -78,7 +79,7 @@ def test_rmsnorm_block():
     m = RMSNorm(512).cuda()
     with torch.no_grad():
         m.weight.uniform_(0.5, 1.5)
-    _compare(m, torch.randn(3, 100, 512, device="cuda"), lambda mod, t: mod(t), rel=2e-2, grad_rel=3e-2)
+    _compare(m, torch.randn(3, 100, 512, device="cuda"), lambda mod, t: mod(t), rel=2e-2, grad_rel=3e-2, expect=("rmsnorm_fwd",))
 
 
 @pytest.mark.parametrize("S,H,Hk,Dq,Dv,topk", [(256, 4, 4, 64, 64, 0), (512, 4, 1, 192, 128, 96), (384, 2, 2, 192, 128, 200),

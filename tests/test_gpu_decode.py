@@ -84,9 +84,9 @@ def test_serving_paged_attention_uses_kernel():
                      advance=layer == 1)
     table, lengths = build_paged_block_table(m, [7, 9])
     q = torch.randn(2, 16, 576, device="cuda").bfloat16()
-    before = B.launch_count()
+    before = B.launch_count("paged_decode")
     out = paged_latent_decode_attention(q, m, 1, table, lengths, d_v=512, scale=576 ** -0.5)
-    assert B.launch_count() > before
+    assert B.launch_count("paged_decode") == before + 1
     ref = decode_attention_reference(q, m.k_pool[:, 1], None, table, lengths, scale=576 ** -0.5, d_v=512)
     _check(out, ref)
 
@@ -103,9 +103,9 @@ def test_model_decode_steps_use_kernel_and_match_eager(kw):
     with torch.no_grad():
         s = I.DecodeSession(m)
         s.forward(ids[:, :32])
-        before = B.launch_count()
+        before = B.launch_count("paged_decode")
         got = [s.forward(ids[:, i:i + 1])[:, -1].float() for i in range(32, 40)]
-        assert B.launch_count() > before
+        assert B.launch_count("paged_decode") >= before + 8 * 2      # one decode-attention launch per A layer per token
         with B.use_kernels(False):
             r = I.DecodeSession(m)
             r.forward(ids[:, :32])

@@ -45,9 +45,9 @@ def test_m2rnn_mixer_uses_kernel_and_matches_eager():
     torch.manual_seed(1)
     mix = M2RNNMixer(M2RNNConfig(d_model=256, k_head_dim=64, v_head_dim=16, num_v_heads=4, num_f_heads=4, num_g_heads=4)).cuda().bfloat16()
     x = (torch.randn(2, 96, 256, device="cuda") * 0.5).bfloat16()
-    n0 = B.launch_count()
+    n0, c0 = B.launch_count("m2rnn_fwd"), B.launch_count("conv_silu_fwd")
     out, _ = mix(x)
-    assert B.launch_count() > n0
+    assert B.launch_count("m2rnn_fwd") == n0 + 1 and B.launch_count("conv_silu_fwd") == c0 + 1
     with B.use_kernels(False):
         ref, _ = mix(x)
     assert torch.allclose(out.float(), ref.float(), atol=5e-2, rtol=5e-2)

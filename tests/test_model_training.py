@@ -160,6 +160,22 @@ def test_stp_loss_range():
     assert float(s) < 1e-5          # straight trajectory → zero curvature penalty
 
 
+def test_adamw_bias_correction_matches_torch_adamw():
+    from cppmega_mlx_b200.training.optimizers import make_adamw
+    torch.manual_seed(0)
+    w0 = torch.randn(40, 30) * 0.1
+    mine = [("w", torch.nn.Parameter(w0.clone()))]
+    theirs = torch.nn.Parameter(w0.clone())
+    opt = make_adamw(mine, learning_rate=1e-2, weight_decay=0.1, bias_correction=True)
+    ref = torch.optim.AdamW([theirs], lr=1e-2, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.1)
+    for _ in range(4):
+        g = torch.randn(40, 30) * 0.01
+        mine[0][1].grad, theirs.grad = g.clone(), g.clone()
+        opt.step()
+        ref.step()
+    assert torch.allclose(mine[0][1], theirs, atol=1e-6, rtol=1e-5)
+
+
 def test_muon_split_and_newton_schulz():
     m = _tiny()
     muon, other = split_param_groups(m)

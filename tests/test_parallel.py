@@ -102,6 +102,66 @@ def test_expert_parallel_matches_single_rank():
     assert all(run_ranks(_ep_rank, 2))
 
 
+def test_plan_slots_overflow_is_dropped_and_slots_stay_inside_the_buffer():
+    """The fused path's slot computation with a deliberately small receive buffer: every kept slot is inside the buffer and
+    unique per destination, every assignment that would not fit is marked −1, and all ranks agree on the layout."""
+    from cppmega_mlx_b200.parallel.ep import plan_slots
+    torch.manual_seed(0)
+    W, Le, A = 3, 2, 700
+    es = [torch.randint(0, W * Le, (A,)) for _ in range(W)]
+    es[1][:500] = 4                                              # a skewed router: rank 1 sends most rows to one expert
+    C = torch.stack([torch.bincount(e, minlength=W * Le).view(W, Le) for e in es])      # [src, dst, expert]
+    cap = 512
+    seen = [set() for _ in range(W)]
+    dropped = 0
+    for r in range(W):
+        dest, slot, keep, pad_off, pad_end, tot = plan_slots(es[r], C, r, Le, cap)
+        full = plan_slots(es[r], C, r, Le, None)[1]
+        assert torch.equal(keep, full < cap) and torch.equal(slot[keep], full[keep]) and bool((slot[~keep] == -1).all())
+        assert bool((slot[keep] >= 0).all()) and bool((slot[keep] < cap).all())
+        assert torch.equal(dest.long(), es[r] // Le)
+        for d, sl in zip(dest[keep].tolist(), slot[keep].tolist()):
+            assert sl not in seen[d]                             # no two assignments share a row of a receive buffer
+            seen[d].add(sl)
+        e_local = es[r][keep] % Le
+        lo, hi = pad_off[dest[keep].long(), e_local], pad_off[dest[keep].long(), e_local] + tot[dest[keep].long(), e_local]
+        assert bool(((slot[keep] >= lo) & (slot[keep] < hi)).all())     # inside its expert's segment
+        dropped += int((~keep).sum())
+    assert dropped > 0 and int(pad_end[:, -1].max()) > cap       # the case really overflows
+
+
+def _ep_capacity_rank(rank, world):
+    """With a capacity, the all-to-all path drops exactly the assignments ``plan_slots`` marks: the result equals the
+    uncapped path with those assignments' gate weights set to zero."""
+    from cppmega_mlx_b200.nn.moe import MoE, MoEConfig
+    from cppmega_mlx_b200.parallel import ep as EP
+    st = PS.init_parallel_state(ep=world)
+    cfg = MoEConfig(d_model=16, num_experts=4, top_k=2, expert_hidden_size=8, shared_expert_hidden_size=None, scoring="sigmoid")
+    torch.manual_seed(0)
+    full = MoE(cfg)
+    local = MoE(cfg, ep_group=st.ep_group)
+    EP.shard_experts_(full, local)
+    torch.manual_seed(7 + rank)
+    T = 300
+    flat = torch.randn(T, 16)
+    top_idx = torch.stack([torch.zeros(T, dtype=torch.long), 1 + torch.randint(0, 3, (T,))], 1)   # every token also picks expert 0
+    top_w = torch.rand(T, 2)
+    cap = 384
+    got = EP.ep_moe_forward(local, flat, top_idx, top_w, capacity_rows=cap)
+    mine = torch.bincount(top_idx.reshape(-1), minlength=4).view(world, 2)
+    allc = [torch.empty_like(mine) for _ in range(world)]
+    torch.distributed.all_gather(allc, mine)
+    keep = EP.plan_slots(top_idx.reshape(-1), torch.stack(allc), rank, 2, cap)[2].view(T, 2)
+    ref = EP.ep_moe_forward(local, flat, top_idx, top_w * keep)
+    assert int((~keep).sum()) > 0 or rank == 0
+    assert torch.allclose(got, ref, atol=1e-6)
+    return int((~keep).sum())
+
+
+def test_expert_parallel_capacity_drops_match_plan():
+    assert sum(run_ranks(_ep_capacity_rank, 2)) > 0
+
+
 def _pp_rank(rank, world):
     from cppmega_mlx_b200.ops import linear_cross_entropy
     from cppmega_mlx_b200.recipes.model_factory import build_local_gb10_quarter_tiny_smoke_model
