@@ -534,11 +534,8 @@ template <int DKB, int DVB, bool SHARED>
 int launch_decode(cmb::DecodeParams& p, long long ext2, long long ext3, cudaStream_t stream) {
   using Cfg = cmb::DecCfg<DKB, DVB, SHARED>;
   auto kern = cmb::paged_decode_kernel<DKB, DVB, SHARED>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 103;
-    attr_set = true;
-  }
+  static std::atomic<unsigned long long> attr_done{0};
+  if (cmb_host::set_smem_limit_once_per_device(attr_done, reinterpret_cast<const void*>(kern), Cfg::SMEM_BYTES)) return 103;
   // Dense key ranges whose 64-key tiles decompose into whole boxes inside one page go through TMA.
   const bool paged = p.table != nullptr;
   const int ps = p.page_size;

@@ -568,15 +568,7 @@ static int make_tmap_5d(CUtensorMap* out, const void* base, int elem_bytes, uint
   return r == CUDA_SUCCESS ? 0 : 1000 + static_cast<int>(r);
 }
 
-static int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
-}
+static int sm_count() { return sm_count_current_device(); }
 
 struct GemmArgs {
   const void* A;
@@ -631,11 +623,8 @@ static int launch_gemm(const GemmArgs& g) {
     if (rc) return rc + 20000;
   }
   auto kern = cmb::gemm_bf16_kernel<BN, A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 103;
-    attr_set = true;
-  }
+  static std::atomic<unsigned long long> attr_done{0};
+  if (set_smem_limit_once_per_device(attr_done, reinterpret_cast<const void*>(kern), Cfg::SMEM_BYTES)) return 103;
   const long long num_tiles = static_cast<long long>((g.M + cmb::GEMM_BM - 1) / cmb::GEMM_BM) * ((g.N + BN - 1) / BN) *
                               g.nb[0] * g.nb[1] * g.nb[2];
   if (num_tiles > 0x7fffffffLL) return 106;

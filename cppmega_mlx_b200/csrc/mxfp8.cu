@@ -364,14 +364,9 @@ static int launch_mx(const void* A, const void* sfa, const void* B, const void* 
   if (rc) return rc + 10000;
   rc = cmb_host::make_tmap_2d(&tmC, C, 2, M, N, ldc, 32, 64, 128);
   if (rc) return rc + 20000;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(cmb::gemm_mxfp8_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 103;
-    attr_set = true;
-  }
-  int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  static std::atomic<unsigned long long> attr_done{0};
+  if (cmb_host::set_smem_limit_once_per_device(attr_done, reinterpret_cast<const void*>(cmb::gemm_mxfp8_kernel<BN>), Cfg::SMEM_BYTES)) return 103;
+  const int sms = cmb_host::sm_count_current_device();
   const long long tiles = static_cast<long long>((M + cmb::MX_BM - 1) / cmb::MX_BM) * ((N + BN - 1) / BN);
   int grid = sms;
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;

@@ -13,6 +13,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace cmb {
 
 // Status codes written to status[0] (first error wins); status[1..3] carry detail.
@@ -295,5 +297,30 @@ void bind_context_once();
 // box = [box_rows, box_cols]. Returns 0 on success.
 int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
                  uint32_t box_rows, uint32_t box_cols, int swizzle_bytes);
+
+// Raises a kernel's dynamic shared-memory limit once per device: function attributes belong to the device that was current
+// when they were set, so a process that drives several GPUs must set them on each.  `done` is a bit mask over device
+// ordinals kept by the caller (one static per kernel instantiation).  Returns 0 or 103.
+inline int set_smem_limit_once_per_device(std::atomic<unsigned long long>& done, const void* kern, int bytes) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 103;
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (done.load(std::memory_order_acquire) & bit) return 0;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return 103;
+  done.fetch_or(bit, std::memory_order_release);
+  return 0;
+}
+// Multiprocessor count of the current device (cached per device ordinal).
+inline int sm_count_current_device() {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int n = cache[dev & 63].load(std::memory_order_relaxed);
+  if (n == 0) {
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cache[dev & 63].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
 
 }  // namespace cmb_host

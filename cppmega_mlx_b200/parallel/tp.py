@@ -136,7 +136,7 @@ class ColumnParallelLinear(nn.Module):
 
     def __init__(self, full: Linear, group, *, sequence_parallel: bool = False, blocks: int = 1):
         super().__init__()
-        self.group, self.sequence_parallel = group, sequence_parallel
+        self.group, self.sequence_parallel, self.blocks = group, sequence_parallel, blocks
         self.weight = nn.Parameter(shard_rows(full.weight.detach(), group, blocks=blocks).clone())
 
     def forward(self, x):

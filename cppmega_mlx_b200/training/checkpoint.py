@@ -307,6 +307,9 @@ def _filter_owned(optimizer, sd: dict) -> dict:
 
 
 def _load_optimizer_state(optimizer, sd: dict) -> None:
+    if hasattr(optimizer, "load_full_state"):    # composite sharded wrapper (dense ZeRO-1 + local experts)
+        optimizer.load_full_state(sd, _filter_owned)
+        return
     if hasattr(optimizer, "gather_full_state"):  # sharded wrapper: inner keeps what this rank owns
         optimizer.step_count = int(sd.get("step", 0))
         inner_sd = sd["inner"] if "inner" in sd else sd
@@ -356,18 +359,55 @@ def _write_weights(weights: dict[str, torch.Tensor], weights_path: Path, max_sha
 # ----------------------------------------------------------------------------------------------- save
 def save_checkpoint(model: torch.nn.Module, path, *, optimizer=None, training_step=None, metadata: dict | None = None,
                     reference_names: bool = True, max_shard_bytes: int | None = None) -> dict[str, Any]:
-    """Write a checkpoint; in a distributed run every rank must call (state is gathered), rank 0 writes."""
+    """Write a checkpoint; in a distributed run every rank must call (state is gathered), rank 0 writes.
+
+    Tensor-parallel FFN slices and expert-parallel expert banks are gathered to their logical tensors first (and sliced
+    again by ``load_checkpoint``), so the files never depend on the parallel layout.  If the writer fails, every rank
+    raises instead of waiting in a barrier."""
     metadata = dict(metadata or {})
     weights_path, metadata_path, optimizer_path = checkpoint_paths(path)
     reject_unsupported_fields(metadata, metadata_path)
     rng = _rng_contract(metadata, metadata_path, default_snapshot=optimizer is not None or training_step is not None)
+    # Collectives first, on every rank: tensor- / expert-parallel slices are gathered to logical tensors and the sharded
+    # optimizer state to its world-size independent form.  Only then does the writer rank touch the file system.
+    from ..parallel.sharded_state import consolidated_parameters, map_state_tree, sharded_specs
+    specs = sharded_specs(model)
+    weights = consolidated_parameters(model, specs)
     opt_state = _optimizer_full_state(optimizer) if (optimizer is not None and optimizer_path is not None) else None
+    if opt_state is not None and specs:
+        try:
+            opt_state = map_state_tree(opt_state, specs, dict(model.named_parameters()), to_logical=True)
+        except ValueError as e:
+            raise CheckpointError(f"checkpoint {path}: {e}") from e
     step_state = training_step.state_dict() if training_step is not None else None
-    if not _is_writer():
-        _barrier()
-        return {}
+    payload, error = {}, None
+    if _is_writer():
+        try:
+            payload = _write_checkpoint(model, weights, opt_state, step_state, optimizer, metadata, rng, weights_path, metadata_path,
+                                        optimizer_path, reference_names, max_shard_bytes)
+        except Exception as e:  # noqa: BLE001 - re-raised below, after the other ranks have been told
+            error = e
+    ok = _all_ranks_agree(error is None)      # also the "files are complete" barrier; never leaves the other ranks waiting
+    if error is not None:
+        raise error
+    if not ok:
+        raise CheckpointError(f"checkpoint {path}: the writer rank failed; nothing usable was written")
+    return payload
+
+
+def _all_ranks_agree(ok_here: bool) -> bool:
+    """Rank 0 tells every rank whether its write succeeded (doubles as the barrier after a save)."""
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()):
+        return ok_here
+    flag = [bool(ok_here)]
+    dist.broadcast_object_list(flag, src=0)
+    return bool(flag[0])
+
+
+def _write_checkpoint(model, weights, opt_state, step_state, optimizer, metadata, rng, weights_path, metadata_path, optimizer_path,
+                      reference_names, max_shard_bytes) -> dict[str, Any]:
     weights_path.parent.mkdir(parents=True, exist_ok=True)
-    weights = {n: p.detach() for n, p in model.named_parameters()}
     if getattr(getattr(model, "config", None), "tie_embeddings", False):
         weights.pop("lm_head.weight", None)
     if reference_names:
@@ -412,7 +452,6 @@ def save_checkpoint(model: torch.nn.Module, path, *, optimizer=None, training_st
     tmp = metadata_path.with_name(metadata_path.name + f".tmp.{os.getpid()}")
     tmp.write_text(json.dumps(payload, indent=2, sort_keys=True) + "\n")
     os.replace(tmp, metadata_path)  # metadata last: a directory without it is an incomplete checkpoint
-    _barrier()
     return payload
 
 
@@ -459,9 +498,14 @@ def load_checkpoint(model: torch.nn.Module, path, *, optimizer=None, training_st
     stored = _read_weights(weights_path, meta)
     if sorted(stored) != sorted(meta["tensors"]):
         raise CheckpointError(f"checkpoint {path}: weight file tensors do not match metadata.tensors")
-    params = dict(model.named_parameters())
+    from ..parallel.sharded_state import logical_shape, map_state_tree, sharded_specs, slice_local
+    specs = sharded_specs(model)                      # parameters of which this rank holds a tensor- / expert-parallel slice
+    local_params = dict(model.named_parameters())
+    params = {(specs[n].logical_name if n in specs else n): p for n, p in local_params.items()}
+    spec_of = {s.logical_name: s for s in specs.values()}
     tied = getattr(getattr(model, "config", None), "tie_embeddings", False)
-    wanted = {n: p.shape for n, p in params.items() if not (tied and n == "lm_head.weight")}
+    wanted = {n: (logical_shape(p.shape, spec_of[n]) if n in spec_of else p.shape) for n, p in params.items()
+              if not (tied and n == "lm_head.weight")}
     try:
         mapped = from_reference_names(stored, wanted)
     except KeyError as e:
@@ -491,12 +535,16 @@ def load_checkpoint(model: torch.nn.Module, path, *, optimizer=None, training_st
     # ---- mutation starts here
     with torch.no_grad():
         for n, t in mapped.items():
+            if n in spec_of:
+                t = slice_local(t, spec_of[n])
             params[n].copy_(t.to(params[n].device, params[n].dtype))
         named_buffers = dict(model.named_buffers())
         for n, t in buffers.items():
             if n in named_buffers and named_buffers[n].shape == t.shape:
                 named_buffers[n].copy_(t.to(named_buffers[n].device, named_buffers[n].dtype))
     if optimizer is not None:
+        if specs:
+            opt_tree = map_state_tree(opt_tree, specs, local_params, to_logical=False)
         _load_optimizer_state(optimizer, opt_tree)
     if training_step is not None:
         sd = dict(meta["training_state"]["state"])

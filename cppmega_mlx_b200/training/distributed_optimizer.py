@@ -283,6 +283,25 @@ class ExpertParallelZeRO1Optimizer:
     def state_dict(self) -> dict:
         return {"step": self.step_count, "dense": self.dense.state_dict(), "experts": self.experts.state_dict() if self.experts is not None else {}}
 
+    def gather_full_state(self) -> dict:
+        """World-size independent dense state plus this rank's expert state (keyed by local parameter names; the checkpoint
+        writer gathers expert-parallel slices to logical tensors).  A collective: every rank calls."""
+        e = self.experts
+        es = {} if e is None else (e.gather_full_state() if hasattr(e, "gather_full_state") else e.state_dict())
+        return {"dense": self.dense.gather_full_state(), "experts": es}
+
+    def load_full_state(self, sd: dict, filter_owned) -> None:
+        inner = sd["inner"] if "inner" in sd else sd
+        self.step_count = int(sd.get("step", 0))
+        self.dense.step_count = self.step_count
+        self.dense.inner.load_state_dict(filter_owned(self.dense.inner, inner["dense"]))
+        e = self.experts
+        if e is not None and inner.get("experts"):
+            target = e.inner if hasattr(e, "inner") else e
+            target.load_state_dict(filter_owned(target, inner["experts"]))
+            if hasattr(e, "inner"):
+                e.step_count = self.step_count
+
     def load_state_dict(self, sd: dict) -> None:
         self.step_count = int(sd.get("step", 0))
         self.dense.load_state_dict(sd["dense"])
