@@ -63,7 +63,7 @@ def test_mamba3_block():
     torch.manual_seed(0)
     m = Mamba3Block(Mamba3Config(d_model=256, headdim=64, d_state=64, ngroups=2, chunk_size=64, d_conv=4)).cuda()
     x = torch.randn(2, 256, 256, device="cuda") * 0.5
-    _compare(m, x, lambda mod, t: mod(t)[0], expect=("conv_silu_fwd", "m3_prep_dt_fwd", "m3_xw", "gemm_bf16_batched"))
+    _compare(m, x, lambda mod, t: mod(t)[0], expect=("conv_silu_fwd", "m3_xw", "m3_state_pass", "gemm_bf16_batched"))
 
 
 def test_feed_forward_block():
