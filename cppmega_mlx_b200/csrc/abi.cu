@@ -3,7 +3,7 @@
 // reference's native-bridge probe (cppmega_mlx/nn/_tilelang/native_bridge/tilelang_mlx_tvm_ffi_bridge.cpp:32-70).
 #include <cuda_runtime.h>
 
-extern "C" int cmb_abi_version() { return 2; }
+extern "C" int cmb_abi_version() { return 3; }
 
 extern "C" int cmb_device_sm_count() {
   int dev = 0, n = 0;

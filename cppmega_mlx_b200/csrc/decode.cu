@@ -66,22 +66,6 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
-__device__ __forceinline__ void named_bar_sync(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-// Barrier over `threads` threads that also ANDs a predicate, so that every participant takes the same exit decision.
-__device__ __forceinline__ bool named_bar_and(int id, int threads, bool pred) {
-  uint32_t out;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.b32 p, %3, 0;\n\t"
-      "barrier.cta.red.and.pred q, %1, %2, p;\n\t"
-      "selp.u32 %0, 1, 0, q;\n\t}\n"
-      : "=r"(out)
-      : "r"(id), "r"(threads), "r"(static_cast<uint32_t>(pred))
-      : "memory");
-  return out != 0;
-}
 __device__ __forceinline__ int float_order(float x) {
   const int i = __float_as_int(x);
   return i >= 0 ? i : i ^ 0x7fffffff;

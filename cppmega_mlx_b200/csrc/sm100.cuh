@@ -264,6 +264,23 @@ __host__ __device__ constexpr uint32_t make_idesc_mx(int m, int n, int a_fmt, in
          (static_cast<uint32_t>(m >> 4) << 24) | (static_cast<uint32_t>(a_sf_id) << 29);
 }
 
+// ----------------------------------------------------------------------------- named barriers
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// Barrier over `threads` threads that also ANDs a predicate, so that every participant takes the same exit decision.
+__device__ __forceinline__ bool named_bar_and(int id, int threads, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %3, 0;\n\t"
+      "barrier.cta.red.and.pred q, %1, %2, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}\n"
+      : "=r"(out)
+      : "r"(id), "r"(threads), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return out != 0;
+}
 // ----------------------------------------------------------------------------- small helpers
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

@@ -22,7 +22,7 @@ import torch
 
 _CSRC = Path(__file__).resolve().parent.parent / "csrc"
 LIB_NAME = "libcppmega_b200.so"
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 _enabled = True  # process-wide on purpose: autograd runs backward (and checkpoint recomputation) on its own threads
 _lib = None

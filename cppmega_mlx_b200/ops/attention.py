@@ -1,4 +1,9 @@
-"""Causal attention under an explicit key bitmask, on the batched tcgen05 GEMM.
+"""Causal attention under an explicit key bitmask.
+
+Head sizes (64, 64), (128, 128) and (192, 128) run the fused kernels of ``csrc/flash_attn.cu``: one forward launch (scores,
+online softmax and P·V with S and P resident in TMEM / shared memory) and two backward launches (dK/dV per key tile, dQ per
+query tile); no S×S tensor exists and memory is O(S).  Other head sizes (the 576/512 latent form of the sparse-MLA op) run
+the GEMM pipeline described below.
 
 This is the engine behind both the sparse-MLA op (latent form: ``K = kv``, ``V = kv[..., :d_v]``, all
 heads share one KV group) and the multi-head form the MLA block uses for training (per-head K/V with
@@ -97,11 +102,42 @@ def _scores_pass(q, k, mask, scale, *, lse=None, delta=None, P=None, dO=None, v=
     return P
 
 
+FLASH_SHAPES = ((64, 64), (128, 128), (192, 128))
+
+
+def flash_supported(q, k, v) -> bool:
+    """Head sizes the fused kernel (``csrc/flash_attn.cu``) is instantiated for."""
+    return ((q.shape[3], v.shape[3]) in FLASH_SHAPES and q.shape[0] <= 65535 and q.shape[2] <= 65535
+            and hasattr(B.load_library(), "cmb_flash_fwd"))
+
+
+def flash_forward(q, k, v, mask, scale):
+    """One launch: O [B,S,H,Dv] bf16 and lse [B,H,S] fp32 (natural log; +inf where a row sees no key). No S×S tensor exists."""
+    lib = B.load_library()
+    Bn, S, H, Dq = q.shape
+    Hk, Dv = v.shape[2], v.shape[3]
+    out = torch.empty(Bn, S, H, Dv, dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty(Bn, H, S, dtype=torch.float32, device=q.device)
+    W = 0 if mask is None else mask.shape[-1]
+    ip = (ctypes.c_int * 7)(Bn, S, H, Hk, Dq, Dv, W)
+    lp = (ctypes.c_longlong * 13)(q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1),
+                                  v.stride(2), out.stride(0), out.stride(1), out.stride(2), S * W)
+    B.check(lib.cmb_flash_fwd(B.ptr(q), B.ptr(k), B.ptr(v), B.ptr(mask), B.ptr(out), B.ptr(lse), ip, lp, ctypes.c_float(scale),
+                              B.ptr(B.status_buffer(q.device)), B.stream_ptr()), "flash_fwd")
+    return out, lse
+
+
 class _MaskedAttentionFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, mask, scale):
         Bn, S, H, Dq = q.shape
         Hk, Dv = v.shape[2], v.shape[3]
+        if flash_supported(q, k, v):
+            O, lse = flash_forward(q, k, v, mask, scale)
+            ctx.save_for_backward(q, k, v, mask if mask is not None else q.new_zeros(0), lse, O)
+            ctx.scale, ctx.has_mask = scale, mask is not None
+            ctx.mark_non_differentiable(lse)
+            return O, lse
         lse = _scores_pass(q, k, mask, scale)
         P = _scores_pass(q, k, mask, scale, lse=lse)
         O = torch.empty(Bn, S, H, Dv, dtype=torch.bfloat16, device=q.device)
@@ -126,6 +162,18 @@ class _MaskedAttentionFn(torch.autograd.Function):
         gO = gO.contiguous()
         delta = torch.empty(Bn, H, S, dtype=torch.float32, device=dev)
         B.check(lib.cmb_attn_delta(B.ptr(gO), B.ptr(O), B.ptr(delta), Bn, S, H, Dv, B.stream_ptr()), "attn_delta")
+        if flash_supported(q, k, v) and hasattr(lib, "cmb_flash_bwd"):
+            # two fused launches (dK/dV per key tile, dQ per query tile); a GQA group is summed inside the key-tile kernel
+            dQ = torch.empty(Bn, S, H, Dq, dtype=bf, device=dev)
+            dK = torch.empty(Bn, S, Hk, Dq, dtype=bf, device=dev)
+            dV = torch.empty(Bn, S, Hk, Dv, dtype=bf, device=dev)
+            W = 0 if mask is None else mask.shape[-1]
+            ip = (ctypes.c_int * 7)(Bn, S, H, Hk, Dq, Dv, W)
+            strides = [t.stride(i) for t in (q, k, v, gO, dQ, dK, dV) for i in (0, 1, 2)]
+            lp = (ctypes.c_longlong * 22)(*strides, S * W)
+            B.check(lib.cmb_flash_bwd(B.ptr(q), B.ptr(k), B.ptr(v), B.ptr(gO), B.ptr(mask), B.ptr(lse), B.ptr(delta), B.ptr(dQ), B.ptr(dK),
+                                      B.ptr(dV), ip, lp, ctypes.c_float(scale), B.ptr(B.status_buffer(dev)), B.stream_ptr()), "flash_bwd")
+            return dQ, dK, dV, None, None
         P = _scores_pass(q, k, mask, scale, lse=lse)
         nb, sP = (H, 1, Bn), (S * S, 0, H * S * S)
         # dV = Pᵀ dO   (contraction over queries t ≥ the key tile)

@@ -69,6 +69,20 @@ def case_zero1(rank, world, dev):
                           "max_param_diff": float(diff), "rank_spread": float(spread)}))
 
 
+def case_zero1det(rank, world, dev):
+    """Determinism of the fused ZeRO-1 step: two runs from the same seeds end with bit-identical parameters on every rank
+    (each owner sums the peers' gradients in a fixed rank order; nothing in the step uses atomics)."""
+    from cppmega_mlx_b200.ops import _backend as B
+    l_a, p_a = _train("fused", 3, dev, rank, world)
+    l_b, p_b = _train("fused", 3, dev, rank, world)
+    torch.cuda.synchronize()
+    B.check_status()
+    same = torch.tensor([int(torch.equal(p_a, p_b))], device=dev)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(json.dumps({"case": "zero1det", "world": world, "bitwise_equal": bool(int(same)), "loss_a": l_a, "loss_b": l_b}))
+
+
 def _time(fn, iters=10, warmup=3):
     for _ in range(warmup):
         fn()
@@ -172,11 +186,53 @@ def case_ep(rank, world, dev):
                           "rel_err_vs_nccl[y,dx,dw_gate_up,dw_down,dw_router]": errs, "ms_fwd_bwd_nccl": t_nccl, "ms_fwd_bwd_fused": t_fused}))
 
 
+def case_epdrop(rank, world, dev):
+    """A router that sends every token to expert 0 (plus one random expert) into a receive buffer that is far too small: the
+    fused path drops the assignments that do not fit (slot −1, skipped by the kernels, counted), never writes outside a buffer
+    (status words stay clean) and agrees with the all-to-all path under the same drop rule."""
+    from cppmega_mlx_b200.nn.moe import MoE, MoEConfig
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.parallel import ep as EP
+    from cppmega_mlx_b200.parallel.fused_ep import FusedEPComm, fused_ep_moe_forward
+    T, d, E, k, hid = 512, 256, 8, 2, 128
+    cfg = MoEConfig(d_model=d, num_experts=E, top_k=k, expert_hidden_size=hid, shared_expert_hidden_size=None, activation="swiglu",
+                    scoring="sigmoid", aux_loss_free=True)
+    torch.manual_seed(0)
+    full = MoE(cfg).to(dev, torch.bfloat16)
+    g = dist.group.WORLD
+    local = MoE(cfg, ep_group=g).to(dev, torch.bfloat16)
+    EP.shard_experts_(full, local)
+    torch.manual_seed(100 + rank)
+    x = (torch.randn(T, d, device=dev) * 0.5).bfloat16()
+    idx = torch.stack([torch.zeros(T, dtype=torch.long, device=dev), 1 + torch.randint(0, E - 1, (T,), device=dev)], 1)
+    w = torch.rand(T, k, device=dev)
+    comm = FusedEPComm(g, dev, max_tokens=T, top_k=k, d_model=d, num_experts=E, capacity_rows=512)
+    outs = []
+    for fused in (False, True):
+        xs = x.clone().requires_grad_()
+        local.zero_grad()
+        y = fused_ep_moe_forward(local, comm, xs, idx, w) if fused else EP.ep_moe_forward(local, xs, idx, w, capacity_rows=comm.rows)
+        y.backward(torch.ones_like(y) * 0.01)
+        outs.append((y.detach(), xs.grad.clone(), local.experts.w_down.grad.clone()))
+    torch.cuda.synchronize()
+    B.check_status()                                       # no slot outside a buffer was ever presented to a kernel
+    dropped = torch.tensor([comm.dropped_assignments()], device=dev)
+    dist.all_reduce(dropped)
+    errs = []
+    for r_, o_ in zip(*outs):
+        e = (r_.float() - o_.float()).abs().max() / r_.float().abs().max().clamp_min(1e-6)
+        dist.all_reduce(e, op=dist.ReduceOp.MAX)
+        errs.append(float(e))
+    if rank == 0:
+        print(json.dumps({"case": "epdrop", "world": world, "capacity_rows": comm.rows, "dropped_total": int(dropped),
+                          "rel_err_vs_nccl[y,dx,dw_down]": errs}))
+
+
 def main():
     case = sys.argv[1] if len(sys.argv) > 1 else "zero1"
     rank, world, dev = _setup()
     try:
-        {"zero1": case_zero1, "tp": case_tp, "ep": case_ep}[case](rank, world, dev)
+        {"zero1": case_zero1, "zero1det": case_zero1det, "tp": case_tp, "ep": case_ep, "epdrop": case_epdrop}[case](rank, world, dev)
     finally:
         dist.barrier()
         dist.destroy_process_group()

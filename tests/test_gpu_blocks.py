@@ -83,7 +83,8 @@ def test_rmsnorm_block():
 
 
 @pytest.mark.parametrize("S,H,Hk,Dq,Dv,topk", [(256, 4, 4, 64, 64, 0), (512, 4, 1, 192, 128, 96), (384, 2, 2, 192, 128, 200),
-                                               (128, 2, 1, 64, 32, 40)])
+                                               (128, 2, 1, 64, 32, 40), (200, 2, 2, 128, 128, 50), (1000, 2, 1, 192, 128, 300),
+                                               (72, 3, 3, 64, 64, 0)])
 def test_masked_attention_matches_reference(S, H, Hk, Dq, Dv, topk):
     from cppmega_mlx_b200 import ops
     from cppmega_mlx_b200.ops import _backend as B
@@ -103,7 +104,9 @@ def test_masked_attention_matches_reference(S, H, Hk, Dq, Dv, topk):
         bits = A.build_mask_bits(idx, S)
         mask_bool = ops.indices_to_mask(idx[:, :, None, :], S)[:, 0]
     assert A.supported(q, k, v)
+    n_flash = B.launch_count("flash_fwd")
     O, lse = ops.masked_attention(q, k, v, bits)
+    assert B.launch_count("flash_fwd") == n_flash + (1 if (Dq, Dv) in A.FLASH_SHAPES else 0)     # the fused kernel ran for its head sizes
     gO = torch.randn_like(O)
     gq, gk, gv = torch.autograd.grad(O, [q, k, v], gO)
     torch.cuda.synchronize()

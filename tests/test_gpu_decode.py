@@ -98,7 +98,10 @@ def test_model_decode_steps_use_kernel_and_match_eager(kw):
     from cppmega_mlx_b200.ops import _backend as B
     from cppmega_mlx_b200.recipes.model_factory import build_local_gb10_quarter_tiny_smoke_model
     torch.manual_seed(0)
-    m = build_local_gb10_quarter_tiny_smoke_model(pattern="AA", depth=2, **kw).eval().cuda().bfloat16()
+    # latent rows of 512 + 64 columns: the geometry the decode kernel is built for (a toy latent width would legitimately
+    # run the PyTorch path, and the launch counter below would say so)
+    m = build_local_gb10_quarter_tiny_smoke_model(pattern="AA", depth=2, mla_kv_lora_rank=512, mla_qk_rope_head_dim=64,
+                                                  dsa_indexer_head_dim=64, **kw).eval().cuda().bfloat16()
     ids = torch.randint(4, 100, (2, 40), device="cuda")
     with torch.no_grad():
         s = I.DecodeSession(m)

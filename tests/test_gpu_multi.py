@@ -17,18 +17,55 @@ def _need(n):
         pytest.skip(f"needs {n} GPUs")
 
 
-def _torchrun(n, script_args, timeout=600):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+def _free_port() -> int:
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _torchrun(n, script_args, timeout=600, extra_env=None):
+    # NVLS off and plain peer loads / stores in our own kernels: a rank that died while bound to a multicast object would
+    # fault its peers; a free port, so concurrent jobs on a shared machine cannot collide.
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", **(extra_env or {}))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-           "--master-port", "29641"] + script_args
+           "--master-port", str(_free_port())] + script_args
     return subprocess.run(cmd, cwd=REPO, env=env, capture_output=True, text=True, timeout=timeout)
 
 
-def test_fused_zero1_matches_nccl_zero1_two_gpus():
-    _need(2)
-    res = _torchrun(2, ["-m", "cppmega_mlx_b200.parallel.selftest", "zero1"])
+def _selftest(case, n=2, extra_env=None):
+    _need(n)
+    res = _torchrun(n, ["-m", "cppmega_mlx_b200.parallel.selftest", case], extra_env=extra_env)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
-    line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
-    out = json.loads(line)
+    return json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+
+
+def test_fused_zero1_matches_nccl_zero1_two_gpus():
+    out = _selftest("zero1")
     assert out["max_param_diff"] < 2e-2, out
+    assert out["rank_spread"] == 0.0, out
     assert all(abs(a - b) < 5e-2 for a, b in zip(out["loss_fused"], out["loss_nccl"])), out
+
+
+def test_fused_zero1_is_bitwise_deterministic_two_gpus():
+    out = _selftest("zero1det")
+    assert out["bitwise_equal"], out
+    assert out["loss_a"] == out["loss_b"], out
+
+
+def test_fused_tp_pairs_match_nccl_two_gpus():
+    """GEMM → reduce-scatter and all-gather → GEMM over peer memory against the NCCL pairs (small shape)."""
+    out = _selftest("tp", extra_env={"CMB_TP_SMALL": "1"})
+    assert all(e < 3e-2 for e in out["rel_err_vs_nccl[y,dx,dw_up,dw_down]"]), out
+    assert out["rel_err_vs_fp32_single_gpu"] < 3e-2, out
+
+
+def test_fused_ep_dispatch_combine_matches_all_to_all_two_gpus():
+    out = _selftest("ep", extra_env={"CMB_EP_SMALL": "1"})
+    assert all(e < 5e-2 for e in out["rel_err_vs_nccl[y,dx,dw_gate_up,dw_down,dw_router]"]), out
+
+
+def test_fused_ep_overflow_is_dropped_not_written_two_gpus():
+    out = _selftest("epdrop")
+    assert out["dropped_total"] > 0, out
+    assert all(e < 5e-2 for e in out["rel_err_vs_nccl[y,dx,dw_down]"]), out
