@@ -247,6 +247,58 @@ def bench_sparse_mla(args) -> list[dict]:
     return rows
 
 
+def bench_flash(args) -> list[dict]:
+    """Fused masked causal attention (``csrc/flash_attn.cu``) at the training shapes: multi-head MLA form 192/128 with the
+    top-2048 bitmask (the 1B hybrid's A layers: B4 S4096 H16), the same at S8192 H28 B2, and a plain causal 128/128 case; against
+    the GEMM pipeline the same op used before (statistics pass, P in HBM) and, forward only, the PyTorch restatement.  TFLOP/s count
+    the causal-dense products: forward 2·(Dq+Dv) per (query, key ≤ query) pair, backward 2.5×."""
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops import attention as A
+    pk = peaks()
+    dev = "cuda"
+    rows = []
+    for (b, S, H, Hk, dq, dv, topk, label) in ((4, 4096, 16, 16, 192, 128, 2048, "MLA heads, top-2048 mask"), (2, 8192, 28, 28, 192, 128, 2048, "MLA heads S8192"),
+                                              (4, 4096, 16, 4, 128, 128, 0, "GQA 128/128 causal")):
+        if args.only and args.only not in label:
+            continue
+        torch.manual_seed(0)
+        q = torch.randn(b, S, H, dq, device=dev).bfloat16().requires_grad_()
+        k = torch.randn(b, S, Hk, dq, device=dev).bfloat16().requires_grad_()
+        v = torch.randn(b, S, Hk, dv, device=dev).bfloat16().requires_grad_()
+        bits = None
+        if topk:
+            ends = torch.arange(1, S + 1, device=dev, dtype=torch.int32).repeat(b)
+            idx = ops.topk_select(torch.randn(b * S, S, device=dev), topk, None, ends).view(b, S, topk)
+            bits = A.build_mask_bits(idx, S)
+            del idx
+        pairs = b * H * S * (S + 1) / 2
+        fl_f = 2.0 * pairs * (dq + dv)
+
+        def fwd():
+            return ops.masked_attention(q, k, v, bits)[0]
+        with torch.no_grad():
+            ms_f = time_cuda(fwd, iters=args.iters, warmup=args.warmup)
+        ms_fb = time_cuda(_fb(fwd, q, k, v), iters=args.iters, warmup=args.warmup)
+        row = {"op": f"flash attention {label} B{b} S{S} H{H}/{Hk} d{dq}/{dv}", "fwd_ms": ms_f, "fwd_tflops": fl_f / ms_f / 1e9,
+               "fwd_frac_of_measured_peak": fl_f / ms_f / 1e9 / pk["bf16_tflops"], "fwd_bwd_ms": ms_fb, "fwd_bwd_tflops": 3.5 * fl_f / ms_fb / 1e9,
+               "fwd_bwd_frac_of_measured_peak": 3.5 * fl_f / ms_fb / 1e9 / pk["bf16_tflops"]}
+        if not args.no_eager:
+            saved = A.FLASH_SHAPES
+            A.FLASH_SHAPES = ()                       # the GEMM pipeline this op ran on before the fused kernels
+            try:
+                with torch.no_grad():
+                    row["gemm_pipeline_fwd_ms"] = time_cuda(fwd, iters=3, warmup=1)
+                row["gemm_pipeline_fwd_bwd_ms"] = time_cuda(_fb(fwd, q, k, v), iters=3, warmup=1)
+            finally:
+                A.FLASH_SHAPES = saved
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+        del q, k, v, bits
+        torch.cuda.empty_cache()
+    return rows
+
+
 def bench_linears(args) -> list[dict]:
     """Decode-step linears for 1–32 activation rows: the CUDA-core streaming kernel (≤ 8 rows), the warp-MMA streaming kernel
     (≤ 32 rows), the 128-row tcgen05 GEMM and cuBLAS (``F.linear``), each as a CUDA graph of calls over a rotation of weight
@@ -599,7 +651,7 @@ def bench_serving(args) -> list[dict]:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "dsa_loss", "linears", "mamba3_step", "decode", "decode_loop", "serving", "decode_trace", "decode_profile", "step_profile", "all"])
+    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "flash", "dsa_loss", "linears", "mamba3_step", "decode", "decode_loop", "serving", "decode_trace", "decode_profile", "step_profile", "all"])
     ap.add_argument("--json", default=None)
     ap.add_argument("--only", default=None, help="run the single case with this label (small captures under a profiler)")
     ap.add_argument("--iters", type=int, default=10)
@@ -617,6 +669,8 @@ def main(argv=None) -> int:
         rows += bench_composite(args)
     if args.op in ("mxfp8", "all"):
         rows += bench_mxfp8(args)
+    if args.op in ("flash", "all"):
+        rows += bench_flash(args)
     if args.op in ("m2rnn", "all"):
         rows += bench_m2rnn(args)
     if args.op in ("sparse_mla", "all"):

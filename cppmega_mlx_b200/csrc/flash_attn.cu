@@ -11,8 +11,8 @@
 //   O  += P · V_tile           tcgen05.mma 128×Dv×16 into the resident O accumulator in TMEM (V read MN-major in place)
 //
 // Neither S nor P ever reaches global memory; the score product is formed once.  The running maximum is only moved when
-// a tile exceeds it by 2⁸ (the denominator sums the same bf16-rounded probabilities that the tensor cores multiply, so
-// the lazy reference is exact); O is rescaled in TMEM only then.  Output: O (bf16) and the log-sum-exp per row.
+// a tile exceeds it by 2⁸ (probabilities then stay below 2⁸, well inside bf16 / fp32 range, and numerator and denominator
+// share the reference, so the lazy reference is exact up to rounding); O is rescaled in TMEM only then.  Output: O (bf16) and the log-sum-exp per row.
 //
 // Roles in a 320-thread CTA: warp 0 TMA producer (Q once; K as a ring of [128 keys × 64 columns] blocks so that a
 // 192-wide head needs 5 blocks of buffering instead of two whole tiles; V double-buffered), warp 1 issues every MMA,
@@ -232,23 +232,40 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       bool got = mbar_wait(&s_full[buf], (j >> 1) & 1, abort_flag, status, ST_TIMEOUT_TMEM_FULL);
       tc_fence_after();
+      // Raw scores stay unscaled: the softmax scale is positive, so the maximum commutes with it and the scaling rides on the
+      // exponent's fused multiply-add.  Masking is skipped for warps whose 32 rows see every key of the tile (the common case
+      // below the diagonal without a bitmask), which removes a select per element.
       float t[64];
       {
         uint32_t r[32];
         tmem_ld_x32(tmem_base + lane_addr + buf * FA_BN + half * 64, r);
         tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) t[c] = ((bits[0] >> c) & 1u) ? __uint_as_float(r[c]) * p.scale_log2 : -INFINITY;
+        for (int c = 0; c < 32; ++c) t[c] = __uint_as_float(r[c]);
         tmem_ld_x32(tmem_base + lane_addr + buf * FA_BN + half * 64 + 32, r);
         tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) t[32 + c] = ((bits[1] >> c) & 1u) ? __uint_as_float(r[c]) * p.scale_log2 : -INFINITY;
+        for (int c = 0; c < 32; ++c) t[32 + c] = __uint_as_float(r[c]);
       }
       tc_fence_before();
       mbar_arrive(&s_free[buf]);
-      float lmax = -INFINITY;
+      if (!__all_sync(0xffffffffu, (bits[0] & bits[1]) == 0xffffffffu)) {
 #pragma unroll
-      for (int c = 0; c < 64; ++c) lmax = fmaxf(lmax, t[c]);
+        for (int c = 0; c < 32; ++c) {
+          t[c] = ((bits[0] >> c) & 1u) ? t[c] : -INFINITY;
+          t[32 + c] = ((bits[1] >> c) & 1u) ? t[32 + c] : -INFINITY;
+        }
+      }
+      float lmax;
+      {   // eight independent chains: the reduction is latency-bound otherwise (two warps per scheduler cannot hide it)
+        float m8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m8[i] = t[i];
+#pragma unroll
+        for (int c = 8; c < 64; ++c) m8[c & 7] = fmaxf(m8[c & 7], t[c]);
+        lmax = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+      }
+      lmax *= p.scale_log2;
       float* mx = xch + buf * 256;
       mx[half * 128 + row] = lmax;
       if (!named_bar_and(bar_id, 64, got)) {
@@ -284,22 +301,25 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_wait_st();
         }
       }
-      // P row → shared memory: block `half`, line `row`, eight 16-byte chunks at (chunk ^ (row & 7))
+      // P row → shared memory: block `half`, line `row`, eight 16-byte chunks at (chunk ^ (row & 7)).  exp2(−inf) = 0 covers
+      // masked keys; a row that has seen no key yet uses 0 as its reference so that −inf − m stays −inf.
+      const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
       uint8_t* prow = ps + half * FA_BLK + row * 128;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
         uint32_t w4[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float a0 = t[8 * ch + 2 * i], a1 = t[8 * ch + 2 * i + 1];
-          const __nv_bfloat162 pb = __floats2bfloat162_rn(a0 == -INFINITY ? 0.f : exp2f(a0 - m_ref),
-                                                          a1 == -INFINITY ? 0.f : exp2f(a1 - m_ref));
-          const float2 back = __bfloat1622float2(pb);
-          l_part += back.x + back.y;
-          w4[i] = *reinterpret_cast<const uint32_t*>(&pb);
+          const float p0 = exp2f(fmaf(t[8 * ch + 2 * i], p.scale_log2, neg_m));
+          const float p1 = exp2f(fmaf(t[8 * ch + 2 * i + 1], p.scale_log2, neg_m));
+          acc[2 * i] += p0;
+          acc[2 * i + 1] += p1;
+          w4[i] = pack_bf16x2(p0, p1);
         }
         *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
       }
+      l_part += ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_full);
@@ -413,7 +433,7 @@ extern "C" int cmb_flash_fwd(const void* q, const void* k, const void* v, const 
   a.B = ip[0]; a.S = ip[1]; a.H = ip[2]; a.Hk = ip[3]; a.Dq = ip[4]; a.Dv = ip[5];
   a.q_sb = lp[0]; a.q_ss = lp[1]; a.q_sh = lp[2]; a.k_sb = lp[3]; a.k_ss = lp[4]; a.k_sh = lp[5];
   a.v_sb = lp[6]; a.v_ss = lp[7]; a.v_sh = lp[8];
-  if (a.B <= 0 || a.S <= 0 || a.H <= 0 || a.Hk <= 0 || a.H % a.Hk || a.B > 65535 || a.H > 65535) return 1;
+  if (a.B <= 0 || a.S <= 0 || a.H <= 0 || a.Hk <= 0 || a.H % a.Hk || a.B > 65535 || a.H > 65535 || !(scale > 0.f)) return 1;
   cmb::FlashParams p{};
   p.B = a.B; p.S = a.S; p.H = a.H; p.Hk = a.Hk;
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -629,13 +649,43 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
       delta_row = row_ok ? p.delta[o] : 0.f;
       if (p.mask != nullptr && row_ok) mrow = p.mask + b * p.mask_sb + static_cast<long long>(grow) * p.mask_words;
     }
+    // Per-step side inputs are fetched one step ahead so that their global-memory latency hides behind the previous step:
+    // DQ mode needs this row's mask word for the step's 32 keys; DKV mode needs, per query column, lse, δ and the mask word
+    // of this warp's 32 keys (lane c fetches column c; the warp shares them through its private staging row).
+    auto fetch = [&](int n, unsigned& word, float4& a) {
+      word = 0u;
+      a = make_float4(INFINITY, 0.f, __uint_as_float(0u), 0.f);
+      if (n >= NT) return;
+      const int c0n = (sub_first + n % sub_count) * FB_SUB + half * 32;
+      if (MODE == BWD_DQ) {
+        if (row_ok && c0n < p.S) {
+          word = 0xffffffffu;
+          if (mrow != nullptr) word = (c0n >> 5) < p.mask_words ? __ldg(mrow + (c0n >> 5)) : 0u;
+        }
+      } else {
+        const int hq = h_first + n / sub_count;
+        const int qc = c0n + lane;
+        if (qc < p.S) {
+          const long long o = (static_cast<long long>(b) * p.H + hq) * p.S + qc;
+          a.x = __ldg(p.lse + o) * LOG2E;
+          a.y = __ldg(p.delta + o);
+          unsigned w = 0xffffffffu;
+          if (p.mask != nullptr) {
+            const int wi = (row0 + quarter * 32) >> 5;
+            w = wi < p.mask_words ? __ldg(p.mask + b * p.mask_sb + static_cast<long long>(qc) * p.mask_words + wi) : 0u;
+          }
+          a.z = __uint_as_float(w);
+        }
+      }
+    };
+    unsigned word_next;
+    float4 aux_next;
+    fetch(0, word_next, aux_next);
     for (int n = 0; n < NT; ++n) {
       const int c0 = (sub_first + n % sub_count) * FB_SUB + half * 32;   // global index of this thread's first column
-      unsigned bits = 0u;
+      unsigned bits = word_next;
       if (MODE == BWD_DQ) {
         if (row_ok && c0 < p.S) {
-          bits = 0xffffffffu;
-          if (mrow != nullptr) bits = (c0 >> 5) < p.mask_words ? __ldg(mrow + (c0 >> 5)) : 0u;
           const int lim = grow - c0;
           if (lim < 0) bits = 0u;
           else if (lim < 31) bits &= (2u << lim) - 1u;
@@ -643,27 +693,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
           if (rem < 32) bits &= (1u << rem) - 1u;
         }
       } else {
-        // column statistics: lane c fetches those of query c0 + c, the warp shares them through its private staging row
-        const int hq = h_first + n / sub_count;
-        const int qc = c0 + lane;
-        float4 a = make_float4(INFINITY, 0.f, 0.f, 0.f);
-        if (qc < p.S) {
-          const long long o = (static_cast<long long>(b) * p.H + hq) * p.S + qc;
-          a.x = p.lse[o] * LOG2E;
-          a.y = p.delta[o];
-          unsigned w = 0xffffffffu;
-          if (p.mask != nullptr) {
-            const int wi = (row0 + quarter * 32) >> 5;
-            w = wi < p.mask_words ? __ldg(p.mask + b * p.mask_sb + static_cast<long long>(qc) * p.mask_words + wi) : 0u;
-          }
-          a.z = __uint_as_float(w);
-        } else {
-          a.z = __uint_as_float(0u);
-        }
         __syncwarp();            // everyone is done reading the previous step's row
-        my_aux[lane] = a;
+        my_aux[lane] = aux_next;
         __syncwarp();
       }
+      fetch(n + 1, word_next, aux_next);
       if (!mbar_wait(x_full, n & 1, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
       uint32_t x1[32], x2[32];
@@ -690,9 +724,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmR1, const __grid_constant
             l2 = a.x;
             dl = a.y;
           }
-          const float pe = on ? exp2f(__uint_as_float(x1[c + e]) * p.scale_log2 - l2) : 0.f;
+          // exp2(x·c − lse): an empty row has lse = +inf and yields 0; the softmax scale rides on the fused multiply-add
+          const float pe = on ? exp2f(fmaf(__uint_as_float(x1[c + e]), p.scale_log2, -l2)) : 0.f;
           pv[e] = pe;
-          dv[e] = pe * (__uint_as_float(x2[c + e]) - dl) * p.scale;
+          dv[e] = (pe * p.scale) * (__uint_as_float(x2[c + e]) - dl);
         }
         pw[c >> 1] = pack_bf16x2(pv[0], pv[1]);
         dw[c >> 1] = pack_bf16x2(dv[0], dv[1]);
@@ -822,7 +857,7 @@ extern "C" int cmb_flash_bwd(const void* q, const void* k, const void* v, const 
   a.B = ip[0]; a.S = ip[1]; a.H = ip[2]; a.Hk = ip[3]; a.Dq = ip[4]; a.Dv = ip[5];
   a.q_sb = lp[0]; a.q_ss = lp[1]; a.q_sh = lp[2]; a.k_sb = lp[3]; a.k_ss = lp[4]; a.k_sh = lp[5];
   a.v_sb = lp[6]; a.v_ss = lp[7]; a.v_sh = lp[8];
-  if (a.B <= 0 || a.S <= 0 || a.H <= 0 || a.Hk <= 0 || a.H % a.Hk || a.B > 65535 || a.H > 65535) return 1;
+  if (a.B <= 0 || a.S <= 0 || a.H <= 0 || a.Hk <= 0 || a.H % a.Hk || a.B > 65535 || a.H > 65535 || !(scale > 0.f)) return 1;
   for (int i = 12; i < 21; ++i)
     if (lp[i] & 7) return 1;
   if ((reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv)) & 15) return 1;

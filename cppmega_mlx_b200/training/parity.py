@@ -97,3 +97,129 @@ def forward_parity_manifest(model, input_ids: torch.Tensor, artifact_path, *, la
         ours = {"hidden": h, "logits": model.lm_head(h)}
     model.train(was)
     return parity_against_artifact(label, ours, artifact_path)
+
+
+# ----------------------------------------------------------------------------------------------- MTP loss parity
+MTP_ARTIFACT_FORMAT = "cppmega_mtp_reference_v1"
+PREFLIGHT_STATUSES = ("not_supplied", "missing", "invalid", "valid")
+
+
+def loss_values_sha256(loss_values: Mapping[str, Any]) -> str:
+    """Checksum over the loss scalars of an artifact (keys sorted, values as repr of their float), so a manifest can show that
+    the numbers it compared are the numbers the artifact was published with."""
+    import hashlib
+    blob = json.dumps({k: repr(float(v)) for k, v in sorted(loss_values.items())}, sort_keys=True).encode()
+    return hashlib.sha256(blob).hexdigest()
+
+
+def validate_mtp_artifact(payload: Any, *, profile: str | None, mtp_depth: int, mtp_beta: float, mtp_lambda: float) -> None:
+    """Contract of an external MTP reference artifact (JSON): format tag, the profile and MTP hyper-parameters it was produced
+    with (they must equal ours — comparing losses of different objectives proves nothing), finite ``loss_values`` with a main
+    loss, one entry per depth and the total, and a matching checksum.  Raises ``ValueError`` naming the first violation."""
+    if not isinstance(payload, Mapping):
+        raise ValueError("artifact must be a JSON object")
+    if payload.get("format") != MTP_ARTIFACT_FORMAT:
+        raise ValueError(f"artifact format must be {MTP_ARTIFACT_FORMAT!r}")
+    if profile is not None and payload.get("profile") != profile:
+        raise ValueError(f"artifact profile {payload.get('profile')!r} is not {profile!r}")
+    if payload.get("mtp_depth") != mtp_depth:
+        raise ValueError(f"artifact mtp_depth {payload.get('mtp_depth')!r} is not {mtp_depth}")
+    for key, want in (("mtp_beta", mtp_beta), ("mtp_lambda", mtp_lambda)):
+        got = payload.get(key)
+        if not isinstance(got, (int, float)) or isinstance(got, bool) or abs(float(got) - want) > 1e-12:
+            raise ValueError(f"artifact {key} {got!r} is not {want}")
+    lv = payload.get("loss_values")
+    if not isinstance(lv, Mapping):
+        raise ValueError("artifact loss_values must be an object")
+    need = ["main_loss", "total_loss"] + [f"mtp_loss_depth_{d + 1}" for d in range(mtp_depth)]
+    for k in need:
+        v = lv.get(k)
+        if not isinstance(v, (int, float)) or isinstance(v, bool) or v != v or v in (float("inf"), float("-inf")):
+            raise ValueError(f"artifact loss_values.{k} must be a finite number")
+    if payload.get("loss_values_sha256") != loss_values_sha256({k: lv[k] for k in need}):
+        raise ValueError("artifact loss_values_sha256 does not match its loss_values")
+
+
+def mtp_artifact_preflight(artifact_path, **contract) -> dict:
+    """Status of the external artifact without comparing anything: ``not_supplied`` / ``missing`` / ``invalid`` / ``valid``."""
+    out = {"artifact": None if artifact_path is None else str(artifact_path), "artifact_contract": {"format": MTP_ARTIFACT_FORMAT, **contract},
+           "artifact_error": None, "payload": None}
+    if artifact_path is None:
+        return {**out, "artifact_preflight_status": "not_supplied", "artifact_error": "no reference artifact path was supplied"}
+    p = Path(artifact_path)
+    if not p.is_file():
+        return {**out, "artifact_preflight_status": "missing", "artifact_error": f"reference artifact not found: {p}"}
+    try:
+        payload = json.loads(p.read_text())
+        validate_mtp_artifact(payload, **contract)
+    except (OSError, ValueError) as e:
+        return {**out, "artifact_preflight_status": "invalid", "artifact_error": str(e)}
+    return {**out, "artifact_preflight_status": "valid", "payload": payload}
+
+
+def local_mtp_loss_values(model, batch) -> dict[str, float]:
+    """Main next-token loss, the MTP loss of every depth, their weighted total and the global gradient norm of the total on
+    ``model`` for ``batch`` (one forward + backward; gradients are cleared afterwards)."""
+    from ..data.batch import ensure_lm_batch
+    from .loss import _targets_and_mask, masked_cross_entropy
+    from .mtp import compute_mtp_step_weights, next_token_and_mtp_loss
+    cfg = model.config
+    head = getattr(model, "mtp_head", None)
+    depth = int(getattr(cfg, "mtp_depth", 0)) if (head is not None and getattr(cfg, "mtp_enabled", False)) else 0
+    if depth <= 0:
+        raise ValueError("the model has no MTP head (mtp_enabled is off)")
+    model.zero_grad(set_to_none=True)
+    b = ensure_lm_batch(batch)
+    dev = next(model.parameters()).device
+    t, valid = _targets_and_mask(b)
+    t, valid = t.to(dev), valid.to(dev)
+    side = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in b.side_inputs().items()}
+    h = model.decoder_hidden_states(b.inputs.to(dev), **side)
+    main = masked_cross_entropy(model.lm_head(h), t, valid)
+    tt = torch.where(valid, t, torch.full_like(t, head.config.ignore_index))
+    mtp_loss, per, _ = head.loss(h, tt, document_ids=side.get("document_ids"))
+    total = next_token_and_mtp_loss(main, mtp_loss, loss_weight=head.config.loss_weight)
+    total.backward()
+    gsq = sum(float(p.grad.float().pow(2).sum()) for p in model.parameters() if p.grad is not None)
+    model.zero_grad(set_to_none=True)
+    vals = {"main_loss": float(main.detach()), "total_loss": float(total.detach()), "mtp_loss": float(mtp_loss.detach()), "grad_norm": gsq ** 0.5}
+    for d in range(depth):
+        vals[f"mtp_loss_depth_{d + 1}"] = float(per[d].detach())
+    vals["mtp_depth_weights"] = [float(w) for w in compute_mtp_step_weights(depth, float(cfg.mtp_decay))]
+    return vals
+
+
+def mtp_parity_manifest(model, batch, artifact_path, *, profile: str | None = None, atol: float = 1e-2, rtol: float = 1e-2) -> dict:
+    """Fail-closed MTP parity manifest: local loss values are always recorded; the verdict is ``blocked`` without an artifact,
+    ``refused`` for a missing or invalid one, and ``pass`` / ``fail`` only when a valid artifact's numbers were actually compared."""
+    cfg = model.config
+    contract = dict(profile=profile, mtp_depth=int(cfg.mtp_depth), mtp_beta=float(cfg.mtp_decay), mtp_lambda=float(cfg.mtp_loss_weight))
+    pre = mtp_artifact_preflight(artifact_path, **contract)
+    local = local_mtp_loss_values(model, batch)
+    scalar_keys = [k for k in local if k.startswith(("main_loss", "total_loss", "mtp_loss_depth_"))]
+    receipts, status = [], {"not_supplied": "blocked", "missing": STATUS_REFUSED, "invalid": STATUS_REFUSED}.get(pre["artifact_preflight_status"])
+    if status is None:
+        theirs = pre["payload"]["loss_values"]
+        for k in scalar_keys:
+            receipts.append(compare_tensors(k, torch.tensor([local[k]]), torch.tensor([float(theirs[k])]), atol=atol, rtol=rtol).to_dict())
+        if "grad_norm" in theirs:
+            receipts.append(compare_tensors("grad_norm", torch.tensor([local["grad_norm"]]), torch.tensor([float(theirs["grad_norm"])]),
+                                            atol=atol, rtol=5 * rtol).to_dict())
+        status = STATUS_PASS if all(r["status"] == STATUS_PASS for r in receipts) else STATUS_FAIL
+    pre.pop("payload")
+    return {"label": "mtp", "status": status, "profile": profile, "mtp_depth": contract["mtp_depth"], "mtp_beta": contract["mtp_beta"],
+            "mtp_lambda": contract["mtp_lambda"], "reference": {**pre, "evaluated_by_this_manifest": bool(receipts)},
+            "local": {"loss_values": local, "loss_values_sha256": loss_values_sha256({k: local[k] for k in scalar_keys})},
+            "receipts": receipts, "tolerances": {"atol": atol, "rtol": rtol}}
+
+
+def export_mtp_artifact(model, batch, path, *, profile: str | None = None) -> dict:
+    """Write this build's own MTP loss values in the artifact format (what another implementation would compare against)."""
+    cfg = model.config
+    local = local_mtp_loss_values(model, batch)
+    scalars = {k: v for k, v in local.items() if k.startswith(("main_loss", "total_loss", "mtp_loss_depth_"))}
+    payload = {"format": MTP_ARTIFACT_FORMAT, "profile": profile, "mtp_depth": int(cfg.mtp_depth), "mtp_beta": float(cfg.mtp_decay),
+               "mtp_lambda": float(cfg.mtp_loss_weight), "loss_values": {**scalars, "grad_norm": local["grad_norm"]},
+               "loss_values_sha256": loss_values_sha256(scalars)}
+    Path(path).write_text(json.dumps(payload, indent=2, sort_keys=True) + "\n")
+    return payload

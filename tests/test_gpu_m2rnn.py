@@ -39,6 +39,46 @@ def test_m2rnn_fwd_bwd(K, nq, nk, nv, nw, nf, S):
     B.check_status()
 
 
+@pytest.mark.parametrize("nq,nk,nv,nw,nf,S,with_h0", [(2, 2, 2, 2, 2, 70, True), (1, 1, 2, 1, 2, 130, False), (2, 1, 2, 2, 1, 64, True)])
+def test_m2rnn_wide_heads_tensor_core_fwd_bwd(nq, nk, nv, nw, nf, S, with_h0):
+    """K = 64, V = 128: the tcgen05 time-loop kernels (checkpoint every 64 steps + replay in backward) against the fp32 recurrence,
+    over sequence lengths below, at and across checkpoint boundaries, grouped head counts and packed strided inputs."""
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops import m2rnn_cuda
+    from cppmega_mlx_b200.ops.m2rnn_scan import m2rnn_scan, m2rnn_scan_reference
+    torch.manual_seed(1)
+    dev, b, K, V = "cuda", 2, 64, 128
+    packed = (torch.randn(b, S, nq * K + nk * K + nv * V, device=dev) * 0.3).bfloat16().requires_grad_()
+    q = packed[..., :nq * K].view(b, S, nq, K)
+    k = packed[..., nq * K:(nq + nk) * K].view(b, S, nk, K)
+    v = packed[..., (nq + nk) * K:].view(b, S, nv, V)
+    W = (torch.randn(nw, V, V, device=dev) * 0.06).bfloat16().requires_grad_()
+    f = torch.rand(b, S, nf, device=dev).mul(0.5).add(0.4).bfloat16().requires_grad_()
+    H = max(nq, nk, nv, nw, nf)
+    h0 = (torch.randn(b, H, K, V, device=dev) * 0.1).bfloat16().requires_grad_() if with_h0 else None
+    leaves = [packed, W, f] + ([h0] if with_h0 else [])
+    assert m2rnn_cuda.supported(q, k, v, W, f)
+    n0, n1 = B.launch_count("m2rnn_tc_fwd"), B.launch_count("m2rnn_tc_bwd")
+    y, hl = m2rnn_scan(q, k, v, W, f, h0)
+    wy, wh = torch.randn_like(y.float()), torch.randn_like(hl.float())
+    ((y.float() * wy).sum() + (hl.float() * wh).sum()).backward()
+    assert B.launch_count("m2rnn_tc_fwd") == n0 + 1 and B.launch_count("m2rnn_tc_bwd") == n1 + 1
+    torch.cuda.synchronize()
+    B.check_status()
+    got = [t.grad.float().clone() for t in leaves]
+    for t in leaves:
+        t.grad = None
+    with B.use_kernels(False):
+        yr, hr = m2rnn_scan_reference(q.float(), k.float(), v.float(), W.float(), f.float(), None if h0 is None else h0.float())
+    ((yr * wy).sum() + (hr * wh).sum()).backward()
+    ref = [t.grad.float() for t in leaves]
+    assert torch.allclose(y.float(), yr, atol=4e-2, rtol=4e-2)
+    assert torch.allclose(hl.float(), hr, atol=3e-2, rtol=3e-2)
+    for name, a, r in zip(("qkv", "W", "f", "h0"), got, ref):
+        err = float((a - r).abs().max()) / max(float(r.abs().max()), 1e-3)
+        assert err < 6e-2, (name, err)
+
+
 def test_m2rnn_mixer_uses_kernel_and_matches_eager():
     from cppmega_mlx_b200.nn.m2rnn import M2RNNConfig, M2RNNMixer
     from cppmega_mlx_b200.ops import _backend as B
