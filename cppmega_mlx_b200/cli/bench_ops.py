@@ -189,24 +189,32 @@ def bench_mxfp8(args) -> list[dict]:
 
 
 def bench_m2rnn(args) -> list[dict]:
+    """The two M2RNN head geometries: K64/V16 (CUDA-core time loop, the quarter-size recipes) and K64/V128 (tcgen05 time loop with
+    checkpoint + replay backward, the 56-layer profile: 28 heads, sequence 8192, micro-batch 2)."""
     from cppmega_mlx_b200.ops import _backend as B
     from cppmega_mlx_b200.ops.m2rnn_scan import m2rnn_scan
     rows = []
-    b, S, H, K, V = 4, 4096, 4, 64, 16
-    q = (torch.randn(b, S, H, K, device="cuda") * 0.5).bfloat16().requires_grad_()
-    k = (torch.randn(b, S, H, K, device="cuda") * 0.5).bfloat16().requires_grad_()
-    v = (torch.randn(b, S, H, V, device="cuda") * 0.5).bfloat16().requires_grad_()
-    W = (torch.randn(H, V, V, device="cuda") * 0.2).bfloat16().requires_grad_()
-    f = torch.rand(b, S, H, device="cuda").mul(0.5).add(0.4).bfloat16().requires_grad_()
-    run = _fb(lambda: m2rnn_scan(q, k, v, W, f)[0], q, k, v, W, f)
-    ms = time_cuda(run, iters=args.iters, warmup=args.warmup)
-    row = {"op": "m2rnn scan fwd+bwd B4 S4096 H4 K64 V16", "ms": ms, "us_per_token_step": ms * 1e3 / S / 2}
-    if not args.no_eager:
-        with B.use_kernels(False):
-            row["eager_ms"] = time_cuda(run, iters=1, warmup=1)
-        row["speedup_vs_eager"] = row["eager_ms"] / ms
-    rows.append(row)
-    print(json.dumps(row), flush=True)
+    for (b, S, H, K, V, eager_ok) in ((4, 4096, 4, 64, 16, True), (2, 8192, 28, 64, 128, False)):
+        if args.only and args.only not in f"V{V}":
+            continue
+        q = (torch.randn(b, S, H, K, device="cuda") * 0.5).bfloat16().requires_grad_()
+        k = (torch.randn(b, S, H, K, device="cuda") * 0.5).bfloat16().requires_grad_()
+        v = (torch.randn(b, S, H, V, device="cuda") * 0.5).bfloat16().requires_grad_()
+        W = (torch.randn(H, V, V, device="cuda") * (0.2 if V == 16 else 0.05)).bfloat16().requires_grad_()
+        f = torch.rand(b, S, H, device="cuda").mul(0.5).add(0.4).bfloat16().requires_grad_()
+        with torch.no_grad():
+            ms_f = time_cuda(lambda: m2rnn_scan(q, k, v, W, f)[0], iters=args.iters, warmup=args.warmup)
+        run = _fb(lambda: m2rnn_scan(q, k, v, W, f)[0], q, k, v, W, f)
+        ms = time_cuda(run, iters=args.iters, warmup=args.warmup)
+        row = {"op": f"m2rnn scan B{b} S{S} H{H} K{K} V{V}", "fwd_ms": ms_f, "fwd_us_per_step": ms_f * 1e3 / S, "fwd_bwd_ms": ms,
+               "fwd_bwd_us_per_step": ms * 1e3 / S, "ctas": b * H}
+        if eager_ok and not args.no_eager:
+            with B.use_kernels(False):
+                row["eager_ms"] = time_cuda(run, iters=1, warmup=1)
+            row["speedup_vs_eager"] = row["eager_ms"] / ms
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+    B.check_status()
     return rows
 
 

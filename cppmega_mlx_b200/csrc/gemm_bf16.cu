@@ -46,6 +46,8 @@ enum : int {
   GEMM_EPI_EXP_MASK = 256,       // P = [mask] · exp(scale·acc − r[t])
   GEMM_EPI_DS = 512,             // dS = aux · (acc − r[t]) · scale   (aux has C's layout, bf16)
   GEMM_EPI_AXPBY = 1024,         // scale · acc + scale2 · aux        (aux has C's layout, bf16)
+  GEMM_EPI_SYM_MIRROR = 2048,    // with CAUSAL_SKIP on a symmetric product (bf16 C): every element whose transposed position lies
+                                 // in a skipped tile is also stored there, so the full matrix exists after one launch
 };
 
 struct GemmParams {
@@ -65,6 +67,7 @@ struct GemmParams {
   float* stats;              // SOFTMAX_STATS output: float2 per (problem, row, tile_n, half)
   const int* tile_group;     // grouped (MoE) mode: B's dim-2 index for each 128-row tile of A / C; nullptr = batched rule
   const int* k_ranges;       // grouped wgrad: contraction range [k_begin, k_end) per dim-2 problem (multiples of 64)
+  __nv_bfloat16* c_base;     // SYM_MIRROR: C as a plain pointer (the mirrored elements are stored with ordinary stores)
   int* status;
 };
 
@@ -289,6 +292,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool e_ds = (p.flags & GEMM_EPI_DS) != 0;
     const bool attn = e_stats || e_expm || e_ds;
     const bool e_axpby = (p.flags & GEMM_EPI_AXPBY) != 0;
+    const bool e_mirror = (p.flags & GEMM_EPI_SYM_MIRROR) != 0 && !out_f32;
     uint8_t* cbox = csmem + ew * GEMM_CBOX_BYTES;
     int local = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
@@ -421,6 +425,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (rowexp) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rv);
+        }
+        if (e_mirror && row < p.M && (row / BN) * BN >= (col0 / GEMM_BM) * GEMM_BM + GEMM_BM) {
+          // (col, row) lies in a tile the causal skip left out (its tile would start at column (row / BN)·BN ≥ its first row +
+          // 128): this thread's 32 values go there as column `row`; for a fixed j the warp writes 32 consecutive elements.
+          __nv_bfloat16* cm = p.c_base + tc.i2 * p.sC2 + tc.i3 * p.sC3 + tc.i4 * p.sC4 + row;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) cm[static_cast<long long>(col0 + j) * p.ldc] = __float2bfloat16(__uint_as_float(r[j]));
         }
         // Stage into the swizzled box: row `lane`, 16-byte chunk ch lands at chunk (ch ^ (lane & 7)).
         const bool new_box = out_f32 || (c & 1) == 0;
@@ -643,6 +655,7 @@ static int launch_gemm(const GemmArgs& g) {
   p.mask = g.mask; p.mask_sb = g.mask_sb; p.mask_words = g.mask_words;
   p.scale = g.scale; p.scale2 = g.scale2; p.stats = g.stats;
   p.tile_group = g.tile_group; p.k_ranges = g.k_ranges;
+  p.c_base = static_cast<__nv_bfloat16*>(g.C);
   p.status = g.status;
   kern<<<grid, cmb::GEMM_THREADS, Cfg::SMEM_BYTES, g.stream>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 104;

@@ -322,3 +322,97 @@ extern "C" int cmb_m2rnn_bwd(const void* q, const void* k, const void* v, const 
   else cmb::m2rnn_bwd_kernel<32><<<p.B * p.H, 128, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Post-recurrence gate of the M2RNN mixer in one pass each way:   out = (y + v·D) · silu(g)
+// y [B,S,H,V] is the recurrence output (dense); v [B,S,nv,V] and g [B,S,ng,V] are strided slices of packed projections whose
+// heads are shared by H/nv (H/ng) consecutive output heads; D [H,V].  Backward returns dy (dense), and per expanded head dv
+// and dg (the caller folds heads that share an input) plus dD accumulated over all tokens.
+// Reference fusion: cppmega_mlx/nn/_tilelang/m2rnn_path_c.py:2421 (forward), :2519 (backward).
+namespace cmb {
+
+struct M2PostParams {
+  const __nv_bfloat16 *y, *v, *g;
+  const float* D;                    // [H,V] or null (no residual)
+  __nv_bfloat16* out;
+  long long sv_b, sv_s, sg_b, sg_s;  // element strides of v and g (batch, token)
+  int B, S, H, V, nv, ng;
+  const __nv_bfloat16* dout;
+  __nv_bfloat16* dy;
+  float *dv, *dg, *dD;               // [B,S,H,V] ×2, [H,V] (dD pre-zeroed)
+};
+
+__global__ void __launch_bounds__(256) m2rnn_post_fwd_kernel(const M2PostParams p) {
+  const int HV = p.H * p.V;
+  const int hw = blockIdx.x * blockDim.x + threadIdx.x;
+  if (hw >= HV) return;
+  const int h = hw / p.V, w = hw % p.V;
+  const int hv = h / (p.H / p.nv), hg = h / (p.H / p.ng);
+  const float d = p.D != nullptr ? p.D[hw] : 0.f;
+  const long long tokens = static_cast<long long>(p.B) * p.S;
+  for (long long t = blockIdx.y; t < tokens; t += gridDim.y) {
+    const long long b = t / p.S, s = t % p.S;
+    const float yv = __bfloat162float(p.y[t * HV + hw]);
+    const float vv = __bfloat162float(p.v[b * p.sv_b + s * p.sv_s + hv * p.V + w]);
+    const float gv = __bfloat162float(p.g[b * p.sg_b + s * p.sg_s + hg * p.V + w]);
+    const float sg = gv / (1.f + __expf(-gv));
+    p.out[t * HV + hw] = __float2bfloat16((yv + vv * d) * sg);
+  }
+}
+
+__global__ void __launch_bounds__(256) m2rnn_post_bwd_kernel(const M2PostParams p) {
+  const int HV = p.H * p.V;
+  const int hw = blockIdx.x * blockDim.x + threadIdx.x;
+  if (hw >= HV) return;
+  const int h = hw / p.V, w = hw % p.V;
+  const int hv = h / (p.H / p.nv), hg = h / (p.H / p.ng);
+  const float d = p.D != nullptr ? p.D[hw] : 0.f;
+  const long long tokens = static_cast<long long>(p.B) * p.S;
+  float accD = 0.f;
+  for (long long t = blockIdx.y; t < tokens; t += gridDim.y) {
+    const long long b = t / p.S, s = t % p.S;
+    const float yv = __bfloat162float(p.y[t * HV + hw]);
+    const float vv = __bfloat162float(p.v[b * p.sv_b + s * p.sv_s + hv * p.V + w]);
+    const float gv = __bfloat162float(p.g[b * p.sg_b + s * p.sg_s + hg * p.V + w]);
+    const float go = __bfloat162float(p.dout[t * HV + hw]);
+    const float sig = 1.f / (1.f + __expf(-gv));
+    const float sg = gv * sig;
+    const float gy = go * sg;                       // ∂L/∂(y + v·D)
+    p.dy[t * HV + hw] = __float2bfloat16(gy);
+    p.dv[t * HV + hw] = gy * d;
+    p.dg[t * HV + hw] = go * (yv + vv * d) * (sig * (1.f + gv * (1.f - sig)));
+    accD = fmaf(gy, vv, accD);
+  }
+  if (p.dD != nullptr) atomicAdd(&p.dD[hw], accD);
+}
+
+}  // namespace cmb
+
+// ip = {B, S, H, V, nv, ng}; lp = {sv_b, sv_s, sg_b, sg_s}.
+extern "C" int cmb_m2rnn_post_fwd(const void* y, const void* v, const void* g, const float* D, void* out, const int* ip, const long long* lp,
+                                  void* stream) {
+  cmb::M2PostParams p{};
+  p.y = static_cast<const __nv_bfloat16*>(y); p.v = static_cast<const __nv_bfloat16*>(v); p.g = static_cast<const __nv_bfloat16*>(g);
+  p.D = D; p.out = static_cast<__nv_bfloat16*>(out);
+  p.B = ip[0]; p.S = ip[1]; p.H = ip[2]; p.V = ip[3]; p.nv = ip[4]; p.ng = ip[5];
+  p.sv_b = lp[0]; p.sv_s = lp[1]; p.sg_b = lp[2]; p.sg_s = lp[3];
+  if (p.B <= 0 || p.S <= 0 || p.H <= 0 || p.V <= 0 || p.nv <= 0 || p.ng <= 0 || p.H % p.nv || p.H % p.ng) return -1;
+  const int HV = p.H * p.V;
+  dim3 grid((HV + 255) / 256, static_cast<unsigned>(min(static_cast<long long>(p.B) * p.S, 148LL * 16 / ((HV + 255) / 256) + 1)));
+  cmb::m2rnn_post_fwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int cmb_m2rnn_post_bwd(const void* y, const void* v, const void* g, const float* D, const void* dout, void* dy, float* dv, float* dg,
+                                  float* dD, const int* ip, const long long* lp, void* stream) {
+  cmb::M2PostParams p{};
+  p.y = static_cast<const __nv_bfloat16*>(y); p.v = static_cast<const __nv_bfloat16*>(v); p.g = static_cast<const __nv_bfloat16*>(g);
+  p.D = D; p.dout = static_cast<const __nv_bfloat16*>(dout); p.dy = static_cast<__nv_bfloat16*>(dy); p.dv = dv; p.dg = dg; p.dD = dD;
+  p.B = ip[0]; p.S = ip[1]; p.H = ip[2]; p.V = ip[3]; p.nv = ip[4]; p.ng = ip[5];
+  p.sv_b = lp[0]; p.sv_s = lp[1]; p.sg_b = lp[2]; p.sg_s = lp[3];
+  if (p.B <= 0 || p.S <= 0 || p.H <= 0 || p.V <= 0 || p.nv <= 0 || p.ng <= 0 || p.H % p.nv || p.H % p.ng) return -1;
+  const int HV = p.H * p.V;
+  dim3 grid((HV + 255) / 256, static_cast<unsigned>(min(static_cast<long long>(p.B) * p.S, 148LL * 16 / ((HV + 255) / 256) + 1)));
+  cmb::m2rnn_post_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

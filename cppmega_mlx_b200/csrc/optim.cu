@@ -297,6 +297,135 @@ extern "C" int cmb_axpy_update(void* p, const void* u, int64_t n, int dtype, flo
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
+// ---------------------------------------------------------------------------------------------- multi-tensor forms
+// One launch over a table of tensors (device memory).  A block owns one 4096-element chunk of one tensor; `chunk_start[t]` is the
+// first chunk of tensor t (prefix sums, n + 1 entries), found by binary search.  Every entry carries its own pointers, so the
+// tensors may live anywhere (views of flat ZeRO-1 buffers, group workspaces of the batched Newton–Schulz, autograd's gradients).
+namespace cmb {
+
+constexpr int MT_CHUNK_ELEMS = 4096;
+
+struct TensorEntry {
+  void* p;            // parameter (dtype `dt`)
+  const void* g;      // gradient (same dtype) or null
+  float* s0;          // fp32 state 0 (Adam m / Muon momentum)
+  float* s1;          // fp32 state 1 (Adam v) or null
+  __nv_bfloat16* u;   // Muon: bf16 update in / out of Newton–Schulz
+  float* sumsq;       // Muon: Σ u² slot of this tensor
+  long long numel;
+  float coef;         // Muon: learning-rate factor of this tensor
+  int pad;
+};
+
+__device__ __forceinline__ int mt_find(const int* __restrict__ chunk_start, int n, int chunk) {
+  int lo = 0, hi = n - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (chunk_start[mid] <= chunk) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) muon_momentum_multi_kernel(const TensorEntry* __restrict__ tab, const int* __restrict__ chunk_start, int n,
+                                                                   float mu, float wd, int nesterov) {
+  __shared__ float red[8];
+  const int t = mt_find(chunk_start, n, blockIdx.x);
+  const TensorEntry e = tab[t];
+  const long long i0 = static_cast<long long>(blockIdx.x - chunk_start[t]) * MT_CHUNK_ELEMS;
+  const long long i1 = min(e.numel, i0 + MT_CHUNK_ELEMS);
+  const T* g = static_cast<const T*>(e.g);
+  const T* p = static_cast<const T*>(e.p);
+  float acc = 0.f;
+  for (long long i = i0 + threadIdx.x; i < i1; i += 256) {
+    const float gi = Cvt<T>::ld(g, i) + wd * Cvt<T>::ld(p, i);
+    const float vi = mu * e.s0[i] + (1.f - mu) * gi;
+    e.s0[i] = vi;
+    const float u = nesterov ? gi * (1.f - mu) + vi * mu : vi;
+    acc += u * u;
+    e.u[i] = __float2bfloat16(u);
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 8) {
+    float r = red[threadIdx.x];
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) r += __shfl_xor_sync(0xffu, r, o);
+    if (threadIdx.x == 0) atomicAdd(e.sumsq, r);
+  }
+}
+
+// u ← u / (sqrt(Σu²) + eps) for every tensor of the table.
+__global__ void __launch_bounds__(256) scale_inv_norm_multi_kernel(const TensorEntry* __restrict__ tab, const int* __restrict__ chunk_start, int n,
+                                                                    float eps) {
+  const int t = mt_find(chunk_start, n, blockIdx.x);
+  const TensorEntry e = tab[t];
+  const long long i0 = static_cast<long long>(blockIdx.x - chunk_start[t]) * MT_CHUNK_ELEMS;
+  const long long i1 = min(e.numel, i0 + MT_CHUNK_ELEMS);
+  const float inv = 1.f / (sqrtf(*e.sumsq) + eps);
+  for (long long i = i0 + threadIdx.x; i < i1; i += 256) e.u[i] = __float2bfloat16(__bfloat162float(e.u[i]) * inv);
+}
+
+// p ← p − coef_t · u for every tensor of the table (u = the orthogonalised update).
+template <typename T>
+__global__ void __launch_bounds__(256) axpy_update_multi_kernel(const TensorEntry* __restrict__ tab, const int* __restrict__ chunk_start, int n) {
+  const int t = mt_find(chunk_start, n, blockIdx.x);
+  const TensorEntry e = tab[t];
+  const long long i0 = static_cast<long long>(blockIdx.x - chunk_start[t]) * MT_CHUNK_ELEMS;
+  const long long i1 = min(e.numel, i0 + MT_CHUNK_ELEMS);
+  T* p = static_cast<T*>(e.p);
+  for (long long i = i0 + threadIdx.x; i < i1; i += 256) Cvt<T>::st(p, i, Cvt<T>::ld(p, i) - e.coef * __bfloat162float(e.u[i]));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) adamw_multi_kernel(const TensorEntry* __restrict__ tab, const int* __restrict__ chunk_start, int n, float lr,
+                                                           float b1, float b2, float eps, float wd, float c1, float c2) {
+  const int t = mt_find(chunk_start, n, blockIdx.x);
+  const TensorEntry e = tab[t];
+  const long long i0 = static_cast<long long>(blockIdx.x - chunk_start[t]) * MT_CHUNK_ELEMS;
+  const long long i1 = min(e.numel, i0 + MT_CHUNK_ELEMS);
+  T* p = static_cast<T*>(e.p);
+  const T* g = static_cast<const T*>(e.g);
+  for (long long i = i0 + threadIdx.x; i < i1; i += 256) {
+    const float gi = Cvt<T>::ld(g, i);
+    const float mi = b1 * e.s0[i] + (1.f - b1) * gi;
+    const float vi = b2 * e.s1[i] + (1.f - b2) * gi * gi;
+    e.s0[i] = mi;
+    e.s1[i] = vi;
+    Cvt<T>::st(p, i, Cvt<T>::ld(p, i) * (1.f - lr * wd) - lr * c1 * mi / (sqrtf(vi) * c2 + eps));
+  }
+}
+
+}  // namespace cmb
+
+// `tab`: device array of n entries {p, g, s0, s1, u, sumsq, numel (int64), coef (fp32), pad} (64 bytes); `chunk_start`: device int32[n + 1],
+// prefix sums of ceil(numel / 4096).  `op`: 0 Muon momentum (+Σu² into the entries' sumsq slots, which the caller zeroed), 1 Frobenius
+// normalisation of u, 2 p −= coef·u, 3 AdamW.  f = {mu, wd, nesterov} | {eps} | {} | {lr, b1, b2, eps, wd, c1, c2}.
+extern "C" int cmb_optim_multi(int op, const void* tab, const int* chunk_start, int n, int total_chunks, int dtype, const float* f, void* stream) {
+  if (n <= 0 || total_chunks <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const cmb::TensorEntry* t = static_cast<const cmb::TensorEntry*>(tab);
+  switch (op) {
+    case 0:
+      CMB_DISPATCH_DTYPE(dtype, (cmb::muon_momentum_multi_kernel<T><<<total_chunks, 256, 0, s>>>(t, chunk_start, n, f[0], f[1], static_cast<int>(f[2]))));
+      break;
+    case 1:
+      cmb::scale_inv_norm_multi_kernel<<<total_chunks, 256, 0, s>>>(t, chunk_start, n, f[0]);
+      break;
+    case 2:
+      CMB_DISPATCH_DTYPE(dtype, (cmb::axpy_update_multi_kernel<T><<<total_chunks, 256, 0, s>>>(t, chunk_start, n)));
+      break;
+    case 3:
+      CMB_DISPATCH_DTYPE(dtype, (cmb::adamw_multi_kernel<T><<<total_chunks, 256, 0, s>>>(t, chunk_start, n, f[0], f[1], f[2], f[3], f[4], f[5], f[6])));
+      break;
+    default:
+      return 1;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
 // ---------------------------------------------------------------------------------------------- symmetric completion
 namespace cmb {
 // G[i][j] = G[j][i] for j > i (n×n bf16, row pitch ld): completes a matrix whose lower triangle was computed by a GEMM that

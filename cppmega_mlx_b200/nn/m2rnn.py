@@ -144,13 +144,9 @@ class M2RNNMixer(nn.Module):
         f = m2rnn_softplus_decay_gate(tail[..., :self.f_dim], self.A_log, self.dt_bias)
         out, h = ops.m2rnn_scan(q, k, v, self.state_weight.to(q.dtype), f, h0=h0)
         H = c.num_heads
-        if self.D is not None:
-            vb = v if c.num_v_heads == H else v.repeat_interleave(H // c.num_v_heads, dim=2)
-            out = out + vb * self.D.to(out.dtype)
         g = tail[..., self.f_dim:].reshape(b, s, c.num_g_heads, c.v_head_dim)
-        if c.num_g_heads != H:
-            g = g.repeat_interleave(H // c.num_g_heads, dim=2)
-        out = (out * F.silu(g)).reshape(b, s, H * c.v_head_dim)
+        # residual and output gate in one pass: (y + v·D) · silu(g), heads of v / g broadcast inside the kernel
+        out = ops.m2rnn_post_gate(out, v, g, self.D).reshape(b, s, H * c.v_head_dim)
         out = self.out_proj(self.g_norm(out))
         if not return_state:
             return out, h

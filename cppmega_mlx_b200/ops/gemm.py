@@ -69,6 +69,7 @@ EPI_SOFTMAX_STATS = 128
 EPI_EXP_MASK = 256
 EPI_DS = 512
 EPI_AXPBY = 1024
+EPI_SYM_MIRROR = 2048   # with CAUSAL_SKIP on a symmetric product: the skipped tiles are filled from the computed ones in the same launch
 
 
 def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, M: int, N: int, K: int, a_mn: bool,

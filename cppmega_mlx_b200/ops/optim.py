@@ -111,3 +111,108 @@ def muon_step_(p, g, v, lr, momentum, wd, nesterov, ns_steps):
     coef = lr * max(1.0, p.shape[0] / p.shape[1]) ** 0.5
     B.check(lib.cmb_axpy_update(B.ptr(p), B.ptr(o), ctypes.c_int64(p.numel()), _DT[p.dtype], ctypes.c_float(coef),
                                 B.stream_ptr()), "axpy_update")
+
+
+# ----------------------------------------------------------------------------------------------- multi-tensor / batched forms
+MT_CHUNK_ELEMS = 4096
+OP_MUON_MOMENTUM, OP_SCALE_INV_NORM, OP_AXPY_UPDATE, OP_ADAMW = 0, 1, 2, 3
+_ENTRY = [("p", "<u8"), ("g", "<u8"), ("s0", "<u8"), ("s1", "<u8"), ("u", "<u8"), ("sumsq", "<u8"), ("numel", "<i8"), ("coef", "<f4"), ("pad", "<i4")]
+
+
+class TensorTable:
+    """Device-side table for ``cmb_optim_multi``: one launch updates every tensor listed.  ``rows`` are dicts with the raw
+    addresses (``p``, ``g``, ``s0``, ``s1``, ``u``, ``sumsq``), ``numel`` and ``coef``.  The upload is skipped while the rows are
+    unchanged from the previous call (flat ZeRO-1 buffers and cached workspaces keep their addresses from step to step)."""
+
+    def __init__(self, device):
+        self.device = device
+        self.key = None
+        self.tab = self.chunks = None
+        self.n = self.total_chunks = 0
+
+    def update(self, rows: list[dict]) -> "TensorTable":
+        import numpy as np
+        key = tuple(tuple(sorted(r.items())) for r in rows)
+        if key == self.key:
+            return self
+        arr = np.zeros(len(rows), dtype=_ENTRY)
+        starts = np.zeros(len(rows) + 1, dtype=np.int32)
+        for i, r in enumerate(rows):
+            for k in ("p", "g", "s0", "s1", "u", "sumsq"):
+                arr[i][k] = r.get(k, 0)
+            arr[i]["numel"] = r["numel"]
+            arr[i]["coef"] = r.get("coef", 0.0)
+            starts[i + 1] = starts[i] + (r["numel"] + MT_CHUNK_ELEMS - 1) // MT_CHUNK_ELEMS
+        self.tab = torch.from_numpy(arr.view(np.uint8).copy()).to(self.device)
+        self.chunks = torch.from_numpy(starts).to(self.device)
+        self.n, self.total_chunks, self.key = len(rows), int(starts[-1]), key
+        return self
+
+    def launch(self, op: int, dtype: torch.dtype, scalars, what: str) -> None:
+        if self.n == 0:
+            return
+        lib = B.load_library()
+        f = (ctypes.c_float * 8)(*([float(x) for x in scalars] + [0.0] * (8 - len(scalars))))
+        B.check(lib.cmb_optim_multi(op, B.ptr(self.tab), B.ptr(self.chunks), self.n, self.total_chunks, _DT[dtype], f, B.stream_ptr()), what)
+
+
+def newton_schulz5_batched_(x: torch.Tensor, nxt: torch.Tensor, g: torch.Tensor, poly: torch.Tensor, steps: int = 5,
+                            coeffs=(3.4445, -4.7750, 2.0315)) -> torch.Tensor:
+    """Quintic Newton–Schulz on a stack ``x`` [n, rows, cols] of already normalised bf16 matrices of one shape: every product is one
+    batched tcgen05 GEMM over the stack (three launches per step whatever n), which also fills the GPU where a single Gram
+    product of a 2048-wide matrix occupies half of it.  The symmetric products compute the tiles on or below the diagonal and
+    store the mirrored elements from the same epilogue.  ``nxt`` / ``g`` / ``poly`` are workspaces ([n, rows, cols], [n, m, m] × 2);
+    returns whichever of ``x`` / ``nxt`` holds the result."""
+    from .gemm import CAUSAL_SKIP, EPI_AXPBY, EPI_SYM_MIRROR, gemm_batched
+    a, b, c = coeffs
+    n, rows, cols = x.shape
+    tall = rows > cols
+    m = min(rows, cols)
+    sym = CAUSAL_SKIP | EPI_SYM_MIRROR if m >= 512 else 0
+    nb, sX, sG = (n, 1, 1), (rows * cols, 0, 0), (m * m, 0, 0)
+    for _ in range(steps):
+        gemm_batched(x, x, g, M=m, N=m, K=rows if tall else cols, a_mn=tall, b_mn=tall, lda=cols, ldb=cols, ldc=m, nb=nb, sA=sX, sB=sX, sC=sG,
+                     flags=sym)                                                                     # G = XᵀX or XXᵀ
+        gemm_batched(g, g, poly, M=m, N=m, K=m, a_mn=False, b_mn=False, lda=m, ldb=m, ldc=m, nb=nb, sA=sG, sB=sG, sC=sG, flags=sym | EPI_AXPBY,
+                     aux=g, scale=c, scale2=b)                                                      # bG + cG²
+        if tall:
+            gemm_batched(x, poly, nxt, M=rows, N=cols, K=cols, a_mn=False, b_mn=False, lda=cols, ldb=m, ldc=cols, nb=nb, sA=sX, sB=sG, sC=sX,
+                         flags=EPI_AXPBY, aux=x, scale=1.0, scale2=a)                               # aX + X·poly
+        else:
+            gemm_batched(poly, x, nxt, M=rows, N=cols, K=rows, a_mn=False, b_mn=True, lda=m, ldb=cols, ldc=cols, nb=nb, sA=sG, sB=sX, sC=sX,
+                         flags=EPI_AXPBY, aux=x, scale=1.0, scale2=a)                               # aX + poly·X
+        x, nxt = nxt, x
+    return x
+
+
+class MuonBatchPlan:
+    """Work plan of one Muon step over many matrices: matrices of equal shape are stacked (at most ``max_stack`` per stack) into
+    cached workspaces, the element-wise stages (momentum + Σu², normalisation, final update) are one multi-tensor launch each,
+    and Newton–Schulz runs per stack as batched GEMMs on a few side streams."""
+
+    def __init__(self, device, max_stack: int = 8):
+        self.device, self.max_stack = device, max_stack
+        self.ws: dict = {}
+        self.tab_in, self.tab_out = TensorTable(device), TensorTable(device)
+        self.sumsq = None
+
+    def stacks(self, shapes: list[tuple[int, int]]):
+        """Group tensor indices by shape into stacks; returns [(shape, [indices])] largest first."""
+        by: dict = {}
+        for i, sh in enumerate(shapes):
+            by.setdefault(tuple(sh), []).append(i)
+        out = []
+        for sh, idx in by.items():
+            for j in range(0, len(idx), self.max_stack):
+                out.append((sh, idx[j:j + self.max_stack]))
+        out.sort(key=lambda t: -(t[0][0] * t[0][1] * len(t[1])))
+        return out
+
+    def workspace(self, key, shape, n):
+        w = self.ws.get(key)
+        if w is None or w[0].shape[0] != n:
+            r, c = shape
+            m = min(r, c)
+            mk = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=self.device)
+            w = self.ws[key] = (mk(n, r, c), mk(n, r, c), mk(n, m, m), mk(n, m, m))
+        return w

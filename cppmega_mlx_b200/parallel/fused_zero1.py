@@ -57,7 +57,6 @@ class FusedZeRO1Comm:
     def try_fused_step(self, opt) -> bool:
         if not self._supported(opt):
             return False
-        from ..ops.optim import newton_schulz5_bf16_
         from ..training.optimizers import AdamWFP32Moments, newton_schulz5
         lib = B.load_library()
         flat, W, rank = self.flat, opt.world, opt.rank
@@ -81,35 +80,64 @@ class FusedZeRO1Comm:
                                         F32(adamw.lr), F32(b1), F32(b2), F32(adamw.eps), F32(adamw.weight_decay), F32(c1),
                                         F32(c2), st()), "zero1_adamw")
         if muon is not None:
+            from ..ops.optim import OP_SCALE_INV_NORM, MuonBatchPlan, newton_schulz5_batched_
             from ..training.optimizers import ns_streams
             muon.step_count += 1
             dev = flat.params.device
+            work = [(name, p) for name, p in muon.params]
+            for name, p in work:
+                if flat.slots[name][2] % 8:
+                    raise RuntimeError(f"fused Muon needs an element count that is a multiple of 8, got {tuple(p.shape)} for {name}")
+            fast = [(n_, p) for n_, p in work if p.shape[0] % 8 == 0 and p.shape[1] % 8 == 0]
+            slow = [(n_, p) for n_, p in work if p.shape[0] % 8 or p.shape[1] % 8]
+            plan = getattr(self, "_plan", None)
+            if plan is None:
+                plan = self._plan = MuonBatchPlan(dev)
+            nf = len(fast)
+            if plan.sumsq is None or plan.sumsq.numel() != nf + len(slow):
+                plan.sumsq = torch.zeros(nf + len(slow), dtype=torch.float32, device=dev)
+            else:
+                plan.sumsq.zero_()
+
+            def reduce_into(name, p, u, sumsq_slot):
+                owner, off, n = flat.slots[name]
+                s = muon.state_for(name, p)
+                B.check(lib.cmb_zero1_muon_reduce(gp, pp, rank, W, I64(owner * flat.segment + off), I64(n), B.ptr(s["v"]), B.ptr(u), B.ptr(sumsq_slot),
+                                                  F32(muon.momentum), F32(muon.weight_decay), int(muon.nesterov), st()), "zero1_muon_reduce")
+
+            def push(name, p, o):
+                owner, off, n = flat.slots[name]
+                coef = muon.lr * max(1.0, p.shape[0] / p.shape[1]) ** 0.5
+                B.check(lib.cmb_zero1_push_update(pp, rank, W, I64(owner * flat.segment + off), I64(n), B.ptr(o), F32(coef), st()), "zero1_push_update")
+
+            # (1) reduce the peers' gradients of every owned matrix into its slot of a same-shape stack (+ momentum, Σu²)
+            stacks = plan.stacks([tuple(p.shape) for _, p in fast])
+            rows, jobs = [None] * nf, []
+            for sh, idx in stacks:
+                x, nxt, gws, poly = plan.workspace((sh, idx[0]), sh, len(idx))
+                jobs.append((x, nxt, gws, poly, idx))
+                for j, i in enumerate(idx):
+                    reduce_into(fast[i][0], fast[i][1], x[j], plan.sumsq[i:i + 1])
+                    rows[i] = dict(u=x[j].data_ptr(), sumsq=plan.sumsq.data_ptr() + 4 * i, numel=fast[i][1].numel())
+            # (2) Frobenius normalisation of all of them in one launch, (3) Newton–Schulz per stack as batched GEMMs on side streams
+            plan.tab_in.update(rows)
+            plan.tab_in.launch(OP_SCALE_INV_NORM, torch.bfloat16, (1e-7,), "scale_inv_norm_multi")
             main = torch.cuda.current_stream(dev)
             ready = main.record_event()
             streams = ns_streams(dev)
             for s_ in streams:
                 s_.wait_event(ready)
-            work = sorted(muon.params, key=lambda np_: -np_[1].numel())
-            for i, (name, p) in enumerate(work):          # independent matrices: reduce → Newton–Schulz → push, several at a time
-                with torch.cuda.stream(streams[i % len(streams)]):
-                    owner, off, n = flat.slots[name]
-                    goff = owner * flat.segment + off
-                    s = muon.state_for(name, p)
-                    rows, cols = p.shape
-                    if n % 8:
-                        raise RuntimeError(f"fused Muon needs an element count that is a multiple of 8, got {tuple(p.shape)} for {name}")
-                    u = torch.empty(rows, cols, dtype=torch.bfloat16, device=p.device)
-                    sumsq = torch.zeros(1, dtype=torch.float32, device=p.device)
-                    B.check(lib.cmb_zero1_muon_reduce(gp, pp, rank, W, I64(goff), I64(n), B.ptr(s["v"]), B.ptr(u), B.ptr(sumsq),
-                                                      F32(muon.momentum), F32(muon.weight_decay), int(muon.nesterov), st()),
-                            "zero1_muon_reduce")
-                    if rows % 8 or cols % 8:   # too narrow for the tensor-core iteration (e.g. a 4-row gate): same maths in PyTorch ops
-                        o = newton_schulz5(u, steps=muon.ns_steps, ns_carrier="bf16", output_dtype=torch.bfloat16).contiguous()
-                    else:
-                        o = newton_schulz5_bf16_(u, sumsq, muon.ns_steps)
-                    coef = muon.lr * max(1.0, rows / cols) ** 0.5
-                    B.check(lib.cmb_zero1_push_update(pp, rank, W, I64(goff), I64(n), B.ptr(o), F32(coef), st()), "zero1_push_update")
+            results = []
+            for k_, (x, nxt, gws, poly, idx) in enumerate(jobs):
+                with torch.cuda.stream(streams[k_ % len(streams)]):
+                    res = newton_schulz5_batched_(x, nxt, gws, poly, muon.ns_steps)
+                    for j, i in enumerate(idx):          # (4) owner pushes p − lr·U into every rank's parameter buffer
+                        push(fast[i][0], fast[i][1], res[j])
             for s_ in streams:
                 main.wait_stream(s_)
+            for k_, (name, p) in enumerate(slow):         # too narrow for the tensor-core iteration (e.g. a 4-row gate): same maths in PyTorch ops
+                u = torch.empty(p.shape, dtype=torch.bfloat16, device=dev)
+                reduce_into(name, p, u, plan.sumsq[nf + k_:nf + k_ + 1])
+                push(name, p, newton_schulz5(u, steps=muon.ns_steps, ns_carrier="bf16", output_dtype=torch.bfloat16).contiguous())
         self.barrier()  # all parameters delivered everywhere; all gradients consumed
         return True

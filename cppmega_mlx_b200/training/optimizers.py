@@ -141,6 +141,44 @@ class AdamWFP32Moments(Optimizer):
         p.copy_(pf)
 
 
+def _adamw_step_multi(self, grads=None) -> None:
+    """All tensors of one dtype on one GPU are updated by a single multi-tensor launch; the rest go one by one."""
+    work = []
+    for name, p in self.params:
+        g = grads.get(name) if grads is not None else p.grad
+        if g is not None:
+            work.append((name, g, p, self.state_for(name, p)))
+    if not work:
+        self.step_count += 1
+        return
+    ok = lambda g, p: p.is_cuda and B.kernels_enabled() and p.is_contiguous() and g.is_contiguous() and p.dtype == g.dtype and \
+        p.dtype in (torch.bfloat16, torch.float32, torch.float16)
+    fast = [w for w in work if ok(w[1], w[2]) and w[2].dtype == work[0][2].dtype and w[2].device == work[0][2].device]
+    if len(fast) < 2:
+        return Optimizer.step(self, grads)
+    self.step_count += 1
+    fast_ids = {id(w[2]) for w in fast}
+    for name, g, p, st in work:
+        if id(p) not in fast_ids:
+            self.apply_single(name, g, p, st)
+    from ..ops.optim import OP_ADAMW, TensorTable
+    dev = fast[0][2].device
+    tab = getattr(self, "_table", None)
+    if tab is None or tab.device != dev:
+        tab = self._table = TensorTable(dev)
+    b1, b2 = self.betas
+    if self.bias_correction:
+        t = self.step_count
+        c1, c2 = 1.0 / (1 - b1 ** t), (1 - b2 ** t) ** -0.5
+    else:
+        c1 = c2 = 1.0
+    tab.update([dict(p=p.data_ptr(), g=g.data_ptr(), s0=st["m"].data_ptr(), s1=st["v"].data_ptr(), numel=p.numel()) for _, g, p, st in fast])
+    tab.launch(OP_ADAMW, fast[0][2].dtype, (self.lr, b1, b2, self.eps, self.weight_decay, c1, c2), "adamw_multi")
+
+
+AdamWFP32Moments.step = torch.no_grad()(_adamw_step_multi)
+
+
 def make_adamw(params, *, learning_rate=1e-3, weight_decay: float = 0.01, betas=None, eps: float = 1e-8,
                bias_correction: bool = False) -> AdamWFP32Moments:
     return AdamWFP32Moments(params, learning_rate, (0.9, 0.999) if betas is None else betas, eps, weight_decay,
@@ -270,7 +308,16 @@ def ns_streams(device) -> list:
     return _ns_stream_pool[key]
 
 
+def _muon_fast_path(self, g, p) -> bool:
+    return (p.is_cuda and B.kernels_enabled() and self.ns_carrier == "bf16" and p.dim() == 2 and p.is_contiguous() and g.is_contiguous()
+            and p.dtype == g.dtype and p.shape[0] % 8 == 0 and p.shape[1] % 8 == 0 and p.dtype in (torch.bfloat16, torch.float32)
+            and type(self) is MuonWithNSCarrier)
+
+
 def _muon_step_multistream(self, grads=None) -> None:
+    """One Muon step over all matrices.  On the GPU the element-wise stages are one multi-tensor launch each and Newton–Schulz runs
+    per stack of equally shaped matrices as batched GEMMs (``ops.optim.MuonBatchPlan``); anything the kernels do not cover
+    (fp32 carrier, odd shapes, CPU) takes the per-tensor path."""
     self.step_count += 1
     work = []
     for name, p in self.params:
@@ -279,23 +326,55 @@ def _muon_step_multistream(self, grads=None) -> None:
             work.append((name, g, p, self.state_for(name, p)))
     if not work:
         return
-    dev = work[0][2].device
-    if dev.type != "cuda" or not B.kernels_enabled() or len(work) < 2:
-        for name, g, p, st in work:
+    fast = [w for w in work if _muon_fast_path(self, w[1], w[2])]
+    if fast:
+        dt0 = fast[0][2].dtype
+        fast = [w for w in fast if w[2].dtype == dt0 and w[2].device == fast[0][2].device]
+    fast_ids = {id(w[2]) for w in fast}
+    for name, g, p, st in work:
+        if id(p) not in fast_ids:
             self.apply_single(name, g, p, st)
+    if not fast:
         return
+    from ..ops.optim import OP_AXPY_UPDATE, OP_MUON_MOMENTUM, OP_SCALE_INV_NORM, MuonBatchPlan, newton_schulz5_batched_
+    dev = fast[0][2].device
+    plan = getattr(self, "_batch_plan", None)
+    if plan is None or plan.device != dev:
+        plan = self._batch_plan = MuonBatchPlan(dev)
+    n = len(fast)
+    if plan.sumsq is None or plan.sumsq.numel() != n:
+        plan.sumsq = torch.zeros(n, dtype=torch.float32, device=dev)
+    else:
+        plan.sumsq.zero_()
+    lr = self.lr
+    stacks = plan.stacks([tuple(w[2].shape) for w in fast])
+    rows_in, rows_out, jobs = [None] * n, [None] * n, []
+    for sh, idx in stacks:
+        x, nxt, gws, poly = plan.workspace((sh, idx[0]), sh, len(idx))
+        res = nxt if self.ns_steps % 2 else x
+        jobs.append((x, nxt, gws, poly))
+        coef = lr * max(1.0, sh[0] / sh[1]) ** 0.5
+        for j, i in enumerate(idx):
+            _, g, p, st = fast[i]
+            rows_in[i] = dict(p=p.data_ptr(), g=g.data_ptr(), s0=st["v"].data_ptr(), u=x[j].data_ptr(),
+                              sumsq=plan.sumsq.data_ptr() + 4 * i, numel=p.numel(), coef=coef)
+            rows_out[i] = dict(p=p.data_ptr(), u=res[j].data_ptr(), numel=p.numel(), coef=coef)
+    dt = fast[0][2].dtype
+    plan.tab_in.update(rows_in)
+    plan.tab_in.launch(OP_MUON_MOMENTUM, dt, (self.momentum, self.weight_decay, 1.0 if self.nesterov else 0.0), "muon_momentum_multi")
+    plan.tab_in.launch(OP_SCALE_INV_NORM, dt, (1e-7,), "scale_inv_norm_multi")
     main = torch.cuda.current_stream(dev)
     ready = main.record_event()
     streams = ns_streams(dev)
-    # largest first, dealt round-robin: the streams finish at about the same time
-    work.sort(key=lambda w: -w[2].numel())
     for s in streams:
         s.wait_event(ready)
-    for i, (name, g, p, st) in enumerate(work):
-        with torch.cuda.stream(streams[i % len(streams)]):
-            self.apply_single(name, g, p, st)
+    for k, (x, nxt, gws, poly) in enumerate(jobs):      # stacks are sorted largest first and dealt round-robin
+        with torch.cuda.stream(streams[k % len(streams)]):
+            newton_schulz5_batched_(x, nxt, gws, poly, self.ns_steps)
     for s in streams:
         main.wait_stream(s)
+    plan.tab_out.update(rows_out)
+    plan.tab_out.launch(OP_AXPY_UPDATE, dt, (), "axpy_update_multi")
 
 
 MuonWithNSCarrier.step = torch.no_grad()(_muon_step_multistream)

@@ -91,3 +91,30 @@ def test_m2rnn_mixer_uses_kernel_and_matches_eager():
     with B.use_kernels(False):
         ref, _ = mix(x)
     assert torch.allclose(out.float(), ref.float(), atol=5e-2, rtol=5e-2)
+
+
+@pytest.mark.parametrize("H,nv,ng,V", [(4, 4, 4, 16), (4, 2, 1, 16), (2, 2, 2, 128)])
+def test_m2rnn_post_gate_kernel_matches_reference(H, nv, ng, V):
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B
+    torch.manual_seed(2)
+    b, s = 2, 37
+    y = torch.randn(b, s, H, V, device="cuda").bfloat16().requires_grad_()
+    pack = torch.randn(b, s, 3 + nv * V + ng * V, device="cuda").bfloat16().requires_grad_()      # v and g are strided slices
+    v = pack[..., 3:3 + nv * V].view(b, s, nv, V)
+    g = pack[..., 3 + nv * V:].view(b, s, ng, V)
+    D = torch.randn(H, V, device="cuda").bfloat16().requires_grad_()
+    n0 = B.launch_count("m2rnn_post_fwd")
+    out = ops.m2rnn_post_gate(y, v, g, D)
+    assert B.launch_count("m2rnn_post_fwd") == n0 + 1
+    w = torch.randn_like(out.float())
+    (out.float() * w).sum().backward()
+    got = [t.grad.float().clone() for t in (y, pack, D)]
+    for t in (y, pack, D):
+        t.grad = None
+    ref = ops.m2rnn_post_gate_reference(y.float(), v.float(), g.float(), D.float())
+    (ref * w).sum().backward()
+    assert torch.allclose(out.float(), ref, atol=3e-2, rtol=3e-2)
+    for a, t in zip(got, (y, pack, D)):
+        r = t.grad.float()
+        assert (a - r).abs().max() <= 3e-2 * r.abs().max() + 3e-2

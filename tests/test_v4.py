@@ -198,3 +198,38 @@ def test_convert_moe_to_fp8_keeps_the_layer_function_and_halves_expert_bytes():
     assert (got - ref).abs().max() < 6e-2 * ref.abs().max()
     assert torch.allclose(got, dense, atol=1e-4, rtol=1e-3)
     assert "experts.w_gate_up_fp8" in moe.state_dict() and "experts.w_down_scale_inv" in moe.state_dict()
+
+
+def test_fp8_lightning_indexer_selects_like_the_bf16_indexer():
+    """wq_b in e4m3 + 128×128 block scales: the index scores stay within FP8 rounding of the bf16 indexer's and the top-k sets
+    overlap almost entirely; the token-wise quantiser round-trips within e4m3 precision; checkpoint injection validates dtypes."""
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.nn.lightning_indexer_fp8 import (LightningIndexerFP8, convert_indexer_to_fp8, quantize_indexer_weights_for_fp8,
+                                                           token_dequant_fp8, token_quant_fp8)
+    from cppmega_mlx_b200.nn.mla import LightningIndexer, LightningIndexerConfig
+    torch.manual_seed(0)
+    cfg = LightningIndexerConfig(hidden_size=64, q_lora_rank=160, n_heads=4, head_dim=32, rope_head_dim=16, index_topk=12)
+    ref = LightningIndexer(cfg)
+    fp8 = convert_indexer_to_fp8(ref)
+    assert isinstance(fp8, LightningIndexerFP8) and fp8.wq_b.weight_fp8.dtype == torch.float8_e4m3fn
+    assert tuple(fp8.wq_b.weight_scale_inv.shape) == (1, 2)                       # ceil(128/128) × ceil(160/128) blocks
+    x, qr = torch.randn(2, 40, 64), torch.randn(2, 40, 160)
+    cos, sin = ops.rope_tables(40, 16, 10000.0)
+    q0, k0, w0 = ref.project(x, qr, cos, sin)
+    q1, k1, w1 = fp8.project(x, qr, cos, sin)
+    assert torch.equal(k0, k1) and torch.equal(w0, w1)
+    s0, s1 = ref.scores(q0, k0, w0), fp8.scores(q1, k1, w1)
+    assert (s0 - s1).abs().max() < 0.08 * s0.abs().max()
+    i0, i1 = ref.select(q0, k0, w0), fp8.select(q1, k1, w1)
+    overlap = sum(len(set(a.tolist()) & set(b.tolist()) - {-1}) for a, b in zip(i0.reshape(-1, 12), i1.reshape(-1, 12)))
+    total = int((i0 >= 0).sum())
+    assert overlap >= 0.85 * total
+    q8, sc = token_quant_fp8(qr)
+    assert q8.dtype == torch.float8_e4m3fn and sc.shape == (2, 40, 1)
+    assert (token_dequant_fp8(q8, sc, torch.float32) - qr).abs().max() <= 0.07 * qr.abs().amax(-1).max()
+    act = convert_indexer_to_fp8(ref, fp8_activations=True)
+    assert (act.scores(*act.project(x, qr, cos, sin)) - s0).abs().max() < 0.12 * s0.abs().max()
+    t = quantize_indexer_weights_for_fp8(ref)
+    with pytest.raises(TypeError):
+        fp8.load_fp8_weights(t["wq_b_fp8"].float(), t["wq_b_scale_inv"], t["wk"], t["weights_proj"])
+    fp8.load_fp8_weights(t["wq_b_fp8"].view(torch.uint8), t["wq_b_scale_inv"], t["wk"], t["weights_proj"])      # raw byte storage is accepted
