@@ -68,6 +68,8 @@ struct GemmParams {
   const int* tile_group;     // grouped (MoE) mode: B's dim-2 index for each 128-row tile of A / C; nullptr = batched rule
   const int* k_ranges;       // grouped wgrad: contraction range [k_begin, k_end) per dim-2 problem (multiples of 64)
   __nv_bfloat16* c_base;     // SYM_MIRROR: C as a plain pointer (the mirrored elements are stored with ordinary stores)
+  const int* m_limit;        // optional device scalar: row tiles starting at or beyond *m_limit are neither computed nor written
+                             // (the used part of a statically sized, token-sorted buffer is only known on the device)
   int* status;
 };
 
@@ -128,8 +130,8 @@ __device__ __forceinline__ TileCoord tile_coords(int t, int num_m, int num_n, in
   return c;
 }
 
-__device__ __forceinline__ bool tile_skipped(int flags, int m0, int n0) {
-  return (flags & GEMM_CAUSAL_SKIP) && n0 >= m0 + GEMM_BM;
+__device__ __forceinline__ bool tile_skipped(int flags, int m0, int n0, int m_limit) {
+  return ((flags & GEMM_CAUSAL_SKIP) && n0 >= m0 + GEMM_BM) || m0 >= m_limit;
 }
 __device__ __forceinline__ void k_range(int flags, int m0, int num_kb, const int* k_ranges, int i2, int& kb0, int& kb1) {
   kb0 = (flags & GEMM_K_LOWER) ? m0 / GEMM_BK : 0;
@@ -164,6 +166,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_tiles = num_m * num_n * p.nb2 * p.nb3 * p.nb4;
   const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
   int* status = p.status;
+  const int m_limit = p.m_limit != nullptr ? *p.m_limit : 0x7fffffff;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -200,7 +203,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int m0 = tc.tm * GEMM_BM, n0 = tc.tn * BN;
         const int a2 = tc.i2 / p.a_div2;
         const int b2 = p.tile_group != nullptr ? p.tile_group[tc.tm] : tc.i2 / p.b_div2;
-        if (tile_skipped(p.flags, m0, n0)) continue;
+        if (tile_skipped(p.flags, m0, n0, m_limit)) continue;
         int kb0, kb1;
         k_range(p.flags, m0, num_kb, p.k_ranges, tc.i2, kb0, kb1);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -244,7 +247,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3);
         const int m0 = tc.tm * GEMM_BM;
-        if (tile_skipped(p.flags, m0, tc.tn * BN)) continue;
+        if (tile_skipped(p.flags, m0, tc.tn * BN, m_limit)) continue;
         int kb0, kb1;
         k_range(p.flags, m0, num_kb, p.k_ranges, tc.i2, kb0, kb1);
         const int buf = local & 1;
@@ -297,7 +300,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int local = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3);
-      if (tile_skipped(p.flags, tc.tm * GEMM_BM, tc.tn * BN)) continue;
+      if (tile_skipped(p.flags, tc.tm * GEMM_BM, tc.tn * BN, m_limit)) continue;
       const int buf = local & 1;
       const uint32_t aphase = (local >> 1) & 1;
       ++local;
@@ -603,6 +606,7 @@ struct GemmArgs {
   float* stats;
   const int* tile_group;
   const int* k_ranges;
+  const int* m_limit;
   int b_groups;  // grouped mode: number of dim-2 slices of B (independent of the problem batch count)
   int* status;
   int max_ctas;
@@ -656,6 +660,7 @@ static int launch_gemm(const GemmArgs& g) {
   p.scale = g.scale; p.scale2 = g.scale2; p.stats = g.stats;
   p.tile_group = g.tile_group; p.k_ranges = g.k_ranges;
   p.c_base = static_cast<__nv_bfloat16*>(g.C);
+  p.m_limit = g.m_limit;
   p.status = g.status;
   kern<<<grid, cmb::GEMM_THREADS, Cfg::SMEM_BYTES, g.stream>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 104;
@@ -699,7 +704,7 @@ extern "C" int cmb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
 
 // Batched form. `ip` = {M, N, K, a_mn, b_mn, flags, a_div2, b_div2, max_ctas, mask_words, b_groups}; `lp` = {lda, ldb, ldc, nb2,
 // nb3, nb4, sA2, sA3, sA4, sB2, sB3, sB4, sC2, sC3, sC4, sv2, sv3, sv4, mask_sb} (element counts / strides).
-// `pp` = {row_vec, col_vec, aux, mask, stats, tile_group, k_ranges} device pointers (any may be null). Flags select the
+// `pp` = {row_vec, col_vec, aux, mask, stats, tile_group, k_ranges, m_limit} device pointers (any may be null). Flags select the
 // epilogue, see the enum at the top of this file. Grouped (MoE) use: `tile_group[i]` names B's dim-2 slice for the i-th
 // 128-row tile of A/C (A and C plain 2-D, B stacked per expert); `k_ranges[2e], k_ranges[2e+1]` bound the contraction
 // of dim-2 problem e (wgrad over one expert's rows of the token-sorted buffers).
@@ -717,6 +722,7 @@ extern "C" int cmb_gemm_bf16_batched(const void* A, const void* B, void* C, cons
   g.row_vec = static_cast<const float*>(pp[0]); g.col_vec = static_cast<const float*>(pp[1]);
   g.aux = pp[2]; g.mask = static_cast<const unsigned*>(pp[3]); g.stats = static_cast<float*>(const_cast<void*>(pp[4]));
   g.tile_group = static_cast<const int*>(pp[5]); g.k_ranges = static_cast<const int*>(pp[6]);
+  g.m_limit = static_cast<const int*>(pp[7]);
   g.b_groups = ip[10];
   if (g.tile_group != nullptr && g.b_groups <= 0) return 109;
   g.scale = scale;

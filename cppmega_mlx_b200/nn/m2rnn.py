@@ -106,6 +106,11 @@ class M2RNNMixer(nn.Module):
         dt = torch.exp(torch.empty(c.num_heads).uniform_(math.log(lo), math.log(c.dt_init_max)))
         self.dt_bias = nn.Parameter(dt + torch.log(-torch.expm1(-dt)))
         self.D = nn.Parameter(torch.ones(c.num_heads, c.v_head_dim)) if c.use_residual else None
+        # head parallelism (parallel.tp.tensor_parallelize_mixers): this module then holds 1/tp of every per-head quantity; inputs
+        # whose head count could not be split stay replicated (their gradients are summed over the group), the gated norm takes
+        # its mean square over all ranks' columns, and the output projection's partial products are summed.
+        self.tp_group = None
+        self.tp_replicated: tuple[str, ...] = ()
 
     def initial_h0(self, batch: int, dtype=torch.float32, device=None) -> torch.Tensor:
         c = self.config
@@ -123,7 +128,11 @@ class M2RNNMixer(nn.Module):
             raise ValueError("pass either h0 or mixer_state, not both")
         c = self.config
         b, s, _ = hidden_states.shape
-        proj = self.in_proj(hidden_states)
+        if self.tp_group is not None:
+            from ..parallel.tp import mixed_column_linear
+            proj = mixed_column_linear(hidden_states, self.in_proj.weight, getattr(self, "tp_replicated_rows", 0), self.tp_group)
+        else:
+            proj = self.in_proj(hidden_states)
         conv_end, f_end = self.conv_dim, self.conv_dim + self.f_dim
         raw = proj[..., :conv_end]
         prefix = None
@@ -142,12 +151,25 @@ class M2RNNMixer(nn.Module):
         k = qk[..., self.q_dim:].reshape(b, s, c.num_k_heads, c.k_head_dim)
         v = vflat.reshape(b, s, c.num_v_heads, c.v_head_dim)
         f = m2rnn_softplus_decay_gate(tail[..., :self.f_dim], self.A_log, self.dt_bias)
-        out, h = ops.m2rnn_scan(q, k, v, self.state_weight.to(q.dtype), f, h0=h0)
+        W = self.state_weight.to(q.dtype)
+        if self.tp_group is not None:
+            from ..parallel.tp import copy_to_tp
+            if "q" in self.tp_replicated:
+                q = copy_to_tp(q, self.tp_group)
+            if "k" in self.tp_replicated:
+                k = copy_to_tp(k, self.tp_group)
+            if "w" in self.tp_replicated:
+                W = copy_to_tp(W, self.tp_group)
+        out, h = ops.m2rnn_scan(q, k, v, W, f, h0=h0)
         H = c.num_heads
         g = tail[..., self.f_dim:].reshape(b, s, c.num_g_heads, c.v_head_dim)
         # residual and output gate in one pass: (y + v·D) · silu(g), heads of v / g broadcast inside the kernel
         out = ops.m2rnn_post_gate(out, v, g, self.D).reshape(b, s, H * c.v_head_dim)
-        out = self.out_proj(self.g_norm(out))
+        if self.tp_group is not None:
+            from ..parallel.tp import reduce_from_tp, sharded_rms_norm
+            out = reduce_from_tp(self.out_proj(sharded_rms_norm(out, self.g_norm.weight, self.g_norm.eps, self.tp_group)), self.tp_group)
+        else:
+            out = self.out_proj(self.g_norm(out))
         if not return_state:
             return out, h
         hist = c.conv_kernel - 1

@@ -157,6 +157,7 @@ class MLAAttention(nn.Module):
         self.wo = Linear(H * c.v_head_dim, c.hidden_size, zero_init=c.zero_init_out)
         self.indexer = None
         self.aux_loss: torch.Tensor | None = None
+        self.tp_group = None     # set by parallel.tp.tensor_parallelize_mixers: this module then holds num_heads / tp of the heads
         if c.index_topk > 0:
             self.indexer = LightningIndexer(LightningIndexerConfig(
                 hidden_size=c.hidden_size, q_lora_rank=c.q_lora_rank, n_heads=c.index_n_heads,
@@ -173,14 +174,28 @@ class MLAAttention(nn.Module):
         c = self.config
         b, s, _ = x.shape
         qr = self.q_norm(self.wq_a(x))
-        q = self.wq_b(qr).view(b, s, c.num_heads, c.qk_head_dim)
         kv = self.wkv_a(x)
         c_kv = self.kv_norm(kv[..., :c.kv_lora_rank])
         k_pe = kv[..., c.kv_lora_rank:]
+        qr_h = qr
+        if self.tp_group is not None:
+            # head-parallel: the low-rank projections above are replicated, everything per head below is this rank's slice; the
+            # gradients flowing back into the replicated part are summed over the group here (identity forward)
+            from ..parallel.tp import copy_to_tp
+            qr_h, c_kv, k_pe = copy_to_tp(qr, self.tp_group), copy_to_tp(c_kv, self.tp_group), copy_to_tp(k_pe.contiguous(), self.tp_group)
+        q = self.wq_b(qr_h).view(b, s, c.num_heads, c.qk_head_dim)
         cos, sin = freqs if freqs is not None else ops.rope_tables(s, c.qk_rope_head_dim, c.rope_theta, device=x.device, offset=offset)
         q = ops.apply_rope(q, cos, sin, c.qk_nope_head_dim, c.qk_rope_head_dim)
         k_pe = ops.apply_rope(k_pe[:, :, None, :].contiguous(), cos, sin)[:, :, 0]
         return qr, q, c_kv, k_pe, (cos, sin)
+
+    def _out(self, o):
+        """Output projection; with head parallelism each rank holds the columns of its heads and the partial products are summed."""
+        y = self.wo(o)
+        if self.tp_group is not None:
+            from ..parallel.tp import reduce_from_tp
+            y = reduce_from_tp(y, self.tp_group)
+        return y
 
     def _latent_query(self, q):
         """Fold W_UK into the query: [B,S,H,nope+rope] → [B,S,H,kv_lora+rope]."""
@@ -217,7 +232,7 @@ class MLAAttention(nn.Module):
         out_lat = DA.decode_attention(self._latent_query(q)[:, 0], cache.attention_rows(rows, 1, rows.shape[-1]), None, cache.table(), lengths,
                                       scale=c.qk_head_dim ** -0.5, d_v=c.kv_lora_rank, topk=topk,
                                       max_keys=c.index_topk if topk is not None else cache.capacity)
-        return self.wo(self._latent_output(out_lat[:, None]).reshape(b, 1, c.num_heads * c.v_head_dim))
+        return self._out(self._latent_output(out_lat[:, None]).reshape(b, 1, c.num_heads * c.v_head_dim))
 
     def forward(self, x: torch.Tensor, mask=None, *, kv_cache=None, layer_idx: int = 0, sparse: bool | None = None):
         c = self.config
@@ -264,7 +279,7 @@ class MLAAttention(nn.Module):
             if A.supported(q, k, v):
                 bits = A.build_mask_bits(idx, sk) if idx is not None else None
                 o, _ = A.masked_attention(q, k, v, bits, scale)
-                return self.wo(o.reshape(b, s, c.num_heads * c.v_head_dim))
+                return self._out(o.reshape(b, s, c.num_heads * c.v_head_dim))
         if kv_cache is not None and s == 1 and add_mask is None:
             from ..ops import decode_attention as DA
             rows = latent[:, :, None, :]
@@ -274,7 +289,7 @@ class MLAAttention(nn.Module):
                 lengths = torch.full((b,), sk, dtype=torch.int32, device=x.device)
                 out_lat = DA.decode_attention(q_lat, rows, None, None, lengths, scale=scale, d_v=c.kv_lora_rank, max_keys=sk,
                                               topk=None if idx is None else idx[:, 0].contiguous())
-                return self.wo(self._latent_output(out_lat[:, None]).reshape(b, s, c.num_heads * c.v_head_dim))
+                return self._out(self._latent_output(out_lat[:, None]).reshape(b, s, c.num_heads * c.v_head_dim))
         if idx is not None:
             out_lat, _ = ops.sparse_mla_attention(self._latent_query(q), latent[:, :, None, :], idx[:, :, None, :],
                                                   sm_scale=scale, d_v=c.kv_lora_rank)
@@ -304,7 +319,7 @@ class MLAAttention(nn.Module):
                 o = dense_attention(q.transpose(1, 2), k.transpose(1, 2), _pad_v(v, c).transpose(1, 2), is_causal=True,
                                     scale=scale)
             o = o.transpose(1, 2)[..., :c.v_head_dim]
-        return self.wo(o.reshape(b, s, c.num_heads * c.v_head_dim))
+        return self._out(o.reshape(b, s, c.num_heads * c.v_head_dim))
 
 
 def _pad_v(v, c: MLABlockConfig):

@@ -214,9 +214,48 @@ class MoE(nn.Module):
         if c.shared_expert_hidden_size is not None:
             self.shared_expert = FeedForward(c.d_model, c.shared_expert_hidden_size * c.num_shared_experts, c.activation)
         self.last_load: torch.Tensor | None = None
+        self.tp_group = None      # expert tensor parallelism (parallel.tp.tensor_parallelize_mixers): tokens replicated, experts split
+        self.tp_rank = 0
+
+    def _routed_expert_tp(self, flat: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor) -> torch.Tensor:
+        """Tokens are replicated over the group and every rank holds ``local_experts`` of the experts: a rank evaluates the
+        assignments that name one of its experts and the partial outputs are summed.  Foreign assignments are sorted behind the
+        local segments of the padded buffer, beyond the row limit the grouped GEMMs stop at, so they cost no tensor work."""
+        from ..ops import grouped_gemm_cuda as GG
+        from ..parallel.tp import copy_to_tp, reduce_from_tp
+        T, k = top_idx.shape
+        Le = self.local_experts
+        flat = copy_to_tp(flat, self.tp_group)
+        e = top_idx.reshape(-1)
+        mine = torch.div(e, Le, rounding_mode="floor") == self.tp_rank
+        local_e = torch.where(mine, e - self.tp_rank * Le, torch.full_like(e, Le))        # foreign → sentinel group Le (sorted last)
+        w = copy_to_tp(top_w.reshape(-1), self.tp_group) * mine.to(top_w.dtype)   # the router sees only this rank's share of d(out)/d(w)
+        if ops.kernels_enabled() and GG.supported(flat, self.experts.w_gate_up) and self.config.activation == "swiglu":
+            L = GG.build_layout(local_e, Le + 1)
+            L.num_experts = Le
+            L.k_ranges = L.k_ranges[:Le].contiguous()
+            L.tile_group = L.tile_group.clamp(max=Le - 1)
+            L.used_rows = L.k_ranges[-1, 1:].contiguous()                                  # rows of the local segments only
+            tok = torch.div(L.order, k, rounding_mode="floor")
+            xp = GG.scatter_to_padded(flat, tok, L)
+            yp = self.expert_ffn_padded(xp, L)
+            keep = mine[L.order]
+            ys = torch.where(keep[:, None], yp.index_select(0, L.slot), torch.zeros((), dtype=yp.dtype, device=yp.device))
+            ys = ys * w[L.order].to(yp.dtype)[:, None]
+            out = torch.zeros_like(flat).index_add_(0, tok, ys)
+        else:
+            order = torch.argsort(local_e, stable=True)
+            counts = torch.bincount(local_e, minlength=Le + 1)
+            n_local = int(counts[:Le].sum())
+            tok = torch.div(order[:n_local], k, rounding_mode="floor")
+            ys = self.experts(flat.index_select(0, tok), counts[:Le]) * w[order[:n_local]].to(flat.dtype)[:, None]
+            out = torch.zeros_like(flat).index_add_(0, tok, ys)
+        return reduce_from_tp(out, self.tp_group)
 
     def routed_forward(self, flat: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor) -> torch.Tensor:
         T, k = top_idx.shape
+        if self.tp_group is not None:
+            return self._routed_expert_tp(flat, top_idx, top_w)
         if self.ep_size > 1:
             fused = getattr(self, "fused_ep", None)
             if fused is not None and flat.is_cuda and flat.dtype == torch.bfloat16 and ops.kernels_enabled():

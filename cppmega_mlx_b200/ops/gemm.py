@@ -79,7 +79,8 @@ def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, 
                  sv: tuple[int, int, int] = (0, 0, 0), max_ctas: int = 0, flags: int = 0, aux: torch.Tensor | None = None,
                  mask: torch.Tensor | None = None, mask_words: int = 0, mask_sb: int = 0, scale: float = 1.0,
                  scale2: float = 0.0, stats: torch.Tensor | None = None, out_f32: bool | None = None,
-                 tile_group: torch.Tensor | None = None, k_ranges: torch.Tensor | None = None, b_groups: int = 0) -> torch.Tensor | None:
+                 tile_group: torch.Tensor | None = None, k_ranges: torch.Tensor | None = None, b_groups: int = 0,
+                 m_limit: torch.Tensor | None = None) -> torch.Tensor | None:
     """Strided-batched C (+)= A·Bᵀ. ``a``/``b``/``out`` only supply base pointers; all geometry is explicit:
     pitches ``ld*`` and per-operand element strides over the three batch dims ``nb = (n2, n3, n4)``.
     ``a_div2``/``b_div2`` let ``div`` consecutive dim-2 problems share one operand slice (the operand then has
@@ -87,7 +88,8 @@ def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, 
     ``acc · exp(row_vec[t] − col_vec[s]) · [s ≤ t]``; with ``row_vec`` alone, ``acc · exp(row_vec[t])``.
     ``flags`` adds the causal-range and attention epilogue modes (see ``csrc/gemm_bf16.cu``).  Grouped (MoE) use:
     ``tile_group`` (int32, one entry per 128-row tile of A/C) picks B's dim-2 slice among ``b_groups``; ``k_ranges``
-    (int32 ``[n2, 2]``) bounds the contraction of each dim-2 problem."""
+    (int32 ``[n2, 2]``) bounds the contraction of each dim-2 problem; ``m_limit`` (int32 device scalar) makes the kernel skip every
+    row tile that starts at or beyond it (output rows there are left untouched)."""
     lib = B.load_library()
     f32 = (out is not None and out.dtype == torch.float32) if out_f32 is None else out_f32
     fl = flags | (OUT_F32 if f32 else 0) | (ACCUMULATE if accumulate else 0)

@@ -34,6 +34,8 @@ class GroupedLayout:
     k_ranges: torch.Tensor       # [E, 2] int32
     counts: torch.Tensor         # [E] int64
     valid_rows: torch.Tensor | None = None   # [rows] bool, set by producers that do not clear their buffers
+    used_rows: torch.Tensor | None = None    # int32 device scalar: rows of the padded buffer that belong to some expert segment;
+                                             # the GEMMs skip every 128-row tile beyond it (rows there are neither read nor written)
 
 
 def padded_rows(num_assignments: int, num_experts: int) -> int:
@@ -56,7 +58,7 @@ def build_layout(expert_ids: torch.Tensor, num_experts: int) -> GroupedLayout:
     tile_start = torch.arange(rows // TILE, device=e.device) * TILE
     tile_group = torch.searchsorted(pad_end, tile_start, right=True).clamp_(max=num_experts - 1).int()
     k_ranges = torch.stack([pad_off, pad_end], 1).int().contiguous()
-    return GroupedLayout(num_experts, rows, slot, order, tile_group, k_ranges, counts)
+    return GroupedLayout(num_experts, rows, slot, order, tile_group, k_ranges, counts, used_rows=pad_end[-1:].int())
 
 
 def supported(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -71,7 +73,7 @@ def _fwd(x, w, L: GroupedLayout, b_mn: bool):
     K = out_f if b_mn else in_f
     y = torch.empty(L.rows, N, dtype=torch.bfloat16, device=x.device)
     G.gemm_batched(x, w, y, M=L.rows, N=N, K=K, a_mn=False, b_mn=b_mn, lda=x.stride(0), ldb=in_f, ldc=N, nb=(1, 1, 1),
-                   sA=(0, 0, 0), sB=(out_f * in_f, 0, 0), sC=(0, 0, 0), tile_group=L.tile_group, b_groups=E)
+                   sA=(0, 0, 0), sB=(out_f * in_f, 0, 0), sC=(0, 0, 0), tile_group=L.tile_group, b_groups=E, m_limit=L.used_rows)
     return y
 
 

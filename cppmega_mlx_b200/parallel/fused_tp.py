@@ -98,6 +98,66 @@ class FusedTPComm:
         return y, full.view(W * rows, K)
 
 
+    # -- GEMM → all-reduce (replicated activations) ------------------------------------------------
+    def gemm_all_reduce(self, x: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False) -> torch.Tensor:
+        """Σ_ranks x·wᵀ, complete on every rank: the fused GEMM → reduce-scatter above, then every rank publishes its reduced row
+        block and the copy engines pull the peers' blocks (the all-gather half of the all-reduce) — no NCCL call."""
+        W, r = self.world, self.rank
+        M = x.shape[0]
+        N = w.shape[1] if b_mn else w.shape[0]
+        rows = M // W
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+        mine = self.gemm_reduce_scatter(x, w, b_mn=b_mn)
+        pub = self.publish.tensor[:rows * N].view(rows, N)
+        pub.copy_(mine)
+        y[r * rows:(r + 1) * rows].copy_(mine)
+        self.barrier()                                                    # every reduced block is published
+        for i in range(1, W):
+            p = (r + i) % W
+            y[p * rows:(p + 1) * rows].copy_(self._peer(self.publish, p, 0, (rows, N)), non_blocking=True)
+        self.barrier()                                                    # peers are done reading my block
+        return y
+
+
+class _RowParallelAllReduceFused(torch.autograd.Function):
+    """y = Σ_ranks x_local · w_localᵀ on every rank (replicated activations); backward is local."""
+
+    @staticmethod
+    def forward(ctx, x, w, comm: FusedTPComm):
+        ctx.save_for_backward(x, w)
+        return comm.gemm_all_reduce(x.contiguous(), w)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w = ctx.saved_tensors
+        gy = gy.contiguous()
+        return ops.gemm_raw(gy, w, b_mn=True), ops.gemm_raw(gy, x.contiguous(), a_mn=True, b_mn=True), None
+
+
+class _ColumnParallelCopyFused(torch.autograd.Function):
+    """y_local = x · w_localᵀ with a replicated input; backward sums the ranks' partial dx with the fused GEMM → all-reduce."""
+
+    @staticmethod
+    def forward(ctx, x, w, comm: FusedTPComm):
+        ctx.save_for_backward(x, w)
+        ctx.comm = comm
+        return ops.gemm_raw(x.contiguous(), w)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w = ctx.saved_tensors
+        gy = gy.contiguous()
+        return ctx.comm.gemm_all_reduce(gy, w, b_mn=True), ops.gemm_raw(gy, x.contiguous(), a_mn=True, b_mn=True), None
+
+
+def row_parallel_all_reduce_fused(x_local, w_local, comm):
+    return _RowParallelAllReduceFused.apply(x_local, w_local, comm)
+
+
+def column_parallel_copy_fused(x, w_local, comm):
+    return _ColumnParallelCopyFused.apply(x, w_local, comm)
+
+
 class _ColumnParallelFused(torch.autograd.Function):
     """y_local [M, N/W] = all_gather_S(x_shard) · w_localᵀ ; backward: dx_shard = reduce_scatter_S(dy · w_local)."""
 

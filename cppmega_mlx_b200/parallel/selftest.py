@@ -145,6 +145,42 @@ def case_tp(rank, world, dev):
                           "rel_err_vs_fp32_single_gpu": float(e_abs), "ms_fwd_bwd_nccl": t_nccl, "ms_fwd_bwd_fused": t_fused}))
 
 
+def case_tpar(rank, world, dev):
+    """Tensor-parallel SwiGLU FFN with replicated activations, forward and backward: the fused GEMM → reduce-scatter + gather
+    all-reduce of ``fused_tp.py`` against the NCCL all-reduce of ``tp.py`` (results and device time)."""
+    from cppmega_mlx_b200.nn.basic import FeedForward
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.parallel import tp as TP
+    from cppmega_mlx_b200.parallel.fused_tp import FusedTPComm
+    S, d, hid = (16384, 2048, 5632) if os.environ.get("CMB_TP_SMALL") != "1" else (1024, 256, 512)
+    torch.manual_seed(0)
+    ffn = FeedForward(d, hid, "swiglu").to(dev, torch.bfloat16)
+    x = (torch.randn(S, d, device=dev) * 0.5).bfloat16()
+    g = dist.group.WORLD
+    comm = FusedTPComm(g, dev, max_rows_per_rank=S // world, max_cols=d)
+    mods = {False: TP.TPFeedForward(ffn, g), True: TP.TPFeedForward(ffn, g, fused=comm)}
+
+    def run(fused: bool):
+        m = mods[fused]
+        m.zero_grad()
+        xs = x.clone().requires_grad_()
+        y = m(xs)
+        y.backward(torch.ones_like(y) * 0.01)
+        return y.detach(), xs.grad, m.up.weight.grad.clone(), m.down.weight.grad.clone()
+    ref, out = run(False), run(True)
+    torch.cuda.synchronize()
+    B.check_status()
+    errs = []
+    for r_, o_ in zip(ref, out):
+        e = (r_.float() - o_.float()).abs().max() / r_.float().abs().max().clamp_min(1e-6)
+        dist.all_reduce(e, op=dist.ReduceOp.MAX)
+        errs.append(float(e))
+    t_nccl, t_fused = _time(lambda: run(False)), _time(lambda: run(True))
+    if rank == 0:
+        print(json.dumps({"case": "tpar", "world": world, "shape": [S, d, hid], "rel_err_vs_nccl[y,dx,dw_up,dw_down]": errs,
+                          "ms_fwd_bwd_nccl": t_nccl, "ms_fwd_bwd_fused": t_fused}))
+
+
 def case_ep(rank, world, dev):
     """Expert-parallel MoE layer, forward and backward: fused dispatch/combine kernels vs the NCCL all-to-all path."""
     from cppmega_mlx_b200.nn.moe import MoE, MoEConfig
@@ -232,7 +268,7 @@ def main():
     case = sys.argv[1] if len(sys.argv) > 1 else "zero1"
     rank, world, dev = _setup()
     try:
-        {"zero1": case_zero1, "zero1det": case_zero1det, "tp": case_tp, "ep": case_ep, "epdrop": case_epdrop}[case](rank, world, dev)
+        {"zero1": case_zero1, "zero1det": case_zero1det, "tp": case_tp, "tpar": case_tpar, "ep": case_ep, "epdrop": case_epdrop}[case](rank, world, dev)
     finally:
         dist.barrier()
         dist.destroy_process_group()

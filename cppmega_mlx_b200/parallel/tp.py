@@ -158,29 +158,39 @@ class RowParallelLinear(nn.Module):
 
 
 class TPFeedForward(nn.Module):
-    """SwiGLU / GELU FFN split over the hidden dimension."""
+    """SwiGLU / GELU FFN split over the hidden dimension.  ``fused`` (a ``parallel.fused_tp.FusedTPComm``) replaces the NCCL
+    all-reduces of the replicated-activation form by the GEMM → reduce-scatter kernels over symmetric memory plus a copy-engine
+    gather (forward of the down projection, backward of the up projection)."""
 
-    def __init__(self, full: FeedForward, group, *, sequence_parallel: bool = False):
+    def __init__(self, full: FeedForward, group, *, sequence_parallel: bool = False, fused=None):
         super().__init__()
         self.activation = full.activation
         gated = full.activation == "swiglu"
         self.up = ColumnParallelLinear(full.gate_up_proj if gated else full.up_proj, group, sequence_parallel=sequence_parallel,
                                        blocks=2 if gated else 1)
         self.down = RowParallelLinear(full.down_proj, group, sequence_parallel=sequence_parallel)
+        self.fused = fused if not sequence_parallel else None
+
+    def _act(self, h):
+        return ops.swiglu(h) if self.activation == "swiglu" else (torch.nn.functional.gelu(h) if self.activation == "gelu" else ops.squared_relu(h))
 
     def forward(self, x):
-        h = self.up(x)
-        h = ops.swiglu(h) if self.activation == "swiglu" else (torch.nn.functional.gelu(h) if self.activation == "gelu" else ops.squared_relu(h))
-        return self.down(h)
+        f = self.fused
+        if f is not None and x.is_cuda and x.dtype == torch.bfloat16 and ops.kernels_enabled() and x.numel() // x.shape[-1] % f.world == 0:
+            from .fused_tp import column_parallel_copy_fused, row_parallel_all_reduce_fused
+            x2 = x.reshape(-1, x.shape[-1])
+            h = self._act(column_parallel_copy_fused(x2, self.up.weight, f))
+            return row_parallel_all_reduce_fused(h, self.down.weight, f).view(*x.shape[:-1], -1)
+        return self.down(self._act(self.up(x)))
 
 
-def tensor_parallelize_ffn(model: nn.Module, group, *, sequence_parallel: bool = False) -> int:
+def tensor_parallelize_ffn(model: nn.Module, group, *, sequence_parallel: bool = False, fused=None) -> int:
     """Replace every dense ``FeedForward`` under ``model`` by its TP form (in place); returns how many were replaced."""
     n = 0
     for parent in list(model.modules()):
         for name, child in list(parent.named_children()):
             if isinstance(child, FeedForward):
-                setattr(parent, name, TPFeedForward(child, group, sequence_parallel=sequence_parallel))
+                setattr(parent, name, TPFeedForward(child, group, sequence_parallel=sequence_parallel, fused=fused))
                 n += 1
     return n
 
@@ -194,3 +204,204 @@ def allreduce_replicated_grads(model: nn.Module, group, *, skip=(ColumnParallelL
     for p in model.parameters():
         if id(p) not in sharded and p.grad is not None:
             dist.all_reduce(p.grad, group=group)
+
+
+# ----------------------------------------------------------------------------------------------- head-parallel mixers
+class _AllReduceSum(torch.autograd.Function):
+    """Sum over the group in both directions (a statistic every rank contributes to and every rank consumes)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        x = x.contiguous().clone()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+def sharded_rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, group) -> torch.Tensor:
+    """RMS norm over a feature dimension that is split over ``group``: the mean square is taken over all ranks' columns (one small
+    all-reduce of a [..., 1] tensor), the weight is this rank's slice."""
+    w = _world(group)
+    xf = x.float()
+    ss = xf.pow(2).sum(-1, keepdim=True)
+    if w > 1:
+        ss = _AllReduceSum.apply(ss, group)
+    return (xf * torch.rsqrt(ss / (x.shape[-1] * w) + eps)).to(x.dtype) * weight.to(x.dtype)
+
+
+class _MixedColumnLinear(torch.autograd.Function):
+    """``x · Wᵀ`` where the first ``n_rep`` output rows of ``W`` are replicated over the group (their consumers all-reduce their own
+    gradients, so their share of ``dx`` is already complete on every rank) and the remaining rows are this rank's slice (their
+    share of ``dx`` is a partial sum that has to be added up over the group)."""
+
+    @staticmethod
+    def forward(ctx, x, w, n_rep, group):
+        ctx.save_for_backward(x, w)
+        ctx.n_rep, ctx.group = n_rep, group
+        return ops.linear(x, w)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        n = ctx.n_rep
+        g2 = g.reshape(-1, g.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1])
+        gw = (g2.t() @ x2).to(w.dtype)
+        part = (g2[:, n:] @ w[n:]).contiguous()
+        dist.all_reduce(part, group=ctx.group)
+        gx = part + g2[:, :n] @ w[:n] if n else part
+        return gx.view(x.shape).to(x.dtype), gw, None, None
+
+
+def mixed_column_linear(x, w, n_rep: int, group):
+    return _MixedColumnLinear.apply(x, w, n_rep, group)
+
+
+def _rows(w: torch.Tensor, start: int, n: int) -> torch.Tensor:
+    return w[start:start + n]
+
+
+def _shard_mla(full, group):
+    """Head-parallel copy of an ``MLAAttention``: per-head projections sliced, low-rank projections / norms / indexer replicated."""
+    import dataclasses
+    from ..nn.mla import MLAAttention
+    tp, r = _world(group), dist.get_rank(group)
+    c = full.config
+    if c.num_heads % tp:
+        raise ValueError(f"tensor-parallel size {tp} must divide the {c.num_heads} attention heads")
+    Hl = c.num_heads // tp
+    dev, dt = full.wo.weight.device, full.wo.weight.dtype
+    with torch.device(dev):
+        loc = MLAAttention(dataclasses.replace(c, num_heads=Hl)).to(dt)
+    with torch.no_grad():
+        for name in ("wq_a", "q_norm", "wkv_a", "kv_norm"):
+            getattr(loc, name).load_state_dict(getattr(full, name).state_dict())
+        if full.indexer is not None:
+            loc.indexer.load_state_dict(full.indexer.state_dict())
+        dq, dkv = c.qk_head_dim, c.qk_nope_head_dim + c.v_head_dim
+        loc.wq_b.weight.copy_(_rows(full.wq_b.weight, r * Hl * dq, Hl * dq))
+        loc.wkv_b.weight.copy_(_rows(full.wkv_b.weight, r * Hl * dkv, Hl * dkv))
+        loc.wo.weight.copy_(full.wo.weight[:, r * Hl * c.v_head_dim:(r + 1) * Hl * c.v_head_dim])
+    loc.tp_group = group
+    loc.train(full.training)
+    return loc
+
+
+def _shard_moe(full, group):
+    """Expert-tensor-parallel copy of an ``MoE``: this rank keeps a contiguous slice of the routed experts; router and shared expert
+    are replicated (they see the same tokens on every rank of the group)."""
+    from ..nn.moe import MoE
+    tp, r = _world(group), dist.get_rank(group)
+    c = full.config
+    if full.ep_size > 1:
+        raise ValueError("an expert-parallel MoE cannot also be tensor-parallelized")
+    if c.num_experts % tp:
+        raise ValueError(f"tensor-parallel size {tp} must divide the {c.num_experts} experts")
+    Le = c.num_experts // tp
+    dev, dt = full.experts.w_down.device, full.experts.w_down.dtype
+    with torch.device(dev):
+        loc = MoE(c).to(dt)
+    from ..nn.moe import GroupedExperts
+    with torch.device(dev):
+        loc.experts = GroupedExperts(Le, c.d_model, c.expert_hidden_size, c.activation).to(dt)
+    with torch.no_grad():
+        loc.experts.w_gate_up.copy_(full.experts.w_gate_up[r * Le:(r + 1) * Le])
+        loc.experts.w_down.copy_(full.experts.w_down[r * Le:(r + 1) * Le])
+        loc.router.load_state_dict(full.router.state_dict())
+        if full.shared_expert is not None:
+            loc.shared_expert.load_state_dict(full.shared_expert.state_dict())
+    loc.local_experts, loc.tp_group, loc.tp_rank = Le, group, r
+    loc.train(full.training)
+    return loc
+
+
+def _shard_m2rnn(full, group):
+    """Head-parallel copy of an ``M2RNNMixer``.  Head counts divisible by the group size are split; the others (a single shared
+    q / k head, one state-weight matrix) stay whole on every rank and are listed in ``tp_replicated``."""
+    import dataclasses
+    from ..nn.m2rnn import M2RNNMixer
+    tp, r = _world(group), dist.get_rank(group)
+    c = full.config
+    H = c.num_heads
+    if H % tp:
+        raise ValueError(f"tensor-parallel size {tp} must divide the {H} M2RNN heads")
+    split = lambda n: n // tp if n % tp == 0 else n
+    counts = {k: getattr(c, k) for k in ("num_q_heads", "num_k_heads", "num_v_heads", "num_f_heads", "num_g_heads", "num_weight_heads")}
+    for k in ("num_v_heads", "num_f_heads", "num_g_heads"):
+        if counts[k] != H:
+            raise ValueError(f"head-parallel M2RNN needs {k} == num_heads ({H}), got {counts[k]}")   # grouped v/f/g heads would straddle ranks
+    lc = dataclasses.replace(c, **{k: split(v) for k, v in counts.items()})
+    if lc.num_heads != H // tp:
+        raise ValueError("head-parallel M2RNN: no per-head input could be split")
+    dev, dt = full.out_proj.weight.device, full.out_proj.weight.dtype
+    with torch.device(dev):
+        loc = M2RNNMixer(lc).to(dt)
+    K, V = c.k_head_dim, c.v_head_dim
+
+    def seg(total_heads, width, base):        # rows of the packed projection / conv for one input, this rank's share
+        n = total_heads * width
+        if total_heads % tp:
+            return base, n, base + n          # replicated: the whole segment
+        return base + r * (n // tp), n // tp, base + n
+    rows, conv_rows, base = [], [], 0
+    for heads, width in ((c.num_q_heads, K), (c.num_k_heads, K), (c.num_v_heads, V)):
+        s0, n, base = seg(heads, width, base)
+        rows.append((s0, n))
+        conv_rows.append((s0, n))
+    s0, n, base = seg(c.num_f_heads, 1, base)
+    rows.append((s0, n))
+    s0, n, base = seg(c.num_g_heads, V, base)
+    rows.append((s0, n))
+    pick = lambda w, spans: torch.cat([w[a:a + b] for a, b in spans], 0)
+    Hl = H // tp
+    with torch.no_grad():
+        loc.in_proj.weight.copy_(pick(full.in_proj.weight, rows))
+        loc.conv_weight.copy_(pick(full.conv_weight, conv_rows))
+        loc.conv_bias.copy_(pick(full.conv_bias, conv_rows))
+        loc.g_norm.weight.copy_(full.g_norm.weight[r * Hl * V:(r + 1) * Hl * V])
+        loc.out_proj.weight.copy_(full.out_proj.weight[:, r * Hl * V:(r + 1) * Hl * V])
+        nw = c.num_weight_heads
+        loc.state_weight.copy_(full.state_weight if nw % tp else full.state_weight[r * (nw // tp):(r + 1) * (nw // tp)])
+        loc.A_log.copy_(full.A_log[r * Hl:(r + 1) * Hl])
+        loc.dt_bias.copy_(full.dt_bias[r * Hl:(r + 1) * Hl])
+        if full.D is not None:
+            loc.D.copy_(full.D[r * Hl:(r + 1) * Hl])
+    loc.tp_group = group
+    if c.num_q_heads % tp == 0 and c.num_k_heads % tp:
+        raise ValueError("head-parallel M2RNN: a replicated k segment behind a split q segment is not supported")
+    loc.tp_replicated = tuple(n for n, heads in (("q", c.num_q_heads), ("k", c.num_k_heads), ("w", nw)) if heads % tp)
+    loc.tp_replicated_rows = sum(heads * K for heads in (c.num_q_heads, c.num_k_heads) if heads % tp)   # leading rows of in_proj
+    loc.train(full.training)
+    return loc
+
+
+def tensor_parallelize_mixers(model: nn.Module, group, *, kinds=("mla", "moe", "m2rnn")) -> dict[str, int]:
+    """Replace the attention (low-rank MLA), MoE and M2RNN mixers under ``model`` by their head- / expert-parallel forms (in place);
+    returns how many of each were replaced.  Inputs and outputs of every mixer stay replicated over the group (the partial output
+    products are all-reduced), so it composes with ``tensor_parallelize_ffn`` and leaves other mixers untouched: Mamba3 blocks
+    stay replicated — their B / C rotation takes its phase from the first ``ngroups`` heads of the layer, which would have to be
+    shipped to every rank."""
+    from ..nn.m2rnn import M2RNNMixer
+    from ..nn.mla import MLAAttention
+    from ..nn.moe import MoE
+    done = {"mla": 0, "moe": 0, "m2rnn": 0}
+    if _world(group) == 1:
+        return done
+    for parent in list(model.modules()):
+        for name, child in list(parent.named_children()):
+            if isinstance(child, MLAAttention) and "mla" in kinds and child.tp_group is None:
+                setattr(parent, name, _shard_mla(child, group))
+                done["mla"] += 1
+            elif isinstance(child, MoE) and "moe" in kinds and child.tp_group is None and child.ep_size == 1:
+                setattr(parent, name, _shard_moe(child, group))
+                done["moe"] += 1
+            elif isinstance(child, M2RNNMixer) and "m2rnn" in kinds and child.tp_group is None:
+                setattr(parent, name, _shard_m2rnn(child, group))
+                done["m2rnn"] += 1
+    return done

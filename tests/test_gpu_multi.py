@@ -60,6 +60,12 @@ def test_fused_tp_pairs_match_nccl_two_gpus():
     assert out["rel_err_vs_fp32_single_gpu"] < 3e-2, out
 
 
+def test_fused_tp_all_reduce_ffn_matches_nccl_two_gpus():
+    """The replicated-activation FFN (what ``bench.py --tp 2 --tp-fused`` runs): fused GEMM → reduce-scatter + gather vs NCCL all-reduce."""
+    out = _selftest("tpar", extra_env={"CMB_TP_SMALL": "1"})
+    assert all(e < 3e-2 for e in out["rel_err_vs_nccl[y,dx,dw_up,dw_down]"]), out
+
+
 def test_fused_ep_dispatch_combine_matches_all_to_all_two_gpus():
     out = _selftest("ep", extra_env={"CMB_EP_SMALL": "1"})
     assert all(e < 5e-2 for e in out["rel_err_vs_nccl[y,dx,dw_gate_up,dw_down,dw_router]"]), out

@@ -69,6 +69,61 @@ def test_tensor_parallel_ffn_matches_single_rank(sp):
     assert all(run_ranks(_tp_rank, 2, sp))
 
 
+def _tp_mixers_rank(rank, world):
+    """A stack with every mixer kind (M, A, E, R) plus dense FFNs: head- / expert-parallel mixers and column/row-parallel FFNs on two
+    ranks reproduce the single-process forward, the input gradient and the (sliced or replicated) parameter gradients."""
+    from cppmega_mlx_b200.models.hybrid_lm import HybridTinyConfig, HybridTinyLM
+    from cppmega_mlx_b200.parallel import tp as TP
+    st = PS.init_parallel_state(tp=world)
+    cfg = HybridTinyConfig(vocab_size=64, hidden_size=32, pattern="MAER", depth=4, num_attention_heads=4, max_seq_length=16, mamba_head_dim=16,
+                           mamba_state_dim=8, mamba_chunk_size=8, mamba_groups=2, moe_num_experts=4, moe_top_k=2, moe_expert_hidden_size=16,
+                           moe_shared_expert_hidden_size=16, m2rnn_k_head_dim=4, m2rnn_v_head_dim=4, m2rnn_num_q_heads=1, m2rnn_num_k_heads=2,
+                           m2rnn_num_v_heads=4, m2rnn_num_f_heads=4, m2rnn_num_g_heads=4, mla_low_rank=True, mla_q_lora_rank=16,
+                           mla_kv_lora_rank=16, mla_qk_nope_head_dim=8, mla_qk_rope_head_dim=4, mla_v_head_dim=8, ffn_hidden_size=48,
+                           position_embedding=False)
+    torch.manual_seed(0)
+    full = HybridTinyLM(cfg)
+    with torch.no_grad():
+        for p in full.parameters():
+            if p.dim() == 2 and float(p.abs().sum()) == 0:
+                p.normal_(std=0.05)             # zero-initialised output projections would hide the mixers
+    ids = torch.randint(0, 64, (2, 12))
+    ref = full(ids)
+    ref.square().mean().backward()
+    ref_g = {n: p.grad.clone() for n, p in full.named_parameters() if p.grad is not None}
+    full.zero_grad()
+    tpm = HybridTinyLM(cfg)
+    tpm.load_state_dict(full.state_dict())
+    done = TP.tensor_parallelize_mixers(tpm, st.tp_group)
+    assert done == {"mla": 1, "moe": 1, "m2rnn": 1}, done
+    assert TP.tensor_parallelize_ffn(tpm, st.tp_group) >= 3          # the dense FFNs (and the MoE layer's shared expert)
+    out = tpm(ids)
+    assert torch.allclose(out, ref.detach(), atol=2e-5), float((out - ref).abs().max())
+    out.square().mean().backward()
+    g = {n: p.grad for n, p in tpm.named_parameters() if p.grad is not None}
+    H, r = 4, rank
+    checks = 0
+    for n, want in ref_g.items():
+        if n in g and g[n].shape == want.shape:                    # replicated parameters: identical full gradients on every rank
+            assert torch.allclose(g[n], want, atol=3e-5), (n, float((g[n] - want).abs().max()))
+            checks += 1
+    a = "layers.1.block."
+    assert torch.allclose(g[a + "wo.weight"], ref_g[a + "wo.weight"][:, r * 16:(r + 1) * 16], atol=3e-5)
+    assert torch.allclose(g[a + "wq_b.weight"], ref_g[a + "wq_b.weight"][r * 24:(r + 1) * 24], atol=3e-5)
+    e = "layers.2.block.experts."
+    assert torch.allclose(g[e + "w_down"], ref_g[e + "w_down"][r * 2:(r + 1) * 2], atol=3e-5)
+    m = "layers.3.block."
+    assert torch.allclose(g[m + "out_proj.weight"], ref_g[m + "out_proj.weight"][:, r * 8:(r + 1) * 8], atol=3e-5)
+    assert torch.allclose(g[m + "state_weight"], ref_g[m + "state_weight"], atol=3e-5)          # one shared matrix: replicated, gradient summed
+    assert torch.allclose(g[m + "A_log"], ref_g[m + "A_log"][r * 2:(r + 1) * 2], atol=3e-5)
+    assert checks > 10
+    return True
+
+
+def test_tensor_parallel_mixers_match_single_rank():
+    assert all(run_ranks(_tp_mixers_rank, 2))
+
+
 def _ep_rank(rank, world):
     from cppmega_mlx_b200.nn.moe import MoE, MoEConfig
     from cppmega_mlx_b200.parallel import ep as EP
