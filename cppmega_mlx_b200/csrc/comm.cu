@@ -1,5 +1,5 @@
 // Kernels that talk to peer GPUs through symmetric memory over NVLink / NVSwitch (plain peer loads and stores
-// by default; `multimem` only where a multicast address is passed in).  Every rank maps every peer's
+// only; no `multimem` form is built).  Every rank maps every peer's
 // buffers, so `bufs[r]` below is rank r's copy of the same logical buffer.
 //
 //  * cmb_comm_barrier        epoch-flag barrier: release-store my epoch into every peer's pad, acquire-poll my pad.
@@ -185,6 +185,151 @@ __global__ void __launch_bounds__(256) zero1_push_update_kernel(PeerPtrs params,
   }
 }
 
+// ---------------------------------------------------------------------------------------------- bucketed, overlappable forms
+// A bucket is a set of tensors whose gradients become final together (one layer).  As soon as a rank's backward pass has
+// produced them it raises its flag for the bucket in every peer's flag block; the owner's kernel for that bucket waits
+// (bounded) until all W flags show the current step, then reduces the peers' gradients of the ranges it owns, updates and —
+// for AdamW ranges — pushes the new parameters to every rank, all while the backward pass of the earlier layers is still
+// running on the main stream.  No rank reads a bucket's weights again in the same backward pass once its flag is up, so the
+// early parameter push is safe.  `ranges` is a device table; a launch covers all ranges of one bucket.
+struct Z1Range {
+  long long off;          // element offset inside the flat buffers (multiple of 8)
+  long long n;            // elements
+  float* s0;              // AdamW m / Muon momentum
+  float* s1;              // AdamW v
+  __nv_bfloat16* u;       // Muon: Newton–Schulz input (reduce) / orthogonalised update (push)
+  float* sumsq;           // Muon: Σu² slot
+  float coef;             // push: learning-rate factor
+  int pad;
+};
+
+// All threads of the block return the same verdict. flags = my flag block + bucket·COMM_MAX_RANKS.
+__device__ __forceinline__ bool wait_bucket_flags(const int* flags, int world, int epoch, long long spin_limit, int* status, int rank, int bucket) {
+  bool ok = true;
+  if (flags != nullptr && threadIdx.x < world) {
+    ok = false;
+    for (long long i = 0; i < spin_limit; ++i) {
+      if (ld_acquire_sys(flags + threadIdx.x) >= epoch) {
+        ok = true;
+        break;
+      }
+      __nanosleep(128);
+    }
+    if (!ok && status != nullptr && atomicCAS(status, 0, ST_TIMEOUT_PEER_FLAG) == 0) {
+      status[1] = rank;
+      status[2] = threadIdx.x;
+      status[3] = (bucket << 20) | (epoch & 0xfffff);
+    }
+    __threadfence_system();
+  }
+  return __syncthreads_and(ok);
+}
+
+__global__ void zero1_bucket_signal_kernel(PeerPtrs pads, int rank, int world, int bucket, int epoch) {
+  const int t = threadIdx.x;
+  if (t < world) {
+    __threadfence_system();       // this rank's gradient stores of the bucket (ordered before this launch on the stream) are visible first
+    st_release_sys(static_cast<int*>(pads.p[t]) + bucket * COMM_MAX_RANKS + rank, epoch);
+  }
+}
+
+__global__ void __launch_bounds__(256) zero1_adamw_ranges_kernel(PeerPtrs grads, PeerPtrs params, int rank, int world, const Z1Range* __restrict__ ranges,
+                                                                  int nranges, float lr, float b1, float b2, float eps, float wd, float c1, float c2,
+                                                                  float inv_world, const int* flags, int bucket, int epoch, long long spin_limit,
+                                                                  int* status) {
+  if (!wait_bucket_flags(flags, world, epoch, spin_limit, status, rank, bucket)) return;
+  const __nv_bfloat16* myp = static_cast<const __nv_bfloat16*>(params.p[rank]);
+  for (int ri = 0; ri < nranges; ++ri) {
+    const Z1Range rg = ranges[ri];
+    const long long nvec = rg.n >> 3;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const long long e = rg.off + 8 * i;
+      float g[8], p[8];
+      reduce8(grads, world, e, inv_world, g);
+      unpack8(*reinterpret_cast<const uint4*>(myp + e), p);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const long long j = 8 * i + k;
+        const float mi = b1 * rg.s0[j] + (1.f - b1) * g[k];
+        const float vi = b2 * rg.s1[j] + (1.f - b2) * g[k] * g[k];
+        rg.s0[j] = mi;
+        rg.s1[j] = vi;
+        p[k] = p[k] * (1.f - lr * wd) - lr * c1 * mi / (sqrtf(vi) * c2 + eps);
+      }
+      const uint4 out = pack8(p);
+      for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + e) = out;
+    }
+    for (long long j = (nvec << 3) + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; j < rg.n; j += static_cast<long long>(gridDim.x) * blockDim.x) {
+      float g = 0.f;
+      for (int r = 0; r < world; ++r) g += __bfloat162float(static_cast<const __nv_bfloat16*>(grads.p[r])[rg.off + j]);
+      g *= inv_world;
+      const float mi = b1 * rg.s0[j] + (1.f - b1) * g;
+      const float vi = b2 * rg.s1[j] + (1.f - b2) * g * g;
+      rg.s0[j] = mi;
+      rg.s1[j] = vi;
+      const __nv_bfloat16 o = __float2bfloat16(__bfloat162float(myp[rg.off + j]) * (1.f - lr * wd) - lr * c1 * mi / (sqrtf(vi) * c2 + eps));
+      for (int r = 0; r < world; ++r) static_cast<__nv_bfloat16*>(params.p[r])[rg.off + j] = o;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) zero1_muon_reduce_ranges_kernel(PeerPtrs grads, PeerPtrs params, int rank, int world,
+                                                                        const Z1Range* __restrict__ ranges, int nranges, float mu, float wd, int nesterov,
+                                                                        float inv_world, const int* flags, int bucket, int epoch, long long spin_limit,
+                                                                        int* status) {
+  __shared__ float red[8];
+  if (!wait_bucket_flags(flags, world, epoch, spin_limit, status, rank, bucket)) return;
+  const __nv_bfloat16* myp = static_cast<const __nv_bfloat16*>(params.p[rank]);
+  for (int ri = 0; ri < nranges; ++ri) {
+    const Z1Range rg = ranges[ri];
+    const long long nvec = rg.n >> 3;
+    float acc = 0.f;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const long long e = rg.off + 8 * i;
+      float g[8], p[8], o[8];
+      reduce8(grads, world, e, inv_world, g);
+      unpack8(*reinterpret_cast<const uint4*>(myp + e), p);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const long long j = 8 * i + k;
+        const float gi = g[k] + wd * p[k];
+        const float vi = mu * rg.s0[j] + (1.f - mu) * gi;
+        rg.s0[j] = vi;
+        o[k] = nesterov ? gi * (1.f - mu) + vi * mu : vi;
+        acc += o[k] * o[k];
+      }
+      *reinterpret_cast<uint4*>(rg.u + 8 * i) = pack8(o);
+    }
+    acc = warp_sum(acc);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < 8; ++w) t += red[w];
+      atomicAdd(rg.sumsq, t);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) zero1_push_ranges_kernel(PeerPtrs params, int rank, int world, const Z1Range* __restrict__ ranges, int nranges) {
+  const __nv_bfloat16* myp = static_cast<const __nv_bfloat16*>(params.p[rank]);
+  for (int ri = 0; ri < nranges; ++ri) {
+    const Z1Range rg = ranges[ri];
+    const long long nvec = rg.n >> 3;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const long long e = rg.off + 8 * i;
+      float p[8], d[8];
+      unpack8(*reinterpret_cast<const uint4*>(myp + e), p);
+      unpack8(*reinterpret_cast<const uint4*>(rg.u + 8 * i), d);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) p[k] -= rg.coef * d[k];
+      const uint4 out = pack8(p);
+      for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + e) = out;
+    }
+  }
+}
+
 static inline int comm_grid(long long nvec) {
   long long b = (nvec + 255) / 256;
   const long long cap = 148LL * 4;
@@ -235,5 +380,61 @@ extern "C" int cmb_zero1_push_update(const long long* param_ptrs, int rank, int 
   if (n <= 0) return 0;
   cmb::zero1_push_update_kernel<<<cmb::comm_grid(n / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       p, rank, world, off, n, static_cast<const __nv_bfloat16*>(u), coef);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// ---- bucketed forms. `ranges`: device array of {off, n (int64), s0, s1, u, sumsq (pointers), coef (fp32), pad} (56 bytes → 56, 8-byte aligned);
+// `flag_ptrs[r]`: rank r's int32[nbuckets · 16] flag block; a negative `bucket` skips the flag wait (the caller has synchronised already).
+extern "C" int cmb_zero1_bucket_signal(const long long* flag_ptrs, int rank, int world, int bucket, int epoch, void* stream) {
+  cmb::PeerPtrs pads;
+  if (!cmb::fill(pads, flag_ptrs, world) || bucket < 0) return 1;
+  cmb::zero1_bucket_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pads, rank, world, bucket, epoch);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_zero1_adamw_ranges(const long long* grad_ptrs, const long long* param_ptrs, const long long* flag_ptrs, int rank, int world,
+                                      const void* ranges, int nranges, long long total_elems, const float* f, int bucket, int epoch,
+                                      long long spin_limit, int* status, int max_blocks, void* stream) {
+  cmb::PeerPtrs g, p, fl;
+  if (!cmb::fill(g, grad_ptrs, world) || !cmb::fill(p, param_ptrs, world)) return 1;
+  if (nranges <= 0) return 0;
+  const int* flags = nullptr;
+  if (bucket >= 0) {
+    if (!cmb::fill(fl, flag_ptrs, world)) return 1;
+    flags = static_cast<const int*>(fl.p[rank]) + bucket * cmb::COMM_MAX_RANKS;
+  }
+  int grid = cmb::comm_grid((total_elems + 7) / 8);
+  if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
+  cmb::zero1_adamw_ranges_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      g, p, rank, world, static_cast<const cmb::Z1Range*>(ranges), nranges, f[0], f[1], f[2], f[3], f[4], f[5], f[6], 1.f / world, flags, bucket, epoch,
+      spin_limit, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_zero1_muon_reduce_ranges(const long long* grad_ptrs, const long long* param_ptrs, const long long* flag_ptrs, int rank, int world,
+                                            const void* ranges, int nranges, long long total_elems, float mu, float wd, int nesterov, int bucket,
+                                            int epoch, long long spin_limit, int* status, int max_blocks, void* stream) {
+  cmb::PeerPtrs g, p, fl;
+  if (!cmb::fill(g, grad_ptrs, world) || !cmb::fill(p, param_ptrs, world)) return 1;
+  if (nranges <= 0) return 0;
+  const int* flags = nullptr;
+  if (bucket >= 0) {
+    if (!cmb::fill(fl, flag_ptrs, world)) return 1;
+    flags = static_cast<const int*>(fl.p[rank]) + bucket * cmb::COMM_MAX_RANKS;
+  }
+  int grid = cmb::comm_grid(total_elems / 8);
+  if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
+  cmb::zero1_muon_reduce_ranges_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      g, p, rank, world, static_cast<const cmb::Z1Range*>(ranges), nranges, mu, wd, nesterov, 1.f / world, flags, bucket, epoch, spin_limit, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_zero1_push_ranges(const long long* param_ptrs, int rank, int world, const void* ranges, int nranges, long long total_elems,
+                                     void* stream) {
+  cmb::PeerPtrs p;
+  if (!cmb::fill(p, param_ptrs, world)) return 1;
+  if (nranges <= 0) return 0;
+  cmb::zero1_push_ranges_kernel<<<cmb::comm_grid(total_elems / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      p, rank, world, static_cast<const cmb::Z1Range*>(ranges), nranges);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }

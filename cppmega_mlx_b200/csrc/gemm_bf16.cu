@@ -702,7 +702,7 @@ extern "C" int cmb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   return cmb_host::dispatch(g, a_mn_major, b_mn_major);
 }
 
-// Batched form. `ip` = {M, N, K, a_mn, b_mn, flags, a_div2, b_div2, max_ctas, mask_words, b_groups}; `lp` = {lda, ldb, ldc, nb2,
+// Batched form. `ip` = {M, N, K, a_mn, b_mn, flags, a_div2, b_div2, max_ctas, mask_words, b_groups, number of `pp` entries}; `lp` = {lda, ldb, ldc, nb2,
 // nb3, nb4, sA2, sA3, sA4, sB2, sB3, sB4, sC2, sC3, sC4, sv2, sv3, sv4, mask_sb} (element counts / strides).
 // `pp` = {row_vec, col_vec, aux, mask, stats, tile_group, k_ranges, m_limit} device pointers (any may be null). Flags select the
 // epilogue, see the enum at the top of this file. Grouped (MoE) use: `tile_group[i]` names B's dim-2 slice for the i-th
@@ -722,7 +722,7 @@ extern "C" int cmb_gemm_bf16_batched(const void* A, const void* B, void* C, cons
   g.row_vec = static_cast<const float*>(pp[0]); g.col_vec = static_cast<const float*>(pp[1]);
   g.aux = pp[2]; g.mask = static_cast<const unsigned*>(pp[3]); g.stats = static_cast<float*>(const_cast<void*>(pp[4]));
   g.tile_group = static_cast<const int*>(pp[5]); g.k_ranges = static_cast<const int*>(pp[6]);
-  g.m_limit = static_cast<const int*>(pp[7]);
+  g.m_limit = ip[11] >= 8 ? static_cast<const int*>(pp[7]) : nullptr;   // ip[11]: how many entries `pp` holds (older callers pass 7)
   g.b_groups = ip[10];
   if (g.tile_group != nullptr && g.b_groups <= 0) return 109;
   g.scale = scale;

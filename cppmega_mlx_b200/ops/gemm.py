@@ -95,9 +95,9 @@ def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, 
     fl = flags | (OUT_F32 if f32 else 0) | (ACCUMULATE if accumulate else 0)
     if row_vec is not None and not (flags & (EPI_EXP_MASK | EPI_DS)):
         fl |= EPI_DECAY_MASK if col_vec is not None else EPI_ROW_EXP
-    ip = (ctypes.c_int * 11)(M, N, K, int(a_mn), int(b_mn), fl, a_div2, b_div2, max_ctas, mask_words, int(b_groups))
+    ip = (ctypes.c_int * 12)(M, N, K, int(a_mn), int(b_mn), fl, a_div2, b_div2, max_ctas, mask_words, int(b_groups), 8)
     lp = (ctypes.c_longlong * 19)(lda, ldb, ldc, *nb, *sA, *sB, *sC, *sv, mask_sb)
-    pp = (ctypes.c_void_p * 7)(*(None if t is None else t.data_ptr() for t in (row_vec, col_vec, aux, mask, stats, tile_group, k_ranges)))
+    pp = (ctypes.c_void_p * 8)(*(None if t is None else t.data_ptr() for t in (row_vec, col_vec, aux, mask, stats, tile_group, k_ranges, m_limit)))
     st = B.status_buffer(a.device)
     rc = lib.cmb_gemm_bf16_batched(B.ptr(a), B.ptr(b), B.ptr(out), ip, lp, pp, ctypes.c_float(scale), ctypes.c_float(scale2), B.ptr(st),
                                    B.stream_ptr())
