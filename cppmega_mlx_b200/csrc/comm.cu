@@ -199,7 +199,7 @@ struct Z1Range {
   float* s1;              // AdamW v
   __nv_bfloat16* u;       // Muon: Newton–Schulz input (reduce) / orthogonalised update (push)
   float* sumsq;           // Muon: Σu² slot
-  float coef;             // push: learning-rate factor
+  float coef;             // push: shape factor of the learning rate
   int pad;
 };
 
@@ -312,7 +312,8 @@ __global__ void __launch_bounds__(256) zero1_muon_reduce_ranges_kernel(PeerPtrs 
   }
 }
 
-__global__ void __launch_bounds__(256) zero1_push_ranges_kernel(PeerPtrs params, int rank, int world, const Z1Range* __restrict__ ranges, int nranges) {
+__global__ void __launch_bounds__(256) zero1_push_ranges_kernel(PeerPtrs params, int rank, int world, const Z1Range* __restrict__ ranges, int nranges,
+                                                                 float lr) {
   const __nv_bfloat16* myp = static_cast<const __nv_bfloat16*>(params.p[rank]);
   for (int ri = 0; ri < nranges; ++ri) {
     const Z1Range rg = ranges[ri];
@@ -323,7 +324,7 @@ __global__ void __launch_bounds__(256) zero1_push_ranges_kernel(PeerPtrs params,
       unpack8(*reinterpret_cast<const uint4*>(myp + e), p);
       unpack8(*reinterpret_cast<const uint4*>(rg.u + 8 * i), d);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) p[k] -= rg.coef * d[k];
+      for (int k = 0; k < 8; ++k) p[k] -= lr * rg.coef * d[k];
       const uint4 out = pack8(p);
       for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + e) = out;
     }
@@ -430,11 +431,11 @@ extern "C" int cmb_zero1_muon_reduce_ranges(const long long* grad_ptrs, const lo
 }
 
 extern "C" int cmb_zero1_push_ranges(const long long* param_ptrs, int rank, int world, const void* ranges, int nranges, long long total_elems,
-                                     void* stream) {
+                                     float lr, void* stream) {
   cmb::PeerPtrs p;
   if (!cmb::fill(p, param_ptrs, world)) return 1;
   if (nranges <= 0) return 0;
   cmb::zero1_push_ranges_kernel<<<cmb::comm_grid(total_elems / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      p, rank, world, static_cast<const cmb::Z1Range*>(ranges), nranges);
+      p, rank, world, static_cast<const cmb::Z1Range*>(ranges), nranges, lr);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }

@@ -121,6 +121,10 @@ class PretrainingStep:
             b = b.to(self.device, non_blocking=True)
         self.model.train()
         out = self.loss_fn(self.model, b)
+        if (self.state.micro_step + 1) % self.grad_accum_steps == 0 and self.max_grad_norm is None:
+            arm = getattr(self.optimizer, "arm_overlap", None)      # sharded optimizers start reducing a layer once its gradients are final
+            if arm is not None:
+                arm()
         (out.loss / self.grad_accum_steps).backward()
         self.state.micro_step += 1
         boundary = self.state.micro_step % self.grad_accum_steps == 0

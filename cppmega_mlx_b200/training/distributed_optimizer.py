@@ -175,6 +175,13 @@ class DistributedZeRO1Optimizer:
                     f.segment_view(f.params, r).copy_(t)
 
     # -- step ------------------------------------------------------------------------------------
+    def arm_overlap(self) -> None:
+        """Tell the fused path that the backward pass about to run is the last one before ``step()``: each layer's reduction and
+        update may then start as soon as that layer's gradients are complete.  Do not call it when the gradients are still to be
+        modified between backward and ``step()`` (clipping, scaling)."""
+        if self._fused is not None:
+            self._fused.arm_overlap()
+
     @torch.no_grad()
     def step(self) -> None:
         self.step_count += 1
@@ -270,6 +277,9 @@ class ExpertParallelZeRO1Optimizer:
         self.dense.zero_grad()
         if self.experts is not None:
             self.experts.zero_grad()
+
+    def arm_overlap(self) -> None:
+        self.dense.arm_overlap()
 
     @torch.no_grad()
     def step(self) -> None:
