@@ -192,13 +192,14 @@ __global__ void __launch_bounds__(256) zero1_push_update_kernel(PeerPtrs params,
 // for AdamW ranges — pushes the new parameters to every rank, all while the backward pass of the earlier layers is still
 // running on the main stream.  No rank reads a bucket's weights again in the same backward pass once its flag is up, so the
 // early parameter push is safe.  `ranges` is a device table; a launch covers all ranges of one bucket.
+constexpr int Z1_PARTS = 148 * 4;      // the grid cap of the range kernels (comm_grid)
 struct Z1Range {
   long long off;          // element offset inside the flat buffers (multiple of 8)
   long long n;            // elements
   float* s0;              // AdamW m / Muon momentum
   float* s1;              // AdamW v
   __nv_bfloat16* u;       // Muon: Newton–Schulz input (reduce) / orthogonalised update (push)
-  float* sumsq;           // Muon: Σu² slot
+  float* sumsq;           // Muon: this tensor's row of Z1_PARTS per-block partial sums of u² (block b writes slot b)
   float coef;             // push: shape factor of the learning rate
   int pad;
 };
@@ -307,8 +308,27 @@ __global__ void __launch_bounds__(256) zero1_muon_reduce_ranges_kernel(PeerPtrs 
     if (threadIdx.x == 0) {
       float t = 0.f;
       for (int w = 0; w < 8; ++w) t += red[w];
-      atomicAdd(rg.sumsq, t);
+      rg.sumsq[blockIdx.x] = t;      // no atomics: the finalize kernel adds the row in a fixed order, so a step is reproducible bit for bit
     }
+  }
+}
+
+// sumsq[t] = Σ_b partials[t][b] in a fixed order, and the row is cleared for the next step.  One block per tensor.
+__global__ void __launch_bounds__(256) zero1_sumsq_finalize_kernel(float* __restrict__ partials, float* __restrict__ sumsq) {
+  __shared__ float red[8];
+  float* row = partials + static_cast<long long>(blockIdx.x) * Z1_PARTS;
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < Z1_PARTS; i += 256) {
+    acc += row[i];
+    row[i] = 0.f;
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < 8; ++w) t += red[w];
+    sumsq[blockIdx.x] = t;
   }
 }
 
@@ -333,7 +353,7 @@ __global__ void __launch_bounds__(256) zero1_push_ranges_kernel(PeerPtrs params,
 
 static inline int comm_grid(long long nvec) {
   long long b = (nvec + 255) / 256;
-  const long long cap = 148LL * 4;
+  const long long cap = Z1_PARTS;
   return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
 }
 static inline bool fill(PeerPtrs& out, const long long* ptrs, int world) {
@@ -427,6 +447,12 @@ extern "C" int cmb_zero1_muon_reduce_ranges(const long long* grad_ptrs, const lo
   if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
   cmb::zero1_muon_reduce_ranges_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       g, p, rank, world, static_cast<const cmb::Z1Range*>(ranges), nranges, mu, wd, nesterov, 1.f / world, flags, bucket, epoch, spin_limit, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_zero1_sumsq_finalize(float* partials, float* sumsq, int ntensors, void* stream) {
+  if (ntensors <= 0) return 0;
+  cmb::zero1_sumsq_finalize_kernel<<<ntensors, 256, 0, static_cast<cudaStream_t>(stream)>>>(partials, sumsq);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

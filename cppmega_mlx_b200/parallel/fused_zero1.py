@@ -14,8 +14,11 @@ parameter pushes, and the Muon momentum stage therefore run while the main strea
 layers: once every rank has raised a bucket's flag no rank reads that bucket's weights again before the step ends, so pushing
 new parameters early is safe.  After backward only the Newton–Schulz chains, the Muon pushes and whatever bucket was not
 complete remain, closed by one epoch barrier ("all parameters delivered, all gradients consumed").  The hooks act only when the
-training step has armed them for its last micro-batch (``arm_overlap``); otherwise every bucket is launched from ``step()``,
-which is the same code path without the overlap.
+training step has armed them for its last micro-batch (``arm_overlap``) and ``CPPMEGA_ZERO1_OVERLAP=1`` is set; otherwise
+every bucket is launched from ``step()``, which is the same code path without the overlap.  The overlap is off by default: over
+NVLink the whole exchange of a 1.76 B-parameter model costs 2.6 ms per step on two B200s when it runs after backward
+(331.2 ms against 328.2 ms with no communication at all), and running the memory-bound update kernels beside the backward GEMMs
+slowed those by as much as it hid (333.4 ms).  It is there for fabrics or models where the exchange is not that cheap.
 
 Per step and rank this moves (W−1)/W of the owned segment over NVLink in each direction.
 """
@@ -35,7 +38,13 @@ F32 = ctypes.c_float
 MAX_RANKS = 16
 _RANGE = [("off", "<i8"), ("n", "<i8"), ("s0", "<u8"), ("s1", "<u8"), ("u", "<u8"), ("sumsq", "<u8"), ("coef", "<f4"), ("pad", "<i4")]
 _LAYER = re.compile(r"(?:^|\.)layers\.(\d+)\.")
-REDUCER_BLOCKS = 64       # grid cap of a bucket kernel launched during backward (leaves the SMs to the backward GEMMs)
+Z1_PARTS = 148 * 4         # per-block partial sums of u² per Muon tensor (the range kernels' grid cap)
+
+
+def _reducer_blocks() -> int:
+    """Grid cap of a bucket kernel launched during backward (0 = the full grid).  A small cap leaves the SMs to the backward GEMMs
+    but lets the side stream fall behind: on two B200s 16 blocks cost 29 ms per step and 64 blocks 8 ms against the full grid."""
+    return int(os.environ.get("CPPMEGA_ZERO1_REDUCER_BLOCKS", "0"))
 
 
 def _table(rows: list[dict], device) -> torch.Tensor | None:
@@ -69,7 +78,7 @@ class FusedZeRO1Comm:
         self.bufs: list[SymmetricBuffer] = []
         self.barrier: EpochBarrier | None = None
         self.enabled = True
-        self.overlap = os.environ.get("CPPMEGA_ZERO1_OVERLAP", "1") != "0"
+        self.overlap = os.environ.get("CPPMEGA_ZERO1_OVERLAP", "0") == "1"
         self.armed = False
         self.epoch = 0
         self.buckets: list[_Bucket] | None = None
@@ -131,7 +140,9 @@ class FusedZeRO1Comm:
                 (fast if p.shape[0] % 8 == 0 and p.shape[1] % 8 == 0 else self.slow_muon).append((n, p))
         self.plan = MuonBatchPlan(dev)
         self.fast = fast
-        self.sumsq = torch.zeros(max(1, len(fast) + len(self.slow_muon)), dtype=torch.float32, device=dev)
+        self.n_muon = len(fast) + len(self.slow_muon)
+        self.sumsq = torch.zeros(max(1, self.n_muon), dtype=torch.float32, device=dev)
+        self.parts = torch.zeros(max(1, self.n_muon) * Z1_PARTS, dtype=torch.float32, device=dev)   # written by block index, summed in fixed order
         self.stacks = []
         u_of, self.res_of = {}, {}
         steps = muon.ns_steps if muon is not None else 0
@@ -145,13 +156,13 @@ class FusedZeRO1Comm:
         for k_, (n, p) in enumerate(self.slow_muon):     # reduced with the bucket like the others; orthogonalised by PyTorch ops in step()
             owner, off, cnt = flat.slots[n]
             bucket_of[n].muon.append(dict(off=owner * flat.segment + off, n=cnt, s0=muon.state_for(n, p)["v"].data_ptr(),
-                                          u=self.slow_u[k_].data_ptr(), sumsq=self.sumsq.data_ptr() + 4 * (len(fast) + k_)))
+                                          u=self.slow_u[k_].data_ptr(), sumsq=self.parts.data_ptr() + 4 * Z1_PARTS * (len(fast) + k_)))
         norm_rows = []
         for i, (n, p) in enumerate(fast):
             owner, off, cnt = flat.slots[n]
             st = muon.state_for(n, p)
             bucket_of[n].muon.append(dict(off=owner * flat.segment + off, n=cnt, s0=st["v"].data_ptr(), u=u_of[i].data_ptr(),
-                                          sumsq=self.sumsq.data_ptr() + 4 * i))
+                                          sumsq=self.parts.data_ptr() + 4 * Z1_PARTS * i))
             norm_rows.append(dict(u=u_of[i].data_ptr(), sumsq=self.sumsq.data_ptr() + 4 * i, numel=cnt))
         self.norm_tab = TensorTable(dev).update(norm_rows) if norm_rows else None
         for n, p in adamw.params:
@@ -219,7 +230,7 @@ class FusedZeRO1Comm:
         main = torch.cuda.current_stream(dev)
         self.sig_stream.wait_event(main.record_event())                    # the bucket's gradients are final on the main stream
         status = B.ptr(B.status_buffer(dev))
-        cap = REDUCER_BLOCKS if during_backward else 0
+        cap = _reducer_blocks() if during_backward else 0
         with torch.cuda.stream(self.sig_stream):
             B.check(lib.cmb_zero1_bucket_signal(fp, rank, W, b.idx, epoch, B.stream_ptr()), "zero1_bucket_signal")
             raised = self.sig_stream.record_event()
@@ -263,6 +274,7 @@ class FusedZeRO1Comm:
         adamw.step_count += 1
         if muon is not None:
             muon.step_count += 1
+            B.check(lib.cmb_zero1_sumsq_finalize(B.ptr(self.parts), B.ptr(self.sumsq), self.n_muon, B.stream_ptr()), "zero1_sumsq_finalize")
             if self.norm_tab is not None:
                 self.norm_tab.launch(OP_SCALE_INV_NORM, torch.bfloat16, (1e-7,), "scale_inv_norm_multi")
             ready = main.record_event()
@@ -291,7 +303,6 @@ class FusedZeRO1Comm:
                 o = newton_schulz5(self.slow_u[k_], steps=muon.ns_steps, ns_carrier="bf16", output_dtype=torch.bfloat16).contiguous()
                 B.check(lib.cmb_zero1_push_update(pp, rank, W, I64(goff), I64(cnt), B.ptr(o), F32(lr * max(1.0, p.shape[0] / p.shape[1]) ** 0.5),
                                                   B.stream_ptr()), "zero1_push_update")
-            self.sumsq.zero_()                       # Σu² slots start the next step at zero (they are accumulated during its backward)
         self.barrier()  # all parameters delivered everywhere; all gradients consumed
         self._reset_pending()
         return True

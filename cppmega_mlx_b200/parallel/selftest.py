@@ -59,6 +59,8 @@ def case_zero1(rank, world, dev):
     B.check_status()
     diff = (p_n - p_f).abs().max()
     dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+    mean = (p_n - p_f).abs().mean()
+    dist.all_reduce(mean, op=dist.ReduceOp.MAX)
     # every rank must hold identical parameters after the fused step
     ref = p_f.clone()
     dist.broadcast(ref, 0)
@@ -66,7 +68,7 @@ def case_zero1(rank, world, dev):
     dist.all_reduce(spread, op=dist.ReduceOp.MAX)
     if rank == 0:
         print(json.dumps({"case": "zero1", "world": world, "loss_nccl": l_n, "loss_fused": l_f,
-                          "max_param_diff": float(diff), "rank_spread": float(spread)}))
+                          "max_param_diff": float(diff), "mean_param_diff": float(mean), "rank_spread": float(spread)}))
 
 
 def case_zero1det(rank, world, dev):

