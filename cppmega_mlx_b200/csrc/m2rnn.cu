@@ -324,6 +324,77 @@ extern "C" int cmb_m2rnn_bwd(const void* q, const void* k, const void* v, const 
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
+// One-token step for decoding: the state h [B,H,K,V] (fp32) is read, advanced by one token and written back, y = q·h.
+// One CTA per (batch, head); thread (grp, w) owns column w of R = K / (256 / V) consecutive state rows, so W[v][w] is read once
+// per thread (coalesced over w) and the state rows come from shared memory as broadcasts.  No history is kept.
+namespace cmb {
+template <int K, int V>
+__global__ void __launch_bounds__(256) m2rnn_step_kernel(M2Params p) {
+  constexpr int GROUPS = 256 / V, R = K / GROUPS;
+  static_assert(GROUPS >= 1 && R >= 1 && R * GROUPS == K, "row split");
+  __shared__ float hs[K * V];
+  __shared__ float qs[K], ks[K];
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H, tid = threadIdx.x;
+  const int hq = h / (p.H / p.nq), hk = h / (p.H / p.nk), hv = h / (p.H / p.nv), hw = h / (p.H / p.nw), hf = h / (p.H / p.nf);
+  const long long hoff = static_cast<long long>(bh) * K * V;
+  for (int i = tid; i < K * V; i += 256) hs[i] = p.h0 != nullptr ? p.h0[hoff + i] : 0.f;
+  if (tid < K) {
+    qs[tid] = __bfloat162float(p.q[b * p.sq_b + static_cast<long long>(hq) * K + tid]);
+    ks[tid] = __bfloat162float(p.k[b * p.sk_b + static_cast<long long>(hk) * K + tid]);
+  }
+  __syncthreads();
+  const int w = tid % V, r0 = (tid / V) * R;
+  const float* Wh = p.W + static_cast<long long>(hw) * V * V;
+  float acc[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r] = 0.f;
+  for (int v = 0; v < V; ++v) {
+    const float wv = Wh[v * V + w];
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = fmaf(hs[(r0 + r) * V + v], wv, acc[r]);
+  }
+  const float vt = __bfloat162float(p.v[b * p.sv_b + static_cast<long long>(hv) * V + w]);
+  const float ft = p.f[static_cast<long long>(b) * p.nf + hf];
+  float hn[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) hn[r] = ft * hs[(r0 + r) * V + w] + (1.f - ft) * tanhf(acc[r] + ks[r0 + r] * vt);
+  __syncthreads();      // every thread has read the old rows it needs
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    hs[(r0 + r) * V + w] = hn[r];
+    p.h_last[hoff + (r0 + r) * V + w] = hn[r];
+  }
+  __syncthreads();
+  if (tid < V) {
+    float y = 0.f;
+#pragma unroll 8
+    for (int kk = 0; kk < K; ++kk) y = fmaf(qs[kk], hs[kk * V + tid], y);
+    p.y[static_cast<long long>(bh) * V + tid] = __float2bfloat16(y);
+  }
+}
+}  // namespace cmb
+
+// Same argument convention as cmb_m2rnn_fwd with S = 1 (the strides over tokens are unused); covers (K,V) = (32,16), (64,16), (64,128).
+extern "C" int cmb_m2rnn_step(const void* q, const void* k, const void* v, const float* f, const float* W, const float* h0, void* y,
+                              float* h_last, const int* ip, const long long* lp, void* stream) {
+  cmb::M2Params p{};
+  p.q = static_cast<const __nv_bfloat16*>(q); p.k = static_cast<const __nv_bfloat16*>(k); p.v = static_cast<const __nv_bfloat16*>(v);
+  p.f = f; p.W = W; p.h0 = h0; p.y = static_cast<__nv_bfloat16*>(y); p.h_last = h_last;
+  p.B = ip[0]; p.S = ip[1]; p.H = ip[2]; p.nq = ip[5]; p.nk = ip[6]; p.nv = ip[7]; p.nw = ip[8]; p.nf = ip[9];
+  p.sq_b = lp[0]; p.sq_s = lp[1]; p.sk_b = lp[2]; p.sk_s = lp[3]; p.sv_b = lp[4]; p.sv_s = lp[5];
+  if (p.S != 1 || p.B <= 0 || p.H <= 0 || h_last == nullptr || y == nullptr) return -1;
+  for (int n : {p.nq, p.nk, p.nv, p.nw, p.nf})
+    if (n <= 0 || p.H % n) return -1;
+  auto st = static_cast<cudaStream_t>(stream);
+  const int K = ip[3], V = ip[4];
+  if (K == 32 && V == 16) cmb::m2rnn_step_kernel<32, 16><<<p.B * p.H, 256, 0, st>>>(p);
+  else if (K == 64 && V == 16) cmb::m2rnn_step_kernel<64, 16><<<p.B * p.H, 256, 0, st>>>(p);
+  else if (K == 64 && V == 128) cmb::m2rnn_step_kernel<64, 128><<<p.B * p.H, 256, 0, st>>>(p);
+  else return -1;
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
 // Post-recurrence gate of the M2RNN mixer in one pass each way:   out = (y + v·D) · silu(g)
 // y [B,S,H,V] is the recurrence output (dense); v [B,S,nv,V] and g [B,S,ng,V] are strided slices of packed projections whose
 // heads are shared by H/nv (H/ng) consecutive output heads; D [H,V].  Backward returns dy (dense), and per expanded head dv

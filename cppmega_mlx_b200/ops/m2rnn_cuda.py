@@ -161,7 +161,25 @@ class _M2RNNTcFn(torch.autograd.Function):
                 _fold(dW.sum(0), nw, 0).to(w_dtype), _fold(df, nf).to(f_dtype), dh0.to(h0_dtype) if has_h0 else None)
 
 
+def step(q, k, v, W, f, h0):
+    """One token without autograd (decode): ``csrc/m2rnn.cu`` ``m2rnn_step_kernel``; the state stays fp32 end to end."""
+    lib = B.load_library()
+    b, _, _, K = q.shape
+    V = v.shape[3]
+    H, ip, lp = _geom(q, k, v, W, f)
+    Wf, ff = W.float().contiguous(), f.float().contiguous()
+    h0f = None if h0 is None else h0.float().contiguous()
+    y = torch.empty(b, 1, H, V, dtype=torch.bfloat16, device=q.device)
+    h_last = torch.empty(b, H, K, V, dtype=torch.float32, device=q.device)
+    B.check(lib.cmb_m2rnn_step(B.ptr(q), B.ptr(k), B.ptr(v), B.ptr(ff), B.ptr(Wf), B.ptr(h0f), B.ptr(y), B.ptr(h_last), ip, lp, B.stream_ptr()),
+            "m2rnn_step")
+    return y, h_last.to(q.dtype if h0 is None else h0.dtype)
+
+
 def apply(q, k, v, W, f, h0):
+    if (q.shape[1] == 1 and hasattr(B.load_library(), "cmb_m2rnn_step")
+            and not (torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, W, f) + ((h0,) if h0 is not None else ())))):
+        return step(q, k, v, W, f, h0)
     if _is_tc(q, v):
         return _M2RNNTcFn.apply(q, k, v, W, f, h0)
     return _M2RNNFn.apply(q, k, v, W, f, h0)

@@ -6,7 +6,8 @@ gathered, scored (``q·k·scale``), masked, soft-maxed in fp32 and multiplied wi
 channels of the same rows.  Returns the output [B,S,H,d_v] and the log-sum-exp [B,S,H].
 A query whose slots are all ``-1`` yields zeros (and lse = -inf).
 
-Oracle parity: ``cppmega_mlx/nn/sparse_mla.py:125-210``.  CUDA path: ``csrc/sparse_mla.cu``.
+Oracle parity: ``cppmega_mlx/nn/sparse_mla.py:125-210``.  CUDA path: the fused tcgen05 attention kernels of ``csrc/flash_attn.cu``
+(through ``ops/attention.py``) for training and prefill, the gather kernels of ``csrc/decode.cu`` for decode.
 """
 from __future__ import annotations
 

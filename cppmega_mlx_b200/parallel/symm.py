@@ -39,13 +39,6 @@ class SymmetricBuffer:
         self.peer_ptrs = (ctypes.c_longlong * self.world)(*ptrs)
         self.tensor.zero_()
 
-    @property
-    def multicast_ptr(self) -> int:
-        try:
-            return int(self.handle.multicast_ptr)
-        except Exception:  # noqa: BLE001
-            return 0
-
 
 class EpochBarrier:
     def __init__(self, device: torch.device, group=None):

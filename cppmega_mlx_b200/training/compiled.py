@@ -64,9 +64,12 @@ def batch_signature(b: LMTokenBatch) -> tuple:
 class PretrainingStep:
     def __init__(self, model: torch.nn.Module, optimizer, *, loss_fn: Callable[[Any, Any], LossOutput] | None = None,
                  grad_accum_steps: int = 1, compile: bool = False, max_grad_norm: float | None = None,
-                 device: torch.device | str | None = None, sync_metrics: bool = True, post_step: Callable | None = None):
+                 device: torch.device | str | None = None, sync_metrics: bool = True, post_step: Callable | None = None,
+                 nonfinite_policy: str | None = None):
         if grad_accum_steps <= 0:
             raise ValueError("grad_accum_steps must be positive")
+        if nonfinite_policy not in (None, "skip", "raise"):
+            raise ValueError("nonfinite_policy must be None, 'skip' or 'raise'")
         self.model, self.optimizer = model, optimizer
         self.loss_fn = loss_fn or make_loss_fn(backend="cce")
         self.grad_accum_steps = grad_accum_steps
@@ -76,6 +79,12 @@ class PretrainingStep:
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
         self.sync_metrics = sync_metrics
         self.post_step = post_step
+        # What to do when a micro-batch's loss is NaN or infinite (costs one device→host read per micro-batch when set):
+        # "skip" drops the whole accumulation window (no update, gradients cleared, ``skipped_updates`` counted; every
+        # data-parallel rank takes the same decision), "raise" stops the run.  None trusts the loss.
+        self.nonfinite_policy = nonfinite_policy
+        self.skipped_updates = 0
+        self._window_bad = False
         self._signature: tuple | None = None
         self._ev0 = self._ev1 = None
 
@@ -108,6 +117,18 @@ class PretrainingStep:
         elif sig != self._signature:
             raise ValueError(f"batch signature changed: expected {self._signature}, got {sig}")
 
+    def _loss_is_bad(self, loss: torch.Tensor) -> bool:
+        if self.nonfinite_policy is None:
+            return False
+        flag = torch.isfinite(loss.detach()).logical_not().to(torch.int32).reshape(1)
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)          # one rank's bad loss skips the update everywhere
+        bad = bool(int(flag))
+        if bad and self.nonfinite_policy == "raise":
+            raise FloatingPointError(f"non-finite loss at step {self.state.step}, micro-batch {self.state.micro_step}")
+        return bad
+
     def __call__(self, batch) -> PretrainingMetrics:
         b = normalize_batch(batch)
         self._check_signature(b)
@@ -123,13 +144,21 @@ class PretrainingStep:
         out = self.loss_fn(self.model, b)
         if (self.state.micro_step + 1) % self.grad_accum_steps == 0 and self.max_grad_norm is None:
             arm = getattr(self.optimizer, "arm_overlap", None)      # sharded optimizers start reducing a layer once its gradients are final
-            if arm is not None:
+            if arm is not None and self.nonfinite_policy is None:
                 arm()
-        (out.loss / self.grad_accum_steps).backward()
+        bad = self._loss_is_bad(out.loss)
+        if not bad:
+            (out.loss / self.grad_accum_steps).backward()
+        self._window_bad = self._window_bad or bad
         self.state.micro_step += 1
         boundary = self.state.micro_step % self.grad_accum_steps == 0
         gnorm = None
-        if boundary:
+        if boundary and self._window_bad:
+            self._window_bad = False
+            self.skipped_updates += 1
+            self.optimizer.zero_grad()
+            boundary = False
+        elif boundary:
             if self.max_grad_norm is not None:
                 from .optimizers import clip_grad_norm_
                 gnorm = float(clip_grad_norm_([p for p in self.model.parameters()], self.max_grad_norm))

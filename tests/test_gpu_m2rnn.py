@@ -118,3 +118,32 @@ def test_m2rnn_post_gate_kernel_matches_reference(H, nv, ng, V):
     for a, t in zip(got, (y, pack, D)):
         r = t.grad.float()
         assert (a - r).abs().max() <= 3e-2 * r.abs().max() + 3e-2
+
+
+@pytest.mark.parametrize("K,V,nq,nk,nv,nw,nf,with_h0", [(64, 16, 1, 1, 4, 2, 4, True), (32, 16, 2, 2, 2, 1, 2, False), (64, 128, 1, 1, 2, 2, 2, True)])
+def test_m2rnn_one_token_step_kernel(K, V, nq, nk, nv, nw, nf, with_h0):
+    """Decode: a single token without autograd runs the step kernel (no history, no tensor-memory setup) and matches the recurrence."""
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops.m2rnn_scan import m2rnn_scan, m2rnn_scan_reference
+    torch.manual_seed(1)
+    dev, b = "cuda", 3
+    packed = (torch.randn(b, 1, nq * K + nk * K + nv * V, device=dev) * 0.5).bfloat16()
+    q = packed[..., :nq * K].view(b, 1, nq, K)
+    k = packed[..., nq * K:(nq + nk) * K].view(b, 1, nk, K)
+    v = packed[..., (nq + nk) * K:].view(b, 1, nv, V)
+    W = (torch.randn(nw, V, V, device=dev) * (0.2 if V == 16 else 0.05)).bfloat16()
+    f = torch.rand(b, 1, nf, device=dev).mul(0.5).add(0.4).bfloat16()
+    H = max(nq, nk, nv, nw, nf)
+    h0 = (torch.randn(b, H, K, V, device=dev) * 0.3).float() if with_h0 else None
+    n0 = B.launch_count("m2rnn_step")
+    with torch.no_grad():
+        y, h = m2rnn_scan(q, k, v, W, f, h0)
+        y2, h2 = m2rnn_scan(q, k, v, W, f, h)           # a second token from the returned state
+    assert B.launch_count("m2rnn_step") == n0 + 2
+    yr, hr = m2rnn_scan_reference(q.float(), k.float(), v.float(), W.float(), f.float(), h0)
+    yr2, hr2 = m2rnn_scan_reference(q.float(), k.float(), v.float(), W.float(), f.float(), hr)
+    assert torch.allclose(y.float(), yr, atol=3e-2, rtol=3e-2)
+    assert torch.allclose(h.float(), hr, atol=2e-2, rtol=2e-2)
+    assert torch.allclose(y2.float(), yr2, atol=4e-2, rtol=4e-2)
+    assert torch.allclose(h2.float(), hr2, atol=3e-2, rtol=3e-2)
+    B.check_status()
