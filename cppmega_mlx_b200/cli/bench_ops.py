@@ -307,6 +307,72 @@ def bench_flash(args) -> list[dict]:
     return rows
 
 
+def bench_fused_local(args) -> list[dict]:
+    """The peer-memory kernels of the fused collectives with every "rank" living on this one GPU (the peer pointer tables point at
+    local buffers): the ZeRO-1 reduce + AdamW + push kernel over W = 2 gradient / parameter copies, the Muon reduce and push kernels,
+    and the expert-parallel dispatch / gather kernels with world = 1.  Same code, same access pattern, HBM instead of NVLink: this
+    is the form a single-GPU profiler capture can replay; the rates over real links come from ``parallel.selftest zero1bw / ep``."""
+    import ctypes
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.parallel.fused_zero1 import _table
+    pk = peaks()
+    dev = torch.device("cuda")
+    lib = B.load_library()
+    I64, F32 = ctypes.c_longlong, ctypes.c_float
+    W, n = 2, args.fused_elems
+    rows = []
+    g = [torch.randn(n, device=dev).mul_(0.01).bfloat16() for _ in range(W)]
+    p = [torch.randn(n, device=dev).mul_(0.02).bfloat16() for _ in range(W)]
+    m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    u = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+    parts = torch.zeros(148 * 4, device=dev)
+    gp = (ctypes.c_longlong * W)(*[t.data_ptr() for t in g])
+    pp = (ctypes.c_longlong * W)(*[t.data_ptr() for t in p])
+    st = B.ptr(B.status_buffer(dev))
+    f = (ctypes.c_float * 8)(1e-3, 0.9, 0.999, 1e-8, 0.01, 1.0, 1.0, 0.0)
+    tab_a = _table([dict(off=0, n=n, s0=m.data_ptr(), s1=v.data_ptr())], dev)
+    tab_m = _table([dict(off=0, n=n, s0=m.data_ptr(), u=u.data_ptr(), sumsq=parts.data_ptr())], dev)
+    tab_p = _table([dict(off=0, n=n, u=u.data_ptr(), coef=1.0)], dev)
+
+    def adamw():
+        B.check(lib.cmb_zero1_adamw_ranges(gp, pp, gp, 0, W, B.ptr(tab_a), 1, I64(n), f, -1, 0, I64(0), st, 0, B.stream_ptr()), "zero1_adamw_ranges")
+
+    def muon():
+        B.check(lib.cmb_zero1_muon_reduce_ranges(gp, pp, gp, 0, W, B.ptr(tab_m), 1, I64(n), F32(0.95), F32(0.0), 1, -1, 0, I64(0), st, 0, B.stream_ptr()),
+                "zero1_muon_reduce_ranges")
+
+    def push():
+        B.check(lib.cmb_zero1_push_ranges(pp, 0, W, B.ptr(tab_p), 1, I64(n), F32(1e-3), B.stream_ptr()), "zero1_push_ranges")
+    for name, fn, bytes_per in (("zero1_adamw_ranges W=2 local", adamw, 2 * W + 2 + 16 + 2 * W), ("zero1_muon_reduce_ranges W=2 local", muon, 2 * W + 2 + 8 + 2),
+                                ("zero1_push_ranges W=2 local", push, 2 + 2 + 2 * W)):
+        ms = time_cuda(fn, iters=args.iters, warmup=args.warmup)
+        rows.append({"op": name, "elems": n, "ms": ms, "GBs": n * bytes_per / ms / 1e6, "frac_of_measured_hbm": n * bytes_per / ms / 1e6 / pk["hbm_gbs"]})
+        print(json.dumps(rows[-1]), flush=True)
+    del g, p, m, v, u
+    # expert-parallel dispatch (row scatter into the owner's padded expert-sorted buffer) and gather, world = 1
+    T, d, k = args.fused_tokens, 2048, 6
+    x = torch.randn(T, d, device=dev).bfloat16()
+    nassign = T * k
+    tok = torch.arange(nassign, device=dev, dtype=torch.int64) // k
+    slot = torch.randperm(nassign, device=dev).to(torch.int64)
+    rank0 = torch.zeros(nassign, device=dev, dtype=torch.int32)
+    recv = torch.zeros(nassign, d, device=dev, dtype=torch.bfloat16)
+    rp = (ctypes.c_longlong * 1)(recv.data_ptr())
+    out = torch.empty(nassign, d, dtype=torch.bfloat16, device=dev)
+
+    def dispatch():
+        B.check(lib.cmb_ep_dispatch(B.ptr(x), B.ptr(tok), B.ptr(rank0), B.ptr(slot), None, rp, 1, I64(nassign), d, I64(nassign), st, B.stream_ptr()), "ep_dispatch")
+
+    def gather():
+        B.check(lib.cmb_ep_combine(rp, 1, B.ptr(rank0), B.ptr(slot), None, B.ptr(out), I64(nassign), 1, d, I64(nassign), st, B.stream_ptr()), "ep_gather")
+    for name, fn, nbytes in (("ep_dispatch world=1", dispatch, nassign * d * 2 + T * d * 2), ("ep_gather world=1", gather, 2 * nassign * d * 2)):
+        ms = time_cuda(fn, iters=args.iters, warmup=args.warmup)
+        rows.append({"op": name, "tokens": T, "top_k": k, "d": d, "ms": ms, "GBs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / pk["hbm_gbs"]})
+        print(json.dumps(rows[-1]), flush=True)
+    B.check_status()
+    return rows
+
+
 def bench_linears(args) -> list[dict]:
     """Decode-step linears for 1–32 activation rows: the CUDA-core streaming kernel (≤ 8 rows), the warp-MMA streaming kernel
     (≤ 32 rows), the 128-row tcgen05 GEMM and cuBLAS (``F.linear``), each as a CUDA graph of calls over a rotation of weight
@@ -659,7 +725,7 @@ def bench_serving(args) -> list[dict]:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "flash", "dsa_loss", "linears", "mamba3_step", "decode", "decode_loop", "serving", "decode_trace", "decode_profile", "step_profile", "all"])
+    ap.add_argument("op", choices=["gemm", "composite", "mxfp8", "m2rnn", "sparse_mla", "flash", "fused_local", "dsa_loss", "linears", "mamba3_step", "decode", "decode_loop", "serving", "decode_trace", "decode_profile", "step_profile", "all"])
     ap.add_argument("--json", default=None)
     ap.add_argument("--only", default=None, help="run the single case with this label (small captures under a profiler)")
     ap.add_argument("--iters", type=int, default=10)
@@ -669,6 +735,8 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=1, help="decode_profile: sequences in the batch")
     ap.add_argument("--prompt", type=int, default=512, help="decode_profile: prompt length")
     ap.add_argument("--groups", type=int, default=8, help="mamba3_step: B/C groups")
+    ap.add_argument("--fused-elems", type=int, default=128 * 1024 * 1024, help="fused_local: elements of the owned ZeRO-1 range")
+    ap.add_argument("--fused-tokens", type=int, default=16384, help="fused_local: tokens of the expert-parallel dispatch")
     args = ap.parse_args(argv)
     rows = []
     if args.op in ("gemm", "all"):
@@ -679,6 +747,8 @@ def main(argv=None) -> int:
         rows += bench_mxfp8(args)
     if args.op in ("flash", "all"):
         rows += bench_flash(args)
+    if args.op in ("fused_local", "all"):
+        rows += bench_fused_local(args)
     if args.op in ("m2rnn", "all"):
         rows += bench_m2rnn(args)
     if args.op in ("sparse_mla", "all"):

@@ -4,11 +4,12 @@
 //
 //  * cmb_comm_barrier        epoch-flag barrier: release-store my epoch into every peer's pad, acquire-poll my pad.
 //                            The poll is bounded; on expiry a status word is set and the kernel returns.
-//  * cmb_zero1_adamw         ZeRO-1 for AdamW-owned tensors in ONE kernel: sum the W peers' bf16 gradients of the
-//                            owned range (the reduce-scatter), bf16→fp32, AdamW on local fp32 moments, and push the
-//                            new bf16 parameters into every rank's parameter buffer (the all-gather).
-//  * cmb_zero1_muon_reduce   same gradient reduction fused with Muon's momentum stage: writes the bf16 Newton–Schulz
-//                            input and accumulates its squared norm.
+//  * cmb_zero1_adamw_ranges ZeRO-1 for AdamW-owned tensors in ONE kernel over a table of ranges: sum the W peers' bf16
+//                            gradients of each owned range (the reduce-scatter), bf16→fp32, AdamW on local fp32 moments,
+//                            and push the new bf16 parameters into every rank's parameter buffer (the all-gather).
+//  * cmb_zero1_muon_reduce_ranges  same gradient reduction fused with Muon's momentum stage: writes the bf16 Newton–Schulz
+//                            input and per-block partial sums of its squared norm (added in fixed order by
+//                            cmb_zero1_sumsq_finalize).
 //  * cmb_zero1_push_update   p ← p − coef·u for an owned tensor, stored to every rank (all-gather side of Muon).
 //
 // These replace the reference's per-leaf all_sum for gradients and its all_sum-of-zero-padded-shards "gather"
@@ -89,82 +90,14 @@ __device__ __forceinline__ void reduce8(const PeerPtrs& grads, int world, long l
   for (int i = 0; i < 8; ++i) g[i] *= inv_world;
 }
 
-// off: element offset of the tensor inside the flat buffers (multiple of 8); n: element count (tail handled scalar).
-__global__ void __launch_bounds__(256) zero1_adamw_kernel(PeerPtrs grads, PeerPtrs params, int rank, int world,
-                                                           long long off, long long n, float* __restrict__ m,
-                                                           float* __restrict__ v, float lr, float b1, float b2, float eps,
-                                                           float wd, float c1, float c2, float inv_world) {
-  const long long nvec = n >> 3;
-  const __nv_bfloat16* myp = static_cast<const __nv_bfloat16*>(params.p[rank]);
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long e = off + 8 * i;
-    float g[8], p[8];
-    reduce8(grads, world, e, inv_world, g);
-    unpack8(*reinterpret_cast<const uint4*>(myp + e), p);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const long long j = 8 * i + k;
-      const float mi = b1 * m[j] + (1.f - b1) * g[k];
-      const float vi = b2 * v[j] + (1.f - b2) * g[k] * g[k];
-      m[j] = mi;
-      v[j] = vi;
-      p[k] = p[k] * (1.f - lr * wd) - lr * c1 * mi / (sqrtf(vi) * c2 + eps);
-    }
-    const uint4 out = pack8(p);
-    for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + e) = out;
-  }
-  // scalar tail (n % 8)
-  const long long tail0 = nvec << 3;
-  for (long long j = tail0 + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; j < n;
-       j += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float g = 0.f;
-    for (int r = 0; r < world; ++r) g += __bfloat162float(static_cast<const __nv_bfloat16*>(grads.p[r])[off + j]);
-    g *= inv_world;
-    const float mi = b1 * m[j] + (1.f - b1) * g;
-    const float vi = b2 * v[j] + (1.f - b2) * g * g;
-    m[j] = mi;
-    v[j] = vi;
-    const float pn = __bfloat162float(myp[off + j]) * (1.f - lr * wd) - lr * c1 * mi / (sqrtf(vi) * c2 + eps);
-    const __nv_bfloat16 o = __float2bfloat16(pn);
-    for (int r = 0; r < world; ++r) static_cast<__nv_bfloat16*>(params.p[r])[off + j] = o;
-  }
+// Eight consecutive fp32 state values as two 16-byte accesses (state tensors are 32-byte aligned at multiples of 8 elements).
+__device__ __forceinline__ void ld8f(const float* p, float (&x)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
 }
-
-// Gradient reduction fused with Muon's momentum stage (n % 8 == 0 for 2-D weights with cols % 8 == 0).
-__global__ void __launch_bounds__(256) zero1_muon_reduce_kernel(PeerPtrs grads, PeerPtrs params, int rank, int world,
-                                                                 long long off, long long n, float* __restrict__ v,
-                                                                 __nv_bfloat16* __restrict__ u, float* __restrict__ sumsq,
-                                                                 float mu, float wd, int nesterov, float inv_world) {
-  __shared__ float red[8];
-  const long long nvec = n >> 3;
-  const __nv_bfloat16* myp = static_cast<const __nv_bfloat16*>(params.p[rank]);
-  float acc = 0.f;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long e = off + 8 * i;
-    float g[8], p[8], o[8];
-    reduce8(grads, world, e, inv_world, g);
-    unpack8(*reinterpret_cast<const uint4*>(myp + e), p);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const long long j = 8 * i + k;
-      const float gi = g[k] + wd * p[k];
-      const float vi = mu * v[j] + (1.f - mu) * gi;
-      v[j] = vi;
-      o[k] = nesterov ? gi * (1.f - mu) + vi * mu : vi;
-      acc += o[k] * o[k];
-    }
-    *reinterpret_cast<uint4*>(u + 8 * i) = pack8(o);
-  }
-  acc = warp_sum(acc);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float t = 0.f;
-    for (int w = 0; w < 8; ++w) t += red[w];
-    atomicAdd(sumsq, t);
-  }
+__device__ __forceinline__ void st8f(float* p, const float (&x)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(x[4], x[5], x[6], x[7]);
 }
 
 __global__ void __launch_bounds__(256) zero1_push_update_kernel(PeerPtrs params, int rank, int world, long long off,
@@ -245,18 +178,19 @@ __global__ void __launch_bounds__(256) zero1_adamw_ranges_kernel(PeerPtrs grads,
     const long long nvec = rg.n >> 3;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<long long>(gridDim.x) * blockDim.x) {
       const long long e = rg.off + 8 * i;
-      float g[8], p[8];
+      float g[8], p[8], mm[8], vv[8];
       reduce8(grads, world, e, inv_world, g);
       unpack8(*reinterpret_cast<const uint4*>(myp + e), p);
+      ld8f(rg.s0 + 8 * i, mm);
+      ld8f(rg.s1 + 8 * i, vv);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const long long j = 8 * i + k;
-        const float mi = b1 * rg.s0[j] + (1.f - b1) * g[k];
-        const float vi = b2 * rg.s1[j] + (1.f - b2) * g[k] * g[k];
-        rg.s0[j] = mi;
-        rg.s1[j] = vi;
-        p[k] = p[k] * (1.f - lr * wd) - lr * c1 * mi / (sqrtf(vi) * c2 + eps);
+        mm[k] = b1 * mm[k] + (1.f - b1) * g[k];
+        vv[k] = b2 * vv[k] + (1.f - b2) * g[k] * g[k];
+        p[k] = p[k] * (1.f - lr * wd) - lr * c1 * mm[k] / (sqrtf(vv[k]) * c2 + eps);
       }
+      st8f(rg.s0 + 8 * i, mm);
+      st8f(rg.s1 + 8 * i, vv);
       const uint4 out = pack8(p);
       for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + e) = out;
     }
@@ -287,18 +221,18 @@ __global__ void __launch_bounds__(256) zero1_muon_reduce_ranges_kernel(PeerPtrs 
     float acc = 0.f;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec; i += static_cast<long long>(gridDim.x) * blockDim.x) {
       const long long e = rg.off + 8 * i;
-      float g[8], p[8], o[8];
+      float g[8], p[8], o[8], vv[8];
       reduce8(grads, world, e, inv_world, g);
       unpack8(*reinterpret_cast<const uint4*>(myp + e), p);
+      ld8f(rg.s0 + 8 * i, vv);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const long long j = 8 * i + k;
         const float gi = g[k] + wd * p[k];
-        const float vi = mu * rg.s0[j] + (1.f - mu) * gi;
-        rg.s0[j] = vi;
-        o[k] = nesterov ? gi * (1.f - mu) + vi * mu : vi;
+        vv[k] = mu * vv[k] + (1.f - mu) * gi;
+        o[k] = nesterov ? gi * (1.f - mu) + vv[k] * mu : vv[k];
         acc += o[k] * o[k];
       }
+      st8f(rg.s0 + 8 * i, vv);
       *reinterpret_cast<uint4*>(rg.u + 8 * i) = pack8(o);
     }
     acc = warp_sum(acc);
@@ -372,27 +306,7 @@ extern "C" int cmb_comm_barrier(const long long* pad_ptrs, int rank, int world, 
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
-extern "C" int cmb_zero1_adamw(const long long* grad_ptrs, const long long* param_ptrs, int rank, int world, long long off,
-                               long long n, float* m, float* v, float lr, float b1, float b2, float eps, float wd, float c1,
-                               float c2, void* stream) {
-  cmb::PeerPtrs g, p;
-  if (!cmb::fill(g, grad_ptrs, world) || !cmb::fill(p, param_ptrs, world) || (off & 7)) return 1;
-  if (n <= 0) return 0;
-  cmb::zero1_adamw_kernel<<<cmb::comm_grid((n + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      g, p, rank, world, off, n, m, v, lr, b1, b2, eps, wd, c1, c2, 1.f / world);
-  return cudaGetLastError() == cudaSuccess ? 0 : 2;
-}
 
-extern "C" int cmb_zero1_muon_reduce(const long long* grad_ptrs, const long long* param_ptrs, int rank, int world,
-                                     long long off, long long n, float* v, void* u, float* sumsq, float mu, float wd,
-                                     int nesterov, void* stream) {
-  cmb::PeerPtrs g, p;
-  if (!cmb::fill(g, grad_ptrs, world) || !cmb::fill(p, param_ptrs, world) || (off & 7) || (n & 7)) return 1;
-  if (n <= 0) return 0;
-  cmb::zero1_muon_reduce_kernel<<<cmb::comm_grid(n / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      g, p, rank, world, off, n, v, static_cast<__nv_bfloat16*>(u), sumsq, mu, wd, nesterov, 1.f / world);
-  return cudaGetLastError() == cudaSuccess ? 0 : 2;
-}
 
 extern "C" int cmb_zero1_push_update(const long long* param_ptrs, int rank, int world, long long off, long long n,
                                      const void* u, float coef, void* stream) {

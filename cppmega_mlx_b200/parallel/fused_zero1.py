@@ -14,11 +14,13 @@ parameter pushes, and the Muon momentum stage therefore run while the main strea
 layers: once every rank has raised a bucket's flag no rank reads that bucket's weights again before the step ends, so pushing
 new parameters early is safe.  After backward only the Newton–Schulz chains, the Muon pushes and whatever bucket was not
 complete remain, closed by one epoch barrier ("all parameters delivered, all gradients consumed").  The hooks act only when the
-training step has armed them for its last micro-batch (``arm_overlap``) and ``CPPMEGA_ZERO1_OVERLAP=1`` is set; otherwise
-every bucket is launched from ``step()``, which is the same code path without the overlap.  The overlap is off by default: over
-NVLink the whole exchange of a 1.76 B-parameter model costs 2.6 ms per step on two B200s when it runs after backward
-(331.2 ms against 328.2 ms with no communication at all), and running the memory-bound update kernels beside the backward GEMMs
-slowed those by as much as it hid (333.4 ms).  It is there for fabrics or models where the exchange is not that cheap.
+training step has armed them for its last micro-batch (``arm_overlap``); otherwise every bucket is launched from ``step()``,
+which is the same code path without the overlap.  ``CPPMEGA_ZERO1_OVERLAP`` = ``1`` / ``0`` / ``auto`` (default): on from four
+ranks up.  Measured with the 1.76 B-parameter hybrid on B200s: on two ranks each owner's kernels are bound by local HBM, the whole
+exchange costs 2.6 ms per step after backward (331.2 ms against 328.2 ms with no communication at all) and running it beside the
+backward GEMMs slows those by as much as it hides (333.4 ms); on eight ranks the kernels are bound by the links ((W−1)/W of all
+gradients in and of all parameters out per rank, 9 ms after backward) and the overlap takes the step from 308.6 to 301.5 ms,
+2 ms above the run with no communication.
 
 Per step and rank this moves (W−1)/W of the owned segment over NVLink in each direction.
 """
@@ -78,7 +80,7 @@ class FusedZeRO1Comm:
         self.bufs: list[SymmetricBuffer] = []
         self.barrier: EpochBarrier | None = None
         self.enabled = True
-        self.overlap = os.environ.get("CPPMEGA_ZERO1_OVERLAP", "0") == "1"
+        self.overlap = None                  # decided in bind(): needs the group size
         self.armed = False
         self.epoch = 0
         self.buckets: list[_Bucket] | None = None
@@ -95,6 +97,8 @@ class FusedZeRO1Comm:
         if flat.dtype != torch.bfloat16 or flat.grad_dtype != torch.bfloat16:
             self.enabled = False
         self.barrier = EpochBarrier(flat.params.device, self.group)
+        mode = os.environ.get("CPPMEGA_ZERO1_OVERLAP", "auto")
+        self.overlap = mode == "1" or (mode == "auto" and self.params_buf.world >= 4)
 
     # ------------------------------------------------------------------------------------------
     def _supported(self, opt) -> bool:

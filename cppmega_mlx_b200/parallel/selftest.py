@@ -71,18 +71,107 @@ def case_zero1(rank, world, dev):
                           "max_param_diff": float(diff), "mean_param_diff": float(mean), "rank_spread": float(spread)}))
 
 
+def _optimizer_only(steps: int, dev, rank: int, world: int):
+    """`steps` fused optimizer steps on gradients filled from a seeded generator (no forward / backward, whose small reductions
+    use floating-point atomics and are outside this check)."""
+    from cppmega_mlx_b200.models.hybrid_lm import HybridTinyConfig, HybridTinyLM
+    from cppmega_mlx_b200.training.distributed_optimizer import DistributedZeRO1Optimizer
+    from cppmega_mlx_b200.training.optimizers import make_muon
+    torch.manual_seed(0)
+    cfg = HybridTinyConfig(vocab_size=512, hidden_size=256, pattern="MA", depth=2, num_attention_heads=4, max_seq_length=256,
+                           mamba_head_dim=64, mamba_state_dim=64, mamba_chunk_size=64, mamba_groups=2, mla_low_rank=True,
+                           mla_q_lora_rank=128, mla_kv_lora_rank=128, mla_qk_nope_head_dim=64, mla_qk_rope_head_dim=32,
+                           mla_v_head_dim=64, ffn_hidden_size=512, position_embedding=False)
+    model = HybridTinyLM(cfg).to(dev, torch.bfloat16)
+    opt = DistributedZeRO1Optimizer(model, lambda ps: make_muon(ps, lr_muon=2e-2, lr_adamw=1e-3, ns_carrier="bf16"), comm="fused")
+    opt.zero_grad()
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    for _ in range(steps):
+        for p in model.parameters():
+            p.grad.copy_(torch.randn(p.shape, generator=gen, device=dev) * 0.01)
+        opt.step()
+        opt.zero_grad()
+    return torch.cat([p.detach().float().reshape(-1) for p in model.parameters()])
+
+
 def case_zero1det(rank, world, dev):
-    """Determinism of the fused ZeRO-1 step: two runs from the same seeds end with bit-identical parameters on every rank
-    (each owner sums the peers' gradients in a fixed rank order; nothing in the step uses atomics)."""
+    """Determinism of the fused ZeRO-1 step: from the same parameters and the same per-rank gradients, two runs of three steps
+    end with bit-identical parameters on every rank (each owner sums the peers' gradients in a fixed rank order, the squared norms
+    are added per block in a fixed order, and nothing in the step uses atomics)."""
     from cppmega_mlx_b200.ops import _backend as B
-    l_a, p_a = _train("fused", 3, dev, rank, world)
-    l_b, p_b = _train("fused", 3, dev, rank, world)
+    p_a = _optimizer_only(3, dev, rank, world)
+    p_b = _optimizer_only(3, dev, rank, world)
     torch.cuda.synchronize()
     B.check_status()
     same = torch.tensor([int(torch.equal(p_a, p_b))], device=dev)
     dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    ref = p_a.clone()
+    dist.broadcast(ref, 0)
+    spread = (ref - p_a).abs().max()
+    dist.all_reduce(spread, op=dist.ReduceOp.MAX)
     if rank == 0:
-        print(json.dumps({"case": "zero1det", "world": world, "bitwise_equal": bool(int(same)), "loss_a": l_a, "loss_b": l_b}))
+        print(json.dumps({"case": "zero1det", "world": world, "bitwise_equal": bool(int(same)), "rank_spread": float(spread),
+                          "finite": bool(torch.isfinite(p_a).all())}))
+
+
+def case_zero1bw(rank, world, dev):
+    """Rate of the three ZeRO-1 range kernels on one large owned range per rank, no flag wait (bucket −1): the fused
+    reduce + AdamW + push kernel, the Muon reduce + momentum kernel (link reads only) and the Muon push kernel (link writes only).
+    Each is compared with the slower of its link time (bytes crossing NVLink per direction ÷ 770 GB/s measured peer copy) and its
+    local HBM time (bytes this GPU's memory serves, the peers' reads and writes included, ÷ the measured copy rate)."""
+    import ctypes
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.parallel.fused_zero1 import _table
+    from cppmega_mlx_b200.parallel.symm import EpochBarrier, SymmetricBuffer
+    n = int(os.environ.get("CMB_ZERO1BW_ELEMS", str(128 * 1024 * 1024)))          # owned elements per rank
+    lib = B.load_library()
+    grads, params = SymmetricBuffer(world * n, torch.bfloat16, dev), SymmetricBuffer(world * n, torch.bfloat16, dev)
+    grads.tensor.normal_(0, 0.01)
+    params.tensor.normal_(0, 0.02)
+    m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    u = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+    parts = torch.zeros(148 * 4, device=dev)
+    bar = EpochBarrier(dev)
+    tab_a = _table([dict(off=rank * n, n=n, s0=m.data_ptr(), s1=v.data_ptr())], dev)
+    tab_m = _table([dict(off=rank * n, n=n, s0=m.data_ptr(), u=u.data_ptr(), sumsq=parts.data_ptr())], dev)
+    tab_p = _table([dict(off=rank * n, n=n, u=u.data_ptr(), coef=1.0)], dev)
+    st = B.ptr(B.status_buffer(dev))
+    I64, F32 = ctypes.c_longlong, ctypes.c_float
+    f = (ctypes.c_float * 8)(1e-3, 0.9, 0.999, 1e-8, 0.01, 1.0, 1.0, 0.0)
+    gp, pp = grads.peer_ptrs, params.peer_ptrs
+
+    def adamw():
+        B.check(lib.cmb_zero1_adamw_ranges(gp, pp, gp, rank, world, B.ptr(tab_a), 1, I64(n), f, -1, 0, I64(0), st, 0, B.stream_ptr()), "zero1_adamw_ranges")
+
+    def muon():
+        B.check(lib.cmb_zero1_muon_reduce_ranges(gp, pp, gp, rank, world, B.ptr(tab_m), 1, I64(n), F32(0.95), F32(0.0), 1, -1, 0, I64(0), st, 0,
+                                                 B.stream_ptr()), "zero1_muon_reduce_ranges")
+
+    def push():
+        B.check(lib.cmb_zero1_push_ranges(pp, rank, world, B.ptr(tab_p), 1, I64(n), F32(1e-3), B.stream_ptr()), "zero1_push_ranges")
+
+    def timed(fn):
+        def step():
+            bar()                 # ranks start together; the barrier kernel is inside the timed region on every rank alike
+            fn()
+        return _time(step, iters=8)
+    t_bar = _time(bar, iters=8)
+    hbm = float(os.environ.get("CMB_HBM_GBS", "6551")) * 1e9
+    link = 770e9
+    W = world
+    rows = {}
+    # bytes per element: (over the link per direction, served by this GPU's HBM)
+    for name, fn, link_b, hbm_b in (("adamw_ranges", adamw, 2 * (W - 1), 2 + 2 + 16 + 2 + 4 * (W - 1)),
+                                    ("muon_reduce_ranges", muon, 2 * (W - 1), 2 + 2 + 8 + 2 + 2 * (W - 1)),
+                                    ("push_ranges", push, 2 * (W - 1), 2 + 2 + 2 + 2 * (W - 1))):
+        t = timed(fn) - t_bar
+        bound = max(n * link_b / link, n * hbm_b / hbm) * 1e3
+        rows[name] = {"ms": t, "link_GBs_per_direction": n * link_b / t / 1e6, "hbm_GBs": n * hbm_b / t / 1e6, "roofline_ms": bound,
+                      "achieved_over_roofline": bound / t, "bound": "link" if n * link_b / link > n * hbm_b / hbm else "hbm"}
+    torch.cuda.synchronize()
+    B.check_status()
+    if rank == 0:
+        print(json.dumps({"case": "zero1bw", "world": world, "owned_elems_per_rank": n, "barrier_ms": t_bar, **rows}))
 
 
 def _time(fn, iters=10, warmup=3):
@@ -270,7 +359,7 @@ def main():
     case = sys.argv[1] if len(sys.argv) > 1 else "zero1"
     rank, world, dev = _setup()
     try:
-        {"zero1": case_zero1, "zero1det": case_zero1det, "tp": case_tp, "tpar": case_tpar, "ep": case_ep, "epdrop": case_epdrop}[case](rank, world, dev)
+        {"zero1": case_zero1, "zero1det": case_zero1det, "zero1bw": case_zero1bw, "tp": case_tp, "tpar": case_tpar, "ep": case_ep, "epdrop": case_epdrop}[case](rank, world, dev)
     finally:
         dist.barrier()
         dist.destroy_process_group()

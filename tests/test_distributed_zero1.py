@@ -112,3 +112,28 @@ def test_flat_buffers_alias_nothing_and_the_audit_sees_a_planted_overlap():
     tied = torch.nn.Sequential(torch.nn.Linear(4, 4, bias=False), torch.nn.Linear(4, 4, bias=False))
     tied[1].weight = tied[0].weight
     assert audit_grad_buffer_aliasing(tied)["overlaps"] == []
+
+
+def test_owner_assignment_by_cost_balances_newton_schulz_work():
+    """``assign_owners`` is deterministic, and with ``muon_owner_cost`` the matrices Muon orthogonalises are spread by their
+    tensor-core work rather than by size (an embedding-sized AdamW tensor no longer counts like a matrix of the same size)."""
+    import torch
+    from cppmega_mlx_b200.training.distributed_optimizer import assign_owners, muon_owner_cost
+    from cppmega_mlx_b200.training.optimizers import is_muon_compatible
+    named = [("embed_tokens.weight", torch.empty(16384, 512, device="meta"))]
+    named += [(f"layers.{i}.ffn.up.weight", torch.empty(2048, 1024, device="meta")) for i in range(12)]
+    named += [(f"layers.{i}.norm.weight", torch.empty(1024, device="meta")) for i in range(12)]
+
+    def ns(n, p):
+        return 0.0 if not is_muon_compatible(n, p) else float(min(p.shape)) ** 2 * max(p.shape)
+    by_size, by_cost = assign_owners(named, 4), assign_owners(named, 4, muon_owner_cost)
+    assert by_cost == assign_owners(named, 4, muon_owner_cost)
+    assert set(by_size) == set(by_cost) == {n for n, _ in named}
+
+    def spread(owners):
+        load = [0.0] * 4
+        for n, p in named:
+            load[owners[n]] += ns(n, p)
+        return max(load) - min(load)
+    assert spread(by_cost) < spread(by_size)
+    assert spread(by_cost) == 0.0          # 12 equal matrices over 4 ranks
