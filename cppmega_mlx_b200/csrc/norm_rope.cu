@@ -234,42 +234,61 @@ __global__ void __launch_bounds__(256) add_rmsnorm_block_kernel(const __nv_bfloa
   }
 }
 
+// Shared memory of the backward warp kernel: one fp32 dw partial row per warp plus the weight as bf16.
+static inline size_t rmsnorm_bwd_warp_smem(int cols) { return static_cast<size_t>(cols) * (4 * sizeof(float) + sizeof(__nv_bfloat16)); }
+
+__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(b[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+// The row stays in registers as the packed bf16 it was loaded as (2·VPL 16-byte vectors per lane, all loads issued before the
+// first use) and is unpacked once per pass; the dw partial of a warp lives in its own shared-memory row, updated with plain
+// 16-byte read-modify-writes (a lane owns its columns), so the kernel needs ~100 registers instead of ~220 and four to five CTAs
+// fit on an SM: enough loads in flight to keep HBM busy.
 template <int VPL>
-__global__ void __launch_bounds__(128) rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ gy,
-                                                                const __nv_bfloat16* __restrict__ x,
-                                                                const __nv_bfloat16* __restrict__ w,
-                                                                const float* __restrict__ rstd, __nv_bfloat16* __restrict__ gx,
-                                                                float* __restrict__ gw_part, int64_t rows, int cols) {
-  extern __shared__ float gws[];   // [cols] CTA-level dw partial
+__global__ void __launch_bounds__(128, 4) rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ gy,
+                                                                   const __nv_bfloat16* __restrict__ x,
+                                                                   const __nv_bfloat16* __restrict__ w,
+                                                                   const float* __restrict__ rstd, __nv_bfloat16* __restrict__ gx,
+                                                                   float* __restrict__ gw_part, int64_t rows, int cols) {
+  extern __shared__ __align__(16) float gws[];   // [4][cols] per-warp dw partials, then the weight as bf16 [cols]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = cols >> 3;
-  for (int i = threadIdx.x; i < cols; i += 128) gws[i] = 0.f;
+  __nv_bfloat16* ws = reinterpret_cast<__nv_bfloat16*>(gws + 4 * cols);
+  for (int i = threadIdx.x; i < 4 * cols; i += 128) gws[i] = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += 128) reinterpret_cast<uint4*>(ws)[v] = reinterpret_cast<const uint4*>(w)[v];
   __syncthreads();
-  float acc[VPL][8];
-#pragma unroll
-  for (int a = 0; a < VPL; ++a)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[a][i] = 0.f;
+  float* mine = gws + warp * cols;
   for (int64_t row = blockIdx.x * 4 + warp; row < rows; row += static_cast<int64_t>(gridDim.x) * 4) {
     const __nv_bfloat16* xr = x + row * cols;
     const __nv_bfloat16* gr = gy + row * cols;
+    uint4 rx[VPL], rg[VPL];
+#pragma unroll
+    for (int a = 0; a < VPL; ++a) {
+      const int v = lane + 32 * a;
+      if (v < nvec) {
+        rx[a] = *reinterpret_cast<const uint4*>(xr + 8 * v);
+        rg[a] = *reinterpret_cast<const uint4*>(gr + 8 * v);
+      }
+    }
     const float r = rstd[row];
-    float fx[VPL][8], fg[VPL][8];
     float dot = 0.f;
 #pragma unroll
     for (int a = 0; a < VPL; ++a) {
       const int v = lane + 32 * a;
       if (v < nvec) {
-        float fw[8];
-        load8(xr + 8 * v, fx[a]);
-        load8(gr + 8 * v, fg[a]);
-        load8(w + 8 * v, fw);
+        float fx[8], fg[8], fw[8];
+        unpack8(rx[a], fx);
+        unpack8(rg[a], fg);
+        unpack8(reinterpret_cast<const uint4*>(ws)[v], fw);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          acc[a][i] += fg[a][i] * fx[a][i] * r;
-          fg[a][i] *= fw[i];                 // from here on g·w
-          dot += fg[a][i] * fx[a][i];
-        }
+        for (int i = 0; i < 8; ++i) dot += fg[i] * fw[i] * fx[i];
       }
     }
     dot = warp_sum(dot);
@@ -279,23 +298,25 @@ __global__ void __launch_bounds__(128) rmsnorm_bwd_warp_kernel(const __nv_bfloat
     for (int a = 0; a < VPL; ++a) {
       const int v = lane + 32 * a;
       if (v < nvec) {
-        float o[8];
+        float fx[8], fg[8], fw[8], o[8];
+        unpack8(rx[a], fx);
+        unpack8(rg[a], fg);
+        unpack8(reinterpret_cast<const uint4*>(ws)[v], fw);
+        float4* acc = reinterpret_cast<float4*>(mine + 8 * v);
+        float4 a0 = acc[0], a1 = acc[1];
+        a0.x += fg[0] * fx[0] * r; a0.y += fg[1] * fx[1] * r; a0.z += fg[2] * fx[2] * r; a0.w += fg[3] * fx[3] * r;
+        a1.x += fg[4] * fx[4] * r; a1.y += fg[5] * fx[5] * r; a1.z += fg[6] * fx[6] * r; a1.w += fg[7] * fx[7] * r;
+        acc[0] = a0;
+        acc[1] = a1;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = fg[a][i] * r - fx[a][i] * c;
+        for (int i = 0; i < 8; ++i) o[i] = fg[i] * fw[i] * r - fx[i] * c;
         store8(gxr + 8 * v, o);
       }
     }
   }
-#pragma unroll
-  for (int a = 0; a < VPL; ++a) {
-    const int v = lane + 32 * a;
-    if (v < nvec) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) atomicAdd(&gws[8 * v + i], acc[a][i]);
-    }
-  }
   __syncthreads();
-  for (int i = threadIdx.x; i < cols; i += 128) gw_part[static_cast<size_t>(blockIdx.x) * cols + i] = gws[i];
+  for (int i = threadIdx.x; i < cols; i += 128)
+    gw_part[static_cast<size_t>(blockIdx.x) * cols + i] = (gws[i] + gws[cols + i]) + (gws[2 * cols + i] + gws[3 * cols + i]);
 }
 
 // SwiGLU: y = silu(g) * u with gu = [.., 2H] laid out as [gate | up] halves.
@@ -398,7 +419,7 @@ extern "C" int cmb_rmsnorm_bwd(const void* gy, const void* x, const void* w, con
   if (cols % 8) return 1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (cols <= 2048 && rows >= 4) {   // a CTA without rows still writes its (zero) dw partial
-    cmb::rmsnorm_bwd_warp_kernel<8><<<nblk, 128, cols * sizeof(float), s>>>(
+    cmb::rmsnorm_bwd_warp_kernel<8><<<nblk, 128, cmb::rmsnorm_bwd_warp_smem(cols), s>>>(
         static_cast<const __nv_bfloat16*>(gy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
         static_cast<const float*>(rstd), static_cast<__nv_bfloat16*>(gx), static_cast<float*>(gw_part), rows, cols);
     return cudaGetLastError() == cudaSuccess ? 0 : 2;
@@ -483,7 +504,7 @@ extern "C" int cmb_rmsnorm_bwd_noalloc(const void* gy, const void* x, const void
   // kernel, so nothing left over from an earlier call can leak in and no clearing is needed.
   // Same kernel choice as cmb_rmsnorm_bwd, so both entry points return identical bits.
   if (cols <= 2048 && rows >= 4)
-    cmb::rmsnorm_bwd_warp_kernel<8><<<nblk, 128, cols * sizeof(float), s>>>(
+    cmb::rmsnorm_bwd_warp_kernel<8><<<nblk, 128, cmb::rmsnorm_bwd_warp_smem(cols), s>>>(
         static_cast<const __nv_bfloat16*>(gy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
         static_cast<const float*>(rstd), static_cast<__nv_bfloat16*>(gx), scratch, rows, cols);
   else

@@ -39,18 +39,22 @@ def _compare(module, x, call, rel=6e-2, grad_rel=1e-1, expect=()):
             close(p.grad, pr[n].grad, f"grad {n}", 1.5e-1)
 
 
-def test_conv_silu_op():
+@pytest.mark.parametrize("S,n_head,C,C1,n_tail", [(77, 40, 96, 64, 10),      # pitch 146: the narrow (4-byte) kernels
+                                                  (77, 40, 96, 64, 8),       # everything a multiple of 8: the wide kernels, ragged tiles
+                                                  (200, 36, 100, 60, 8),     # multiples of 4 only: narrow forward, wide backward
+                                                  (130, 0, 512, 256, 0)])    # two channel blocks per row, several runs
+def test_conv_silu_op(S, n_head, C, C1, n_tail):
     from cppmega_mlx_b200 import ops
     torch.manual_seed(0)
-    proj = torch.randn(2, 77, 40 + 96 + 10, device="cuda").bfloat16().requires_grad_()
-    w = (torch.randn(96, 4, 1, device="cuda") * 0.3).bfloat16().requires_grad_()
-    bias = (torch.randn(96, device="cuda") * 0.1).bfloat16().requires_grad_()
-    head, o1, o2, tail = ops.packed_split_conv_silu(proj, 40, 96, 64, w, bias)
+    proj = torch.randn(2, S, n_head + C + n_tail, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(C, 4, 1, device="cuda") * 0.3).bfloat16().requires_grad_()
+    bias = (torch.randn(C, device="cuda") * 0.1).bfloat16().requires_grad_()
+    head, o1, o2, tail = ops.packed_split_conv_silu(proj, n_head, C, C1, w, bias)
     loss = (o1.float() ** 2).sum() + o2.float().sum() * 0.5 + head.float().sum() + (tail.float() ** 2).sum()
     loss.backward()
     pr, wr, br = (t.detach().float().requires_grad_() for t in (proj, w, bias))
-    r1, r2 = ops.conv.causal_conv1d_silu_reference(pr, 40, 96, 64, wr, br)
-    lr = (r1 ** 2).sum() + r2.sum() * 0.5 + pr[..., :40].sum() + (pr[..., 136:] ** 2).sum()
+    r1, r2 = ops.conv.causal_conv1d_silu_reference(pr, n_head, C, C1, wr, br)
+    lr = (r1 ** 2).sum() + r2.sum() * 0.5 + pr[..., :n_head].sum() + (pr[..., n_head + C:] ** 2).sum()
     lr.backward()
     assert (o1.float() - r1).abs().max() < 3e-2 and (o2.float() - r2).abs().max() < 3e-2
     assert (proj.grad.float() - pr.grad).abs().max() < 0.1 * pr.grad.abs().max()
