@@ -198,21 +198,6 @@ __global__ void __launch_bounds__(256) conv_silu_bwd_kernel(const __nv_bfloat16*
 constexpr int CONV_WTS = 16;   // tokens per warp, forward
 constexpr int CONV_WRUN = 64;  // tokens per warp, backward
 
-__device__ __forceinline__ void unpack8_bf16(const uint4& q, float (&f)[8]) {
-  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&q);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(b[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-__device__ __forceinline__ void unpack4_bf16(const uint2& q, float (&f)[4]) {
-  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&q);
-  const float2 t0 = __bfloat1622float2(b[0]), t1 = __bfloat1622float2(b[1]);
-  f[0] = t0.x; f[1] = t0.y; f[2] = t1.x; f[3] = t1.y;
-}
-
 __global__ void __launch_bounds__(256, 2) conv_silu_fwd_w8_kernel(const __nv_bfloat16* __restrict__ in, long long ld_in, int c_off,
                                                                 const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ bias,
                                                                 __nv_bfloat16* __restrict__ out1, __nv_bfloat16* __restrict__ out2, int Bn, int S,

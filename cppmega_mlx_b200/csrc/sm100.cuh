@@ -286,6 +286,23 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+
+// 8 / 4 packed bf16 values (one 16- / 8-byte access) → fp32.
+__device__ __forceinline__ void unpack8_bf16(const uint4& q, float (&f)[8]) {
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(b[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void unpack4_bf16(const uint2& q, float (&f)[4]) {
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&q);
+  const float2 t0 = __bfloat1622float2(b[0]), t1 = __bfloat1622float2(b[1]);
+  f[0] = t0.x; f[1] = t0.y; f[2] = t1.x; f[3] = t1.y;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
