@@ -111,15 +111,39 @@ struct TileCoord {
   int tm, tn, i2, i3, i4;
 };
 
-__device__ __forceinline__ TileCoord tile_coords(int t, int num_m, int num_n, int nb2, int nb3) {
+// With CAUSAL_SKIP only the tiles that touch the lower triangle are enumerated (row tm keeps its first causal_kept(tm) column
+// tiles), so a persistent CTA's share of the index space is a share of the real work: striding over all tiles and skipping left
+// the CTAs with up to 1.5× the mean number of kept tiles.
+__host__ __device__ __forceinline__ int causal_kept(int tm, int num_n, int bn) {
+  const int k = (tm * GEMM_BM + GEMM_BM - 1) / bn + 1;
+  return k < num_n ? k : num_n;
+}
+__host__ __device__ __forceinline__ int tiles_per_problem(int flags, int num_m, int num_n, int bn) {
+  if (!(flags & GEMM_CAUSAL_SKIP)) return num_m * num_n;
+  int n = 0;
+  for (int tm = 0; tm < num_m; ++tm) n += causal_kept(tm, num_n, bn);
+  return n;
+}
+
+__device__ __forceinline__ TileCoord tile_coords(int t, int num_m, int num_n, int nb2, int nb3, int per_problem, bool causal, int bn) {
   TileCoord c;
-  const int per_problem = num_m * num_n;
   const int batch = t / per_problem;
   const int r0 = t - batch * per_problem;
   c.i2 = batch % nb2;
   const int q = batch / nb2;
   c.i3 = q % nb3;
   c.i4 = q / nb3;
+  if (causal) {
+    int acc = 0, tm = 0;
+    for (; tm < num_m - 1; ++tm) {
+      const int k = causal_kept(tm, num_n, bn);
+      if (r0 < acc + k) break;
+      acc += k;
+    }
+    c.tm = tm;
+    c.tn = r0 - acc;
+    return c;
+  }
   const int per_group = GEMM_GROUP_M * num_n;
   const int g = r0 / per_group;
   const int first_m = g * GEMM_GROUP_M;
@@ -163,7 +187,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int num_m = (p.M + GEMM_BM - 1) / GEMM_BM;
   const int num_n = (p.N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n * p.nb2 * p.nb3 * p.nb4;
+  const bool causal = (p.flags & GEMM_CAUSAL_SKIP) != 0;
+  const int per_problem = tiles_per_problem(p.flags, num_m, num_n, BN);
+  const int num_tiles = per_problem * p.nb2 * p.nb3 * p.nb4;
   const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
   int* status = p.status;
   const int m_limit = p.m_limit != nullptr ? *p.m_limit : 0x7fffffff;
@@ -199,7 +225,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3);
+        const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3, per_problem, causal, BN);
         const int m0 = tc.tm * GEMM_BM, n0 = tc.tn * BN;
         const int a2 = tc.i2 / p.a_div2;
         const int b2 = p.tile_group != nullptr ? p.tile_group[tc.tm] : tc.i2 / p.b_div2;
@@ -245,7 +271,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int local = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3);
+        const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3, per_problem, causal, BN);
         const int m0 = tc.tm * GEMM_BM;
         if (tile_skipped(p.flags, m0, tc.tn * BN, m_limit)) continue;
         int kb0, kb1;
@@ -299,7 +325,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint8_t* cbox = csmem + ew * GEMM_CBOX_BYTES;
     int local = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3);
+      const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3, per_problem, causal, BN);
       if (tile_skipped(p.flags, tc.tm * GEMM_BM, tc.tn * BN, m_limit)) continue;
       const int buf = local & 1;
       const uint32_t aphase = (local >> 1) & 1;
@@ -330,17 +356,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const __nv_bfloat16* auxrow = nullptr;
       if ((e_ds || e_axpby) && row < p.M)
         auxrow = p.aux + tc.i2 * p.sC2 + tc.i3 * p.sC3 + tc.i4 * p.sC4 + static_cast<long long>(row) * p.ldc;
+      const bool aux_aligned = auxrow != nullptr && (reinterpret_cast<uintptr_t>(auxrow) & 15) == 0;
       float run_m = -INFINITY, run_l = 0.f;
 #pragma unroll 1
       for (int c = 0; c < (BN / 2) / 32; ++c) {
         uint32_t r[32];
+        const int col0 = ncol0 + c * 32;
+        // AXPBY: this row's 32 aux values as four 16-byte loads, issued before the accumulator read so the two latencies overlap
+        uint4 ax[4];
+        const bool ax_wide = e_axpby && auxrow != nullptr && aux_aligned && col0 + 32 <= p.N;
+        if (ax_wide) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) ax[q] = *reinterpret_cast<const uint4*>(auxrow + col0 + 8 * q);
+        }
         tmem_ld_x32(taddr + c * 32, r);
         tmem_wait_ld();
         if (empty_k) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        const int col0 = ncol0 + c * 32;
         if (attn) {
           // keys this row may see inside the 32-column chunk: mask word ∧ causal ∧ in range
           unsigned bits = 0u;
@@ -401,7 +435,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
         }
-        if (e_axpby) {
+        if (ax_wide) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float f[8];
+            unpack8_bf16(ax[q], f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r[8 * q + i] = __float_as_uint(p.scale * __uint_as_float(r[8 * q + i]) + p.scale2 * f[i]);
+          }
+        } else if (e_axpby) {
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
             float lo = 0.f, hi = 0.f;
@@ -641,7 +683,7 @@ static int launch_gemm(const GemmArgs& g) {
   auto kern = cmb::gemm_bf16_kernel<BN, A_MN, B_MN>;
   static std::atomic<unsigned long long> attr_done{0};
   if (set_smem_limit_once_per_device(attr_done, reinterpret_cast<const void*>(kern), Cfg::SMEM_BYTES)) return 103;
-  const long long num_tiles = static_cast<long long>((g.M + cmb::GEMM_BM - 1) / cmb::GEMM_BM) * ((g.N + BN - 1) / BN) *
+  const long long num_tiles = static_cast<long long>(cmb::tiles_per_problem(g.flags, (g.M + cmb::GEMM_BM - 1) / cmb::GEMM_BM, (g.N + BN - 1) / BN, BN)) *
                               g.nb[0] * g.nb[1] * g.nb[2];
   if (num_tiles > 0x7fffffffLL) return 106;
   int grid = sm_count();
