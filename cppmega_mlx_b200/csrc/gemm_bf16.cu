@@ -46,6 +46,8 @@ enum : int {
   GEMM_EPI_EXP_MASK = 256,       // P = [mask] · exp(scale·acc − r[t])
   GEMM_EPI_DS = 512,             // dS = aux · (acc − r[t]) · scale   (aux has C's layout, bf16)
   GEMM_EPI_AXPBY = 1024,         // scale · acc + scale2 · aux        (aux has C's layout, bf16)
+  GEMM_EPI_AMAX = 4096,          // max |C| over the written elements (NaNs ignored) is folded into *amax with an integer atomicMax:
+                                 // the per-tensor FP8 scale of the product without a reduction pass over it
   GEMM_EPI_SYM_MIRROR = 2048,    // with CAUSAL_SKIP on a symmetric product (bf16 C): every element whose transposed position lies
                                  // in a skipped tile is also stored there, so the full matrix exists after one launch
 };
@@ -68,6 +70,7 @@ struct GemmParams {
   const int* tile_group;     // grouped (MoE) mode: B's dim-2 index for each 128-row tile of A / C; nullptr = batched rule
   const int* k_ranges;       // grouped wgrad: contraction range [k_begin, k_end) per dim-2 problem (multiples of 64)
   __nv_bfloat16* c_base;     // SYM_MIRROR: C as a plain pointer (the mirrored elements are stored with ordinary stores)
+  float* amax;               // EPI_AMAX: one fp32 word (non-negative floats order like their bit patterns)
   const int* m_limit;        // optional device scalar: row tiles starting at or beyond *m_limit are neither computed nor written
                              // (the used part of a statically sized, token-sorted buffer is only known on the device)
   int* status;
@@ -322,6 +325,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool attn = e_stats || e_expm || e_ds;
     const bool e_axpby = (p.flags & GEMM_EPI_AXPBY) != 0;
     const bool e_mirror = (p.flags & GEMM_EPI_SYM_MIRROR) != 0 && !out_f32;
+    const bool e_amax = (p.flags & GEMM_EPI_AMAX) != 0 && p.amax != nullptr;
     uint8_t* cbox = csmem + ew * GEMM_CBOX_BYTES;
     int local = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
@@ -358,6 +362,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         auxrow = p.aux + tc.i2 * p.sC2 + tc.i3 * p.sC3 + tc.i4 * p.sC4 + static_cast<long long>(row) * p.ldc;
       const bool aux_aligned = auxrow != nullptr && (reinterpret_cast<uintptr_t>(auxrow) & 15) == 0;
       float run_m = -INFINITY, run_l = 0.f;
+      float tile_amax = 0.f;
 #pragma unroll 1
       for (int c = 0; c < (BN / 2) / 32; ++c) {
         uint32_t r[32];
@@ -479,6 +484,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int j = 0; j < 32; ++j)
             if (col0 + j < p.N) cm[static_cast<long long>(col0 + j) * p.ldc] = __float2bfloat16(__uint_as_float(r[j]));
         }
+        if (e_amax && row < p.M) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float a = fabsf(__uint_as_float(r[j]));
+            if (col0 + j < p.N && a == a) tile_amax = fmaxf(tile_amax, a);
+          }
+        }
         // Stage into the swizzled box: row `lane`, 16-byte chunk ch lands at chunk (ch ^ (lane & 7)).
         const bool new_box = out_f32 || (c & 1) == 0;
         if (new_box) {
@@ -517,6 +529,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tma_store_commit();
           }
         }
+      }
+      if (e_amax) {
+        tile_amax = warp_max(tile_amax);
+        if (lane == 0 && tile_amax > 0.f) atomicMax(reinterpret_cast<unsigned int*>(p.amax), __float_as_uint(tile_amax));
       }
       if (e_stats && row < p.M) {
         const long long prob = (static_cast<long long>(tc.i4) * p.nb3 + tc.i3) * p.nb2 + tc.i2;
@@ -649,6 +665,7 @@ struct GemmArgs {
   const int* tile_group;
   const int* k_ranges;
   const int* m_limit;
+  float* amax;
   int b_groups;  // grouped mode: number of dim-2 slices of B (independent of the problem batch count)
   int* status;
   int max_ctas;
@@ -703,6 +720,7 @@ static int launch_gemm(const GemmArgs& g) {
   p.tile_group = g.tile_group; p.k_ranges = g.k_ranges;
   p.c_base = static_cast<__nv_bfloat16*>(g.C);
   p.m_limit = g.m_limit;
+  p.amax = g.amax;
   p.status = g.status;
   kern<<<grid, cmb::GEMM_THREADS, Cfg::SMEM_BYTES, g.stream>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 104;
@@ -746,7 +764,7 @@ extern "C" int cmb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
 
 // Batched form. `ip` = {M, N, K, a_mn, b_mn, flags, a_div2, b_div2, max_ctas, mask_words, b_groups, number of `pp` entries}; `lp` = {lda, ldb, ldc, nb2,
 // nb3, nb4, sA2, sA3, sA4, sB2, sB3, sB4, sC2, sC3, sC4, sv2, sv3, sv4, mask_sb} (element counts / strides).
-// `pp` = {row_vec, col_vec, aux, mask, stats, tile_group, k_ranges, m_limit} device pointers (any may be null). Flags select the
+// `pp` = {row_vec, col_vec, aux, mask, stats, tile_group, k_ranges, m_limit, amax} device pointers (any may be null). Flags select the
 // epilogue, see the enum at the top of this file. Grouped (MoE) use: `tile_group[i]` names B's dim-2 slice for the i-th
 // 128-row tile of A/C (A and C plain 2-D, B stacked per expert); `k_ranges[2e], k_ranges[2e+1]` bound the contraction
 // of dim-2 problem e (wgrad over one expert's rows of the token-sorted buffers).
@@ -765,6 +783,8 @@ extern "C" int cmb_gemm_bf16_batched(const void* A, const void* B, void* C, cons
   g.aux = pp[2]; g.mask = static_cast<const unsigned*>(pp[3]); g.stats = static_cast<float*>(const_cast<void*>(pp[4]));
   g.tile_group = static_cast<const int*>(pp[5]); g.k_ranges = static_cast<const int*>(pp[6]);
   g.m_limit = ip[11] >= 8 ? static_cast<const int*>(pp[7]) : nullptr;   // ip[11]: how many entries `pp` holds (older callers pass 7)
+  g.amax = ip[11] >= 9 ? static_cast<float*>(const_cast<void*>(pp[8])) : nullptr;
+  if ((g.flags & cmb::GEMM_EPI_AMAX) && g.amax == nullptr) return 108;
   g.b_groups = ip[10];
   if (g.tile_group != nullptr && g.b_groups <= 0) return 109;
   g.scale = scale;

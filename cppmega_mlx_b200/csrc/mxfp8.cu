@@ -27,28 +27,9 @@ __device__ __forceinline__ long long sf_tiled_offset(int r, int kb, int kblocks1
   return (static_cast<long long>(r >> 7) * kblocks128 + (kb >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (kb & 3);
 }
 
-// One thread per 8 elements; four threads (one quad) per 32-element block.
-__global__ void mxfp8_quant_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
-                                   uint8_t* __restrict__ sf_tiled, uint8_t* __restrict__ sf_plain, int rows, int cols) {
-  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int per_row = cols >> 3;
-  const long long r = gid / per_row;
-  const int c8 = static_cast<int>(gid % per_row);
-  const bool live = r < rows;
-  float v[8];
-  if (live) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(x + r * ldx + c8 * 8);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = __bfloat1622float2(h[i]);
-      v[2 * i] = f.x;
-      v[2 * i + 1] = f.y;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = 0.f;
-  }
+// Quantise the 8 values of this thread (one quad = one 32-element block) and store data + scale byte.
+__device__ __forceinline__ void mxfp8_quant8(const float (&v)[8], bool live, uint8_t* __restrict__ q, long long ldq, uint8_t* __restrict__ sf_tiled,
+                                             uint8_t* __restrict__ sf_plain, long long r, int c8, int cols) {
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
@@ -82,6 +63,58 @@ __global__ void mxfp8_quant_kernel(const __nv_bfloat16* __restrict__ x, long lon
       if (sf_plain != nullptr) sf_plain[r * (cols >> 5) + kb] = byte;
     }
   }
+}
+
+// One thread per 8 elements; four threads (one quad) per 32-element block.
+__global__ void mxfp8_quant_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
+                                   uint8_t* __restrict__ sf_tiled, uint8_t* __restrict__ sf_plain, int rows, int cols) {
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int per_row = cols >> 3;
+  const long long r = gid / per_row;
+  const int c8 = static_cast<int>(gid % per_row);
+  const bool live = r < rows;
+  float v[8];
+  if (live) {
+    unpack8_bf16(*reinterpret_cast<const uint4*>(x + r * ldx + c8 * 8), v);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.f;
+  }
+  mxfp8_quant8(v, live, q, ldq, sf_tiled, sf_plain, r, c8, cols);
+}
+
+// SwiGLU and the quantiser of the following block-scaled product in one pass: gu [rows, 2H] = [gate | up] → y = silu(gate)·up as
+// bf16 [rows, H] (kept for the backward pass) and the same values (after the bf16 rounding, so the result is bit-identical to
+// quantising y in a second pass) as e4m3 + e8m0 scales.  Saves one read of y per expert layer.
+__global__ void swiglu_mxfp8_quant_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ q,
+                                          uint8_t* __restrict__ sf_tiled, int rows, int H) {
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int per_row = H >> 3;
+  const long long r = gid / per_row;
+  const int c8 = static_cast<int>(gid % per_row);
+  const bool live = r < rows;
+  float v[8];
+  if (live) {
+    float g[8], u[8];
+    unpack8_bf16(*reinterpret_cast<const uint4*>(gu + r * 2 * H + c8 * 8), g);
+    unpack8_bf16(*reinterpret_cast<const uint4*>(gu + r * 2 * H + H + c8 * 8), u);
+    uint4 o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = g[2 * i] / (1.f + __expf(-g[2 * i])) * u[2 * i], b = g[2 * i + 1] / (1.f + __expf(-g[2 * i + 1])) * u[2 * i + 1];
+      const __nv_bfloat162 h2 = __floats2bfloat162_rn(a, b);
+      ow[i] = *reinterpret_cast<const uint32_t*>(&h2);
+      const float2 back = __bfloat1622float2(h2);
+      v[2 * i] = back.x;
+      v[2 * i + 1] = back.y;
+    }
+    *reinterpret_cast<uint4*>(y + r * H + c8 * 8) = o;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.f;
+  }
+  mxfp8_quant8(v, live, q, H, sf_tiled, nullptr, r, c8, H);
 }
 
 __global__ void mxfp8_dequant_kernel(const uint8_t* __restrict__ q, long long ldq, const uint8_t* __restrict__ sf_tiled,
@@ -340,6 +373,18 @@ extern "C" int cmb_mxfp8_quant(const void* x, long long ldx, void* q, long long 
   cmb::mxfp8_quant_kernel<<<static_cast<unsigned>(grid), block, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(q), ldq, static_cast<uint8_t*>(sf_tiled),
       static_cast<uint8_t*>(sf_plain), rows, cols);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// gu bf16 [rows, 2H] contiguous → y bf16 [rows, H], q e4m3 [rows, H], tiled scales (zeroed once by the caller).  H % 32 == 0.
+extern "C" int cmb_swiglu_mxfp8_quant(const void* gu, void* y, void* q, void* sf_tiled, int rows, int H, void* stream) {
+  if (rows <= 0 || H <= 0) return 0;
+  if (H % 32) return -1;
+  const long long threads = static_cast<long long>(rows) * (H / 8);
+  const long long grid = (threads + 255) / 256;
+  if (grid > 0x7fffffffLL) return -3;
+  cmb::swiglu_mxfp8_quant_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(y), static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf_tiled), rows, H);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

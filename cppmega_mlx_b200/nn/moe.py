@@ -290,8 +290,9 @@ class MoE(nn.Module):
         if self.config.expert_gemm == "mxfp8":
             from ..ops import mxfp8 as MX
             if MX.grouped_mxfp8_supported(xp, self.experts.w_gate_up) and self.experts.w_down.shape[2] % 128 == 0:
-                h = ops.swiglu(MX.grouped_linear_padded_mxfp8(xp, self.experts.w_gate_up, layout))
-                return MX.grouped_linear_padded_mxfp8(h, self.experts.w_down, layout)
+                # the SwiGLU kernel also emits the e4m3 data and e8m0 scales the down product consumes: no quantiser pass over h
+                h, hq = MX.swiglu_with_mxfp8(MX.grouped_linear_padded_mxfp8(xp, self.experts.w_gate_up, layout))
+                return MX.grouped_linear_padded_mxfp8(h, self.experts.w_down, layout, x_quantized=hq)
         h = ops.swiglu(GG.grouped_linear_padded(xp, self.experts.w_gate_up, layout))
         return GG.grouped_linear_padded(h, self.experts.w_down, layout)
 

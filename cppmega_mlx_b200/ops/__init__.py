@@ -11,6 +11,7 @@ from .mamba3_scan import mamba3_scan, mamba3_scan_chunked, mamba3_scan_sequentia
 from .norm import add_rms_norm, layer_norm_ref, rms_norm, rms_norm_ref
 from .rope import RopeScaling, apply_rope, apply_rope_reference, rope_inv_freq, rope_tables, rope_tables_at, yarn_attention_factor
 from .sparse_mla import indices_to_mask, sparse_mla_attention, sparse_mla_masked_dense, sparse_mla_reference
+from .fp8_scale import fp8_amax, fp8_pack, fp8_quantize, linear_with_amax
 from .sparse_mla_blockscaled import mxfp8_roundtrip_ste, sparse_mla_blockscaled
 from . import decode_attention  # module: decode_attention.decode_attention(...) / .decode_attention_reference(...)
 from .topk import topk_select, topk_select_reference

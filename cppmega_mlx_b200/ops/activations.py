@@ -14,6 +14,15 @@ def swiglu_reference(gu: torch.Tensor) -> torch.Tensor:
     return F.silu(g) * u
 
 
+def swiglu_backward(gy2: torch.Tensor, gu2: torch.Tensor) -> torch.Tensor:
+    """Gradient of ``silu(gate)·up`` w.r.t. the packed ``[gate | up]`` input; both 2-D contiguous bf16 on the GPU."""
+    lib = B.load_library()
+    rows, two_h = gu2.shape
+    ggu = torch.empty_like(gu2)
+    B.check(lib.cmb_swiglu_bwd(B.ptr(gy2), B.ptr(gu2), B.ptr(ggu), ctypes.c_int64(rows), two_h // 2, B.stream_ptr()), "swiglu_bwd")
+    return ggu
+
+
 class _SwiGLUFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, gu):
@@ -28,14 +37,10 @@ class _SwiGLUFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, gy):
-        lib = B.load_library()
         (gu2,) = ctx.saved_tensors
         rows, two_h = gu2.shape
         gy2 = gy.reshape(rows, two_h // 2).contiguous()
-        ggu = torch.empty_like(gu2)
-        B.check(lib.cmb_swiglu_bwd(B.ptr(gy2), B.ptr(gu2), B.ptr(ggu), ctypes.c_int64(rows), two_h // 2, B.stream_ptr()),
-                "swiglu_bwd")
-        return ggu.view(ctx.shape)
+        return swiglu_backward(gy2, gu2).view(ctx.shape)
 
 
 def swiglu(gu: torch.Tensor) -> torch.Tensor:

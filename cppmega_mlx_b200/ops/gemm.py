@@ -69,6 +69,7 @@ EPI_SOFTMAX_STATS = 128
 EPI_EXP_MASK = 256
 EPI_DS = 512
 EPI_AXPBY = 1024
+EPI_AMAX = 4096         # max |C| of the written elements is folded into a device scalar from the epilogue (per-tensor FP8 scale without a pass over C)
 EPI_SYM_MIRROR = 2048   # with CAUSAL_SKIP on a symmetric product: the skipped tiles are filled from the computed ones in the same launch
 
 
@@ -80,7 +81,7 @@ def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, 
                  mask: torch.Tensor | None = None, mask_words: int = 0, mask_sb: int = 0, scale: float = 1.0,
                  scale2: float = 0.0, stats: torch.Tensor | None = None, out_f32: bool | None = None,
                  tile_group: torch.Tensor | None = None, k_ranges: torch.Tensor | None = None, b_groups: int = 0,
-                 m_limit: torch.Tensor | None = None) -> torch.Tensor | None:
+                 m_limit: torch.Tensor | None = None, amax: torch.Tensor | None = None) -> torch.Tensor | None:
     """Strided-batched C (+)= A·Bᵀ. ``a``/``b``/``out`` only supply base pointers; all geometry is explicit:
     pitches ``ld*`` and per-operand element strides over the three batch dims ``nb = (n2, n3, n4)``.
     ``a_div2``/``b_div2`` let ``div`` consecutive dim-2 problems share one operand slice (the operand then has
@@ -95,9 +96,13 @@ def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None, *, 
     fl = flags | (OUT_F32 if f32 else 0) | (ACCUMULATE if accumulate else 0)
     if row_vec is not None and not (flags & (EPI_EXP_MASK | EPI_DS)):
         fl |= EPI_DECAY_MASK if col_vec is not None else EPI_ROW_EXP
-    ip = (ctypes.c_int * 12)(M, N, K, int(a_mn), int(b_mn), fl, a_div2, b_div2, max_ctas, mask_words, int(b_groups), 8)
+    if amax is not None:
+        if amax.dtype != torch.float32 or amax.numel() != 1 or not amax.is_cuda:
+            raise ValueError("amax must be a one-element fp32 CUDA tensor")
+        fl |= EPI_AMAX
+    ip = (ctypes.c_int * 12)(M, N, K, int(a_mn), int(b_mn), fl, a_div2, b_div2, max_ctas, mask_words, int(b_groups), 9)
     lp = (ctypes.c_longlong * 19)(lda, ldb, ldc, *nb, *sA, *sB, *sC, *sv, mask_sb)
-    pp = (ctypes.c_void_p * 8)(*(None if t is None else t.data_ptr() for t in (row_vec, col_vec, aux, mask, stats, tile_group, k_ranges, m_limit)))
+    pp = (ctypes.c_void_p * 9)(*(None if t is None else t.data_ptr() for t in (row_vec, col_vec, aux, mask, stats, tile_group, k_ranges, m_limit, amax)))
     st = B.status_buffer(a.device)
     rc = lib.cmb_gemm_bf16_batched(B.ptr(a), B.ptr(b), B.ptr(out), ip, lp, pp, ctypes.c_float(scale), ctypes.c_float(scale2), B.ptr(st),
                                    B.stream_ptr())

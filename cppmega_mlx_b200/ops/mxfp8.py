@@ -147,15 +147,72 @@ def gemm_mxfp8_grouped(a: MXFP8Tensor, w: MXFP8Tensor, tile_group: torch.Tensor,
     return out
 
 
+_WEIGHT_CACHE: dict = {}
+
+
+def quantize_weight_cached(w: torch.Tensor) -> MXFP8Tensor:
+    """Quantised copy of a stacked expert weight [E, N, K], reused until the parameter is written again (its version counter moves
+    with every optimizer step), so gradient-accumulation micro-batches and evaluation passes do not requantise it."""
+    key = (w.data_ptr(), tuple(w.shape))
+    hit = _WEIGHT_CACHE.get(key)
+    if hit is not None and hit[0] == w._version:
+        return hit[1]
+    E, N, K = w.shape
+    q = quantize_mxfp8(w.detach().reshape(E * N, K))
+    if len(_WEIGHT_CACHE) > 256:
+        _WEIGHT_CACHE.clear()
+    _WEIGHT_CACHE[key] = (w._version, q)
+    return q
+
+
+def swiglu_quantize_mxfp8(gu: torch.Tensor):
+    """``gu`` [R, 2H] bf16 → (``silu(gate)·up`` as bf16 [R, H], the same values as an ``MXFP8Tensor``) in one kernel
+    (``csrc/mxfp8.cu`` ``swiglu_mxfp8_quant_kernel``); bit-identical to ``quantize_mxfp8(swiglu(gu))``."""
+    R, H2 = gu.shape
+    H = H2 // 2
+    if not (B.on_gpu(gu) and gu.dtype == torch.bfloat16 and gu.is_contiguous() and H % BLOCK == 0):
+        raise ValueError("swiglu_quantize_mxfp8 needs a contiguous 2-D bf16 CUDA tensor whose half width is a multiple of 32")
+    lib = B.load_library()
+    y = torch.empty(R, H, dtype=torch.bfloat16, device=gu.device)
+    q = torch.empty(R, H, dtype=torch.uint8, device=gu.device)
+    sf = torch.zeros(((R + 127) // 128) * ((H + 127) // 128) * 512, dtype=torch.uint8, device=gu.device)
+    B.check(lib.cmb_swiglu_mxfp8_quant(B.ptr(gu), B.ptr(y), B.ptr(q), B.ptr(sf), R, H, B.stream_ptr()), "swiglu_mxfp8_quant")
+    return y, MXFP8Tensor(q, sf, (R, H))
+
+
+class _SwigluQuantFn(torch.autograd.Function):
+    """SwiGLU whose forward also emits the MXFP8 operand of the next product; backward is the SwiGLU backward kernel."""
+
+    @staticmethod
+    def forward(ctx, gu):
+        y, q = swiglu_quantize_mxfp8(gu)
+        ctx.save_for_backward(gu)
+        ctx.mark_non_differentiable(q.data, q.scales)
+        return y, q.data, q.scales
+
+    @staticmethod
+    def backward(ctx, gy, _gq, _gs):
+        from .activations import swiglu_backward
+        (gu,) = ctx.saved_tensors
+        return swiglu_backward(gy.contiguous(), gu)
+
+
+def swiglu_with_mxfp8(gu: torch.Tensor):
+    """(h, MXFP8Tensor of h) with autograd through h."""
+    y, qd, qs = _SwigluQuantFn.apply(gu.contiguous())
+    return y, MXFP8Tensor(qd, qs, tuple(y.shape))
+
+
 class _GroupedMXFP8Fn(torch.autograd.Function):
     """Grouped expert product with an MXFP8 forward (block-scaled tcgen05) and a bf16 straight-through backward."""
 
     @staticmethod
-    def forward(ctx, x, w, layout):
+    def forward(ctx, x, w, layout, xq_data, xq_scales):
         E, N, K = w.shape
         ctx.save_for_backward(x, w)
         ctx.layout = layout
-        return gemm_mxfp8_grouped(quantize_mxfp8(x), quantize_mxfp8(w.reshape(E * N, K)), layout.tile_group, E)
+        xq = MXFP8Tensor(xq_data, xq_scales, tuple(x.shape)) if xq_data is not None else quantize_mxfp8(x)
+        return gemm_mxfp8_grouped(xq, quantize_weight_cached(w), layout.tile_group, E)
 
     @staticmethod
     def backward(ctx, gy):
@@ -165,11 +222,13 @@ class _GroupedMXFP8Fn(torch.autograd.Function):
         gy = gy.contiguous()
         gx = GG._fwd(gy, w, L, True) if ctx.needs_input_grad[0] else None
         gw = GG._wgrad(gy, x, L, w.shape) if ctx.needs_input_grad[1] else None
-        return gx, gw, None
+        return gx, gw, None, None, None
 
 
-def grouped_linear_padded_mxfp8(x: torch.Tensor, w: torch.Tensor, layout) -> torch.Tensor:
-    return _GroupedMXFP8Fn.apply(x.contiguous(), w, layout)
+def grouped_linear_padded_mxfp8(x: torch.Tensor, w: torch.Tensor, layout, x_quantized: MXFP8Tensor | None = None) -> torch.Tensor:
+    """``x_quantized``: the MXFP8 form of ``x`` when a producer already made it (``swiglu_with_mxfp8``)."""
+    xq = x_quantized
+    return _GroupedMXFP8Fn.apply(x.contiguous(), w, layout, None if xq is None else xq.data, None if xq is None else xq.scales)
 
 
 def grouped_mxfp8_supported(x: torch.Tensor, w: torch.Tensor) -> bool:

@@ -114,3 +114,61 @@ def test_fp8_block_dequant_kernel_matches_reference():
     x = torch.randn(64, 1040, device="cuda").bfloat16()
     y = lin(x)
     assert torch.allclose(y.float(), x.float() @ ref[0].float().t(), rtol=2e-2, atol=5e-2)
+
+
+def test_fp8_amax_quantize_kernels_match_reference():
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops import fp8_scale as F8
+    torch.manual_seed(0)
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        x = (torch.randn(3, 1000, 257, device="cuda") * 5).to(dtype)
+        x[1, 7, 3] = float("nan")
+        n0 = B.launch_count("fp8_amax")
+        a = F8.fp8_amax(x)
+        assert B.launch_count("fp8_amax") == n0 + 1
+        assert float(a) == float(F8.fp8_amax_reference(x))
+        clean = torch.nan_to_num(x, nan=0.0)
+        q, scale = F8.fp8_pack(clean)
+        ref = F8.fp8_quantize_reference(clean, 448.0 / a.clamp_min(1e-12))
+        same = (q.view(torch.uint8) == ref.view(torch.uint8)).float().mean()
+        assert float(same) > 0.999, float(same)          # the two differ only where x·inv_scale sits on a rounding tie after fp32 rounding
+        assert float((q.float() - ref.float()).abs().max()) <= 32.0
+        assert abs(float(scale) - float(a) / 448) < 1e-6 * float(a)
+    B.check_status()
+
+
+def test_gemm_epilogue_amax_matches_a_pass_over_the_product():
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B
+    torch.manual_seed(1)
+    for (M, N, K) in ((300, 520, 256), (4096, 2048, 1024)):
+        x = torch.randn(M, K, device="cuda").bfloat16()
+        w = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+        y, am = ops.linear_with_amax(x, w)
+        ref = ops.linear(x, w)
+        assert torch.equal(y, ref)
+        # the epilogue sees the fp32 accumulator, the reference the bf16-rounded output
+        assert abs(float(am) - float(ref.float().abs().max())) <= 2 ** -7 * float(am)
+        # folding: a second product into the same scalar keeps the larger value
+        y2, am2 = ops.linear_with_amax(x * 0.01, w, am.clone())
+        assert float(am2) == float(am)
+    B.check_status()
+
+
+def test_swiglu_quant_fused_equals_two_passes_and_moe_uses_it():
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops import mxfp8 as MX
+    torch.manual_seed(2)
+    gu = (torch.randn(700, 2 * 1408, device="cuda") * 2).bfloat16().requires_grad_()
+    h, hq = MX.swiglu_with_mxfp8(gu)
+    ref = ops.swiglu(gu.detach())
+    assert torch.equal(h, ref)
+    two = MX.quantize_mxfp8(ref)
+    assert torch.equal(hq.data, two.data) and torch.equal(hq.scales, two.scales)
+    g = torch.randn_like(h)
+    h.backward(g)
+    gr = gu.detach().clone().requires_grad_()
+    ops.swiglu(gr).backward(g)
+    assert torch.equal(gu.grad, gr.grad)
+    B.check_status()

@@ -261,3 +261,26 @@ def test_sparse_mla_blockscaled_roundtrip_semantics():
     q3, kv3 = torch.randn(1, 4, 2, 24), torch.randn(1, 4, 1, 24)
     i3 = torch.arange(4).view(1, 1, 1, 4).expand(1, 4, 1, 4).int().contiguous()
     assert torch.equal(ops.sparse_mla_blockscaled(q3, kv3, i3)[0], ops.sparse_mla_attention(q3, kv3, i3)[0])
+
+
+def test_fp8_amax_quantize_pack_oracle():
+    """Per-tensor FP8 scaling on the CPU path: NaNs are ignored by the abs-max, quantise clamps to ±448 and rounds to e4m3, and
+    pack's scale reproduces the tensor to e4m3 precision."""
+    import torch
+    from cppmega_mlx_b200 import ops
+    x = torch.randn(7, 33) * 3
+    x[2, 5] = float("nan")
+    x[0, 0] = -37.5
+    a = ops.fp8_amax(x)
+    assert a.shape == (1,) and float(a) == 37.5
+    joint = ops.fp8_amax(torch.full((3,), 50.0), out=a.clone())
+    assert float(joint) == 50.0
+    clean = torch.nan_to_num(x, nan=0.0)
+    q = ops.fp8_quantize(clean, 1000.0)
+    assert q.dtype == torch.float8_e4m3fn and float(q.float().abs().max()) == 448.0
+    q2, scale = ops.fp8_pack(clean)
+    assert abs(float(scale) - 37.5 / 448) < 1e-7
+    back = q2.float() * scale
+    assert float((back - clean).abs().max()) <= 37.5 / 448 * 16 + 1e-6        # half an ulp at the top binade (ulp = 32 · scale)
+    y, am = ops.linear_with_amax(torch.randn(5, 16), torch.randn(8, 16))
+    assert abs(float(am) - float(y.abs().max())) < 1e-6
