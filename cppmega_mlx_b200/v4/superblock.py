@@ -72,16 +72,16 @@ def _build(kind: str, d: int, p: dict) -> nn.Module:
         return V.KimiDeltaAttentionBlock(V.LinearAttentionConfig(d, **p))
     if kind == "nsa":
         h = _heads(d, p)
-        return V.NativeSparseAttentionV4(V.NSAConfig(d, h, d // h, **{k: v for k, v in p.items() if k != "num_heads"}))
+        return V.NativeSparseAttentionV4(V.NSAConfig(d, h, int(p.get("head_dim", d // h)), **{k: v for k, v in p.items() if k not in ("num_heads", "head_dim")}))
     if kind == "csa_hca":
         h = _heads(d, p)
-        return V.CSAHCAHybridV4(V.CSAHCAConfig(d, h, d // h, **{k: v for k, v in p.items() if k != "num_heads"}))
+        return V.CSAHCAHybridV4(V.CSAHCAConfig(d, h, int(p.get("head_dim", d // h)), **{k: v for k, v in p.items() if k not in ("num_heads", "head_dim")}))
     if kind == "lightning_indexer":
         return _IndexedCSAHCA(d, p)
     if kind == "engram":
         return V.EngramV4Block(V.EngramV4Config(d, **p))
     if kind == "mlp":
-        return _Normed(d, FeedForward(d, int(p.get("hidden", 4 * d)), p.get("activation", "swiglu")))
+        return _Normed(d, FeedForward(d, int(p.get("hidden", p.get("intermediate_size", 4 * d))), p.get("activation", "swiglu")))
     if kind == "moe":
         cfg = MoEConfig(d_model=d, **{"activation": "swiglu", "scoring": "sigmoid", "aux_loss_free": True, **p})
         return _Normed(d, MoE(cfg), pick=lambda o: o.output)

@@ -155,3 +155,56 @@ def test_bench_matrix_runs_cells_in_fresh_processes_and_renders(tmp_path):
              {"dtype": "f", "optimizer": "o", "loss_backend": "l", "path": "eager", "status": "ok", "tokens_per_second": 10.0}]
     BM.add_ratios(cells)
     assert cells[0]["ratio_vs_eager"] == 3.0 and "ratio_vs_eager" not in cells[1]
+
+
+def test_v4_parquet_smoke_runs_the_whole_block_cohort_and_writes_a_receipt(capsys, tmp_path):
+    """The V4 smoke builds engram + GDN + KDA + attention + NSA + CSA/HCA + MoE + MLP from the reference's template parameters
+    (head_dim, intermediate_size, use_short_conv, …), reads a token parquet and returns finite losses and timings."""
+    from cppmega_mlx_b200.cli import v4_parquet_smoke as S
+    pq = tmp_path / "tokens.parquet"
+    S.write_synthetic_parquet(pq, rows=6, row_len=49, vocab_size=300)
+    rc = S.main(["--parquet", str(pq), "--hidden-size", "128", "--layers", "6", "--vocab-size", "300", "--seq-len", "48", "--steps", "2",
+                 "--device", "cpu", "--out", str(tmp_path / "reports")])
+    assert rc == 0
+    rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rec["total_blocks"] == 8 and rec["steps"] == 2 and len(rec["per_step"]) == 2
+    assert all(np.isfinite(s["loss"]) and s["total_ms"] > 0 for s in rec["per_step"])
+    assert rec["tokens_per_sec"] > 0
+    assert len(list((tmp_path / "reports").glob("v4_parquet_smoke_h128_L6_*.json"))) == 1
+    assert S.main(["--parquet", str(tmp_path / "missing.parquet"), "--device", "cpu"]) == 1
+    with pytest.raises(ValueError):          # token ids must fit the vocabulary
+        S.main(["--parquet", str(pq), "--hidden-size", "128", "--layers", "6", "--vocab-size", "100", "--seq-len", "48", "--steps", "1", "--device", "cpu"])
+
+
+def test_train_step_receipt_harness_gates_and_optimizer_table(capsys, tmp_path):
+    """The receipt harness on a synthetic shard: steps run, the throughput and acceptance gates are evaluated (a synthetic, shallow,
+    3-step fp32 run can never be accepted), the optimizer table lists all eight choices, and --require-acceptance turns the
+    refusal into a non-zero exit code."""
+    from cppmega_mlx_b200.cli import m04_train_step as M
+    common = ["--synthetic", "--model-profile", "custom", "--vocab-size", "256", "--hidden-size", "32", "--pattern", "MA", "--depth", "2",
+              "--num-attention-heads", "2", "--steps", "3", "--batch-size", "2", "--seq-len", "16", "--dtype", "float32", "--device", "cpu",
+              "--json"]
+    out = tmp_path / "receipt.json"
+    assert M.main(common + ["--output", str(out)]) == 0
+    rec = json.loads(out.read_text())
+    assert rec["status"] == "ok" and len(rec["steps"]) == 3 and np.isfinite(rec["final_loss"])
+    assert rec["acceptance_gate"]["accepted"] is False and "real_parquet_source" in rec["acceptance_gate"]["failed"]
+    assert rec["throughput_claim_gate"]["status"] == "pass" and len(rec["optimizer"]["table"]) == 8
+    assert "kernel_dispatch" in rec
+    capsys.readouterr()
+    assert M.main(common + ["--output", str(tmp_path / "r2.json"), "--require-acceptance"]) != 0
+    assert M.main(common + ["--output", str(tmp_path / "dry.json"), "--dry-run-json"]) == 0
+    assert json.loads((tmp_path / "dry.json").read_text())["status"] == "dry_run"
+
+
+def test_parity_manifest_cli_is_fail_closed_without_an_artifact(capsys, tmp_path):
+    from cppmega_mlx_b200.cli import parity_manifest as P
+    out = tmp_path / "mtp.json"
+    rc = P.main(["mtp", "--tiny", "--no-artifact", "--device", "cpu", "--output", str(out), "--json"])
+    man = json.loads(out.read_text())
+    assert man["status"] == "blocked" and man["reference"]["artifact_preflight_status"] == "not_supplied"
+    assert np.isfinite(man["local"]["loss_values"]["total_loss"])
+    assert rc != 0 or man["status"] == "blocked"
+    out2 = tmp_path / "fwd.json"
+    P.main(["forward", "--tiny", "--no-artifact", "--device", "cpu", "--output", str(out2)])
+    assert json.loads(out2.read_text())["status"] in ("blocked", "refused")
