@@ -103,9 +103,11 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const __nv_bfloat16* _
 }
 
 // One warp per token t: out[t] = Σ_j w[t,j] · ybuf[rank(t,j)][slot(t,j)]  (assignment index = t·k + j; a negative slot is skipped).
+// `rows_out` (optional, [tokens·k, d]) also receives every gathered row unweighted (zeros for a skipped slot): what the backward
+// pass of the weighted sum needs, written in the same pass instead of by a separate gather.
 __global__ void __launch_bounds__(256) ep_combine_kernel(TePeers ybufs, const int* __restrict__ src_rank, const long long* __restrict__ src_slot,
                                                           const float* __restrict__ w, __nv_bfloat16* __restrict__ out, long long tokens, int k,
-                                                          int d, long long rows, int world, int* status) {
+                                                          int d, long long rows, int world, int* status, __nv_bfloat16* __restrict__ rows_out) {
   const int lane = threadIdx.x & 31;
   const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
@@ -117,14 +119,16 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(TePeers ybufs, const in
       for (int j = 0; j < k; ++j) {
         const long long a = t * k + j;
         const long long slot = src_slot[a];
-        if (slot < 0) continue;
         const int sr = src_rank[a];
-        if (slot >= rows || sr < 0 || sr >= world) {
-          if (c == lane * 8) te_report(status, a, slot, sr, lane);
+        const bool bad = slot >= 0 && (slot >= rows || sr < 0 || sr >= world);
+        if (slot < 0 || bad) {
+          if (bad && c == lane * 8) te_report(status, a, slot, sr, lane);
+          if (rows_out != nullptr) *reinterpret_cast<uint4*>(rows_out + a * d + c) = make_uint4(0u, 0u, 0u, 0u);
           continue;
         }
         const float wj = w != nullptr ? w[a] : 1.f;
         const uint4 q = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(ybufs.p[sr]) + slot * d + c);
+        if (rows_out != nullptr) *reinterpret_cast<uint4*>(rows_out + a * d + c) = q;
         const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&q);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -177,6 +181,22 @@ __global__ void __launch_bounds__(256) ep_combine_bwd_kernel(TePeers ybufs, cons
   }
 }
 
+// Private copy of a receive buffer: rows that hold an assignment are copied, padding rows inside the used part become zero, rows at
+// or beyond *used_end (unused capacity; nothing downstream reads them) are left alone.  One warp per row.
+__global__ void __launch_bounds__(256) ep_take_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                                       const unsigned char* __restrict__ valid, const int* __restrict__ used_end, long long rows,
+                                                       int d) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long limit = used_end != nullptr ? min(static_cast<long long>(*used_end), rows) : rows;
+  for (long long r = warp; r < limit; r += nwarps) {
+    const bool v = valid[r] != 0;
+    for (int c = lane * 8; c < d; c += 256)
+      *reinterpret_cast<uint4*>(dst + r * d + c) = v ? *reinterpret_cast<const uint4*>(src + r * d + c) : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
 static bool te_fill(TePeers& out, const long long* ptrs, int world) {
   if (world <= 0 || world > TE_MAX_RANKS) return false;
   for (int r = 0; r < TE_MAX_RANKS; ++r) out.p[r] = r < world ? reinterpret_cast<void*>(ptrs[r]) : nullptr;
@@ -216,7 +236,26 @@ extern "C" int cmb_ep_combine(const long long* ybuf_ptrs, int world, const int* 
   if (!cmb::te_fill(bufs, ybuf_ptrs, world) || (d & 7) || rows < 0) return 1;
   if (tokens <= 0) return 0;
   cmb::ep_combine_kernel<<<cmb::te_grid(tokens, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      bufs, src_rank, src_slot, w, static_cast<__nv_bfloat16*>(out), tokens, k, d, rows, world, status);
+      bufs, src_rank, src_slot, w, static_cast<__nv_bfloat16*>(out), tokens, k, d, rows, world, status, nullptr);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+extern "C" int cmb_ep_take(const void* src, void* dst, const void* valid, const int* used_end, long long rows, int d, void* stream) {
+  if (rows <= 0) return 0;
+  if (d & 7) return 1;
+  cmb::ep_take_kernel<<<cmb::te_grid(rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), static_cast<const unsigned char*>(valid), used_end, rows, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// The weighted combine that also keeps the gathered rows (training forward).
+extern "C" int cmb_ep_combine_rows(const long long* ybuf_ptrs, int world, const int* src_rank, const long long* src_slot, const float* w, void* out,
+                                   void* rows_out, long long tokens, int k, int d, long long rows, int* status, void* stream) {
+  cmb::TePeers bufs;
+  if (!cmb::te_fill(bufs, ybuf_ptrs, world) || (d & 7) || rows < 0) return 1;
+  if (tokens <= 0) return 0;
+  cmb::ep_combine_kernel<<<cmb::te_grid(tokens, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      bufs, src_rank, src_slot, w, static_cast<__nv_bfloat16*>(out), tokens, k, d, rows, world, status, static_cast<__nv_bfloat16*>(rows_out));
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

@@ -48,9 +48,11 @@ class FusedEPComm:
         self.dropped: torch.Tensor | None = None
 
     # -- kernels ---------------------------------------------------------------------------------
-    def dispatch_rows(self, buf: SymmetricBuffer, rows: torch.Tensor, tok: torch.Tensor, dest_rank: torch.Tensor, dest_slot: torch.Tensor) -> None:
+    def dispatch_rows(self, buf: SymmetricBuffer, rows: torch.Tensor, tok: torch.Tensor, dest_rank: torch.Tensor, dest_slot: torch.Tensor,
+                      scale: torch.Tensor | None = None) -> None:
+        """Row ``tok[a]`` of ``rows`` (times ``scale[a]`` if given, fp32 per assignment) → peer ``dest_rank[a]``, row ``dest_slot[a]``."""
         lib = B.load_library()
-        B.check(lib.cmb_ep_dispatch(B.ptr(rows), B.ptr(tok), B.ptr(dest_rank), B.ptr(dest_slot), None, buf.peer_ptrs, self.world,
+        B.check(lib.cmb_ep_dispatch(B.ptr(rows), B.ptr(tok), B.ptr(dest_rank), B.ptr(dest_slot), B.ptr(scale), buf.peer_ptrs, self.world,
                                     I64(tok.numel()), self.d, I64(self.rows), B.ptr(B.status_buffer(self.device)), B.stream_ptr()),
                 "ep_dispatch")
 
@@ -60,6 +62,16 @@ class FusedEPComm:
         B.check(lib.cmb_ep_combine(buf.peer_ptrs, self.world, B.ptr(src_rank), B.ptr(src_slot), None, B.ptr(out), I64(src_slot.numel()), 1, self.d,
                                    I64(self.rows), B.ptr(B.status_buffer(self.device)), B.stream_ptr()), "ep_gather")
         return out
+
+    def combine(self, buf: SymmetricBuffer, src_rank, src_slot, weights, tokens: int, k: int, keep_rows: bool = False):
+        """out[t] = Σ_j w[t,j] · buf[rank(t,j)][slot(t,j)] (w = 1 when ``weights`` is None) in one kernel; with ``keep_rows`` the
+        gathered rows [tokens·k, d] are written by the same pass and returned too."""
+        lib = B.load_library()
+        out = torch.empty(tokens, self.d, dtype=torch.bfloat16, device=self.device)
+        rows = torch.empty(tokens * k, self.d, dtype=torch.bfloat16, device=self.device) if keep_rows else None
+        B.check(lib.cmb_ep_combine_rows(buf.peer_ptrs, self.world, B.ptr(src_rank), B.ptr(src_slot), B.ptr(weights), B.ptr(out), B.ptr(rows),
+                                        I64(tokens), k, self.d, I64(self.rows), B.ptr(B.status_buffer(self.device)), B.stream_ptr()), "ep_combine")
+        return (out, rows) if keep_rows else out
 
     def combine_weighted(self, src_rank, src_slot, weights, tokens: int, k: int) -> torch.Tensor:
         """Inference form: gather + gate weighting + sum over k in one kernel (no autograd)."""
@@ -93,6 +105,7 @@ class FusedEPComm:
         # rows of my buffers that hold a real assignment (segment padding and unused capacity are not written by anyone)
         grp = tile_group.long().repeat_interleave(128)
         layout.valid_rows = (torch.arange(self.rows, device=e.device) - pad_off[r][grp]) < tot[r][grp]
+        layout.used_rows = pad_end[r][-1:].clamp(max=self.rows).int().contiguous()     # the products and copies stop here
         dropped = (~keep).sum()
         self.dropped = dropped if self.dropped is None else self.dropped + dropped
         return dest, slot, layout, dropped
@@ -104,22 +117,29 @@ class FusedEPComm:
         self.dropped = None
         return n
 
-    def take(self, buf: SymmetricBuffer, valid_rows: torch.Tensor) -> torch.Tensor:
-        """Private copy of a receive buffer with every row nobody wrote set to zero (one pass; the buffer is never cleared)."""
+    def take(self, buf: SymmetricBuffer, valid_rows: torch.Tensor, used_rows: torch.Tensor | None = None) -> torch.Tensor:
+        """Private copy of a receive buffer with every row nobody wrote set to zero (one pass; the buffer is never cleared).  With
+        ``used_rows`` (int32 device scalar) the rows at or beyond it — capacity no segment reaches — are neither read nor written:
+        the grouped products skip them by the same scalar."""
         t = buf.tensor.view(self.rows, self.d)
-        return torch.where(valid_rows[:, None], t, torch.zeros((), dtype=t.dtype, device=t.device))
+        lib = B.load_library()
+        if not hasattr(lib, "cmb_ep_take"):
+            return torch.where(valid_rows[:, None], t, torch.zeros((), dtype=t.dtype, device=t.device))
+        out = torch.empty_like(t)
+        B.check(lib.cmb_ep_take(B.ptr(t), B.ptr(out), B.ptr(valid_rows), B.ptr(used_rows), I64(self.rows), self.d, B.stream_ptr()), "ep_take")
+        return out
 
 
 class _Dispatch(torch.autograd.Function):
     """flat [T,d] → this rank's received rows [rows,d] (padded expert-sorted). Backward gathers the row gradients back."""
 
     @staticmethod
-    def forward(ctx, flat, tok, dest, slot, valid_rows, comm: FusedEPComm):
+    def forward(ctx, flat, tok, dest, slot, valid_rows, used_rows, comm: FusedEPComm):
         comm.dispatch_rows(comm.xbuf, flat, tok, dest, slot)
         comm.barrier()                                           # all rows for me have landed
         ctx.comm, ctx.T = comm, flat.shape[0]
         ctx.save_for_backward(tok, dest, slot)
-        return comm.take(comm.xbuf, valid_rows)
+        return comm.take(comm.xbuf, valid_rows, used_rows)
 
     @staticmethod
     def backward(ctx, g_rows):
@@ -127,9 +147,10 @@ class _Dispatch(torch.autograd.Function):
         comm = ctx.comm
         comm.xbuf.tensor.view(comm.rows, comm.d).copy_(g_rows)
         comm.barrier()                                           # every owner has published its row gradients
-        g = comm.gather_rows(comm.xbuf, dest, slot)              # [A,d]
+        k = tok.numel() // ctx.T                                 # assignments are token-major: a = t·k + j
+        g = comm.combine(comm.xbuf, dest, slot, None, ctx.T, k)  # Σ_j of the k row gradients of a token, gathered and summed in one pass
         comm.barrier()                                           # owners may reuse their buffers
-        return torch.zeros(ctx.T, comm.d, dtype=g.dtype, device=g.device).index_add_(0, tok, g), None, None, None, None, None
+        return g, None, None, None, None, None, None
 
 
 class _Gather(torch.autograd.Function):
@@ -154,15 +175,50 @@ class _Gather(torch.autograd.Function):
         return comm.take(comm.ybuf, valid_rows), None, None, None, None
 
 
+class _Combine(torch.autograd.Function):
+    """this rank's expert outputs [rows,d] + gate weights [T,k] → Σ_j w[t,j]·y(t,j) [T,d] in one kernel, which also keeps the gathered
+    rows for the weight gradient.  Backward: dw = ⟨g[t], row(t,j)⟩, and the row gradients w·g[t] go straight from ``g`` to the owners
+    (scaled inside the dispatch kernel): the [T·k, d] products of the unfused form are never materialised."""
+
+    @staticmethod
+    def forward(ctx, y_local, top_w, dest, slot, valid_rows, used_rows, comm: FusedEPComm):
+        T, k = top_w.shape
+        comm.ybuf.tensor.view(comm.rows, comm.d).copy_(y_local)
+        comm.barrier()                                           # every owner has published its outputs
+        w32 = top_w.float().contiguous()
+        out, rows = comm.combine(comm.ybuf, dest, slot, w32, T, k, keep_rows=True)
+        ctx.comm, ctx.w_dtype = comm, top_w.dtype
+        ctx.save_for_backward(dest, slot, valid_rows, w32, rows, used_rows)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        dest, slot, valid_rows, w32, rows, used_rows = ctx.saved_tensors
+        comm = ctx.comm
+        T, k = w32.shape
+        g = g.contiguous()
+        lib = B.load_library()
+        dw = torch.empty(T, k, dtype=torch.float32, device=g.device)
+        local = (ctypes.c_longlong * 1)(rows.data_ptr())         # the kept rows as a one-rank "buffer": dw[a] = ⟨g[a // k], rows[a]⟩
+        zero_rank = torch.zeros(T * k, dtype=torch.int32, device=g.device)
+        own_slot = torch.arange(T * k, dtype=torch.int64, device=g.device)
+        B.check(lib.cmb_ep_combine_bwd(local, 1, B.ptr(zero_rank), B.ptr(own_slot), B.ptr(g), B.ptr(dw), I64(T * k), k, comm.d, I64(T * k),
+                                       B.ptr(B.status_buffer(comm.device)), B.stream_ptr()), "ep_combine_bwd")
+        comm.barrier()                                           # every rank is past its reads of the previous contents
+        tok = own_slot // k
+        comm.dispatch_rows(comm.ybuf, g, tok, dest, slot, scale=w32.reshape(-1))
+        comm.barrier()
+        return comm.take(comm.ybuf, valid_rows, used_rows), dw.to(ctx.w_dtype), None, None, None, None, None
+
+
 def fused_ep_moe_forward(moe, comm: FusedEPComm, flat: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor) -> torch.Tensor:
     """Drop-in for ``parallel.ep.ep_moe_forward`` on GPUs sharing an NVSwitch domain."""
     T, k = top_idx.shape
     dest, slot, layout, _dropped = comm.plan(top_idx.reshape(-1))     # drops are counted in comm.dropped (see dropped_assignments)
     tok = torch.arange(T * k, device=flat.device) // k
-    xp = _Dispatch.apply(flat.contiguous(), tok, dest, slot, layout.valid_rows, comm)
+    xp = _Dispatch.apply(flat.contiguous(), tok, dest, slot, layout.valid_rows, layout.used_rows, comm)
     yp = moe.expert_ffn_padded(xp, layout)
-    rows = _Gather.apply(yp, dest, slot, layout.valid_rows, comm)                # [T·k, d] in assignment order
-    return (rows.view(T, k, -1) * top_w.to(rows.dtype)[..., None]).sum(1)
+    return _Combine.apply(yp, top_w, dest, slot, layout.valid_rows, layout.used_rows, comm)
 
 
 def enable_fused_ep(model: torch.nn.Module, group, device, *, max_tokens: int, capacity_factor: float | None = 2.0) -> FusedEPComm | None:

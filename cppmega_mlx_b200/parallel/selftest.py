@@ -308,6 +308,15 @@ def case_ep(rank, world, dev):
         dist.all_reduce(e, op=dist.ReduceOp.MAX)
         errs.append(float(e))
     t_nccl, t_fused = _time(lambda: run(False), iters=5), _time(lambda: run(True), iters=5)
+    if os.environ.get("CMB_EP_PROFILE") == "1":           # analysis aid: where the fused layer's time goes (rank 0, one forward + backward)
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            run(True)
+            torch.cuda.synchronize()
+        if rank == 0:
+            rows_ = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)[:30]
+            for e in rows_:
+                print(json.dumps({"kernel": e.key[:110], "ms": e.device_time_total / 1e3, "launches": e.count}))
     if rank == 0:
         print(json.dumps({"case": "ep", "world": world, "shape": {"tokens_per_rank": T, "d": d, "experts": E, "top_k": k, "hidden": hid},
                           "rel_err_vs_nccl[y,dx,dw_gate_up,dw_down,dw_router]": errs, "ms_fwd_bwd_nccl": t_nccl, "ms_fwd_bwd_fused": t_fused}))
