@@ -204,6 +204,38 @@ __global__ void __launch_bounds__(256) m3_finalize_fwd_w8_kernel(const float* __
   }
 }
 
+// Intra-chunk matrices of all heads of a group from the group's score tile:  M[b,c,h,t,s] = CB[b,c,g,t,s] · exp(cum_h[t] − cum_h[s]) · [s ≤ t].
+// C·Bᵀ is shared by the H/G heads of a group, so it is formed once per group (fp32) and expanded here per head, instead of running
+// the product once per head with the decay in its epilogue (8× the tiles, each bound by that epilogue).  One thread per 8 columns.
+__global__ void __launch_bounds__(256) m3_expand_decay_kernel(const float* __restrict__ CB, const float* __restrict__ cum,
+                                                               __nv_bfloat16* __restrict__ M, int Bn, int nc, int H, int G, int L) {
+  const int l8 = L >> 3, hg = H / G;
+  const long long n8 = static_cast<long long>(Bn) * nc * H * L * l8;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int s = static_cast<int>(i % l8) * 8;
+    const long long row = i / l8;                 // ((b·nc + c)·H + h)·L + t
+    const int t = static_cast<int>(row % L);
+    const long long bch = row / L;
+    const int h = static_cast<int>(bch % H);
+    const long long bc = bch / H;
+    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+    if (s <= t) {
+      const float* cb = CB + ((bc * G + h / hg) * L + t) * L + s;
+      const float* cr = cum + bch * L;
+      const float4 a0 = *reinterpret_cast<const float4*>(cb), a1 = *reinterpret_cast<const float4*>(cb + 4);
+      const float4 c0 = *reinterpret_cast<const float4*>(cr + s), c1 = *reinterpret_cast<const float4*>(cr + s + 4);
+      const float ct = cr[t];
+      const float v[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      float m[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) m[k] = (s + k <= t) ? v[k] * __expf(ct - cs[k]) : 0.f;
+      o.x = pack_bf16x2(m[0], m[1]); o.y = pack_bf16x2(m[2], m[3]); o.z = pack_bf16x2(m[4], m[5]); o.w = pack_bf16x2(m[6], m[7]);
+    }
+    *reinterpret_cast<uint4*>(M + row * L + s) = o;
+  }
+}
+
 // Backward prologue. One warp per (b,s,h):
 //   dy = dout·silu(z) ; dz = dout·y_pre·silu'(z) ; dye = dy·exp(cum_t) ; dx_acc = D·dy (fp32)
 //   dcum[b,c,h,t] = Σ_p dy·(y_pre − D x)      (row-factor part of d/dcum)
@@ -871,6 +903,13 @@ extern "C" int cmb_m3_finalize_fwd(const float* Y, const void* x, const void* z,
   cmb::m3_finalize_fwd_kernel<<<cmb::grid1d(n2, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       Y, static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(z), D, static_cast<__nv_bfloat16*>(ypre),
       static_cast<__nv_bfloat16*>(out), Bn, S, H, P, zs_b, zs_s, zs_h);
+  return CMB_OK();
+}
+extern "C" int cmb_m3_expand_decay(const float* CB, const float* cum, void* M, int Bn, int nc, int H, int G, int L, void* stream) {
+  if (L % 8 || H % G) return 1;
+  const long long n8 = static_cast<long long>(Bn) * nc * H * L * (L / 8);
+  cmb::m3_expand_decay_kernel<<<cmb::grid1d(n8, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(CB, cum, static_cast<__nv_bfloat16*>(M), Bn, nc, H,
+                                                                                                 G, L);
   return CMB_OK();
 }
 extern "C" int cmb_m3_bwd_pre(const void* dout, const void* z, const void* ypre, const void* x, const float* D,
