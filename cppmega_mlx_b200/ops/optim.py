@@ -203,8 +203,10 @@ class MuonBatchPlan:
             by.setdefault(tuple(sh), []).append(i)
         out = []
         for sh, idx in by.items():
-            for j in range(0, len(idx), self.max_stack):
-                out.append((sh, idx[j:j + self.max_stack]))
+            k = -(-len(idx) // self.max_stack)                   # number of stacks, then equal sizes: 18 matrices → 6 + 6 + 6, not 8 + 8 + 2
+            per = -(-len(idx) // k)                              # (a stack of two fills a quarter of the GPU per product)
+            for j in range(0, len(idx), per):
+                out.append((sh, idx[j:j + per]))
         out.sort(key=lambda t: -(t[0][0] * t[0][1] * len(t[1])))
         return out
 

@@ -78,8 +78,44 @@ def chunked_gated_delta_rule(q, k, v, beta, g, *, scale: float | None = None, in
     return o.to(v.dtype), S
 
 
+KERNEL_HEAD_DIMS = (16, 32, 64, 128)
+
+
+def delta_rule_kernel_supported(q, k, v, beta, g) -> bool:
+    """The forward time-loop kernel (``csrc/delta_rule.cu``) covers CUDA tensors with K == V ∈ {16, 32, 64, 128} when no gradient is
+    needed (prefill of a serving request, evaluation, decode)."""
+    from ..ops import _backend as B
+    if not (q.is_cuda and B.kernels_enabled() and B.has_library() and hasattr(B.load_library(), "cmb_delta_rule_fwd")):
+        return False
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, beta, g)):
+        return False
+    K, V = q.shape[-1], v.shape[-1]
+    return K == V and K in KERNEL_HEAD_DIMS and v.shape[2] % q.shape[2] == 0 and g.dim() in (3, 4) and q.shape[1] > 0
+
+
+def delta_rule_forward_kernel(q, k, v, beta, g, *, scale=None, initial_state=None):
+    """Same contract as ``recurrent_gated_delta_rule`` on the GPU kernel: fp32 state in registers, one CTA per (batch, value head)."""
+    import ctypes
+    from ..ops import _backend as B
+    Bn, T, H, K = q.shape
+    HV, V = v.shape[2], v.shape[3]
+    scale = K ** -0.5 if scale is None else scale
+    f = lambda t: t.detach().float().contiguous()
+    qf, kf, vf, bf, gf = f(q), f(k), f(v), f(beta), f(g)
+    s0 = None if initial_state is None else f(initial_state)
+    o = torch.empty(Bn, T, HV, V, dtype=torch.float32, device=q.device)
+    s_out = torch.empty(Bn, HV, K, V, dtype=torch.float32, device=q.device)
+    ip = (ctypes.c_int * 7)(Bn, T, H, HV, K, V, int(g.dim() == 4))
+    B.check(B.load_library().cmb_delta_rule_fwd(B.ptr(qf), B.ptr(kf), B.ptr(vf), B.ptr(bf), B.ptr(gf), B.ptr(s0), B.ptr(o), B.ptr(s_out), ip,
+                                                ctypes.c_float(scale), B.stream_ptr()), "delta_rule_fwd")
+    return o.to(v.dtype), s_out
+
+
 def gated_delta_rule(q, k, v, beta, g, *, scale=None, initial_state=None, chunk_size: int = 64):
-    """Product path: chunked form (a single token, as in decode, takes the recurrence)."""
+    """Product path: the forward kernel when no gradient is needed and the head size is covered, else the chunked form (a single
+    token, as in decode, takes the recurrence)."""
+    if delta_rule_kernel_supported(q, k, v, beta, g):
+        return delta_rule_forward_kernel(q, k, v, beta, g, scale=scale, initial_state=initial_state)
     if q.shape[1] <= 1:
         return recurrent_gated_delta_rule(q, k, v, beta, g, scale=scale, initial_state=initial_state)
     return chunked_gated_delta_rule(q, k, v, beta, g, scale=scale, initial_state=initial_state, chunk_size=chunk_size)

@@ -183,3 +183,31 @@ def test_add_rms_norm_matches_add_then_norm(rows, cols):
     assert torch.allclose(y.float(), ref_y.float(), rtol=1e-2, atol=1e-3)
     fp = ops.rms_norm_ref(ref_s, w, 1e-5)
     assert torch.allclose(y.float(), fp.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("K,H,HV,per_dim,T,with_s0", [(64, 2, 4, False, 70, True), (64, 2, 2, True, 33, False), (16, 1, 2, True, 9, True),
+                                                      (128, 1, 1, False, 40, False), (32, 2, 2, False, 1, True)])
+def test_delta_rule_forward_kernel_matches_recurrence(K, H, HV, per_dim, T, with_s0):
+    """GDN (scalar decay) and KDA (per-dimension decay) forward kernel against the token-by-token recurrence in fp32."""
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.v4 import delta_rule as DR
+    torch.manual_seed(0)
+    dev, b = "cuda", 2
+    q = torch.randn(b, T, H, K, device=dev) * 0.5
+    k = torch.nn.functional.normalize(torch.randn(b, T, H, K, device=dev), dim=-1)
+    v = torch.randn(b, T, HV, K, device=dev)
+    beta = torch.rand(b, T, HV, device=dev)
+    g = -torch.rand(b, T, HV, K, device=dev) * 0.2 if per_dim else -torch.rand(b, T, HV, device=dev) * 0.2
+    s0 = torch.randn(b, HV, K, K, device=dev) * 0.1 if with_s0 else None
+    n0 = B.launch_count("delta_rule_fwd")
+    with torch.no_grad():
+        o, S = DR.gated_delta_rule(q, k, v, beta, g, initial_state=s0)
+    assert B.launch_count("delta_rule_fwd") == n0 + 1
+    ro, rS = DR.recurrent_gated_delta_rule(q, k, v, beta, g, initial_state=s0)
+    assert torch.allclose(o, ro, atol=2e-4, rtol=2e-4), float((o - ro).abs().max())
+    assert torch.allclose(S, rS, atol=2e-4, rtol=2e-4)
+    # with gradients enabled the differentiable chunked form is used instead
+    with torch.enable_grad():
+        DR.gated_delta_rule(q.requires_grad_(), k, v, beta, g, initial_state=s0)[0].sum().backward()
+    assert B.launch_count("delta_rule_fwd") == n0 + 1 and q.grad is not None
+    B.check_status()
