@@ -589,7 +589,7 @@ __global__ void __launch_bounds__(256) m3_bwd_q_w8s_kernel(const __nv_bfloat16* 
                                                             __nv_bfloat16* __restrict__ dG, int Bn, int nc, int H, int G) {
   constexpr int L = LPR * 8, RPL = 32 / LPR, NL = 4 / RPL;
   __shared__ __align__(16) float scum[L];
-  __shared__ float scol[L];
+  __shared__ __align__(16) float spart[8][L];        // per-warp column sums (no atomics: a lane pair owns its columns inside a warp)
   const int hg = H / G;
   constexpr int rblocks = L / 32;
   const long long blk = blockIdx.x;
@@ -620,18 +620,16 @@ __global__ void __launch_bounds__(256) m3_bwd_q_w8s_kernel(const __nv_bfloat16* 
         rm[k] = *reinterpret_cast<const uint4*>(Mm + mbase + static_cast<long long>(r0 + k * RPL) * L + s);
       }
     }
+    __syncthreads();                                  // the previous head's readers of scum / spart are done
+    for (int i = threadIdx.x; i < L; i += 256) scum[i] = cum[vrow + i];
     __syncthreads();
-    for (int i = threadIdx.x; i < L; i += 256) {
-      scum[i] = cum[vrow + i];
-      scol[i] = 0.f;
-    }
-    __syncthreads();
+    float csum[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) csum[i] = 0.f;
     if (live) {
-      float cs[8], csum[8];
+      float cs[8];
       *reinterpret_cast<float4*>(cs) = *reinterpret_cast<const float4*>(scum + s);
       *reinterpret_cast<float4*>(cs + 4) = *reinterpret_cast<const float4*>(scum + s + 4);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) csum[i] = 0.f;
 #pragma unroll
       for (int k = 0; k < NL; ++k) {
         const int t = r0 + k * RPL;
@@ -646,11 +644,23 @@ __global__ void __launch_bounds__(256) m3_bwd_q_w8s_kernel(const __nv_bfloat16* 
             acc[k][i] += dm[i] * __expf(ct - cs[i]);
           }
       }
+    }
+    // the RPL lanes of a warp that share these 8 columns add up, then one of them publishes the warp's sums
 #pragma unroll
-      for (int i = 0; i < 8; ++i) atomicAdd(&scol[s + i], csum[i]);
+    for (int off = LPR; off < 32; off <<= 1)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) csum[i] += __shfl_xor_sync(0xffffffffu, csum[i], off);
+    if (lane < LPR) {
+      *reinterpret_cast<float4*>(&spart[warp][s]) = make_float4(csum[0], csum[1], csum[2], csum[3]);
+      *reinterpret_cast<float4*>(&spart[warp][s + 4]) = make_float4(csum[4], csum[5], csum[6], csum[7]);
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < smax && i < L; i += 256) atomicAdd(&dcum[vrow + i], -scol[i]);
+    for (int i = threadIdx.x; i < smax && i < L; i += 256) {
+      float tsum = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) tsum += spart[w][i];
+      atomicAdd(&dcum[vrow + i], -tsum);
+    }
   }
   const long long gbase = (((static_cast<long long>(b) * nc + c) * G + g) * L) * L;
 #pragma unroll
