@@ -764,7 +764,7 @@ template <int LPR>
 __global__ void __launch_bounds__(256) m3_bwd_xw_w8_kernel(const float* __restrict__ dXw, const __nv_bfloat16* __restrict__ x,
                                                             const float* __restrict__ cum, float* __restrict__ dx_acc,
                                                             float* __restrict__ dcum, float* __restrict__ dcumL, int Bn, int S, int H,
-                                                            int L) {
+                                                            int L, __nv_bfloat16* __restrict__ gx) {
   constexpr int P = LPR * 8, ROWS = 256 / LPR;
   __shared__ float red[8];
   const int nc = S / L;
@@ -786,8 +786,14 @@ __global__ void __launch_bounds__(256) m3_bwd_xw_w8_kernel(const float* __restri
   unpack8_bf16(*reinterpret_cast<const uint4*>(x + base), xv);
   a0.x += g0.x * w; a0.y += g0.y * w; a0.z += g0.z * w; a0.w += g0.w * w;
   a1.x += g1.x * w; a1.y += g1.y * w; a1.z += g1.z * w; a1.w += g1.w * w;
-  *reinterpret_cast<float4*>(dx_acc + base) = a0;
-  *reinterpret_cast<float4*>(dx_acc + base + 4) = a1;
+  if (gx != nullptr) {               // this is the last contribution to dx: emit the bf16 gradient instead of the fp32 accumulator
+    uint4 o;
+    o.x = pack_bf16x2(a0.x, a0.y); o.y = pack_bf16x2(a0.z, a0.w); o.z = pack_bf16x2(a1.x, a1.y); o.w = pack_bf16x2(a1.z, a1.w);
+    *reinterpret_cast<uint4*>(gx + base) = o;
+  } else {
+    *reinterpret_cast<float4*>(dx_acc + base) = a0;
+    *reinterpret_cast<float4*>(dx_acc + base + 4) = a1;
+  }
   float dw = g0.x * xv[0] + g0.y * xv[1] + g0.z * xv[2] + g0.w * xv[3] + g1.x * xv[4] + g1.y * xv[5] + g1.z * xv[6] + g1.w * xv[7];
 #pragma unroll
   for (int off = LPR / 2; off > 0; off >>= 1) dw += __shfl_xor_sync(0xffffffffu, dw, off);
@@ -979,8 +985,10 @@ extern "C" int cmb_m3_state_bwd(const float* dHy, const void* hc, const float* c
       dHy, static_cast<const bf*>(hc), cum, dhlast, static_cast<bf*>(dS), dcumL, dh0, Bn, nc, H, PN, L);
   return CMB_OK();
 }
+// `gx` (optional, bf16 [B,S,H,P]): when given and the wide kernel applies, the finished gradient is written there in bf16 and dx_acc is
+// left as it was; the return value 10 says so (0: dx_acc was updated and still has to be cast by the caller).
 extern "C" int cmb_m3_bwd_xw(const float* dXw, const void* x, const float* cum, float* dx_acc, float* dcum, float* dcumL,
-                             int Bn, int S, int H, int P, int L, void* stream) {
+                             int Bn, int S, int H, int P, int L, void* gx, void* stream) {
   {
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     const int rows = (P == 32 || P == 64 || P == 128 || P == 256) ? 256 * 8 / P : 0;
@@ -989,9 +997,12 @@ extern "C" int cmb_m3_bwd_xw(const float* dXw, const void* x, const float* cum, 
       if (wblocks > 0x7fffffffLL) return 3;
       auto kern = P == 32 ? cmb::m3_bwd_xw_w8_kernel<4> : P == 64 ? cmb::m3_bwd_xw_w8_kernel<8> : P == 128 ? cmb::m3_bwd_xw_w8_kernel<16>
                                                                                                           : cmb::m3_bwd_xw_w8_kernel<32>;
+      const bool fused = gx != nullptr && (reinterpret_cast<uintptr_t>(gx) & 15) == 0;
       kern<<<static_cast<int>(wblocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(dXw, static_cast<const __nv_bfloat16*>(x), cum, dx_acc, dcum,
-                                                                                    dcumL, Bn, S, H, L);
-      return CMB_OK();
+                                                                                    dcumL, Bn, S, H, L,
+                                                                                    fused ? static_cast<__nv_bfloat16*>(gx) : nullptr);
+      if (cudaGetLastError() != cudaSuccess) return 2;
+      return fused ? 10 : 0;
     }
   }
   const long long warps = static_cast<long long>(Bn) * S * H;

@@ -192,8 +192,10 @@ def scan_backward(g_out, g_hlast, x, Bm, Cm, z, A, dt, D, h0, saved, chunk):
     dXw = torch.empty(Bn, S, H, P, dtype=torch.float32, device=dev)
     gemm_batched(Bg, dS, dXw, M=L, N=P, K=N, a_mn=False, b_mn=False, lda=geo.bc_ld, ldb=geo.st_ld, ldc=geo.x_ld, nb=geo.nbH,
                  sA=geo.bc_s, sB=geo.st_s, sC=geo.x_s, a_div2=hg)
-    B.check(lib.cmb_m3_bwd_xw(B.ptr(dXw), B.ptr(x), B.ptr(cum), B.ptr(dx_acc), B.ptr(dcum), B.ptr(dcumL), Bn, S, H, P, L,
-                              st()), "m3_bwd_xw")
+    gx_bf = torch.empty(Bn, S, H, P, dtype=bf, device=dev)
+    rc = lib.cmb_m3_bwd_xw(B.ptr(dXw), B.ptr(x), B.ptr(cum), B.ptr(dx_acc), B.ptr(dcum), B.ptr(dcumL), Bn, S, H, P, L, B.ptr(gx_bf), st())
+    gx_done = rc == 10                       # the kernel wrote the finished bf16 gradient itself (no fp32 store, no cast pass)
+    B.check(0 if gx_done else rc, "m3_bwd_xw")
     del dXw
     gemm_batched(xw, dS, dB, M=L, N=N, K=hg * P, a_mn=False, b_mn=True, lda=geo.x_ld, ldb=geo.st_ld, ldc=geo.bc_ld,
                  nb=geo.nbG, sA=geo.xg_s, sB=geo.stg_s, sC=geo.bc_s, accumulate=True)
@@ -208,7 +210,7 @@ def scan_backward(g_out, g_hlast, x, Bm, Cm, z, A, dt, D, h0, saved, chunk):
         B.check(lib.cmb_cast_f32_bf16(B.ptr(t), B.ptr(o), I64(t.numel()), st()), "cast")
         return o
 
-    gx = cast(dx_acc).to(x.dtype)
+    gx = (gx_bf if gx_done else cast(dx_acc)).to(x.dtype)
     gB, gC = cast(dB).to(Bm.dtype), cast(dC).to(Cm.dtype)
     gh0 = dh0.to(h0.dtype) if h0 is not None else None
     return gx, gB, gC, dz.to(z.dtype), dA.to(A.dtype), ddt.to(dt.dtype), dD.to(D.dtype), gh0
