@@ -130,7 +130,9 @@ class M2RNNMixer(nn.Module):
         b, s, _ = hidden_states.shape
         if self.tp_group is not None:
             from ..parallel.tp import mixed_column_linear
-            proj = mixed_column_linear(hidden_states, self.in_proj.weight, getattr(self, "tp_replicated_rows", 0), self.tp_group)
+            rep = getattr(self, "in_proj_rep", None)            # replicated leading rows live in their own parameter
+            weight = self.in_proj.weight if rep is None else torch.cat([rep.weight, self.in_proj.weight], 0)
+            proj = mixed_column_linear(hidden_states, weight, getattr(self, "tp_replicated_rows", 0), self.tp_group)
         else:
             proj = self.in_proj(hidden_states)
         conv_end, f_end = self.conv_dim, self.conv_dim + self.f_dim

@@ -36,6 +36,12 @@ def sharded_specs(model: torch.nn.Module) -> dict[str, ShardSpec]:
     specs: dict[str, ShardSpec] = {}
     for mod_name, mod in model.named_modules():
         pre = mod_name + "." if mod_name else ""
+        tpg = getattr(mod, "tp_group", None)
+        if tpg is not None and _world(tpg) > 1 and not isinstance(mod, (TPFeedForward, ColumnParallelLinear, RowParallelLinear)):
+            # head- / expert-sharded mixers (tensor_parallelize_mixers) interleave replicated and sliced rows of packed projections;
+            # no gather rule exists for them, and writing one rank's slice under the logical name would lose the others
+            raise ValueError(f"{mod_name or type(mod).__name__}: a tensor-parallel {type(mod).__name__} cannot be consolidated to logical "
+                             "tensors; checkpoint the model before tensor_parallelize_mixers or load it and re-shard")
         if isinstance(mod, MoE) and mod.ep_size > 1:
             for leaf in ("w_gate_up", "w_down"):
                 n = f"{pre}experts.{leaf}"

@@ -376,7 +376,15 @@ def _shard_m2rnn(full, group):
     if c.num_q_heads % tp == 0 and c.num_k_heads % tp:
         raise ValueError("head-parallel M2RNN: a replicated k segment behind a split q segment is not supported")
     loc.tp_replicated = tuple(n for n, heads in (("q", c.num_q_heads), ("k", c.num_k_heads), ("w", nw)) if heads % tp)
-    loc.tp_replicated_rows = sum(heads * K for heads in (c.num_q_heads, c.num_k_heads) if heads % tp)   # leading rows of in_proj
+    loc.tp_replicated_rows = sum(heads * K for heads in (c.num_q_heads, c.num_k_heads) if heads % tp)   # leading rows of the projection
+    if loc.tp_replicated_rows:
+        # The replicated rows get a parameter of their own: inside one matrix with this rank's slice, a matrix-wise optimizer
+        # (Muon orthogonalises whole matrices) would update them differently on every rank and the copies would drift apart.
+        n = loc.tp_replicated_rows
+        w = loc.in_proj.weight.detach()
+        loc.in_proj_rep = nn.Module()
+        loc.in_proj_rep.weight = nn.Parameter(w[:n].clone())
+        loc.in_proj.weight = nn.Parameter(w[n:].clone())
     loc.train(full.training)
     return loc
 

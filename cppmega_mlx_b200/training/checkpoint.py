@@ -371,7 +371,10 @@ def save_checkpoint(model: torch.nn.Module, path, *, optimizer=None, training_st
     # Collectives first, on every rank: tensor- / expert-parallel slices are gathered to logical tensors and the sharded
     # optimizer state to its world-size independent form.  Only then does the writer rank touch the file system.
     from ..parallel.sharded_state import consolidated_parameters, map_state_tree, sharded_specs
-    specs = sharded_specs(model)
+    try:
+        specs = sharded_specs(model)
+    except ValueError as e:
+        raise CheckpointError(f"checkpoint {path}: {e}") from e
     weights = consolidated_parameters(model, specs)
     opt_state = _optimizer_full_state(optimizer) if (optimizer is not None and optimizer_path is not None) else None
     if opt_state is not None and specs:
@@ -499,7 +502,10 @@ def load_checkpoint(model: torch.nn.Module, path, *, optimizer=None, training_st
     if sorted(stored) != sorted(meta["tensors"]):
         raise CheckpointError(f"checkpoint {path}: weight file tensors do not match metadata.tensors")
     from ..parallel.sharded_state import logical_shape, map_state_tree, sharded_specs, slice_local
-    specs = sharded_specs(model)                      # parameters of which this rank holds a tensor- / expert-parallel slice
+    try:
+        specs = sharded_specs(model)                  # parameters of which this rank holds a tensor- / expert-parallel slice
+    except ValueError as e:
+        raise CheckpointError(f"checkpoint {path}: {e}") from e
     local_params = dict(model.named_parameters())
     params = {(specs[n].logical_name if n in specs else n): p for n, p in local_params.items()}
     spec_of = {s.logical_name: s for s in specs.values()}

@@ -145,3 +145,22 @@ def _failing_writer(rank, world, path):
 def test_writer_failure_reaches_every_rank(tmp_path):
     names = run_ranks(_failing_writer, 2, str(tmp_path / "blocked"), timeout=60)
     assert names[0] != "no error" and names[1] == "CheckpointError"
+
+
+def _mixer_tp_refused(rank, world, path):
+    from cppmega_mlx_b200.models.hybrid_lm import HybridTinyLM
+    from cppmega_mlx_b200.parallel import state as PS
+    from cppmega_mlx_b200.parallel import tp as TP
+    from cppmega_mlx_b200.training import checkpoint as ck
+    st = PS.init_parallel_state(tp=world)
+    torch.manual_seed(0)
+    model = HybridTinyLM(_moe_cfg())
+    assert sum(TP.tensor_parallelize_mixers(model, st.tp_group).values()) > 0
+    with pytest.raises(ck.CheckpointError, match="cannot be consolidated"):
+        ck.save_checkpoint(model, path)
+
+
+def test_head_parallel_mixers_are_refused_not_written_as_one_rank_slice(tmp_path):
+    """No gather rule exists for head- / expert-sharded mixers: saving must fail closed on every rank instead of writing rank 0's
+    slice under the logical parameter names."""
+    run_ranks(_mixer_tp_refused, 2, str(tmp_path / "ckpt"))
