@@ -138,7 +138,9 @@ def main():
             from cppmega_mlx_b200.parallel.fused_ep import enable_fused_ep
             enable_fused_ep(model, ep_group, dev, max_tokens=args.micro_batch * args.seq_len)
     else:
-        opt = DistributedZeRO1Optimizer(model, factory, comm=comm if tp_group is None else "nccl", group=dp_group)
+        # a data-parallel group of one rank (pure tensor parallelism) comes back as None, which must not be read as "the default group"
+        opt = DistributedZeRO1Optimizer(model, factory, comm=comm if tp_group is None else "nccl", group=dp_group,
+                                        single_rank=tp_group is not None and dp == 1)
     opt.zero_grad()
     stepper = PretrainingStep(model, opt, loss_fn=make_loss_fn(backend="cce"), sync_metrics=False, device=dev)
 
@@ -216,7 +218,7 @@ def main():
             "impl": args.impl,
             "config": {"model": f"{args.profile}: {cfg.pattern}x{cfg.depth // len(cfg.pattern)} d{cfg.hidden_size} "
                                 f"ffn{cfg.ffn_hidden_size} vocab{cfg.vocab_size} mtp{cfg.mtp_depth if cfg.mtp_enabled else 0}",
-                       "params": nparams, "global_batch": mb * dp, "seq_len": S, "parallelism": f"dp{dp} zero1 ({comm if args.tp == 1 else 'nccl'})" + (f" ep{args.ep}" if args.ep > 1 else "") + (f" tp{args.tp} (MLA / MoE / M2RNN mixers + dense FFNs; Mamba3 replicated{'; fused FFN all-reduce' if args.tp_fused else ''})" if args.tp > 1 else ""),
+                       "params": nparams, "global_batch": mb * dp, "seq_len": S, "parallelism": f"dp{dp} zero1 ({comm if args.tp == 1 else 'nccl'})" + (f" ep{args.ep}" if args.ep > 1 else "") + (f" tp{args.tp} (Mamba3 / MLA / MoE / M2RNN mixers head- or expert-parallel + dense FFNs{'; fused FFN all-reduce' if args.tp_fused else ''})" if args.tp > 1 else ""),
                        "optimizer": args.optimizer, "expert_gemm": args.expert_gemm, "micro_batch_per_gpu": mb, "grad_checkpoint": ckpt,
                        "l2": "working set per step (weights + activations, tens of GB) far exceeds the 126 MB L2; no flush needed"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "step_ms": spread,

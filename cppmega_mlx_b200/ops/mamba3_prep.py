@@ -34,7 +34,7 @@ def _cumsum_seq(t: torch.Tensor, reverse: bool = False) -> torch.Tensor:
 
 class _Mamba3PrepFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, BC, tail, dt_bias, wB, bB, wC, bC, H, G, N, R, a_floor, eps):
+    def forward(ctx, BC, tail, dt_bias, wB, bB, wC, bC, H, G, N, R, a_floor, eps, phase_dt=None):
         lib = B.load_library()
         b, s = BC.shape[:2]
         dev = BC.device
@@ -47,6 +47,9 @@ class _Mamba3PrepFn(torch.autograd.Function):
         inc = torch.empty(b, s, G, R, **f32)
         B.check(lib.cmb_m3_prep_dt_fwd(B.ptr(tail), I64(tail.shape[-1]), B.ptr(bias32), B.ptr(dt), B.ptr(A), B.ptr(sc), B.ptr(inc), b, s, H, G, R,
                                        F32(a_floor), B.stream_ptr()), "m3_prep_dt_fwd")
+        if phase_dt is not None:
+            # the phase of group g comes from a dt the caller supplies (a head this rank does not hold) instead of local head g
+            inc = (tail[..., 3 * H:].float()[:, :, None, :] * phase_dt.float()[..., None]).contiguous()
         ang = _cumsum_seq(inc)
         Bg = torch.empty(b, s, G, N, dtype=torch.bfloat16, device=dev)
         Cg = torch.empty_like(Bg)
@@ -55,6 +58,7 @@ class _Mamba3PrepFn(torch.autograd.Function):
         B.check(lib.cmb_m3_prep_bc_fwd(B.ptr(BC), B.ptr(sc), B.ptr(ang), B.ptr(w[0]), B.ptr(w[1]), B.ptr(w[2]), B.ptr(w[3]), B.ptr(Bg), B.ptr(Cg),
                                        B.ptr(rstd), B.ptr(scale_g), I64(b * s), H, G, N, R, F32(eps), B.stream_ptr()), "m3_prep_bc_fwd")
         ctx.save_for_backward(BC, tail, bias32, dt, ang, rstd, scale_g, *w)
+        ctx.phase_dt = None if phase_dt is None else phase_dt.detach().float()
         ctx.meta = (H, G, N, R, a_floor, dt_bias.dtype, wB.shape, wB.dtype)
         return Bg, Cg, dt, A
 
@@ -81,12 +85,25 @@ class _Mamba3PrepFn(torch.autograd.Function):
         g_A = g_A.float().contiguous() if g_A is not None else torch.zeros(b, s, H, **f32)
         g_tail = torch.empty(b, s, 3 * H + R, dtype=torch.bfloat16, device=dev)
         g_bias = torch.zeros(H, **f32)
+        g_phase = None
+        kernel_g_inc = g_inc
+        if ctx.phase_dt is not None:      # the phase path does not run through the local heads: its adjoints are formed here
+            angles = tail[..., 3 * H:].float()
+            g_phase = (g_inc * angles[:, :, None, :]).sum(-1)                                  # [B,S,G]
+            g_angles = (g_inc * ctx.phase_dt[..., None]).sum(2)                                # [B,S,R]
+            kernel_g_inc = torch.zeros_like(g_inc)
         B.check(lib.cmb_m3_prep_dt_bwd(B.ptr(tail), I64(tail.shape[-1]), B.ptr(bias32), B.ptr(dt), B.ptr(g_dt), B.ptr(g_A), B.ptr(g_scale),
-                                       B.ptr(g_inc), B.ptr(g_tail), B.ptr(g_bias), b, s, H, G, R, F32(a_floor), B.stream_ptr()), "m3_prep_dt_bwd")
+                                       B.ptr(kernel_g_inc), B.ptr(g_tail), B.ptr(g_bias), b, s, H, G, R, F32(a_floor), B.stream_ptr()),
+                "m3_prep_dt_bwd")
+        if ctx.phase_dt is not None:
+            g_tail[..., 3 * H:] = g_angles.to(g_tail.dtype)
         cast = lambda t: t.to(wdtype).view(wshape)
-        return gBC, g_tail, g_bias.to(bias_dtype), cast(gw[0]), cast(gw[1]), cast(gw[2]), cast(gw[3]), None, None, None, None, None, None
+        return gBC, g_tail, g_bias.to(bias_dtype), cast(gw[0]), cast(gw[1]), cast(gw[2]), cast(gw[3]), None, None, None, None, None, None, g_phase
 
 
-def mamba3_prep(BC, tail, dt_bias, wB, bB, wC, bC, *, nheads: int, ngroups: int, d_state: int, num_angles: int, a_floor: float, eps: float = 1e-5):
-    """→ (Bg [B,S,G,N] bf16, Cg, dt [B,S,H] fp32, A [B,S,H] fp32)."""
-    return _Mamba3PrepFn.apply(BC, tail, dt_bias, wB, bB, wC, bC, nheads, ngroups, d_state, num_angles, float(a_floor), float(eps))
+def mamba3_prep(BC, tail, dt_bias, wB, bB, wC, bC, *, nheads: int, ngroups: int, d_state: int, num_angles: int, a_floor: float, eps: float = 1e-5,
+                phase_dt: torch.Tensor | None = None):
+    """→ (Bg [B,S,G,N] bf16, Cg, dt [B,S,H] fp32, A [B,S,H] fp32).  ``phase_dt`` [B,S,G] (optional, differentiable): the step sizes
+    whose product with the angles is accumulated into the rotary phase of the groups, instead of those of the first ``ngroups``
+    local heads (head-parallel layers, where the phase heads of a rank's groups live on another rank)."""
+    return _Mamba3PrepFn.apply(BC, tail, dt_bias, wB, bB, wC, bC, nheads, ngroups, d_state, num_angles, float(a_floor), float(eps), phase_dt)

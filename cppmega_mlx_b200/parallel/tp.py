@@ -389,16 +389,118 @@ def _shard_m2rnn(full, group):
     return loc
 
 
-def tensor_parallelize_mixers(model: nn.Module, group, *, kinds=("mla", "moe", "m2rnn")) -> dict[str, int]:
-    """Replace the attention (low-rank MLA), MoE and M2RNN mixers under ``model`` by their head- / expert-parallel forms (in place);
-    returns how many of each were replaced.  Inputs and outputs of every mixer stay replicated over the group (the partial output
-    products are all-reduced), so it composes with ``tensor_parallelize_ffn`` and leaves other mixers untouched: Mamba3 blocks
-    stay replicated — their B / C rotation takes its phase from the first ``ngroups`` heads of the layer, which would have to be
-    shipped to every rank."""
+class Mamba3TP(nn.Module):
+    """Head-parallel Mamba3 mixer (training / prefill without a decode cache).  Rank r holds ``nheads / tp`` heads and ``ngroups / tp``
+    B/C groups: its slices of z, x, B, C, dd_A and trap rows of the packed projection, of the conv channels, the norm weights, D and
+    the columns of ``out_proj`` (row-parallel, partial outputs all-reduced).  Two pieces stay replicated in a parameter of their own
+    (``in_proj_rep``: a matrix-wise optimizer must see identical matrices on every rank): the angle rows, which every head uses,
+    and the dd_dt rows of the first ``ngroups`` heads of the layer together with their dt biases (``rep_dt_bias``), because group g
+    rotates with the phase of head index g of the whole layer, a head that lives on rank 0 whichever rank holds group g.  The rank
+    that owns those heads takes their step size from the replicated rows as well, so each exists once.
+    Math: ``nn/mamba3.py`` ``Mamba3Block.forward``."""
+
+    def __init__(self, full, group):
+        super().__init__()
+        from ..nn.basic import Linear
+        c = full.config
+        tp, r = _world(group), dist.get_rank(group)
+        H, G, N, P = c.nheads, c.ngroups, c.d_state, c.headdim
+        if c.effective_mimo_rank != 1:
+            raise ValueError("head-parallel Mamba3 supports mimo_rank 1")
+        if H % tp or G % tp or G > H // tp:
+            raise ValueError(f"head-parallel Mamba3 needs tp | nheads, tp | ngroups and ngroups <= nheads / tp (got {H} heads, {G} groups, tp {tp})")
+        self.config, self.tp_group, self.tp_rank, self.tp_size = c, group, r, tp
+        Hl, Gl = H // tp, G // tp
+        R = full.dims.num_rope_angles
+        d_in, d_l, d_bc, dbc_l = c.d_inner, c.d_inner // tp, G * N, Gl * N
+        self.Hl, self.Gl, self.R, self.d_l, self.dbc_l = Hl, Gl, R, d_l, dbc_l
+        self.n_own = max(0, min(G - r * Hl, Hl))            # local heads whose step size comes from the replicated rows (global index < G)
+        base = 2 * d_in + 2 * d_bc                          # first dd_dt row of the packed projection
+        W = full.in_proj.weight.detach()
+        rows = lambda a, n: W[a:a + n]
+        rep = torch.cat([rows(base, G), rows(base + 3 * H, R)], 0)
+        lo = r * Hl
+        sl = torch.cat([rows(r * d_l, d_l), rows(d_in + r * d_l, d_l), rows(2 * d_in + r * dbc_l, dbc_l), rows(2 * d_in + d_bc + r * dbc_l, dbc_l),
+                        rows(base + lo + self.n_own, Hl - self.n_own), rows(base + H + lo, Hl), rows(base + 2 * H + lo, Hl)], 0)
+        dev, dt = W.device, W.dtype
+        self.in_proj_rep = nn.Module()
+        self.in_proj_rep.weight = nn.Parameter(rep.clone())
+        self.in_proj = nn.Module()
+        self.in_proj.weight = nn.Parameter(sl.clone())
+        cw, cb = full.conv_weight.detach(), full.conv_bias.detach()
+        pick = lambda t: torch.cat([t[r * d_l:(r + 1) * d_l], t[d_in + r * dbc_l:d_in + (r + 1) * dbc_l],
+                                    t[d_in + d_bc + r * dbc_l:d_in + d_bc + (r + 1) * dbc_l]], 0)
+        self.conv_weight, self.conv_bias = nn.Parameter(pick(cw).clone()), nn.Parameter(pick(cb).clone())
+        self.dt_bias = nn.Parameter(full.dt_bias.detach()[lo:lo + Hl].clone())          # entries of the n_own heads are unused here
+        self.rep_dt_bias = nn.Parameter(full.dt_bias.detach()[:G].clone())
+        g0 = r * Gl
+        for n in ("B_norm_weight", "C_norm_weight", "B_bias", "C_bias"):
+            setattr(self, n, nn.Parameter(getattr(full, n).detach()[:, g0:g0 + Gl].clone()))
+        self.D = nn.Parameter(full.D.detach()[lo:lo + Hl].clone())
+        self.out_proj = Linear(d_l, c.d_model).to(dev, dt)
+        with torch.no_grad():
+            self.out_proj.weight.copy_(full.out_proj.weight[:, r * d_l:(r + 1) * d_l])
+        self.train(full.training)
+
+    def forward(self, hidden_states, *, h0=None, cache=None, return_cache: bool = False, cache_out=None):
+        if cache is not None or return_cache or h0 is not None:
+            raise NotImplementedError("the head-parallel Mamba3 mixer has no decode cache; gather the model for serving")
+        import torch.nn.functional as F
+        from ..nn import mamba3 as M3
+        c, g = self.config, self.tp_group
+        b, s, _ = hidden_states.shape
+        G, R, Hl, Gl, d_l, dbc_l, n_own = c.ngroups, self.R, self.Hl, self.Gl, self.d_l, self.dbc_l, self.n_own
+        n_rep = G + R
+        W = torch.cat([self.in_proj_rep.weight, self.in_proj.weight], 0)
+        proj = mixed_column_linear(hidden_states, W, n_rep, g)
+        rep = copy_to_tp(proj[..., :n_rep], g)                      # used differently on every rank: gradients are summed over the group
+        phase_dd, angles = rep[..., :G], rep[..., G:]
+        conv_ch = d_l + 2 * dbc_l
+        head, x, BC, tail_sl = ops.packed_split_conv_silu(proj, n_rep + d_l, conv_ch, d_l, self.conv_weight, self.conv_bias)
+        z = head[..., n_rep:]
+        rep_bias = copy_to_tp(self.rep_dt_bias, g)
+        lo = self.tp_rank * Hl
+        dd_rest, dd_A, trap = torch.split(tail_sl, [Hl - n_own, Hl, Hl], dim=-1)
+        dd_dt = torch.cat([phase_dd[..., lo:lo + n_own], dd_rest], -1) if n_own else dd_rest
+        dt_bias = torch.cat([rep_bias[lo:lo + n_own], self.dt_bias[n_own:]]) if n_own else self.dt_bias
+        g0 = self.tp_rank * Gl
+        phase_dt = F.softplus(phase_dd[..., g0:g0 + Gl].float() + rep_bias[g0:g0 + Gl].float())        # [B,S,Gl]
+        xh, zh = x.reshape(b, s, Hl, c.headdim), z.reshape(b, s, Hl, c.headdim)
+        norm_params = (self.B_norm_weight, self.B_bias, self.C_norm_weight, self.C_bias)
+        Bg = None
+        if ops.kernels_enabled() and hidden_states.is_cuda:
+            from ..ops import mamba3_prep as MP
+            tail = torch.cat([dd_dt, dd_A, trap, angles], -1).contiguous()
+            if MP.supported(BC, tail, norm_params + (dt_bias,), Hl, Gl, c.d_state, R):
+                Bg, Cg, dt, A = MP.mamba3_prep(BC, tail, dt_bias, *norm_params, nheads=Hl, ngroups=Gl, d_state=c.d_state, num_angles=R,
+                                               a_floor=c.A_floor, phase_dt=phase_dt)
+        if Bg is None:
+            Bm, Cm = BC[..., :dbc_l].reshape(b, s, Gl, c.d_state), BC[..., dbc_l:].reshape(b, s, Gl, c.d_state)
+            Bg = M3._rms_norm_last(Bm) * self.B_norm_weight[0].to(Bm.dtype) + self.B_bias[0].to(Bm.dtype)
+            Cg = M3._rms_norm_last(Cm) * self.C_norm_weight[0].to(Cm.dtype) + self.C_bias[0].to(Cm.dtype)
+            dt = F.softplus(dd_dt.float() + dt_bias.float())
+            Bg = Bg * M3.heads_to_group_scale(M3.compute_trapezoidal_scale(dt, trap.float()), Gl)[..., None].to(Bg.dtype)
+            ang_cum = torch.cumsum((angles.float()[:, :, None, :] * phase_dt[..., None]).transpose(1, 3), dim=-1).transpose(1, 3)
+            Bg, Cg = M3.apply_rope_on_state_dim(Bg, ang_cum), M3.apply_rope_on_state_dim(Cg, ang_cum)
+            A = torch.clamp(-F.softplus(dd_A.float()), max=-c.A_floor)
+        y, h = ops.mamba3_scan(xh, Bg, Cg, zh, A, dt, self.D, None, chunk_size=c.chunk_size)
+        return reduce_from_tp(self.out_proj(y.reshape(b, s, d_l)), g), h
+
+
+def _shard_mamba3(full, group):
+    return Mamba3TP(full, group)
+
+
+def tensor_parallelize_mixers(model: nn.Module, group, *, kinds=("mla", "moe", "m2rnn", "mamba3")) -> dict[str, int]:
+    """Replace the attention (low-rank MLA), MoE, M2RNN and Mamba3 mixers under ``model`` by their head- / expert-parallel forms (in
+    place); returns how many of each were replaced.  Inputs and outputs of every mixer stay replicated over the group (the partial
+    output products are all-reduced), so it composes with ``tensor_parallelize_ffn``.  A Mamba3 block whose head / group counts
+    the group size does not divide stays replicated."""
     from ..nn.m2rnn import M2RNNMixer
     from ..nn.mla import MLAAttention
     from ..nn.moe import MoE
-    done = {"mla": 0, "moe": 0, "m2rnn": 0}
+    from ..nn.mamba3 import Mamba3Block
+    done = {"mla": 0, "moe": 0, "m2rnn": 0, "mamba3": 0}
     if _world(group) == 1:
         return done
     for parent in list(model.modules()):
@@ -412,4 +514,9 @@ def tensor_parallelize_mixers(model: nn.Module, group, *, kinds=("mla", "moe", "
             elif isinstance(child, M2RNNMixer) and "m2rnn" in kinds and child.tp_group is None:
                 setattr(parent, name, _shard_m2rnn(child, group))
                 done["m2rnn"] += 1
+            elif isinstance(child, Mamba3Block) and "mamba3" in kinds:
+                c, tp = child.config, _world(group)
+                if c.effective_mimo_rank == 1 and c.nheads % tp == 0 and c.ngroups % tp == 0 and c.ngroups <= c.nheads // tp:
+                    setattr(parent, name, _shard_mamba3(child, group))
+                    done["mamba3"] += 1
     return done

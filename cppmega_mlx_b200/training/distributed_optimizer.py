@@ -111,10 +111,14 @@ class FlatBuffers:
 
 class DistributedZeRO1Optimizer:
     def __init__(self, model_or_params, inner_factory: Callable[[NamedParams], object], *, group=None,
-                 comm: str = "nccl", average: bool = True, owner_cost: Callable[[str, torch.Tensor], float] | None = None):
+                 comm: str = "nccl", average: bool = True, owner_cost: Callable[[str, torch.Tensor], float] | None = None,
+                 single_rank: bool = False):
+        """``group`` is the data-parallel group (``None`` = the default group).  ``single_rank=True`` says that this process is the
+        only member of its data-parallel group although a default group with more ranks exists (a pure tensor-parallel job, whose
+        ranks hold different parameter slices): nothing is reduced or sharded."""
         self.named = named_trainable(model_or_params)
         self.group = group
-        self.initialized = dist.is_available() and dist.is_initialized()
+        self.initialized = dist.is_available() and dist.is_initialized() and not single_rank
         self.world = dist.get_world_size(group) if self.initialized else 1
         self.rank = dist.get_rank(group) if self.initialized else 0
         self.average = average

@@ -146,3 +146,37 @@ def test_prefill_cache_on_fused_path_matches_framework_path(groups, state, seq):
             assert torch.minimum(d, (2 * torch.pi - d).abs()).max() < 6e-2
         else:
             assert (a - r).abs().max() <= 4e-2 * max(1.0, float(r.abs().max())), name
+
+
+def test_fused_prep_with_supplied_phase_dt_equals_the_local_phase_heads():
+    """Head-parallel layers hand the rotary phase's step sizes in from outside.  Supplying exactly the dt of the first ``ngroups``
+    local heads (computed differentiably from the same tail and bias) must reproduce the plain op: outputs, and the gradients of
+    tail and bias once both paths are added up."""
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops import mamba3_prep as MP
+    torch.manual_seed(0)
+    dev, b, s, H, G, N, R = "cuda", 2, 200, 32, 8, 128, 32
+    BC = (torch.randn(b, s, 2 * G * N, device=dev) * 0.5).bfloat16()
+    tail = (torch.randn(b, s, 3 * H + R, device=dev) * 0.5).bfloat16()
+    bias = (torch.randn(H, device=dev) * 0.1).bfloat16()
+    w = [(1 + 0.1 * torch.randn(1, G, N, device=dev)).bfloat16() for _ in range(2)] + [(0.1 * torch.randn(1, G, N, device=dev)).bfloat16() for _ in range(2)]
+    wB, wC, bB, bC = w
+    assert MP.supported(BC, tail, (wB, bB, wC, bC, bias), H, G, N, R)
+    gs = [torch.randn(b, s, G, N, device=dev).bfloat16(), torch.randn(b, s, G, N, device=dev).bfloat16(),
+          torch.randn(b, s, H, device=dev), torch.randn(b, s, H, device=dev)]
+
+    def run(with_phase):
+        t, bi, bc = tail.clone().requires_grad_(), bias.clone().requires_grad_(), BC.clone().requires_grad_()
+        ph = torch.nn.functional.softplus(t[..., :G].float() + bi[:G].float()) if with_phase else None
+        outs = MP.mamba3_prep(bc, t, bi, wB, bB, wC, bC, nheads=H, ngroups=G, d_state=N, num_angles=R, a_floor=0.01, phase_dt=ph)
+        torch.autograd.backward(outs, gs)
+        return [o.detach().float() for o in outs], t.grad.float(), bi.grad.float(), bc.grad.float()
+    o0, gt0, gb0, gbc0 = run(False)
+    o1, gt1, gb1, gbc1 = run(True)
+    B.check_status()
+    for a, c in zip(o0, o1):
+        assert torch.allclose(a, c, atol=2e-2, rtol=2e-2)
+    rel = lambda x, y: float((x - y).abs().max()) / (float(y.abs().max()) + 1e-6)
+    assert rel(gbc1, gbc0) < 2e-2
+    assert rel(gt1, gt0) < 3e-2, rel(gt1, gt0)
+    assert rel(gb1, gb0) < 3e-2, rel(gb1, gb0)

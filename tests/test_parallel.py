@@ -95,7 +95,7 @@ def _tp_mixers_rank(rank, world):
     tpm = HybridTinyLM(cfg)
     tpm.load_state_dict(full.state_dict())
     done = TP.tensor_parallelize_mixers(tpm, st.tp_group)
-    assert done == {"mla": 1, "moe": 1, "m2rnn": 1}, done
+    assert done == {"mla": 1, "moe": 1, "m2rnn": 1, "mamba3": 1}, done
     assert TP.tensor_parallelize_ffn(tpm, st.tp_group) >= 3          # the dense FFNs (and the MoE layer's shared expert)
     out = tpm(ids)
     assert torch.allclose(out, ref.detach(), atol=2e-5), float((out - ref).abs().max())
@@ -116,6 +116,24 @@ def _tp_mixers_rank(rank, world):
     assert torch.allclose(g[m + "out_proj.weight"], ref_g[m + "out_proj.weight"][:, r * 8:(r + 1) * 8], atol=3e-5)
     assert torch.allclose(g[m + "state_weight"], ref_g[m + "state_weight"], atol=3e-5)          # one shared matrix: replicated, gradient summed
     assert torch.allclose(g[m + "A_log"], ref_g[m + "A_log"][r * 2:(r + 1) * 2], atol=3e-5)
+    # Mamba3 (4 heads of 16, 2 groups, d_inner 64): rank r holds heads 2r, 2r+1 and group r; the phase rows (dd_dt of heads 0 and 1)
+    # and the angle rows are replicated with gradients summed over the ranks
+    k = "layers.0.block."
+    w_ref = ref_g[k + "in_proj.weight"]
+    d_in, d_bc, Hm, Gm = 64, 16, 4, 2
+    base = 2 * d_in + 2 * d_bc
+    rep_want = torch.cat([w_ref[base:base + Gm], w_ref[base + 3 * Hm:]], 0)
+    assert torch.allclose(g[k + "in_proj_rep.weight"], rep_want, atol=3e-5), float((g[k + "in_proj_rep.weight"] - rep_want).abs().max())
+    assert torch.allclose(g[k + "rep_dt_bias"], ref_g[k + "dt_bias"][:Gm], atol=3e-5)
+    sl = g[k + "in_proj.weight"]
+    assert torch.allclose(sl[:32], w_ref[r * 32:(r + 1) * 32], atol=3e-5)                                  # z rows of this rank
+    assert torch.allclose(sl[64:72], w_ref[2 * d_in + r * 8:2 * d_in + (r + 1) * 8], atol=3e-5)            # B rows of this rank's group
+    n_own = 2 if r == 0 else 0
+    dd_a_local = sl[80 + (2 - n_own):80 + (2 - n_own) + 2]
+    assert torch.allclose(dd_a_local, w_ref[base + Hm + 2 * r:base + Hm + 2 * r + 2], atol=3e-5)          # dd_A rows
+    assert torch.allclose(g[k + "out_proj.weight"], ref_g[k + "out_proj.weight"][:, r * 32:(r + 1) * 32], atol=3e-5)
+    assert torch.allclose(g[k + "D"], ref_g[k + "D"][2 * r:2 * r + 2], atol=3e-5)
+    assert torch.allclose(g[k + "B_norm_weight"], ref_g[k + "B_norm_weight"][:, r:r + 1], atol=3e-5)
     assert checks > 10
     return True
 
