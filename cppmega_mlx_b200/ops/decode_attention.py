@@ -81,12 +81,15 @@ def choose_splits(batch: int, head_groups: int, max_keys: int) -> int:
 
 
 def decode_attention(q, k_rows, v_rows, table, lengths, *, scale: float, topk=None, d_v: int | None = None,
-                     splits: int | None = None, max_keys: int | None = None):
+                     splits: int | None = None, max_keys: int | None = None, return_lse: bool = False):
     """See the module docstring. ``max_keys`` (an upper bound on the keys any row attends to) only tunes the split count and
-    avoids a device→host read of ``lengths``."""
+    avoids a device→host read of ``lengths``.  ``return_lse`` (kernel path only): also return the natural-log sum-exp of the scaled
+    scores per (row, head), ``-inf`` for a row without a valid key."""
     if v_rows is None and d_v is None:
         raise ValueError("d_v is required when the value is a prefix of the key row")
     if not kernel_supported(q, k_rows, v_rows, d_v):
+        if return_lse:
+            raise ValueError("return_lse needs the kernel path")
         return decode_attention_reference(q, k_rows, v_rows, table, lengths, scale=scale, topk=topk, d_v=d_v)
     lib = B.load_library()
     b, h, dk = q.shape
@@ -112,7 +115,8 @@ def decode_attention(q, k_rows, v_rows, table, lengths, *, scale: float, topk=No
                              k_rows.shape[0])
     lp = (ctypes.c_longlong * 10)(q.stride(0), q.stride(1), ks[0] if paged else 0, ks[1], 0 if paged else ks[0], ks[2],
                                   vs[0] if paged else 0, vs[1], 0 if paged else vs[0], vs[2])
+    lse = torch.empty(b, h, dtype=torch.float32, device=dev) if return_lse else None
     B.check(lib.cmb_paged_decode(B.ptr(q), B.ptr(k_rows), B.ptr(v_rows), B.ptr(tbl), B.ptr(lengths), B.ptr(tk), B.ptr(out),
-                                 B.ptr(None), B.ptr(ws_o), B.ptr(ws_ml[0]), B.ptr(ws_ml[1]), ip, lp, ctypes.c_float(scale),
+                                 B.ptr(lse), B.ptr(ws_o), B.ptr(ws_ml[0]), B.ptr(ws_ml[1]), ip, lp, ctypes.c_float(scale),
                                  B.ptr(B.status_buffer(dev)), B.stream_ptr()), "paged_decode")
-    return out.to(q.dtype)
+    return (out.to(q.dtype), lse) if return_lse else out.to(q.dtype)

@@ -84,12 +84,65 @@ def indices_to_mask(indices: torch.Tensor, skv: int) -> torch.Tensor:
     return mask[..., :skv].permute(0, 2, 1, 3)
 
 
+GATHER_FORM_RATIO = 14     # keys per listed key above which the gather-form forward beats the masked form (see sparse_mla_attention)
+
+
+def _gather_page_size(skv: int) -> int:
+    for ps in (128, 64, 32, 16):
+        if skv % ps == 0:
+            return ps
+    return 0
+
+
+def gather_forward_supported(q, kv, indices, d_v) -> bool:
+    """The gather-form forward kernel (no gradient): one shared latent KV head, the 576 / 512 latent layout the decode kernel covers."""
+    from . import decode_attention as DA
+    if torch.is_grad_enabled() and (q.requires_grad or kv.requires_grad):
+        return False
+    if not (B.on_gpu(q, kv, indices) and q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and B.kernels_enabled()):
+        return False
+    if kv.shape[2] != 1 or indices.shape[2] != 1 or not kv.is_contiguous() or _gather_page_size(kv.shape[1]) == 0:
+        return False
+    b, s, h, d = q.shape
+    ps = _gather_page_size(kv.shape[1])
+    return DA.kernel_supported(q.reshape(b * s, h, d), kv.view(-1, ps, 1, d), None, q.shape[-1] if d_v is None else d_v)
+
+
+def sparse_mla_gather_forward(q, kv, indices, sm_scale: float | None = None, d_v: int | None = None):
+    """Sparse MLA forward in gather form on the tcgen05 decode kernel (``csrc/decode.cu``): every query token is one "request"
+    whose top-k list is gathered row by row from the latent cache (``cp.async`` per row, keys on the MMA M dimension, all heads of
+    the token on N), so the work is S·top-k·H, no S×S product and no mask.  The sequence of batch element b is presented as a pool
+    of pages and every token of b gets b's page list.  Forward only: training takes the differentiable masked form."""
+    from . import decode_attention as DA
+    b, s, h, d = q.shape
+    skv = kv.shape[1]
+    dv = d if d_v is None else d_v
+    scale = d ** -0.5 if sm_scale is None else sm_scale
+    ps = _gather_page_size(skv)
+    w = skv // ps
+    pages = torch.arange(w, device=q.device, dtype=torch.int32)[None] + (torch.arange(b, device=q.device, dtype=torch.int32) * w)[:, None]
+    table = pages.repeat_interleave(s, dim=0)                                     # [b·s, w]
+    lengths = torch.full((b * s,), skv, dtype=torch.int32, device=q.device)
+    out, lse = DA.decode_attention(q.reshape(b * s, h, d), kv.view(b * w, ps, 1, d), None, table, lengths, scale=scale,
+                                   topk=indices.reshape(b * s, -1), d_v=dv, max_keys=indices.shape[-1], return_lse=True)
+    return out.view(b, s, h, dv), lse.view(b, s, h)
+
+
 def sparse_mla_attention(q, kv, indices, sm_scale: float | None = None, d_v: int | None = None):
-    """Differentiable sparse MLA. CUDA bf16 tensors run the sm_100a kernels."""
+    """Differentiable sparse MLA. CUDA bf16 tensors run the sm_100a kernels: without a gradient the gather-form kernel over the
+    top-k rows, with one the masked form."""
+    gather_ok = gather_forward_supported(q, kv, indices, d_v)
     if B.on_gpu(q, kv, indices) and q.dtype == torch.bfloat16:
         from . import sparse_mla_cuda
         if sparse_mla_cuda.supported(q, kv, indices, d_v):
+            # Measured on a B200 (B1, 64 heads, 576/512): the gather kernel costs 0.42 ns per (query, listed key, 16-head group) — it
+            # gathers the rows once per head group —, the masked form 0.062 ns per (query, causal key, 16-head group): the gather form
+            # wins once the list is shorter than about a fourteenth of the keys (top-2048 from 28 K tokens up).
+            if gather_ok and GATHER_FORM_RATIO * indices.shape[-1] <= kv.shape[1]:
+                return sparse_mla_gather_forward(q, kv, indices, sm_scale, d_v)
             return sparse_mla_cuda.apply(q, kv, indices, sm_scale, d_v)
+    if gather_ok:
+        return sparse_mla_gather_forward(q, kv, indices, sm_scale, d_v)
     b, s, _, d = q.shape
     if b * s * indices.shape[2] * indices.shape[3] * d > GATHER_LIMIT_ELEMS:
         return sparse_mla_masked_dense(q, kv, indices, sm_scale, d_v)

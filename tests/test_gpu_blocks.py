@@ -211,3 +211,35 @@ def test_delta_rule_forward_kernel_matches_recurrence(K, H, HV, per_dim, T, with
         DR.gated_delta_rule(q.requires_grad_(), k, v, beta, g, initial_state=s0)[0].sum().backward()
     assert B.launch_count("delta_rule_fwd") == n0 + 1 and q.grad is not None
     B.check_status()
+
+
+@pytest.mark.parametrize("Bn,S,Skv,H,topk", [(1, 200, 256, 64, 64), (2, 96, 192, 16, 40), (1, 33, 48, 128, 48)])
+def test_sparse_mla_gather_form_forward_matches_reference(Bn, S, Skv, H, topk):
+    """Latent form (576-wide rows, 512-wide values, one shared KV head) without a gradient runs the gather kernel: arbitrary key
+    lists (not causal, S != Skv), −1 slots, a row with no valid slot at all."""
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops import sparse_mla as SM
+    torch.manual_seed(5)
+    dev, D, dv = "cuda", 576, 512
+    q = (torch.randn(Bn, S, H, D, device=dev) * 0.2).bfloat16()
+    kv = (torch.randn(Bn, Skv, 1, D, device=dev) * 0.3).bfloat16()
+    idx = torch.stack([torch.stack([torch.randperm(Skv, device=dev)[:topk] for _ in range(S)]) for _ in range(Bn)]).int().view(Bn, S, 1, topk)
+    idx[:, :, :, topk // 2:] = torch.where(torch.rand(Bn, S, 1, topk - topk // 2, device=dev) < 0.3, -1, idx[:, :, :, topk // 2:])
+    idx[0, 3] = -1                                         # a query with no key at all
+    assert SM.gather_forward_supported(q, kv, idx, dv)
+    n0 = B.launch_count("paged_decode")
+    with torch.no_grad():
+        o, lse = SM.sparse_mla_gather_forward(q, kv, idx, d_v=dv)
+        if S != Skv:                                       # a key list the masked (causal, S == Skv) form cannot take: the dispatcher gathers
+            o2, _ = ops.sparse_mla_attention(q, kv, idx, d_v=dv)
+            assert torch.equal(o, o2)
+    assert B.launch_count("paged_decode") == n0 + (2 if S != Skv else 1)
+    orf, lr = ops.sparse_mla_reference(q.float(), kv.float(), idx, d_v=dv)
+    assert (o.float() - orf).abs().max() < 3e-2 * orf.abs().max() + 1e-3
+    fin = torch.isfinite(lr)
+    assert torch.equal(torch.isfinite(lse), fin) and (lse[fin] - lr[fin]).abs().max() < 3e-2
+    assert float(o[0, 3].abs().max()) == 0.0
+    # with a gradient requested the differentiable masked form is taken instead
+    assert not SM.gather_forward_supported(q.requires_grad_(), kv, idx, dv)
+    B.check_status()
