@@ -267,6 +267,19 @@ def _rows(w: torch.Tensor, start: int, n: int) -> torch.Tensor:
     return w[start:start + n]
 
 
+def _span(start: int, n: int) -> torch.Tensor:
+    return torch.arange(start, start + n, dtype=torch.long)
+
+
+def _index_map(logical_leaf: str, dim: int, index: torch.Tensor, size: int, contribute=None):
+    """One entry of a module's ``tp_index_maps``: local index i along ``dim`` is logical index ``index[i]`` of ``logical_leaf``
+    (extent ``size``); ``contribute`` (bool per local index, or one bool for all) says which of them this rank writes when the
+    logical tensor is gathered.  Read by ``parallel.sharded_state.sharded_specs``."""
+    if isinstance(contribute, bool):
+        contribute = None if contribute else torch.zeros(index.numel(), dtype=torch.bool)
+    return (logical_leaf, dim, index, size, contribute)
+
+
 def _shard_mla(full, group):
     """Head-parallel copy of an ``MLAAttention``: per-head projections sliced, low-rank projections / norms / indexer replicated."""
     import dataclasses
@@ -289,6 +302,10 @@ def _shard_mla(full, group):
         loc.wkv_b.weight.copy_(_rows(full.wkv_b.weight, r * Hl * dkv, Hl * dkv))
         loc.wo.weight.copy_(full.wo.weight[:, r * Hl * c.v_head_dim:(r + 1) * Hl * c.v_head_dim])
     loc.tp_group = group
+    H = c.num_heads
+    loc.tp_index_maps = {"wq_b.weight": _index_map("wq_b.weight", 0, _span(r * Hl * dq, Hl * dq), H * dq),
+                         "wkv_b.weight": _index_map("wkv_b.weight", 0, _span(r * Hl * dkv, Hl * dkv), H * dkv),
+                         "wo.weight": _index_map("wo.weight", 1, _span(r * Hl * c.v_head_dim, Hl * c.v_head_dim), H * c.v_head_dim)}
     loc.train(full.training)
     return loc
 
@@ -317,6 +334,7 @@ def _shard_moe(full, group):
         if full.shared_expert is not None:
             loc.shared_expert.load_state_dict(full.shared_expert.state_dict())
     loc.local_experts, loc.tp_group, loc.tp_rank = Le, group, r
+    loc.tp_index_maps = {f"experts.{leaf}": _index_map(f"experts.{leaf}", 0, _span(r * Le, Le), c.num_experts) for leaf in ("w_gate_up", "w_down")}
     loc.train(full.training)
     return loc
 
@@ -344,29 +362,32 @@ def _shard_m2rnn(full, group):
         loc = M2RNNMixer(lc).to(dt)
     K, V = c.k_head_dim, c.v_head_dim
 
-    def seg(total_heads, width, base):        # rows of the packed projection / conv for one input, this rank's share
-        n = total_heads * width
+    def seg(total_heads, width, base):        # logical rows of the packed projection / conv for one input (this rank's share), and
+        n = total_heads * width               # whether the segment is replicated (kept whole on every rank)
         if total_heads % tp:
-            return base, n, base + n          # replicated: the whole segment
-        return base + r * (n // tp), n // tp, base + n
-    rows, conv_rows, base = [], [], 0
+            return _span(base, n), True, base + n
+        return _span(base + r * (n // tp), n // tp), False, base + n
+    rows, conv_rows, conv_rep, base = [], [], [], 0
     for heads, width in ((c.num_q_heads, K), (c.num_k_heads, K), (c.num_v_heads, V)):
-        s0, n, base = seg(heads, width, base)
-        rows.append((s0, n))
-        conv_rows.append((s0, n))
-    s0, n, base = seg(c.num_f_heads, 1, base)
-    rows.append((s0, n))
-    s0, n, base = seg(c.num_g_heads, V, base)
-    rows.append((s0, n))
-    pick = lambda w, spans: torch.cat([w[a:a + b] for a, b in spans], 0)
+        idx, rep, base = seg(heads, width, base)
+        rows.append(idx)
+        conv_rows.append(idx)
+        conv_rep.append(torch.full((idx.numel(),), rep))
+    conv_total = base
+    idx, _, base = seg(c.num_f_heads, 1, base)
+    rows.append(idx)
+    idx, _, base = seg(c.num_g_heads, V, base)
+    rows.append(idx)
+    rows, conv_rows, conv_rep, proj_total = torch.cat(rows), torch.cat(conv_rows), torch.cat(conv_rep), base
     Hl = H // tp
+    nw = c.num_weight_heads
+    dev_idx = lambda t: t.to(dev)
     with torch.no_grad():
-        loc.in_proj.weight.copy_(pick(full.in_proj.weight, rows))
-        loc.conv_weight.copy_(pick(full.conv_weight, conv_rows))
-        loc.conv_bias.copy_(pick(full.conv_bias, conv_rows))
+        loc.in_proj.weight.copy_(full.in_proj.weight.index_select(0, dev_idx(rows)))
+        loc.conv_weight.copy_(full.conv_weight.index_select(0, dev_idx(conv_rows)))
+        loc.conv_bias.copy_(full.conv_bias.index_select(0, dev_idx(conv_rows)))
         loc.g_norm.weight.copy_(full.g_norm.weight[r * Hl * V:(r + 1) * Hl * V])
         loc.out_proj.weight.copy_(full.out_proj.weight[:, r * Hl * V:(r + 1) * Hl * V])
-        nw = c.num_weight_heads
         loc.state_weight.copy_(full.state_weight if nw % tp else full.state_weight[r * (nw // tp):(r + 1) * (nw // tp)])
         loc.A_log.copy_(full.A_log[r * Hl:(r + 1) * Hl])
         loc.dt_bias.copy_(full.dt_bias[r * Hl:(r + 1) * Hl])
@@ -377,14 +398,27 @@ def _shard_m2rnn(full, group):
         raise ValueError("head-parallel M2RNN: a replicated k segment behind a split q segment is not supported")
     loc.tp_replicated = tuple(n for n, heads in (("q", c.num_q_heads), ("k", c.num_k_heads), ("w", nw)) if heads % tp)
     loc.tp_replicated_rows = sum(heads * K for heads in (c.num_q_heads, c.num_k_heads) if heads % tp)   # leading rows of the projection
-    if loc.tp_replicated_rows:
+    n = loc.tp_replicated_rows
+    conv_writes = ~conv_rep if r else None            # replicated rows are written to a checkpoint by the first rank of the group only
+    maps = {"in_proj.weight": _index_map("in_proj.weight", 0, rows[n:], proj_total),
+            "conv_weight": _index_map("conv_weight", 0, conv_rows, conv_total, conv_writes),
+            "conv_bias": _index_map("conv_bias", 0, conv_rows, conv_total, conv_writes),
+            "g_norm.weight": _index_map("g_norm.weight", 0, _span(r * Hl * V, Hl * V), H * V),
+            "out_proj.weight": _index_map("out_proj.weight", 1, _span(r * Hl * V, Hl * V), H * V),
+            "A_log": _index_map("A_log", 0, _span(r * Hl, Hl), H), "dt_bias": _index_map("dt_bias", 0, _span(r * Hl, Hl), H)}
+    if full.D is not None:
+        maps["D"] = _index_map("D", 0, _span(r * Hl, Hl), H)
+    if nw % tp == 0:
+        maps["state_weight"] = _index_map("state_weight", 0, _span(r * (nw // tp), nw // tp), nw)
+    if n:
         # The replicated rows get a parameter of their own: inside one matrix with this rank's slice, a matrix-wise optimizer
         # (Muon orthogonalises whole matrices) would update them differently on every rank and the copies would drift apart.
-        n = loc.tp_replicated_rows
         w = loc.in_proj.weight.detach()
         loc.in_proj_rep = nn.Module()
         loc.in_proj_rep.weight = nn.Parameter(w[:n].clone())
         loc.in_proj.weight = nn.Parameter(w[n:].clone())
+        maps["in_proj_rep.weight"] = _index_map("in_proj.weight", 0, rows[:n], proj_total, r == 0)
+    loc.tp_index_maps = maps
     loc.train(full.training)
     return loc
 
@@ -417,29 +451,38 @@ class Mamba3TP(nn.Module):
         self.n_own = max(0, min(G - r * Hl, Hl))            # local heads whose step size comes from the replicated rows (global index < G)
         base = 2 * d_in + 2 * d_bc                          # first dd_dt row of the packed projection
         W = full.in_proj.weight.detach()
-        rows = lambda a, n: W[a:a + n]
-        rep = torch.cat([rows(base, G), rows(base + 3 * H, R)], 0)
-        lo = r * Hl
-        sl = torch.cat([rows(r * d_l, d_l), rows(d_in + r * d_l, d_l), rows(2 * d_in + r * dbc_l, dbc_l), rows(2 * d_in + d_bc + r * dbc_l, dbc_l),
-                        rows(base + lo + self.n_own, Hl - self.n_own), rows(base + H + lo, Hl), rows(base + 2 * H + lo, Hl)], 0)
+        lo, g0 = r * Hl, r * Gl
+        total = base + 3 * H + R
+        rep_idx = torch.cat([_span(base, G), _span(base + 3 * H, R)])
+        sl_idx = torch.cat([_span(r * d_l, d_l), _span(d_in + r * d_l, d_l), _span(2 * d_in + r * dbc_l, dbc_l), _span(2 * d_in + d_bc + r * dbc_l, dbc_l),
+                            _span(base + lo + self.n_own, Hl - self.n_own), _span(base + H + lo, Hl), _span(base + 2 * H + lo, Hl)])
         dev, dt = W.device, W.dtype
         self.in_proj_rep = nn.Module()
-        self.in_proj_rep.weight = nn.Parameter(rep.clone())
+        self.in_proj_rep.weight = nn.Parameter(W.index_select(0, rep_idx.to(dev)).clone())
         self.in_proj = nn.Module()
-        self.in_proj.weight = nn.Parameter(sl.clone())
-        cw, cb = full.conv_weight.detach(), full.conv_bias.detach()
-        pick = lambda t: torch.cat([t[r * d_l:(r + 1) * d_l], t[d_in + r * dbc_l:d_in + (r + 1) * dbc_l],
-                                    t[d_in + d_bc + r * dbc_l:d_in + d_bc + (r + 1) * dbc_l]], 0)
-        self.conv_weight, self.conv_bias = nn.Parameter(pick(cw).clone()), nn.Parameter(pick(cb).clone())
+        self.in_proj.weight = nn.Parameter(W.index_select(0, sl_idx.to(dev)).clone())
+        conv_idx = torch.cat([_span(r * d_l, d_l), _span(d_in + r * dbc_l, dbc_l), _span(d_in + d_bc + r * dbc_l, dbc_l)])
+        self.conv_weight = nn.Parameter(full.conv_weight.detach().index_select(0, conv_idx.to(dev)).clone())
+        self.conv_bias = nn.Parameter(full.conv_bias.detach().index_select(0, conv_idx.to(dev)).clone())
         self.dt_bias = nn.Parameter(full.dt_bias.detach()[lo:lo + Hl].clone())          # entries of the n_own heads are unused here
         self.rep_dt_bias = nn.Parameter(full.dt_bias.detach()[:G].clone())
-        g0 = r * Gl
         for n in ("B_norm_weight", "C_norm_weight", "B_bias", "C_bias"):
             setattr(self, n, nn.Parameter(getattr(full, n).detach()[:, g0:g0 + Gl].clone()))
         self.D = nn.Parameter(full.D.detach()[lo:lo + Hl].clone())
         self.out_proj = Linear(d_l, c.d_model).to(dev, dt)
         with torch.no_grad():
             self.out_proj.weight.copy_(full.out_proj.weight[:, r * d_l:(r + 1) * d_l])
+        conv_total = d_in + 2 * d_bc
+        own_dt = torch.arange(Hl) >= self.n_own          # the other step-size biases live in rep_dt_bias
+        self.tp_index_maps = {
+            "in_proj_rep.weight": _index_map("in_proj.weight", 0, rep_idx, total, r == 0),
+            "in_proj.weight": _index_map("in_proj.weight", 0, sl_idx, total),
+            "conv_weight": _index_map("conv_weight", 0, conv_idx, conv_total), "conv_bias": _index_map("conv_bias", 0, conv_idx, conv_total),
+            "rep_dt_bias": _index_map("dt_bias", 0, _span(0, G), H, r == 0),
+            "dt_bias": _index_map("dt_bias", 0, _span(lo, Hl), H, own_dt),
+            "D": _index_map("D", 0, _span(lo, Hl), H),
+            "out_proj.weight": _index_map("out_proj.weight", 1, _span(r * d_l, d_l), d_in),
+            **{n: _index_map(n, 1, _span(g0, Gl), G) for n in ("B_norm_weight", "C_norm_weight", "B_bias", "C_bias")}}
         self.train(full.training)
 
     def forward(self, hidden_states, *, h0=None, cache=None, return_cache: bool = False, cache_out=None):

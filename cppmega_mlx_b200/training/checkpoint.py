@@ -507,10 +507,12 @@ def load_checkpoint(model: torch.nn.Module, path, *, optimizer=None, training_st
     except ValueError as e:
         raise CheckpointError(f"checkpoint {path}: {e}") from e
     local_params = dict(model.named_parameters())
-    params = {(specs[n].logical_name if n in specs else n): p for n, p in local_params.items()}
-    spec_of = {s.logical_name: s for s in specs.values()}
+    targets: dict[str, list] = {}                    # logical name -> [(local parameter, its spec or None)]; several for a logical tensor
+    for n, p in local_params.items():                # that is spread over more than one local parameter
+        sp = specs.get(n)
+        targets.setdefault(sp.logical_name if sp else n, []).append((p, sp))
     tied = getattr(getattr(model, "config", None), "tie_embeddings", False)
-    wanted = {n: (logical_shape(p.shape, spec_of[n]) if n in spec_of else p.shape) for n, p in params.items()
+    wanted = {n: (logical_shape(ps[0][0].shape, ps[0][1]) if ps[0][1] is not None else ps[0][0].shape) for n, ps in targets.items()
               if not (tied and n == "lm_head.weight")}
     try:
         mapped = from_reference_names(stored, wanted)
@@ -541,9 +543,8 @@ def load_checkpoint(model: torch.nn.Module, path, *, optimizer=None, training_st
     # ---- mutation starts here
     with torch.no_grad():
         for n, t in mapped.items():
-            if n in spec_of:
-                t = slice_local(t, spec_of[n])
-            params[n].copy_(t.to(params[n].device, params[n].dtype))
+            for p, sp in targets[n]:
+                p.copy_((slice_local(t, sp) if sp is not None else t).to(p.device, p.dtype))
         named_buffers = dict(model.named_buffers())
         for n, t in buffers.items():
             if n in named_buffers and named_buffers[n].shape == t.shape:
