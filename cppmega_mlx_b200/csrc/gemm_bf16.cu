@@ -21,6 +21,8 @@
 //
 // Takes the role of the reference's dense `mx.matmul` call sites ("Path A",
 // docs/production_kernel_routing.md:62-140); there is no GEMM kernel in the reference to compare to.
+#include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 #include "sm100.cuh"
@@ -76,12 +78,15 @@ struct GemmParams {
   int* status;
 };
 
-template <int BN>
+// PAIR = 1: two CTAs of a cluster share one 256×BN tile (tcgen05 cta_group::2).  Each stages its own 128 rows of A and half of
+// B's rows, so a stage is 32 KB instead of 48 KB per CTA and the ring is six deep.
+template <int BN, int PAIR = 0>
 struct GemmCfg {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
-  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;      // rows of B this CTA stages
+  static constexpr int B_BYTES = B_ROWS * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = PAIR ? 6 : ((BN == 256) ? 4 : 6);
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int C_BYTES = GEMM_EPI_WARPS * GEMM_CBOX_BYTES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + C_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
@@ -92,6 +97,16 @@ __device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* m
   asm volatile(
       "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+      "r"(c3), "r"(c4)
+      : "memory");
+}
+// The same load issued by a CTA of a pair: the transaction bytes are counted on `bar_cluster_addr`, an mbarrier that may live in
+// the other CTA of the pair (the issuing CTA's barrier of the even CTA collects both halves of a stage).
+__device__ __forceinline__ void tma_load_5d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int c0, int c1,
+                                                 int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2),
       "r"(c3), "r"(c4)
       : "memory");
 }
@@ -169,11 +184,18 @@ __device__ __forceinline__ void k_range(int flags, int m0, int num_kb, const int
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int PAIR = 0>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, PAIR>;
+  // PAIR: launched as clusters of two CTAs.  Both walk the same sequence of 256-row tiles; CTA `rank` owns rows
+  // [rank·128, rank·128 + 128) of the tile and rows [rank·BN/2, …) of B's tile.  The even CTA's MMA thread issues for both.
+  constexpr int TILE_M = GEMM_BM << PAIR;
+  const int cta_rank = PAIR ? static_cast<int>(cluster_ctarank()) : 0;
+  const int first_tile = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int tile_stride = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int m_off = cta_rank * GEMM_BM;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -188,9 +210,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_m = (p.M + GEMM_BM - 1) / GEMM_BM;
+  const int num_m = (p.M + TILE_M - 1) / TILE_M;
   const int num_n = (p.N + BN - 1) / BN;
-  const bool causal = (p.flags & GEMM_CAUSAL_SKIP) != 0;
+  const bool causal = (p.flags & GEMM_CAUSAL_SKIP) != 0;   // never with PAIR (the host does not pair such launches)
   const int per_problem = tiles_per_problem(p.flags, num_m, num_n, BN);
   const int num_tiles = per_problem * p.nb2 * p.nb3 * p.nb4;
   const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
@@ -204,7 +226,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
-      mbar_init(&tempty_bar[b], GEMM_EPI_WARPS);
+      mbar_init(&tempty_bar[b], GEMM_EPI_WARPS << PAIR);   // PAIR: the epilogue warps of both CTAs release the even CTA's barrier
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -213,11 +235,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR)
+    cluster_sync_all();   // the other CTA's barriers are initialised before anything signals them
+  else
+    __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -227,9 +257,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
         const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3, per_problem, causal, BN);
-        const int m0 = tc.tm * GEMM_BM, n0 = tc.tn * BN;
+        const int m0 = tc.tm * TILE_M + m_off, n0 = tc.tn * BN + cta_rank * Cfg::B_ROWS;
         const int a2 = tc.i2 / p.a_div2;
         const int b2 = p.tile_group != nullptr ? p.tile_group[tc.tm] : tc.i2 / p.b_div2;
         if (tile_skipped(p.flags, m0, n0, m_limit)) continue;
@@ -242,21 +272,41 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
-          mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
           const int k0 = kb * GEMM_BK;
-          if (A_MN) {
+          if (PAIR) {
+            // both CTAs' bytes are counted on the even CTA's barrier, which only its own producer arms
+            const uint32_t lead_full = mapa_u32(smem_u32(&full_bar[stage]), 0);
+            if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::STAGE_BYTES);
+            if (A_MN) {
 #pragma unroll
-            for (int i = 0; i < GEMM_BM / 64; ++i)
-              tma_load_5d(sa + i * (GEMM_BK * 128), &tmA, &full_bar[stage], m0 + 64 * i, k0, a2, tc.i3, tc.i4);
-          } else {
-            tma_load_5d(sa, &tmA, &full_bar[stage], k0, m0, a2, tc.i3, tc.i4);
-          }
-          if (B_MN) {
+              for (int i = 0; i < GEMM_BM / 64; ++i)
+                tma_load_5d_pair(sa + i * (GEMM_BK * 128), &tmA, lead_full, m0 + 64 * i, k0, a2, tc.i3, tc.i4);
+            } else {
+              tma_load_5d_pair(sa, &tmA, lead_full, k0, m0, a2, tc.i3, tc.i4);
+            }
+            if (B_MN) {
 #pragma unroll
-            for (int i = 0; i < BN / 64; ++i)
-              tma_load_5d(sb + i * (GEMM_BK * 128), &tmB, &full_bar[stage], n0 + 64 * i, k0, b2, tc.i3, tc.i4);
+              for (int i = 0; i < Cfg::B_ROWS / 64; ++i)
+                tma_load_5d_pair(sb + i * (GEMM_BK * 128), &tmB, lead_full, n0 + 64 * i, k0, b2, tc.i3, tc.i4);
+            } else {
+              tma_load_5d_pair(sb, &tmB, lead_full, k0, n0, b2, tc.i3, tc.i4);
+            }
           } else {
-            tma_load_5d(sb, &tmB, &full_bar[stage], k0, n0, b2, tc.i3, tc.i4);
+            mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+            if (A_MN) {
+#pragma unroll
+              for (int i = 0; i < GEMM_BM / 64; ++i)
+                tma_load_5d(sa + i * (GEMM_BK * 128), &tmA, &full_bar[stage], m0 + 64 * i, k0, a2, tc.i3, tc.i4);
+            } else {
+              tma_load_5d(sa, &tmA, &full_bar[stage], k0, m0, a2, tc.i3, tc.i4);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int i = 0; i < BN / 64; ++i)
+                tma_load_5d(sb + i * (GEMM_BK * 128), &tmB, &full_bar[stage], n0 + 64 * i, k0, b2, tc.i3, tc.i4);
+            } else {
+              tma_load_5d(sb, &tmB, &full_bar[stage], k0, n0, b2, tc.i3, tc.i4);
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -267,15 +317,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(GEMM_BM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc(TILE_M, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
         const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3, per_problem, causal, BN);
-        const int m0 = tc.tm * GEMM_BM;
+        const int m0 = tc.tm * TILE_M;
         if (tile_skipped(p.flags, m0, tc.tn * BN, m_limit)) continue;
         int kb0, kb1;
         k_range(p.flags, m0, num_kb, p.k_ranges, tc.i2, kb0, kb1);
@@ -299,15 +349,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                         : make_smem_desc_sw128(sa + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc_sw128(sb + k * 2048, GEMM_BK * 128, 1024)
                                         : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-            umma_f16(tmem_d, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (PAIR)
+              umma_f16_pair(tmem_d, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else
+              umma_f16(tmem_d, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(&empty_bar[stage]);
+          if (PAIR)
+            umma_commit_pair(&empty_bar[stage], 3);   // the stage goes back to both CTAs' producers
+          else
+            umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) umma_commit(&tfull_bar[buf]);
+        if (ok) {
+          if (PAIR)
+            umma_commit_pair(&tfull_bar[buf], 3);
+          else
+            umma_commit(&tfull_bar[buf]);
+        }
       }
     }
   } else {
@@ -328,9 +389,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool e_amax = (p.flags & GEMM_EPI_AMAX) != 0 && p.amax != nullptr;
     uint8_t* cbox = csmem + ew * GEMM_CBOX_BYTES;
     int local = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    const uint32_t lead_tempty = PAIR ? mapa_u32(smem_u32(&tempty_bar[0]), 0) : 0u;
+    for (int t = first_tile; t < num_tiles; t += tile_stride) {
       const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3, per_problem, causal, BN);
-      if (tile_skipped(p.flags, tc.tm * GEMM_BM, tc.tn * BN, m_limit)) continue;
+      const int tile_m0 = tc.tm * TILE_M + m_off;
+      if (tile_skipped(p.flags, tile_m0, tc.tn * BN, m_limit)) continue;
       const int buf = local & 1;
       const uint32_t aphase = (local >> 1) & 1;
       ++local;
@@ -339,10 +402,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool empty_k = false;
       if (p.k_ranges != nullptr) {  // a problem with no contraction steps leaves the accumulator unwritten: emit zeros
         int kb0, kb1;
-        k_range(p.flags, tc.tm * GEMM_BM, num_kb, p.k_ranges, tc.i2, kb0, kb1);
+        k_range(p.flags, tile_m0, num_kb, p.k_ranges, tc.i2, kb0, kb1);
         empty_k = kb0 >= kb1;
       }
-      const int row0 = tc.tm * GEMM_BM + quarter * 32;
+      const int row0 = tile_m0 + quarter * 32;
       const int row = row0 + lane;
       const int ncol0 = tc.tn * BN + half * (BN / 2);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + half * (BN / 2);
@@ -541,7 +604,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+      if (lane == 0) {
+        if (PAIR)
+          mbar_arrive_cluster(lead_tempty + buf * 8);
+        else
+          mbar_arrive(&tempty_bar[buf]);
+      }
     }
     if (lane == 0) tma_store_wait<0>();  // all global writes done before the staging memory goes away
   }
@@ -554,10 +622,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int i = 0; i < 64; ++i) __nanosleep(2000);
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR)
+    cluster_sync_all();   // neither CTA leaves (or frees TMEM) while the other may still signal its barriers or read its tiles
+  else
+    __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (PAIR)
+      tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+    else
+      tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
@@ -672,9 +746,29 @@ struct GemmArgs {
   cudaStream_t stream;
 };
 
-template <int BN, bool A_MN, bool B_MN>
+// Launches that may run as CTA pairs: plain dense products (any of the element-wise epilogues), nothing whose tile set or
+// contraction range depends on the 128-row tile (causal skipping, per-tile groups, row limits), and at least one full 256-row tile.
+static bool pair_eligible(const GemmArgs& g) {
+  constexpr int no = cmb::GEMM_CAUSAL_SKIP | cmb::GEMM_K_UPPER | cmb::GEMM_K_LOWER | cmb::GEMM_EPI_SOFTMAX_STATS | cmb::GEMM_EPI_EXP_MASK |
+                     cmb::GEMM_EPI_DS | cmb::GEMM_EPI_SYM_MIRROR;
+  return (g.flags & no) == 0 && g.tile_group == nullptr && g.k_ranges == nullptr && g.m_limit == nullptr && g.M >= 256;
+}
+
+// 0 = off, 1 = on for eligible launches (the default: 4–13 % faster on the model's projection shapes).  The environment
+// variable CPPMEGA_GEMM_PAIR sets the initial value;
+// cmb_gemm_set_pair_mode changes it for the process.
+static std::atomic<int>& pair_mode_ref() {
+  static std::atomic<int> mode{[] {
+    const char* e = std::getenv("CPPMEGA_GEMM_PAIR");
+    return e != nullptr ? (std::atoi(e) != 0 ? 1 : 0) : 1;
+  }()};
+  return mode;
+}
+static int pair_mode() { return pair_mode_ref().load(std::memory_order_relaxed); }
+
+template <int BN, bool A_MN, bool B_MN, int PAIR = 0>
 static int launch_gemm(const GemmArgs& g) {
-  using Cfg = cmb::GemmCfg<BN>;
+  using Cfg = cmb::GemmCfg<BN, PAIR>;
   CUtensorMap tmA, tmB, tmC;
   int rc;
   uint64_t nbA[3] = {g.nb[0] / g.a_div2, g.nb[1], g.nb[2]};
@@ -688,7 +782,7 @@ static int launch_gemm(const GemmArgs& g) {
   if (B_MN)
     rc = make_tmap_5d(&tmB, g.B, 2, g.K, g.N, g.ldb, nbB, g.sB, cmb::GEMM_BK, 64);
   else
-    rc = make_tmap_5d(&tmB, g.B, 2, g.N, g.K, g.ldb, nbB, g.sB, BN, cmb::GEMM_BK);
+    rc = make_tmap_5d(&tmB, g.B, 2, g.N, g.K, g.ldb, nbB, g.sB, Cfg::B_ROWS, cmb::GEMM_BK);
   if (rc) return rc + 10000;
   const bool f32 = (g.flags & cmb::GEMM_OUT_F32) != 0;
   if (g.flags & cmb::GEMM_EPI_SOFTMAX_STATS) {
@@ -697,14 +791,19 @@ static int launch_gemm(const GemmArgs& g) {
     rc = make_tmap_5d(&tmC, g.C, f32 ? 4 : 2, g.M, g.N, g.ldc, g.nb, g.sC, 32, f32 ? 32 : 64);
     if (rc) return rc + 20000;
   }
-  auto kern = cmb::gemm_bf16_kernel<BN, A_MN, B_MN>;
+  auto kern = cmb::gemm_bf16_kernel<BN, A_MN, B_MN, PAIR>;
   static std::atomic<unsigned long long> attr_done{0};
   if (set_smem_limit_once_per_device(attr_done, reinterpret_cast<const void*>(kern), Cfg::SMEM_BYTES)) return 103;
-  const long long num_tiles = static_cast<long long>(cmb::tiles_per_problem(g.flags, (g.M + cmb::GEMM_BM - 1) / cmb::GEMM_BM, (g.N + BN - 1) / BN, BN)) *
+  constexpr int tile_m = cmb::GEMM_BM << PAIR;
+  const long long num_tiles = static_cast<long long>(cmb::tiles_per_problem(g.flags, (g.M + tile_m - 1) / tile_m, (g.N + BN - 1) / BN, BN)) *
                               g.nb[0] * g.nb[1] * g.nb[2];
   if (num_tiles > 0x7fffffffLL) return 106;
   int grid = sm_count();
   if (g.max_ctas > 0 && g.max_ctas < grid) grid = g.max_ctas;
+  if (PAIR) {
+    grid /= 2;                                  // pairs
+    if (grid < 1) grid = 1;
+  }
   if (num_tiles < grid) grid = static_cast<int>(num_tiles);
   cmb::GemmParams p;
   p.M = g.M; p.N = g.N; p.K = g.K;
@@ -722,6 +821,21 @@ static int launch_gemm(const GemmArgs& g) {
   p.m_limit = g.m_limit;
   p.amax = g.amax;
   p.status = g.status;
+  if (PAIR) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * grid);
+    cfg.blockDim = dim3(cmb::GEMM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = g.stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, p) == cudaSuccess ? 0 : 104;
+  }
   kern<<<grid, cmb::GEMM_THREADS, Cfg::SMEM_BYTES, g.stream>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 104;
 }
@@ -731,6 +845,12 @@ static int dispatch(const GemmArgs& g, int a_mn, int b_mn) {
   if (g.a_div2 <= 0 || g.b_div2 <= 0 || g.nb[0] % g.a_div2 || g.nb[0] % g.b_div2) return 107;
   const bool big = g.N > 128;
 #define CMB_GEMM_CASE(BN_, AM_, BM_) return launch_gemm<BN_, AM_, BM_>(g)
+  if (big && pair_mode() == 1 && pair_eligible(g)) {
+    if (!a_mn && !b_mn) return launch_gemm<256, false, false, 1>(g);
+    if (!a_mn && b_mn) return launch_gemm<256, false, true, 1>(g);
+    if (a_mn && !b_mn) return launch_gemm<256, true, false, 1>(g);
+    return launch_gemm<256, true, true, 1>(g);
+  }
   if (big) {
     if (!a_mn && !b_mn) CMB_GEMM_CASE(256, false, false);
     if (!a_mn && b_mn) CMB_GEMM_CASE(256, false, true);
@@ -746,6 +866,9 @@ static int dispatch(const GemmArgs& g, int a_mn, int b_mn) {
 }
 
 }  // namespace cmb_host
+
+// Process-wide switch for the CTA-pair (cta_group::2) form of eligible launches; returns the previous value.
+extern "C" int cmb_gemm_set_pair_mode(int mode) { return cmb_host::pair_mode_ref().exchange(mode != 0 ? 1 : 0); }
 
 // C ABI. A is M×K (K-major, row pitch lda) or, with a_mn_major, stored K×M (row pitch lda).
 // B is N×K (K-major) or, with b_mn_major, stored K×N. C is M×N row-major (pitch ldc), bf16 unless

@@ -19,6 +19,13 @@ EPI_DECAY_MASK = 4
 EPI_ROW_EXP = 8
 
 
+def set_pair_mode(on: bool) -> bool:
+    """Run eligible launches (plain dense products with N > 128 and M >= 256) as CTA pairs: two SMs issue one 256-row
+    ``tcgen05.mma.cta_group::2`` per step and each stages only half of B.  Returns the previous setting.  The environment
+    variable ``CPPMEGA_GEMM_PAIR`` sets the initial value."""
+    return bool(B.load_library().cmb_gemm_set_pair_mode(int(bool(on))))
+
+
 def _ok(t: torch.Tensor) -> bool:
     return (t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0
             and t.data_ptr() % 16 == 0)

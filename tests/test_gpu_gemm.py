@@ -147,3 +147,38 @@ def test_small_m_linear_split_k_matches_fp32(M, N, K):
     ref = x.float() @ w.float().t()
     assert y.shape == (M, N) and y.dtype == torch.bfloat16 and y.is_contiguous()
     assert (y.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 512, 256), (1000, 328, 192), (4096, 2048, 2048), (384, 5632, 512)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_cta_pair_form_matches_fp32(M, N, K, a_mn, b_mn):
+    """The cta_group::2 form (two SMs per 256-row tile, half of B staged per CTA) against fp32, every operand layout, ragged
+    edges in M and N, bf16 / fp32 / accumulating outputs and the alpha·acc + beta·aux epilogue."""
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops import gemm as G
+    torch.manual_seed(M + N + K)
+    dev = "cuda"
+    a = torch.randn((K, M) if a_mn else (M, K), device=dev).bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device=dev).bfloat16()
+    ref = _ref(a, b, a_mn, b_mn)
+    tol = 2e-2 * (K ** 0.5) + 1e-2 * ref.abs().max().item()
+    prev = G.set_pair_mode(True)
+    try:
+        c = ops.gemm_raw(a, b, a_mn=a_mn, b_mn=b_mn)
+        c32 = ops.gemm_raw(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+        acc = torch.ones(M, N, device=dev, dtype=torch.float32)
+        ops.gemm_raw(a, b, a_mn=a_mn, b_mn=b_mn, out=acc, accumulate=True)
+        aux = torch.randn(M, N, device=dev).bfloat16()
+        ax = G.gemm_axpby(a, b, aux, a_mn=a_mn, b_mn=b_mn, alpha=0.5, beta=2.0)
+        torch.cuda.synchronize()
+        B.check_status()
+    finally:
+        G.set_pair_mode(prev)
+    assert (c.float() - ref).abs().max().item() < tol
+    assert (c32 - ref).abs().max().item() < 1e-3 * (K ** 0.5) + 1e-4 * ref.abs().max().item()
+    assert (acc - 1.0 - ref).abs().max().item() < 1e-3 * (K ** 0.5) + 1e-4 * ref.abs().max().item()
+    assert (ax.float() - (0.5 * ref + 2.0 * aux.float())).abs().max().item() < tol
+    # the pair form is bit-identical to the single-CTA form: same products, same accumulation order
+    c1 = ops.gemm_raw(a, b, a_mn=a_mn, b_mn=b_mn)
+    assert torch.equal(c, c1)
