@@ -680,7 +680,7 @@ def step_profile(args) -> list[dict]:
     ev = sorted([e for e in prof.key_averages() if e.device_time_total > 0], key=lambda e: -e.device_time_total)
     total = sum(e.device_time_total for e in ev)
     rows = [{"op": "training step kernel", "name": e.key[:110], "ms": e.device_time_total / 1e3, "launches": e.count,
-             "share": e.device_time_total / total} for e in ev[:40]]
+             "share": e.device_time_total / total} for e in ev[:90]]
     print(json.dumps({"op": "training step kernel time, total", "ms": total / 1e3}), flush=True)
     for r in rows:
         print(json.dumps(r), flush=True)

@@ -132,18 +132,20 @@ struct TileCoord {
 // With CAUSAL_SKIP only the tiles that touch the lower triangle are enumerated (row tm keeps its first causal_kept(tm) column
 // tiles), so a persistent CTA's share of the index space is a share of the real work: striding over all tiles and skipping left
 // the CTAs with up to 1.5× the mean number of kept tiles.
-__host__ __device__ __forceinline__ int causal_kept(int tm, int num_n, int bn) {
-  const int k = (tm * GEMM_BM + GEMM_BM - 1) / bn + 1;
+// `tile_m` is the row extent of a tile: 128, or 256 for a CTA pair.
+__host__ __device__ __forceinline__ int causal_kept(int tm, int num_n, int bn, int tile_m = GEMM_BM) {
+  const int k = (tm * tile_m + tile_m - 1) / bn + 1;
   return k < num_n ? k : num_n;
 }
-__host__ __device__ __forceinline__ int tiles_per_problem(int flags, int num_m, int num_n, int bn) {
+__host__ __device__ __forceinline__ int tiles_per_problem(int flags, int num_m, int num_n, int bn, int tile_m = GEMM_BM) {
   if (!(flags & GEMM_CAUSAL_SKIP)) return num_m * num_n;
   int n = 0;
-  for (int tm = 0; tm < num_m; ++tm) n += causal_kept(tm, num_n, bn);
+  for (int tm = 0; tm < num_m; ++tm) n += causal_kept(tm, num_n, bn, tile_m);
   return n;
 }
 
-__device__ __forceinline__ TileCoord tile_coords(int t, int num_m, int num_n, int nb2, int nb3, int per_problem, bool causal, int bn) {
+__device__ __forceinline__ TileCoord tile_coords(int t, int num_m, int num_n, int nb2, int nb3, int per_problem, bool causal, int bn,
+                                                 int tile_m = GEMM_BM) {
   TileCoord c;
   const int batch = t / per_problem;
   const int r0 = t - batch * per_problem;
@@ -154,7 +156,7 @@ __device__ __forceinline__ TileCoord tile_coords(int t, int num_m, int num_n, in
   if (causal) {
     int acc = 0, tm = 0;
     for (; tm < num_m - 1; ++tm) {
-      const int k = causal_kept(tm, num_n, bn);
+      const int k = causal_kept(tm, num_n, bn, tile_m);
       if (r0 < acc + k) break;
       acc += k;
     }
@@ -172,8 +174,9 @@ __device__ __forceinline__ TileCoord tile_coords(int t, int num_m, int num_n, in
   return c;
 }
 
-__device__ __forceinline__ bool tile_skipped(int flags, int m0, int n0, int m_limit) {
-  return ((flags & GEMM_CAUSAL_SKIP) && n0 >= m0 + GEMM_BM) || m0 >= m_limit;
+// `m0` is the first row of the whole tile (of the pair's 256 rows in the pair form), so both CTAs of a pair decide alike.
+__device__ __forceinline__ bool tile_skipped(int flags, int m0, int n0, int m_limit, int tile_m = GEMM_BM) {
+  return ((flags & GEMM_CAUSAL_SKIP) && n0 >= m0 + tile_m) || m0 >= m_limit;
 }
 __device__ __forceinline__ void k_range(int flags, int m0, int num_kb, const int* k_ranges, int i2, int& kb0, int& kb1) {
   kb0 = (flags & GEMM_K_LOWER) ? m0 / GEMM_BK : 0;
@@ -212,8 +215,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int num_m = (p.M + TILE_M - 1) / TILE_M;
   const int num_n = (p.N + BN - 1) / BN;
-  const bool causal = (p.flags & GEMM_CAUSAL_SKIP) != 0;   // never with PAIR (the host does not pair such launches)
-  const int per_problem = tiles_per_problem(p.flags, num_m, num_n, BN);
+  const bool causal = (p.flags & GEMM_CAUSAL_SKIP) != 0;
+  const int per_problem = tiles_per_problem(p.flags, num_m, num_n, BN, TILE_M);
   const int num_tiles = per_problem * p.nb2 * p.nb3 * p.nb4;
   const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
   int* status = p.status;
@@ -258,11 +261,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
-        const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3, per_problem, causal, BN);
+        const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3, per_problem, causal, BN, TILE_M);
         const int m0 = tc.tm * TILE_M + m_off, n0 = tc.tn * BN + cta_rank * Cfg::B_ROWS;
         const int a2 = tc.i2 / p.a_div2;
         const int b2 = p.tile_group != nullptr ? p.tile_group[tc.tm] : tc.i2 / p.b_div2;
-        if (tile_skipped(p.flags, m0, n0, m_limit)) continue;
+        if (tile_skipped(p.flags, tc.tm * TILE_M, tc.tn * BN, m_limit, TILE_M)) continue;
         int kb0, kb1;
         k_range(p.flags, m0, num_kb, p.k_ranges, tc.i2, kb0, kb1);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -324,9 +327,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int local = 0;
       bool ok = true;
       for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
-        const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3, per_problem, causal, BN);
+        const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3, per_problem, causal, BN, TILE_M);
         const int m0 = tc.tm * TILE_M;
-        if (tile_skipped(p.flags, m0, tc.tn * BN, m_limit)) continue;
+        if (tile_skipped(p.flags, m0, tc.tn * BN, m_limit, TILE_M)) continue;
         int kb0, kb1;
         k_range(p.flags, m0, num_kb, p.k_ranges, tc.i2, kb0, kb1);
         const int buf = local & 1;
@@ -391,9 +394,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int local = 0;
     const uint32_t lead_tempty = PAIR ? mapa_u32(smem_u32(&tempty_bar[0]), 0) : 0u;
     for (int t = first_tile; t < num_tiles; t += tile_stride) {
-      const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3, per_problem, causal, BN);
+      const TileCoord tc = tile_coords(t, num_m, num_n, p.nb2, p.nb3, per_problem, causal, BN, TILE_M);
       const int tile_m0 = tc.tm * TILE_M + m_off;
-      if (tile_skipped(p.flags, tile_m0, tc.tn * BN, m_limit)) continue;
+      if (tile_skipped(p.flags, tc.tm * TILE_M, tc.tn * BN, m_limit, TILE_M)) continue;
       const int buf = local & 1;
       const uint32_t aphase = (local >> 1) & 1;
       ++local;
@@ -539,9 +542,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rv);
         }
-        if (e_mirror && row < p.M && (row / BN) * BN >= (col0 / GEMM_BM) * GEMM_BM + GEMM_BM) {
+        if (e_mirror && row < p.M && (row / BN) * BN >= (col0 / TILE_M) * TILE_M + TILE_M) {
           // (col, row) lies in a tile the causal skip left out (its tile would start at column (row / BN)·BN ≥ its first row +
-          // 128): this thread's 32 values go there as column `row`; for a fixed j the warp writes 32 consecutive elements.
+          // the tile height): this thread's 32 values go there as column `row`; for a fixed j the warp writes 32 consecutive elements.
           __nv_bfloat16* cm = p.c_base + tc.i2 * p.sC2 + tc.i3 * p.sC3 + tc.i4 * p.sC4 + row;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
@@ -746,11 +749,11 @@ struct GemmArgs {
   cudaStream_t stream;
 };
 
-// Launches that may run as CTA pairs: plain dense products (any of the element-wise epilogues), nothing whose tile set or
-// contraction range depends on the 128-row tile (causal skipping, per-tile groups, row limits), and at least one full 256-row tile.
+// Launches that may run as CTA pairs: dense products with the element-wise epilogues, with or without lower-triangle tile
+// skipping and the symmetric mirror; nothing whose contraction range or operand depends on the 128-row tile (attention
+// epilogues, per-tile groups, row limits), and at least one full 256-row tile.
 static bool pair_eligible(const GemmArgs& g) {
-  constexpr int no = cmb::GEMM_CAUSAL_SKIP | cmb::GEMM_K_UPPER | cmb::GEMM_K_LOWER | cmb::GEMM_EPI_SOFTMAX_STATS | cmb::GEMM_EPI_EXP_MASK |
-                     cmb::GEMM_EPI_DS | cmb::GEMM_EPI_SYM_MIRROR;
+  constexpr int no = cmb::GEMM_K_UPPER | cmb::GEMM_K_LOWER | cmb::GEMM_EPI_SOFTMAX_STATS | cmb::GEMM_EPI_EXP_MASK | cmb::GEMM_EPI_DS;
   return (g.flags & no) == 0 && g.tile_group == nullptr && g.k_ranges == nullptr && g.m_limit == nullptr && g.M >= 256;
 }
 
@@ -795,7 +798,7 @@ static int launch_gemm(const GemmArgs& g) {
   static std::atomic<unsigned long long> attr_done{0};
   if (set_smem_limit_once_per_device(attr_done, reinterpret_cast<const void*>(kern), Cfg::SMEM_BYTES)) return 103;
   constexpr int tile_m = cmb::GEMM_BM << PAIR;
-  const long long num_tiles = static_cast<long long>(cmb::tiles_per_problem(g.flags, (g.M + tile_m - 1) / tile_m, (g.N + BN - 1) / BN, BN)) *
+  const long long num_tiles = static_cast<long long>(cmb::tiles_per_problem(g.flags, (g.M + tile_m - 1) / tile_m, (g.N + BN - 1) / BN, BN, tile_m)) *
                               g.nb[0] * g.nb[1] * g.nb[2];
   if (num_tiles > 0x7fffffffLL) return 106;
   int grid = sm_count();

@@ -182,3 +182,29 @@ def test_gemm_cta_pair_form_matches_fp32(M, N, K, a_mn, b_mn):
     # the pair form is bit-identical to the single-CTA form: same products, same accumulation order
     c1 = ops.gemm_raw(a, b, a_mn=a_mn, b_mn=b_mn)
     assert torch.equal(c, c1)
+
+
+@pytest.mark.parametrize("m,k,batch", [(512, 256, 1), (1024, 320, 3), (768, 2048, 2)])
+def test_symmetric_product_with_mirror_in_cta_pair_form(m, k, batch):
+    """X·Xᵀ with lower-triangle tile skipping and the in-epilogue mirror: the pair form (256-row tiles) fills the whole matrix,
+    matches fp32 and equals the single-CTA form bit for bit."""
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.ops import gemm as G
+    torch.manual_seed(m + k)
+    x = torch.randn(batch, m, k, device="cuda").bfloat16()
+    ref = x.float() @ x.float().transpose(1, 2)
+    outs = {}
+    for mode in (True, False):
+        prev = G.set_pair_mode(mode)
+        try:
+            out = torch.full((batch, m, m), float("nan"), device="cuda", dtype=torch.bfloat16)
+            G.gemm_batched(x, x, out, M=m, N=m, K=k, a_mn=False, b_mn=False, lda=k, ldb=k, ldc=m, nb=(batch, 1, 1), sA=(m * k, 0, 0),
+                           sB=(m * k, 0, 0), sC=(m * m, 0, 0), flags=G.CAUSAL_SKIP | G.EPI_SYM_MIRROR)
+            torch.cuda.synchronize()
+            B.check_status()
+        finally:
+            G.set_pair_mode(prev)
+        outs[mode] = out
+    assert not bool(torch.isnan(outs[True]).any())
+    assert (outs[True].float() - ref).abs().max().item() < 2e-2 * (k ** 0.5) + 1e-2 * ref.abs().max().item()
+    assert torch.equal(outs[True], outs[False])
