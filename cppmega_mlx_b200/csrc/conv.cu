@@ -421,6 +421,33 @@ __global__ void __launch_bounds__(256, 2) conv_silu_bwd_w4_kernel(const __nv_bfl
   }
 }
 
+// Rows of `width` bytes between two pitched 2-D buffers (a dense gradient into its columns of a packed one): 16 bytes per
+// thread and step when pointers, pitches and width allow, 2 bytes otherwise.
+template <typename V>
+__global__ void __launch_bounds__(256) copy2d_kernel(const uint8_t* __restrict__ src, long long src_pitch, uint8_t* __restrict__ dst,
+                                                     long long dst_pitch, long long rows, int vec_per_row) {
+  const long long total = rows * vec_per_row;
+  const long long stride = gridDim.x * 256ll;
+  for (long long i0 = blockIdx.x * 256ll + threadIdx.x; i0 < total; i0 += 4 * stride) {
+    V v[4];
+    long long off[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {      // four loads in flight per thread before the first store
+      const long long i = i0 + u * stride;
+      off[u] = -1;
+      if (i < total) {
+        const long long r = i / vec_per_row;
+        const long long c = (i - r * vec_per_row) * static_cast<long long>(sizeof(V));
+        v[u] = *reinterpret_cast<const V*>(src + r * src_pitch + c);
+        off[u] = r * dst_pitch + c;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (off[u] >= 0) *reinterpret_cast<V*>(dst + off[u]) = v[u];
+  }
+}
+
 }  // namespace cmb
 
 extern "C" int cmb_conv_silu_fwd(const void* in, long long ld_in, int c_off, const void* w, const void* bias, void* out1,
@@ -467,5 +494,26 @@ extern "C" int cmb_conv_silu_bwd(const void* in, long long ld_in, int c_off, con
   kern<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const bf*>(in), ld_in, c_off, static_cast<const bf*>(w),
                                                             static_cast<const bf*>(bias), static_cast<const bf*>(dy1), static_cast<const bf*>(dy2),
                                                             static_cast<bf*>(din), ld_din, dw, dbias, Bn, S, C, C1, K);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// dst[r, 0:width) = src[r, 0:width) for `rows` rows; pitches and width in bytes (width even).
+extern "C" int cmb_copy2d(const void* src, long long src_pitch, void* dst, long long dst_pitch, long long rows, long long width,
+                          void* stream) {
+  if (rows <= 0 || width <= 0) return 0;
+  if (width % 2 || src_pitch % 2 || dst_pitch % 2) return 1;
+  const auto a = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) | static_cast<uintptr_t>(src_pitch) |
+                 static_cast<uintptr_t>(dst_pitch) | static_cast<uintptr_t>(width);
+  const int vb = (a & 15) == 0 ? 16 : 2;
+  const long long total = rows * (width / vb);
+  const int sms = cmb_host::sm_count_current_device();
+  const int grid = static_cast<int>(std::min<long long>((total + 255) / 256, static_cast<long long>(sms) * 16));
+  auto st = static_cast<cudaStream_t>(stream);
+  if (vb == 16)
+    cmb::copy2d_kernel<uint4><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_pitch, static_cast<uint8_t*>(dst), dst_pitch, rows,
+                                                    static_cast<int>(width / 16));
+  else
+    cmb::copy2d_kernel<uint16_t><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_pitch, static_cast<uint8_t*>(dst), dst_pitch, rows,
+                                                       static_cast<int>(width / 2));
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }

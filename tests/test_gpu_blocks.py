@@ -50,12 +50,17 @@ def test_conv_silu_op(S, n_head, C, C1, n_tail):
     w = (torch.randn(C, 4, 1, device="cuda") * 0.3).bfloat16().requires_grad_()
     bias = (torch.randn(C, device="cuda") * 0.1).bfloat16().requires_grad_()
     head, o1, o2, tail = ops.packed_split_conv_silu(proj, n_head, C, C1, w, bias)
-    loss = (o1.float() ** 2).sum() + o2.float().sum() * 0.5 + head.float().sum() + (tail.float() ** 2).sum()
+    hc = torch.randn(2, S, n_head, device="cuda").bfloat16()        # a dense head gradient: the pitched-copy kernel packs it
+    loss = (o1.float() ** 2).sum() + o2.float().sum() * 0.5 + (head * hc).float().sum() + (tail.float() ** 2).sum()
     loss.backward()
     pr, wr, br = (t.detach().float().requires_grad_() for t in (proj, w, bias))
     r1, r2 = ops.conv.causal_conv1d_silu_reference(pr, n_head, C, C1, wr, br)
-    lr = (r1 ** 2).sum() + r2.sum() * 0.5 + pr[..., :n_head].sum() + (pr[..., n_head + C:] ** 2).sum()
+    lr = (r1 ** 2).sum() + r2.sum() * 0.5 + (pr[..., :n_head] * hc.float()).sum() + (pr[..., n_head + C:] ** 2).sum()
     lr.backward()
+    assert torch.equal(proj.grad[..., :n_head], hc)
+    if n_tail:
+        gt, rt = proj.grad[..., n_head + C:].float(), pr.grad[..., n_head + C:]
+        assert (gt - rt).abs().max() <= 2e-2 * (rt.abs().max() + 1e-6)
     assert (o1.float() - r1).abs().max() < 3e-2 and (o2.float() - r2).abs().max() < 3e-2
     assert (proj.grad.float() - pr.grad).abs().max() < 0.1 * pr.grad.abs().max()
     assert (w.grad.float() - wr.grad).abs().max() < 0.05 * wr.grad.abs().max() + 0.05
