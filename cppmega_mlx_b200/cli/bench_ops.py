@@ -34,8 +34,11 @@ GEMM_SHAPES = [
 
 def bench_gemm(args) -> list[dict]:
     from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import gemm as G
     pk = peaks()
     rows = []
+    if args.gemm_pair is not None:          # 1 / 0: the CTA-pair (cta_group::2) form on / off for this run; default: the library's
+        G.set_pair_mode(bool(args.gemm_pair))
     for M, N, K, a_mn, b_mn, label in GEMM_SHAPES:
         if args.only and args.only != label:
             continue
@@ -47,7 +50,7 @@ def bench_gemm(args) -> list[dict]:
         Bt = b if b_mn else b.t()
         lib = time_cuda(lambda: torch.matmul(A, Bt, out=out), iters=args.iters, warmup=args.warmup)
         fl = 2.0 * M * N * K
-        rows.append({"op": "gemm_bf16", "label": label, "M": M, "N": N, "K": K, "a_mn": a_mn, "b_mn": b_mn, "ms": ours,
+        rows.append({"op": "gemm_bf16", "label": label, "M": M, "N": N, "K": K, "a_mn": a_mn, "b_mn": b_mn, "pair": args.gemm_pair, "ms": ours,
                      "tflops": fl / ours / 1e9, "cublas_ms": lib, "cublas_tflops": fl / lib / 1e9,
                      "frac_of_measured_peak": fl / ours / 1e9 / pk["bf16_tflops"], "vs_cublas": lib / ours})
         print(json.dumps(rows[-1]), flush=True)
@@ -731,6 +734,7 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-eager", action="store_true")
+    ap.add_argument("--gemm-pair", type=int, default=None, choices=[0, 1], help="gemm: force the CTA-pair form off / on")
     ap.add_argument("--mla-seq", type=int, default=8192)
     ap.add_argument("--batch", type=int, default=1, help="decode_profile: sequences in the batch")
     ap.add_argument("--prompt", type=int, default=512, help="decode_profile: prompt length")
