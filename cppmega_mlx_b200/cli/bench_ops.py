@@ -338,14 +338,14 @@ def bench_fused_local(args) -> list[dict]:
     tab_p = _table([dict(off=0, n=n, u=u.data_ptr(), coef=1.0)], dev)
 
     def adamw():
-        B.check(lib.cmb_zero1_adamw_ranges(gp, pp, gp, 0, W, B.ptr(tab_a), 1, I64(n), f, -1, 0, I64(0), st, 0, B.stream_ptr()), "zero1_adamw_ranges")
+        B.check(lib.cmb_zero1_adamw_ranges(gp, pp, gp, 0, W, B.ptr(tab_a), 1, I64(n), f, -1, 0, I64(0), st, 0, 0, B.stream_ptr()), "zero1_adamw_ranges")
 
     def muon():
-        B.check(lib.cmb_zero1_muon_reduce_ranges(gp, pp, gp, 0, W, B.ptr(tab_m), 1, I64(n), F32(0.95), F32(0.0), 1, -1, 0, I64(0), st, 0, B.stream_ptr()),
+        B.check(lib.cmb_zero1_muon_reduce_ranges(gp, pp, gp, 0, W, B.ptr(tab_m), 1, I64(n), F32(0.95), F32(0.0), 1, -1, 0, I64(0), st, 0, 0, B.stream_ptr()),
                 "zero1_muon_reduce_ranges")
 
     def push():
-        B.check(lib.cmb_zero1_push_ranges(pp, 0, W, B.ptr(tab_p), 1, I64(n), F32(1e-3), B.stream_ptr()), "zero1_push_ranges")
+        B.check(lib.cmb_zero1_push_ranges(pp, 0, W, B.ptr(tab_p), 1, I64(n), F32(1e-3), 0, B.stream_ptr()), "zero1_push_ranges")
     for name, fn, bytes_per in (("zero1_adamw_ranges W=2 local", adamw, 2 * W + 2 + 16 + 2 * W), ("zero1_muon_reduce_ranges W=2 local", muon, 2 * W + 2 + 8 + 2),
                                 ("zero1_push_ranges W=2 local", push, 2 + 2 + 2 * W)):
         ms = time_cuda(fn, iters=args.iters, warmup=args.warmup)

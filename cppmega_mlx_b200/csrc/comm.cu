@@ -1,6 +1,8 @@
-// Kernels that talk to peer GPUs through symmetric memory over NVLink / NVSwitch (plain peer loads and stores
-// only; no `multimem` form is built).  Every rank maps every peer's
-// buffers, so `bufs[r]` below is rank r's copy of the same logical buffer.
+// Kernels that talk to peer GPUs through symmetric memory over NVLink / NVSwitch.  Every rank maps every peer's
+// buffers, so `bufs[r]` below is rank r's copy of the same logical buffer.  Two forms of the ZeRO-1 kernels exist: plain
+// peer loads and stores (one per rank), and — when the buffers are bound to an NVSwitch multicast object and the caller asks
+// for it — `multimem.ld_reduce` (the switch adds the W ranks' gradients, one load per 16 bytes) and `multimem.st` (one store
+// reaches every rank's parameter buffer).
 //
 //  * cmb_comm_barrier        epoch-flag barrier: release-store my epoch into every peer's pad, acquire-poll my pad.
 //                            The poll is bounded; on expiry a status word is set and the kernel returns.
@@ -22,6 +24,7 @@ constexpr int COMM_MAX_RANKS = 16;
 
 struct PeerPtrs {
   void* p[COMM_MAX_RANKS];
+  void* mc;   // multicast address of the same buffer (one access reaches every rank's copy), or nullptr
 };
 
 __device__ __forceinline__ void st_release_sys(int* addr, int v) {
@@ -75,8 +78,37 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return v;
 }
 
+// Sum over all ranks of 8 consecutive bf16 values at a multicast address (fp32 accumulation in the switch, bf16 result).
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+// 16 bytes to every rank's copy.
+__device__ __forceinline__ void multimem_st_16(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+// 16 bytes at element offset `e` to every rank: one multicast store, or one store per peer.
+__device__ __forceinline__ void store_all_16(const PeerPtrs& bufs, int world, long long e, const uint4& v) {
+  if (bufs.mc != nullptr) {
+    multimem_st_16(static_cast<__nv_bfloat16*>(bufs.mc) + e, v);
+  } else {
+    for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(bufs.p[r]) + e) = v;
+  }
+}
+
 // Sum of the W ranks' gradients for 8 consecutive elements starting at flat offset `e` (16-byte aligned).
 __device__ __forceinline__ void reduce8(const PeerPtrs& grads, int world, long long e, float inv_world, float (&g)[8]) {
+  if (grads.mc != nullptr) {
+    unpack8(multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(grads.mc) + e), g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] *= inv_world;
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < 8; ++i) g[i] = 0.f;
   for (int r = 0; r < world; ++r) {
@@ -113,8 +145,7 @@ __global__ void __launch_bounds__(256) zero1_push_update_kernel(PeerPtrs params,
     unpack8(*reinterpret_cast<const uint4*>(u + 8 * i), d);
 #pragma unroll
     for (int k = 0; k < 8; ++k) p[k] -= coef * d[k];
-    const uint4 out = pack8(p);
-    for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + e) = out;
+    store_all_16(params, world, e, pack8(p));
   }
 }
 
@@ -191,8 +222,7 @@ __global__ void __launch_bounds__(256) zero1_adamw_ranges_kernel(PeerPtrs grads,
       }
       st8f(rg.s0 + 8 * i, mm);
       st8f(rg.s1 + 8 * i, vv);
-      const uint4 out = pack8(p);
-      for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + e) = out;
+      store_all_16(params, world, e, pack8(p));
     }
     for (long long j = (nvec << 3) + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; j < rg.n; j += static_cast<long long>(gridDim.x) * blockDim.x) {
       float g = 0.f;
@@ -279,8 +309,7 @@ __global__ void __launch_bounds__(256) zero1_push_ranges_kernel(PeerPtrs params,
       unpack8(*reinterpret_cast<const uint4*>(rg.u + 8 * i), d);
 #pragma unroll
       for (int k = 0; k < 8; ++k) p[k] -= lr * rg.coef * d[k];
-      const uint4 out = pack8(p);
-      for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + e) = out;
+      store_all_16(params, world, e, pack8(p));
     }
   }
 }
@@ -290,9 +319,11 @@ static inline int comm_grid(long long nvec) {
   const long long cap = Z1_PARTS;
   return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
 }
-static inline bool fill(PeerPtrs& out, const long long* ptrs, int world) {
+// `ptrs` holds the W peer addresses; with `use_mc` it holds one more entry, the multicast address (0 = none).
+static inline bool fill(PeerPtrs& out, const long long* ptrs, int world, int use_mc = 0) {
   if (world < 1 || world > COMM_MAX_RANKS) return false;
   for (int r = 0; r < COMM_MAX_RANKS; ++r) out.p[r] = r < world ? reinterpret_cast<void*>(ptrs[r]) : nullptr;
+  out.mc = use_mc ? reinterpret_cast<void*>(ptrs[world]) : nullptr;
   return true;
 }
 
@@ -318,7 +349,8 @@ extern "C" int cmb_zero1_push_update(const long long* param_ptrs, int rank, int 
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
-// ---- bucketed forms. `ranges`: device array of {off, n (int64), s0, s1, u, sumsq (pointers), coef (fp32), pad} (56 bytes → 56, 8-byte aligned);
+// ---- bucketed forms. With `use_mc` the pointer arrays of the gradient and parameter buffers carry one more entry, the buffer's
+// multicast address, and the vector paths use `multimem` (the scalar tails keep plain peer accesses).  `ranges`: device array of {off, n (int64), s0, s1, u, sumsq (pointers), coef (fp32), pad} (56 bytes → 56, 8-byte aligned);
 // `flag_ptrs[r]`: rank r's int32[nbuckets · 16] flag block; a negative `bucket` skips the flag wait (the caller has synchronised already).
 extern "C" int cmb_zero1_bucket_signal(const long long* flag_ptrs, int rank, int world, int bucket, int epoch, void* stream) {
   cmb::PeerPtrs pads;
@@ -329,9 +361,9 @@ extern "C" int cmb_zero1_bucket_signal(const long long* flag_ptrs, int rank, int
 
 extern "C" int cmb_zero1_adamw_ranges(const long long* grad_ptrs, const long long* param_ptrs, const long long* flag_ptrs, int rank, int world,
                                       const void* ranges, int nranges, long long total_elems, const float* f, int bucket, int epoch,
-                                      long long spin_limit, int* status, int max_blocks, void* stream) {
+                                      long long spin_limit, int* status, int max_blocks, int use_mc, void* stream) {
   cmb::PeerPtrs g, p, fl;
-  if (!cmb::fill(g, grad_ptrs, world) || !cmb::fill(p, param_ptrs, world)) return 1;
+  if (!cmb::fill(g, grad_ptrs, world, use_mc) || !cmb::fill(p, param_ptrs, world, use_mc)) return 1;
   if (nranges <= 0) return 0;
   const int* flags = nullptr;
   if (bucket >= 0) {
@@ -348,9 +380,9 @@ extern "C" int cmb_zero1_adamw_ranges(const long long* grad_ptrs, const long lon
 
 extern "C" int cmb_zero1_muon_reduce_ranges(const long long* grad_ptrs, const long long* param_ptrs, const long long* flag_ptrs, int rank, int world,
                                             const void* ranges, int nranges, long long total_elems, float mu, float wd, int nesterov, int bucket,
-                                            int epoch, long long spin_limit, int* status, int max_blocks, void* stream) {
+                                            int epoch, long long spin_limit, int* status, int max_blocks, int use_mc, void* stream) {
   cmb::PeerPtrs g, p, fl;
-  if (!cmb::fill(g, grad_ptrs, world) || !cmb::fill(p, param_ptrs, world)) return 1;
+  if (!cmb::fill(g, grad_ptrs, world, use_mc) || !cmb::fill(p, param_ptrs, world)) return 1;
   if (nranges <= 0) return 0;
   const int* flags = nullptr;
   if (bucket >= 0) {
@@ -371,9 +403,9 @@ extern "C" int cmb_zero1_sumsq_finalize(float* partials, float* sumsq, int ntens
 }
 
 extern "C" int cmb_zero1_push_ranges(const long long* param_ptrs, int rank, int world, const void* ranges, int nranges, long long total_elems,
-                                     float lr, void* stream) {
+                                     float lr, int use_mc, void* stream) {
   cmb::PeerPtrs p;
-  if (!cmb::fill(p, param_ptrs, world)) return 1;
+  if (!cmb::fill(p, param_ptrs, world, use_mc)) return 1;
   if (nranges <= 0) return 0;
   cmb::zero1_push_ranges_kernel<<<cmb::comm_grid(total_elems / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       p, rank, world, static_cast<const cmb::Z1Range*>(ranges), nranges, lr);

@@ -99,6 +99,11 @@ class FusedZeRO1Comm:
         self.barrier = EpochBarrier(flat.params.device, self.group)
         mode = os.environ.get("CPPMEGA_ZERO1_OVERLAP", "auto")
         self.overlap = mode == "1" or (mode == "auto" and self.params_buf.world >= 4)
+        # CPPMEGA_ZERO1_MULTIMEM=1: reduce the gradients in the switch (multimem.ld_reduce) and push the parameters with one
+        # multicast store (multimem.st) instead of W peer loads / stores; needs buffers with a multicast binding.  Off by default:
+        # a rank that dies while bound to a multicast object can fault its peers' links, so failure tests keep to plain peer accesses.
+        self.use_mc = int(os.environ.get("CPPMEGA_ZERO1_MULTIMEM", "0") == "1" and self.params_buf.multicast_ptr != 0
+                          and self.grads_buf.multicast_ptr != 0)
 
     # ------------------------------------------------------------------------------------------
     def _supported(self, opt) -> bool:
@@ -247,10 +252,10 @@ class FusedZeRO1Comm:
             if b.adamw:
                 f = (ctypes.c_float * 8)(adamw.lr, adamw.betas[0], adamw.betas[1], adamw.eps, adamw.weight_decay, self._c1, self._c2, 0.0)
                 B.check(lib.cmb_zero1_adamw_ranges(gp, pp, fp, rank, W, B.ptr(b.adamw_tab), len(b.adamw), I64(b.adamw_elems), f, b.idx, epoch,
-                                                   I64(SPIN_LIMIT), status, cap, st), "zero1_adamw_ranges")
+                                                   I64(SPIN_LIMIT), status, cap, self.use_mc, st), "zero1_adamw_ranges")
             if b.muon:
                 B.check(lib.cmb_zero1_muon_reduce_ranges(gp, pp, fp, rank, W, B.ptr(b.muon_tab), len(b.muon), I64(b.muon_elems), F32(muon.momentum),
-                                                         F32(muon.weight_decay), int(muon.nesterov), b.idx, epoch, I64(SPIN_LIMIT), status, cap, st),
+                                                         F32(muon.weight_decay), int(muon.nesterov), b.idx, epoch, I64(SPIN_LIMIT), status, cap, self.use_mc, st),
                         "zero1_muon_reduce_ranges")
         b.launched = True
 
@@ -298,7 +303,7 @@ class FusedZeRO1Comm:
                             rows.append(dict(off=owner * flat.segment + off, n=cnt, u=self.res_of[i].data_ptr(),
                                              coef=max(1.0, p.shape[0] / p.shape[1]) ** 0.5))
                         ent = self.push_tabs[k_] = (_table(rows, dev), len(rows), sum(r["n"] for r in rows))
-                    B.check(lib.cmb_zero1_push_ranges(pp, rank, W, B.ptr(ent[0]), ent[1], I64(ent[2]), F32(lr), B.stream_ptr()), "zero1_push_ranges")
+                    B.check(lib.cmb_zero1_push_ranges(pp, rank, W, B.ptr(ent[0]), ent[1], I64(ent[2]), F32(lr), self.use_mc, B.stream_ptr()), "zero1_push_ranges")
             for s_ in streams:
                 main.wait_stream(s_)
             for k_, (n, p) in enumerate(self.slow_muon):   # too narrow for the tensor-core iteration (e.g. a 4-row gate): same maths in PyTorch ops

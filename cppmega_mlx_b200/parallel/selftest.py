@@ -48,6 +48,8 @@ def _train(comm: str, steps: int, dev, rank: int, world: int):
         dist.all_reduce(t)
         losses.append(float(t) / world)
     flat = torch.cat([p.detach().float().reshape(-1) for p in model.parameters()])
+    fused = getattr(opt, "_fused", None)
+    _train.multimem = bool(fused is not None and getattr(fused, "use_mc", 0))     # reported by the zero1 case
     return losses, flat
 
 
@@ -68,7 +70,8 @@ def case_zero1(rank, world, dev):
     dist.all_reduce(spread, op=dist.ReduceOp.MAX)
     if rank == 0:
         print(json.dumps({"case": "zero1", "world": world, "loss_nccl": l_n, "loss_fused": l_f,
-                          "max_param_diff": float(diff), "mean_param_diff": float(mean), "rank_spread": float(spread)}))
+                          "max_param_diff": float(diff), "mean_param_diff": float(mean), "rank_spread": float(spread),
+                          "multimem": _train.multimem}))
 
 
 def _optimizer_only(steps: int, dev, rank: int, world: int):
@@ -139,16 +142,18 @@ def case_zero1bw(rank, world, dev):
     I64, F32 = ctypes.c_longlong, ctypes.c_float
     f = (ctypes.c_float * 8)(1e-3, 0.9, 0.999, 1e-8, 0.01, 1.0, 1.0, 0.0)
     gp, pp = grads.peer_ptrs, params.peer_ptrs
+    # CPPMEGA_ZERO1_MULTIMEM=1: the multimem forms (in-switch reduction, multicast store), if the buffers have a multicast binding
+    mc = int(os.environ.get("CPPMEGA_ZERO1_MULTIMEM", "0") == "1" and grads.multicast_ptr != 0 and params.multicast_ptr != 0)
 
     def adamw():
-        B.check(lib.cmb_zero1_adamw_ranges(gp, pp, gp, rank, world, B.ptr(tab_a), 1, I64(n), f, -1, 0, I64(0), st, 0, B.stream_ptr()), "zero1_adamw_ranges")
+        B.check(lib.cmb_zero1_adamw_ranges(gp, pp, gp, rank, world, B.ptr(tab_a), 1, I64(n), f, -1, 0, I64(0), st, 0, mc, B.stream_ptr()), "zero1_adamw_ranges")
 
     def muon():
-        B.check(lib.cmb_zero1_muon_reduce_ranges(gp, pp, gp, rank, world, B.ptr(tab_m), 1, I64(n), F32(0.95), F32(0.0), 1, -1, 0, I64(0), st, 0,
+        B.check(lib.cmb_zero1_muon_reduce_ranges(gp, pp, gp, rank, world, B.ptr(tab_m), 1, I64(n), F32(0.95), F32(0.0), 1, -1, 0, I64(0), st, 0, mc,
                                                  B.stream_ptr()), "zero1_muon_reduce_ranges")
 
     def push():
-        B.check(lib.cmb_zero1_push_ranges(pp, rank, world, B.ptr(tab_p), 1, I64(n), F32(1e-3), B.stream_ptr()), "zero1_push_ranges")
+        B.check(lib.cmb_zero1_push_ranges(pp, rank, world, B.ptr(tab_p), 1, I64(n), F32(1e-3), mc, B.stream_ptr()), "zero1_push_ranges")
 
     def timed(fn):
         def step():
@@ -171,7 +176,8 @@ def case_zero1bw(rank, world, dev):
     torch.cuda.synchronize()
     B.check_status()
     if rank == 0:
-        print(json.dumps({"case": "zero1bw", "world": world, "owned_elems_per_rank": n, "barrier_ms": t_bar, **rows}))
+        print(json.dumps({"case": "zero1bw", "world": world, "owned_elems_per_rank": n, "multimem": bool(mc),
+                          "multicast_binding": grads.multicast_ptr != 0, "barrier_ms": t_bar, **rows}))
 
 
 def _time(fn, iters=10, warmup=3):

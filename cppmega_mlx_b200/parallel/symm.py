@@ -3,7 +3,8 @@ kernel can load from / store to any rank's copy over NVLink.  Allocation and han
 ``torch.distributed._symmetric_memory`` (CUDA VMM + fabric/IPC handles under the hood); everything that
 *touches* the memory is our own kernels in ``csrc/comm.cu``.
 
-``SymmetricBuffer.peer_ptrs`` is a ctypes ``long long[W]`` of device addresses (index = rank).
+``SymmetricBuffer.peer_ptrs`` is a ctypes ``long long[W + 1]``: the W device addresses (index = rank) and the buffer's
+multicast address (0 if none).
 ``EpochBarrier`` is the flag barrier those kernels are bracketed with: a monotonically increasing epoch per
 barrier object (flags are never reset, so there is no ABA window), bounded polling on the device, status word
 on expiry.
@@ -35,8 +36,13 @@ class SymmetricBuffer:
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         if len(ptrs) != self.world:
             raise RuntimeError("symmetric memory rendezvous returned an unexpected number of peers")
+        if ptrs[self.rank] != self.tensor.data_ptr():
+            raise RuntimeError("symmetric memory: this rank's mapped address is not the tensor's address")
         self.ptr_list = ptrs
-        self.peer_ptrs = (ctypes.c_longlong * self.world)(*ptrs)
+        # NVSwitch multicast address of the buffer (one access reaches every rank's copy; 0 when the allocation has no multicast
+        # binding).  It rides behind the W peer addresses: kernels that take a `use_mc` flag read it from slot W.
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.peer_ptrs = (ctypes.c_longlong * (self.world + 1))(*ptrs, self.multicast_ptr)
         self.tensor.zero_()
 
 

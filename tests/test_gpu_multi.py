@@ -50,6 +50,18 @@ def test_fused_zero1_matches_nccl_zero1_two_gpus():
     assert all(abs(a - b) < 5e-2 for a, b in zip(out["loss_fused"], out["loss_nccl"])), out
 
 
+def test_fused_zero1_multimem_form_matches_nccl_two_gpus():
+    """The same step with the gradients reduced in the switch (multimem.ld_reduce) and the parameters pushed by one multicast
+    store (multimem.st).  Skipped where the symmetric buffers have no multicast binding."""
+    out = _selftest("zero1", extra_env={"CPPMEGA_ZERO1_MULTIMEM": "1"})
+    if not out["multimem"]:
+        pytest.skip("symmetric memory has no multicast binding on this machine")
+    assert out["max_param_diff"] < 5e-2, out
+    assert out["mean_param_diff"] < 2e-3, out
+    assert out["rank_spread"] == 0.0, out
+    assert all(abs(a - b) < 5e-2 for a, b in zip(out["loss_fused"], out["loss_nccl"])), out
+
+
 def test_fused_zero1_is_bitwise_deterministic_two_gpus():
     out = _selftest("zero1det")
     assert out["bitwise_equal"] and out["finite"], out
