@@ -50,6 +50,7 @@ enum : int {
   GEMM_EPI_AXPBY = 1024,         // scale · acc + scale2 · aux        (aux has C's layout, bf16)
   GEMM_EPI_AMAX = 4096,          // max |C| over the written elements (NaNs ignored) is folded into *amax with an integer atomicMax:
                                  // the per-tensor FP8 scale of the product without a reduction pass over it
+  GEMM_EPI_RELU2 = 8192,         // max(acc, 0)²: the squared-ReLU activation of an up projection without a pass over its output
   GEMM_EPI_SYM_MIRROR = 2048,    // with CAUSAL_SKIP on a symmetric product (bf16 C): every element whose transposed position lies
                                  // in a skipped tile is also stored there, so the full matrix exists after one launch
 };
@@ -390,6 +391,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool e_axpby = (p.flags & GEMM_EPI_AXPBY) != 0;
     const bool e_mirror = (p.flags & GEMM_EPI_SYM_MIRROR) != 0 && !out_f32;
     const bool e_amax = (p.flags & GEMM_EPI_AMAX) != 0 && p.amax != nullptr;
+    const bool e_relu2 = (p.flags & GEMM_EPI_RELU2) != 0;
     uint8_t* cbox = csmem + ew * GEMM_CBOX_BYTES;
     int local = 0;
     const uint32_t lead_tempty = PAIR ? mapa_u32(smem_u32(&tempty_bar[0]), 0) : 0u;
@@ -541,6 +543,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (rowexp) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rv);
+        }
+        if (e_relu2) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float v = fmaxf(__uint_as_float(r[j]), 0.f);
+            r[j] = __float_as_uint(v * v);
+          }
         }
         if (e_mirror && row < p.M && (row / BN) * BN >= (col0 / TILE_M) * TILE_M + TILE_M) {
           // (col, row) lies in a tile the causal skip left out (its tile would start at column (row / BN)·BN ≥ its first row +

@@ -111,6 +111,8 @@ class FeedForward(nn.Module):
             h = ops.swiglu(self.gate_up_proj(x))
         elif self.activation == "gelu":
             h = F.gelu(self.up_proj(x))
+        elif type(self.up_proj) is Linear and self.up_proj.bias is None:
+            h = ops.linear_relu2(x, self.up_proj.weight)        # squared ReLU in the GEMM epilogue on the GPU
         else:
             h = ops.squared_relu(self.up_proj(x))
         if self._redo_probe is not None:

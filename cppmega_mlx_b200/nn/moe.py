@@ -230,7 +230,7 @@ class MoE(nn.Module):
         mine = torch.div(e, Le, rounding_mode="floor") == self.tp_rank
         local_e = torch.where(mine, e - self.tp_rank * Le, torch.full_like(e, Le))        # foreign → sentinel group Le (sorted last)
         w = copy_to_tp(top_w.reshape(-1), self.tp_group) * mine.to(top_w.dtype)   # the router sees only this rank's share of d(out)/d(w)
-        if ops.kernels_enabled() and GG.supported(flat, self.experts.w_gate_up) and self.config.activation == "swiglu":
+        if ops.kernels_enabled() and GG.supported(flat, self.experts.w_gate_up):
             L = GG.build_layout(local_e, Le + 1)
             L.num_experts = Le
             L.k_ranges = L.k_ranges[:Le].contiguous()
@@ -266,7 +266,7 @@ class MoE(nn.Module):
         E = self.config.num_experts
         flat_e = top_idx.reshape(-1)
         from ..ops import grouped_gemm_cuda as GG
-        if ops.kernels_enabled() and GG.supported(flat, self.experts.w_gate_up) and self.config.activation == "swiglu":
+        if ops.kernels_enabled() and GG.supported(flat, self.experts.w_gate_up):
             # GPU path: padded expert-sorted buffer + grouped tcgen05 GEMMs; nothing here synchronises with the host.
             L = GG.build_layout(flat_e, E)
             tok = torch.div(L.order, k, rounding_mode="floor")
@@ -285,8 +285,16 @@ class MoE(nn.Module):
         return out
 
     def expert_ffn_padded(self, xp: torch.Tensor, layout) -> torch.Tensor:
-        """gate|up → SwiGLU → down over a padded expert-sorted buffer, in bf16 or (forward only) block-scaled MXFP8."""
+        """up projection → activation → down over a padded expert-sorted buffer, in bf16 or (SwiGLU, forward only) block-scaled
+        MXFP8.  Squared ReLU runs in the up product's epilogue; GELU is one element-wise pass (all three map 0 to 0, so the
+        padding rows stay zero)."""
         from ..ops import grouped_gemm_cuda as GG
+        act = self.config.activation
+        if act == "relu2":
+            return GG.grouped_linear_padded(GG.grouped_linear_padded(xp, self.experts.w_gate_up, layout, act="relu2"), self.experts.w_down, layout)
+        if act == "gelu":
+            return GG.grouped_linear_padded(F.gelu(GG.grouped_linear_padded(xp, self.experts.w_gate_up, layout), approximate="tanh"),
+                                            self.experts.w_down, layout)
         if self.config.expert_gemm == "mxfp8":
             from ..ops import mxfp8 as MX
             if MX.grouped_mxfp8_supported(xp, self.experts.w_gate_up) and self.experts.w_down.shape[2] % 128 == 0:
@@ -299,7 +307,7 @@ class MoE(nn.Module):
     def local_expert_forward(self, xs: torch.Tensor, local_e: torch.Tensor) -> torch.Tensor:
         """Rows ``xs`` sorted by local expert id ``local_e`` → expert outputs in the same order (expert-parallel ranks)."""
         from ..ops import grouped_gemm_cuda as GG
-        if ops.kernels_enabled() and GG.supported(xs, self.experts.w_gate_up) and self.config.activation == "swiglu" and xs.shape[0] > 0:
+        if ops.kernels_enabled() and GG.supported(xs, self.experts.w_gate_up) and xs.shape[0] > 0:
             L = GG.build_layout(local_e, self.local_experts)          # rows are already sorted: order is the identity
             xp = GG.scatter_to_padded(xs, L.order, L)
             return self.expert_ffn_padded(xp, L).index_select(0, L.slot)

@@ -4,7 +4,7 @@ from .activations import squared_relu, swiglu, swiglu_reference
 from .conv import causal_conv1d_silu, packed_split_conv_silu
 from .attention import masked_attention, masked_attention_reference
 from .cce import linear_cross_entropy, linear_cross_entropy_reference
-from .gemm import gemm_batched, gemm_raw, linear, matmul_nt
+from .gemm import gemm_batched, gemm_raw, linear, linear_relu2, matmul_nt
 from .m2rnn_post import m2rnn_post_gate, m2rnn_post_gate_reference
 from .m2rnn_scan import broadcast_m2rnn_heads, m2rnn_scan, m2rnn_scan_reference
 from .mamba3_scan import mamba3_scan, mamba3_scan_chunked, mamba3_scan_sequential

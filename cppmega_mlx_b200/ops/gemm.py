@@ -77,6 +77,7 @@ EPI_EXP_MASK = 256
 EPI_DS = 512
 EPI_AXPBY = 1024
 EPI_AMAX = 4096         # max |C| of the written elements is folded into a device scalar from the epilogue (per-tensor FP8 scale without a pass over C)
+EPI_RELU2 = 8192        # max(acc, 0)²
 EPI_SYM_MIRROR = 2048   # with CAUSAL_SKIP on a symmetric product: the skipped tiles are filled from the computed ones in the same launch
 
 
@@ -269,3 +270,38 @@ def gemm_axpby(a, b, aux, *, a_mn=False, b_mn=False, alpha: float = 1.0, beta: f
     return gemm_batched(a, b, out, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, lda=a.stride(0), ldb=b.stride(0), ldc=out.stride(0),
                         nb=(1, 1, 1), sA=(0, 0, 0), sB=(0, 0, 0), sC=(0, 0, 0), flags=EPI_AXPBY, aux=aux, scale=alpha,
                         scale2=beta)
+
+
+class _LinearRelu2Fn(torch.autograd.Function):
+    """y = relu(x·Wᵀ)² with the activation in the GEMM epilogue.  The pre-activation is never stored: relu(z) = sqrt(y), so the
+    backward scales the incoming gradient by 2·sqrt(y) and runs the usual data / weight gradient products."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        x2 = x.reshape(-1, x.shape[-1])
+        M, K = x2.shape
+        N = w.shape[0]
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+        gemm_batched(x2, w, y, M=M, N=N, K=K, a_mn=False, b_mn=False, lda=x2.stride(0), ldb=w.stride(0), ldc=N, nb=(1, 1, 1),
+                     sA=(0, 0, 0), sB=(0, 0, 0), sC=(0, 0, 0), flags=EPI_RELU2)
+        ctx.save_for_backward(x2, w, y)
+        ctx.shape = x.shape
+        return y.view(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, w, y = ctx.saved_tensors
+        gz = (gy.reshape(y.shape).float() * (2.0 * y.float().sqrt())).to(torch.bfloat16)
+        gx = gemm_raw(gz, w, b_mn=True).view(ctx.shape) if ctx.needs_input_grad[0] else None      # gz · W
+        gw = gemm_raw(gz, x2, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None          # gzᵀ · x
+        return gx, gw
+
+
+def linear_relu2(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``relu(x @ w.T) ** 2`` (the squared-ReLU up projection, ``cppmega_mlx/kernels/metal_ops.py:175-217`` for the
+    activation); one tcgen05 launch on the GPU, PyTorch ops elsewhere."""
+    x2 = x.reshape(-1, x.shape[-1]) if x.dim() != 2 else x
+    if (_kernel_ok(x, w) and x2.is_contiguous() and _ok(x2) and _ok(w) and w.is_contiguous() and x2.shape[0] > 0 and w.shape[0] % 8 == 0):
+        return _LinearRelu2Fn.apply(x, w)
+    r = torch.relu(torch.nn.functional.linear(x, w))
+    return r * r

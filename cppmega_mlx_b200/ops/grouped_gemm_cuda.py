@@ -66,14 +66,15 @@ def supported(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.shape[-1] % 8 == 0 and w.shape[1] % 8 == 0 and w.shape[2] == x.shape[-1])
 
 
-def _fwd(x, w, L: GroupedLayout, b_mn: bool):
-    """b_mn False: Y[rows,out] = X·W[e]ᵀ (W [E,out,in]).  b_mn True: Y[rows,in] = X·W[e] (X has `out` columns)."""
+def _fwd(x, w, L: GroupedLayout, b_mn: bool, flags: int = 0):
+    """b_mn False: Y[rows,out] = X·W[e]ᵀ (W [E,out,in]).  b_mn True: Y[rows,in] = X·W[e] (X has `out` columns).
+    ``flags``: an element-wise epilogue of the GEMM (``gemm.EPI_RELU2``)."""
     E, out_f, in_f = w.shape
     N = in_f if b_mn else out_f
     K = out_f if b_mn else in_f
     y = torch.empty(L.rows, N, dtype=torch.bfloat16, device=x.device)
     G.gemm_batched(x, w, y, M=L.rows, N=N, K=K, a_mn=False, b_mn=b_mn, lda=x.stride(0), ldb=in_f, ldc=N, nb=(1, 1, 1),
-                   sA=(0, 0, 0), sB=(out_f * in_f, 0, 0), sC=(0, 0, 0), tile_group=L.tile_group, b_groups=E, m_limit=L.used_rows)
+                   sA=(0, 0, 0), sB=(out_f * in_f, 0, 0), sC=(0, 0, 0), tile_group=L.tile_group, b_groups=E, m_limit=L.used_rows, flags=flags)
     return y
 
 
@@ -87,24 +88,40 @@ def _wgrad(gy, x, L: GroupedLayout, shape):
 
 class _GroupedLinearPadded(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, L):
-        ctx.save_for_backward(x, w)
-        ctx.L = L
-        return _fwd(x, w, L, False)
+    def forward(ctx, x, w, L, act):
+        ctx.L, ctx.act = L, act
+        y = _fwd(x, w, L, False, G.EPI_RELU2 if act == "relu2" else 0)
+        if act == "relu2":
+            ctx.save_for_backward(x, w, y)      # relu(z) = sqrt(y): the pre-activation is not kept
+        else:
+            ctx.save_for_backward(x, w)
+        return y
 
     @staticmethod
     def backward(ctx, gy):
-        x, w = ctx.saved_tensors
         L = ctx.L
-        gy = gy.contiguous()
+        if ctx.act == "relu2":
+            x, w, y = ctx.saved_tensors
+            rows = int(y.shape[0])
+            # rows beyond the used part of the buffer were never written by the forward product
+            gz = gy.float() * (2.0 * y.float().sqrt())
+            if L.used_rows is not None:
+                gz = torch.where(torch.arange(rows, device=y.device)[:, None] < L.used_rows, gz, 0.0)
+            gy = gz.to(torch.bfloat16)
+        else:
+            x, w = ctx.saved_tensors
+            gy = gy.contiguous()
         gx = _fwd(gy, w, L, True) if ctx.needs_input_grad[0] else None
         gw = _wgrad(gy, x, L, w.shape) if ctx.needs_input_grad[1] else None
-        return gx, gw, None
+        return gx, gw, None, None
 
 
-def grouped_linear_padded(x: torch.Tensor, w: torch.Tensor, layout: GroupedLayout) -> torch.Tensor:
-    """x [layout.rows, in] (padding rows zero) × w [E, out, in] → [layout.rows, out]; differentiable."""
-    return _GroupedLinearPadded.apply(x.contiguous(), w, layout)
+def grouped_linear_padded(x: torch.Tensor, w: torch.Tensor, layout: GroupedLayout, act: str | None = None) -> torch.Tensor:
+    """x [layout.rows, in] (padding rows zero) × w [E, out, in] → [layout.rows, out]; differentiable.  ``act="relu2"`` applies
+    relu(·)² in the GEMM epilogue."""
+    if act not in (None, "relu2"):
+        raise ValueError(f"unsupported fused activation {act!r}")
+    return _GroupedLinearPadded.apply(x.contiguous(), w, layout, act)
 
 
 def scatter_to_padded(flat: torch.Tensor, tok: torch.Tensor, layout: GroupedLayout) -> torch.Tensor:

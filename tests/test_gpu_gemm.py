@@ -208,3 +208,54 @@ def test_symmetric_product_with_mirror_in_cta_pair_form(m, k, batch):
     assert not bool(torch.isnan(outs[True]).any())
     assert (outs[True].float() - ref).abs().max().item() < 2e-2 * (k ** 0.5) + 1e-2 * ref.abs().max().item()
     assert torch.equal(outs[True], outs[False])
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 384, 256), (130, 136, 64), (4096, 2048, 1024)])
+def test_linear_relu2_epilogue_matches_fp32(M, N, K):
+    """relu(x·Wᵀ)² from the GEMM epilogue, forward and both gradients, against fp32 PyTorch ops."""
+    from cppmega_mlx_b200 import ops
+    torch.manual_seed(M + N)
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(N, K, device="cuda") * 0.1).bfloat16().requires_grad_()
+    y = ops.linear_relu2(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = torch.relu(xr @ wr.t()) ** 2
+    yr.backward(g.float())
+    close = lambda a, b, r: (a.float() - b).abs().max().item() <= r * (b.abs().max().item() + 1e-6)
+    assert close(y, yr, 2e-2)
+    assert close(x.grad, xr.grad, 3e-2)
+    assert close(w.grad, wr.grad, 3e-2)
+
+
+@pytest.mark.parametrize("act", ["relu2", "gelu"])
+def test_moe_experts_with_non_gated_activations_use_the_grouped_kernels(act):
+    """relu2 / gelu experts run the padded grouped GEMMs (relu2 fused into the up product's epilogue) and match the per-expert
+    PyTorch loop of the same bf16 module, outputs and gradients."""
+    from cppmega_mlx_b200.nn.moe import MoE, MoEConfig
+    from cppmega_mlx_b200.ops import _backend as B
+    torch.manual_seed(0)
+    cfg = MoEConfig(d_model=128, num_experts=8, top_k=2, expert_hidden_size=256, activation=act, shared_expert_hidden_size=None)
+    moe = MoE(cfg).cuda().bfloat16()
+    x0 = (torch.randn(4, 96, 128, device="cuda") * 0.5).bfloat16()
+
+    def run(kernels: bool):
+        moe.zero_grad()
+        x = x0.clone().requires_grad_()
+        with B.use_kernels(kernels):
+            before = B.launch_count()
+            y = moe(x)
+            y = y[0] if isinstance(y, tuple) else y
+            launches = B.launch_count() - before
+            y.float().square().mean().backward()
+        return y.detach().float(), x.grad.float(), moe.experts.w_gate_up.grad.float().clone(), moe.experts.w_down.grad.float().clone(), launches
+    yk, gxk, gu_k, gd_k, n_k = run(True)
+    yr, gxr, gu_r, gd_r, _ = run(False)
+    B.check_status()
+    assert n_k > 0
+    close = lambda a, b, r: (a - b).abs().max().item() <= r * (b.abs().max().item() + 1e-9)
+    assert close(yk, yr, 3e-2)
+    assert close(gxk, gxr, 6e-2)
+    assert close(gu_k, gu_r, 6e-2)
+    assert close(gd_k, gd_r, 6e-2)
