@@ -32,6 +32,37 @@ class ManifoldBranchMixerConfig:
             raise ValueError("blend_alpha must be non-negative")
 
 
+class _SinkhornFn(torch.autograd.Function):
+    """``csrc/sinkhorn.cu``: one thread per matrix, the whole iteration (and its reverse) in one launch."""
+
+    @staticmethod
+    def forward(ctx, raw, iters, epsilon):
+        import ctypes
+        from ..ops import _backend as B
+        raw = raw.float().contiguous()
+        out = torch.empty_like(raw)
+        B.check(B.load_library().cmb_sinkhorn_fwd(B.ptr(raw), B.ptr(out), ctypes.c_longlong(raw.shape[0]), raw.shape[-1], int(iters),
+                                                  ctypes.c_float(epsilon), B.stream_ptr()), "sinkhorn_fwd")
+        ctx.save_for_backward(raw)
+        ctx.meta = (int(iters), float(epsilon))
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        import ctypes
+        from ..ops import _backend as B
+        (raw,) = ctx.saved_tensors
+        iters, epsilon = ctx.meta
+        g = g.float().contiguous()
+        graw = torch.empty_like(raw)
+        B.check(B.load_library().cmb_sinkhorn_bwd(B.ptr(raw), B.ptr(g), B.ptr(graw), ctypes.c_longlong(raw.shape[0]), raw.shape[-1], iters,
+                                                  ctypes.c_float(epsilon), B.stream_ptr()), "sinkhorn_bwd")
+        return graw, None, None
+
+
+SINKHORN_KERNEL_MAX_N, SINKHORN_KERNEL_MAX_ITERS = 8, 16
+
+
 def sinkhorn_normalize(raw_matrix: torch.Tensor, *, iters: int = 5, epsilon: float = 1e-6) -> torch.Tensor:
     if raw_matrix.dim() != 3 or raw_matrix.shape[-1] != raw_matrix.shape[-2]:
         raise ValueError("raw_matrix must be a batch of square matrices")
@@ -39,6 +70,10 @@ def sinkhorn_normalize(raw_matrix: torch.Tensor, *, iters: int = 5, epsilon: flo
         raise TypeError("raw_matrix must use a floating dtype")
     if iters < 0 or epsilon <= 0:
         raise ValueError("iters must be >= 0 and epsilon > 0")
+    from ..ops import _backend as B
+    if (B.on_gpu(raw_matrix) and 2 <= raw_matrix.shape[-1] <= SINKHORN_KERNEL_MAX_N and iters <= SINKHORN_KERNEL_MAX_ITERS
+            and raw_matrix.shape[0] > 0):
+        return _SinkhornFn.apply(raw_matrix, int(iters), float(epsilon))
     t = torch.softmax(raw_matrix.float(), dim=-2)
     for _ in range(int(iters)):
         t = t / t.sum(-1, keepdim=True).clamp(min=epsilon)

@@ -248,3 +248,22 @@ def test_sparse_mla_gather_form_forward_matches_reference(Bn, S, Skv, H, topk):
     # with a gradient requested the differentiable masked form is taken instead
     assert not SM.gather_forward_supported(q.requires_grad_(), kv, idx, dv)
     B.check_status()
+
+
+@pytest.mark.parametrize("n,iters,batch", [(3, 5, 4), (4, 5, 37), (8, 16, 300), (2, 0, 5)])
+def test_sinkhorn_kernel_matches_pytorch_ops(n, iters, batch):
+    """Forward and backward of the one-launch Sinkhorn kernel against the element-wise PyTorch iteration in fp32."""
+    from cppmega_mlx_b200.nn.mhc import sinkhorn_normalize
+    from cppmega_mlx_b200.ops import _backend as B
+    torch.manual_seed(n * 100 + iters)
+    raw = (torch.randn(batch, n, n, device="cuda") * 2.0).requires_grad_()
+    g = torch.randn(batch, n, n, device="cuda")
+    out = sinkhorn_normalize(raw, iters=iters)
+    out.backward(g)
+    ref_in = raw.detach().clone().requires_grad_()
+    with B.use_kernels(False):
+        ref = sinkhorn_normalize(ref_in, iters=iters)
+        ref.backward(g)
+    B.check_status()
+    assert (out - ref).abs().max().item() < 1e-5
+    assert (raw.grad - ref_in.grad).abs().max().item() < 1e-4 * (1.0 + ref_in.grad.abs().max().item())
