@@ -17,7 +17,7 @@ __global__ void __launch_bounds__(THREADS) cce_rows_kernel(__nv_bfloat16* __rest
                                                             const int* __restrict__ targets,
                                                             const uint8_t* __restrict__ valid,
                                                             float* __restrict__ loss_rows, int64_t rows, int V,
-                                                            const float* __restrict__ scale_ptr, int write_grad) {
+                                                            const float* __restrict__ scale_ptr, int write_grad, int* status) {
   __shared__ float red_m[THREADS / 32];
   __shared__ float red_s[THREADS / 32];
   __shared__ float bcast[2];
@@ -68,9 +68,20 @@ __global__ void __launch_bounds__(THREADS) cce_rows_kernel(__nv_bfloat16* __rest
         M = nm;
       }
       const float lse = M + __logf(S);
-      const int t = targets[row];
+      int t = targets[row];
+      bool in_range = t >= 0 && t < V;
+      if (!in_range && valid[row]) {
+        // a target outside the vocabulary: the row contributes nothing, nothing is read at that index, and the first such row
+        // is reported through the status block (code, row, target, vocabulary size)
+        if (status != nullptr && atomicCAS(status, 0, ST_BAD_ARGUMENT) == 0) {
+          status[1] = static_cast<int>(row);
+          status[2] = t;
+          status[3] = V;
+        }
+      }
+      if (!in_range) t = 0;
       const float tl = __bfloat162float(lr[t]);
-      const float ok = valid[row] ? 1.f : 0.f;
+      const float ok = (valid[row] && in_range) ? 1.f : 0.f;
       loss_rows[row] = ok * (lse - tl);
       bcast[0] = lse;
       bcast[1] = ok * scale;
@@ -102,11 +113,11 @@ __global__ void __launch_bounds__(THREADS) cce_rows_kernel(__nv_bfloat16* __rest
 // scale_ptr: device scalar (1 / number of valid targets), so the caller never syncs to learn the count.
 // logits: bf16 [rows, V] (V % 8 == 0, rows contiguous), overwritten with dlogits when write_grad != 0.
 extern "C" int cmb_cce_rows(void* logits, const int* targets, const uint8_t* valid, float* loss_rows, int64_t rows,
-                            int V, const float* scale_ptr, int write_grad, void* stream) {
+                            int V, const float* scale_ptr, int write_grad, int* status, void* stream) {
   if (V % 8) return 1;
   if (rows <= 0) return 0;
   const int grid = static_cast<int>(rows < 148 * 8 ? rows : 148 * 8);
   cmb::cce_rows_kernel<512><<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__nv_bfloat16*>(logits), targets, valid, loss_rows, rows, V, scale_ptr, write_grad);
+      static_cast<__nv_bfloat16*>(logits), targets, valid, loss_rows, rows, V, scale_ptr, write_grad, status);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }

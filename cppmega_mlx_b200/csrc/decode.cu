@@ -38,6 +38,7 @@ struct DecodeParams {
   long long v_page, v_row, v_batch, v_head;
   const int* table;              // [B, table_w] page ids, or nullptr for a contiguous cache
   int table_w, page_size;
+  int n_pages;                   // pages in the pool (0 = unknown): page ids from the table are checked against it
   const int* lengths;            // [B]
   const int* topk;               // [B, topk_n] key positions (−1 = unused) or nullptr
   int topk_n;
@@ -244,6 +245,18 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
 #pragma unroll
       for (int it = 0; it < RPL; ++it)
         page[it] = (p.table != nullptr && pos[it] >= 0) ? __ldg(p.table + static_cast<long long>(b) * p.table_w + pos[it] / p.page_size) : 0;
+#pragma unroll
+      for (int it = 0; it < RPL; ++it) {
+        // a page id outside the pool: the row is dropped like a key past the sequence, and the first one is reported
+        if (p.n_pages > 0 && pos[it] >= 0 && (page[it] < 0 || page[it] >= p.n_pages)) {
+          if (p.status != nullptr && atomicCAS(p.status, 0, ST_BAD_ARGUMENT) == 0) {
+            p.status[1] = b;
+            p.status[2] = page[it];
+            p.status[3] = p.n_pages;
+          }
+          pos[it] = -1;
+        }
+      }
       if (lane == 0) trace_mark(p, t, 0);
       // Phase 2: the copies, once the buffer has been released (the index reads above overlap that wait).
       if (!mbar_wait(&empty_bar[buf], ((t >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
@@ -563,6 +576,7 @@ extern "C" int cmb_paged_decode(const void* q, const void* k, const void* v, con
   p.B = ip[0], p.H = ip[1], p.kv_heads = ip[2];
   const int Dk = ip[3], Dv = ip[4], shared = ip[5];
   p.table_w = ip[6], p.page_size = ip[7] > 0 ? ip[7] : 1, p.topk_n = ip[8], p.splits = ip[9];
+  p.n_pages = table != nullptr ? ip[11] : 0;
   p.q_sb = lp[0], p.q_sh = lp[1];
   p.k_page = lp[2], p.k_row = lp[3], p.k_batch = lp[4], p.k_head = lp[5];
   p.v_page = lp[6], p.v_row = lp[7], p.v_batch = lp[8], p.v_head = lp[9];

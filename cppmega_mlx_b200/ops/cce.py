@@ -44,7 +44,7 @@ def _chunk_loss_and_grads(h, w, t, valid, scale, want_grads, use_kernel):
         loss_rows = torch.empty(rows, dtype=torch.float32, device=h.device)
         B.check(lib.cmb_cce_rows(B.ptr(logits), B.ptr(t), B.ptr(valid), B.ptr(loss_rows), ctypes.c_int64(rows),
                                  ctypes.c_int(V), B.ptr(scale), ctypes.c_int(1 if want_grads else 0),
-                                 B.stream_ptr()), "cce_rows")
+                                 B.ptr(B.status_buffer(h.device)), B.stream_ptr()), "cce_rows")
         return loss_rows.sum(), logits  # logits now hold scale*(softmax-onehot) when want_grads
     logits = (h @ w.t()).float()
     lse = torch.logsumexp(logits, dim=-1)

@@ -70,3 +70,28 @@ def test_ep_dispatch_skips_slots_outside_the_receive_buffer_and_reports_them():
     assert bool((out[1] == 0).all()) and bool((out[3] == 0).all())
     assert status.tolist()[0] == 6 and status.tolist()[2] == 9
     assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0                           # the context is alive
+
+
+def test_cross_entropy_target_outside_the_vocabulary_is_skipped_and_reported():
+    """A target id ≥ V (or negative) in a valid row: nothing is read at that index, the row contributes no loss and no gradient, and
+    the status block names (code, row, target, V).  The other rows are unaffected."""
+    from cppmega_mlx_b200 import ops
+    from cppmega_mlx_b200.ops import _backend as B
+    torch.manual_seed(0)
+    V, D, rows = 512, 64, 40
+    h = (torch.randn(rows, D, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(V, D, device="cuda") * 0.1).bfloat16().requires_grad_()
+    t = torch.randint(0, V, (rows,), device="cuda")
+    bad = t.clone()
+    bad[7] = V + 123
+    B.check_status()
+    loss_bad = ops.linear_cross_entropy(h, w, bad)
+    loss_bad.backward()
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="status words") as e:
+        B.check_status()
+    assert f"[6, 7, {V + 123}, {V}" in str(e.value)           # ST_BAD_ARGUMENT, row 7, the target, the vocabulary size
+    assert bool(torch.isfinite(loss_bad)) and bool(torch.isfinite(h.grad).all())
+    assert float(h.grad[7].abs().max()) == 0.0                 # the bad row has no gradient
+    B.check_status()                                           # reading the status cleared it
+    assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
