@@ -151,11 +151,15 @@ __global__ void __launch_bounds__(THREADS) rmsnorm_bwd_kernel(const __nv_bfloat1
 // Warp-per-row variants for rows of up to VPL·256 columns: the whole row stays in registers (VPL 16-byte vectors per
 // lane), so a row costs one pass over memory, one warp reduction and no block barrier, and every lane has VPL independent
 // loads in flight.  Four warps (rows) per CTA, grid-stride over rows.
+// With `delta` the row normalised is bf16(x + delta), which is also written to `sum` (the residual add that precedes the norm,
+// same arithmetic as an element-wise add followed by the norm).
 template <int VPL>
 __global__ void __launch_bounds__(128) rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x,
                                                                 const __nv_bfloat16* __restrict__ w,
                                                                 __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
-                                                                int64_t rows, int cols, float eps) {
+                                                                int64_t rows, int cols, float eps,
+                                                                const __nv_bfloat16* __restrict__ delta = nullptr,
+                                                                __nv_bfloat16* __restrict__ sum = nullptr) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = cols >> 3;
   for (int64_t row = blockIdx.x * 4 + warp; row < rows; row += static_cast<int64_t>(gridDim.x) * 4) {
@@ -167,6 +171,13 @@ __global__ void __launch_bounds__(128) rmsnorm_fwd_warp_kernel(const __nv_bfloat
       const int v = lane + 32 * a;
       if (v < nvec) {
         load8(xr + 8 * v, f[a]);
+        if (delta != nullptr) {
+          float d[8];
+          load8(delta + row * cols + 8 * v, d);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[a][i] = __bfloat162float(__float2bfloat16(f[a][i] + d[i]));
+          store8(sum + row * cols + 8 * v, f[a]);
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss += f[a][i] * f[a][i];
       }
@@ -256,7 +267,10 @@ __global__ void __launch_bounds__(128, 4) rmsnorm_bwd_warp_kernel(const __nv_bfl
                                                                    const __nv_bfloat16* __restrict__ x,
                                                                    const __nv_bfloat16* __restrict__ w,
                                                                    const float* __restrict__ rstd, __nv_bfloat16* __restrict__ gx,
-                                                                   float* __restrict__ gw_part, int64_t rows, int cols) {
+                                                                   float* __restrict__ gw_part, int64_t rows, int cols,
+                                                                   const __nv_bfloat16* __restrict__ gres = nullptr) {
+  // gres: gradient that reaches the normalised tensor along another path (the residual stream); it is added to gx here
+  // instead of in a separate element-wise pass.
   extern __shared__ __align__(16) float gws[];   // [4][cols] per-warp dw partials, then the weight as bf16 [cols]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = cols >> 3;
@@ -310,6 +324,12 @@ __global__ void __launch_bounds__(128, 4) rmsnorm_bwd_warp_kernel(const __nv_bfl
         acc[1] = a1;
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = fg[i] * fw[i] * r - fx[i] * c;
+        if (gres != nullptr) {
+          float fr[8];
+          unpack8(*reinterpret_cast<const uint4*>(gres + row * cols + 8 * v), fr);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += fr[i];
+        }
         store8(gxr + 8 * v, o);
       }
     }
@@ -400,6 +420,31 @@ extern "C" int cmb_rmsnorm_fwd(const void* x, const void* w, void* y, void* rstd
   cmb::rmsnorm_fwd_kernel<256><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
       static_cast<float*>(rstd), rows, cols, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// Training form of the fused residual add + norm: sum = bf16(h + delta), y = rmsnorm(sum)·w, rstd kept for the backward.
+// cols a multiple of 8 and at most 2048.
+extern "C" int cmb_add_rmsnorm_train(const void* h, const void* delta, const void* w, void* sum, void* y, void* rstd, int64_t rows, int cols,
+                                     float eps, void* stream) {
+  if (cols % 8 || cols > 2048 || rows <= 0) return 1;
+  const int64_t want = (rows + 3) / 4;
+  const int wgrid = static_cast<int>(want < 148 * 16 ? want : 148 * 16);
+  cmb::rmsnorm_fwd_warp_kernel<8><<<wgrid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), static_cast<float*>(rstd), rows,
+      cols, eps, static_cast<const __nv_bfloat16*>(delta), static_cast<__nv_bfloat16*>(sum));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// gx = rmsnorm backward of gy + gres (the gradient arriving on the residual stream); same contract as cmb_rmsnorm_bwd otherwise.
+// cols at most 2048, rows at least 4.
+extern "C" int cmb_rmsnorm_bwd_add(const void* gy, const void* x, const void* w, const void* rstd, const void* gres, void* gx, void* gw_part,
+                                   int64_t rows, int cols, int nblk, void* stream) {
+  if (cols % 8 || cols > 2048 || rows < 4) return 1;
+  cmb::rmsnorm_bwd_warp_kernel<8><<<nblk, 128, cmb::rmsnorm_bwd_warp_smem(cols), static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+      static_cast<const float*>(rstd), static_cast<__nv_bfloat16*>(gx), static_cast<float*>(gw_part), rows, cols,
+      static_cast<const __nv_bfloat16*>(gres));
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

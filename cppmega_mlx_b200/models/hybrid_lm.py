@@ -368,15 +368,15 @@ class HybridTinyBlock(nn.Module):
                 layer_idx: int = 0, pending=None, defer: bool = False):
         """``pending`` is a residual contribution the caller has not added to ``h`` yet (the previous block's FFN output); it
         is added inside the kernel that also computes this block's norm.  With ``defer`` the block returns
-        ``(h, own pending contribution or None)`` instead of the finished stream — the no-gradient decode path uses both so
-        that every residual add of the stack rides on the following norm's launch."""
+        ``(h, own pending contribution or None)`` instead of the finished stream, so that every residual add of the stack rides
+        on the following norm's launch (and, in training, its gradient on that norm's backward launch)."""
         if pending is not None:
             h, normed = ops.add_rms_norm(h, pending, self.norm.weight, self.norm.eps)
         else:
             normed = self.norm(h)
         delta = self.route_delta(normed, mask, document_ids=document_ids, kv_cache=kv_cache,
                                  attention_layer_idx=attention_layer_idx, state=state, layer_idx=layer_idx)
-        if self.mhc is None and self.ffn is not None and not torch.is_grad_enabled():
+        if self.mhc is None and self.ffn is not None:
             updated, normed2 = ops.add_rms_norm(h, delta, self.ffn_norm.weight, self.ffn_norm.eps)
             out = self.ffn(normed2)
             return (updated, out) if defer else updated + out
@@ -485,10 +485,8 @@ class HybridTinyLM(nn.Module):
                       attention_layer_idx=a_idx if layer.backend == "attention" else None)
             if cfg.grad_checkpoint and self.training and kv_cache is None and state is None and torch.is_grad_enabled():
                 h = ckpt.checkpoint(lambda hh, L=layer, K=kw: L(hh, mask, **K), h, use_reentrant=False)
-            elif not torch.is_grad_enabled():
-                h, pending = layer(h, mask, pending=pending, defer=True, **kw)     # residual adds ride on the next norm
             else:
-                h = layer(h, mask, **kw)
+                h, pending = layer(h, mask, pending=pending, defer=True, **kw)     # residual adds ride on the next norm
             if layer.backend == "attention":
                 a_idx += 1
         if pending is not None:

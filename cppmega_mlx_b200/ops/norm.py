@@ -59,12 +59,52 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.
     return rms_norm_ref(x, weight, eps)
 
 
+class _AddRMSNormFn(torch.autograd.Function):
+    """``(s, y) = (h + delta, rms_norm(h + delta))`` in one pass; the backward adds the gradient arriving on ``s`` (the residual
+    stream) inside the norm's backward kernel, so neither direction needs a separate element-wise add."""
+
+    @staticmethod
+    def forward(ctx, h, delta, weight, eps):
+        lib = B.load_library()
+        cols = h.shape[-1]
+        h2, d2 = h.reshape(-1, cols).contiguous(), delta.reshape(-1, cols).contiguous()
+        rows = h2.shape[0]
+        s, y = torch.empty_like(h2), torch.empty_like(h2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=h.device)
+        B.check(lib.cmb_add_rmsnorm_train(B.ptr(h2), B.ptr(d2), B.ptr(weight), B.ptr(s), B.ptr(y), B.ptr(rstd), ctypes.c_int64(rows),
+                                          ctypes.c_int(cols), ctypes.c_float(eps), B.stream_ptr()), "add_rmsnorm_train")
+        ctx.save_for_backward(s, weight, rstd)
+        ctx.shape = h.shape
+        return s.view(h.shape), y.view(h.shape)
+
+    @staticmethod
+    def backward(ctx, g_s, g_y):
+        lib = B.load_library()
+        s, weight, rstd = ctx.saved_tensors
+        rows, cols = s.shape
+        if g_y is None:
+            return g_s, g_s, None, None
+        gy2 = g_y.reshape(rows, cols).contiguous()
+        gs2 = g_s.reshape(rows, cols).contiguous() if g_s is not None else None
+        gx = torch.empty_like(s)
+        nblk = min(rows, 148 * 4)
+        gw_part = torch.empty(nblk, cols, dtype=torch.float32, device=s.device)
+        B.check(lib.cmb_rmsnorm_bwd_add(B.ptr(gy2), B.ptr(s), B.ptr(weight), B.ptr(rstd), B.ptr(gs2), B.ptr(gx), B.ptr(gw_part),
+                                        ctypes.c_int64(rows), ctypes.c_int(cols), ctypes.c_int(nblk), B.stream_ptr()), "rmsnorm_bwd_add")
+        gx = gx.view(ctx.shape)
+        return gx, gx, gw_part.sum(0).to(weight.dtype), None
+
+
 def add_rms_norm(h: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5):
-    """``(h + delta, rms_norm(h + delta, weight))`` — one kernel launch on the GPU when no gradient is needed (decode steps),
-    bit-identical to the two separate ops."""
-    if (not torch.is_grad_enabled() and B.kernels_enabled() and B.on_gpu(h, delta, weight) and h.dtype == torch.bfloat16
-            and delta.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and h.shape == delta.shape
-            and h.shape[-1] % 8 == 0 and h.shape[-1] <= 2048 and h.numel() > 0):
+    """``(h + delta, rms_norm(h + delta, weight))`` — one kernel launch on the GPU, bit-identical to the two separate ops; with
+    gradients enabled the backward is one launch too (``_AddRMSNormFn``)."""
+    fusable = (B.kernels_enabled() and B.on_gpu(h, delta, weight) and h.dtype == torch.bfloat16 and delta.dtype == torch.bfloat16
+               and weight.dtype == torch.bfloat16 and h.shape == delta.shape and h.shape[-1] % 8 == 0 and h.shape[-1] <= 2048
+               and h.numel() > 0)
+    if fusable and torch.is_grad_enabled() and (h.requires_grad or delta.requires_grad or weight.requires_grad) \
+            and h.numel() // h.shape[-1] >= 4:
+        return _AddRMSNormFn.apply(h, delta, weight, eps)
+    if fusable and not torch.is_grad_enabled():
         lib = B.load_library()
         cols = h.shape[-1]
         h2, d2 = h.reshape(-1, cols).contiguous(), delta.reshape(-1, cols).contiguous()

@@ -267,3 +267,32 @@ def test_sinkhorn_kernel_matches_pytorch_ops(n, iters, batch):
     B.check_status()
     assert (out - ref).abs().max().item() < 1e-5
     assert (raw.grad - ref_in.grad).abs().max().item() < 1e-4 * (1.0 + ref_in.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 256), (1000, 2048), (7, 512)])
+def test_add_rms_norm_training_form_matches_separate_ops(rows, cols):
+    """The fused residual add + norm with gradients: outputs bit-identical to add-then-norm, gradients (input, delta, weight)
+    equal to the separate ops' within bf16 rounding, with gradient arriving on both outputs."""
+    from cppmega_mlx_b200 import ops
+    torch.manual_seed(rows + cols)
+    h0 = torch.randn(rows, cols, device="cuda").bfloat16()
+    d0 = (torch.randn(rows, cols, device="cuda") * 0.3).bfloat16()
+    w0 = (1.0 + 0.1 * torch.randn(cols, device="cuda")).bfloat16()
+    gs = torch.randn(rows, cols, device="cuda").bfloat16()
+    gy = torch.randn(rows, cols, device="cuda").bfloat16()
+
+    def run(fused):
+        h, d, w = (t.clone().requires_grad_() for t in (h0, d0, w0))
+        if fused:
+            s, y = ops.add_rms_norm(h, d, w, 1e-5)
+        else:
+            s = h + d
+            y = ops.rms_norm(s, w, 1e-5)
+        torch.autograd.backward([s, y], [gs, gy])
+        return s.detach(), y.detach(), h.grad, d.grad, w.grad
+    sf, yf, ghf, gdf, gwf = run(True)
+    sr, yr, ghr, gdr, gwr = run(False)
+    assert torch.equal(sf, sr) and torch.equal(yf, yr)
+    assert torch.equal(ghf, gdf)
+    assert (ghf.float() - ghr.float()).abs().max().item() <= 2e-2 * (ghr.float().abs().max().item() + 1e-6)
+    assert (gwf.float() - gwr.float()).abs().max().item() <= 2e-2 * (gwr.float().abs().max().item() + 1e-6)
