@@ -5,8 +5,10 @@ Rows are processed in chunks; for each chunk the logits tile is produced by the 
 to (log-sum-exp, target logit) and immediately turned into ``softmax − onehot`` in place, which feeds
 the two gradient GEMMs.  The loss and both gradients come out of one pass, exactly as the reference's
 manual forward+backward does (``cppmega_mlx/training/cut_cross_entropy.py:112`` chunked forward,
-``:147-201`` manual ``(loss, dE, dC)``; default chunk there is 256 rows, here 4096 because a B200
-GEMM needs that many rows to fill 148 SMs).
+``:147-201`` manual ``(loss, dE, dC)``; default chunk there is 256 rows; here a chunk is as many rows as
+keep its bf16 logits within ``MAX_CHUNK_BYTES`` (4 GiB of 180 GB; at least 4096 rows, which a B200 GEMM
+needs to fill 148 SMs) — with one chunk the weight gradient is a single bf16 product instead of an fp32
+accumulation over chunks).
 
 CUDA path: ``csrc/cce.cu`` fuses LSE + target pick + gradient write into one row kernel.
 """
@@ -20,6 +22,12 @@ from . import _backend as B
 from .gemm import gemm_raw
 
 DEFAULT_ROW_CHUNK = 4096
+MAX_CHUNK_BYTES = 4 << 30
+
+
+def auto_row_chunk(vocab: int) -> int:
+    """Rows per chunk: the largest multiple of ``DEFAULT_ROW_CHUNK`` whose bf16 logits stay within ``MAX_CHUNK_BYTES``."""
+    return max(DEFAULT_ROW_CHUNK, (MAX_CHUNK_BYTES // (2 * max(vocab, 1))) // DEFAULT_ROW_CHUNK * DEFAULT_ROW_CHUNK)
 
 
 def linear_cross_entropy_reference(hidden, weight, targets, mask=None, ignore_index: int = -100):
@@ -70,7 +78,13 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
         # the kernel reads 1/n_valid from device memory, so no host sync; the PyTorch path keeps it as a tensor too
         scale = scale_t.reshape(1).contiguous()
         dh = torch.empty_like(hidden) if want else None
-        dw = torch.zeros(weight.shape, dtype=torch.float32 if use_kernel else weight.dtype, device=weight.device) if want else None
+        one_chunk = T <= row_chunk
+        if not want:
+            dw = None
+        elif use_kernel and one_chunk:
+            dw = torch.empty_like(weight)          # written once by the single weight-gradient product
+        else:
+            dw = torch.zeros(weight.shape, dtype=torch.float32 if use_kernel else weight.dtype, device=weight.device)
         total = hidden.new_zeros((), dtype=torch.float32)
         t32 = targets.int().contiguous()
         v8 = valid.to(torch.uint8).contiguous() if use_kernel else valid
@@ -82,7 +96,7 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
             if want:
                 if use_kernel:
                     gemm_raw(dl, weight, b_mn=True, out=dh[r0:r1])            # dh = dl · W
-                    gemm_raw(dl, h.contiguous(), a_mn=True, b_mn=True, out=dw, accumulate=True)  # dW += dlᵀ · h
+                    gemm_raw(dl, h.contiguous(), a_mn=True, b_mn=True, out=dw, accumulate=not one_chunk)  # dW (+)= dlᵀ · h
                 else:
                     dh[r0:r1] = dl @ weight
                     dw += dl.t() @ h
@@ -100,7 +114,7 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
 
 
 def linear_cross_entropy(hidden, weight, targets, mask=None, ignore_index: int = -100,
-                         row_chunk: int = DEFAULT_ROW_CHUNK):
+                         row_chunk: int | None = None):
     """Mean CE of ``hidden @ weightᵀ`` against ``targets`` over valid positions, logits never fully held."""
     D = hidden.shape[-1]
     h2 = hidden.reshape(-1, D)
@@ -109,4 +123,6 @@ def linear_cross_entropy(hidden, weight, targets, mask=None, ignore_index: int =
     if mask is not None:
         valid = valid & mask.reshape(-1).bool()
     t = t.clamp(min=0)
+    if row_chunk is None:
+        row_chunk = auto_row_chunk(weight.shape[0]) if hidden.is_cuda else DEFAULT_ROW_CHUNK
     return _LinearCrossEntropyFn.apply(h2, weight, t, valid, int(row_chunk))
