@@ -45,7 +45,8 @@ def run_cell(args, optimizer: str, batch: int) -> dict:
                "--optimizer", optimizer, "--output", str(out), "--loss-backend", args.loss_backend]
         cmd += ["--synthetic"] if args.data_path is None else ["--data-path", str(args.data_path), "--data-format", args.data_format,
                                                               "--token-key", args.token_key]
-        for flag, val in (("--depth", args.depth), ("--vocab-size", args.vocab_size), ("--hidden-size", args.hidden_size), ("--pattern", args.pattern)):
+        for flag, val in (("--depth", args.depth), ("--vocab-size", args.vocab_size), ("--hidden-size", args.hidden_size), ("--pattern", args.pattern),
+                          ("--num-attention-heads", args.num_attention_heads)):
             if val is not None:
                 cmd += [flag, str(val)]
         if args.grad_checkpoint:
@@ -78,6 +79,7 @@ def main(argv=None) -> int:
     ap.add_argument("--vocab-size", type=int, default=None)
     ap.add_argument("--hidden-size", type=int, default=None)
     ap.add_argument("--pattern", default=None)
+    ap.add_argument("--num-attention-heads", type=int, default=None)
     ap.add_argument("--grad-checkpoint", action="store_true")
     ap.add_argument("--memory-cap-bytes", type=int, default=None)
     ap.add_argument("--cell-timeout", type=float, default=3600.0)
