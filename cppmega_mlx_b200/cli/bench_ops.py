@@ -101,6 +101,25 @@ def bench_composite(args) -> list[dict]:
     x = torch.randn(R, Dm, device=dev).bfloat16().requires_grad_()
     w = torch.ones(Dm, device=dev).bfloat16().requires_grad_()
     add("rmsnorm fwd+bwd 16384x2048", lambda: _fb(lambda: ops.rms_norm(x, w), x, w), algo_bytes=R * Dm * 2 * 5)
+    # residual add + norm, gradients arriving on both the new residual stream and the normed output: one fused launch per
+    # direction against add → norm (forward) and norm backward → add (backward)
+    hres = torch.randn(R, Dm, device=dev).bfloat16().requires_grad_()
+    dres = torch.randn(R, Dm, device=dev).bfloat16().requires_grad_()
+    g_s, g_y = torch.randn(R, Dm, device=dev).bfloat16(), torch.randn(R, Dm, device=dev).bfloat16()
+
+    def add_norm(fused):
+        def run():
+            for t in (hres, dres, w):
+                t.grad = None
+            if fused:
+                s_, y_ = ops.add_rms_norm(hres, dres, w)
+            else:
+                s_ = hres + dres
+                y_ = ops.rms_norm(s_, w)
+            torch.autograd.backward([s_, y_], [g_s, g_y])
+        return run
+    add("add+rmsnorm fwd+bwd 16384x2048 fused", lambda: add_norm(True), algo_bytes=R * Dm * 2 * 8, eager=False)
+    add("add+rmsnorm fwd+bwd 16384x2048 separate ops", lambda: add_norm(False), algo_bytes=R * Dm * 2 * 8, eager=False)
     gu = torch.randn(R, 11264, device=dev).bfloat16().requires_grad_()
     add("swiglu fwd+bwd 16384x5632", lambda: _fb(lambda: ops.swiglu(gu), gu), algo_bytes=R * 5632 * 2 * (3 + 5))
 

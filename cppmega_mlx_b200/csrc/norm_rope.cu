@@ -166,20 +166,44 @@ __global__ void __launch_bounds__(128) rmsnorm_fwd_warp_kernel(const __nv_bfloat
     const __nv_bfloat16* xr = x + row * cols;
     float f[VPL][8];
     float ss = 0.f;
+    if (delta != nullptr) {
+      // every 16-byte load of both operands is issued before the first store to `sum`
+      const __nv_bfloat16* dr = delta + row * cols;
+      uint4 rx[VPL], rd[VPL];
 #pragma unroll
-    for (int a = 0; a < VPL; ++a) {
-      const int v = lane + 32 * a;
-      if (v < nvec) {
-        load8(xr + 8 * v, f[a]);
-        if (delta != nullptr) {
-          float d[8];
-          load8(delta + row * cols + 8 * v, d);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) f[a][i] = __bfloat162float(__float2bfloat16(f[a][i] + d[i]));
-          store8(sum + row * cols + 8 * v, f[a]);
+      for (int a = 0; a < VPL; ++a) {
+        const int v = lane + 32 * a;
+        if (v < nvec) {
+          rx[a] = *reinterpret_cast<const uint4*>(xr + 8 * v);
+          rd[a] = *reinterpret_cast<const uint4*>(dr + 8 * v);
         }
+      }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ss += f[a][i] * f[a][i];
+      for (int a = 0; a < VPL; ++a) {
+        const int v = lane + 32 * a;
+        if (v < nvec) {
+          const __nv_bfloat162* bx = reinterpret_cast<const __nv_bfloat162*>(&rx[a]);
+          const __nv_bfloat162* bd = reinterpret_cast<const __nv_bfloat162*>(&rd[a]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 fx = __bfloat1622float2(bx[i]), fd = __bfloat1622float2(bd[i]);
+            f[a][2 * i] = __bfloat162float(__float2bfloat16(fx.x + fd.x));
+            f[a][2 * i + 1] = __bfloat162float(__float2bfloat16(fx.y + fd.y));
+          }
+          store8(sum + row * cols + 8 * v, f[a]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss += f[a][i] * f[a][i];
+        }
+      }
+    } else {
+#pragma unroll
+      for (int a = 0; a < VPL; ++a) {
+        const int v = lane + 32 * a;
+        if (v < nvec) {
+          load8(xr + 8 * v, f[a]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss += f[a][i] * f[a][i];
+        }
       }
     }
     ss = warp_sum(ss);
@@ -289,6 +313,13 @@ __global__ void __launch_bounds__(128, 4) rmsnorm_bwd_warp_kernel(const __nv_bfl
       if (v < nvec) {
         rx[a] = *reinterpret_cast<const uint4*>(xr + 8 * v);
         rg[a] = *reinterpret_cast<const uint4*>(gr + 8 * v);
+      }
+    }
+    if (gres != nullptr) {   // start the residual-gradient row towards L2 while the reduction below runs
+#pragma unroll
+      for (int a = 0; a < VPL; ++a) {
+        const int v = lane + 32 * a;
+        if (v < nvec) asm volatile("prefetch.global.L2 [%0];" ::"l"(gres + row * cols + 8 * v));
       }
     }
     const float r = rstd[row];
