@@ -130,6 +130,18 @@ class FusedEPComm:
         return out
 
 
+def _publish(comm: "FusedEPComm", buf: SymmetricBuffer, src: torch.Tensor, valid_rows, used_rows) -> None:
+    """Copy this rank's rows into its symmetric buffer for the peers to read.  With the layout's ``valid_rows`` / ``used_rows`` the
+    copy stops at the last used row (the buffer's capacity is a multiple of the expected rows) and is one kernel instead of a
+    full-capacity device copy."""
+    dst = buf.tensor.view(comm.rows, comm.d)
+    lib = B.load_library()
+    if valid_rows is not None and used_rows is not None and hasattr(lib, "cmb_ep_take") and src.is_contiguous() and src.dtype == dst.dtype:
+        B.check(lib.cmb_ep_take(B.ptr(src), B.ptr(dst), B.ptr(valid_rows), B.ptr(used_rows), I64(comm.rows), comm.d, B.stream_ptr()), "ep_take")
+    else:
+        dst.copy_(src)
+
+
 class _Dispatch(torch.autograd.Function):
     """flat [T,d] → this rank's received rows [rows,d] (padded expert-sorted). Backward gathers the row gradients back."""
 
@@ -138,14 +150,14 @@ class _Dispatch(torch.autograd.Function):
         comm.dispatch_rows(comm.xbuf, flat, tok, dest, slot)
         comm.barrier()                                           # all rows for me have landed
         ctx.comm, ctx.T = comm, flat.shape[0]
-        ctx.save_for_backward(tok, dest, slot)
+        ctx.save_for_backward(tok, dest, slot, valid_rows, used_rows)
         return comm.take(comm.xbuf, valid_rows, used_rows)
 
     @staticmethod
     def backward(ctx, g_rows):
-        tok, dest, slot = ctx.saved_tensors
+        tok, dest, slot, valid_rows, used_rows = ctx.saved_tensors
         comm = ctx.comm
-        comm.xbuf.tensor.view(comm.rows, comm.d).copy_(g_rows)
+        _publish(comm, comm.xbuf, g_rows.contiguous(), valid_rows, used_rows)
         comm.barrier()                                           # every owner has published its row gradients
         k = tok.numel() // ctx.T                                 # assignments are token-major: a = t·k + j
         g = comm.combine(comm.xbuf, dest, slot, None, ctx.T, k)  # Σ_j of the k row gradients of a token, gathered and summed in one pass
@@ -183,7 +195,7 @@ class _Combine(torch.autograd.Function):
     @staticmethod
     def forward(ctx, y_local, top_w, dest, slot, valid_rows, used_rows, comm: FusedEPComm):
         T, k = top_w.shape
-        comm.ybuf.tensor.view(comm.rows, comm.d).copy_(y_local)
+        _publish(comm, comm.ybuf, y_local.contiguous(), valid_rows, used_rows)
         comm.barrier()                                           # every owner has published its outputs
         w32 = top_w.float().contiguous()
         out, rows = comm.combine(comm.ybuf, dest, slot, w32, T, k, keep_rows=True)
