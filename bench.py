@@ -41,7 +41,8 @@ def parse_args():
                     help="stub = no communication at all (measurement aid for exposed-communication time; not a valid training run)")
     ap.add_argument("--depth", type=int, default=0, help="override layer count (debugging only; makes the result non-headline)")
     ap.add_argument("--ep", type=int, default=1, help="expert-parallel size for MoE profiles (1 = experts replicated; N = world size)")
-    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree for the dense FFNs (sequence parallel); ZeRO-1 runs over the remaining ranks")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (mixers head- / expert-parallel, dense FFNs column / row parallel); ZeRO-1 runs over the remaining ranks")
+    ap.add_argument("--sp", action="store_true", help="with --tp: sequence-parallel residual stream (gather → mixer / FFN → reduce-scatter instead of all-reduce)")
     ap.add_argument("--tp-fused", action="store_true", help="with --tp: the FFN all-reduces run as fused GEMM → reduce-scatter kernels over peer memory")
     ap.add_argument("--expert-gemm", default="bf16", choices=["bf16", "mxfp8"], help="routed-expert forward GEMMs (MoE profiles)")
     ap.add_argument("--no-e2e", action="store_true")
@@ -121,7 +122,11 @@ def main():
             fused_tp = FusedTPComm(tp_group, dev, max_rows_per_rank=args.micro_batch * args.seq_len // args.tp, max_cols=cfg.hidden_size)
         # attention / MoE / M2RNN mixers head- or expert-parallel, dense FFNs column/row-parallel; activations replicated in the TP group
         tensor_parallelize_mixers(model, tp_group)
-        tensor_parallelize_ffn(model, tp_group, sequence_parallel=False, fused=fused_tp)
+        tensor_parallelize_ffn(model, tp_group, sequence_parallel=args.sp, fused=None if args.sp else fused_tp)
+        if args.sp:
+            # sequence-parallel residual stream: norms / residual adds on S / tp tokens, gather → mixer → reduce-scatter
+            from cppmega_mlx_b200.parallel.tp import enable_sequence_parallel
+            enable_sequence_parallel(model, tp_group)
     nparams = model.num_parameters()
 
     if args.optimizer == "muon_adamw":
@@ -218,7 +223,7 @@ def main():
             "impl": args.impl,
             "config": {"model": f"{args.profile}: {cfg.pattern}x{cfg.depth // len(cfg.pattern)} d{cfg.hidden_size} "
                                 f"ffn{cfg.ffn_hidden_size} vocab{cfg.vocab_size} mtp{cfg.mtp_depth if cfg.mtp_enabled else 0}",
-                       "params": nparams, "global_batch": mb * dp, "seq_len": S, "parallelism": f"dp{dp} zero1 ({comm if args.tp == 1 else 'nccl'})" + (f" ep{args.ep}" if args.ep > 1 else "") + (f" tp{args.tp} (Mamba3 / MLA / MoE / M2RNN mixers head- or expert-parallel + dense FFNs{'; fused FFN all-reduce' if args.tp_fused else ''})" if args.tp > 1 else ""),
+                       "params": nparams, "global_batch": mb * dp, "seq_len": S, "parallelism": f"dp{dp} zero1 ({comm if args.tp == 1 else 'nccl'})" + (f" ep{args.ep}" if args.ep > 1 else "") + (f" tp{args.tp} (Mamba3 / MLA / MoE / M2RNN mixers head- or expert-parallel + dense FFNs{'; fused FFN all-reduce' if args.tp_fused and not args.sp else ''}{'; sequence-parallel residual stream' if args.sp else ''})" if args.tp > 1 else ""),
                        "optimizer": args.optimizer, "expert_gemm": args.expert_gemm, "micro_batch_per_gpu": mb, "grad_checkpoint": ckpt,
                        "l2": "working set per step (weights + activations, tens of GB) far exceeds the 126 MB L2; no flush needed"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "step_ms": spread,

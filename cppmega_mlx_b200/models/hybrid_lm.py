@@ -478,6 +478,12 @@ class HybridTinyLM(nn.Module):
         if document_ids is not None:
             from ..data.packing import document_boundary_mask
             mask = document_boundary_mask(document_ids)[:, None]  # [B,1,S,S] bool, causal ∧ same-document
+        sp_group = getattr(self, "sp_group", None)     # set by parallel.tp.enable_sequence_parallel: blocks work on sequence slices
+        if sp_group is not None:
+            if kv_cache is not None or state is not None:
+                raise NotImplementedError("the sequence-parallel model has no cache / state path")
+            from ..parallel.tp import enter_sequence_parallel, leave_sequence_parallel
+            h = enter_sequence_parallel(h, sp_group, 1)
         a_idx = 0
         pending = None
         for i, layer in enumerate(self.layers):
@@ -489,9 +495,8 @@ class HybridTinyLM(nn.Module):
                 h, pending = layer(h, mask, pending=pending, defer=True, **kw)     # residual adds ride on the next norm
             if layer.backend == "attention":
                 a_idx += 1
-        if pending is not None:
-            return ops.add_rms_norm(h, pending, self.norm.weight, self.norm.eps)[1]
-        return self.norm(h)
+        out = ops.add_rms_norm(h, pending, self.norm.weight, self.norm.eps)[1] if pending is not None else self.norm(h)
+        return leave_sequence_parallel(out, sp_group, 1) if sp_group is not None else out
 
     def num_parameters(self, trainable_only: bool = False) -> int:
         seen, n = set(), 0

@@ -110,6 +110,7 @@ class M2RNNMixer(nn.Module):
         # whose head count could not be split stay replicated (their gradients are summed over the group), the gated norm takes
         # its mean square over all ranks' columns, and the output projection's partial products are summed.
         self.tp_group = None
+        self.sequence_parallel = False     # with tp_group: input / output are this rank's sequence slice
         self.tp_replicated: tuple[str, ...] = ()
 
     def initial_h0(self, batch: int, dtype=torch.float32, device=None) -> torch.Tensor:
@@ -127,12 +128,18 @@ class M2RNNMixer(nn.Module):
         if h0 is not None and mixer_state is not None:
             raise ValueError("pass either h0 or mixer_state, not both")
         c = self.config
+        sp = self.tp_group is not None and self.sequence_parallel
+        if sp:
+            if mixer_state is not None or h0 is not None or return_state:
+                raise NotImplementedError("the sequence-parallel M2RNN mixer has no state hand-over")
+            from ..parallel.tp import gather_sequence
+            hidden_states = gather_sequence(hidden_states, self.tp_group, 1)
         b, s, _ = hidden_states.shape
         if self.tp_group is not None:
             from ..parallel.tp import mixed_column_linear
             rep = getattr(self, "in_proj_rep", None)            # replicated leading rows live in their own parameter
             weight = self.in_proj.weight if rep is None else torch.cat([rep.weight, self.in_proj.weight], 0)
-            proj = mixed_column_linear(hidden_states, weight, getattr(self, "tp_replicated_rows", 0), self.tp_group)
+            proj = mixed_column_linear(hidden_states, weight, getattr(self, "tp_replicated_rows", 0), self.tp_group, partial_dx=sp)
         else:
             proj = self.in_proj(hidden_states)
         conv_end, f_end = self.conv_dim, self.conv_dim + self.f_dim
@@ -168,8 +175,9 @@ class M2RNNMixer(nn.Module):
         # residual and output gate in one pass: (y + v·D) · silu(g), heads of v / g broadcast inside the kernel
         out = ops.m2rnn_post_gate(out, v, g, self.D).reshape(b, s, H * c.v_head_dim)
         if self.tp_group is not None:
-            from ..parallel.tp import reduce_from_tp, sharded_rms_norm
-            out = reduce_from_tp(self.out_proj(sharded_rms_norm(out, self.g_norm.weight, self.g_norm.eps, self.tp_group)), self.tp_group)
+            from ..parallel.tp import reduce_from_tp, reduce_scatter_sequence, sharded_rms_norm
+            out = self.out_proj(sharded_rms_norm(out, self.g_norm.weight, self.g_norm.eps, self.tp_group))
+            out = reduce_scatter_sequence(out, self.tp_group, 1) if sp else reduce_from_tp(out, self.tp_group)
         else:
             out = self.out_proj(self.g_norm(out))
         if not return_state:

@@ -158,6 +158,7 @@ class MLAAttention(nn.Module):
         self.indexer = None
         self.aux_loss: torch.Tensor | None = None
         self.tp_group = None     # set by parallel.tp.tensor_parallelize_mixers: this module then holds num_heads / tp of the heads
+        self.sequence_parallel = False   # with tp_group: input / output are this rank's sequence slice (parallel.tp.enable_sequence_parallel)
         if c.index_topk > 0:
             self.indexer = LightningIndexer(LightningIndexerConfig(
                 hidden_size=c.hidden_size, q_lora_rank=c.q_lora_rank, n_heads=c.index_n_heads,
@@ -190,12 +191,16 @@ class MLAAttention(nn.Module):
         return qr, q, c_kv, k_pe, (cos, sin)
 
     def _out(self, o):
-        """Output projection; with head parallelism each rank holds the columns of its heads and the partial products are summed."""
+        """Output projection; with head parallelism each rank holds the columns of its heads and the partial products are summed
+        (all-reduce, or reduce-scatter over the sequence when the residual stream is sequence parallel)."""
         y = self.wo(o)
         if self.tp_group is not None:
-            from ..parallel.tp import reduce_from_tp
-            y = reduce_from_tp(y, self.tp_group)
+            from ..parallel.tp import reduce_from_tp, reduce_scatter_sequence
+            y = reduce_scatter_sequence(y, self.tp_group, 1) if self._sp() else reduce_from_tp(y, self.tp_group)
         return y
+
+    def _sp(self) -> bool:
+        return self.tp_group is not None and self.sequence_parallel
 
     def _latent_query(self, q):
         """Fold W_UK into the query: [B,S,H,nope+rope] → [B,S,H,kv_lora+rope]."""
@@ -241,6 +246,15 @@ class MLAAttention(nn.Module):
             if s != 1 or isinstance(mask, torch.Tensor):
                 raise ValueError("a static decode cache serves one-token steps without an explicit mask")
             return self._static_step(x, kv_cache, layer_idx, sparse)
+        if self._sp():
+            # sequence parallel: ``x`` is this rank's slice of the sequence.  Everything that reads the gathered input directly
+            # (the low-rank projections, the indexer) computes the same thing on every rank, so its gradient is counted once in
+            # the reduce-scatter that the gather's backward performs.
+            if kv_cache is not None:
+                raise NotImplementedError("sequence-parallel attention has no cache path")
+            from ..parallel.tp import gather_sequence, scale_grad
+            x = scale_grad(gather_sequence(x, self.tp_group, 1), 1.0 / torch.distributed.get_world_size(self.tp_group))
+            b, s, _ = x.shape
         offset = kv_cache.position(layer_idx) if kv_cache is not None else 0
         qr, q, c_kv, k_pe, freqs = self._project(x, offset)
         use_sparse = (self.indexer is not None) if sparse is None else (sparse and self.indexer is not None)
@@ -266,8 +280,20 @@ class MLAAttention(nn.Module):
             from ..ops.dsa_indexer_loss import dsa_indexer_loss
             # teacher: this layer's own attention over the latent keys (detached inside the loss); student: the indexer scores
             k_lat = latent.detach()[:, :, None, :]
-            self.aux_loss = dsa_indexer_loss(self.indexer.scores(iq, idx_k, iw), self._latent_query(q.detach()), k_lat, softmax_scale=scale,
-                                             loss_coeff=c.index_loss_coeff, topk_indices=idx)
+            scores = self.indexer.scores(iq, idx_k, iw)
+            if self.tp_group is not None:
+                # this rank's teacher is the mean over its own heads; the loss gradient is linear in the teacher, so averaging it
+                # over the group gives every rank the gradient of the loss against the mean over all heads
+                from ..parallel.tp import mean_grad_over_tp
+                scores = mean_grad_over_tp(scores, self.tp_group)
+            loss = dsa_indexer_loss(scores, self._latent_query(q.detach()), k_lat, softmax_scale=scale, loss_coeff=c.index_loss_coeff,
+                                    topk_indices=idx)
+            if self.tp_group is not None:
+                # report the group mean of the per-rank values (an upper bound of the all-heads loss: KL is convex in the teacher)
+                mean = loss.detach().clone()
+                torch.distributed.all_reduce(mean, group=self.tp_group)
+                loss = loss + (mean / torch.distributed.get_world_size(self.tp_group) - loss.detach())
+            self.aux_loss = loss
         fresh = kv_cache is None or (offset == 0 and sk == s)     # nothing cached before these tokens (training, or a prefill from scratch)
         if fresh and add_mask is None and x.is_cuda and x.dtype == torch.bfloat16 and ops.kernels_enabled():
             # Training / prefill on the GPU: per-head K,V (192/128 wide) under the top-k bitmask.

@@ -216,6 +216,7 @@ class MoE(nn.Module):
         self.last_load: torch.Tensor | None = None
         self.tp_group = None      # expert tensor parallelism (parallel.tp.tensor_parallelize_mixers): tokens replicated, experts split
         self.tp_rank = 0
+        self.sequence_parallel = False   # with tp_group: input / output are this rank's sequence slice
 
     def _routed_expert_tp(self, flat: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor) -> torch.Tensor:
         """Tokens are replicated over the group and every rank holds ``local_experts`` of the experts: a rank evaluates the
@@ -225,7 +226,9 @@ class MoE(nn.Module):
         from ..parallel.tp import copy_to_tp, reduce_from_tp
         T, k = top_idx.shape
         Le = self.local_experts
-        flat = copy_to_tp(flat, self.tp_group)
+        sp = self.sequence_parallel
+        if not sp:        # sequence parallel: the caller's reduce-scatter adds the token gradients up instead
+            flat = copy_to_tp(flat, self.tp_group)
         e = top_idx.reshape(-1)
         mine = torch.div(e, Le, rounding_mode="floor") == self.tp_rank
         local_e = torch.where(mine, e - self.tp_rank * Le, torch.full_like(e, Le))        # foreign → sentinel group Le (sorted last)
@@ -250,7 +253,7 @@ class MoE(nn.Module):
             tok = torch.div(order[:n_local], k, rounding_mode="floor")
             ys = self.experts(flat.index_select(0, tok), counts[:Le]) * w[order[:n_local]].to(flat.dtype)[:, None]
             out = torch.zeros_like(flat).index_add_(0, tok, ys)
-        return reduce_from_tp(out, self.tp_group)
+        return out if sp else reduce_from_tp(out, self.tp_group)       # sequence parallel: the caller reduce-scatters
 
     def routed_forward(self, flat: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor) -> torch.Tensor:
         T, k = top_idx.shape
@@ -315,6 +318,19 @@ class MoE(nn.Module):
 
     def forward(self, x: torch.Tensor) -> MoEOutput:
         c = self.config
+        if self.tp_group is not None and self.sequence_parallel:
+            # ``x`` is this rank's sequence slice.  Routing and the routed experts see the gathered sequence (the router computes
+            # the same thing on every rank: its share of the input gradient is counted once in the gather's reduce-scatter); the
+            # partial expert outputs are reduce-scattered back to slices; the shared expert works on the slice.
+            from ..parallel.tp import gather_sequence, reduce_scatter_sequence, scale_grad
+            xf = gather_sequence(x, self.tp_group, 1)
+            router = self.router(scale_grad(xf, 1.0 / torch.distributed.get_world_size(self.tp_group)))
+            flat = xf.reshape(-1, c.d_model)
+            routed = self.routed_forward(flat, router.top_indices.reshape(-1, c.top_k), router.top_weights.reshape(-1, c.top_k))
+            routed = reduce_scatter_sequence(routed.view(xf.shape), self.tp_group, 1)
+            shared = self.shared_expert(x) if self.shared_expert is not None else None
+            self.last_load = router.load.detach()
+            return MoEOutput(routed + shared if shared is not None else routed, router, routed, shared)
         router = self.router(x)
         flat = x.reshape(-1, c.d_model)
         routed = self.routed_forward(flat, router.top_indices.reshape(-1, c.top_k), router.top_weights.reshape(-1, c.top_k))

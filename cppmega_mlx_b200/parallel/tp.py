@@ -89,6 +89,80 @@ class _ReduceScatterSeq(torch.autograd.Function):
         return _all_gather_dim(g, ctx.group, ctx.dim), None, None
 
 
+class _EnterSeq(torch.autograd.Function):
+    """Replicated activation → this rank's sequence slice.  Backward all-gathers the slices' gradients, so what produced the
+    replicated activation (computed identically on every rank) sees the complete gradient on every rank."""
+
+    @staticmethod
+    def forward(ctx, x, group, dim):
+        ctx.group, ctx.dim = group, dim
+        return x.chunk(_world(group), dim=dim)[dist.get_rank(group)].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        return _all_gather_dim(g, ctx.group, ctx.dim), None, None
+
+
+class _LeaveSeq(torch.autograd.Function):
+    """Sequence slices → replicated activation whose consumers compute the same thing on every rank: all-gather forward, and
+    backward just this rank's slice of the (identical, complete) gradient — no reduction."""
+
+    @staticmethod
+    def forward(ctx, x, group, dim):
+        ctx.group, ctx.dim = group, dim
+        return _all_gather_dim(x, group, dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g.chunk(_world(ctx.group), dim=ctx.dim)[dist.get_rank(ctx.group)].contiguous(), None, None
+
+
+class _ScaleGrad(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, scale):
+        ctx.scale = scale
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g * ctx.scale, None
+
+
+def scale_grad(x, scale: float):
+    """Identity whose gradient is multiplied by ``scale``.  Inside a sequence-parallel mixer the gathered input's gradient is
+    summed over the group (reduce-scatter); a consumer that computes the same thing on every rank passes its input through
+    ``scale_grad(x, 1 / tp)`` so that the sum counts it once."""
+    return x if scale == 1.0 else _ScaleGrad.apply(x, scale)
+
+
+class _MeanGradTP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g / _world(ctx.group), None
+
+
+def mean_grad_over_tp(x, group):
+    """Identity whose gradient is averaged over the group: for a loss that every rank evaluates on its own share of something the
+    loss is linear in (the attention teacher of the indexer loss is a mean over heads, and the heads are split over the ranks),
+    so that the replicated parameters behind ``x`` receive the gradient of the full loss, identical on every rank."""
+    return x if _world(group) == 1 else _MeanGradTP.apply(x, group)
+
+
+def enter_sequence_parallel(x, group, dim: int = 1):
+    return x if _world(group) == 1 else _EnterSeq.apply(x, group, dim)
+
+
+def leave_sequence_parallel(x, group, dim: int = 1):
+    return x if _world(group) == 1 else _LeaveSeq.apply(x, group, dim)
+
+
 def copy_to_tp(x, group):
     return x if _world(group) == 1 else _CopyToTP.apply(x, group)
 
@@ -241,9 +315,9 @@ class _MixedColumnLinear(torch.autograd.Function):
     share of ``dx`` is a partial sum that has to be added up over the group)."""
 
     @staticmethod
-    def forward(ctx, x, w, n_rep, group):
+    def forward(ctx, x, w, n_rep, group, partial_dx):
         ctx.save_for_backward(x, w)
-        ctx.n_rep, ctx.group = n_rep, group
+        ctx.n_rep, ctx.group, ctx.partial_dx = n_rep, group, partial_dx
         return ops.linear(x, w)
 
     @staticmethod
@@ -254,13 +328,18 @@ class _MixedColumnLinear(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         gw = (g2.t() @ x2).to(w.dtype)
         part = (g2[:, n:] @ w[n:]).contiguous()
-        dist.all_reduce(part, group=ctx.group)
-        gx = part + g2[:, :n] @ w[:n] if n else part
-        return gx.view(x.shape).to(x.dtype), gw, None, None
+        if ctx.partial_dx:
+            # sequence parallel: the caller's reduce-scatter adds dx up over the group, so the slice's share stays a partial sum
+            # and the replicated rows' share (complete and identical on every rank) is counted once in that sum
+            gx = part + (g2[:, :n] @ w[:n]) / _world(ctx.group) if n else part
+        else:
+            dist.all_reduce(part, group=ctx.group)
+            gx = part + g2[:, :n] @ w[:n] if n else part
+        return gx.view(x.shape).to(x.dtype), gw, None, None, None
 
 
-def mixed_column_linear(x, w, n_rep: int, group):
-    return _MixedColumnLinear.apply(x, w, n_rep, group)
+def mixed_column_linear(x, w, n_rep: int, group, partial_dx: bool = False):
+    return _MixedColumnLinear.apply(x, w, n_rep, group, partial_dx)
 
 
 def _rows(w: torch.Tensor, start: int, n: int) -> torch.Tensor:
@@ -444,6 +523,7 @@ class Mamba3TP(nn.Module):
         if H % tp or G % tp or G > H // tp:
             raise ValueError(f"head-parallel Mamba3 needs tp | nheads, tp | ngroups and ngroups <= nheads / tp (got {H} heads, {G} groups, tp {tp})")
         self.config, self.tp_group, self.tp_rank, self.tp_size = c, group, r, tp
+        self.sequence_parallel = False     # input / output are this rank's sequence slice (enable_sequence_parallel)
         Hl, Gl = H // tp, G // tp
         R = full.dims.num_rope_angles
         d_in, d_l, d_bc, dbc_l = c.d_inner, c.d_inner // tp, G * N, Gl * N
@@ -491,11 +571,14 @@ class Mamba3TP(nn.Module):
         import torch.nn.functional as F
         from ..nn import mamba3 as M3
         c, g = self.config, self.tp_group
+        sp = self.sequence_parallel
+        if sp:
+            hidden_states = gather_sequence(hidden_states, g, 1)
         b, s, _ = hidden_states.shape
         G, R, Hl, Gl, d_l, dbc_l, n_own = c.ngroups, self.R, self.Hl, self.Gl, self.d_l, self.dbc_l, self.n_own
         n_rep = G + R
         W = torch.cat([self.in_proj_rep.weight, self.in_proj.weight], 0)
-        proj = mixed_column_linear(hidden_states, W, n_rep, g)
+        proj = mixed_column_linear(hidden_states, W, n_rep, g, partial_dx=sp)
         rep = copy_to_tp(proj[..., :n_rep], g)                      # used differently on every rank: gradients are summed over the group
         phase_dd, angles = rep[..., :G], rep[..., G:]
         conv_ch = d_l + 2 * dbc_l
@@ -527,7 +610,8 @@ class Mamba3TP(nn.Module):
             Bg, Cg = M3.apply_rope_on_state_dim(Bg, ang_cum), M3.apply_rope_on_state_dim(Cg, ang_cum)
             A = torch.clamp(-F.softplus(dd_A.float()), max=-c.A_floor)
         y, h = ops.mamba3_scan(xh, Bg, Cg, zh, A, dt, self.D, None, chunk_size=c.chunk_size)
-        return reduce_from_tp(self.out_proj(y.reshape(b, s, d_l)), g), h
+        out = self.out_proj(y.reshape(b, s, d_l))
+        return (reduce_scatter_sequence(out, g, 1) if sp else reduce_from_tp(out, g)), h
 
 
 def _shard_mamba3(full, group):
@@ -563,3 +647,55 @@ def tensor_parallelize_mixers(model: nn.Module, group, *, kinds=("mla", "moe", "
                     setattr(parent, name, _shard_mamba3(child, group))
                     done["mamba3"] += 1
     return done
+
+
+# ----------------------------------------------------------------------------------------------- sequence parallelism
+def enable_sequence_parallel(model: nn.Module, group) -> list[nn.Parameter]:
+    """Make the residual stream of ``model`` sequence parallel over ``group``: between the blocks every rank holds S / tp tokens,
+    so the norms, residual adds and every other per-token op run on a slice; each mixer gathers its input over the sequence and
+    reduce-scatters its partial output (the same bytes as the all-reduce they replace), and so does every tensor-parallel FFN.
+    Call after ``tensor_parallelize_mixers`` and ``tensor_parallelize_ffn(..., sequence_parallel=True)``: every mixer must be
+    head- / expert-parallel and every FFN tensor parallel.  The model scatters its embeddings on entry and gathers the final
+    hidden states on exit (``sp_group``).  Parameters that are applied to slices — the blocks' norm weights and the final norm —
+    see only this rank's tokens, so their gradients have to be added up over the group after the backward pass:
+    ``allreduce_sequence_parallel_grads(model)``; the list of those parameters is returned."""
+    if _world(group) == 1:
+        return []
+    if not hasattr(model, "layers") or not hasattr(model, "norm"):
+        raise ValueError("enable_sequence_parallel needs a model with .layers (blocks) and .norm (final norm)")
+    partial: list[nn.Parameter] = []
+    for i, layer in enumerate(model.layers):
+        mixer = getattr(layer, "block", None)
+        if mixer is None or getattr(mixer, "tp_group", None) is None or not hasattr(mixer, "sequence_parallel"):
+            raise ValueError(f"layer {i}: {type(mixer).__name__} is not head- / expert-parallel; sequence parallelism needs every mixer sharded")
+        if getattr(layer, "mhc", None) is not None:
+            raise ValueError(f"layer {i}: the branch mixer is not supported under sequence parallelism")
+        ffn = getattr(layer, "ffn", None)
+        for f_ in [ffn] + [m for m in mixer.modules() if isinstance(m, (FeedForward, TPFeedForward))]:
+            if f_ is None:
+                continue
+            if not isinstance(f_, TPFeedForward) or not (f_.up.sequence_parallel and f_.down.sequence_parallel):
+                raise ValueError(f"layer {i}: run tensor_parallelize_ffn(model, group, sequence_parallel=True) first")
+        mixer.sequence_parallel = True
+        inner = {id(p) for m in (mixer, ffn) if m is not None for p in m.parameters()}
+        partial += [p for p in layer.parameters() if id(p) not in inner]
+    partial += list(model.norm.parameters())
+    model.sp_group = group
+    model._sp_partial_params = partial
+    return partial
+
+
+def allreduce_sequence_parallel_grads(model: nn.Module) -> None:
+    """Sum, over the sequence-parallel group, the gradients of the parameters that were applied to sequence slices (one
+    all-reduce of their concatenation).  Call after the last backward pass of a step, before the optimizer."""
+    group = getattr(model, "sp_group", None)
+    params = [p for p in getattr(model, "_sp_partial_params", []) if p.grad is not None]
+    if group is None or not params:
+        return
+    flat = torch.cat([p.grad.reshape(-1).float() for p in params])
+    dist.all_reduce(flat, group=group)
+    off = 0
+    for p in params:
+        n = p.grad.numel()
+        p.grad.copy_(flat[off:off + n].view_as(p.grad))
+        off += n

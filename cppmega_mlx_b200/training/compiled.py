@@ -142,7 +142,10 @@ class PretrainingStep:
             b = b.to(self.device, non_blocking=True)
         self.model.train()
         out = self.loss_fn(self.model, b)
-        if (self.state.micro_step + 1) % self.grad_accum_steps == 0 and self.max_grad_norm is None:
+        # a sequence-parallel model sums some gradients over its tensor-parallel group after the backward pass
+        # (parallel.tp.allreduce_sequence_parallel_grads), so they are not final when autograd produces them
+        sp = getattr(self.model, "sp_group", None) is not None
+        if (self.state.micro_step + 1) % self.grad_accum_steps == 0 and self.max_grad_norm is None and not sp:
             arm = getattr(self.optimizer, "arm_overlap", None)      # sharded optimizers start reducing a layer once its gradients are final
             if arm is not None and self.nonfinite_policy is None:
                 arm()
@@ -159,6 +162,9 @@ class PretrainingStep:
             self.optimizer.zero_grad()
             boundary = False
         elif boundary:
+            if sp:
+                from ..parallel.tp import allreduce_sequence_parallel_grads
+                allreduce_sequence_parallel_grads(self.model)
             if self.max_grad_norm is not None:
                 from .optimizers import clip_grad_norm_
                 gnorm = float(clip_grad_norm_([p for p in self.model.parameters()], self.max_grad_norm))
