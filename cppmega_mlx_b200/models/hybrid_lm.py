@@ -482,8 +482,13 @@ class HybridTinyLM(nn.Module):
         if sp_group is not None:
             if kv_cache is not None or state is not None:
                 raise NotImplementedError("the sequence-parallel model has no cache / state path")
-            from ..parallel.tp import enter_sequence_parallel, leave_sequence_parallel
-            h = enter_sequence_parallel(h, sp_group, 1)
+            from ..parallel.tp import enter_sequence_parallel, leave_sequence_parallel, set_sequence_parallel_dim
+            tp_ = torch.distributed.get_world_size(sp_group)
+            sp_dim = 0 if (h.shape[0] % tp_ == 0 and h.shape[0] > 1) else 1      # split the batch when it divides: leading-dimension slices
+            if h.shape[sp_dim] % tp_:
+                raise ValueError(f"sequence parallelism over {tp_} ranks needs the batch or the sequence length to divide, got {tuple(h.shape[:2])}")
+            set_sequence_parallel_dim(self, sp_dim)
+            h = enter_sequence_parallel(h, sp_group, sp_dim)
         a_idx = 0
         pending = None
         for i, layer in enumerate(self.layers):
@@ -496,7 +501,7 @@ class HybridTinyLM(nn.Module):
             if layer.backend == "attention":
                 a_idx += 1
         out = ops.add_rms_norm(h, pending, self.norm.weight, self.norm.eps)[1] if pending is not None else self.norm(h)
-        return leave_sequence_parallel(out, sp_group, 1) if sp_group is not None else out
+        return leave_sequence_parallel(out, sp_group, sp_dim) if sp_group is not None else out
 
     def num_parameters(self, trainable_only: bool = False) -> int:
         seen, n = set(), 0

@@ -110,7 +110,8 @@ class M2RNNMixer(nn.Module):
         # whose head count could not be split stay replicated (their gradients are summed over the group), the gated norm takes
         # its mean square over all ranks' columns, and the output projection's partial products are summed.
         self.tp_group = None
-        self.sequence_parallel = False     # with tp_group: input / output are this rank's sequence slice
+        self.sequence_parallel = False     # with tp_group: input / output are this rank's slice of the tokens
+        self.sp_dim = 1                    # … along the sequence (1) or the batch (0)
         self.tp_replicated: tuple[str, ...] = ()
 
     def initial_h0(self, batch: int, dtype=torch.float32, device=None) -> torch.Tensor:
@@ -133,7 +134,7 @@ class M2RNNMixer(nn.Module):
             if mixer_state is not None or h0 is not None or return_state:
                 raise NotImplementedError("the sequence-parallel M2RNN mixer has no state hand-over")
             from ..parallel.tp import gather_sequence
-            hidden_states = gather_sequence(hidden_states, self.tp_group, 1)
+            hidden_states = gather_sequence(hidden_states, self.tp_group, self.sp_dim)
         b, s, _ = hidden_states.shape
         if self.tp_group is not None:
             from ..parallel.tp import mixed_column_linear
@@ -177,7 +178,7 @@ class M2RNNMixer(nn.Module):
         if self.tp_group is not None:
             from ..parallel.tp import reduce_from_tp, reduce_scatter_sequence, sharded_rms_norm
             out = self.out_proj(sharded_rms_norm(out, self.g_norm.weight, self.g_norm.eps, self.tp_group))
-            out = reduce_scatter_sequence(out, self.tp_group, 1) if sp else reduce_from_tp(out, self.tp_group)
+            out = reduce_scatter_sequence(out, self.tp_group, self.sp_dim) if sp else reduce_from_tp(out, self.tp_group)
         else:
             out = self.out_proj(self.g_norm(out))
         if not return_state:

@@ -158,7 +158,8 @@ class MLAAttention(nn.Module):
         self.indexer = None
         self.aux_loss: torch.Tensor | None = None
         self.tp_group = None     # set by parallel.tp.tensor_parallelize_mixers: this module then holds num_heads / tp of the heads
-        self.sequence_parallel = False   # with tp_group: input / output are this rank's sequence slice (parallel.tp.enable_sequence_parallel)
+        self.sequence_parallel = False   # with tp_group: input / output are this rank's slice of the tokens (parallel.tp.enable_sequence_parallel)
+        self.sp_dim = 1                  # … along the sequence (1) or the batch (0)
         if c.index_topk > 0:
             self.indexer = LightningIndexer(LightningIndexerConfig(
                 hidden_size=c.hidden_size, q_lora_rank=c.q_lora_rank, n_heads=c.index_n_heads,
@@ -196,7 +197,7 @@ class MLAAttention(nn.Module):
         y = self.wo(o)
         if self.tp_group is not None:
             from ..parallel.tp import reduce_from_tp, reduce_scatter_sequence
-            y = reduce_scatter_sequence(y, self.tp_group, 1) if self._sp() else reduce_from_tp(y, self.tp_group)
+            y = reduce_scatter_sequence(y, self.tp_group, self.sp_dim) if self._sp() else reduce_from_tp(y, self.tp_group)
         return y
 
     def _sp(self) -> bool:
@@ -253,7 +254,7 @@ class MLAAttention(nn.Module):
             if kv_cache is not None:
                 raise NotImplementedError("sequence-parallel attention has no cache path")
             from ..parallel.tp import gather_sequence, scale_grad
-            x = scale_grad(gather_sequence(x, self.tp_group, 1), 1.0 / torch.distributed.get_world_size(self.tp_group))
+            x = scale_grad(gather_sequence(x, self.tp_group, self.sp_dim), 1.0 / torch.distributed.get_world_size(self.tp_group))
             b, s, _ = x.shape
         offset = kv_cache.position(layer_idx) if kv_cache is not None else 0
         qr, q, c_kv, k_pe, freqs = self._project(x, offset)

@@ -216,7 +216,8 @@ class MoE(nn.Module):
         self.last_load: torch.Tensor | None = None
         self.tp_group = None      # expert tensor parallelism (parallel.tp.tensor_parallelize_mixers): tokens replicated, experts split
         self.tp_rank = 0
-        self.sequence_parallel = False   # with tp_group: input / output are this rank's sequence slice
+        self.sequence_parallel = False   # with tp_group: input / output are this rank's slice of the tokens
+        self.sp_dim = 1                  # … along the sequence (1) or the batch (0)
 
     def _routed_expert_tp(self, flat: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor) -> torch.Tensor:
         """Tokens are replicated over the group and every rank holds ``local_experts`` of the experts: a rank evaluates the
@@ -323,11 +324,11 @@ class MoE(nn.Module):
             # the same thing on every rank: its share of the input gradient is counted once in the gather's reduce-scatter); the
             # partial expert outputs are reduce-scattered back to slices; the shared expert works on the slice.
             from ..parallel.tp import gather_sequence, reduce_scatter_sequence, scale_grad
-            xf = gather_sequence(x, self.tp_group, 1)
+            xf = gather_sequence(x, self.tp_group, self.sp_dim)
             router = self.router(scale_grad(xf, 1.0 / torch.distributed.get_world_size(self.tp_group)))
             flat = xf.reshape(-1, c.d_model)
             routed = self.routed_forward(flat, router.top_indices.reshape(-1, c.top_k), router.top_weights.reshape(-1, c.top_k))
-            routed = reduce_scatter_sequence(routed.view(xf.shape), self.tp_group, 1)
+            routed = reduce_scatter_sequence(routed.view(xf.shape), self.tp_group, self.sp_dim)
             shared = self.shared_expert(x) if self.shared_expert is not None else None
             self.last_load = router.load.detach()
             return MoEOutput(routed + shared if shared is not None else routed, router, routed, shared)

@@ -46,15 +46,34 @@ class _ReduceFromTP(torch.autograd.Function):
         return g, None
 
 
+def _leading(x, dim) -> bool:
+    """Slices along ``dim`` are contiguous blocks of the flat buffer (dim 0, or only extents of 1 before it)."""
+    return all(s == 1 for s in x.shape[:dim])
+
+
 def _all_gather_dim(x, group, dim):
     w = _world(group)
+    x = x.contiguous()
+    if _leading(x, dim) and dist.get_backend(group) == "nccl":
+        shape = list(x.shape)
+        shape[dim] *= w
+        out = x.new_empty(shape)
+        dist.all_gather_into_tensor(out, x, group=group)      # one collective, no concatenation pass
+        return out
     parts = [torch.empty_like(x) for _ in range(w)]
-    dist.all_gather(parts, x.contiguous(), group=group)
+    dist.all_gather(parts, x, group=group)
     return torch.cat(parts, dim=dim)
 
 
 def _reduce_scatter_dim(x, group, dim):
     w, r = _world(group), dist.get_rank(group)
+    if dist.get_backend(group) == "nccl" and _leading(x, dim) and x.shape[dim] % w == 0:
+        x = x.contiguous()
+        shape = list(x.shape)
+        shape[dim] //= w
+        out = x.new_empty(shape)
+        dist.reduce_scatter_tensor(out, x, group=group)
+        return out
     chunks = [c.contiguous() for c in x.chunk(w, dim=dim)]
     if dist.get_backend(group) == "nccl":
         out = torch.empty_like(chunks[0])
@@ -214,7 +233,7 @@ class ColumnParallelLinear(nn.Module):
         self.weight = nn.Parameter(shard_rows(full.weight.detach(), group, blocks=blocks).clone())
 
     def forward(self, x):
-        x = gather_sequence(x, self.group) if self.sequence_parallel else copy_to_tp(x, self.group)
+        x = gather_sequence(x, self.group, getattr(self, "sp_dim", 1)) if self.sequence_parallel else copy_to_tp(x, self.group)
         return ops.linear(x, self.weight)
 
 
@@ -228,7 +247,7 @@ class RowParallelLinear(nn.Module):
 
     def forward(self, x):
         y = ops.linear(x, self.weight)
-        return reduce_scatter_sequence(y, self.group) if self.sequence_parallel else reduce_from_tp(y, self.group)
+        return reduce_scatter_sequence(y, self.group, getattr(self, "sp_dim", 1)) if self.sequence_parallel else reduce_from_tp(y, self.group)
 
 
 class TPFeedForward(nn.Module):
@@ -523,7 +542,8 @@ class Mamba3TP(nn.Module):
         if H % tp or G % tp or G > H // tp:
             raise ValueError(f"head-parallel Mamba3 needs tp | nheads, tp | ngroups and ngroups <= nheads / tp (got {H} heads, {G} groups, tp {tp})")
         self.config, self.tp_group, self.tp_rank, self.tp_size = c, group, r, tp
-        self.sequence_parallel = False     # input / output are this rank's sequence slice (enable_sequence_parallel)
+        self.sequence_parallel = False     # input / output are this rank's slice of the tokens (enable_sequence_parallel)
+        self.sp_dim = 1                    # … along the sequence, or along the batch (0) when the batch divides evenly
         Hl, Gl = H // tp, G // tp
         R = full.dims.num_rope_angles
         d_in, d_l, d_bc, dbc_l = c.d_inner, c.d_inner // tp, G * N, Gl * N
@@ -573,7 +593,7 @@ class Mamba3TP(nn.Module):
         c, g = self.config, self.tp_group
         sp = self.sequence_parallel
         if sp:
-            hidden_states = gather_sequence(hidden_states, g, 1)
+            hidden_states = gather_sequence(hidden_states, g, self.sp_dim)
         b, s, _ = hidden_states.shape
         G, R, Hl, Gl, d_l, dbc_l, n_own = c.ngroups, self.R, self.Hl, self.Gl, self.d_l, self.dbc_l, self.n_own
         n_rep = G + R
@@ -611,7 +631,7 @@ class Mamba3TP(nn.Module):
             A = torch.clamp(-F.softplus(dd_A.float()), max=-c.A_floor)
         y, h = ops.mamba3_scan(xh, Bg, Cg, zh, A, dt, self.D, None, chunk_size=c.chunk_size)
         out = self.out_proj(y.reshape(b, s, d_l))
-        return (reduce_scatter_sequence(out, g, 1) if sp else reduce_from_tp(out, g)), h
+        return (reduce_scatter_sequence(out, g, self.sp_dim) if sp else reduce_from_tp(out, g)), h
 
 
 def _shard_mamba3(full, group):
@@ -683,6 +703,15 @@ def enable_sequence_parallel(model: nn.Module, group) -> list[nn.Parameter]:
     model.sp_group = group
     model._sp_partial_params = partial
     return partial
+
+
+def set_sequence_parallel_dim(model: nn.Module, dim: int) -> None:
+    """Which dimension of [B, S, d] the ranks split between the blocks: the sequence (1), or the batch (0) — per-token work does
+    not care, and slices along the leading dimension gather / reduce-scatter in place, with no re-packing pass.  The model calls
+    this at the start of every forward pass (0 when the batch divides by the group size or is 1 … then dim 1 is leading too)."""
+    for m in model.modules():
+        if getattr(m, "sequence_parallel", False):
+            m.sp_dim = dim
 
 
 def allreduce_sequence_parallel_grads(model: nn.Module) -> None:

@@ -142,7 +142,7 @@ def test_tensor_parallel_mixers_match_single_rank():
     assert all(run_ranks(_tp_mixers_rank, 2))
 
 
-def _sp_mixers_rank(rank, world, aux):
+def _sp_mixers_rank(rank, world, aux, batch):
     """The same stack with a sequence-parallel residual stream: every rank holds half of the tokens between the blocks; output,
     the gradient of the embeddings (entry of the region), the norm weights (summed over the group afterwards) and the sliced /
     replicated mixer parameters all match the single-process model.  ``aux``: the MoE router's balance loss and the attention
@@ -165,7 +165,7 @@ def _sp_mixers_rank(rank, world, aux):
             if p.dim() == 2 and float(p.abs().sum()) == 0:
                 p.normal_(std=0.05)
     full.train()
-    ids = torch.randint(0, 64, (2, 12))
+    ids = torch.randint(0, 64, (batch, 12))      # an even batch is split over the ranks, an odd one keeps whole rows and splits the sequence
 
     def loss_of(m):
         out = m(ids)
@@ -217,9 +217,9 @@ def _sp_mixers_rank(rank, world, aux):
     return True
 
 
-@pytest.mark.parametrize("aux", [False, True])
-def test_sequence_parallel_stack_matches_single_rank(aux):
-    assert all(run_ranks(_sp_mixers_rank, 2, aux))
+@pytest.mark.parametrize("aux,batch", [(False, 2), (True, 2), (True, 3)])
+def test_sequence_parallel_stack_matches_single_rank(aux, batch):
+    assert all(run_ranks(_sp_mixers_rank, 2, aux, batch))
 
 
 def _ep_rank(rank, world):
