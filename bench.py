@@ -119,10 +119,11 @@ def main():
         fused_tp = None
         if args.tp_fused and ours:
             from cppmega_mlx_b200.parallel.fused_tp import FusedTPComm
-            fused_tp = FusedTPComm(tp_group, dev, max_rows_per_rank=args.micro_batch * args.seq_len // args.tp, max_cols=cfg.hidden_size)
+            fused_tp = FusedTPComm(tp_group, dev, max_rows_per_rank=args.micro_batch * args.seq_len // args.tp,
+                                   max_cols=max(cfg.hidden_size, 2 * cfg.ffn_hidden_size // args.tp) if args.sp else cfg.hidden_size)
         # attention / MoE / M2RNN mixers head- or expert-parallel, dense FFNs column/row-parallel; activations replicated in the TP group
         tensor_parallelize_mixers(model, tp_group)
-        tensor_parallelize_ffn(model, tp_group, sequence_parallel=args.sp, fused=None if args.sp else fused_tp)
+        tensor_parallelize_ffn(model, tp_group, sequence_parallel=args.sp, fused=fused_tp)
         if args.sp:
             # sequence-parallel residual stream: norms / residual adds on S / tp tokens, gather → mixer → reduce-scatter
             from cppmega_mlx_b200.parallel.tp import enable_sequence_parallel
@@ -223,7 +224,7 @@ def main():
             "impl": args.impl,
             "config": {"model": f"{args.profile}: {cfg.pattern}x{cfg.depth // len(cfg.pattern)} d{cfg.hidden_size} "
                                 f"ffn{cfg.ffn_hidden_size} vocab{cfg.vocab_size} mtp{cfg.mtp_depth if cfg.mtp_enabled else 0}",
-                       "params": nparams, "global_batch": mb * dp, "seq_len": S, "parallelism": f"dp{dp} zero1 ({comm if args.tp == 1 else 'nccl'})" + (f" ep{args.ep}" if args.ep > 1 else "") + (f" tp{args.tp} (Mamba3 / MLA / MoE / M2RNN mixers head- or expert-parallel + dense FFNs{'; fused FFN all-reduce' if args.tp_fused and not args.sp else ''}{'; sequence-parallel residual stream' if args.sp else ''})" if args.tp > 1 else ""),
+                       "params": nparams, "global_batch": mb * dp, "seq_len": S, "parallelism": f"dp{dp} zero1 ({comm if args.tp == 1 else 'nccl'})" + (f" ep{args.ep}" if args.ep > 1 else "") + (f" tp{args.tp} (Mamba3 / MLA / MoE / M2RNN mixers head- or expert-parallel + dense FFNs{'; fused FFN collectives' if args.tp_fused else ''}{'; sequence-parallel residual stream' if args.sp else ''})" if args.tp > 1 else ""),
                        "optimizer": args.optimizer, "expert_gemm": args.expert_gemm, "micro_batch_per_gpu": mb, "grad_checkpoint": ckpt,
                        "l2": "working set per step (weights + activations, tens of GB) far exceeds the 126 MB L2; no flush needed"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "step_ms": spread,

@@ -262,14 +262,22 @@ class TPFeedForward(nn.Module):
         self.up = ColumnParallelLinear(full.gate_up_proj if gated else full.up_proj, group, sequence_parallel=sequence_parallel,
                                        blocks=2 if gated else 1)
         self.down = RowParallelLinear(full.down_proj, group, sequence_parallel=sequence_parallel)
-        self.fused = fused if not sequence_parallel else None
+        self.fused = fused
 
     def _act(self, h):
         return ops.swiglu(h) if self.activation == "swiglu" else (torch.nn.functional.gelu(h) if self.activation == "gelu" else ops.squared_relu(h))
 
     def forward(self, x):
         f = self.fused
-        if f is not None and x.is_cuda and x.dtype == torch.bfloat16 and ops.kernels_enabled() and x.numel() // x.shape[-1] % f.world == 0:
+        usable = f is not None and x.is_cuda and x.dtype == torch.bfloat16 and ops.kernels_enabled()
+        if usable and self.up.sequence_parallel:
+            # sequence parallel: ``x`` is this rank's block of the flattened tokens when the split runs along the leading dimension;
+            # all-gather → GEMM and GEMM → reduce-scatter then run as the fused pairs over peer memory
+            if getattr(self.up, "sp_dim", 1) == 0 or x.shape[0] == 1:
+                from .fused_tp import column_parallel_fused, row_parallel_fused
+                h = self._act(column_parallel_fused(x.reshape(-1, x.shape[-1]), self.up.weight, f))
+                return row_parallel_fused(h, self.down.weight, f).view(x.shape)
+        elif usable and x.numel() // x.shape[-1] % f.world == 0:
             from .fused_tp import column_parallel_copy_fused, row_parallel_all_reduce_fused
             x2 = x.reshape(-1, x.shape[-1])
             h = self._act(column_parallel_copy_fused(x2, self.up.weight, f))
