@@ -46,6 +46,8 @@ def parse_args():
     ap.add_argument("--tp-fused", action="store_true", help="with --tp: the FFN all-reduces run as fused GEMM → reduce-scatter kernels over peer memory")
     ap.add_argument("--expert-gemm", default="bf16", choices=["bf16", "mxfp8"], help="routed-expert forward GEMMs (MoE profiles)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--kernel-table", type=int, default=0, metavar="N",
+                    help="after the timed region: one extra step under torch.profiler, rank 0 prints its N costliest kernels to stderr")
     ap.add_argument("--grad-checkpoint", default="auto", choices=["auto", "on", "off"],
                     help="per-block activation recomputation; auto = on for the eager arm (it does not fit otherwise)")
     return ap.parse_args()
@@ -197,6 +199,19 @@ def main():
     B.check_status()
     ms_per_step = ms / args.steps
     value = tokens_per_step / (ms_per_step / 1e3)
+
+    if args.kernel_table:
+        # analysis aid, after the timed region: one more step under torch.profiler, rank 0 lists where its device time went
+        from torch.profiler import ProfilerActivity, profile
+        barrier()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            stepper(dev_batches[args.warmup])
+            torch.cuda.synchronize()
+        if rank == 0:
+            rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)[:args.kernel_table]
+            for e in rows:
+                print(json.dumps({"kernel": e.key[:120], "ms": round(e.device_time_total / 1e3, 3), "launches": e.count}), file=sys.stderr)
+        barrier()
 
     # ---- end-to-end timing through the public stepper API ------------------------------------------
     e2e = None
