@@ -314,6 +314,50 @@ __global__ void __launch_bounds__(256) zero1_push_ranges_kernel(PeerPtrs params,
   }
 }
 
+// ---------------------------------------------------------------------------------------------- stand-alone all-reduce
+// Sum of every rank's copy of a symmetric buffer, left in every rank's copy.  The caller brackets the launch with the epoch
+// barrier (all inputs written before, all outputs visible after).  Rank r reduces the r-th slice of 16-byte vectors and
+// publishes it to everyone (a reduce-scatter and an all-gather in one pass):
+//   multimem form — one `multimem.ld_reduce` (the switch adds the W copies) and one `multimem.st` (the switch replicates) per
+//                   vector: this GPU receives one vector and sends one, whatever W is;
+//   peer form     — W loads (fixed rank order: bitwise reproducible) and W stores per vector.
+// `dtype`: 0 = fp32 (4 elements per vector), 1 = bf16 (8 per vector, fp32 accumulation).
+template <int DTYPE>
+__global__ void __launch_bounds__(256) allreduce_kernel(PeerPtrs bufs, int rank, int world, long long nvec) {
+  const long long per = (nvec + world - 1) / world;
+  const long long lo = rank * per, hi = min(nvec, lo + per);
+  for (long long i = lo + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < hi; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    uint4 out;
+    if (bufs.mc != nullptr) {
+      const char* a = static_cast<const char*>(bufs.mc) + i * 16;
+      if (DTYPE == 1) {
+        out = multimem_ld_reduce_bf16x8(a);
+      } else {
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(out.x), "=r"(out.y), "=r"(out.z), "=r"(out.w)
+                     : "l"(a)
+                     : "memory");
+      }
+      multimem_st_16(static_cast<char*>(bufs.mc) + i * 16, out);
+    } else {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < world; ++r) {
+        const uint4 q = *(static_cast<const uint4*>(bufs.p[r]) + i);
+        if (DTYPE == 1) {
+          float f[8];
+          unpack8(q, f);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[k] += f[k];
+        } else {
+          acc[0] += __uint_as_float(q.x); acc[1] += __uint_as_float(q.y); acc[2] += __uint_as_float(q.z); acc[3] += __uint_as_float(q.w);
+        }
+      }
+      out = DTYPE == 1 ? pack8(acc) : make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
+      for (int r = 0; r < world; ++r) *(static_cast<uint4*>(bufs.p[r]) + i) = out;
+    }
+  }
+}
+
 static inline int comm_grid(long long nvec) {
   long long b = (nvec + 255) / 256;
   const long long cap = Z1_PARTS;
@@ -409,5 +453,21 @@ extern "C" int cmb_zero1_push_ranges(const long long* param_ptrs, int rank, int 
   if (nranges <= 0) return 0;
   cmb::zero1_push_ranges_kernel<<<cmb::comm_grid(total_elems / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       p, rank, world, static_cast<const cmb::Z1Range*>(ranges), nranges, lr);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// In-place all-reduce (sum) of a symmetric buffer of `nbytes` bytes (a multiple of 16); see allreduce_kernel.  `buf_ptrs` holds the W
+// peer addresses followed, with `use_mc`, by the multicast address.  Bracket with cmb_comm_barrier on the same stream.
+extern "C" int cmb_symm_allreduce(const long long* buf_ptrs, int rank, int world, long long nbytes, int dtype, int use_mc, void* stream) {
+  cmb::PeerPtrs b;
+  if (!cmb::fill(b, buf_ptrs, world, use_mc) || (nbytes & 15) || (dtype != 0 && dtype != 1)) return 1;
+  if (nbytes <= 0) return 0;
+  const long long nvec = nbytes / 16;
+  const int grid = cmb::comm_grid((nvec + world - 1) / world);
+  auto st = static_cast<cudaStream_t>(stream);
+  if (dtype == 1)
+    cmb::allreduce_kernel<1><<<grid, 256, 0, st>>>(b, rank, world, nvec);
+  else
+    cmb::allreduce_kernel<0><<<grid, 256, 0, st>>>(b, rank, world, nvec);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }

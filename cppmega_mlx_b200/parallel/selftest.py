@@ -180,6 +180,38 @@ def case_zero1bw(rank, world, dev):
                           "multicast_binding": grads.multicast_ptr != 0, "barrier_ms": t_bar, **rows}))
 
 
+def case_allreduce(rank, world, dev):
+    """The stand-alone symmetric-memory all-reduce (peer form and, where the buffer has a multicast binding, multimem form)
+    against NCCL: fp32 and bf16, a length that is not a multiple of the vector width, and its latency on a small message."""
+    from cppmega_mlx_b200.ops import _backend as B
+    from cppmega_mlx_b200.parallel.symm import SymmetricAllReduce
+    out = {"case": "allreduce", "world": world}
+    for dtype, name in ((torch.float32, "fp32"), (torch.bfloat16, "bf16")):
+        for mm in (False, True):
+            red = SymmetricAllReduce(1 << 20, dtype, dev, multimem=mm)
+            if mm and not red.use_mc:
+                out[f"{name}_multimem"] = "no multicast binding"
+                continue
+            worst = 0.0
+            for n in (1 << 20, 99_991, 7):
+                g = torch.Generator(device=dev).manual_seed(1000 * rank + n)
+                x = torch.randn(n, generator=g, device=dev).to(dtype)
+                ref = x.clone()
+                dist.all_reduce(ref)
+                got = red(x.clone())
+                tol = 1e-5 if dtype == torch.float32 else 2e-2
+                worst = max(worst, float((got.float() - ref.float()).abs().max() / (ref.float().abs().max() + 1e-6)))
+                assert worst < tol, (name, mm, n, worst)
+            small = torch.ones(8192, device=dev, dtype=dtype)
+            t_ours = _time(lambda: red(small), iters=20)
+            t_nccl = _time(lambda: dist.all_reduce(small), iters=20)
+            out[f"{name}_{'multimem' if mm else 'peer'}"] = {"max_rel_err": worst, "ms_8192_elems": t_ours, "ms_nccl": t_nccl}
+    torch.cuda.synchronize()
+    B.check_status()
+    if rank == 0:
+        print(json.dumps(out))
+
+
 def _time(fn, iters=10, warmup=3):
     for _ in range(warmup):
         fn()
@@ -374,7 +406,7 @@ def main():
     case = sys.argv[1] if len(sys.argv) > 1 else "zero1"
     rank, world, dev = _setup()
     try:
-        {"zero1": case_zero1, "zero1det": case_zero1det, "zero1bw": case_zero1bw, "tp": case_tp, "tpar": case_tpar, "ep": case_ep, "epdrop": case_epdrop}[case](rank, world, dev)
+        {"zero1": case_zero1, "zero1det": case_zero1det, "zero1bw": case_zero1bw, "allreduce": case_allreduce, "tp": case_tp, "tpar": case_tpar, "ep": case_ep, "epdrop": case_epdrop}[case](rank, world, dev)
     finally:
         dist.barrier()
         dist.destroy_process_group()

@@ -61,3 +61,40 @@ class EpochBarrier:
         st = B.status_buffer(self.device)
         B.check(lib.cmb_comm_barrier(self.pad.peer_ptrs, self.pad.rank, self.pad.world, self.epoch,
                                      ctypes.c_longlong(SPIN_LIMIT), B.ptr(st), B.stream_ptr()), "comm_barrier")
+
+
+class SymmetricAllReduce:
+    """In-place sum over the group of up to ``numel`` elements (fp32 or bf16) through one symmetric buffer: copy in, barrier, one
+    kernel in which every rank reduces its slice and publishes it to all (``csrc/comm.cu`` ``allreduce_kernel``), barrier, copy
+    out.  ``multimem=True`` uses the in-switch reduction and the multicast store when the buffer has a multicast binding; the
+    default is plain peer loads / stores in a fixed rank order (bitwise reproducible, and safe if a rank dies mid-step).
+    Meant for the small, latency-bound reductions of a step (norm-weight gradients, loss statistics): three short launches on the
+    caller's stream, no NCCL kernel."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device: torch.device, group=None, *, multimem: bool = False):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("SymmetricAllReduce supports float32 and bfloat16")
+        per_vec = 16 // torch.empty((), dtype=dtype).element_size()
+        self.capacity = (numel + per_vec - 1) // per_vec * per_vec
+        self.dtype, self.device = dtype, device
+        self.buf = SymmetricBuffer(self.capacity, dtype, device, group)
+        self.barrier = EpochBarrier(device, group)
+        self.use_mc = int(bool(multimem) and self.buf.multicast_ptr != 0)
+
+    def __call__(self, t: torch.Tensor) -> torch.Tensor:
+        n = t.numel()
+        if n > self.capacity or t.dtype != self.dtype:
+            raise ValueError(f"tensor of {n} {t.dtype} elements does not fit this reducer ({self.capacity} {self.dtype})")
+        per_vec = 16 // t.element_size()
+        padded = (n + per_vec - 1) // per_vec * per_vec
+        view = self.buf.tensor[:padded]
+        view[:n].copy_(t.reshape(-1))
+        if padded > n:
+            view[n:].zero_()
+        lib = B.load_library()
+        self.barrier()                                      # every rank's input is in its buffer
+        B.check(lib.cmb_symm_allreduce(self.buf.peer_ptrs, self.buf.rank, self.buf.world, ctypes.c_longlong(padded * t.element_size()),
+                                       1 if t.dtype == torch.bfloat16 else 0, self.use_mc, B.stream_ptr()), "symm_allreduce")
+        self.barrier()                                      # every slice has been published to this rank
+        t.copy_(view[:n].view_as(t))
+        return t

@@ -62,6 +62,15 @@ def test_fused_zero1_multimem_form_matches_nccl_two_gpus():
     assert all(abs(a - b) < 5e-2 for a, b in zip(out["loss_fused"], out["loss_nccl"])), out
 
 
+def test_symmetric_memory_all_reduce_matches_nccl_two_gpus():
+    """Stand-alone all-reduce over one symmetric buffer, peer form and (where bound) multimem form, fp32 and bf16, ragged lengths."""
+    out = _selftest("allreduce")
+    assert out["fp32_peer"]["max_rel_err"] < 1e-5 and out["bf16_peer"]["max_rel_err"] < 2e-2, out
+    for k in ("fp32_multimem", "bf16_multimem"):
+        if isinstance(out[k], dict):
+            assert out[k]["max_rel_err"] < (1e-5 if k.startswith("fp32") else 2e-2), out
+
+
 def test_fused_zero1_is_bitwise_deterministic_two_gpus():
     out = _selftest("zero1det")
     assert out["bitwise_equal"] and out["finite"], out
