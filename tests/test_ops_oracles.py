@@ -170,6 +170,35 @@ def test_cut_cross_entropy_matches_materialised():
     assert all(torch.allclose(a, c, atol=1e-5) for a, c in zip(g, gr))
 
 
+@pytest.mark.parametrize("row_chunk", [7, 50, 4096])
+def test_cut_cross_entropy_is_independent_of_the_row_chunk(row_chunk):
+    """One chunk, several ragged chunks or one chunk per few rows: same loss and gradients (the weight gradient accumulates over
+    chunks, or is written once when a single chunk covers the rows)."""
+    torch.manual_seed(16)
+    h = torch.randn(50, 16, requires_grad=True)
+    w = torch.randn(40, 16, requires_grad=True)
+    t = torch.randint(0, 40, (50,))
+    t[3] = -100
+    mask = torch.ones(50, dtype=torch.bool)
+    mask[10:14] = False
+    loss = ops.linear_cross_entropy(h, w, t, mask=mask, row_chunk=row_chunk)
+    tt = t.clone()
+    tt[~mask] = -100
+    ref = F.cross_entropy(h @ w.t(), tt, ignore_index=-100)
+    assert torch.allclose(loss, ref, atol=1e-5)
+    g = torch.autograd.grad(loss * 3.0, (h, w))                # a scaled upstream gradient reaches both gradients
+    gr = torch.autograd.grad(ref * 3.0, (h, w))
+    assert all(torch.allclose(a, c, atol=2e-5) for a, c in zip(g, gr))
+
+
+def test_cut_cross_entropy_chunk_size_follows_the_logits_budget():
+    from cppmega_mlx_b200.ops import cce
+    assert cce.auto_row_chunk(65536) == 32768                  # 4 GiB of bf16 logits: the flagship's 16384 rows are one chunk
+    assert cce.auto_row_chunk(131072) == 16384
+    assert cce.auto_row_chunk(1 << 22) == cce.DEFAULT_ROW_CHUNK    # never below the rows a GEMM needs to fill the GPU
+    assert cce.auto_row_chunk(512) % cce.DEFAULT_ROW_CHUNK == 0
+
+
 def test_grouped_linear_matches_per_expert_loop():
     from cppmega_mlx_b200.ops.grouped_gemm import grouped_linear
     torch.manual_seed(7)
