@@ -222,6 +222,49 @@ def test_sequence_parallel_stack_matches_single_rank(aux, batch):
     assert all(run_ranks(_sp_mixers_rank, 2, aux, batch))
 
 
+def _sp_refusals_rank(rank, world):
+    """enable_sequence_parallel refuses a stack whose mixers are not all sharded, and one whose FFNs are tensor parallel without
+    sequence parallelism; the gradient scale and the group-mean gradient are identities forward."""
+    from cppmega_mlx_b200.models.hybrid_lm import HybridTinyConfig, HybridTinyLM
+    from cppmega_mlx_b200.parallel import tp as TP
+    st = PS.init_parallel_state(tp=world)
+    cfg = HybridTinyConfig(vocab_size=64, hidden_size=32, pattern="MA", depth=2, num_attention_heads=4, max_seq_length=16, mamba_head_dim=16,
+                           mamba_state_dim=8, mamba_chunk_size=8, mamba_groups=2, mla_low_rank=True, mla_q_lora_rank=16, mla_kv_lora_rank=16,
+                           mla_qk_nope_head_dim=8, mla_qk_rope_head_dim=4, mla_v_head_dim=8, ffn_hidden_size=48, position_embedding=False)
+    torch.manual_seed(0)
+    m = HybridTinyLM(cfg)
+    TP.tensor_parallelize_ffn(m, st.tp_group, sequence_parallel=True)
+    with pytest.raises(ValueError, match="not head- / expert-parallel"):
+        TP.enable_sequence_parallel(m, st.tp_group)
+    m2 = HybridTinyLM(cfg)
+    TP.tensor_parallelize_mixers(m2, st.tp_group)
+    TP.tensor_parallelize_ffn(m2, st.tp_group, sequence_parallel=False)
+    with pytest.raises(ValueError, match="sequence_parallel=True"):
+        TP.enable_sequence_parallel(m2, st.tp_group)
+    assert getattr(m2, "sp_group", None) is None
+    x = torch.randn(3, 5, requires_grad=True)
+    y = TP.scale_grad(x, 0.25)
+    assert torch.equal(y, x)
+    y.sum().backward()
+    assert torch.allclose(x.grad, torch.full_like(x, 0.25))
+    z = torch.full((4,), float(rank + 1), requires_grad=True)
+    (TP.mean_grad_over_tp(z, st.tp_group) * (rank + 1.0)).sum().backward()       # local gradients 1 and 2: every rank ends with 1.5
+    assert torch.allclose(z.grad, torch.full((4,), 1.5))
+    # leaving the region hands back the local slice of an identical gradient; entering it gathers the slices' gradients
+    full = torch.arange(8.0).reshape(1, 8, 1).requires_grad_()
+    sl = TP.enter_sequence_parallel(full, st.tp_group, 1)
+    assert sl.shape == (1, 4, 1) and float(sl[0, 0, 0]) == 4.0 * rank
+    back = TP.leave_sequence_parallel(sl * 2.0, st.tp_group, 1)
+    assert torch.equal(back.detach(), full.detach() * 2.0)
+    back.sum().backward()
+    assert torch.allclose(full.grad, torch.full_like(full, 2.0))
+    return True
+
+
+def test_sequence_parallel_refusals_and_gradient_helpers():
+    assert all(run_ranks(_sp_refusals_rank, 2))
+
+
 def _ep_rank(rank, world):
     from cppmega_mlx_b200.nn.moe import MoE, MoEConfig
     from cppmega_mlx_b200.parallel import ep as EP
