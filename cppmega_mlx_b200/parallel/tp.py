@@ -530,7 +530,7 @@ def _shard_m2rnn(full, group):
 
 
 class Mamba3TP(nn.Module):
-    """Head-parallel Mamba3 mixer (training / prefill without a decode cache).  Rank r holds ``nheads / tp`` heads and ``ngroups / tp``
+    """Head-parallel Mamba3 mixer (training, prefill and cached decode).  Rank r holds ``nheads / tp`` heads and ``ngroups / tp``
     B/C groups: its slices of z, x, B, C, dd_A and trap rows of the packed projection, of the conv channels, the norm weights, D and
     the columns of ``out_proj`` (row-parallel, partial outputs all-reduced).  Two pieces stay replicated in a parameter of their own
     (``in_proj_rep``: a matrix-wise optimizer must see identical matrices on every rank): the angle rows, which every head uses,
@@ -593,9 +593,85 @@ class Mamba3TP(nn.Module):
             **{n: _index_map(n, 1, _span(g0, Gl), G) for n in ("B_norm_weight", "C_norm_weight", "B_bias", "C_bias")}}
         self.train(full.training)
 
+    # -- decode cache ------------------------------------------------------------------------------
+    def mamba_state_shapes_per_request(self):
+        """Per-request shapes of this rank's share of the decode cache: the phases of its ``ngroups / tp`` groups (the only phases
+        its B and C rotate with), and state, last key and last value of its ``nheads / tp`` heads."""
+        c = self.config
+        return (self.Gl, self.R), (self.Hl, c.headdim, c.d_state), (1, self.Hl, c.d_state), (self.Hl, c.headdim)
+
+    def zero_cache_state(self, batch: int, *, dtype=torch.float32, device=None):
+        from ..nn.mamba3 import Mamba3CacheState
+        if batch <= 0:
+            raise ValueError("batch must be positive")
+        z = lambda sh: torch.zeros(batch, *sh, dtype=dtype, device=device)
+        a, s, k, v = self.mamba_state_shapes_per_request()
+        return Mamba3CacheState(z(a), z(s), z(k), z(v), z((self.config.d_conv - 1, self.conv_weight.shape[0])))
+
+    def _forward_cached(self, hidden_states, cache, return_cache):
+        """Prefill that leaves a cache behind, and the continuation from one (any number of new tokens).  Every cached quantity is
+        this rank's share only — nothing of the cache crosses the group — and the result equals the unsharded block run over the whole
+        sequence at once (``nn/mamba3.py`` ``Mamba3Block.forward``, the path taken with ``cache`` set)."""
+        import math
+        import torch.nn.functional as F
+        from ..nn import mamba3 as M3
+        c, g = self.config, self.tp_group
+        b, s, _ = hidden_states.shape
+        G, R, Hl, Gl, d_l, dbc_l, n_own, N = c.ngroups, self.R, self.Hl, self.Gl, self.d_l, self.dbc_l, self.n_own, c.d_state
+        n_rep, conv_ch = G + R, d_l + 2 * dbc_l
+        W = torch.cat([self.in_proj_rep.weight, self.in_proj.weight], 0)
+        proj = mixed_column_linear(hidden_states, W, n_rep, g)
+        rep = copy_to_tp(proj[..., :n_rep], g)
+        phase_dd, angles = rep[..., :G].float(), rep[..., G:].float()
+        prefix = cache.conv if cache is not None else None
+        head, x, BC, tail_sl = ops.packed_split_conv_silu(proj, n_rep + d_l, conv_ch, d_l, self.conv_weight, self.conv_bias, prefix=prefix)
+        raw = proj[..., n_rep + d_l:n_rep + d_l + conv_ch]                      # pre-conv inputs: the next call's conv window
+        z = head[..., n_rep:]
+        rep_bias = copy_to_tp(self.rep_dt_bias, g).float()
+        lo, g0 = self.tp_rank * Hl, self.tp_rank * Gl
+        dd_rest, dd_A, trap = torch.split(tail_sl.float(), [Hl - n_own, Hl, Hl], dim=-1)
+        dd_dt = torch.cat([phase_dd[..., lo:lo + n_own], dd_rest], -1) if n_own else dd_rest
+        dt_bias = torch.cat([rep_bias[lo:lo + n_own], self.dt_bias[n_own:].float()]) if n_own else self.dt_bias.float()
+        dt = F.softplus(dd_dt + dt_bias)                                                                  # [B,S,Hl]
+        phase_dt = F.softplus(phase_dd[..., g0:g0 + Gl] + rep_bias[g0:g0 + Gl])                          # [B,S,Gl]
+        xh, zh = x.reshape(b, s, Hl, c.headdim), z.reshape(b, s, Hl, c.headdim)
+        Bm, Cm = BC[..., :dbc_l].reshape(b, s, Gl, N), BC[..., dbc_l:].reshape(b, s, Gl, N)
+        Bn = M3._rms_norm_last(Bm) * self.B_norm_weight[0].to(Bm.dtype) + self.B_bias[0].to(Bm.dtype)
+        Cn = M3._rms_norm_last(Cm) * self.C_norm_weight[0].to(Cm.dtype) + self.C_bias[0].to(Cm.dtype)
+        Bg = Bn * M3.heads_to_group_scale(M3.compute_trapezoidal_scale(dt, trap), Gl)[..., None].to(Bn.dtype)
+        ang_cum = torch.cumsum((angles[:, :, None, :] * phase_dt[..., None]).transpose(1, 3), dim=-1).transpose(1, 3)     # [B,S,Gl,R]
+        if cache is not None:
+            ang_cum = ang_cum + cache.angle_dt[:, None].float()
+        Bg, Cg = M3.apply_rope_on_state_dim(Bg, ang_cum), M3.apply_rope_on_state_dim(Cn, ang_cum)
+        A = torch.clamp(-F.softplus(dd_A), max=-c.A_floor)
+        state0 = cache.ssm if cache is not None else None
+        if cache is not None and s > 0:
+            # the cached state lacks the last token's look-ahead term (its successor was unknown then); the successor's step size
+            # completes it: x_last ⊗ B_last · dt[0]·(1 − σ(trap[0]))
+            late = M3.heads_to_group_scale(dt[:, :1] * (1.0 - torch.sigmoid(trap[:, :1])), Gl)[:, 0]                      # [B,Gl]
+            k_mean = cache.k.float().mean(1) * late.repeat_interleave(Hl // Gl, dim=1)[..., None]                         # [B,Hl,N]
+            state0 = (state0.float() + cache.v.float()[..., None] * k_mean[:, :, None, :]).to(state0.dtype)
+        y, h = ops.mamba3_scan(xh, Bg, Cg, zh, A, dt, self.D, state0, chunk_size=c.chunk_size)
+        out = reduce_from_tp(self.out_proj(y.reshape(b, s, d_l)), g)
+        if not return_cache:
+            return out, h
+        if s == 0:
+            return out, (cache if cache is not None else self.zero_cache_state(b, dtype=hidden_states.dtype, device=hidden_states.device))
+        k_last = M3.apply_rope_on_state_dim(Bn[:, -1:], ang_cum[:, -1:])[:, 0]                                            # [B,Gl,N]
+        k_last = k_last.repeat_interleave(Hl // Gl, dim=1)[:, None]                                                       # [B,1,Hl,N]
+        hist = c.d_conv - 1
+        src = raw if prefix is None else torch.cat([prefix.to(raw.dtype), raw], dim=1)
+        conv_state = src[:, -hist:] if src.shape[1] >= hist else F.pad(src, (0, 0, hist - src.shape[1], 0))
+        return out, M3.Mamba3CacheState(angle_dt=torch.remainder(ang_cum[:, -1], 2 * math.pi).to(hidden_states.dtype), ssm=h,
+                                        k=k_last.to(hidden_states.dtype), v=xh[:, -1], conv=conv_state.contiguous())
+
     def forward(self, hidden_states, *, h0=None, cache=None, return_cache: bool = False, cache_out=None):
-        if cache is not None or return_cache or h0 is not None:
-            raise NotImplementedError("the head-parallel Mamba3 mixer has no decode cache; gather the model for serving")
+        if h0 is not None:
+            raise NotImplementedError("the head-parallel Mamba3 mixer takes its initial state through a cache, not h0")
+        if cache is not None or return_cache:
+            if self.sequence_parallel:
+                raise NotImplementedError("decode caches and a sequence-parallel residual stream do not combine: serve without it")
+            return self._forward_cached(hidden_states, cache, return_cache)      # cache_out is a hint of the one-kernel step; unused here
         import torch.nn.functional as F
         from ..nn import mamba3 as M3
         c, g = self.config, self.tp_group

@@ -142,6 +142,78 @@ def test_tensor_parallel_mixers_match_single_rank():
     assert all(run_ranks(_tp_mixers_rank, 2))
 
 
+def _tp_decode_rank(rank, world):
+    """Cached decode on the head- / expert-parallel stack: prefill + one-token steps through a ``DecodeSession`` give the logits the
+    unsharded model gives through its own session (each rank keeps its own share of every cache), and the Mamba3 mixer alone
+    continues from a cache in chunks of several tokens as well.  The comparison is piece by piece: the trapezoid rule looks one
+    token ahead, so the last position of a piece differs from an uninterrupted run in both forms alike, and the state catches up
+    when the next token arrives."""
+    from cppmega_mlx_b200.inference import DecodeSession
+    from cppmega_mlx_b200.models.hybrid_lm import HybridTinyConfig, HybridTinyLM
+    from cppmega_mlx_b200.parallel import tp as TP
+    st = PS.init_parallel_state(tp=world)
+    cfg = HybridTinyConfig(vocab_size=64, hidden_size=32, pattern="MAER", depth=4, num_attention_heads=4, max_seq_length=16, mamba_head_dim=16,
+                           mamba_state_dim=8, mamba_chunk_size=8, mamba_groups=2, moe_num_experts=4, moe_top_k=2, moe_expert_hidden_size=16,
+                           moe_shared_expert_hidden_size=16, m2rnn_k_head_dim=4, m2rnn_v_head_dim=4, m2rnn_num_q_heads=1, m2rnn_num_k_heads=2,
+                           m2rnn_num_v_heads=4, m2rnn_num_f_heads=4, m2rnn_num_g_heads=4, mla_low_rank=True, mla_q_lora_rank=16,
+                           mla_kv_lora_rank=16, mla_qk_nope_head_dim=8, mla_qk_rope_head_dim=4, mla_v_head_dim=8, ffn_hidden_size=48,
+                           position_embedding=False)
+    torch.manual_seed(0)
+    full = HybridTinyLM(cfg).eval()
+    with torch.no_grad():
+        for p in full.parameters():
+            if p.dim() == 2 and float(p.abs().sum()) == 0:
+                p.normal_(std=0.05)
+    ids = torch.randint(0, 64, (2, 12))
+    pieces = [slice(0, 7)] + [slice(t, t + 1) for t in range(7, 12)]
+    with torch.no_grad():
+        s0 = DecodeSession(full)
+        ref = torch.cat([s0.forward(ids[:, p]) for p in pieces], 1)
+    tpm = HybridTinyLM(cfg).eval()
+    tpm.load_state_dict(full.state_dict())
+    assert TP.tensor_parallelize_mixers(tpm, st.tp_group)["mamba3"] == 1
+    TP.tensor_parallelize_ffn(tpm, st.tp_group)
+    with torch.no_grad():
+        sess = DecodeSession(tpm)
+        got = torch.cat([sess.forward(ids[:, p]) for p in pieces], 1)
+    assert torch.allclose(got, ref, atol=3e-5), float((got - ref).abs().max())
+    mam = tpm.layers[0].block
+    assert isinstance(mam, TP.Mamba3TP)
+    c = mam.config
+    assert mam.mamba_state_shapes_per_request() == ((1, mam.R), (2, c.headdim, c.d_state), (1, 2, c.d_state), (2, c.headdim))
+    x = torch.randn(2, 11, 32)
+    with torch.no_grad():
+        blk = full.layers[0].block
+        whole, _ = blk(x)
+        w0, wc = blk(x[:, :4], return_cache=True)
+        w1, wc = blk(x[:, 4:5], cache=wc, return_cache=True)
+        w2, wc = blk(x[:, 5:9], cache=wc, return_cache=True)
+        want = torch.cat([w0, w1, w2, blk(x[:, 9:], cache=wc)[0]], 1)
+        a, cache = mam(x[:, :4], return_cache=True)
+        assert cache.ssm.shape == (2, 2, c.headdim, c.d_state) and cache.angle_dt.shape == (2, 1, mam.R) and cache.conv.shape[1] == c.d_conv - 1
+        b, cache = mam(x[:, 4:5], cache=cache, return_cache=True)          # one token
+        d, cache = mam(x[:, 5:9], cache=cache, return_cache=True)          # a chunk of several
+        e, _ = mam(x[:, 9:], cache=cache)                                  # the last piece leaves no cache behind
+        z0 = mam.zero_cache_state(2)
+        assert z0.k.shape == (2, 1, 2, c.d_state) and z0.conv.shape == (2, c.d_conv - 1, mam.conv_weight.shape[0])
+    got = torch.cat([a, b, d, e], 1)
+    assert torch.allclose(got, want, atol=3e-5), float((got - want).abs().max())
+    assert torch.allclose(got[:, -1], whole[:, -1], atol=3e-5) and torch.allclose(got[:, :3], whole[:, :3], atol=3e-5)
+    lo = rank * 2                                                       # the caches are slices of the unsharded block's cache
+    assert torch.allclose(cache.ssm, wc.ssm[:, lo:lo + 2], atol=3e-5) and torch.allclose(cache.k, wc.k[:, :, lo:lo + 2], atol=3e-5)
+    assert torch.allclose(cache.angle_dt, wc.angle_dt[:, rank:rank + 1], atol=3e-5)      # group r turns with the phase of head r
+    with pytest.raises(NotImplementedError, match="through a cache"):
+        mam(x, h0=torch.zeros(2, 2, c.headdim, c.d_state))
+    mam.sequence_parallel = True
+    with pytest.raises(NotImplementedError, match="do not combine"):
+        mam(x, return_cache=True)
+    return True
+
+
+def test_tensor_parallel_cached_decode_matches_full_forward():
+    assert all(run_ranks(_tp_decode_rank, 2))
+
+
 def _sp_mixers_rank(rank, world, aux, batch):
     """The same stack with a sequence-parallel residual stream: every rank holds half of the tokens between the blocks; output,
     the gradient of the embeddings (entry of the region), the norm weights (summed over the group afterwards) and the sliced /
