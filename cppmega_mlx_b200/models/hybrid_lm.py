@@ -446,6 +446,12 @@ class HybridTinyLM(nn.Module):
                               state: HybridDecodeState | None = None, position_offset: int | None = None):
         if input_ids.dim() != 2:
             raise ValueError(f"input_ids must be shaped (B, S), got {tuple(input_ids.shape)}")
+        cp_group = getattr(self, "cp_group", None)     # set by parallel.cp.enable_context_parallel: input_ids are this rank's slice
+        if cp_group is not None and kv_cache is None and state is None:
+            from ..parallel.cp import context_parallel_hidden_states
+            return context_parallel_hidden_states(self, input_ids, cp_group, structure_ids=structure_ids, dep_levels=dep_levels,
+                                                  ast_depth_ids=ast_depth_ids, sibling_index_ids=sibling_index_ids,
+                                                  node_type_ids=node_type_ids, document_ids=document_ids)
         cfg = self.config
         b, s = input_ids.shape
         if kv_cache is not None and document_ids is not None:

@@ -145,7 +145,9 @@ class PretrainingStep:
         # a sequence-parallel model sums some gradients over its tensor-parallel group after the backward pass
         # (parallel.tp.allreduce_sequence_parallel_grads), so they are not final when autograd produces them
         sp = getattr(self.model, "sp_group", None) is not None
-        if (self.state.micro_step + 1) % self.grad_accum_steps == 0 and self.max_grad_norm is None and not sp:
+        # a context-parallel backward pass waits on its neighbours layer by layer (parallel.cp): no collectives in between
+        cp = getattr(self.model, "cp_group", None) is not None
+        if (self.state.micro_step + 1) % self.grad_accum_steps == 0 and self.max_grad_norm is None and not sp and not cp:
             arm = getattr(self.optimizer, "arm_overlap", None)      # sharded optimizers start reducing a layer once its gradients are final
             if arm is not None and self.nonfinite_policy is None:
                 arm()

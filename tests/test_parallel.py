@@ -494,3 +494,109 @@ def test_expert_parallel_zero1_trains_and_keeps_replicas_in_sync():
     out = run_ranks(_ep_zero1_rank, 2)
     for losses, spread, n_local in out:
         assert losses[-1] < losses[0] and spread == 0.0 and n_local == 2      # 4 experts over 2 ranks; dense weights identical everywhere
+
+
+class _CatCache:
+    """A KV cache that grows by concatenation, so autograd runs through it (the serving cache writes in place)."""
+    static = False
+
+    def __init__(self):
+        self.rows, self.offset = {}, 0
+
+    def position(self, layer_idx):
+        return self.offset
+
+    def _grow(self, key, t):
+        if t is None:
+            return None
+        self.rows[key] = t if key not in self.rows else torch.cat([self.rows[key], t], 1)
+        return self.rows[key]
+
+    def update_and_fetch(self, layer_idx, k, v):
+        return self._grow((layer_idx, "k"), k), self._grow((layer_idx, "v"), v)
+
+    def update_and_fetch_latent(self, layer_idx, latent, idx_k):
+        return self._grow((layer_idx, "l"), latent), self._grow((layer_idx, "i"), idx_k)
+
+
+def _cp_rank(rank, world):
+    """Context parallelism: the sequence split over the ranks (weights replicated) gives the logits, the loss and — after averaging
+    over the group — the parameter gradients of the single-process model evaluated piecewise with the pieces cut at the slice
+    boundaries (prefill, then continue from the cache; the graph runs through the cache and the recurrent states)."""
+    from cppmega_mlx_b200.models.hybrid_lm import HybridDecodeState, HybridTinyConfig, HybridTinyLM
+    from cppmega_mlx_b200.parallel import cp as CP
+    st = PS.init_parallel_state(tp=1)
+    group = torch.distributed.group.WORLD
+    for pattern, low_rank in (("MARE", True), ("AMRM", False)):
+        cfg = HybridTinyConfig(vocab_size=64, hidden_size=32, pattern=pattern, depth=4, num_attention_heads=4, max_seq_length=24, mamba_head_dim=16,
+                               mamba_state_dim=8, mamba_chunk_size=4, mamba_groups=2, moe_num_experts=4, moe_top_k=2, moe_expert_hidden_size=16,
+                               moe_shared_expert_hidden_size=16, m2rnn_k_head_dim=4, m2rnn_v_head_dim=4, m2rnn_num_q_heads=1, m2rnn_num_k_heads=2,
+                               m2rnn_num_v_heads=4, m2rnn_num_f_heads=4, m2rnn_num_g_heads=4, mla_low_rank=low_rank, mla_q_lora_rank=16,
+                               mla_kv_lora_rank=16, mla_qk_nope_head_dim=8, mla_qk_rope_head_dim=4, mla_v_head_dim=8, ffn_hidden_size=48,
+                               position_embedding=not low_rank, moe_aux_loss_coeff=0.0)
+        torch.manual_seed(0)
+        model = HybridTinyLM(cfg)
+        with torch.no_grad():
+            for p in model.parameters():
+                if p.dim() == 2 and float(p.abs().sum()) == 0:
+                    p.normal_(std=0.05)
+        S = 6 * world
+        ids = torch.randint(0, 64, (2, S + 1))
+        inp, tgt = ids[:, :-1], ids[:, 1:]
+        ce = torch.nn.functional.cross_entropy
+        # single process, piecewise with autograd through cache and states
+        kv, state, outs = _CatCache(), HybridDecodeState(), []
+        n = S // world
+        for r in range(world):
+            outs.append(model(inp[:, r * n:(r + 1) * n], kv_cache=kv, state=state))
+            kv.offset += n
+        ref = torch.cat(outs, 1)
+        ref_loss = ce(ref.reshape(-1, 64), tgt.reshape(-1))
+        ref_loss.backward()
+        ref_g = {k: p.grad.clone() for k, p in model.named_parameters() if p.grad is not None}
+        model.zero_grad()
+        # the pieces on different ranks
+        mine = CP.shard_sequence(inp, group)
+        assert mine.shape == (2, n) and torch.equal(mine, inp[:, rank * n:(rank + 1) * n])
+        logits = CP.context_parallel_forward(model, mine, group)
+        assert torch.allclose(logits, ref.detach()[:, rank * n:(rank + 1) * n], atol=3e-5), (pattern, float((logits - ref.detach()[:, rank * n:(rank + 1) * n]).abs().max()))
+        loss = ce(logits.reshape(-1, 64), CP.shard_sequence(tgt, group).reshape(-1))
+        loss.backward()
+        CP.allreduce_context_parallel_grads(model, group)
+        total = loss.detach().clone()
+        torch.distributed.all_reduce(total)
+        assert abs(float(total) / world - float(ref_loss)) < 1e-5
+        got = {k: p.grad for k, p in model.named_parameters()}
+        assert set(ref_g) <= set(got)
+        for k, want in ref_g.items():
+            assert torch.allclose(got[k], want, atol=3e-5), (pattern, k, float((got[k] - want).abs().max()))
+    # the switch on the model: loss functions and the training step then work on the rank's part of the batch as they are
+    from cppmega_mlx_b200.data.batch import LMTokenBatch
+    from cppmega_mlx_b200.training.loss import make_loss_fn
+    CP.enable_context_parallel(model, group)
+    assert torch.allclose(model(mine), logits.detach(), atol=1e-6)
+    part = CP.shard_batch(LMTokenBatch(ids), group)
+    assert torch.equal(part.inputs, mine) and torch.equal(part.targets, CP.shard_sequence(tgt, group))
+    model.zero_grad()
+    out = make_loss_fn(backend="cross_entropy")(model, part)
+    assert abs(float(out.loss) - float(loss)) < 1e-5
+    out.loss.backward()
+    CP.allreduce_context_parallel_grads(model, group)
+    for k, want in ref_g.items():
+        assert torch.allclose(dict(model.named_parameters())[k].grad, want, atol=3e-5), k
+    CP.disable_context_parallel(model)
+    assert model(inp).shape == (2, S, 64)
+    with pytest.raises(ValueError, match="sequence length to divide"):
+        CP.shard_batch(LMTokenBatch(ids[:, :-1]), group)
+    # refusals: a sequence that does not divide, layers without a state to continue from
+    with pytest.raises(ValueError, match="sequence length to divide"):
+        CP.shard_sequence(torch.zeros(1, 2 * world + 1), group)
+    eng = HybridTinyLM(HybridTinyConfig(vocab_size=64, hidden_size=32, pattern="AN", depth=2, num_attention_heads=4, max_seq_length=24))
+    with pytest.raises(NotImplementedError, match="continue from a state"):
+        CP.context_parallel_forward(eng, mine, group)
+    return True
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_context_parallel_matches_piecewise_single_rank(world):
+    assert all(run_ranks(_cp_rank, world))
