@@ -219,6 +219,26 @@ class CausalSelfAttention(nn.Module):
         self.v_proj = Linear(c.d_model, c.kv_proj_dim, bias=c.bias)
         self.sparse_kv_proj = Linear(c.d_model, c.kv_proj_dim, bias=c.bias) if c.mode == "dsa" else None
         self.out_proj = Linear(c.q_proj_dim, c.d_model, bias=c.bias)
+        # head parallelism (parallel.tp.tensor_parallelize_mixers): this module then holds 1/tp of the query and key/value heads;
+        # the input's gradient and the output projection's partial products are summed over the group.
+        self.tp_group = None
+        self.sequence_parallel = False     # with tp_group: input / output are this rank's slice of the tokens
+        self.sp_dim = 1                    # … along the sequence (1) or the batch (0)
+
+    def _enter(self, x):
+        if self.tp_group is None:
+            return x
+        from ..parallel.tp import copy_to_tp, gather_sequence
+        # every product below is this rank's heads only, so the gather's backward (a reduce-scatter) adds up the partial input
+        # gradients by itself; without sequence parallelism an identity with an all-reduce in backward does
+        return gather_sequence(x, self.tp_group, self.sp_dim) if self.sequence_parallel else copy_to_tp(x, self.tp_group)
+
+    def _out(self, o):
+        y = self.out_proj(o)
+        if self.tp_group is None:
+            return y
+        from ..parallel.tp import reduce_from_tp, reduce_scatter_sequence
+        return reduce_scatter_sequence(y, self.tp_group, self.sp_dim) if self.sequence_parallel else reduce_from_tp(y, self.tp_group)
 
     def _rope(self, x, offset: int):
         c = self.config
@@ -235,7 +255,7 @@ class CausalSelfAttention(nn.Module):
         c = self.config
         b = x.shape[0]
         cos, sin = cache.rope(c.q_head_dim, c.rope_theta, c.rope_scaling())    # [B, D/2]: one row per sequence
-        xt = x.transpose(0, 1)                                                 # [1, B, d]: the batch plays the sequence axis
+        xt = self._enter(x).transpose(0, 1)                                    # [1, B, d]: the batch plays the sequence axis
         rope = (lambda t: ops.apply_rope(t, cos, sin)) if c.use_rope else (lambda t: t)
         q = rope(self.q_proj(xt).view(1, b, c.num_q_heads, c.q_head_dim))[0]   # [B, H, D]
         lengths = cache.lengths()
@@ -255,7 +275,7 @@ class CausalSelfAttention(nn.Module):
             vv = cache.write_b(layer_idx, self.v_proj(xt).view(b, 1, c.kv_heads, c.q_head_dim))
             out = DA.decode_attention(q, cache.attention_rows(kk, c.kv_heads, c.q_head_dim), cache.attention_rows(vv, c.kv_heads, c.q_head_dim),
                                       cache.table(), lengths, scale=scale, max_keys=cache.capacity)
-        return self.out_proj(out.reshape(b, 1, c.q_proj_dim))
+        return self._out(out.reshape(b, 1, c.q_proj_dim))
 
     def forward(self, hidden_states: torch.Tensor, mask: torch.Tensor | str | None = "causal", *, kv_cache=None,
                 layer_idx: int = 0, sinks: torch.Tensor | None = None) -> torch.Tensor:
@@ -265,6 +285,11 @@ class CausalSelfAttention(nn.Module):
             if s != 1 or isinstance(mask, torch.Tensor) or sinks is not None:
                 raise ValueError("a static decode cache serves one-token steps without an explicit mask or sinks")
             return self._static_step(hidden_states, kv_cache, layer_idx)
+        if self.tp_group is not None:
+            if self.sequence_parallel and kv_cache is not None:
+                raise NotImplementedError("sequence-parallel attention has no cache path")
+            hidden_states = self._enter(hidden_states)
+            b, s, _ = hidden_states.shape
         offset = kv_cache.position(layer_idx) if kv_cache is not None else 0
         q = self._rope(self.q_proj(hidden_states).view(b, s, c.num_q_heads, c.q_head_dim), offset)
         if c.mode == "dsa":
@@ -280,7 +305,7 @@ class CausalSelfAttention(nn.Module):
             else:
                 idx = causal_sparse_indices(b, s, c.kv_heads, min(c.sparse_topk, s), device=hidden_states.device)
             out, _ = ops.sparse_mla_attention(q, kv, idx)
-            return self.out_proj(out.reshape(b, s, c.q_proj_dim))
+            return self._out(out.reshape(b, s, c.q_proj_dim))
         k = self._rope(self.k_proj(hidden_states).view(b, s, c.kv_heads, c.q_head_dim), offset)
         v = self.v_proj(hidden_states).view(b, s, c.kv_heads, c.q_head_dim)
         if kv_cache is not None:
@@ -292,7 +317,7 @@ class CausalSelfAttention(nn.Module):
             if DA.kernel_supported(q[:, 0], k, v, None):   # decode step on the GPU: split-KV tensor-core kernel over the cache
                 lengths = torch.full((b,), klen, dtype=torch.int32, device=q.device)
                 out = DA.decode_attention(q[:, 0], k, v, None, lengths, scale=c.q_head_dim ** -0.5, max_keys=klen)
-                return self.out_proj(out.reshape(b, s, c.q_proj_dim))
+                return self._out(out.reshape(b, s, c.q_proj_dim))
         qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
         if plain_causal and c.sliding_window is None and klen == s and sinks is None:
             out = dense_attention(qh, kh, vh, is_causal=True)
@@ -305,4 +330,4 @@ class CausalSelfAttention(nn.Module):
                     extra = extra[None]
                 m = m & extra
             out = dense_attention(qh, kh, vh, mask=m, sinks=sinks)
-        return self.out_proj(out.transpose(1, 2).reshape(b, s, c.q_proj_dim))
+        return self._out(out.transpose(1, 2).reshape(b, s, c.q_proj_dim))

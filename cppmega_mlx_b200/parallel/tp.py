@@ -416,6 +416,39 @@ def _shard_mla(full, group):
     return loc
 
 
+def _shard_attention(full, group):
+    """Head-parallel copy of a ``CausalSelfAttention`` (plain q / k / v heads): rank r holds ``num_q_heads / tp`` query heads with the
+    ``kv_heads / tp`` key / value heads they read (grouped-query groups stay together), i.e. row slices of the q / k / v (and shared
+    sparse key-value) projections and the matching columns of the output projection."""
+    import dataclasses
+    from ..nn.attention import CausalSelfAttention
+    tp, r = _world(group), dist.get_rank(group)
+    c = full.config
+    if c.num_q_heads % tp or c.kv_heads % tp:
+        raise ValueError(f"tensor-parallel size {tp} must divide the {c.num_q_heads} query and {c.kv_heads} key/value heads")
+    if c.bias:
+        raise ValueError("head-parallel attention with projection biases is not supported")
+    Hq, Hkv, D = c.num_q_heads // tp, c.kv_heads // tp, c.q_head_dim
+    lc = dataclasses.replace(c, num_q_heads=Hq, num_kv_heads=None if c.num_kv_heads is None else Hkv, head_dim=D)
+    dev, dt = full.out_proj.weight.device, full.out_proj.weight.dtype
+    with torch.device(dev):
+        loc = CausalSelfAttention(lc).to(dt)
+    maps = {}
+    with torch.no_grad():
+        for name, n in (("q_proj", Hq * D), ("k_proj", Hkv * D), ("v_proj", Hkv * D), ("sparse_kv_proj", Hkv * D)):
+            src = getattr(full, name)
+            if src is None:
+                continue
+            getattr(loc, name).weight.copy_(_rows(src.weight, r * n, n))
+            maps[name + ".weight"] = _index_map(name + ".weight", 0, _span(r * n, n), n * tp)
+        loc.out_proj.weight.copy_(full.out_proj.weight[:, r * Hq * D:(r + 1) * Hq * D])
+        maps["out_proj.weight"] = _index_map("out_proj.weight", 1, _span(r * Hq * D, Hq * D), Hq * D * tp)
+    loc.tp_group = group
+    loc.tp_index_maps = maps
+    loc.train(full.training)
+    return loc
+
+
 def _shard_moe(full, group):
     """Expert-tensor-parallel copy of an ``MoE``: this rank keeps a contiguous slice of the routed experts; router and shared expert
     are replicated (they see the same tokens on every rank of the group)."""
@@ -722,23 +755,32 @@ def _shard_mamba3(full, group):
     return Mamba3TP(full, group)
 
 
-def tensor_parallelize_mixers(model: nn.Module, group, *, kinds=("mla", "moe", "m2rnn", "mamba3")) -> dict[str, int]:
-    """Replace the attention (low-rank MLA), MoE, M2RNN and Mamba3 mixers under ``model`` by their head- / expert-parallel forms (in
-    place); returns how many of each were replaced.  Inputs and outputs of every mixer stay replicated over the group (the partial
+def tensor_parallelize_mixers(model: nn.Module, group, *, kinds=("mla", "attention", "moe", "m2rnn", "mamba3")) -> dict[str, int]:
+    """Replace the attention (low-rank MLA, or plain q / k / v heads), MoE, M2RNN and Mamba3 mixers under ``model`` by their head- /
+    expert-parallel forms (in place); returns how many of each were replaced (kinds that replaced nothing and are not among the
+    four original ones are left out of the result).  Inputs and outputs of every mixer stay replicated over the group (the partial
     output products are all-reduced), so it composes with ``tensor_parallelize_ffn``.  A Mamba3 block whose head / group counts
-    the group size does not divide stays replicated."""
+    the group size does not divide, and a plain attention block whose head counts it does not divide or that has biases, stay
+    replicated."""
     from ..nn.m2rnn import M2RNNMixer
     from ..nn.mla import MLAAttention
     from ..nn.moe import MoE
     from ..nn.mamba3 import Mamba3Block
+    from ..nn.attention import CausalSelfAttention
     done = {"mla": 0, "moe": 0, "m2rnn": 0, "mamba3": 0}
     if _world(group) == 1:
         return done
+    tp = _world(group)
     for parent in list(model.modules()):
         for name, child in list(parent.named_children()):
             if isinstance(child, MLAAttention) and "mla" in kinds and child.tp_group is None:
                 setattr(parent, name, _shard_mla(child, group))
                 done["mla"] += 1
+            elif isinstance(child, CausalSelfAttention) and "attention" in kinds and child.tp_group is None:
+                c = child.config
+                if c.num_q_heads % tp == 0 and c.kv_heads % tp == 0 and not c.bias:
+                    setattr(parent, name, _shard_attention(child, group))
+                    done["attention"] = done.get("attention", 0) + 1
             elif isinstance(child, MoE) and "moe" in kinds and child.tp_group is None and child.ep_size == 1:
                 setattr(parent, name, _shard_moe(child, group))
                 done["moe"] += 1

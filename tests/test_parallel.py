@@ -600,3 +600,80 @@ def _cp_rank(rank, world):
 @pytest.mark.parametrize("world", [2, 3])
 def test_context_parallel_matches_piecewise_single_rank(world):
     assert all(run_ranks(_cp_rank, world))
+
+
+def _tp_plain_attention_rank(rank, world, mode):
+    """Plain q / k / v attention (grouped-query, and the shared sparse key-value form) head-parallel on two ranks: forward, input
+    and parameter gradients, the sequence-parallel stack, and cached decode reproduce the single-process model."""
+    from cppmega_mlx_b200.inference import DecodeSession
+    from cppmega_mlx_b200.models.hybrid_lm import HybridTinyConfig, HybridTinyLM
+    from cppmega_mlx_b200.nn.attention import CausalSelfAttention
+    from cppmega_mlx_b200.parallel import tp as TP
+    st = PS.init_parallel_state(tp=world)
+    cfg = HybridTinyConfig(vocab_size=64, hidden_size=32, pattern="AA", depth=2, num_attention_heads=4, num_attention_kv_heads=2, attention_mode=mode,
+                           attention_sparse_topk=5, max_seq_length=16, ffn_hidden_size=48, position_embedding=False)
+    torch.manual_seed(0)
+    full = HybridTinyLM(cfg)
+    with torch.no_grad():
+        for p in full.parameters():
+            if p.dim() == 2 and float(p.abs().sum()) == 0:
+                p.normal_(std=0.05)
+    ids = torch.randint(0, 64, (2, 12))
+    ref = full(ids)
+    ref.square().mean().backward()
+    ref_g = {n: p.grad.clone() for n, p in full.named_parameters() if p.grad is not None}
+    full.zero_grad()
+
+    def sharded(sp):
+        m = HybridTinyLM(cfg)
+        m.load_state_dict(full.state_dict())
+        done = TP.tensor_parallelize_mixers(m, st.tp_group)
+        assert done["attention"] == 2 and done["mla"] == 0, done
+        assert TP.tensor_parallelize_ffn(m, st.tp_group, sequence_parallel=sp) == 2
+        if sp:
+            TP.enable_sequence_parallel(m, st.tp_group)
+        return m
+    r = rank
+    kv_name = "sparse_kv_proj" if mode == "dsa" else "k_proj"
+    for sp in (False, True):
+        m = sharded(sp)
+        blk = m.layers[0].block
+        assert isinstance(blk, CausalSelfAttention) and blk.config.num_q_heads == 2 and blk.config.kv_heads == 1 and blk.config.q_head_dim == 8
+        assert set(blk.tp_index_maps) >= {"q_proj.weight", "out_proj.weight", kv_name + ".weight"}
+        out = m(ids)
+        assert torch.allclose(out, ref.detach(), atol=3e-5), (sp, float((out - ref).abs().max()))
+        out.square().mean().backward()
+        if sp:
+            TP.allreduce_sequence_parallel_grads(m)
+        g = {n: p.grad for n, p in m.named_parameters() if p.grad is not None}
+        for n in ("token_embedding.weight", "norm.weight", "layers.1.norm.weight"):
+            assert torch.allclose(g[n], ref_g[n], atol=3e-5), (sp, n, float((g[n] - ref_g[n]).abs().max()))
+        a = "layers.1.block."
+        assert torch.allclose(g[a + "q_proj.weight"], ref_g[a + "q_proj.weight"][r * 16:(r + 1) * 16], atol=3e-5)
+        assert torch.allclose(g[a + kv_name + ".weight"], ref_g[a + kv_name + ".weight"][r * 8:(r + 1) * 8], atol=3e-5)
+        assert torch.allclose(g[a + "out_proj.weight"], ref_g[a + "out_proj.weight"][:, r * 16:(r + 1) * 16], atol=3e-5)
+    # the logical (consolidated) view of the sharded parameters is the unsharded model
+    from cppmega_mlx_b200.parallel.sharded_state import consolidated_parameters
+    whole = consolidated_parameters(sharded(False))
+    want_sd = full.state_dict()
+    assert set(whole) == set(want_sd) and all(torch.equal(whole[n], want_sd[n]) for n in want_sd)
+    # cached decode: every rank keeps the keys / values of its own heads
+    m = sharded(False).eval()
+    pieces = [slice(0, 7)] + [slice(t, t + 1) for t in range(7, 12)]
+    with torch.no_grad():
+        s0, s1 = DecodeSession(full.eval()), DecodeSession(m)
+        want = torch.cat([s0.forward(ids[:, p]) for p in pieces], 1)
+        got = torch.cat([s1.forward(ids[:, p]) for p in pieces], 1)
+    assert torch.allclose(got, want, atol=3e-5), float((got - want).abs().max())
+    # a head count the group does not divide stays replicated
+    odd = HybridTinyLM(HybridTinyConfig(vocab_size=64, hidden_size=48, pattern="A", depth=1, num_attention_heads=3, max_seq_length=16,
+                                        mamba_head_dim=16, position_embedding=False))
+    assert TP.tensor_parallelize_mixers(odd, st.tp_group).get("attention", 0) == 0
+    with pytest.raises(ValueError, match="must divide"):
+        TP._shard_attention(odd.layers[0].block, st.tp_group)
+    return True
+
+
+@pytest.mark.parametrize("mode", ["gqa", "dsa"])
+def test_tensor_parallel_plain_attention_matches_single_rank(mode):
+    assert all(run_ranks(_tp_plain_attention_rank, 2, mode))
