@@ -208,3 +208,31 @@ def test_parity_manifest_cli_is_fail_closed_without_an_artifact(capsys, tmp_path
     out2 = tmp_path / "fwd.json"
     P.main(["forward", "--tiny", "--no-artifact", "--device", "cpu", "--output", str(out2)])
     assert json.loads(out2.read_text())["status"] in ("blocked", "refused")
+
+
+def test_cut_ce_receipt_and_route_gradient_probe(capsys, tmp_path):
+    import json
+
+    from cppmega_mlx_b200.cli import bench_cce, probe_route_grad
+    out_file = tmp_path / "cce.jsonl"
+    rc, out = _run_main(bench_cce, ["--batch-size", "2", "--seq-len", "48", "--vocab-size", "512", "--hidden", "32", "--row-chunk", "16",
+                                    "--iters", "2", "--warmup", "1", "--output", str(out_file)], capsys)
+    rows = [json.loads(l) for l in out]
+    assert rc == 0 and [r.get("form") for r in rows[:2]] == ["materialized", "cut"] and rows[2]["status"] == "ok"
+    assert rows[1]["loss_abs_diff_vs_materialized"] < 1e-5 and rows[1]["max_grad_abs_diff_vs_materialized"] < 1e-6
+    assert rows[2]["memory_ratio_cut_vs_materialized"] == pytest.approx(16 * 4 / (96 * 8))      # one chunk of fp32 logits against all rows twice
+    assert len(out_file.read_text().splitlines()) == 3
+    rc, out = _run_main(bench_cce, ["--seq-len", "0"], capsys)
+    assert rc == 2 and json.loads(out[-1])["status"] == "error"
+
+    rc, out = _run_main(probe_route_grad, ["--tiny", "--seq-len", "16", "--batch-size", "2", "--model-profile", "nam56r_56l"], capsys)
+    rep = json.loads(out[-1])
+    assert rc == 0 and rep["status"] == "ok" and [r["route"] for r in rep["routes"]] == ["reference", "kernels"]
+    ref, ker = rep["routes"]
+    assert ref["loss_finite"] and ref["grad_norm"] > 0 and not ref["nonfinite_gradients"] and ref["total_kernel_calls"] == 0
+    assert ker["loss_abs_diff_vs_reference"] < 1e-5 and ker["max_grad_rel_diff_vs_reference"]["value"] < 1e-4     # no GPU here: both routes are the restatements
+    assert set("".join(rep["pattern"])) >= set("AMER")
+    rc, out = _run_main(probe_route_grad, ["--routes", "metal"], capsys)
+    assert rc == 2 and "routes must be taken from" in json.loads(out[-1])["error"]
+    rc, out = _run_main(probe_route_grad, ["--model-profile", "nope"], capsys)
+    assert rc == 2 and "unknown model profile" in json.loads(out[-1])["error"]
