@@ -11,6 +11,9 @@ routing, the loss) runs on the slice as it is.  The mixers that look along the s
   travels back the same way in the backward pass.  Rank r is therefore one recurrent layer behind rank r−1 (a skew, not a stall: it
   works on layer i while rank r−1 works on layer i+1) until the next attention layer's gather lines the ranks up again.
 
+It composes with head- / expert-parallel mixers (``parallel/tp.py``): every tensor-parallel group then holds one slice of the
+sequence, and states and key rows travel between the ranks with the same tensor-parallel index.
+
 The model code is untouched: the two hand-offs are objects with the interface of the decode-time KV cache and recurrent-state
 holder (``inference/engine.py`` ``HybridKVCache``, ``models/hybrid_lm.py`` ``HybridDecodeState``), so a context-parallel forward is
 the model's own cached forward with the *previous ranks* in the place of the *previous tokens*.

@@ -677,3 +677,50 @@ def _tp_plain_attention_rank(rank, world, mode):
 @pytest.mark.parametrize("mode", ["gqa", "dsa"])
 def test_tensor_parallel_plain_attention_matches_single_rank(mode):
     assert all(run_ranks(_tp_plain_attention_rank, 2, mode))
+
+
+def _cp_tp_rank(rank, world):
+    """Context parallelism over the data-parallel axis combined with head- / expert-parallel mixers (2 × 2 ranks): each
+    tensor-parallel pair holds half of the sequence, the recurrent states travel between the ranks with the same tensor-parallel
+    index, and the logits are those of the single-process piecewise evaluation."""
+    from cppmega_mlx_b200.models.hybrid_lm import HybridDecodeState, HybridTinyConfig, HybridTinyLM
+    from cppmega_mlx_b200.parallel import cp as CP
+    from cppmega_mlx_b200.parallel import tp as TP
+    st = PS.init_parallel_state(tp=2)
+    cp_group = st.dp_group
+    assert torch.distributed.get_world_size(cp_group) == 2
+    cfg = HybridTinyConfig(vocab_size=64, hidden_size=32, pattern="MARE", depth=4, num_attention_heads=4, max_seq_length=16, mamba_head_dim=16,
+                           mamba_state_dim=8, mamba_chunk_size=4, mamba_groups=2, moe_num_experts=4, moe_top_k=2, moe_expert_hidden_size=16,
+                           moe_shared_expert_hidden_size=16, m2rnn_k_head_dim=4, m2rnn_v_head_dim=4, m2rnn_num_q_heads=1, m2rnn_num_k_heads=2,
+                           m2rnn_num_v_heads=4, m2rnn_num_f_heads=4, m2rnn_num_g_heads=4, mla_low_rank=True, mla_q_lora_rank=16,
+                           mla_kv_lora_rank=16, mla_qk_nope_head_dim=8, mla_qk_rope_head_dim=4, mla_v_head_dim=8, ffn_hidden_size=48,
+                           position_embedding=False, moe_aux_loss_coeff=0.0)
+    torch.manual_seed(0)
+    full = HybridTinyLM(cfg)
+    with torch.no_grad():
+        for p in full.parameters():
+            if p.dim() == 2 and float(p.abs().sum()) == 0:
+                p.normal_(std=0.05)
+    ids = torch.randint(0, 64, (2, 12))
+    kv, state, outs = _CatCache(), HybridDecodeState(), []
+    with torch.no_grad():
+        for r in range(2):
+            outs.append(full(ids[:, r * 6:(r + 1) * 6], kv_cache=kv, state=state))
+            kv.offset += 6
+    ref = torch.cat(outs, 1)
+    m = HybridTinyLM(cfg)
+    m.load_state_dict(full.state_dict())
+    assert sum(TP.tensor_parallelize_mixers(m, st.tp_group).values()) == 4
+    TP.tensor_parallelize_ffn(m, st.tp_group)
+    CP.enable_context_parallel(m, cp_group)
+    mine = CP.shard_sequence(ids, cp_group)
+    c = torch.distributed.get_rank(cp_group)
+    out = m(mine)
+    assert torch.allclose(out, ref[:, c * 6:(c + 1) * 6], atol=3e-5), float((out - ref[:, c * 6:(c + 1) * 6]).abs().max())
+    out.square().mean().backward()                       # the backward hand-offs pair up as well
+    assert all(torch.isfinite(p.grad).all() for p in m.parameters() if p.grad is not None)
+    return True
+
+
+def test_context_parallel_composes_with_tensor_parallel_mixers():
+    assert all(run_ranks(_cp_tp_rank, 4))
