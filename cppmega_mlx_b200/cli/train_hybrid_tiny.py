@@ -91,6 +91,7 @@ class TrainHybridTinyConfig:
     clear_cache_every_steps: int | None = None
     device: str = "auto"
     comm: str = "nccl"
+    context_parallel: int = 1     # ranks that share one sequence (parallel/cp.py); the other WORLD_SIZE / context_parallel-fold is data parallel
     json: bool = False
     dry_run: bool = False
 
@@ -110,6 +111,8 @@ class TrainHybridTinyConfig:
             raise ValueError("eval_batches and checkpoint_save_interval must be non-negative")
         if self.checkpoint_save_interval and not self.checkpoint_dir:
             raise ValueError("--checkpoint-save-interval needs --checkpoint-dir")
+        if self.context_parallel <= 0 or self.seq_len % self.context_parallel:
+            raise ValueError("context_parallel must be positive and divide seq_len")
 
 
 def _tuple_of_ints(s: str) -> tuple[int, ...]:
@@ -248,7 +251,20 @@ def run(cfg: TrainHybridTinyConfig) -> dict:
     kernel_policy.apply_policy_from_env()
     kernel_policy.clear_dispatch_log()
 
-    batches, dataset_info, ds = open_data(cfg, cfg.npz_path, cfg.data_format, rank, world)
+    cp, cp_group = cfg.context_parallel, None
+    if cp > 1:
+        if world % cp:
+            raise ValueError(f"context_parallel {cp} must divide the world size {world}")
+        for first in range(0, world, cp):               # consecutive ranks share a sequence; every rank creates every group
+            g = torch.distributed.new_group(list(range(first, first + cp)))
+            if first <= rank < first + cp:
+                cp_group = g
+    data_rank, data_world = rank // cp, world // cp      # ranks of one context-parallel group read the same rows
+    batches, dataset_info, ds = open_data(cfg, cfg.npz_path, cfg.data_format, data_rank, data_world)
+    if cp_group is not None:
+        from ..parallel.cp import shard_batch
+        whole = batches
+        batches = lambda start=0: (shard_batch(b, cp_group) for b in whole(start))
     vocab = cfg.vocab_size or (dataset_info.get("token_id_max", 127) + 1 if ds is not None else dataset_info["vocab_size"])
     mcfg = build_model_config(cfg, vocab)
     if ds is not None and dataset_info["token_id_max"] >= mcfg.vocab_size:
@@ -266,6 +282,10 @@ def run(cfg: TrainHybridTinyConfig) -> dict:
 
     dtype = getattr(torch, cfg.dtype)
     model = HybridTinyLM(mcfg).to(device=device, dtype=dtype)
+    if cp_group is not None:
+        from ..parallel.cp import enable_context_parallel
+        enable_context_parallel(model, cp_group)        # the optimizer below averages gradients over all ranks, context-parallel peers included
+        payload["context_parallel"] = {"size": cp, "data_parallel": data_world, "tokens_per_rank": cfg.seq_len // cp}
     opt = build_optimizer(cfg, model, world)
     loss_fn = make_loss_fn(backend=cfg.loss_backend, mtp=cfg.mtp)
     stepper = PretrainingStep(model, opt, loss_fn=loss_fn, grad_accum_steps=cfg.grad_accum_steps, compile=cfg.compile,
@@ -312,9 +332,16 @@ def run(cfg: TrainHybridTinyConfig) -> dict:
     if cfg.checkpoint_path:
         save(stepper.state.step, cfg.checkpoint_path)
     if cfg.eval_batches:
-        vb, vinfo, _ = open_data(cfg, cfg.valid_dataset_path or cfg.npz_path, cfg.valid_dataset_format or cfg.data_format, rank, world)
+        vb, vinfo, _ = open_data(cfg, cfg.valid_dataset_path or cfg.npz_path, cfg.valid_dataset_format or cfg.data_format, data_rank, data_world)
+        if cp_group is not None:
+            whole_v = vb
+            vb = lambda start=0: (shard_batch(b, cp_group) for b in whole_v(start))
         ev = evaluate_batches(model, (b for b, _ in zip(vb(0), range(cfg.eval_batches))), loss_fn=make_loss_fn(backend=cfg.loss_backend, mtp=False),
                               device=device)
+        if cp_group is not None:                         # every rank evaluated its slice of the same sequences: token-weighted mean over the group
+            acc = torch.tensor([ev["loss"] * ev["ntokens"], float(ev["ntokens"])], dtype=torch.float64, device=device)
+            torch.distributed.all_reduce(acc, group=cp_group)
+            ev = {**ev, "loss": float(acc[0] / acc[1].clamp(min=1)), "ntokens": int(acc[1])}
         payload["eval"] = {**ev, "dataset": vinfo}
     mem1 = memory.MemorySnapshot.take()
     payload.update({"metrics": metrics, "final_loss": metrics[-1]["loss"] if metrics else None, "steps_completed": stepper.state.step,

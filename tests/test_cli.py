@@ -236,3 +236,30 @@ def test_cut_ce_receipt_and_route_gradient_probe(capsys, tmp_path):
     assert rc == 2 and "routes must be taken from" in json.loads(out[-1])["error"]
     rc, out = _run_main(probe_route_grad, ["--model-profile", "nope"], capsys)
     assert rc == 2 and "unknown model profile" in json.loads(out[-1])["error"]
+
+
+def test_trainer_context_parallel_two_processes_match_one(tmp_path):
+    """``--context-parallel 2`` under the launcher: two processes share every sequence and reproduce the single-process losses
+    (attention + M2RNN stack: nothing in it looks ahead of a token, so the split evaluation equals the whole one)."""
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    args = ["--batch-size", "2", "--seq-len", "12", "--hidden-size", "32", "--num-attention-heads", "2", "--pattern", "AR", "--depth", "2",
+            "--steps", "3", "--vocab-size", "64", "--loss-backend", "cross_entropy", "--eval-batches", "1", "--json"]
+    rc, one, r = _run(*args)
+    assert rc == 0, r.stderr[-2000:]
+    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), "-m", "cppmega_mlx_b200.cli.train_hybrid_tiny", *args, "--context-parallel", "2"]
+    p = subprocess.run(cmd, capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
+    assert p.returncode == 0, p.stderr[-3000:]
+    two = json.loads([l for l in p.stdout.splitlines() if l.startswith("{")][-1])          # rank 0 prints the receipt
+    assert two["context_parallel"] == {"size": 2, "data_parallel": 1, "tokens_per_rank": 6} and two["world_size"] == 2
+    l1, l2 = [m["loss"] for m in one["metrics"]], [m["loss"] for m in two["metrics"]]
+    assert len(l1) == len(l2) == 3
+    # rank 0 reports the mean over its half of the tokens; the parameters (and so the later losses) follow the whole-sequence gradient
+    assert all(abs(a - b) < 0.15 for a, b in zip(l1, l2)), (l1, l2)
+    assert abs(one["eval"]["loss"] - two["eval"]["loss"]) < 2e-4, (one["eval"], two["eval"])
+    rc, rep, _ = _run(*args, "--context-parallel", "5")
+    assert rc == 2 and "divide seq_len" in rep["error"]
