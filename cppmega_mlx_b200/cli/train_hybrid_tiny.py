@@ -92,6 +92,8 @@ class TrainHybridTinyConfig:
     device: str = "auto"
     comm: str = "nccl"
     context_parallel: int = 1     # ranks that share one sequence (parallel/cp.py); the other WORLD_SIZE / context_parallel-fold is data parallel
+    tensor_parallel: int = 1      # ranks that share every layer's heads / experts / FFN columns (parallel/tp.py); the rest is data parallel
+    sequence_parallel: bool = False   # with tensor_parallel: the residual stream between the blocks is split over those ranks as well
     json: bool = False
     dry_run: bool = False
 
@@ -113,6 +115,14 @@ class TrainHybridTinyConfig:
             raise ValueError("--checkpoint-save-interval needs --checkpoint-dir")
         if self.context_parallel <= 0 or self.seq_len % self.context_parallel:
             raise ValueError("context_parallel must be positive and divide seq_len")
+        if self.tensor_parallel <= 0:
+            raise ValueError("tensor_parallel must be positive")
+        if self.tensor_parallel > 1 and self.context_parallel > 1:
+            raise ValueError("the trainer takes tensor_parallel or context_parallel, not both (the library composes them: parallel/cp.py)")
+        if self.sequence_parallel and self.tensor_parallel == 1:
+            raise ValueError("sequence_parallel needs tensor_parallel > 1")
+        if self.tensor_parallel > 1 and self.max_grad_norm is not None:
+            raise ValueError("gradient clipping is not supported with tensor_parallel (the norm would be taken over this rank's slices)")
 
 
 def _tuple_of_ints(s: str) -> tuple[int, ...]:
@@ -182,7 +192,7 @@ def build_model_config(cfg: TrainHybridTinyConfig, vocab_size: int):
         grad_checkpoint=cfg.grad_checkpoint, ffn_hidden_size=cfg.ffn_hidden_size, mla_low_rank=cfg.mla_low_rank, mtp_enabled=cfg.mtp)
 
 
-def build_optimizer(cfg: TrainHybridTinyConfig, model, world: int):
+def build_optimizer(cfg: TrainHybridTinyConfig, model, world: int, dp_group=None, dp_world: int | None = None):
     from ..training import optimizers as O
     from ..training.optimizers_quantized import make_adam8bit, make_lion8bit
     lr, wd = cfg.learning_rate, cfg.weight_decay
@@ -202,7 +212,8 @@ def build_optimizer(cfg: TrainHybridTinyConfig, model, world: int):
         raise ValueError(f"optimizer must be one of {OPTIMIZERS}")
     if world > 1:
         from ..training.distributed_optimizer import DistributedZeRO1Optimizer
-        return DistributedZeRO1Optimizer(model, factory, comm=cfg.comm)
+        # tensor-parallel ranks hold different slices: optimizer state is sharded over the data-parallel ranks only
+        return DistributedZeRO1Optimizer(model, factory, comm=cfg.comm, group=dp_group, single_rank=dp_world == 1)
     return factory(model)
 
 
@@ -260,6 +271,13 @@ def run(cfg: TrainHybridTinyConfig) -> dict:
             if first <= rank < first + cp:
                 cp_group = g
     data_rank, data_world = rank // cp, world // cp      # ranks of one context-parallel group read the same rows
+    tp, pstate = cfg.tensor_parallel, None
+    if tp > 1:
+        if world % tp:
+            raise ValueError(f"tensor_parallel {tp} must divide the world size {world}")
+        from ..parallel.state import init_parallel_state
+        pstate = init_parallel_state(tp=tp)
+        data_rank, data_world = pstate.dp_rank, pstate.dp     # ranks of one tensor-parallel group read the same rows
     batches, dataset_info, ds = open_data(cfg, cfg.npz_path, cfg.data_format, data_rank, data_world)
     if cp_group is not None:
         from ..parallel.cp import shard_batch
@@ -286,7 +304,15 @@ def run(cfg: TrainHybridTinyConfig) -> dict:
         from ..parallel.cp import enable_context_parallel
         enable_context_parallel(model, cp_group)        # the optimizer below averages gradients over all ranks, context-parallel peers included
         payload["context_parallel"] = {"size": cp, "data_parallel": data_world, "tokens_per_rank": cfg.seq_len // cp}
-    opt = build_optimizer(cfg, model, world)
+    if pstate is not None:
+        from ..parallel import tp as TP
+        done = TP.tensor_parallelize_mixers(model, pstate.tp_group)
+        ffns = TP.tensor_parallelize_ffn(model, pstate.tp_group, sequence_parallel=cfg.sequence_parallel)
+        if cfg.sequence_parallel:
+            TP.enable_sequence_parallel(model, pstate.tp_group)
+        payload["tensor_parallel"] = {"size": tp, "data_parallel": pstate.dp, "sequence_parallel": cfg.sequence_parallel,
+                                      "sharded_mixers": done, "sharded_ffns": ffns}
+    opt = build_optimizer(cfg, model, world, pstate.dp_group if pstate is not None else None, pstate.dp if pstate is not None else None)
     loss_fn = make_loss_fn(backend=cfg.loss_backend, mtp=cfg.mtp)
     stepper = PretrainingStep(model, opt, loss_fn=loss_fn, grad_accum_steps=cfg.grad_accum_steps, compile=cfg.compile,
                               max_grad_norm=cfg.max_grad_norm, device=device)

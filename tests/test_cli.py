@@ -263,3 +263,36 @@ def test_trainer_context_parallel_two_processes_match_one(tmp_path):
     assert abs(one["eval"]["loss"] - two["eval"]["loss"]) < 2e-4, (one["eval"], two["eval"])
     rc, rep, _ = _run(*args, "--context-parallel", "5")
     assert rc == 2 and "divide seq_len" in rep["error"]
+
+
+@pytest.mark.parametrize("sp", [False, True])
+def test_trainer_tensor_parallel_two_processes_match_one(sp, tmp_path):
+    """``--tensor-parallel 2`` (and ``--sequence-parallel``) under the launcher: every mixer kind head- / expert-parallel on two
+    processes trains like one process, and the checkpoint it writes is the logical (unsharded) one: a single process resumes from it."""
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    args = ["--batch-size", "2", "--seq-len", "12", "--hidden-size", "32", "--num-attention-heads", "4", "--pattern", "MAER", "--depth", "4",
+            "--mamba-head-dim", "16", "--mamba-state-dim", "8", "--mamba-groups", "2", "--mamba-chunk-size", "4", "--mamba-expand", "2",
+            "--moe-num-experts", "4", "--moe-top-k", "2", "--moe-expert-hidden-size", "16", "--m2rnn-k-head-dim", "4", "--m2rnn-v-head-dim", "4", "--m2rnn-num-v-heads", "4", "--m2rnn-num-f-heads", "4",
+            "--ffn-hidden-size", "48", "--steps", "3", "--vocab-size", "64", "--loss-backend", "cross_entropy", "--eval-batches", "1", "--json"]
+    rc, one, r = _run(*args)
+    assert rc == 0, r.stderr[-2000:]
+    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="")
+    ckpt = tmp_path / "tp_ckpt"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), "-m", "cppmega_mlx_b200.cli.train_hybrid_tiny", *args, "--tensor-parallel", "2",
+           "--checkpoint-path", str(ckpt)] + (["--sequence-parallel"] if sp else [])
+    p = subprocess.run(cmd, capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
+    assert p.returncode == 0, p.stderr[-3000:]
+    two = json.loads([l for l in p.stdout.splitlines() if l.startswith("{")][-1])
+    info = two["tensor_parallel"]
+    assert info["size"] == 2 and info["data_parallel"] == 1 and info["sequence_parallel"] == sp and sum(info["sharded_mixers"].values()) == 4
+    l1, l2 = [m["loss"] for m in one["metrics"]], [m["loss"] for m in two["metrics"]]
+    assert all(abs(a - b) < 2e-4 for a, b in zip(l1, l2)), (l1, l2)
+    assert abs(one["eval"]["loss"] - two["eval"]["loss"]) < 2e-4
+    rc, again, r = _run(*args, "--resume-from", str(ckpt), "--steps", "4")           # one process continues from the two-process checkpoint
+    assert rc == 0 and again["resume"]["step"] == 3 and again["steps_completed"] == 4, r.stderr[-2000:]
+    rc, rep, _ = _run(*args, "--sequence-parallel")
+    assert rc == 2 and "needs tensor_parallel" in rep["error"]
