@@ -94,6 +94,7 @@ class TrainHybridTinyConfig:
     context_parallel: int = 1     # ranks that share one sequence (parallel/cp.py); the other WORLD_SIZE / context_parallel-fold is data parallel
     tensor_parallel: int = 1      # ranks that share every layer's heads / experts / FFN columns (parallel/tp.py); the rest is data parallel
     sequence_parallel: bool = False   # with tensor_parallel: the residual stream between the blocks is split over those ranks as well
+    expert_parallel: int = 1      # 1, or WORLD_SIZE: the routed experts are spread over all ranks (parallel/ep.py), everything else is data parallel
     json: bool = False
     dry_run: bool = False
 
@@ -119,6 +120,8 @@ class TrainHybridTinyConfig:
             raise ValueError("tensor_parallel must be positive")
         if self.tensor_parallel > 1 and self.context_parallel > 1:
             raise ValueError("the trainer takes tensor_parallel or context_parallel, not both (the library composes them: parallel/cp.py)")
+        if self.expert_parallel <= 0 or (self.expert_parallel > 1 and (self.tensor_parallel > 1 or self.context_parallel > 1)):
+            raise ValueError("expert_parallel must be positive and is not combined with tensor_parallel / context_parallel here")
         if self.sequence_parallel and self.tensor_parallel == 1:
             raise ValueError("sequence_parallel needs tensor_parallel > 1")
         if self.tensor_parallel > 1 and self.max_grad_norm is not None:
@@ -210,6 +213,9 @@ def build_optimizer(cfg: TrainHybridTinyConfig, model, world: int, dp_group=None
         if o == "lion8bit":
             return make_lion8bit(params, learning_rate=lr, weight_decay=wd)
         raise ValueError(f"optimizer must be one of {OPTIMIZERS}")
+    if world > 1 and cfg.expert_parallel > 1:
+        from ..training.distributed_optimizer import ExpertParallelZeRO1Optimizer
+        return ExpertParallelZeRO1Optimizer(model, factory, ep_size=cfg.expert_parallel, comm=cfg.comm)
     if world > 1:
         from ..training.distributed_optimizer import DistributedZeRO1Optimizer
         # tensor-parallel ranks hold different slices: optimizer state is sharded over the data-parallel ranks only
@@ -299,7 +305,13 @@ def run(cfg: TrainHybridTinyConfig) -> dict:
         payload["memory_plan_applied"] = memory.apply_memory_limit_plan(plan)
 
     dtype = getattr(torch, cfg.dtype)
-    model = HybridTinyLM(mcfg).to(device=device, dtype=dtype)
+    ep_group = None
+    if cfg.expert_parallel > 1:
+        if cfg.expert_parallel != world:
+            raise ValueError(f"expert_parallel must equal the world size ({world}), got {cfg.expert_parallel}")
+        ep_group = torch.distributed.group.WORLD
+        payload["expert_parallel"] = {"size": world, "experts_per_rank": mcfg.moe_num_experts // world}
+    model = HybridTinyLM(mcfg, ep_group=ep_group).to(device=device, dtype=dtype)
     if cp_group is not None:
         from ..parallel.cp import enable_context_parallel
         enable_context_parallel(model, cp_group)        # the optimizer below averages gradients over all ranks, context-parallel peers included

@@ -296,3 +296,32 @@ def test_trainer_tensor_parallel_two_processes_match_one(sp, tmp_path):
     assert rc == 0 and again["resume"]["step"] == 3 and again["steps_completed"] == 4, r.stderr[-2000:]
     rc, rep, _ = _run(*args, "--sequence-parallel")
     assert rc == 2 and "needs tensor_parallel" in rep["error"]
+
+
+def test_trainer_expert_parallel_two_processes_and_logical_checkpoint(tmp_path):
+    """``--expert-parallel 2`` under the launcher: the routed experts are spread over both processes, the dense part is ZeRO-1 data
+    parallel, and the checkpoint holds all experts: one process resumes from it with the whole bank."""
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    args = ["--batch-size", "2", "--seq-len", "12", "--hidden-size", "32", "--num-attention-heads", "4", "--pattern", "AE", "--depth", "2",
+            "--moe-num-experts", "4", "--moe-top-k", "2", "--moe-expert-hidden-size", "16", "--vocab-size", "64", "--loss-backend", "cross_entropy",
+            "--learning-rate", "0.01", "--json"]
+    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="")
+    ckpt = tmp_path / "ep_ckpt"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), "-m", "cppmega_mlx_b200.cli.train_hybrid_tiny", *args, "--steps", "8", "--expert-parallel", "2",
+           "--checkpoint-path", str(ckpt)]
+    p = subprocess.run(cmd, capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
+    assert p.returncode == 0, p.stderr[-3000:]
+    two = json.loads([l for l in p.stdout.splitlines() if l.startswith("{")][-1])
+    assert two["expert_parallel"] == {"size": 2, "experts_per_rank": 2} and two["optimizer"]["class"]
+    losses = [m["loss"] for m in two["metrics"]]
+    import math
+    assert len(losses) == 8 and all(math.isfinite(l) and l < 6.0 for l in losses)          # synthetic tokens are random: the loss stays near ln(64)
+    rc, again, r = _run(*args, "--resume-from", str(ckpt), "--steps", "9")
+    assert rc == 0 and again["resume"]["step"] == 8 and again["steps_completed"] == 9, r.stderr[-2000:]
+    assert abs(again["metrics"][0]["loss"] - losses[-1]) < 1.0                      # continues from the trained weights, not from scratch
+    rc, rep, _ = _run(*args, "--expert-parallel", "2")
+    assert rc == 2 and "must equal the world size" in rep["error"]
