@@ -724,3 +724,37 @@ def _cp_tp_rank(rank, world):
 
 def test_context_parallel_composes_with_tensor_parallel_mixers():
     assert all(run_ranks(_cp_tp_rank, 4))
+
+
+def _profile_sp_rank(rank, world, name):
+    """The routing of a named production profile (pattern, sparse-attention ranks) at toy width: every mixer kind it contains is
+    head- / expert-parallel, the residual stream sequence parallel, and the logits are those of the single-process model."""
+    from cppmega_mlx_b200.models.hybrid_lm import HybridTinyLM
+    from cppmega_mlx_b200.parallel import tp as TP
+    from cppmega_mlx_b200.recipes.model_factory import get_model_profile
+    st = PS.init_parallel_state(tp=world)
+    cfg = get_model_profile(name).tiny_smoke_config(position_embedding=False, dsa_indexer_loss_coeff=0.0)
+    torch.manual_seed(0)
+    full = HybridTinyLM(cfg).eval()
+    with torch.no_grad():
+        for p in full.parameters():
+            if p.dim() == 2 and float(p.abs().sum()) == 0:
+                p.normal_(std=0.05)
+    ids = torch.randint(0, cfg.vocab_size, (2, 16))
+    with torch.no_grad():
+        ref = full(ids)
+    m = HybridTinyLM(cfg).eval()
+    m.load_state_dict(full.state_dict())
+    done = TP.tensor_parallelize_mixers(m, st.tp_group)
+    assert sum(done.values()) == cfg.depth, (done, cfg.pattern)              # nothing stayed replicated
+    TP.tensor_parallelize_ffn(m, st.tp_group, sequence_parallel=True)
+    TP.enable_sequence_parallel(m, st.tp_group)
+    with torch.no_grad():
+        out = m(ids)
+    assert torch.allclose(out, ref, atol=5e-5), (name, float((out - ref).abs().max()))
+    return True
+
+
+@pytest.mark.parametrize("name", ["local_gb10_quarter", "nam56r_56l"])
+def test_production_profile_routing_is_fully_tensor_and_sequence_parallel(name):
+    assert all(run_ranks(_profile_sp_rank, 2, name))
