@@ -156,6 +156,8 @@ def _rms_norm_last(x, eps: float = 1e-5):
 
 
 class Mamba3Block(nn.Module):
+    _context_parallel_capable = True     # forward accepts the parallel-scan handle of parallel/cp.py in the place of a cache
+
     def __init__(self, config: Mamba3Config):
         super().__init__()
         self.config = config
@@ -227,6 +229,9 @@ class Mamba3Block(nn.Module):
             raise ValueError(f"hidden_states must be shaped (B,S,D), got {tuple(hidden_states.shape)}")
         if h0 is not None and cache is not None:
             raise ValueError("pass either h0 or cache, not both")
+        if getattr(cache, "context_parallel", False):
+            # context parallelism (parallel/cp.py): the other ranks of the group hold the rest of the sequence
+            return cache.run(self, hidden_states), cache
         c = self.config
         b, s, _ = hidden_states.shape
         proj = self.in_proj(hidden_states)

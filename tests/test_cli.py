@@ -240,12 +240,14 @@ def test_cut_ce_receipt_and_route_gradient_probe(capsys, tmp_path):
 
 def test_trainer_context_parallel_two_processes_match_one(tmp_path):
     """``--context-parallel 2`` under the launcher: two processes share every sequence and reproduce the single-process losses
-    (attention + M2RNN stack: nothing in it looks ahead of a token, so the split evaluation equals the whole one)."""
+    (Mamba3 scans on both ranks at once with the boundary terms exchanged, M2RNN continues from the first rank's state, attention
+    gathers the keys: the split evaluation equals the whole one)."""
     import socket
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    args = ["--batch-size", "2", "--seq-len", "12", "--hidden-size", "32", "--num-attention-heads", "2", "--pattern", "AR", "--depth", "2",
+    args = ["--batch-size", "2", "--seq-len", "12", "--hidden-size", "32", "--num-attention-heads", "2", "--pattern", "MAR", "--depth", "3",
+            "--mamba-head-dim", "8", "--mamba-state-dim", "8", "--mamba-chunk-size", "4",
             "--steps", "3", "--vocab-size", "64", "--loss-backend", "cross_entropy", "--eval-batches", "1", "--json"]
     rc, one, r = _run(*args)
     assert rc == 0, r.stderr[-2000:]

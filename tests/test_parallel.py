@@ -519,10 +519,11 @@ class _CatCache:
         return self._grow((layer_idx, "l"), latent), self._grow((layer_idx, "i"), idx_k)
 
 
-def _cp_rank(rank, world):
+def _cp_rank(rank, world, parallel):
     """Context parallelism: the sequence split over the ranks (weights replicated) gives the logits, the loss and — after averaging
-    over the group — the parameter gradients of the single-process model evaluated piecewise with the pieces cut at the slice
-    boundaries (prefill, then continue from the cache; the graph runs through the cache and the recurrent states)."""
+    over the group — the parameter gradients of the single-process model.  With the Mamba3 layers scanning on all ranks at once
+    (``parallel``) that is the plain forward over the whole sequence; with the state hand-off form it is the piecewise evaluation
+    cut at the slice boundaries (prefill, then continue from the cache; the graph runs through the cache and the states)."""
     from cppmega_mlx_b200.models.hybrid_lm import HybridDecodeState, HybridTinyConfig, HybridTinyLM
     from cppmega_mlx_b200.parallel import cp as CP
     st = PS.init_parallel_state(tp=1)
@@ -545,12 +546,16 @@ def _cp_rank(rank, world):
         inp, tgt = ids[:, :-1], ids[:, 1:]
         ce = torch.nn.functional.cross_entropy
         # single process, piecewise with autograd through cache and states
-        kv, state, outs = _CatCache(), HybridDecodeState(), []
         n = S // world
-        for r in range(world):
-            outs.append(model(inp[:, r * n:(r + 1) * n], kv_cache=kv, state=state))
-            kv.offset += n
-        ref = torch.cat(outs, 1)
+        model.cp_parallel_mamba = parallel
+        if parallel:
+            ref = model(inp)
+        else:
+            kv, state, outs = _CatCache(), HybridDecodeState(), []
+            for r in range(world):
+                outs.append(model(inp[:, r * n:(r + 1) * n], kv_cache=kv, state=state))
+                kv.offset += n
+            ref = torch.cat(outs, 1)
         ref_loss = ce(ref.reshape(-1, 64), tgt.reshape(-1))
         ref_loss.backward()
         ref_g = {k: p.grad.clone() for k, p in model.named_parameters() if p.grad is not None}
@@ -573,7 +578,7 @@ def _cp_rank(rank, world):
     # the switch on the model: loss functions and the training step then work on the rank's part of the batch as they are
     from cppmega_mlx_b200.data.batch import LMTokenBatch
     from cppmega_mlx_b200.training.loss import make_loss_fn
-    CP.enable_context_parallel(model, group)
+    CP.enable_context_parallel(model, group, parallel_mamba=parallel)
     assert torch.allclose(model(mine), logits.detach(), atol=1e-6)
     part = CP.shard_batch(LMTokenBatch(ids), group)
     assert torch.equal(part.inputs, mine) and torch.equal(part.targets, CP.shard_sequence(tgt, group))
@@ -597,9 +602,9 @@ def _cp_rank(rank, world):
     return True
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_context_parallel_matches_piecewise_single_rank(world):
-    assert all(run_ranks(_cp_rank, world))
+@pytest.mark.parametrize("world,parallel", [(2, False), (3, False), (2, True), (3, True), (4, True)])
+def test_context_parallel_matches_single_rank(world, parallel):
+    assert all(run_ranks(_cp_rank, world, parallel))
 
 
 def _tp_plain_attention_rank(rank, world, mode):
