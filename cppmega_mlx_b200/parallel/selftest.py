@@ -402,14 +402,115 @@ def case_epdrop(rank, world, dev):
                           "rel_err_vs_nccl[y,dx,dw_down]": errs}))
 
 
+def _mixer_stack(dev, pattern: str, max_seq: int):
+    from cppmega_mlx_b200.models.hybrid_lm import HybridTinyConfig, HybridTinyLM
+    torch.manual_seed(0)
+    cfg = HybridTinyConfig(vocab_size=512, hidden_size=256, pattern=pattern, depth=len(pattern), num_attention_heads=4, max_seq_length=max_seq,
+                           mamba_head_dim=64, mamba_state_dim=64, mamba_chunk_size=64, mamba_groups=2, mla_low_rank=True,
+                           mla_q_lora_rank=128, mla_kv_lora_rank=128, mla_qk_nope_head_dim=64, mla_qk_rope_head_dim=32,
+                           mla_v_head_dim=64, m2rnn_k_head_dim=64, m2rnn_v_head_dim=16, m2rnn_num_v_heads=4, m2rnn_num_f_heads=4,
+                           m2rnn_num_g_heads=4, ffn_hidden_size=512, position_embedding=False)
+    model = HybridTinyLM(cfg)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() == 2 and float(p.abs().sum()) == 0:
+                p.normal_(std=0.02)                      # zero-initialised output projections would hide the mixers
+    return model.to(dev, torch.bfloat16)
+
+
+def _rel(a, b) -> float:
+    a, b = a.detach().float(), b.detach().float()
+    return float((a - b).norm() / (b.norm() + 1e-12))
+
+
+def case_cp(rank, world, dev):
+    """Context parallelism over all ranks (Mamba3 scanning on all ranks at once, M2RNN handing its state on, latent keys gathered)
+    against the same model run over the whole sequence on one GPU: logits, loss and group-averaged parameter gradients."""
+    from cppmega_mlx_b200.parallel import cp as CP
+    n = 256
+    S = n * world
+    model = _mixer_stack(dev, "MAR", S)
+    gen = torch.Generator().manual_seed(7)
+    ids = torch.randint(0, 512, (2, S + 1), generator=gen).to(dev)
+    inp, tgt = ids[:, :-1], ids[:, 1:]
+    ce = torch.nn.functional.cross_entropy
+    ref = model(inp)
+    ref_loss = ce(ref.float().reshape(-1, 512), tgt.reshape(-1))
+    ref_loss.backward()
+    ref_g = {k: p.grad.float().clone() for k, p in model.named_parameters() if p.grad is not None}
+    model.zero_grad()
+    group = dist.group.WORLD
+    CP.enable_context_parallel(model, group)
+    mine = CP.shard_sequence(inp, group)
+    out = model(mine)
+    loss = ce(out.float().reshape(-1, 512), CP.shard_sequence(tgt, group).reshape(-1))
+    loss.backward()
+    CP.allreduce_context_parallel_grads(model, group)
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+    rel_logits = torch.tensor([_rel(out, ref.detach()[:, rank * n:(rank + 1) * n])], device=dev)
+    dist.all_reduce(rel_logits, op=dist.ReduceOp.MAX)
+    total = loss.detach().clone()
+    dist.all_reduce(total)
+    worst, name = 0.0, None
+    for k, want in ref_g.items():
+        g = dict(model.named_parameters())[k].grad
+        if g is None or float(want.norm()) < 1e-6:
+            continue
+        e = _rel(g, want)
+        if e > worst:
+            worst, name = e, k
+    if rank == 0:
+        print(json.dumps({"case": "cp", "world": world, "tokens_per_rank": n, "rel_err_logits": float(rel_logits),
+                          "loss_whole": float(ref_loss), "loss_mean_over_ranks": float(total) / world,
+                          "max_rel_err_grad": worst, "worst_parameter": name}))
+
+
+def case_tpdecode(rank, world, dev):
+    """Cached decode on the head-parallel stack (every rank keeps its share of each cache): prefill and one-token steps against the
+    unsharded model's own session."""
+    from cppmega_mlx_b200.inference import DecodeSession
+    from cppmega_mlx_b200.parallel import tp as TP
+    from cppmega_mlx_b200.parallel.state import init_parallel_state
+    st = init_parallel_state(tp=world)
+    full = _mixer_stack(dev, "MAR", 256).eval()
+    shard = _mixer_stack(dev, "MAR", 256).eval()
+    shard.load_state_dict(full.state_dict())
+    done = TP.tensor_parallelize_mixers(shard, st.tp_group)
+    TP.tensor_parallelize_ffn(shard, st.tp_group)
+    gen = torch.Generator().manual_seed(11)
+    ids = torch.randint(0, 512, (2, 72), generator=gen).to(dev)
+    pieces = [slice(0, 64)] + [slice(t, t + 1) for t in range(64, 72)]
+    with torch.no_grad():
+        s0, s1 = DecodeSession(full), DecodeSession(shard)
+        want = torch.cat([s0.forward(ids[:, p]) for p in pieces], 1)
+        got = torch.cat([s1.forward(ids[:, p]) for p in pieces], 1)
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+    err = torch.tensor([_rel(got[:, :64], want[:, :64]), _rel(got[:, 64:], want[:, 64:])], device=dev)
+    dist.all_reduce(err, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(json.dumps({"case": "tpdecode", "world": world, "sharded_mixers": done, "rel_err_prefill": float(err[0]),
+                          "rel_err_decode_steps": float(err[1]), "finite": bool(torch.isfinite(got).all())}))
+
+
 def main():
     case = sys.argv[1] if len(sys.argv) > 1 else "zero1"
     rank, world, dev = _setup()
+    cases = {"zero1": case_zero1, "zero1det": case_zero1det, "zero1bw": case_zero1bw, "allreduce": case_allreduce, "tp": case_tp, "tpar": case_tpar,
+             "ep": case_ep, "epdrop": case_epdrop, "cp": case_cp, "tpdecode": case_tpdecode}
     try:
-        {"zero1": case_zero1, "zero1det": case_zero1det, "zero1bw": case_zero1bw, "allreduce": case_allreduce, "tp": case_tp, "tpar": case_tpar, "ep": case_ep, "epdrop": case_epdrop}[case](rank, world, dev)
-    finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        cases[case](rank, world, dev)
+    except BaseException:
+        # the other ranks may be inside a collective that this rank will never join: report and leave without entering another
+        # one (a barrier here would wait for them forever and hide the traceback); the launcher ends the remaining ranks
+        import traceback
+        traceback.print_exc()
+        sys.stderr.flush()
+        sys.stdout.flush()
+        os._exit(1)
+    dist.barrier()
+    dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -99,3 +99,12 @@ def test_fused_ep_overflow_is_dropped_not_written_two_gpus():
     out = _selftest("epdrop")
     assert out["dropped_total"] > 0, out
     assert all(e < 5e-2 for e in out["rel_err_vs_nccl[y,dx,dw_down]"]), out
+
+
+def test_head_parallel_cached_decode_matches_unsharded_session_two_gpus():
+    """Prefill + one-token steps on the head-parallel stack (Mamba3, MLA, M2RNN; every rank keeps its share of the caches) against the
+    unsharded model's own decode session, bf16 with the kernels on."""
+    out = _selftest("tpdecode")
+    assert out["finite"] and out["sharded_mixers"]["mamba3"] == 1 and out["sharded_mixers"]["mla"] == 1 and out["sharded_mixers"]["m2rnn"] == 1, out
+    assert out["rel_err_prefill"] < 4e-2 and out["rel_err_decode_steps"] < 4e-2, out
+
