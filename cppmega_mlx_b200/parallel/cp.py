@@ -12,10 +12,10 @@ routing, the loss) runs on the slice as it is.  The mixers that look along the s
   their slice from a zero state, all-gather (final state, total decay) pairs, fold the pairs of the lower ranks into the state
   their slice really starts from, and scan again from it.  The result is the single-device forward exactly.
 * **M2RNN** (not linear: tanh), and Mamba3 layers that are head-parallel or asked to (``parallel_mamba=False``), continue from the
-  state the previous rank ended in: conv window, recurrent state and (Mamba3) accumulated
-  phase and pending trapezoid term travel rank → rank as one point-to-point message per layer, and the gradient of that state
-  travels back the same way in the backward pass.  Rank r is therefore one recurrent layer behind rank r−1 (a skew, not a stall: it
-  works on layer i while rank r−1 works on layer i+1) until the next attention layer's gather lines the ranks up again.
+  state the previous rank ended in: conv window, recurrent state and (Mamba3) accumulated phase and pending trapezoid term travel
+  rank → rank as one point-to-point message per layer, and the gradient of that state travels back the same way in the backward
+  pass.  Rank r is therefore one such layer behind rank r−1 (a skew, not a stall: it works on layer i while rank r−1 works on
+  layer i+1) until the next gather lines the ranks up again.
 
 It composes with head- / expert-parallel mixers (``parallel/tp.py``): every tensor-parallel group then holds one slice of the
 sequence, and states and key rows travel between the ranks with the same tensor-parallel index.
@@ -28,8 +28,9 @@ The reference has no context parallelism (its checkpoint loader refuses ``contex
 ``cppmega_mlx/training/checkpoint.py:52-98``).  With the hand-off form of Mamba3 the result equals the model's own piecewise
 evaluation with the pieces cut at the slice boundaries (prefill, then continue from the cache): the trapezoid rule, which looks one
 token ahead, then completes the last token of a slice inside the state it hands on, exactly as cached decoding does.  Activation
-checkpointing is not applied under context parallelism (a recomputed layer would repeat its messages).  Gradients: every rank's loss is
-the mean over its own tokens; ``allreduce_context_parallel_grads`` averages the parameter gradients over the group, which gives the
+checkpointing is not applied under context parallelism (a recomputed layer would repeat its messages).  Verified on CPU ranks
+(gloo); a two-GPU NCCL run has not completed yet, so treat the GPU path as unverified.  Gradients: every rank's loss is the mean
+over its own tokens; ``allreduce_context_parallel_grads`` averages the parameter gradients over the group, which gives the
 gradient of the mean over the whole sequence.
 """
 from __future__ import annotations
@@ -40,7 +41,8 @@ import torch.distributed as dist
 from .tp import gather_sequence
 
 __all__ = ["shard_sequence", "shard_batch", "enable_context_parallel", "disable_context_parallel", "ContextParallelKV",
-           "ContextParallelState", "mamba3_context_parallel_forward", "context_parallel_hidden_states", "context_parallel_forward", "allreduce_context_parallel_grads"]
+           "ContextParallelState", "mamba3_context_parallel_forward", "context_parallel_hidden_states", "context_parallel_forward",
+           "allreduce_context_parallel_grads"]
 
 
 def shard_sequence(x: torch.Tensor, group, dim: int = 1) -> torch.Tensor:
