@@ -96,13 +96,12 @@ class _RecvState(torch.autograd.Function):
     @staticmethod
     def forward(ctx, anchor, numel, src, group):
         ctx.src, ctx.group = src, group
-        buf = torch.empty(numel, dtype=torch.float32, device=anchor.device)
-        dist.recv(buf, src=_peer(group, src), group=group)
-        return buf
+        like = torch.empty(numel, dtype=torch.float32, device=anchor.device)
+        return _exchange(None, None, like, src, group)      # batched point-to-point form: NCCL orders unbatched calls like collectives
 
     @staticmethod
     def backward(ctx, g):
-        dist.send(g.contiguous().float(), dst=_peer(ctx.group, ctx.src), group=ctx.group)
+        _exchange(g.contiguous().float(), ctx.src, None, None, ctx.group)
         return None, None, None, None
 
 
@@ -113,14 +112,13 @@ class _SendState(torch.autograd.Function):
     @staticmethod
     def forward(ctx, flat, dst, group):
         ctx.dst, ctx.group, ctx.n = dst, group, flat.numel()
-        dist.send(flat.contiguous(), dst=_peer(group, dst), group=group)
+        _exchange(flat, dst, None, None, group)
         return flat.new_zeros(())
 
     @staticmethod
     def backward(ctx, _):
-        buf = torch.empty(ctx.n, dtype=torch.float32, device=_.device)
-        dist.recv(buf, src=_peer(ctx.group, ctx.dst), group=ctx.group)
-        return buf, None, None
+        like = torch.empty(ctx.n, dtype=torch.float32, device=_.device)
+        return _exchange(None, None, like, ctx.dst, ctx.group), None, None
 
 
 def _exchange(send: torch.Tensor | None, dst: int | None, recv_like: torch.Tensor | None, src: int | None, group):
