@@ -478,6 +478,14 @@ def _shard_moe(full, group):
     return loc
 
 
+def _m2rnn_shardable(c, tp: int) -> bool:
+    """Whether ``_shard_m2rnn`` accepts this configuration (its refusals, as a predicate)."""
+    H = c.num_heads
+    if H % tp or any(getattr(c, k) != H for k in ("num_v_heads", "num_f_heads", "num_g_heads")):
+        return False
+    return not (c.num_q_heads % tp == 0 and c.num_k_heads % tp)
+
+
 def _shard_m2rnn(full, group):
     """Head-parallel copy of an ``M2RNNMixer``.  Head counts divisible by the group size are split; the others (a single shared
     q / k head, one state-weight matrix) stay whole on every rank and are listed in ``tp_replicated``."""
@@ -760,8 +768,8 @@ def tensor_parallelize_mixers(model: nn.Module, group, *, kinds=("mla", "attenti
     expert-parallel forms (in place); returns how many of each were replaced (kinds that replaced nothing and are not among the
     four original ones are left out of the result).  Inputs and outputs of every mixer stay replicated over the group (the partial
     output products are all-reduced), so it composes with ``tensor_parallelize_ffn``.  A Mamba3 block whose head / group counts
-    the group size does not divide, and a plain attention block whose head counts it does not divide or that has biases, stay
-    replicated."""
+    the group size does not divide, a plain attention block whose head counts it does not divide or that has biases, and an M2RNN
+    mixer whose value / forget / gate heads are grouped stay replicated (every rank then computes them in full)."""
     from ..nn.m2rnn import M2RNNMixer
     from ..nn.mla import MLAAttention
     from ..nn.moe import MoE
@@ -785,8 +793,9 @@ def tensor_parallelize_mixers(model: nn.Module, group, *, kinds=("mla", "attenti
                 setattr(parent, name, _shard_moe(child, group))
                 done["moe"] += 1
             elif isinstance(child, M2RNNMixer) and "m2rnn" in kinds and child.tp_group is None:
-                setattr(parent, name, _shard_m2rnn(child, group))
-                done["m2rnn"] += 1
+                if _m2rnn_shardable(child.config, tp):          # grouped v / f / g heads would straddle ranks: such a mixer stays replicated
+                    setattr(parent, name, _shard_m2rnn(child, group))
+                    done["m2rnn"] += 1
             elif isinstance(child, Mamba3Block) and "mamba3" in kinds:
                 c, tp = child.config, _world(group)
                 if c.effective_mimo_rank == 1 and c.nheads % tp == 0 and c.ngroups % tp == 0 and c.ngroups <= c.nheads // tp:

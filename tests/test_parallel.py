@@ -676,6 +676,18 @@ def _tp_plain_attention_rank(rank, world, mode):
     assert TP.tensor_parallelize_mixers(odd, st.tp_group).get("attention", 0) == 0
     with pytest.raises(ValueError, match="must divide"):
         TP._shard_attention(odd.layers[0].block, st.tp_group)
+    # an M2RNN mixer with grouped value heads stays replicated too, and still gives the single-process result
+    grouped = HybridTinyConfig(vocab_size=64, hidden_size=32, pattern="R", depth=1, num_attention_heads=4, max_seq_length=16, m2rnn_k_head_dim=4,
+                               m2rnn_v_head_dim=4, m2rnn_num_v_heads=2, m2rnn_num_f_heads=2, m2rnn_num_g_heads=4, position_embedding=False)
+    torch.manual_seed(1)
+    g0 = HybridTinyLM(grouped).eval()
+    g1 = HybridTinyLM(grouped).eval()
+    g1.load_state_dict(g0.state_dict())
+    assert TP.tensor_parallelize_mixers(g1, st.tp_group)["m2rnn"] == 0
+    with torch.no_grad():
+        assert torch.allclose(g1(ids), g0(ids), atol=1e-6)
+    with pytest.raises(ValueError, match="needs num_v_heads == num_heads"):
+        TP._shard_m2rnn(g0.layers[0].block, st.tp_group)
     return True
 
 
