@@ -296,6 +296,10 @@ class MLAAttention(nn.Module):
                 loss = loss + (mean / torch.distributed.get_world_size(self.tp_group) - loss.detach())
             self.aux_loss = loss
         fresh = kv_cache is None or (offset == 0 and sk == s)     # nothing cached before these tokens (training, or a prefill from scratch)
+        if fresh and getattr(kv_cache, "differentiable", False):
+            # a cache that is part of the autograd graph (context parallelism: its fetch is a gather over the ranks, whose backward is
+            # a collective every rank must reach): take this rank's rows as fetched, so that the fetch stays on the backward path
+            c_kv, k_pe = latent[..., :c.kv_lora_rank].contiguous(), latent[..., c.kv_lora_rank:].contiguous()
         if fresh and add_mask is None and x.is_cuda and x.dtype == torch.bfloat16 and ops.kernels_enabled():
             # Training / prefill on the GPU: per-head K,V (192/128 wide) under the top-k bitmask.
             from ..ops import attention as A

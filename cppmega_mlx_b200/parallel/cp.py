@@ -29,7 +29,8 @@ The reference has no context parallelism (its checkpoint loader refuses ``contex
 evaluation with the pieces cut at the slice boundaries (prefill, then continue from the cache): the trapezoid rule, which looks one
 token ahead, then completes the last token of a slice inside the state it hands on, exactly as cached decoding does.  Activation
 checkpointing is not applied under context parallelism (a recomputed layer would repeat its messages).  Verified on CPU ranks
-(gloo); a two-GPU NCCL run has not completed yet, so treat the GPU path as unverified.  Gradients: every rank's loss is the mean
+(gloo); not yet on GPUs.  Rule for every exchange in this file: what a rank receives or gathers must be used in its graph on every
+rank (if need be through a zero-weight term), because the backward of an exchange is another exchange that all its ranks must reach.  Gradients: every rank's loss is the mean
 over its own tokens; ``allreduce_context_parallel_grads`` averages the parameter gradients over the group, which gives the
 gradient of the mean over the whole sequence.
 """
@@ -281,6 +282,7 @@ class ContextParallelKV:
     layer hands in the rows of its own tokens and gets back the rows of tokens ``[0, end of its slice)``."""
 
     static = False
+    differentiable = True     # the fetch is a gather whose backward is a collective: a layer must use what it fetched on every rank
 
     def __init__(self, local_tokens: int, group):
         self.group = group
